@@ -1,0 +1,260 @@
+// Row-wise glue kernels: embedding gather, zero-centred RMSNorm with residual add, the MoE
+// routing / ordering / gather / combine steps around the grouped GEMMs.
+//
+// Reference counterparts: engine/fast/kernels.py:506-522 (add + RMSNorm), engine/fast/fused.py:553-579
+// and engine/fast/prefill_kernels.py:194-230 (softmax/top-k, per-expert counts, expert order),
+// engine/fast/moe_prefill.py:92-154 (device-side tile table), engine/fast/prefill_kernels.py:253-272
+// (top-k weighted combine). Everything stays on the device: no host synchronisation between the
+// router and the expert GEMMs.
+#include "common.cuh"
+
+namespace b200 {
+
+// ------------------------------------------------------------------ embedding
+__global__ void embed_kernel(const int64_t* tokens, const bf16* table, bf16* out, int H, int vocab) {
+  const int t = blockIdx.x;
+  int64_t tok = tokens[t];
+  if (tok < 0 || tok >= vocab) tok = 0;
+  const uint4* src = reinterpret_cast<const uint4*>(table + tok * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// ------------------------------------------------------------------ (add +) RMSNorm
+// res' = bf16(res + x) (or x when res == nullptr); y = bf16(res' * rsqrt(mean(res'^2)+eps) * (1 + w)).
+// One CTA per row, 8 elements per thread per step. `res_out` may alias `res` or `x`.
+template <bool ZERO_CENTRED>
+__global__ void add_rmsnorm_kernel(const bf16* x, const bf16* res, const bf16* w, bf16* res_out, bf16* y, int H,
+                                   float eps) {
+  const size_t row = static_cast<size_t>(blockIdx.x) * H;
+  extern __shared__ float vals[];  // H floats
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 xv = *reinterpret_cast<const uint4*>(x + row + i);
+    const bf16* xe = reinterpret_cast<const bf16*>(&xv);
+    uint4 rv;
+    const bf16* re = reinterpret_cast<const bf16*>(&rv);
+    if (res) rv = *reinterpret_cast<const uint4*>(res + row + i);
+    uint4 ov;
+    bf16* oe = reinterpret_cast<bf16*>(&ov);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      bf16 s = res ? __float2bfloat16(__bfloat162float(xe[j]) + __bfloat162float(re[j])) : xe[j];
+      oe[j] = s;
+      const float f = __bfloat162float(s);
+      vals[i + j] = f;
+      ss += f * f;
+    }
+    if (res_out) *reinterpret_cast<uint4*>(res_out + row + i) = ov;
+  }
+  __shared__ float part[32];
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < static_cast<int>(blockDim.x >> 5); ++i) tot += part[i];  // fixed order
+  const float inv = rsqrtf(tot / H + eps);
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 wv = *reinterpret_cast<const uint4*>(w + i);
+    const bf16* we = reinterpret_cast<const bf16*>(&wv);
+    uint4 ov;
+    bf16* oe = reinterpret_cast<bf16*>(&ov);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float g = ZERO_CENTRED ? 1.0f + __bfloat162float(we[j]) : __bfloat162float(we[j]);
+      oe[j] = __float2bfloat16(vals[i + j] * inv * g);
+    }
+    *reinterpret_cast<uint4*>(y + row + i) = ov;
+  }
+}
+
+// ------------------------------------------------------------------ MoE routing
+// One warp per row: fp32 softmax over E router logits, iterative top-k with ties to the lower
+// expert id, renormalise, round weights to bf16; pair k (the last) is the shared expert with
+// weight sigmoid(logit[E]) when `shared` is set. Also counts rows per expert.
+constexpr int MAX_PER_LANE = 16;  // E <= 512
+
+__global__ void route_kernel(const float* logits, int ldl, int T, int E, int top_k, int shared, float* wts, int* idx,
+                             int* counts) {
+  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp_global >= T) return;
+  const float* row = logits + static_cast<size_t>(warp_global) * ldl;
+  float v[MAX_PER_LANE];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < MAX_PER_LANE; ++i) {
+    const int e = i * 32 + lane;
+    v[i] = e < E ? row[e] : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAX_PER_LANE; ++i) {
+    v[i] = (i * 32 + lane) < E ? expf(v[i] - mx) : -1.0f;
+    sum += v[i] > 0.f ? v[i] : 0.f;
+  }
+  sum = warp_sum(sum);
+  const int P = top_k + (shared ? 1 : 0);
+  float sel_w = 0.f;  // lane j keeps the j-th selected probability
+  int sel_e = 0;
+  float tot = 0.f;
+  for (int k = 0; k < top_k; ++k) {
+    float bm = -1.0f;
+    int be = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+      const int e = i * 32 + lane;
+      if (v[i] > bm) { bm = v[i]; be = e; }  // ascending e within a lane: first maximum kept
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, bm, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (om > bm || (om == bm && oe < be)) { bm = om; be = oe; }
+    }
+    if ((be & 31) == lane) v[be >> 5] = -1.0f;  // remove the winner
+    const float pr = bm / sum;
+    tot += pr;
+    if (lane == k) { sel_w = pr; sel_e = be; }
+  }
+  if (lane < top_k) {
+    const float wv = __bfloat162float(__float2bfloat16(sel_w / tot));
+    wts[static_cast<size_t>(warp_global) * P + lane] = wv;
+    idx[static_cast<size_t>(warp_global) * P + lane] = sel_e;
+    atomicAdd(&counts[sel_e], 1);
+  }
+  if (shared && lane == 0) {
+    const float sg = sigmoid_f(row[E]);
+    wts[static_cast<size_t>(warp_global) * P + top_k] = __bfloat162float(__float2bfloat16(sg));
+    idx[static_cast<size_t>(warp_global) * P + top_k] = E;
+    atomicAdd(&counts[E], 1);
+  }
+}
+
+// One CTA: exclusive offsets per expert, the token-tile table (expert, row0, nrows) and its length;
+// clears the scatter cursors. Experts are laid out in id order, rows of one expert contiguous.
+__global__ void moe_plan_kernel(const int* counts, int Et, int bt, int* offsets, int* cursors, int4* tiles,
+                                int* n_tiles, int max_tiles) {
+  __shared__ int s_off[1025];
+  __shared__ int s_tile[1025];
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    int acc = 0, tacc = 0;
+    for (int e = 0; e < Et; ++e) {
+      s_off[e] = acc; s_tile[e] = tacc;
+      acc += counts[e];
+      tacc += (counts[e] + bt - 1) / bt;
+    }
+    s_off[Et] = acc; s_tile[Et] = tacc;
+    *n_tiles = tacc < max_tiles ? tacc : max_tiles;
+  }
+  __syncthreads();
+  for (int e = tid; e <= Et; e += blockDim.x) {
+    offsets[e] = s_off[e];
+    if (e < Et) {
+      cursors[e] = 0;
+      const int c = counts[e];
+      for (int i = 0, t = s_tile[e]; i * bt < c && t < max_tiles; ++i, ++t)
+        tiles[t] = make_int4(e, s_off[e] + i * bt, min(bt, c - i * bt), 0);
+    }
+  }
+}
+
+// Each (row, pair) takes the next free position of its expert's range. The order inside an expert
+// does not influence any output value: every sorted row is computed on its own.
+__global__ void moe_scatter_kernel(const int* idx, int n_pairs, int Et, const int* offsets, int* cursors, int* perm,
+                                   int* inv, int* err) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_pairs) return;
+  const int e = idx[i];
+  if (e < 0 || e >= Et) { atomicCAS(err, 0, ERR_BAD_INDEX); return; }
+  const int pos = offsets[e] + atomicAdd(&cursors[e], 1);
+  perm[pos] = i;
+  inv[i] = pos;
+}
+
+// x_sorted[pos] = x[perm[pos] / P]
+__global__ void moe_gather_kernel(const bf16* x, const int* perm, int P, int H, bf16* xs) {
+  const int pos = blockIdx.x;
+  const int t = perm[pos] / P;
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H);
+  uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(pos) * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// out[t] = bf16( sum_j w[t,j] * pair_out[inv[t,j]] ) in pair order, fp32 accumulation, rounded once.
+__global__ void moe_combine_kernel(const bf16* pair_out, const float* wts, const int* inv, int P, int H, bf16* out) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < P; ++j) {
+      const float wv = wts[static_cast<size_t>(t) * P + j];
+      const int pos = inv[static_cast<size_t>(t) * P + j];
+      uint4 pv = *reinterpret_cast<const uint4*>(pair_out + static_cast<size_t>(pos) * H + i);
+      const bf16* pe = reinterpret_cast<const bf16*>(&pv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += wv * __bfloat162float(pe[k]);
+    }
+    uint4 ov;
+    bf16* oe = reinterpret_cast<bf16*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) oe[k] = __float2bfloat16(acc[k]);
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + i) = ov;
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+#define CHECK_LAUNCH() return cudaGetLastError() == cudaSuccess ? 0 : -4
+
+extern "C" int b200_embed(const int64_t* tokens, const void* table, void* out, int T, int H, int vocab, cudaStream_t st) {
+  if (T <= 0) return 0;
+  embed_kernel<<<T, 128, 0, st>>>(tokens, static_cast<const bf16*>(table), static_cast<bf16*>(out), H, vocab);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_add_rmsnorm(const void* x, const void* res, const void* w, void* res_out, void* y, int T, int H,
+                                float eps, int zero_centred, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8) return -7;
+  const int threads = H >= 2048 ? 256 : 128;
+  auto k = zero_centred ? add_rmsnorm_kernel<true> : add_rmsnorm_kernel<false>;
+  k<<<T, threads, H * sizeof(float), st>>>(static_cast<const bf16*>(x), static_cast<const bf16*>(res),
+                                            static_cast<const bf16*>(w), static_cast<bf16*>(res_out),
+                                            static_cast<bf16*>(y), H, eps);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_moe_route(const float* logits, int ldl, int T, int E, int top_k, int shared, float* wts, int* idx,
+                              int* counts, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (E > 32 * MAX_PER_LANE || top_k > 32) return -7;
+  cudaMemsetAsync(counts, 0, sizeof(int) * (E + 1), st);
+  route_kernel<<<(T + 3) / 4, 128, 0, st>>>(logits, ldl, T, E, top_k, shared, wts, idx, counts);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_moe_plan(const int* counts, const int* idx, int n_pairs, int Et, int bt, int* offsets, int* cursors,
+                             void* tiles, int* n_tiles, int max_tiles, int* perm, int* inv, int* err, cudaStream_t st) {
+  if (Et > 1024) return -7;
+  moe_plan_kernel<<<1, 256, 0, st>>>(counts, Et, bt, offsets, cursors, static_cast<int4*>(tiles), n_tiles, max_tiles);
+  moe_scatter_kernel<<<(n_pairs + 255) / 256, 256, 0, st>>>(idx, n_pairs, Et, offsets, cursors, perm, inv, err);
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_moe_gather(const void* x, const int* perm, int n_pairs, int P, int H, void* xs, cudaStream_t st) {
+  if (n_pairs <= 0) return 0;
+  moe_gather_kernel<<<n_pairs, 128, 0, st>>>(static_cast<const bf16*>(x), perm, P, H, static_cast<bf16*>(xs));
+  CHECK_LAUNCH();
+}
+
+extern "C" int b200_moe_combine(const void* pair_out, const float* wts, const int* inv, int T, int P, int H, void* out,
+                                cudaStream_t st) {
+  if (T <= 0) return 0;
+  moe_combine_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(pair_out), wts, inv, P, H, static_cast<bf16*>(out));
+  CHECK_LAUNCH();
+}

@@ -1,0 +1,184 @@
+// Gated DeltaNet decode: short-conv step, gated delta rule on the fp32 recurrent state, gated
+// RMSNorm. One (row, value head) per CTA; the 128 x 128 fp32 state tile is read once into
+// registers (32 values per thread), updated and written back once, so the kernel moves the
+// state-streaming minimum (reference: engine/fast/hip/gdn_chain.hip:132-386 keeps the tile in
+// registers the same way; engine/fast/kernels.py:573-633 are its unfused Triton forms).
+//
+// Work split inside a CTA of 4*DV threads: thread (p, c) owns state column c for key rows
+// [p*DK/4, (p+1)*DK/4). The four partial sums of a column are always combined as
+// ((p0 + p1) + (p2 + p3)), and the layout never depends on the number of rows in the launch,
+// so a sequence's state and outputs are bit-identical for any batch size.
+//
+// G rows per sequence (speculative verify) are processed in order on the same register tile;
+// the state after row j can be stored to `ring` so that the host can commit the accepted prefix.
+#include "common.cuh"
+
+namespace b200 {
+
+// ------------------------------------------------------------------ conv step
+// mixed: [B*G, ld] rows (row b*G + j), conv input at columns [0, C). conv_state: [slots, C, KW-1].
+// out: [B*G, C] = silu(sum_k w[c,k] * window[k]). The slot's state ends as the last KW-1 inputs;
+// with G > 1 the state after each row is also kept in ring_conv [B, G, C, KW-1] when given.
+template <int KW>
+__global__ void gdn_conv_step_kernel(const bf16* mixed, int ld, const int* slots, bf16* conv_state, const bf16* conv_w,
+                                     bf16* out, bf16* ring_conv, int C, int G) {
+  const int b = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int slot = slots[b];
+  bf16* st = conv_state + (static_cast<size_t>(slot) * C + c) * (KW - 1);
+  float win[KW];
+  float w[KW];
+#pragma unroll
+  for (int k = 0; k < KW - 1; ++k) win[k] = __bfloat162float(st[k]);
+#pragma unroll
+  for (int k = 0; k < KW; ++k) w[k] = __bfloat162float(conv_w[c * KW + k]);
+  for (int j = 0; j < G; ++j) {
+    const size_t row = static_cast<size_t>(b) * G + j;
+    win[KW - 1] = __bfloat162float(mixed[row * ld + c]);
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < KW; ++k) acc += win[k] * w[k];
+    out[row * C + c] = __float2bfloat16(silu_f(acc));
+#pragma unroll
+    for (int k = 0; k < KW - 1; ++k) win[k] = win[k + 1];
+    if (ring_conv) {
+      bf16* r = ring_conv + ((static_cast<size_t>(b) * G + j) * C + c) * (KW - 1);
+#pragma unroll
+      for (int k = 0; k < KW - 1; ++k) r[k] = __float2bfloat16(win[k]);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < KW - 1; ++k) st[k] = __float2bfloat16(win[k]);
+}
+
+// ------------------------------------------------------------------ delta-rule step
+template <int DK, int DV>
+__global__ void __launch_bounds__(4 * DV)
+gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
+                const bf16* mixed,      // [B*G, ld] z at column z_off, b at b_off, a at a_off
+                int ld, int z_off, int b_off, int a_off,
+                const int* slots, float* rec_state,  // [slots, HV, DK, DV]
+                const float* A_log, const float* dt_bias, const bf16* gnorm_w,
+                bf16* out,              // [B*G, HV*DV]
+                float* ring_rec,        // optional [B, G, HV, DK, DV]
+                int HK, int HV, int G, float eps) {
+  constexpr int KP = DK / 4;  // key rows per partition
+  const int b = blockIdx.y, h = blockIdx.x;
+  const int c = threadIdx.x % DV, p = threadIdx.x / DV;
+  const int hk = h / (HV / HK);
+  const int key_dim = HK * DK;
+  const int C = 2 * key_dim + HV * DV;
+  const int slot = slots[b];
+  float* S = rec_state + ((static_cast<size_t>(slot) * HV + h) * DK) * DV;
+
+  __shared__ float sq[DK], sk[DK];
+  __shared__ float red[4][DV][2];
+  __shared__ float nred[4][3];
+  __shared__ float wred[4 * DV / 32];
+
+  float s[KP];
+#pragma unroll
+  for (int i = 0; i < KP; ++i) s[i] = S[static_cast<size_t>(p * KP + i) * DV + c];
+
+  for (int j = 0; j < G; ++j) {
+    const size_t row = static_cast<size_t>(b) * G + j;
+    const bf16* co = conv_out + row * C;
+    // q and k of the key head: L2 normalise (q also scaled by DK^-0.5)
+    float ssq = 0.f, ssk = 0.f, sqk = 0.f;
+    if (threadIdx.x < DK) {
+      const float qv = __bfloat162float(co[hk * DK + threadIdx.x]);
+      const float kv = __bfloat162float(co[key_dim + hk * DK + threadIdx.x]);
+      sq[threadIdx.x] = qv; sk[threadIdx.x] = kv;
+      ssq = qv * qv; ssk = kv * kv; sqk = qv * kv;
+    }
+    ssq = warp_sum(ssq); ssk = warp_sum(ssk); sqk = warp_sum(sqk);
+    if ((threadIdx.x & 31) == 0 && threadIdx.x < DK) {
+      nred[threadIdx.x >> 5][0] = ssq; nred[threadIdx.x >> 5][1] = ssk; nred[threadIdx.x >> 5][2] = sqk;
+    }
+    __syncthreads();
+    float tq = 0.f, tk = 0.f, tqk = 0.f;
+#pragma unroll
+    for (int i = 0; i < DK / 32; ++i) { tq += nred[i][0]; tk += nred[i][1]; tqk += nred[i][2]; }
+    const float qs = rsqrtf(tq + 1e-6f) * rsqrtf(static_cast<float>(DK));
+    const float ks = rsqrtf(tk + 1e-6f);
+    const float kq = tqk * qs * ks;  // k . q of the normalised vectors
+
+    const float a = __bfloat162float(mixed[row * ld + a_off + h]);
+    const float bb = __bfloat162float(mixed[row * ld + b_off + h]);
+    const float decay = __expf(-__expf(A_log[h]) * softplus_f(a + dt_bias[h]));
+    const float beta = sigmoid_f(bb);
+
+    // partial S^T k and S^T q over this thread's key rows (state decayed first)
+    float pk = 0.f, pq = 0.f;
+#pragma unroll
+    for (int i = 0; i < KP; ++i) {
+      s[i] *= decay;
+      pk += s[i] * (sk[p * KP + i] * ks);
+      pq += s[i] * (sq[p * KP + i] * qs);
+    }
+    red[p][c][0] = pk; red[p][c][1] = pq;
+    __syncthreads();
+    const float kv_mem = (red[0][c][0] + red[1][c][0]) + (red[2][c][0] + red[3][c][0]);
+    const float sq_mem = (red[0][c][1] + red[1][c][1]) + (red[2][c][1] + red[3][c][1]);
+    const float v = __bfloat162float(co[2 * key_dim + h * DV + c]);
+    const float delta = (v - kv_mem) * beta;
+#pragma unroll
+    for (int i = 0; i < KP; ++i) s[i] += (sk[p * KP + i] * ks) * delta;
+    const float o = sq_mem + delta * kq;  // = S_new^T q
+
+    // gated RMSNorm over the head's DV outputs
+    const bf16 ob = __float2bfloat16(o);
+    const float of = __bfloat162float(ob);
+    float ss = (p == 0) ? of * of : 0.f;
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) wred[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < DV / 32; ++i) tot += wred[i];  // partition 0's warps only
+    if (p == 0) {
+      const float inv = rsqrtf(tot / DV + eps);
+      const float z = __bfloat162float(mixed[row * ld + z_off + h * DV + c]);
+      const float nb = __bfloat162float(__float2bfloat16(of * inv));
+      out[row * (HV * DV) + h * DV + c] = __float2bfloat16(__bfloat162float(gnorm_w[c]) * nb * silu_f(z));
+    }
+    if (ring_rec) {
+      float* R = ring_rec + (((static_cast<size_t>(b) * G + j) * HV + h) * DK) * DV;
+#pragma unroll
+      for (int i = 0; i < KP; ++i) R[static_cast<size_t>(p * KP + i) * DV + c] = s[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < KP; ++i) S[static_cast<size_t>(p * KP + i) * DV + c] = s[i];
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gdn_decode(const void* mixed, int ld, const int* slots, void* conv_state, void* rec_state,
+                               const void* conv_w, const float* A_log, const float* dt_bias, const void* gnorm_w,
+                               void* conv_out, void* out, void* ring_conv, float* ring_rec, int B, int G, int HK, int HV,
+                               int DK, int DV, int KW, float eps, cudaStream_t st) {
+  if (B <= 0) return 0;
+  const int key_dim = HK * DK, value_dim = HV * DV, C = 2 * key_dim + value_dim;
+  if (KW != 4) return -7;
+  dim3 cgrid((C + 127) / 128, B);
+  gdn_conv_step_kernel<4><<<cgrid, 128, 0, st>>>(static_cast<const bf16*>(mixed), ld, slots,
+                                                 static_cast<bf16*>(conv_state), static_cast<const bf16*>(conv_w),
+                                                 static_cast<bf16*>(conv_out), static_cast<bf16*>(ring_conv), C, G);
+  dim3 grid(HV, B);
+  const int z_off = C, b_off = C + value_dim, a_off = C + value_dim + HV;
+#define LAUNCH_STEP(DKV)                                                                                           \
+  gdn_step_kernel<DKV, DKV><<<grid, 4 * DKV, 0, st>>>(                                                             \
+      static_cast<const bf16*>(conv_out), static_cast<const bf16*>(mixed), ld, z_off, b_off, a_off, slots,         \
+      static_cast<float*>(rec_state), A_log, dt_bias, static_cast<const bf16*>(gnorm_w), static_cast<bf16*>(out), \
+      ring_rec, HK, HV, G, eps)
+  if (DK == 128 && DV == 128) LAUNCH_STEP(128);
+  else if (DK == 32 && DV == 32) LAUNCH_STEP(32);
+  else if (DK == 64 && DV == 64) LAUNCH_STEP(64);
+  else return -7;
+#undef LAUNCH_STEP
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -1,0 +1,356 @@
+// Weight-stationary ("swap-AB") bf16 GEMM on the sm_100a tensor cores.
+//
+//   out[t, n] = sum_k X[t, k] * W[n, k]          X: [T, K] activations, W: [N, K] weights
+//
+// The MMA's M dimension (128 TMEM lanes) runs over *weight rows*, its N dimension over
+// *token rows* (16..256 per tile). A decode step with a handful of rows and a prefill pass
+// with thousands therefore use the same instruction shape along K; the accumulation order of
+// one output element never depends on how many other rows share the launch, which is what
+// keeps a request's greedy tokens identical whether it is served alone or in a batch (the
+// reference gets the same property from fixed GEMV tiles, engine/fast/mfma.py:6-11, 60-71).
+//
+// Pipeline per CTA (192 threads): warp 0 = TMA producer, warp 1 = tcgen05.mma issuer and TMEM
+// owner, warps 2..5 = epilogue (one TMEM lane quarter each). Operand tiles are 64 bf16 wide
+// (128 bytes, TMA 128B swizzle), STAGES deep, guarded by full/empty mbarriers; tcgen05.commit
+// releases a stage when the MMAs that read it have finished. No cluster multicast is used.
+//
+// Variants (template): plain store (bf16 or fp32), SiLU(gate)*up over two accumulators,
+// per-tile argmax partials for the LM head, and a grouped mode where a device-side tile table
+// names (expert, first row, row count) for each token tile of an expert-sorted activation
+// buffer (replaces the reference's Triton GEMV / grouped GEMM family: engine/fast/mfma.py:90-179,
+// engine/fast/moe_prefill.py:156-319, engine/fast/fused.py:581-692).
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int BM = 128;  // weight rows per tile (TMEM lanes)
+constexpr int BK = 64;   // bf16 per operand row per stage (128 bytes)
+constexpr int UMMA_K = 16;
+
+enum Epilogue : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_ARGMAX = 3 };
+
+struct GemmParams {
+  int N;             // weight rows (per expert when grouped)
+  int K;
+  int T;             // activation rows (dense) or capacity of the sorted buffer (grouped)
+  int ldo;           // output row stride in elements
+  void* out;         // bf16 or fp32 [T, ldo]
+  const int4* tiles; // grouped: (expert, row0, nrows, 0) per token tile
+  const int* n_tiles;// grouped: number of valid entries in `tiles`
+  int up_offset;     // EPI_SILU_MUL: row offset of the "up" half inside W
+  float* part_max;   // EPI_ARGMAX: [n_tiles_n, T]
+  int* part_idx;     // EPI_ARGMAX: [n_tiles_n, T]
+  int* err;          // error word (0 = ok)
+};
+
+template <int BT, int EPI>
+struct Cfg {
+  static constexpr int A_TILES = (EPI == EPI_SILU_MUL) ? 2 : 1;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BT * BK * 2;
+  static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
+  static constexpr int BUDGET = 200 * 1024;
+  static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int TMEM_COLS_RAW = A_TILES * BT;
+  static constexpr int TMEM_COLS = TMEM_COLS_RAW <= 32 ? 32 : TMEM_COLS_RAW <= 64 ? 64 : TMEM_COLS_RAW <= 128 ? 128 : TMEM_COLS_RAW <= 256 ? 256 : 512;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BT, int EPI, bool GROUPED>
+__global__ void __launch_bounds__(192, 1)
+gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmParams p) {
+  using C = Cfg<BT, EPI>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + C::STAGES;
+  uint64_t* acc_full = bars + 2 * C::STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  __shared__ float red_max[4][BT > 0 ? BT : 1];
+  __shared__ int red_idx[4][BT > 0 ? BT : 1];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM;
+  int expert = 0, row0 = blockIdx.y * BT, nrows = BT;
+  if (GROUPED) {
+    const int nt = *p.n_tiles;
+    if (static_cast<int>(blockIdx.y) >= nt) return;  // whole CTA leaves before any barrier or TMEM use
+    const int4 t = p.tiles[blockIdx.y];
+    expert = t.x; row0 = t.y; nrows = t.z;
+  } else {
+    nrows = min(BT, p.T - row0);
+  }
+  const int num_k = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      for (int kb = 0; kb < num_k; ++kb) {
+        const int s = kb % C::STAGES;
+        const uint32_t ph = (kb / C::STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, p.err, ERR_WAIT_EMPTY, abort_flag)) break;
+        uint8_t* st = smem + s * C::STAGE_BYTES;
+        mbar_expect_tx(&full[s], C::STAGE_BYTES);
+        if (GROUPED) {
+          tma_load_3d(st, &tmW, &full[s], kb * BK, n0, expert);
+          if (EPI == EPI_SILU_MUL) tma_load_3d(st + C::A_BYTES, &tmW, &full[s], kb * BK, p.up_offset + n0, expert);
+        } else {
+          tma_load_2d(st, &tmW, &full[s], kb * BK, n0);
+          if (EPI == EPI_SILU_MUL) tma_load_2d(st + C::A_BYTES, &tmW, &full[s], kb * BK, p.up_offset + n0);
+        }
+        tma_load_2d(st + C::A_TILES * C::A_BYTES, &tmX, &full[s], kb * BK, row0);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BT);
+      bool ok = true;
+      for (int kb = 0; kb < num_k && ok; ++kb) {
+        const int s = kb % C::STAGES;
+        const uint32_t ph = (kb / C::STAGES) & 1;
+        ok = mbar_wait(&full[s], ph, p.err, ERR_WAIT_FULL, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+        const uint32_t b_addr = a_addr + C::A_TILES * C::A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint32_t koff = k * UMMA_K * 2;  // bytes inside the 128-byte swizzled row
+          const uint64_t db = umma_smem_desc(b_addr + koff);
+          umma_bf16(tmem, umma_smem_desc(a_addr + koff), db, idesc, (kb | k) != 0);
+          if (EPI == EPI_SILU_MUL)
+            umma_bf16(tmem + BT, umma_smem_desc(a_addr + C::A_BYTES + koff), db, idesc, (kb | k) != 0);
+        }
+        umma_commit(&empty[s]);  // stage reusable once these MMAs have read it
+      }
+      umma_commit(acc_full);     // always arrive so that the epilogue is released
+    }
+  } else {
+    // ---------------- epilogue: warp q owns TMEM lanes [32q, 32q+32)
+    const int q = warp & 3;
+    const bool ok = mbar_wait(acc_full, 0, p.err, ERR_WAIT_TMEM, abort_flag) && !*abort_flag;
+    tc_fence_after();
+    const int n = n0 + q * 32 + lane;
+    const bool n_ok = n < p.N;
+    if (ok) {
+#pragma unroll 1
+      for (int c = 0; c < BT; c += 16) {
+        if (c >= nrows && EPI != EPI_ARGMAX) break;  // warp-uniform
+        float v[16];
+        tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + c, v);
+        if (EPI == EPI_SILU_MUL) {
+          float u[16];
+          tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + BT + c, u);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            // round gate and up to bf16 first, as the unfused sequence of ops does
+            const float g = __bfloat162float(__float2bfloat16(v[j]));
+            const float uu = __bfloat162float(__float2bfloat16(u[j]));
+            v[j] = __bfloat162float(__float2bfloat16(silu_f(g))) * uu;
+          }
+        }
+        if (EPI == EPI_ARGMAX) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float m = n_ok ? v[j] : -INFINITY;
+            int idx = n;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+              const float om = __shfl_xor_sync(0xffffffffu, m, o);
+              const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+              if (om > m || (om == m && oi < idx)) { m = om; idx = oi; }
+            }
+            if (lane == 0) { red_max[q][c + j] = m; red_idx[q][c + j] = idx; }
+          }
+        } else if (n_ok) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c + j < nrows) {
+              const size_t o = static_cast<size_t>(row0 + c + j) * p.ldo + n;
+              if (EPI == EPI_F32) reinterpret_cast<float*>(p.out)[o] = v[j];
+              else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16(v[j]);
+            }
+          }
+        }
+      }
+    }
+    if (EPI == EPI_ARGMAX) {
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+      const int t = (warp - 2) * 32 + lane;
+      for (int c = t; c < BT; c += 128) {
+        if (c < nrows && ok) {
+          float m = red_max[0][c]; int idx = red_idx[0][c];
+#pragma unroll
+          for (int w = 1; w < 4; ++w) {
+            const float om = red_max[w][c]; const int oi = red_idx[w][c];
+            if (om > m || (om == m && oi < idx)) { m = om; idx = oi; }
+          }
+          const size_t o = static_cast<size_t>(blockIdx.x) * p.T + row0 + c;
+          p.part_max[o] = m; p.part_idx[o] = idx;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, C::TMEM_COLS); }
+}
+
+// Reduce the LM-head partials of each row over the vocabulary tiles, first maximum wins.
+__global__ void argmax_finish_kernel(const float* part_max, const int* part_idx, int n_tiles, int T, int64_t* out,
+                                     float* out_val) {
+  const int t = blockIdx.x;
+  float m = -INFINITY; int idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < n_tiles; i += blockDim.x) {
+    const float om = part_max[static_cast<size_t>(i) * T + t]; const int oi = part_idx[static_cast<size_t>(i) * T + t];
+    if (om > m || (om == m && oi < idx)) { m = om; idx = oi; }
+  }
+  __shared__ float sm[32]; __shared__ int si[32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, o); const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (om > m || (om == m && oi < idx)) { m = om; idx = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sm[threadIdx.x >> 5] = m; si[threadIdx.x >> 5] = idx; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < static_cast<int>(blockDim.x >> 5); ++w)
+      if (sm[w] > m || (sm[w] == m && si[w] < idx)) { m = sm[w]; idx = si[w]; }
+    out[t] = idx;
+    if (out_val) out_val[t] = m;
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                             const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess) fn = reinterpret_cast<EncodeFn>(ptr);
+  }
+  return fn;
+}
+
+// bf16 tensor [d2, d1, d0] (d0 contiguous), box {BK, box1, 1}, 128-byte swizzle, zero fill.
+static int make_map(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t ld1, uint64_t ld2,
+                    uint32_t box1) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {ld1 * 2, ld2 * 2};
+  cuuint32_t box[3] = {BK, box1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const int rank = d2 > 0 ? 3 : 2;
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+template <int BT, int EPI, bool GROUPED>
+static int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int grid_y, cudaStream_t st) {
+  using C = Cfg<BT, EPI>;
+  auto kern = gemm_swapab_kernel<BT, EPI, GROUPED>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess) return -3;
+    configured = true;
+  }
+  dim3 grid((p.N + BM - 1) / BM, grid_y);
+  kern<<<grid, 192, C::SMEM, st>>>(tw, tx, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+template <int EPI, bool GROUPED>
+static int dispatch_bt(int bt, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int grid_y, cudaStream_t st) {
+  switch (bt) {
+    case 16: return launch<16, EPI, GROUPED>(tw, tx, p, grid_y, st);
+    case 32: return launch<32, EPI, GROUPED>(tw, tx, p, grid_y, st);
+    case 64: return launch<64, EPI, GROUPED>(tw, tx, p, grid_y, st);
+    case 128: return launch<128, EPI, GROUPED>(tw, tx, p, grid_y, st);
+    case 256: if (EPI != EPI_SILU_MUL) return launch<(EPI != EPI_SILU_MUL ? 256 : 128), EPI, GROUPED>(tw, tx, p, grid_y, st);
+    default: return -5;
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Token-tile width for a dense GEMM over T rows: a function of T only through the tile
+// count, never through the per-element arithmetic.
+extern "C" int b200_pick_bt(int T) {
+  if (T <= 16) return 16;
+  if (T <= 32) return 32;
+  if (T <= 64) return 64;
+  if (T <= 128) return 128;
+  return 256;
+}
+
+// Dense: out[T, N] = X[T, K] W[N, K]^T.   epi: 0 bf16, 1 fp32, 2 silu(gate)*up (N = rows of each half, W has 2N rows
+// with the up half at row `up_offset`), 3 argmax partials (part_max/part_idx sized [ceil(N/128), T]).
+extern "C" int b200_gemm_dense(const void* X, const void* W, void* out, int T, int N, int K, int ldx, int ldw, int ldo,
+                               int epi, int up_offset, int bt, float* part_max, int* part_idx, int* err,
+                               cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (bt <= 0) bt = b200_pick_bt(T);
+  if (epi == EPI_SILU_MUL && bt > 128) bt = 128;
+  CUtensorMap tw, tx;
+  const int w_rows = (epi == EPI_SILU_MUL) ? up_offset + N : N;
+  if (make_map(&tw, W, K, w_rows, 0, ldw, 0, BM)) return -1;
+  if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
+  GemmParams p{N, K, T, ldo, out, nullptr, nullptr, up_offset, part_max, part_idx, err};
+  const int gy = (T + bt - 1) / bt;
+  switch (epi) {
+    case EPI_BF16: return dispatch_bt<EPI_BF16, false>(bt, tw, tx, p, gy, st);
+    case EPI_F32: return dispatch_bt<EPI_F32, false>(bt, tw, tx, p, gy, st);
+    case EPI_SILU_MUL: return dispatch_bt<EPI_SILU_MUL, false>(bt, tw, tx, p, gy, st);
+    case EPI_ARGMAX: return dispatch_bt<EPI_ARGMAX, false>(bt, tw, tx, p, gy, st);
+  }
+  return -6;
+}
+
+// Grouped: X is the expert-sorted activation buffer [cap, K]; tile i covers rows
+// [tiles[i].y, +tiles[i].z) of expert tiles[i].x; W is [E, rows, K]. `max_tiles` bounds the grid.
+extern "C" int b200_gemm_grouped(const void* X, const void* W, void* out, int cap, int E, int N, int w_rows, int K,
+                                 int ldo, int epi, int up_offset, int bt, const void* tiles, const int* n_tiles,
+                                 int max_tiles, int* err, cudaStream_t st) {
+  if (max_tiles <= 0) return 0;
+  CUtensorMap tw, tx;
+  if (make_map(&tw, W, K, w_rows, E, K, static_cast<uint64_t>(w_rows) * K, BM)) return -1;
+  if (make_map(&tx, X, K, cap, 0, K, 0, bt)) return -1;
+  GemmParams p{N, K, cap, ldo, out, reinterpret_cast<const int4*>(tiles), n_tiles, up_offset, nullptr, nullptr, err};
+  switch (epi) {
+    case EPI_BF16: return dispatch_bt<EPI_BF16, true>(bt, tw, tx, p, max_tiles, st);
+    case EPI_SILU_MUL: return dispatch_bt<EPI_SILU_MUL, true>(bt, tw, tx, p, max_tiles, st);
+  }
+  return -6;
+}
+
+extern "C" int b200_argmax_finish(const float* part_max, const int* part_idx, int n_tiles, int T, int64_t* out,
+                                  float* out_val, cudaStream_t st) {
+  if (T <= 0) return 0;
+  argmax_finish_kernel<<<T, 256, 0, st>>>(part_max, part_idx, n_tiles, T, out, out_val);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

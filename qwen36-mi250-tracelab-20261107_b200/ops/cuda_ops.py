@@ -1,0 +1,294 @@
+"""ctypes bindings of the sm_100a kernel library, with the same call signatures as ``torch_ops``.
+
+The library (``ops/cuda/libb200serve_kernels.so``) is built ahead of time by
+``ops/build.py`` and must be present on a GPU machine: importing this module on a
+machine with a CUDA device and no library raises, so a missing build can never
+turn into a silent PyTorch fallback. Every launcher takes raw device pointers and
+the current CUDA stream, which makes each call capturable in a CUDA graph
+(the reference gets graph-capturable launches from ``hipModuleLaunchKernel`` on the
+current stream, ``engine/fast/hipmega_rtc.py:150-215``).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from ..config import PAGE_SIZE
+from . import torch_ops
+from .build import lib_path
+
+_lib = None
+ATTN_Z = 32  # context lanes of the decode attention (fixed: part of the numerics contract)
+
+EPI_BF16, EPI_F32, EPI_SILU_MUL, EPI_ARGMAX = 0, 1, 2, 3
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        path = lib_path()
+        if not path.exists():
+            raise KernelError(f"{path} is missing: run `python -m b200serve.ops.build` (or __graft_entry__.build())")
+        _lib = ctypes.CDLL(str(path))
+        for name in dir(_Sig):
+            if name.startswith("b200_"):
+                fn = getattr(_lib, name)
+                fn.restype = c_int
+                fn.argtypes = getattr(_Sig, name)
+    return _lib
+
+
+P, I, F = c_void_p, c_int, c_float
+
+
+class _Sig:
+    b200_pick_bt = [I]
+    b200_gemm_dense = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, P, P]
+    b200_gemm_grouped = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, I, P, P]
+    b200_argmax_finish = [P, P, I, I, P, P, P]
+    b200_embed = [P, P, P, I, I, I, P]
+    b200_add_rmsnorm = [P, P, P, P, P, I, I, F, I, P]
+    b200_moe_route = [P, I, I, I, I, I, P, P, P, P]
+    b200_moe_plan = [P, P, I, I, I, P, P, P, P, I, P, P, P, P]
+    b200_moe_gather = [P, P, I, I, I, P, P]
+    b200_moe_combine = [P, P, P, I, I, I, P, P]
+    b200_gdn_decode = [P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P]
+    b200_attn_prep = [P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P, P]
+    b200_paged_attn = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
+
+
+def _ptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{what} failed with code {rc}")
+
+
+_err: dict[int, torch.Tensor] = {}
+
+
+def err_word(device: torch.device) -> torch.Tensor:
+    """The per-device error word kernels write when a bounded wait or an index check fails."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _err:
+        _err[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _err[idx]
+
+
+def check_errors(device: torch.device) -> None:
+    """Read the error word (synchronises) and raise if any kernel recorded a failure."""
+    code = int(err_word(device).item())
+    if code:
+        err_word(device).zero_()
+        names = {1: "TMA stage never arrived", 2: "no free pipeline stage", 3: "accumulator never completed",
+                 4: "peer flag never arrived", 5: "index out of range"}
+        raise KernelError(f"device-side failure {code}: {names.get(code, 'unknown')}")
+
+
+# --------------------------------------------------------------------------- GEMM family
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None, bt: int = 0) -> torch.Tensor:
+    """``x [T, K] @ w[N, K].T`` on tcgen05; bf16 in, bf16 (default) or fp32 out."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    T, K = x.shape
+    N = w.shape[0]
+    f32 = out_dtype == torch.float32
+    out = torch.empty(T, N, dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
+    if T == 0:
+        return out
+    assert x.stride(1) == 1 and w.stride(1) == 1 and K % 8 == 0
+    rc = lib().b200_gemm_dense(
+        _ptr(x), _ptr(w), _ptr(out), T, N, K, x.stride(0), w.stride(0), N, EPI_F32 if f32 else EPI_BF16, 0, bt,
+        None, None, _ptr(err_word(x.device)), _stream(),
+    )
+    _check(rc, "gemm_dense")
+    return out
+
+
+def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(x @ Wg.T) * (x @ Wu.T)`` with ``w_gate_up = [Wg; Wu]``, fused in the GEMM epilogue."""
+    T, K = x.shape
+    inter = w_gate_up.shape[0] // 2
+    out = torch.empty(T, inter, dtype=torch.bfloat16, device=x.device)
+    rc = lib().b200_gemm_dense(
+        _ptr(x), _ptr(w_gate_up), _ptr(out), T, inter, K, x.stride(0), w_gate_up.stride(0), inter, EPI_SILU_MUL,
+        inter, 0, None, None, _ptr(err_word(x.device)), _stream(),
+    )
+    _check(rc, "gemm_dense(silu_mul)")
+    return out
+
+
+def lm_head_argmax(x: torch.Tensor, w: torch.Tensor, return_value: bool = False):
+    """Greedy token per row: LM-head GEMM with per-tile argmax partials, then one reduce. Ties to the lower id."""
+    T, K = x.shape
+    V = w.shape[0]
+    n_tiles = (V + 127) // 128
+    pmax = torch.empty(n_tiles, T, dtype=torch.float32, device=x.device)
+    pidx = torch.empty(n_tiles, T, dtype=torch.int32, device=x.device)
+    out = torch.empty(T, dtype=torch.int64, device=x.device)
+    val = torch.empty(T, dtype=torch.float32, device=x.device) if return_value else None
+    rc = lib().b200_gemm_dense(
+        _ptr(x), _ptr(w), None, T, V, K, x.stride(0), w.stride(0), 0, EPI_ARGMAX, 0, 0, _ptr(pmax), _ptr(pidx),
+        _ptr(err_word(x.device)), _stream(),
+    )
+    _check(rc, "gemm_dense(argmax)")
+    _check(lib().b200_argmax_finish(_ptr(pmax), _ptr(pidx), n_tiles, T, _ptr(out), _ptr(val), _stream()), "argmax_finish")
+    return (out, val) if return_value else out
+
+
+# --------------------------------------------------------------------------- norms
+def add_rmsnorm(x: torch.Tensor, res: torch.Tensor | None, w: torch.Tensor, eps: float):
+    T, H = x.shape
+    y = torch.empty_like(x)
+    new = torch.empty_like(x) if res is not None else x
+    rc = lib().b200_add_rmsnorm(
+        _ptr(x), _ptr(res), _ptr(w), _ptr(new) if res is not None else None, _ptr(y), T, H, eps, 1, _stream()
+    )
+    _check(rc, "add_rmsnorm")
+    return new, y
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    return add_rmsnorm(x2, None, w, eps)[1].view(shape)
+
+
+def embed(tokens: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    T = tokens.shape[0]
+    out = torch.empty(T, table.shape[1], dtype=table.dtype, device=table.device)
+    _check(lib().b200_embed(_ptr(tokens), _ptr(table), _ptr(out), T, table.shape[1], table.shape[0], _stream()), "embed")
+    return out
+
+
+# --------------------------------------------------------------------------- MoE
+def moe_bt(T: int, pairs_per_row: int, n_experts: int) -> int:
+    """Token-tile width of the grouped GEMMs from the expected rows per routed expert."""
+    per = T * max(1, pairs_per_row - 1) / max(1, n_experts)
+    for bt in (16, 32, 64, 128):
+        if per <= bt:
+            return bt
+    return 128
+
+
+def moe_block(x: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, n_experts: int,
+              top_k: int, shared_merged: bool) -> torch.Tensor:
+    """Router GEMM, top-k, expert-sorted grouped gate/up + SiLU-mul, grouped down, weighted combine."""
+    T, H = x.shape
+    dev = x.device
+    Et = w_gate_up.shape[0]
+    inter = w_down.shape[2]
+    Pn = top_k + (1 if shared_merged else 0)
+    n_pairs = T * Pn
+    L = lib()
+    st = _stream()
+    err = err_word(dev)
+    logits = linear(x, router, out_dtype=torch.float32)
+    wts = torch.empty(T, Pn, dtype=torch.float32, device=dev)
+    idx = torch.empty(T, Pn, dtype=torch.int32, device=dev)
+    ints = torch.empty(3 * (Et + 1) + 1 + 2 * n_pairs, dtype=torch.int32, device=dev)
+    counts, offsets, cursors = ints[: Et + 1], ints[Et + 1 : 2 * Et + 2], ints[2 * Et + 2 : 3 * Et + 3]
+    n_tiles = ints[3 * Et + 3 : 3 * Et + 4]
+    perm = ints[3 * Et + 4 : 3 * Et + 4 + n_pairs]
+    inv = ints[3 * Et + 4 + n_pairs :]
+    _check(L.b200_moe_route(_ptr(logits), logits.stride(0), T, n_experts, top_k, int(shared_merged), _ptr(wts),
+                            _ptr(idx), _ptr(counts), st), "moe_route")
+    bt = moe_bt(T, Pn, n_experts)
+    max_tiles = min(Et, n_pairs) + n_pairs // bt + 1
+    tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device=dev)
+    _check(L.b200_moe_plan(_ptr(counts), _ptr(idx), n_pairs, Et, bt, _ptr(offsets), _ptr(cursors), _ptr(tiles),
+                           _ptr(n_tiles), max_tiles, _ptr(perm), _ptr(inv), _ptr(err), st), "moe_plan")
+    xs = torch.empty(n_pairs, H, dtype=x.dtype, device=dev)
+    _check(L.b200_moe_gather(_ptr(x), _ptr(perm), n_pairs, Pn, H, _ptr(xs), st), "moe_gather")
+    act = torch.empty(n_pairs, inter, dtype=x.dtype, device=dev)
+    _check(L.b200_gemm_grouped(_ptr(xs), _ptr(w_gate_up), _ptr(act), n_pairs, Et, inter, 2 * inter, H, inter,
+                               EPI_SILU_MUL, inter, bt, _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err), st),
+           "gemm_grouped(gate_up)")
+    pair_out = torch.empty(n_pairs, H, dtype=x.dtype, device=dev)
+    _check(L.b200_gemm_grouped(_ptr(act), _ptr(w_down), _ptr(pair_out), n_pairs, Et, H, H, inter, H, EPI_BF16, 0, bt,
+                               _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err), st), "gemm_grouped(down)")
+    out = torch.empty_like(x)
+    _check(L.b200_moe_combine(_ptr(pair_out), _ptr(wts), _ptr(inv), T, Pn, H, _ptr(out), st), "moe_combine")
+    return out
+
+
+# --------------------------------------------------------------------------- GDN
+def gdn_decode(mixed, slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnorm_w, n_k, n_v, dk, dv, eps,
+               G: int = 1, ring=None) -> torch.Tensor:
+    """Conv step + delta rule + gated norm for ``B*G`` rows (``G`` consecutive rows per slot)."""
+    rows = mixed.shape[0]
+    B = rows // G
+    C = 2 * n_k * dk + n_v * dv
+    conv_out = torch.empty(rows, C, dtype=mixed.dtype, device=mixed.device)
+    out = torch.empty(rows, n_v * dv, dtype=mixed.dtype, device=mixed.device)
+    slots32 = slots if slots.dtype == torch.int32 else slots.to(torch.int32)
+    rc = lib().b200_gdn_decode(
+        _ptr(mixed), mixed.stride(0), _ptr(slots32), _ptr(conv_state), _ptr(rec_state), _ptr(conv_w), _ptr(A_log),
+        _ptr(dt_bias), _ptr(gnorm_w), _ptr(conv_out), _ptr(out), _ptr(ring[0]) if ring else None,
+        _ptr(ring[1]) if ring else None, B, G, n_k, n_v, dk, dv, conv_w.shape[1], eps, _stream(),
+    )
+    _check(rc, "gdn_decode")
+    return out
+
+
+def gdn_prefill(mixed, seg_starts, seg_slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnorm_w, n_k, n_v, dk,
+                dv, eps) -> torch.Tensor:
+    """Chunked prefill of the delta rule. Batched PyTorch over equal-length groups for now."""
+    return torch_ops.gdn_prefill_batched(
+        mixed, seg_starts, seg_slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnorm_w, n_k, n_v, dk, dv, eps
+    )
+
+
+# --------------------------------------------------------------------------- attention
+def attention(qkv, positions, seq_of_row, block_tables, kv_layer, q_norm, k_norm, n_q, n_kv, head_dim, rotary_dim,
+              theta, eps, G: int, seg_starts=None, seg_pos0=None) -> torch.Tensor:
+    """q/k norm + RoPE + KV page write, then gated attention over the paged cache.
+
+    ``G > 0``: every sequence has exactly ``G`` rows (decode ``G = 1``, verify ``G = k + 1``) and the
+    flash-decoding kernel runs. ``G = 0``: ragged prefill spans; the page gather + softmax
+    runs in PyTorch per sequence after the fused prep kernel.
+    """
+    rows = qkv.shape[0]
+    dev = qkv.device
+    q = torch.empty(rows, n_q, head_dim, dtype=qkv.dtype, device=dev)
+    gate = torch.empty(rows, n_q * head_dim, dtype=qkv.dtype, device=dev)
+    num_pages = kv_layer.shape[0]
+    rc = lib().b200_attn_prep(
+        _ptr(qkv), qkv.stride(0), _ptr(positions), _ptr(block_tables), block_tables.stride(0), _ptr(seq_of_row),
+        _ptr(q_norm), _ptr(k_norm), _ptr(q), _ptr(gate), _ptr(kv_layer), rows, n_q, n_kv, head_dim, rotary_dim,
+        theta, eps, num_pages, _ptr(err_word(dev)), _stream(),
+    )
+    _check(rc, "attn_prep")
+    if G == 0:
+        return torch_ops.paged_attention(q, gate, kv_layer, block_tables, seg_starts, seg_pos0)
+    B = rows // G
+    part_acc = torch.empty(rows, n_q, ATTN_Z, head_dim, dtype=torch.float32, device=dev)
+    part_ml = torch.empty(rows, n_q, ATTN_Z, 2, dtype=torch.float32, device=dev)
+    out = torch.empty(rows, n_q * head_dim, dtype=qkv.dtype, device=dev)
+    rc = lib().b200_paged_attn(
+        _ptr(q), _ptr(gate), _ptr(kv_layer), _ptr(block_tables), block_tables.stride(0), _ptr(positions),
+        _ptr(part_acc), _ptr(part_ml), _ptr(out), B, G, n_q, n_kv, head_dim, ATTN_Z, num_pages, _stream(),
+    )
+    _check(rc, "paged_attn")
+    return out
+
+
+def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
+    return torch.argmax(logits, dim=-1)
+
+
+__all__ = [n for n in dir() if not n.startswith("_")]

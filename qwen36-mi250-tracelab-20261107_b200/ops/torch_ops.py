@@ -353,21 +353,145 @@ def gdn_decode(
     dk: int,
     dv: int,
     eps: float,
+    G: int = 1,
+    ring=None,
 ) -> torch.Tensor:
-    """One decode token per row: conv step, recurrent delta rule, gated norm; state in place."""
-    B = mixed.shape[0]
-    qkv, z, b, a = gdn_split(mixed, n_k * dk, n_v * dv, n_v)
-    g, beta = gdn_gates(a, b, A_log, dt_bias)
+    """Decode rows: conv step, recurrent delta rule, gated norm; slot state updated in place.
+
+    ``mixed [B*G, .]`` holds ``G`` consecutive rows per slot (``G = 1`` plain decode, ``G = k+1``
+    speculative verify), processed in order. With ``ring = (conv [B,G,C,K-1], rec [B,G,Hv,dk,dv])``
+    the state after every row is also stored, so that a verify step can commit any prefix.
+    """
+    rows = mixed.shape[0]
+    B = rows // G
+    qkv_all, z_all, b_all, a_all = gdn_split(mixed, n_k * dk, n_v * dv, n_v)
+    g_all, beta_all = gdn_gates(a_all, b_all, A_log, dt_bias)
     sl = slots.long()
-    win = torch.cat([conv_state[sl].to(mixed.dtype), qkv[:, :, None]], dim=-1)  # [B, C, K]
-    conv_out = F.silu((win.float() * conv_w.float()[None]).sum(-1)).to(mixed.dtype)
-    conv_state[sl] = win[:, :, 1:].to(conv_state.dtype)
-    q, k, v = _gdn_qkv_heads(conv_out, n_k, n_v, dk, dv)
-    S = rec_state[sl]
-    o = gdn_recurrent_step(q, k, v, g, beta, S)
+    out = torch.empty(rows, n_v * dv, dtype=mixed.dtype, device=mixed.device)
+    base = torch.arange(B, device=mixed.device) * G
+    conv = conv_state[sl].to(mixed.dtype)
+    S = rec_state[sl].clone()
+    for j in range(G):
+        r = base + j
+        win = torch.cat([conv, qkv_all[r][:, :, None]], dim=-1)  # [B, C, K]
+        conv_out = F.silu((win.float() * conv_w.float()[None]).sum(-1)).to(mixed.dtype)
+        conv = win[:, :, 1:]
+        q, k, v = _gdn_qkv_heads(conv_out, n_k, n_v, dk, dv)
+        o = gdn_recurrent_step(q, k, v, g_all[r], beta_all[r], S)
+        out[r] = gated_rmsnorm(o.to(mixed.dtype), z_all[r].reshape(B, n_v, dv), gnorm_w, eps).reshape(B, n_v * dv)
+        if ring is not None:
+            ring[0][:, j] = conv.to(ring[0].dtype)
+            ring[1][:, j] = S
+    conv_state[sl] = conv.to(conv_state.dtype)
     rec_state[sl] = S
-    out = gated_rmsnorm(o.to(mixed.dtype), z.reshape(B, n_v, dv), gnorm_w, eps)
-    return out.reshape(B, n_v * dv)
+    return out
+
+
+def gdn_prefill_batched(
+    mixed, seg_starts, seg_slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnorm_w, n_k, n_v, dk, dv, eps,
+    chunk: int = GDN_CHUNK,
+) -> torch.Tensor:
+    """``gdn_prefill`` vectorised over sequences: spans are padded to a common chunk count with
+    identity rows (``beta = 0``, ``g = 0``, zero inputs), which leave the state untouched."""
+    dev = mixed.device
+    T = mixed.shape[0]
+    nseg = len(seg_slots)
+    lens = [seg_starts[i + 1] - seg_starts[i] for i in range(nseg)]
+    Lmax = max(lens)
+    Lp = (Lmax + chunk - 1) // chunk * chunk
+    nc = Lp // chunk
+    K = conv_w.shape[1]
+    qkv, z, b, a = gdn_split(mixed, n_k * dk, n_v * dv, n_v)
+    g_all, beta_all = gdn_gates(a, b, A_log, dt_bias)
+    # row r of segment i sits at padded index (i, r - start_i)
+    seg_of_row = torch.repeat_interleave(torch.arange(nseg, device=dev), torch.tensor(lens, device=dev))
+    starts = torch.tensor(seg_starts[:-1], device=dev)
+    off = torch.arange(T, device=dev) - starts[seg_of_row]
+    slots = torch.tensor(seg_slots, device=dev)
+    lens_t = torch.tensor(lens, device=dev)
+    C = qkv.shape[1]
+    xin = torch.zeros(nseg, K - 1 + Lp, C, dtype=mixed.dtype, device=dev)
+    xin[:, : K - 1] = conv_state[slots].transpose(1, 2).to(mixed.dtype)
+    xin[seg_of_row, off + K - 1] = qkv
+    win = xin.unfold(1, K, 1)  # [nseg, Lp, C, K]
+    conv_out = F.silu((win.float() * conv_w.float()[None, None]).sum(-1)).to(mixed.dtype)
+    tail_idx = lens_t[:, None] + torch.arange(K - 1, device=dev)[None, :]  # last K-1 inputs of each span
+    conv_state[slots] = torch.gather(xin, 1, tail_idx[:, :, None].expand(-1, -1, C)).transpose(1, 2).to(conv_state.dtype)
+    q, k, v = _gdn_qkv_heads(conv_out.reshape(nseg * Lp, C), n_k, n_v, dk, dv)
+    valid = (torch.arange(Lp, device=dev)[None, :] < lens_t[:, None]).reshape(nseg * Lp, 1, 1)
+    q, k, v = q * valid, k * valid, v * valid
+    g = torch.zeros(nseg, Lp, n_v, dtype=torch.float32, device=dev)
+    beta = torch.zeros(nseg, Lp, n_v, dtype=torch.float32, device=dev)
+    g[seg_of_row, off] = g_all
+    beta[seg_of_row, off] = beta_all
+    # [nseg, Hv, nc, chunk, d]
+    q, k, v = (t.view(nseg, Lp, n_v, -1).permute(0, 2, 1, 3).reshape(nseg, n_v, nc, chunk, -1) for t in (q, k, v))
+    g = g.permute(0, 2, 1).reshape(nseg, n_v, nc, chunk)
+    beta = beta.permute(0, 2, 1).reshape(nseg, n_v, nc, chunk)
+    gc = g.cumsum(-1)
+    decay = (gc[..., :, None] - gc[..., None, :]).tril().exp().tril()
+    kb = k * beta[..., None]
+    A = ((kb @ k.transpose(-1, -2)) * decay).tril(-1)
+    eye = torch.eye(chunk, dtype=A.dtype, device=dev)
+    Tinv = torch.linalg.solve_triangular(eye + A, eye.expand_as(A).contiguous(), upper=False, unitriangular=True)
+    u = Tinv @ (v * beta[..., None])
+    w = Tinv @ (kb * gc.exp()[..., None])
+    qk = ((q @ k.transpose(-1, -2)) * decay).tril()
+    out = torch.empty(nseg, n_v, nc, chunk, dv, dtype=torch.float32, device=dev)
+    S = rec_state[slots].float().clone()
+    for c in range(nc):
+        v_new = u[:, :, c] - w[:, :, c] @ S
+        out[:, :, c] = (q[:, :, c] * gc[:, :, c].exp()[..., None]) @ S + qk[:, :, c] @ v_new
+        last = gc[:, :, c, -1]
+        S = S * last.exp()[..., None, None] + (
+            k[:, :, c] * (last[..., None] - gc[:, :, c]).exp()[..., None]
+        ).transpose(-1, -2) @ v_new
+    rec_state[slots] = S
+    o = out.reshape(nseg, n_v, Lp, dv).permute(0, 2, 1, 3)[seg_of_row, off]  # [T, Hv, dv]
+    return gated_rmsnorm(o.to(mixed.dtype), z.reshape(T, n_v, dv), gnorm_w, eps).reshape(T, n_v * dv)
+
+
+# --------------------------------------------------------------------------- composite blocks
+def embed(tokens: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    return table[tokens]
+
+
+def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    inter = w_gate_up.shape[0] // 2
+    gu = linear(x, w_gate_up)
+    return F.silu(gu[:, :inter].float()).to(x.dtype) * gu[:, inter:]
+
+
+def lm_head_argmax(x: torch.Tensor, w: torch.Tensor, return_value: bool = False):
+    logits = linear(x, w, out_dtype=torch.float32)
+    idx = argmax_rows(logits)
+    if return_value:
+        return idx, logits.gather(1, idx[:, None])[:, 0]
+    return idx
+
+
+def moe_block(x, router, w_gate_up, w_down, n_experts: int, top_k: int, shared_merged: bool) -> torch.Tensor:
+    """Router, top-k and experts; with ``shared_merged`` router row ``E`` is the shared gate and
+    expert ``E`` the shared expert, selected for every row with weight ``sigmoid(logit_E)``."""
+    logits = linear(x, router, out_dtype=torch.float32)
+    wts, idx = router_topk(logits[:, :n_experts], top_k)
+    if shared_merged:
+        wts = torch.cat([wts, torch.sigmoid(logits[:, n_experts : n_experts + 1])], dim=1)
+        idx = torch.cat([idx, torch.full_like(idx[:, :1], n_experts)], dim=1)
+    return moe_experts(x, wts.to(x.dtype), idx, w_gate_up, w_down)
+
+
+def attention(qkv, positions, seq_of_row, block_tables, kv_layer, q_norm, k_norm, n_q, n_kv, head_dim, rotary_dim,
+              theta, eps, G: int, seg_starts=None, seg_pos0=None) -> torch.Tensor:
+    """q/k norm, RoPE, KV page write and causal gated attention over the paged cache (see ``cuda_ops.attention``)."""
+    q, gate, k, v = attn_prep(qkv, positions, q_norm, k_norm, n_q, n_kv, head_dim, rotary_dim, theta, eps)
+    page_ids = block_tables[seq_of_row.long(), positions // PAGE_SIZE].long()
+    kv_write(kv_layer, k, v, page_ids, positions % PAGE_SIZE)
+    if G > 0:
+        B = qkv.shape[0] // G
+        seg_starts = [i * G for i in range(B + 1)]
+        seg_pos0 = positions[::G].tolist()
+    return paged_attention(q, gate, kv_layer, block_tables, seg_starts, seg_pos0)
 
 
 # --------------------------------------------------------------------------- head

@@ -1,0 +1,225 @@
+"""Each sm_100a kernel against the plain PyTorch fp32 reference of the same op."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def C():
+    from b200serve.ops import cuda_ops
+
+    cuda_ops.lib()
+    return cuda_ops
+
+
+@pytest.fixture(scope="module")
+def O():
+    from b200serve.ops import torch_ops
+
+    return torch_ops
+
+
+def _bf(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, device="cuda", generator=g) * scale).to(torch.bfloat16)
+
+
+def _close(got, ref, atol, rtol, what=""):
+    got, ref = got.float(), ref.float()
+    err = (got - ref).abs()
+    tol = atol + rtol * ref.abs()
+    bad = (err > tol).sum().item()
+    assert bad == 0, f"{what}: {bad}/{err.numel()} off, max err {err.max().item():.4g}, ref max {ref.abs().max().item():.4g}"
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 128, 64), (5, 256, 128), (16, 384, 2048), (33, 1000, 512), (128, 4096, 2048),
+                                   (300, 777, 256), (1024, 2048, 2048)])
+def test_gemm_dense(C, T, N, K):
+    x, w = _bf(T, K, seed=1), _bf(N, K, scale=0.05, seed=2)
+    ref = x.float() @ w.float().t()
+    _close(C.linear(x, w), ref, 2e-2, 1e-2, "bf16 out")
+    _close(C.linear(x, w, out_dtype=torch.float32), ref, 1e-3, 1e-3, "fp32 out")
+    C.check_errors(x.device)
+
+
+def test_gemm_rows_are_batch_invariant(C):
+    x, w = _bf(256, 2048, seed=3), _bf(1024, 2048, scale=0.05, seed=4)
+    full = C.linear(x, w, out_dtype=torch.float32)
+    for rows in (1, 7, 16, 40, 100):
+        part = C.linear(x[:rows].contiguous(), w, out_dtype=torch.float32)
+        assert torch.equal(part, full[:rows]), rows
+    C.check_errors(x.device)
+
+
+@pytest.mark.parametrize("T,I,K", [(3, 64, 128), (40, 512, 2048), (200, 512, 2048)])
+def test_gemm_silu_mul(C, O, T, I, K):
+    x, w = _bf(T, K, seed=5), _bf(2 * I, K, scale=0.05, seed=6)
+    ref = O.linear_silu_mul(x.float(), w.float())
+    _close(C.linear_silu_mul(x, w), ref, 2e-2, 2e-2)
+    C.check_errors(x.device)
+
+
+@pytest.mark.parametrize("T,V", [(1, 1024), (9, 5000), (130, 20000)])
+def test_lm_head_argmax(C, T, V):
+    x, w = _bf(T, 256, seed=7), _bf(V, 256, seed=8)
+    logits = C.linear(x, w, out_dtype=torch.float32)
+    idx, val = C.lm_head_argmax(x, w, return_value=True)
+    assert torch.equal(idx, logits.argmax(-1))
+    assert torch.equal(val, logits.max(-1).values)
+    C.check_errors(x.device)
+
+
+@pytest.mark.parametrize("T,H", [(1, 128), (77, 2048), (4, 4096)])
+def test_add_rmsnorm(C, O, T, H):
+    x, r, w = _bf(T, H, seed=9), _bf(T, H, seed=10), _bf(H, scale=0.1, seed=11)
+    new, y = C.add_rmsnorm(x, r, w, 1e-6)
+    rn, ry = O.add_rmsnorm(x, r, w, 1e-6)
+    assert torch.equal(new, rn)
+    _close(y, O.rmsnorm(rn.float(), w.float(), 1e-6), 2e-2, 1e-2)
+    _, y1 = C.add_rmsnorm(x, None, w, 1e-6)
+    _close(y1, O.rmsnorm(x.float(), w.float(), 1e-6), 2e-2, 1e-2)
+
+
+def test_embed(C):
+    table = _bf(1000, 128, seed=12)
+    tok = torch.randint(0, 1000, (50,), device="cuda")
+    assert torch.equal(C.embed(tok, table), table[tok])
+
+
+@pytest.mark.parametrize("T,E,k,H,I", [(1, 8, 2, 128, 64), (37, 8, 2, 128, 64), (128, 256, 8, 2048, 512),
+                                       (700, 64, 4, 256, 128)])
+def test_moe_block(C, O, T, E, k, H, I):
+    x = _bf(T, H, seed=13)
+    router = _bf(E + 1, H, scale=0.3, seed=14)
+    wgu, wd = _bf(E + 1, 2 * I, H, scale=0.05, seed=15), _bf(E + 1, H, I, scale=0.05, seed=16)
+    got = C.moe_block(x, router, wgu, wd, E, k, True)
+    C.check_errors(x.device)
+    # reference from the kernel's own fp32 router logits, so that near-tied experts cannot differ
+    logits = C.linear(x, router, out_dtype=torch.float32)
+    wts, idx = O.router_topk(logits[:, :E], k)
+    wts = torch.cat([wts, torch.sigmoid(logits[:, E:E + 1])], 1).to(torch.bfloat16)
+    idx = torch.cat([idx, torch.full_like(idx[:, :1], E)], 1)
+    ref = O.moe_experts(x.float(), wts.float(), idx, wgu.float(), wd.float())
+    _close(got, ref, 3e-2 * ref.abs().max().item(), 3e-2)
+
+
+def test_route_ties_pick_lower_id(C):
+    import ctypes  # noqa: F401
+
+    T, E, k = 4, 256, 8
+    logits = torch.zeros(T, E + 1, device="cuda")
+    logits[1, 100:120] = 1.0
+    logits[2, ::2] = 0.5
+    x = torch.zeros(T, 64, device="cuda", dtype=torch.bfloat16)
+    wts = torch.empty(T, k + 1, device="cuda")
+    idx = torch.empty(T, k + 1, dtype=torch.int32, device="cuda")
+    counts = torch.empty(E + 1, dtype=torch.int32, device="cuda")
+    rc = C.lib().b200_moe_route(logits.data_ptr(), E + 1, T, E, k, 1, wts.data_ptr(), idx.data_ptr(),
+                                counts.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert idx[0, :k].tolist() == list(range(8))
+    assert idx[1, :k].tolist() == list(range(100, 108))
+    assert idx[2, :k].tolist() == list(range(0, 16, 2))
+    assert torch.allclose(wts[:, :k].sum(1), torch.ones(T, device="cuda"), atol=2e-2)
+    assert counts.sum().item() == T * (k + 1) and counts[E].item() == T
+    del x
+
+
+def _gdn_setup(cfg_dims, B, G, seed):
+    n_k, n_v, dk, dv = cfg_dims
+    Cdim = 2 * n_k * dk + n_v * dv
+    rows = Cdim + n_v * dv + 2 * n_v
+    mixed = _bf(B * G, rows, seed=seed)
+    conv_w = _bf(Cdim, 4, scale=0.3, seed=seed + 1)
+    g = torch.Generator(device="cuda").manual_seed(seed + 2)
+    A_log = torch.rand(n_v, device="cuda", generator=g) * 2
+    dt_bias = torch.randn(n_v, device="cuda", generator=g)
+    gw = (1 + 0.1 * torch.randn(dv, device="cuda", generator=g)).to(torch.bfloat16)
+    S = B + 3
+    conv = _bf(S, Cdim, 3, seed=seed + 3)
+    rec = torch.randn(S, n_v, dk, dv, device="cuda", generator=g) * 0.2
+    slots = torch.randperm(S - 1, device="cuda", generator=g)[:B].to(torch.int32) + 1
+    return mixed, slots, conv, rec, (conv_w, A_log, dt_bias, gw, n_k, n_v, dk, dv, 1e-6)
+
+
+@pytest.mark.parametrize("dims,B,G", [((2, 4, 32, 32), 3, 1), ((16, 32, 128, 128), 5, 1), ((16, 32, 128, 128), 2, 4),
+                                      ((2, 4, 32, 32), 4, 3)])
+def test_gdn_decode(C, O, dims, B, G):
+    mixed, slots, conv, rec, args = _gdn_setup(dims, B, G, seed=20)
+    n_v, dk, dv = dims[1], dims[2], dims[3]
+    Cdim = conv.shape[1]
+    conv_r, rec_r = conv.float().clone(), rec.clone()
+    a = list(args)
+    ref_args = (a[0].float(), a[1], a[2], a[3].float(), *a[4:])
+    ring_r = (torch.empty(B, G, Cdim, 3, device="cuda"), torch.empty(B, G, n_v, dk, dv, device="cuda"))
+    ref = O.gdn_decode(mixed.float(), slots, conv_r, rec_r, *ref_args, G=G, ring=ring_r)
+    ring = (torch.empty(B, G, Cdim, 3, device="cuda", dtype=torch.bfloat16), torch.empty(B, G, n_v, dk, dv, device="cuda"))
+    got = C.gdn_decode(mixed, slots, conv, rec, *args, G=G, ring=ring)
+    _close(got, ref, 3e-2, 3e-2, "out")
+    _close(rec, rec_r, 5e-3, 2e-2, "state")
+    _close(conv, conv_r, 1e-6, 0, "conv state")
+    _close(ring[1], ring_r[1], 5e-3, 2e-2, "ring")
+    _close(ring[0], ring_r[0], 1e-6, 0, "conv ring")
+
+
+def test_gdn_decode_batch_invariant(C):
+    mixed, slots, conv, rec, args = _gdn_setup((16, 32, 128, 128), 6, 1, seed=30)
+    c1, r1 = conv.clone(), rec.clone()
+    full = C.gdn_decode(mixed, slots, c1, r1, *args)
+    c2, r2 = conv.clone(), rec.clone()
+    one = C.gdn_decode(mixed[2:3].contiguous(), slots[2:3].contiguous(), c2, r2, *args)
+    assert torch.equal(one, full[2:3])
+    assert torch.equal(r2[slots[2].item()], r1[slots[2].item()])
+
+
+@pytest.mark.parametrize("n_q,n_kv,D,rot,B,G", [(4, 1, 32, 8, 3, 1), (16, 2, 256, 64, 4, 1), (16, 2, 256, 64, 2, 3)])
+def test_attention_decode(C, O, n_q, n_kv, D, rot, B, G):
+    g = torch.Generator(device="cuda").manual_seed(40)
+    pages, maxp = 40, 8
+    kv = (torch.randn(pages, 2, n_kv, 64, D, device="cuda", generator=g)).to(torch.bfloat16)
+    lens = torch.tensor([5, 64, 130, 301][:B], device="cuda")  # tokens already in the cache
+    tables = torch.zeros(B, maxp, dtype=torch.int32, device="cuda")
+    perm = torch.randperm(pages - 1, device="cuda", generator=g) + 1
+    for b in range(B):
+        tables[b] = perm[b * maxp:(b + 1) * maxp]
+    qkv = _bf(B * G, n_q * 2 * D + 2 * n_kv * D, seed=41)
+    positions = (lens[:, None] + torch.arange(G, device="cuda")[None]).reshape(-1)
+    seq = torch.repeat_interleave(torch.arange(B, device="cuda", dtype=torch.int32), G)
+    qn, kn = _bf(D, scale=0.1, seed=42), _bf(D, scale=0.1, seed=43)
+    kv_ref = kv.float().clone()
+    ref = O.attention(qkv.float(), positions, seq, tables, kv_ref, qn.float(), kn.float(), n_q, n_kv, D, rot, 1e7,
+                      1e-6, G)
+    got = C.attention(qkv, positions, seq, tables, kv, qn, kn, n_q, n_kv, D, rot, 1e7, 1e-6, G)
+    C.check_errors(qkv.device)
+    _close(kv, kv_ref, 3e-2, 2e-2, "kv pages")
+    _close(got, ref, 3e-2, 3e-2, "attention out")
+
+
+def test_tiny_model_cuda_matches_fp32_oracle(C, O):
+    from b200serve.config import ModelConfig
+    from b200serve.models.checkpoint import random_weights
+    from b200serve.models.qwen36 import Model, PackedBatch
+
+    cfg = ModelConfig.tiny()
+    w32 = random_weights(cfg, seed=0, device="cuda", dtype=torch.float32, std=0.05)
+    w16 = w32.to(dtype=torch.bfloat16)
+    ref_m = Model(w16.to(dtype=torch.float32), 16, 4, ops=O)
+    got_m = Model(w16, 16, 4, ops=C)
+    toks = torch.randint(0, cfg.vocab_size, (90,)).tolist()
+    tables = torch.tensor([[1, 2, 3], [4, 5, 6]], dtype=torch.int32)
+    outs = []
+    for m in (ref_m, got_m):
+        hs = []
+        b = PackedBatch.prefill([toks[:70], toks[10:50]], [1, 2], [0, 0], tables, "cuda")
+        h = m.forward(b)
+        hs.append(m.logits(h)[[69, 109]])
+        for t in range(3):
+            b = PackedBatch.uniform([toks[70 + t], toks[50 + t]], [70 + t, 40 + t], [1, 2], tables, 1, "cuda")
+            hs.append(m.logits(m.forward(b)))
+        outs.append(torch.cat(hs).float())
+    C.check_errors(torch.device("cuda"))
+    ref, got = outs
+    cos = torch.nn.functional.cosine_similarity(ref, got, dim=-1)
+    assert cos.min().item() > 0.99, cos
