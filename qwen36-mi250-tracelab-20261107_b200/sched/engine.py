@@ -1,0 +1,428 @@
+"""Continuous-batching engine: admission, chunked packed prefill, batched decode, retirement.
+
+One thread owns the model and calls ``step()`` in a loop (the reference's ``Worker`` is the
+only thread that touches its model as well, ``engine/server.py:94-296``). Each iteration
+
+1. drains the submission queue and admits requests (prefix-cache claim, slot and page
+   allocation),
+2. runs at most one packed prefill pass: the next chunk-aligned span of every pending
+   request under a token budget (reference: ``PackedPrefill``, ``engine/generator.py:1127-1230``),
+3. runs one decode step for every running request (a CUDA graph per batch bucket on GPU),
+4. emits tokens, finishes requests and parks their state as session tails.
+
+Prefill rows and decode rows never share a forward pass, and span boundaries depend only on
+(prompt, cached start, chunk size); with batch-invariant kernels this makes every request's
+greedy tokens identical to the same request served alone.
+"""
+
+from __future__ import annotations
+
+import queue
+import time
+from typing import Iterable
+
+import torch
+
+from ..cache.pools import OutOfCapacity, PagePool, SlotPool
+from ..cache.prefix import PrefixCache
+from ..config import PAGE_SIZE, EngineConfig, ModelConfig
+from ..models.checkpoint import Weights
+from ..models.qwen36 import Model, PackedBatch
+from ..ops import torch_ops
+from .request import EngineError, Generation, Sampling, TokenEvent
+from .sampling import pick_token
+
+
+def _select_ops(device: torch.device):
+    if device.type == "cuda":
+        from ..ops import cuda_ops
+
+        cuda_ops.lib()  # raises when the kernel library is missing: never fall back silently on a GPU
+        return cuda_ops
+    return torch_ops
+
+
+class Engine:
+    def __init__(self, weights: Weights, cfg: EngineConfig | None = None, ops=None) -> None:
+        self.cfg = cfg or EngineConfig()
+        self.mcfg: ModelConfig = weights.config
+        self.device = weights.device
+        self.ops = ops or _select_ops(self.device)
+        c = self.cfg
+        self.chunk = max(PAGE_SIZE, (c.prefill_chunk_tokens + PAGE_SIZE - 1) // PAGE_SIZE * PAGE_SIZE)
+        self.max_model_len = c.max_model_len
+        self.max_pages_per_seq = (self.max_model_len + PAGE_SIZE - 1) // PAGE_SIZE + 1
+        n_slots = c.state_slots or (c.max_seqs * 2 + 2)
+        n_pages = c.kv_pages or self._auto_pages(weights, n_slots)
+        self.model = Model(weights, n_pages, n_slots, ops=self.ops)
+        self.pages = PagePool(n_pages)
+        self.slots = SlotPool(n_slots)
+        page_bytes = self.model.kv[:, 0].numel() * self.model.kv.element_size()
+        slot_bytes = self.mcfg.gdn_state_bytes()
+        self.cache = PrefixCache(
+            self.pages, self.slots, page_bytes, slot_bytes, c.prefix_cache_entries, c.prefix_cache_tokens,
+            int(c.prefix_cache_gib * (1 << 30)),
+        )
+        self.pages.on_pressure = self.cache.evict_one
+        self.slots.on_pressure = self.cache.evict_one
+        self.eos = set(self.mcfg.eos_token_ids)
+        self._inbox: "queue.SimpleQueue[Generation]" = queue.SimpleQueue()
+        self.waiting: list[Generation] = []
+        self.prefilling: list[Generation] = []
+        self.running: list[Generation] = []
+        self.stats = dict(
+            decode_steps=0, decoded_tokens=0, largest_batch=0, prefill_passes=0, prefill_segments=0,
+            prefilled_tokens=0, cached_tokens=0, requests=0, finished=0, failed=0,
+            mtp_verify_steps=0, mtp_proposed=0, mtp_accepted=0,
+        )
+        self._graphs = None
+        if self.device.type == "cuda" and c.cuda_graphs:
+            from .graphs import DecodeGraphs
+
+            self._graphs = DecodeGraphs(self)
+        self.spec = None
+        if c.mtp and weights.mtp is not None:
+            from ..spec.controller import SpecController
+
+            self.spec = SpecController(self)
+
+    # ------------------------------------------------------------------ sizing
+    def _auto_pages(self, weights: Weights, n_slots: int) -> int:
+        c, m = self.cfg, self.mcfg
+        per_page = m.kv_bytes_per_token(2 if weights.dtype != torch.float32 else 4) * PAGE_SIZE
+        if self.device.type != "cuda":
+            return min(4096, c.max_seqs * (min(self.max_model_len, 8192) // PAGE_SIZE + 2) + 64)
+        free, _total = torch.cuda.mem_get_info(self.device)
+        budget = free * c.kv_fraction - c.reserve_gb * (1 << 30) - n_slots * m.gdn_state_bytes()
+        pages = int(budget // per_page)
+        need = self.max_pages_per_seq + 8  # at least one full-length sequence (reference: model.py:492-521)
+        if pages < min(need, 64):
+            raise RuntimeError(f"not enough device memory for the KV pool ({pages} pages)")
+        return pages
+
+    # ------------------------------------------------------------------ public API
+    def submit(self, gen: Generation) -> Generation:
+        self._inbox.put(gen)
+        return gen
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.prefilling or self.running) or not self._inbox.empty()
+
+    def generate(self, prompts: Iterable[list[int]], sampling: Sampling | list[Sampling]) -> list[Generation]:
+        """Offline convenience: run the given prompts to completion and return their generations."""
+        prompts = list(prompts)
+        samplings = sampling if isinstance(sampling, list) else [sampling] * len(prompts)
+        gens = [self.submit(Generation(p, s)) for p, s in zip(prompts, samplings)]
+        while any(not g.done for g in gens):
+            self.step()
+        return gens
+
+    def validate(self, prompt: list[int], sampling: Sampling) -> None:
+        if not prompt:
+            raise EngineError("the prompt is empty")
+        if len(prompt) >= self.max_model_len:
+            raise EngineError(
+                f"the prompt has {len(prompt)} tokens; this model's context is {self.max_model_len} tokens"
+            )
+        if sampling.max_tokens is not None and len(prompt) + sampling.max_tokens > self.max_model_len:
+            raise EngineError(
+                f"prompt ({len(prompt)} tokens) plus max_tokens ({sampling.max_tokens}) exceeds the "
+                f"context of {self.max_model_len} tokens"
+            )
+        v = self.mcfg.vocab_size
+        if any((t < 0 or t >= v) for t in prompt):
+            raise EngineError(f"the prompt contains a token id outside [0, {v})")
+
+    # ------------------------------------------------------------------ admission
+    def _spans(self, start: int, end: int) -> list[tuple[int, int]]:
+        """Chunk-aligned spans covering ``[start, end)`` exactly once."""
+        spans, a = [], start
+        while a < end:
+            b = min(end, (a // self.chunk + 1) * self.chunk)
+            spans.append((a, b))
+            a = b
+        return spans
+
+    def _claim(self, gen: Generation) -> None:
+        """Give the request a state slot and any cached prefix (reference: ``_claim``, generator.py:932-973)."""
+        entry = self.cache.lookup(gen.prompt)
+        if entry is not None and entry.kind == "tail":
+            gen.slot, gen.pages, gen.computed = entry.slot, list(entry.pages), entry.length
+        elif entry is not None:
+            try:
+                gen.slot = self.slots.alloc()
+            except OutOfCapacity:
+                raise EngineError("all sequence slots are busy", 503, "service_unavailable") from None
+            self.model.copy_slot(entry.slot, gen.slot)
+            self.pages.incref(entry.pages)
+            gen.pages, gen.computed = list(entry.pages), entry.length
+        else:
+            try:
+                gen.slot = self.slots.alloc()
+            except OutOfCapacity:
+                raise EngineError("all sequence slots are busy", 503, "service_unavailable") from None
+            self.model.reset_slot(gen.slot)
+            gen.pages, gen.computed = [], 0
+        gen.cached_tokens = gen.computed
+        gen.mtp_computed = 0
+        L = len(gen.prompt)
+        gen.spans = self._spans(gen.computed, L)
+        boundary = (L - 1) // self.chunk * self.chunk
+        gen.snapshot_at = boundary if boundary > gen.computed else 0
+        if gen.sampling.max_tokens is None:
+            gen.sampling.max_tokens = self.max_model_len - L
+        if gen.sampling.seed is not None or not gen.sampling.greedy:
+            gen.rng = torch.Generator(device="cpu")
+            gen.rng.manual_seed(gen.sampling.seed if gen.sampling.seed is not None else gen.id * 7919 + int(time.time()))
+
+    def _admit(self) -> None:
+        while True:
+            try:
+                self.waiting.append(self._inbox.get_nowait())
+            except queue.Empty:
+                break
+        while self.waiting and len(self.prefilling) + len(self.running) < self.cfg.max_seqs:
+            gen = self.waiting.pop(0)
+            self.stats["requests"] += 1
+            if gen.cancelled.is_set():
+                self._finish(gen, "cancelled", retire=False)
+                continue
+            try:
+                self.validate(gen.prompt, gen.sampling)
+                if gen.sampling.max_tokens == 0:
+                    self._finish(gen, "length", retire=False)
+                    continue
+                self._claim(gen)
+            except EngineError as e:
+                self._fail(gen, e)
+                continue
+            self.stats["cached_tokens"] += gen.cached_tokens
+            self.prefilling.append(gen)
+
+    # ------------------------------------------------------------------ pages
+    def _ensure_pages(self, gen: Generation, upto_tokens: int) -> None:
+        need = (upto_tokens + PAGE_SIZE - 1) // PAGE_SIZE - len(gen.pages)
+        if need > 0:
+            gen.pages.extend(self.pages.alloc(need))
+
+    def _table(self, gens: list[Generation], width: int | None = None) -> torch.Tensor:
+        width = width or max(1, max(len(g.pages) for g in gens))
+        t = torch.zeros(len(gens), width, dtype=torch.int32)
+        for i, g in enumerate(gens):
+            if g.pages:
+                t[i, : len(g.pages)] = torch.tensor(g.pages, dtype=torch.int32)
+        return t
+
+    # ------------------------------------------------------------------ prefill
+    def _prefill_pass(self) -> bool:
+        budget = self.cfg.prefill_pack_tokens
+        picked: list[Generation] = []
+        for gen in list(self.prefilling):
+            if gen.cancelled.is_set():
+                self.prefilling.remove(gen)
+                self._finish(gen, "cancelled")
+                continue
+            a, b = gen.spans[0]
+            if picked and b - a > budget:
+                continue
+            try:
+                self._ensure_pages(gen, b)
+            except OutOfCapacity:
+                if not picked and not self.running:
+                    self.prefilling.remove(gen)
+                    self._fail(gen, EngineError("the KV cache is full", 503, "service_unavailable"))
+                continue
+            picked.append(gen)
+            budget -= b - a
+            if budget <= 0:
+                break
+        if not picked:
+            return False
+        spans = [g.spans[0] for g in picked]
+        batch = PackedBatch.prefill(
+            [g.prompt[a:b] for g, (a, b) in zip(picked, spans)], [g.slot for g in picked],
+            [a for a, _ in spans], self._table(picked), self.device,
+        )
+        try:
+            hidden = self.model.forward(batch)
+        except Exception as e:  # fail the packed requests only; the engine keeps serving
+            for g in picked:
+                self.prefilling.remove(g)
+                self._fail(g, EngineError(f"prefill failed: {e}", 500, "internal_error"))
+            return True
+        self.stats["prefill_passes"] += 1
+        self.stats["prefill_segments"] += len(picked)
+        self.stats["prefilled_tokens"] += sum(b - a for a, b in spans)
+        finished_rows, finished = [], []
+        for i, (g, (a, b)) in enumerate(zip(picked, spans)):
+            g.spans.pop(0)
+            g.computed = b
+            if g.snapshot_at and b == g.snapshot_at:
+                self._snapshot(g)
+            if not g.spans:
+                finished_rows.append(batch.seg_starts[i + 1] - 1)
+                finished.append(g)
+        if self.spec is not None:
+            self.spec.after_prefill(picked, spans, batch, hidden)
+        if finished:
+            rows = torch.tensor(finished_rows, device=self.device)
+            self._sample_and_emit(finished, hidden[rows])
+            for g in finished:
+                self.prefilling.remove(g)
+                if not g.done:
+                    self.running.append(g)
+            if self.spec is not None:
+                self.spec.first_drafts([g for g in finished if not g.done])
+        return True
+
+    def _snapshot(self, gen: Generation) -> None:
+        if self.cache.has_snapshot(gen.prompt, gen.computed):
+            return
+        try:
+            slot = self.slots.alloc()
+        except OutOfCapacity:
+            return
+        self.model.copy_slot(gen.slot, slot)
+        if not self.cache.store_snapshot(gen.prompt, gen.computed, gen.pages, slot):
+            self.slots.release(slot)
+
+    # ------------------------------------------------------------------ decode
+    def _decode_step(self) -> bool:
+        for gen in list(self.running):
+            if gen.cancelled.is_set():
+                self.running.remove(gen)
+                self._finish(gen, "cancelled")
+        if not self.running:
+            return False
+        if self.spec is not None and self.spec.step(self.running):
+            self._reap()
+            return True
+        batch_gens = []
+        for gen in list(self.running):
+            try:
+                self._ensure_pages(gen, gen.computed + 1)
+                batch_gens.append(gen)
+            except OutOfCapacity:
+                self.running.remove(gen)
+                self._fail(gen, EngineError("the KV cache is full", 503, "service_unavailable"))
+        if not batch_gens:
+            return False
+        B = len(batch_gens)
+        tokens = [g.next_token for g in batch_gens]
+        positions = [g.computed for g in batch_gens]
+        need_logits = any(self._needs_logits(g) for g in batch_gens)
+        try:
+            if self._graphs is not None and self._graphs.usable(batch_gens):
+                hidden, greedy = self._graphs.run(batch_gens, tokens, positions)
+            else:
+                batch = PackedBatch.uniform(tokens, positions, [g.slot for g in batch_gens], self._table(batch_gens), 1, self.device)
+                hidden = self.model.forward(batch)
+                greedy = None
+        except Exception as e:
+            for g in batch_gens:
+                self.running.remove(g)
+                self._fail(g, EngineError(f"decode failed: {e}", 500, "internal_error"))
+            return True
+        for g in batch_gens:
+            g.computed += 1
+        self.stats["decode_steps"] += 1
+        self.stats["decoded_tokens"] += B
+        self.stats["largest_batch"] = max(self.stats["largest_batch"], B)
+        self._sample_and_emit(batch_gens, hidden, greedy if not need_logits else None)
+        self._reap()
+        return True
+
+    def _reap(self) -> None:
+        self.running = [g for g in self.running if not g.done]
+
+    # ------------------------------------------------------------------ sampling / emission
+    def _needs_logits(self, g: Generation) -> bool:
+        s = g.sampling
+        return (not s.greedy) or (len(g.output) < s.min_tokens and bool(self.eos))
+
+    def _sample_and_emit(self, gens: list[Generation], hidden: torch.Tensor, greedy: torch.Tensor | None = None) -> None:
+        """Pick the next token of each request from its hidden row, emit it and finish on EOS / length."""
+        need = [i for i, g in enumerate(gens) if self._needs_logits(g)]
+        picks: list[int]
+        if not need:
+            if greedy is None:
+                greedy = self.model.greedy(hidden)
+            picks = greedy[: len(gens)].tolist()
+        else:
+            if greedy is None:
+                greedy = self.model.greedy(hidden)
+            picks = greedy[: len(gens)].tolist()
+            logits = self.model.logits(hidden[torch.tensor(need, device=self.device)]).float().cpu()
+            for j, i in enumerate(need):
+                g = gens[i]
+                mask_eos = len(g.output) < g.sampling.min_tokens
+                picks[i] = pick_token(logits[j], g.sampling, g.rng, self.eos if mask_eos else None)
+        for g, tok in zip(gens, picks):
+            self._accept_token(g, int(tok))
+
+    def _accept_token(self, g: Generation, tok: int) -> None:
+        """Book one sampled token: EOS ends the request without emitting it (unless ignored)."""
+        if g.done:
+            return
+        if tok in self.eos and not g.sampling.ignore_eos:
+            self._finish(g, "stop")
+            return
+        g.output.append(tok)
+        g.next_token = tok
+        if len(g.output) >= g.sampling.max_tokens:
+            g.emit(TokenEvent(tok, "length"))
+            self._finish(g, "length", emit=False)
+        else:
+            g.emit(TokenEvent(tok, None))
+
+    # ------------------------------------------------------------------ retirement
+    def _finish(self, g: Generation, reason: str, retire: bool = True, emit: bool = True) -> None:
+        if g.done:
+            return
+        g.finish_reason = reason
+        self.stats["finished"] += 1
+        if retire and g.slot:
+            if self.spec is not None:
+                self.spec.settle(g)
+            covered = g.tokens[: g.computed]
+            if g.computed > 0 and len(covered) == g.computed:
+                keep = (g.computed + PAGE_SIZE - 1) // PAGE_SIZE
+                if len(g.pages) > keep:
+                    self.pages.release(g.pages[keep:])
+                    g.pages = g.pages[:keep]
+                self.cache.store_tail(covered, g.pages, g.slot)
+            else:
+                self.pages.release(g.pages)
+                self.slots.release(g.slot)
+            g.slot, g.pages = 0, []
+        if emit:
+            g.emit(TokenEvent(None, reason))
+
+    def _fail(self, g: Generation, err: EngineError) -> None:
+        self.stats["failed"] += 1
+        if g.slot:
+            self.pages.release(g.pages)
+            self.slots.release(g.slot)
+            g.slot, g.pages = 0, []
+        g.finish_reason = "error"
+        g.emit(TokenEvent(None, "error", err))
+
+    # ------------------------------------------------------------------ loop
+    def step(self) -> bool:
+        """One scheduler iteration. Returns False when there was nothing to do."""
+        self._admit()
+        did = self._prefill_pass()
+        did = self._decode_step() or did
+        return did
+
+    def health(self) -> dict:
+        out = dict(self.stats)
+        cs = self.cache.stats
+        out.update(
+            prefix_cache_entries=len(self.cache), prefix_cache_bytes=self.cache.bytes,
+            prefix_cache_tail_hits=cs.tail_hits, prefix_cache_snapshot_hits=cs.snapshot_hits,
+            prefix_cache_evictions=cs.evictions, kv_pages_free=self.pages.free, kv_pages_total=self.pages.num_pages - 1,
+            slots_free=self.slots.free, running=len(self.running), prefilling=len(self.prefilling),
+            waiting=len(self.waiting),
+        )
+        return out
