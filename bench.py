@@ -1,0 +1,248 @@
+"""Headline benchmark: decode throughput of Qwen3.6-35B-A3B (bf16, random init) on N B200s.
+
+    python bench.py --gpus N --steps K --warmup W          (N > 1: launched by torch.distributed.run)
+
+Config: every GPU serves ``--batch`` concurrent requests with ``--prompt-len`` uniform-random
+prompt tokens (greedy, ignore_eos); a *step* is one decode iteration of the engine, i.e. one
+new token for every running request. ``value`` is the whole-job output tokens/s over exactly K
+steps timed on the device with CUDA events (max over ranks). ``e2e`` is the same K steps driven
+through the public engine API (``Engine.submit`` / ``Engine.step``): each step copies its inputs
+from pinned host memory to the device and reads the sampled tokens back.
+
+With ``--impl reference`` the unmodified reference under ``baseline/_ref`` is run for the same
+metric, or a one-line reason is printed when it cannot run in this image.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+BASELINE_TOK_S = None  # the reference publishes no number for this hardware
+
+
+def parse() -> argparse.Namespace:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=128, help="concurrent requests per GPU")
+    ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp_ep"])
+    ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (result marked invalid)")
+    ap.add_argument("--mtp", type=int, default=0, help="MTP draft depth (0 = plain decode)")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def reference_arm(args: argparse.Namespace) -> None:
+    import importlib.util
+
+    out = {"impl": "reference"}
+    ref = ROOT / "baseline" / "_ref" / "engine"
+    if not ref.exists():
+        out["unavailable"] = ("reference is not pip-installable (no setup.py/pyproject.toml) and baseline/_ref/engine "
+                              "is absent on this box")
+    elif importlib.util.find_spec("accelerate") is None:
+        out["unavailable"] = ("reference Generator.load calls from_pretrained(device_map='auto') on CUDA "
+                              "(engine/generator.py:651-663), which needs the accelerate package: not in this image "
+                              "nor in /opt/wheelhouse")
+    else:
+        out["unavailable"] = "reference run path not exercised in this image (accelerate appeared; rerun needed)"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps(out), flush=True)
+
+
+def main() -> None:
+    args = parse()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    import torch
+    import torch.distributed as dist
+
+    from b200serve.config import EngineConfig, ModelConfig
+    from b200serve.models.checkpoint import random_weights
+    from b200serve.ops import cuda_ops
+    from b200serve.sched.engine import Engine
+    from b200serve.sched.request import Generation, Sampling
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, P, K, W = args.batch, args.prompt_len, args.steps, args.warmup
+
+    mcfg = ModelConfig.qwen36_35b_a3b() if not args.layers else ModelConfig(num_hidden_layers=args.layers)
+    weights = random_weights(mcfg, seed=1234 + rank, device=dev, dtype=torch.bfloat16)
+    total_out = K + max(W, 3) + 64 + (B * P) // 4096  # room for the tokens decoded while later prompts prefill
+    ecfg = EngineConfig(
+        max_model_len=P + 2 * total_out + 64, max_seqs=B, state_slots=B + 2, prefill_chunk_tokens=2048,
+        prefill_pack_tokens=8192, kv_pages=B * ((P + 2 * total_out) // 64 + 2) + 2, mtp=bool(args.mtp),
+        spec_k=args.mtp, decode_buckets=(B,),
+    )
+    engine = Engine(weights, ecfg)
+
+    def run_phase(timed_steps: int, warm: int, e2e: bool):
+        """Prefill B fresh requests, run `warm` untimed decode steps, then time `timed_steps` steps."""
+        engine.cache.clear()
+        g = torch.Generator().manual_seed(99 + rank + (1000 if e2e else 0))
+        gens = [
+            engine.submit(Generation(torch.randint(0, mcfg.vocab_size, (P,), generator=g).tolist(),
+                                     Sampling(max_tokens=total_out, ignore_eos=True)))
+            for _ in range(B)
+        ]
+        while engine.prefilling or engine.waiting or not engine._inbox.empty():
+            engine.step()  # prefill passes (each also advances already-running requests by one token)
+        if not e2e:  # the device-resident loop runs ahead of the host: give every request its pages now
+            for x in gens:
+                engine._ensure_pages(x, x.computed + timed_steps + 2)
+        for _ in range(warm):
+            engine.step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        produced0 = sum(len(x.output) for x in gens)
+        t0 = time.perf_counter()
+        start.record()
+        if e2e:
+            for _ in range(timed_steps):
+                engine.step()
+        else:
+            bucket = engine._graphs.buckets[B]
+            for _ in range(timed_steps):
+                bucket.graph.replay()
+                bucket.tokens.copy_(bucket.picks)  # feed the picks back on the device
+                bucket.positions.add_(1)
+        end.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end)
+        produced = sum(len(x.output) for x in gens) - produced0 if e2e else timed_steps * B
+        for x in gens:
+            x.cancelled.set()
+        engine.step()
+        return ms, wall, produced
+
+    sampler = ClockSampler(local)
+    # e2e first (through the public API), then the device-resident kernel loop on the same engine
+    e2e_ms, e2e_wall, e2e_tokens = run_phase(K, W, e2e=True)
+    launches_per_step = None
+    sampler.start()
+    ms, _wall, tokens = run_phase(K, max(W, 3), e2e=False)
+    clocks = sampler.stop()
+    cuda_ops.check_errors(dev)
+
+    def reduce_max(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms = reduce_max(ms)
+    e2e_s = reduce_max(max(e2e_wall, e2e_ms / 1e3))
+    value = world * tokens / (ms / 1e3)
+    e2e_value = world * e2e_tokens / e2e_s
+    bucket = engine._graphs.buckets[B]
+    h2d = (bucket.h_tokens.numel() * 8 + bucket.h_positions.numel() * 8 + bucket.h_slots.numel() * 4
+           + bucket.h_tables.numel() * 4)
+    d2h = bucket.h_picks.numel() * 8
+    n_gdn, n_attn = len(mcfg.gdn_layers), len(mcfg.attention_layers)
+    # kernels per decode step: 2 norms + 2 projections + router + 7 MoE kernels per layer, 2 (GDN) or 3 (attention)
+    # mixer kernels, embedding, final norm, LM head + argmax reduce
+    launches_per_step = (n_gdn + n_attn) * 12 + n_gdn * 2 + n_attn * 3 + 4
+    if rank == 0:
+        line = {
+            "metric": "output tok/s (whole box, max over ranks), decode", "value": round(value, 1), "unit": "tok/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None if BASELINE_TOK_S is None else value / BASELINE_TOK_S,
+            "dtype": "bf16", "data": "synthetic (uniform-random prompt tokens, random-init weights)",
+            "impl": "ours",
+            "config": {
+                "model": "Qwen3.6-35B-A3B" + (f"[{args.layers} layers: INVALID]" if args.layers else ""),
+                "global_batch": B * world, "seq_len": P, "parallelism": f"{args.parallelism}{world}",
+                "batch_per_gpu": B, "l2": "working set per step (weights + KV + GDN state) far exceeds the 126 MB L2",
+                "mtp_depth": args.mtp,
+            },
+            "clocks": clocks,
+            "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3 / K, 4)},
+            "gpu_launches": launches_per_step * K,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,55 @@
+"""The engine on the CUDA kernel path: batching must not change a request's greedy tokens."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(max_seqs=8, graphs=True):
+    from b200serve.config import EngineConfig, ModelConfig
+    from b200serve.models.checkpoint import random_weights
+    from b200serve.sched.engine import Engine
+
+    cfg = ModelConfig.tiny()
+    w = random_weights(cfg, seed=0, device="cuda", dtype=torch.bfloat16, std=0.05, lm_head_std=0.5)
+    ecfg = EngineConfig(max_model_len=1024, prefill_chunk_tokens=64, max_seqs=max_seqs, mtp=False, kv_pages=256,
+                        cuda_graphs=graphs, decode_buckets=(1, 4, 8))
+    return Engine(w, ecfg)
+
+
+def _prompts(n, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(3, 1024, (int(torch.randint(16, 200, (1,), generator=g)),), generator=g).tolist() for _ in range(n)]
+
+
+def test_gpu_batched_equals_solo_with_graphs():
+    from b200serve.ops import cuda_ops
+    from b200serve.sched.request import Sampling
+
+    prompts = _prompts(8)
+    s = Sampling(max_tokens=24, ignore_eos=True)
+    eng = _mk()
+    batched = [g.output for g in eng.generate(prompts, s)]
+    assert eng._graphs is not None and eng._graphs.buckets and not eng._graphs.errors
+    assert all(len(o) == 24 for o in batched)
+    solo_eng = _mk()
+    for p, out in zip(prompts[:3], batched[:3]):
+        solo_eng.cache.clear()
+        assert solo_eng.generate([p], s)[0].output == out
+    eager = _mk(graphs=False)
+    assert [g.output for g in eager.generate(prompts[:3], s)] == batched[:3]
+    cuda_ops.check_errors(torch.device("cuda"))
+
+
+def test_gpu_session_tail_reuse_matches_cold():
+    from b200serve.sched.request import Sampling
+
+    eng = _mk()
+    p = _prompts(1, seed=3)[0]
+    s = Sampling(max_tokens=9, ignore_eos=True)
+    a = eng.generate([p], s)[0]
+    nxt = p + a.output + [5, 6, 7]
+    c = eng.generate([nxt], s)[0]
+    assert c.cached_tokens >= len(p)
+    assert len(c.output) == 9
