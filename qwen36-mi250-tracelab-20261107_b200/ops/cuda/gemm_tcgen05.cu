@@ -354,3 +354,50 @@ extern "C" int b200_argmax_finish(const float* part_max, const int* part_idx, in
   argmax_finish_kernel<<<T, 256, 0, st>>>(part_max, part_idx, n_tiles, T, out, out_val);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// ------------------------------------------------------------------ allocation-free greedy head
+// See b200serve_noalloc.h. The per-tile (max, index) partials of the LM-head argmax live in a
+// fixed device array instead of caller-provided workspace.
+#include <stdio.h>
+
+#include "b200serve_noalloc.h"
+
+namespace {
+constexpr size_t NOALLOC_PART_ELEMS = static_cast<size_t>(B200_NOALLOC_MAX_ROWS) * B200_NOALLOC_MAX_TILES;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_PART_ELEMS * (sizeof(float) + sizeof(int))];
+constexpr int NOALLOC_MAX_DEVICES = 64;
+void* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+}  // namespace
+
+extern "C" int b200_lm_head_argmax_noalloc(const void* X, const void* W, int64_t* out_idx, float* out_val, int T, int V,
+                                           int K, int ldx, int ldw, int* err, cudaStream_t st) {
+  if (T <= 0) return 0;
+  const int n_tiles = (V + BM - 1) / BM;
+  if (T > B200_NOALLOC_MAX_ROWS || n_tiles > B200_NOALLOC_MAX_TILES) {
+    fprintf(stderr,
+            "b200_lm_head_argmax_noalloc: %d rows x %d vocabulary entries exceed the built-in scratch "
+            "(at most %d rows and %d entries)\n",
+            T, V, B200_NOALLOC_MAX_ROWS, B200_NOALLOC_MAX_TILES * BM);
+    return B200_NOALLOC_TOO_LARGE;
+  }
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return B200_NOALLOC_BAD_DEVICE;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // The array's name is only a host-side handle; the device address of this device's copy has to be
+    // asked for, once, with the device current. Not a stream operation: do the first call outside capture.
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return B200_NOALLOC_NO_SYMBOL;
+    g_noalloc_ptr[dev] = p;
+  }
+  float* part_max = static_cast<float*>(g_noalloc_ptr[dev]);
+  int* part_idx = reinterpret_cast<int*>(part_max + NOALLOC_PART_ELEMS);
+  const int bt = b200_pick_bt(T);
+  CUtensorMap tw, tx;
+  if (make_map(&tw, W, K, V, 0, ldw, 0, BM)) return -1;
+  if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
+  GemmParams p{V, K, T, 0, nullptr, nullptr, nullptr, 0, part_max, part_idx, err};
+  const int rc = dispatch_bt<EPI_ARGMAX, false>(bt, tw, tx, p, (T + bt - 1) / bt, st);
+  if (rc) return rc;
+  argmax_finish_kernel<<<T, 256, 0, st>>>(part_max, part_idx, n_tiles, T, out_idx, out_val);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
