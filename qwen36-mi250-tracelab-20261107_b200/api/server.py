@@ -1,0 +1,385 @@
+"""OpenAI-compatible HTTP server: ``/health``, ``/v1/models``, ``/v1/completions``,
+``/v1/chat/completions`` (streaming over SSE or not).
+
+Threads: one engine worker owns the model and runs ``Engine.step()``; every HTTP connection has
+its own handler thread that parses, tokenises, then turns the request's token events into text
+(incremental detokenisation, stop strings, reasoning/content split) and writes the response. The
+port opens only after the weights are loaded, so ``/health`` 200 means ready (reference:
+``engine/server.py:1-21, 488-620, 623-729``; there, detokenisation runs on the engine thread).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import queue
+import sys
+import threading
+import time
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+from typing import Any, Iterator
+
+from ..config import EngineConfig
+from ..obs import looptimers, reqstamps
+from ..sched.request import EngineError, Generation, TokenEvent
+from . import protocol
+from .protocol import ChatRequest, CompletionRequest, Envelope, RequestError, Usage
+from .text import Detokenizer, StopMatcher
+
+
+class EngineWorker(threading.Thread):
+    """The only thread that touches the model."""
+
+    def __init__(self, engine) -> None:
+        super().__init__(name="engine-worker", daemon=True)
+        self.engine = engine
+        self.wake = threading.Event()
+        self.stopping = False
+        self.fatal: BaseException | None = None
+
+    def submit(self, gen: Generation) -> None:
+        self.engine.submit(gen)
+        self.wake.set()
+
+    def run(self) -> None:
+        eng = self.engine
+        while not self.stopping:
+            try:
+                looptimers.begin()
+                busy = eng.step()
+                looptimers.end(len(eng.running))
+            except BaseException as e:  # noqa: BLE001 - keep the failure visible on /health
+                self.fatal = e
+                import traceback
+
+                traceback.print_exc()
+                time.sleep(0.05)
+                continue
+            if not busy and not eng.has_work():
+                self.wake.wait(timeout=0.05)
+                self.wake.clear()
+
+    def stop(self) -> None:
+        self.stopping = True
+        self.wake.set()
+
+
+class _TextStream:
+    """Token events -> (reasoning delta, content delta), with stop strings applied to content."""
+
+    def __init__(self, codec, stops: list[str], thinking: bool) -> None:
+        self.codec = codec
+        self.in_reasoning = thinking
+        self.detok = Detokenizer(codec.tok)
+        self.matcher = StopMatcher(stops)
+        self.content: list[str] = []
+        self.reasoning: list[str] = []
+
+    @property
+    def stopped(self) -> bool:
+        return self.matcher.stopped
+
+    def push(self, token: int) -> tuple[str, str]:
+        if self.in_reasoning and token == self.codec.think_end_id:
+            tail = self.detok.flush()
+            self.reasoning.append(tail)
+            self.in_reasoning = False
+            self.detok = Detokenizer(self.codec.tok)
+            return tail, ""
+        text = self.detok.push(token)
+        if self.in_reasoning:
+            self.reasoning.append(text)
+            return text, ""
+        out = self.matcher.push(text)
+        self.content.append(out)
+        return "", out
+
+    def flush(self) -> tuple[str, str]:
+        tail = self.detok.flush()
+        if self.in_reasoning:
+            self.reasoning.append(tail)
+            return tail, ""
+        out = self.matcher.push(tail) + self.matcher.flush()
+        self.content.append(out)
+        return "", out
+
+
+class Service:
+    """Everything the handlers need: engine worker, tokenizer, served model name."""
+
+    def __init__(self, engine, codec, model_name: str) -> None:
+        self.engine = engine
+        self.codec = codec
+        self.model_name = model_name
+        self.worker = EngineWorker(engine)
+        self.worker.start()
+
+    # ------------------------------------------------------------------ request -> events
+    def _events(self, prompt: list[int], sampling) -> tuple[Generation, "queue.Queue[TokenEvent]"]:
+        q: "queue.Queue[TokenEvent]" = queue.Queue()
+        gen = Generation(prompt, sampling, on_event=lambda g, e: q.put(e))
+        self.worker.submit(gen)
+        return gen, q
+
+    def run(self, request: CompletionRequest | ChatRequest, prompt: list[int]) -> Iterator[dict[str, Any]]:
+        """Yield response objects: chunks (and an optional usage chunk) when streaming, else one body.
+
+        Raises ``RequestError`` before the first yield when the engine refuses the request.
+        """
+        chat = isinstance(request, ChatRequest)
+        gen, q = self._events(prompt, request.sampling)
+        env = Envelope(self.model_name, "chat.completion" if chat else "text_completion")
+        text = _TextStream(self.codec, request.sampling.stop, chat and request.thinking)
+        usage = Usage(len(prompt))
+        ids: list[int] = []
+        finish = "length"
+        first = True
+        try:
+            while True:
+                ev = q.get()
+                if ev.error is not None:
+                    raise RequestError(str(ev.error), ev.error.status)
+                if first:
+                    first = False
+                    usage.cached_tokens = gen.cached_tokens
+                    if request.stream and chat:
+                        yield protocol.chat_chunk(env, {"role": "assistant", "content": ""}, None, None,
+                                                  request.return_token_ids)
+                reasoning = content = ""
+                if ev.token is not None:
+                    ids.append(ev.token)
+                    usage.completion_tokens += 1
+                    reasoning, content = text.push(ev.token)
+                done = ev.finish_reason
+                if text.stopped:
+                    done = "stop"
+                    gen.cancelled.set()
+                    self.worker.wake.set()
+                elif done is not None:
+                    r2, c2 = text.flush()
+                    reasoning, content = reasoning + r2, content + c2
+                    if text.stopped:
+                        done = "stop"
+                if done == "cancelled":
+                    done = "stop"
+                if request.stream:
+                    if chat:
+                        delta: dict[str, Any] = {"content": content}
+                        if reasoning:
+                            delta = {"reasoning_content": reasoning, **({"content": content} if content else {})}
+                        yield protocol.chat_chunk(env, delta, ev.token, done, request.return_token_ids)
+                    else:
+                        yield protocol.completion_chunk(env, content, ev.token, done, request.return_token_ids)
+                if done is not None:
+                    finish = done
+                    break
+            if request.stream:
+                if request.include_usage:
+                    yield protocol.usage_chunk(env, usage)
+            elif chat:
+                yield protocol.chat_response(env, "".join(text.content),
+                                             "".join(text.reasoning) if request.thinking else None, ids, finish,
+                                             usage, request.return_token_ids)
+            else:
+                yield protocol.completion_response(env, "".join(text.content), ids, finish, usage,
+                                                   request.return_token_ids)
+        finally:
+            if not gen.done:
+                gen.cancelled.set()  # client went away or the consumer stopped early
+                self.worker.wake.set()
+
+    def tokenize(self, request: CompletionRequest | ChatRequest) -> list[int]:
+        if isinstance(request, ChatRequest):
+            try:
+                return self.codec.encode_chat(request.messages, request.tools, **request.template_kwargs)
+            except RequestError:
+                raise
+            except Exception as e:  # jinja raises many kinds
+                raise RequestError(f"the chat template rejected the messages: {e}") from e
+        if isinstance(request.prompt, str):
+            return self.codec.encode(request.prompt)
+        return list(request.prompt)
+
+    def health(self) -> dict[str, Any]:
+        body: dict[str, Any] = {"status": "ok" if self.worker.fatal is None else "degraded"}
+        body.update(self.engine.health())
+        if self.codec is not None:
+            body.update(self.codec.encoder.stats)
+        if looptimers.ENABLED:
+            body["loop_timers"] = looptimers.summary()
+        if reqstamps.ENABLED:
+            body["request_stamps"] = reqstamps.summary()
+        return body
+
+
+class Handler(BaseHTTPRequestHandler):
+    protocol_version = "HTTP/1.1"
+    service: Service  # set on the server class
+
+    def log_message(self, fmt: str, *args: Any) -> None:  # quiet
+        return
+
+    # ------------------------------------------------------------------ helpers
+    def _json(self, status: int, body: dict[str, Any]) -> None:
+        data = json.dumps(body).encode()
+        self.send_response(status)
+        self.send_header("Content-Type", "application/json")
+        self.send_header("Content-Length", str(len(data)))
+        self.end_headers()
+        self.wfile.write(data)
+
+    def _error(self, message: str, status: int) -> None:
+        self._json(status, protocol.error_body(message, status))
+
+    # ------------------------------------------------------------------ routes
+    def do_GET(self) -> None:
+        svc = self.server.service  # type: ignore[attr-defined]
+        if self.path == "/health":
+            self._json(200, svc.health())
+        elif self.path == "/v1/models":
+            self._json(200, protocol.models_body(svc.model_name, svc.engine.max_model_len))
+        else:
+            self._error(f"no route {self.path}", 404)
+
+    def do_POST(self) -> None:
+        svc: Service = self.server.service  # type: ignore[attr-defined]
+        stamp = reqstamps.start(self.headers.get("X-Engine-Sent"))
+        try:
+            length = int(self.headers.get("Content-Length") or 0)
+            raw = self.rfile.read(length)
+            try:
+                body = json.loads(raw or b"{}")
+            except json.JSONDecodeError:
+                raise RequestError("the request body is not valid JSON") from None
+            if self.path == "/v1/completions":
+                request = protocol.parse_completion(body)
+            elif self.path == "/v1/chat/completions":
+                request = protocol.parse_chat(body)
+            else:
+                raise RequestError(f"no route {self.path}", 404)
+            if request.model is not None and request.model != svc.model_name:
+                raise RequestError(f"model {request.model!r} is not served here (serving {svc.model_name!r})", 404)
+            reqstamps.mark(stamp, "parsed")
+            prompt = svc.tokenize(request)
+            svc.engine.validate(prompt, request.sampling)
+            reqstamps.mark(stamp, "tokenized")
+            events = svc.run(request, prompt)
+            first = next(events)  # engine refusals surface here, before any header is sent
+        except RequestError as e:
+            self._error(str(e), e.status)
+            return
+        except EngineError as e:
+            self._error(str(e), e.status)
+            return
+        except StopIteration:
+            self._error("the request produced no response", 500)
+            return
+        except Exception as e:  # noqa: BLE001
+            self._error(f"internal error: {e}", 500)
+            return
+        reqstamps.mark(stamp, "first_event")
+        if not request.stream:
+            self._json(200, first)
+            reqstamps.finish(stamp)
+            return
+        try:
+            self.send_response(200)
+            self.send_header("Content-Type", "text/event-stream")
+            self.send_header("Cache-Control", "no-cache")
+            self.send_header("Connection", "close")
+            self.end_headers()
+            self.wfile.write(b"data: " + json.dumps(first).encode() + b"\n\n")
+            self.wfile.flush()
+            reqstamps.mark(stamp, "first_byte")
+            for ev in events:
+                self.wfile.write(b"data: " + json.dumps(ev).encode() + b"\n\n")
+                self.wfile.flush()
+            self.wfile.write(b"data: [DONE]\n\n")
+            self.wfile.flush()
+        except (BrokenPipeError, ConnectionResetError, OSError):
+            events.close()  # runs the generator's finally: cancels the generation
+        finally:
+            self.close_connection = True
+            reqstamps.finish(stamp)
+
+
+class Server(ThreadingHTTPServer):
+    daemon_threads = True
+    allow_reuse_address = True
+    request_queue_size = 256
+
+    def __init__(self, addr: tuple[str, int], service: Service) -> None:
+        super().__init__(addr, Handler)
+        self.service = service
+
+
+# --------------------------------------------------------------------------- process entry
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="b200serve", description="B200-native Qwen3.6-35B-A3B serving engine")
+    env = os.environ.get
+    ap.add_argument("--model", required=True, help="checkpoint directory (HF layout)")
+    ap.add_argument("--revision", default=None)
+    ap.add_argument("--served-model-name", default=None)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--max-model-len", type=int, default=262144)
+    ap.add_argument("--prefill-chunk-tokens", type=int, default=2048)
+    ap.add_argument("--prefix-cache-tokens", type=int, default=4194304)
+    ap.add_argument("--prefix-cache-entries", type=int, default=128)
+    ap.add_argument("--prefix-cache-gib", type=float, default=16.0)
+    ap.add_argument("--experts-implementation", default=None, help="accepted for compatibility; one implementation exists")
+    ap.add_argument("--replicas", type=int, default=int(env("ENGINE_REPLICAS", "0")) or None)
+    ap.add_argument("--gpus-per-replica", type=int, default=int(env("ENGINE_GPUS_PER_REPLICA", "0")) or None)
+    ap.add_argument("--replica-devices", default=env("ENGINE_REPLICA_DEVICES"))
+    ap.add_argument("--device", default=env("ENGINE_DEVICE", "auto"), choices=["auto", "cpu", "cuda"])
+    ap.add_argument("--max-seqs", type=int, default=int(env("ENGINE_SLOTS", "128")))
+    return ap
+
+
+def load_service(args: argparse.Namespace) -> Service:
+    import torch
+
+    from ..models.checkpoint import load_checkpoint
+    from ..sched.engine import Engine
+    from .tokenizer import TextCodec
+
+    use_cuda = args.device == "cuda" or (args.device == "auto" and torch.cuda.is_available())
+    device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
+    dtype = torch.bfloat16 if use_cuda else torch.float32
+    t0 = time.time()
+    weights = load_checkpoint(args.model, device=device, dtype=dtype)
+    cfg = EngineConfig.from_env(
+        model=args.model, max_model_len=args.max_model_len, prefill_chunk_tokens=args.prefill_chunk_tokens,
+        prefix_cache_tokens=args.prefix_cache_tokens, prefix_cache_entries=args.prefix_cache_entries,
+        prefix_cache_gib=args.prefix_cache_gib, max_seqs=args.max_seqs,
+    )
+    engine = Engine(weights, cfg)
+    codec = TextCodec(args.model)
+    name = args.served_model_name or args.model
+    print(f"engine: loaded {args.model} on {device} ({weights.nbytes() / 1e9:.2f} GB) in {time.time() - t0:.1f} s; "
+          f"kv_pages={engine.pages.num_pages} slots={engine.slots.num_slots} mtp={engine.spec is not None}", flush=True)
+    return Service(engine, codec, name)
+
+
+def main(argv: list[str] | None = None) -> None:
+    args = build_parser().parse_args(argv)
+    from ..router import router
+
+    layout = router.resolve_layout(args.replicas, args.gpus_per_replica, args.replica_devices)
+    if layout is not None and len(layout) > 1:
+        router.serve(sys.argv[1:] if argv is None else argv, args.host, args.port, layout)
+        return
+    service = load_service(args)
+    server = Server((args.host, args.port), service)
+    print(f"engine: serving {service.model_name} on http://{args.host}:{args.port}", flush=True)
+    try:
+        server.serve_forever()
+    except KeyboardInterrupt:
+        pass
+    finally:
+        service.worker.stop()
+
+
+if __name__ == "__main__":
+    main()
