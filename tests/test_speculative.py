@@ -1,0 +1,126 @@
+"""MTP speculative decoding on the CPU oracle path: outputs never change, states stay consistent."""
+
+import pytest
+import torch
+
+from b200serve.config import EngineConfig, ModelConfig
+from b200serve.models.checkpoint import random_weights
+from b200serve.sched.engine import Engine
+from b200serve.sched.request import Sampling
+from b200serve.spec.controller import DepthPolicy
+
+
+@pytest.fixture(scope="module")
+def weights():
+    cfg = ModelConfig.tiny()
+    cfg.eos_token_ids = [2]
+    return random_weights(cfg, seed=0, dtype=torch.float32, std=0.02, lm_head_std=0.5)
+
+
+def _engine(weights, mtp, k=0, kmax=3):
+    return Engine(weights, EngineConfig(max_model_len=1024, prefill_chunk_tokens=64, max_seqs=8, mtp=mtp, spec_k=k,
+                                        spec_kmax=kmax))
+
+
+def _prompts(n, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(3, 1024, (int(torch.randint(16, 150, (1,), generator=g)),), generator=g).tolist() for _ in range(n)]
+
+
+@pytest.fixture(scope="module")
+def plain(weights):
+    prompts = _prompts(4)
+    outs = [g.output for g in _engine(weights, False).generate(prompts, Sampling(max_tokens=20, ignore_eos=True))]
+    return prompts, outs
+
+
+@pytest.mark.parametrize("k", [1, 3])
+def test_served_outputs_with_mtp_equal_plain(weights, plain, k):
+    prompts, outs = plain
+    eng = _engine(weights, True, k=k)
+    got = [g.output for g in eng.generate(prompts, Sampling(max_tokens=20, ignore_eos=True))]
+    assert got == outs
+    assert eng.stats["mtp_verify_steps"] > 0 and eng.stats["mtp_proposed"] > 0
+
+
+@pytest.mark.parametrize("mode", ["right", "wrong", "half"])
+def test_forced_drafts_accept_or_reject_without_changing_outputs(weights, plain, mode):
+    prompts, outs = plain
+    truth = {tuple(p): o for p, o in zip(prompts, outs)}
+    eng = _engine(weights, True, k=3)
+
+    def override(g, k):
+        full = truth[tuple(g.prompt)]
+        nxt = full[len(g.output):len(g.output) + k]
+        if mode == "right":
+            return nxt
+        if mode == "wrong":
+            return [(t + 1) % 1000 + 3 for t in nxt]
+        return nxt[:1] + [(t + 1) % 1000 + 3 for t in nxt[1:]]
+
+    eng.spec.draft_override = override
+    gens = eng.generate(prompts, Sampling(max_tokens=20, ignore_eos=True))
+    assert [g.output for g in gens] == outs
+    st = eng.stats
+    if mode == "right":
+        assert st["mtp_accepted"] == st["mtp_proposed"] > 0
+        assert st["decode_steps"] < 4 * 20 / 2  # several tokens per step
+    elif mode == "wrong":
+        assert st["mtp_accepted"] == 0
+    else:
+        assert 0 < st["mtp_accepted"] < st["mtp_proposed"]
+    # the parked state after speculation continues exactly like a plain engine's
+    eng.spec.draft_override = None
+    nxt = prompts[0] + outs[0] + [7, 8, 9]
+    cont = eng.generate([nxt], Sampling(max_tokens=6, ignore_eos=True))[0]
+    ref = _engine(weights, False).generate([nxt], Sampling(max_tokens=6, ignore_eos=True))[0]
+    assert cont.cached_tokens >= len(prompts[0]) and cont.output == ref.output
+
+
+def test_eos_inside_an_accepted_run_stops_exactly_there(weights, plain):
+    prompts, outs = plain
+    truth = {tuple(p): o for p, o in zip(prompts, outs)}
+    eos_tok = outs[0][5]
+    eng = _engine(weights, True, k=3)
+    eng.eos = {eos_tok}
+    eng.spec.draft_override = lambda g, k: truth[tuple(g.prompt)][len(g.output):len(g.output) + k]
+    g = eng.generate([prompts[0]], Sampling(max_tokens=20))[0]
+    cut = outs[0].index(eos_tok)
+    assert g.finish_reason == "stop" and g.output == outs[0][:cut]
+    ref = _engine(weights, False)
+    ref.eos = {eos_tok}
+    r = ref.generate([prompts[0]], Sampling(max_tokens=20))[0]
+    assert r.output == g.output
+    # a follow-up that reuses the parked tail matches a cold engine
+    eng.spec.draft_override = None
+    nxt = prompts[0] + g.output + [eos_tok, 11, 12]
+    a = eng.generate([nxt], Sampling(max_tokens=5, ignore_eos=True))[0]
+    b = _engine(weights, False).generate([nxt], Sampling(max_tokens=5, ignore_eos=True))[0]
+    assert a.cached_tokens > 0 and a.output == b.output
+
+
+def test_sampling_rows_ride_along_without_drafts(weights):
+    eng = _engine(weights, True, k=2)
+    p = _prompts(2, seed=9)
+    s = [Sampling(max_tokens=10, ignore_eos=True), Sampling(max_tokens=10, temperature=0.7, seed=3, ignore_eos=True)]
+    a = eng.generate(p, s)
+    b = _engine(weights, False).generate(p, s)
+    assert a[0].output == b[0].output  # greedy row unchanged
+    assert len(a[1].output) == 10
+
+
+def test_depth_policy_host_logic():
+    pol = DepthPolicy(kmax=3)
+    pol.accept = [0.9, 0.9, 0.9]
+    assert pol.choose(1, 3) == 3
+    assert pol.choose(1, 1) == 1  # no more drafts than available
+    pol.accept = [0.05, 0.05, 0.05]
+    assert pol.choose(1, 3) == 0
+    pol.table = {(1, 0): 7.0, (1, 1): 7.1, (1, 3): 8.9, (8, 0): 10.0, (8, 1): 30.0, (8, 3): 60.0}
+    pol.accept = [0.6, 0.5, 0.4]
+    assert pol.choose(1, 3) >= 1 and pol.choose(8, 3) == 0
+    fixed = DepthPolicy(kmax=3, fixed=2)
+    assert fixed.choose(4, 3) == 2 and fixed.choose(4, 1) == 1 and fixed.choose(200, 3) == 0
+    before = list(pol.accept)
+    pol.observe(3, 1)  # draft 1 accepted, draft 2 rejected, draft 3 untested
+    assert pol.accept[0] > before[0] and pol.accept[1] < before[1] and pol.accept[2] == before[2]
