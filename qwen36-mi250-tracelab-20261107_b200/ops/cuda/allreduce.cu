@@ -1,0 +1,122 @@
+// One-shot all-reduce over NVLink peer memory for decode-sized activations, with the residual add
+// folded in: out = bf16(residual + sum_r partial_r), every rank pushing its partial into all
+// peers' receive slots and adding the R partials in rank order (reference: the in-graph
+// "LL" all-reduce, engine/fast/tp.py:121-184, which does the same between two ranks with the flag
+// packed into each data word; here a block-level release/acquire flag covers 16 KB of payload).
+//
+// A loopback mode (world == 1, or every pointer of the context naming this rank's own buffers)
+// exercises the whole protocol on a single GPU inside ONE kernel; ranks are never emulated as
+// separate launches that wait on one another.
+#include "comm.cuh"
+
+namespace b200 {
+
+constexpr int AR_THREADS = 256;
+constexpr int AR_ELEMS = 4096;  // floats per block
+
+template <typename TIn>
+__device__ __forceinline__ float to_f(TIn v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename TIn>
+__global__ void __launch_bounds__(AR_THREADS)
+allreduce_push_kernel(CommCtx c, const TIn* in, const bf16* residual, bf16* out, float* out_f32, size_t n) {
+  const int blk = blockIdx.x;
+  const size_t base = static_cast<size_t>(blk) * AR_ELEMS;
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    s_epoch = c.epoch[blk] + 1;
+    c.epoch[blk] = s_epoch;
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint32_t e = s_epoch;
+  // push my partial into every rank's slot [e & 1][my rank]
+  for (int i = threadIdx.x * 4; i < AR_ELEMS; i += AR_THREADS * 4) {
+    const size_t g = base + i;
+    if (g >= n) break;
+    float4 v;
+    v.x = to_f<TIn>(in[g]);
+    v.y = g + 1 < n ? to_f<TIn>(in[g + 1]) : 0.f;
+    v.z = g + 2 < n ? to_f<TIn>(in[g + 2]) : 0.f;
+    v.w = g + 3 < n ? to_f<TIn>(in[g + 3]) : 0.f;
+    for (int r = 0; r < c.world; ++r) *reinterpret_cast<float4*>(comm_slot(c, r, e, c.rank) + g) = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    __threadfence_system();
+    st_release_sys(c.flags[threadIdx.x] + static_cast<size_t>(c.rank) * c.max_blocks + blk, e);
+  }
+  if (threadIdx.x < c.world) {
+    if (!wait_flag(c.flags[c.rank] + static_cast<size_t>(threadIdx.x) * c.max_blocks + blk, e, c.err)) s_ok = 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;  // status word set; output left untouched
+  for (int i = threadIdx.x * 4; i < AR_ELEMS; i += AR_THREADS * 4) {
+    const size_t g = base + i;
+    if (g >= n) break;
+    float4 acc = *reinterpret_cast<const float4*>(comm_slot(c, c.rank, e, 0) + g);
+    for (int r = 1; r < c.world; ++r) {
+      const float4 v = *reinterpret_cast<const float4*>(comm_slot(c, c.rank, e, r) + g);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    float a[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (g + k >= n) break;
+      float v = a[k];
+      if (out_f32) out_f32[g + k] = v;
+      if (out) {
+        if (residual) v = __bfloat162float(__float2bfloat16(v)) + __bfloat162float(residual[g + k]);
+        out[g + k] = __float2bfloat16(v);
+      }
+    }
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// `n` elements (a multiple of 4, at most slot_elems); in_is_f32 selects the partial's dtype.
+// out (bf16, optional residual added) and/or out_f32 receive the sum.
+extern "C" int b200_allreduce_push(const CommCtx* ctx, const void* in, int in_is_f32, const void* residual, void* out,
+                                   float* out_f32, unsigned long long n, cudaStream_t st) {
+  if (n == 0) return 0;
+  if (n % 4 || n > ctx->slot_elems) return -7;
+  const int blocks = static_cast<int>((n + AR_ELEMS - 1) / AR_ELEMS);
+  if (blocks > ctx->max_blocks) return -7;
+  if (in_is_f32)
+    allreduce_push_kernel<float><<<blocks, AR_THREADS, 0, st>>>(*ctx, static_cast<const float*>(in),
+                                                               static_cast<const bf16*>(residual),
+                                                               static_cast<bf16*>(out), out_f32, n);
+  else
+    allreduce_push_kernel<bf16><<<blocks, AR_THREADS, 0, st>>>(*ctx, static_cast<const bf16*>(in),
+                                                              static_cast<const bf16*>(residual),
+                                                              static_cast<bf16*>(out), out_f32, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// ------------------------------------------------------------------ symmetric memory (CUDA IPC)
+extern "C" int b200_symm_alloc(void** ptr, unsigned long long bytes) {
+  if (cudaMalloc(ptr, bytes) != cudaSuccess) return -1;
+  return cudaMemset(*ptr, 0, bytes) == cudaSuccess ? 0 : -2;
+}
+extern "C" int b200_symm_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? 0 : -1; }
+extern "C" int b200_symm_export(void* ptr, void* handle64) {
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, ptr) != cudaSuccess) return -1;
+  memcpy(handle64, &h, sizeof(h));
+  return 0;
+}
+extern "C" int b200_symm_import(const void* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  return cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess ? 0 : -1;
+}
+extern "C" int b200_symm_close(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? 0 : -1; }
+extern "C" int b200_comm_ctx_size() { return static_cast<int>(sizeof(CommCtx)); }

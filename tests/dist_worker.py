@@ -1,0 +1,93 @@
+"""Multi-rank checks run as ``python -m torch.distributed.run --nproc-per-node N tests/dist_worker.py MODE``.
+
+Ranks are processes, one per GPU (NCCL) or CPU ranks over gloo when no GPU is visible.
+Each mode prints ``OK <mode>`` from rank 0 on success; any assertion makes the launcher fail.
+"""
+
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+
+def setup():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
+    if torch.cuda.is_available():
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        dist.init_process_group("nccl", device_id=dev)
+    else:
+        dev = torch.device("cpu")
+        dist.init_process_group("gloo")
+    return rank, world, dev
+
+
+def mode_allreduce(rank, world, dev):
+    from b200serve.ops import cuda_ops
+    from b200serve.parallel.symm import SymmComm
+
+    comm = SymmComm(dev, dist.group.WORLD, slot_elems=1 << 20, max_blocks=1024)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    for T, H in ((1, 2048), (16, 2048), (128, 2048), (7, 512)):
+        for dtype in (torch.float32, torch.bfloat16):
+            for rep in range(3):
+                x = torch.randn(T, H, device=dev, generator=g).to(dtype)
+                res = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+                got = comm.allreduce(x, res)
+                ref = x.float().clone()
+                dist.all_reduce(ref)
+                want = (ref.to(torch.bfloat16).float() + res.float()).to(torch.bfloat16)
+                assert torch.equal(got, want), (T, H, dtype, rep, (got.float() - want.float()).abs().max().item())
+                # every rank holds the same bits
+                gathered = [torch.empty_like(got) for _ in range(world)]
+                dist.all_gather(gathered, got)
+                assert all(torch.equal(gathered[0], t) for t in gathered)
+    # timing: 128 x 2048 (decode batch) and 4 x 2048, device-timed, max over ranks
+    for T in (4, 128):
+        x = torch.randn(T, 2048, device=dev).to(torch.bfloat16)
+        for _ in range(5):
+            comm.allreduce(x)
+        torch.cuda.synchronize(); dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(50):
+            comm.allreduce(x)
+        b.record(); torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / 50 * 1e3], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        y = x.clone()
+        for _ in range(5):
+            dist.all_reduce(y)
+        torch.cuda.synchronize(); dist.barrier()
+        a.record()
+        for _ in range(50):
+            dist.all_reduce(y)
+        b.record(); torch.cuda.synchronize()
+        t2 = torch.tensor([a.elapsed_time(b) / 50 * 1e3], device=dev)
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            print(f"allreduce {T}x2048 bf16 world={world}: push kernel {t.item():.1f} us, NCCL {t2.item():.1f} us", flush=True)
+    cuda_ops.check_errors(dev)
+    dist.barrier()
+    comm.close()
+
+
+MODES = {"allreduce": mode_allreduce}
+
+if __name__ == "__main__":
+    mode = sys.argv[1]
+    rank, world, dev = setup()
+    try:
+        from importlib import import_module
+
+        fn = MODES.get(mode) or getattr(import_module("dist_modes"), "mode_" + mode)
+        fn(rank, world, dev)
+        dist.barrier()
+        if rank == 0:
+            print(f"OK {mode}", flush=True)
+    finally:
+        dist.destroy_process_group()

@@ -1,0 +1,74 @@
+"""NVLink collective kernels on one GPU: loopback group, and a wait that runs out cleanly."""
+
+import ctypes
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_loopback_allreduce_adds_residual():
+    from b200serve.ops import cuda_ops
+    from b200serve.parallel.symm import SymmComm
+
+    dev = torch.device("cuda")
+    comm = SymmComm(dev, None, slot_elems=1 << 18, max_blocks=64)
+    for rep in range(3):  # epochs advance and parities alternate
+        x = torch.randn(33, 2048, device=dev).to(torch.bfloat16)
+        r = torch.randn(33, 2048, device=dev).to(torch.bfloat16)
+        assert torch.equal(comm.allreduce(x, r), x + r)
+        xf = torch.randn(5, 512, device=dev)
+        assert torch.equal(comm.allreduce(xf, out_dtype=torch.float32), xf)
+    cuda_ops.check_errors(dev)
+    comm.close()
+
+
+def test_absent_peer_times_out_with_a_status_and_leaves_the_context_usable():
+    """A two-rank context whose second rank never runs: the bounded wait gives up after about a
+    second, the kernel records ERR_WAIT_PEER and returns, and later launches still work."""
+    from b200serve.ops import cuda_ops
+    from b200serve.parallel import symm
+
+    dev = torch.device("cuda")
+    comm = symm.SymmComm(dev, None, slot_elems=1 << 16, max_blocks=16)
+    # pretend to be rank 0 of 2; "rank 1" is this GPU's own memory, and nothing ever sets its flags
+    big = symm.SymmComm(dev, None, slot_elems=1 << 16, max_blocks=16)
+    ctx = comm.ctx
+    ctx.world = 2
+    ctx.recv[1] = big._own["recv"]
+    ctx.flags[1] = big._own["flags"]
+    # the receive area of a 2-rank group is twice as large: use the second allocation for both
+    ctx.recv[0] = big._own["recv"]
+    x = torch.ones(4, 1024, device=dev, dtype=torch.bfloat16)
+    out = torch.full_like(x, 7.0)
+    rc = symm._lib().b200_allreduce_push(ctypes.byref(ctx), x.data_ptr(), 0, None, out.data_ptr(), None, x.numel(),
+                                         torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(cuda_ops.err_word(dev).item()) == 4
+    with pytest.raises(cuda_ops.KernelError):
+        cuda_ops.check_errors(dev)
+    assert (out == 7.0).all()  # untouched
+    ctx.world = 1
+    y = torch.randn(8, 256, device=dev).to(torch.bfloat16)
+    a = torch.empty_like(y)
+    assert cuda_ops.linear(y, torch.eye(256, device=dev, dtype=torch.bfloat16)).equal(y)
+    cuda_ops.check_errors(dev)
+    comm.close(); big.close()
+    del a
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_rank_allreduce_over_nvlink():
+    env = {"NCCL_NVLS_ENABLE": "0"}
+    import os
+
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29611", str(ROOT / "tests/dist_worker.py"),
+                        "allreduce"], capture_output=True, text=True, timeout=600, env={**os.environ, **env})
+    assert r.returncode == 0 and "OK allreduce" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
