@@ -51,6 +51,7 @@ class LayerWeights:
     shared_gate_up: torch.Tensor | None = None  # only when not merged
     shared_down: torch.Tensor | None = None
     shared_gate: torch.Tensor | None = None
+    expert_map: torch.Tensor | None = None  # expert parallelism: global expert id -> local slot or -1
 
     def tensors(self):
         for k, v in self.__dict__.items():
@@ -75,6 +76,8 @@ class Weights:
     final_norm: torch.Tensor
     layers: list[LayerWeights] = field(default_factory=list)
     mtp: MTPWeights | None = None
+    vocab_start: int = 0  # first vocabulary row held by this rank's lm_head shard
+    full_vocab: int = 0  # vocabulary size of the whole model when lm_head is a shard
 
     @property
     def device(self) -> torch.device:
@@ -108,12 +111,16 @@ class Weights:
             fn("norm", self.final_norm),
             [layer(lw) for lw in self.layers],
             mtp,
+            self.vocab_start,
+            self.full_vocab,
         )
 
     def to(self, device: torch.device | str | None = None, dtype: torch.dtype | None = None) -> "Weights":
         """Move/cast. ``A_log`` and ``dt_bias`` stay fp32 whatever ``dtype`` is."""
 
         def fn(name: str, t: torch.Tensor) -> torch.Tensor:
+            if not t.is_floating_point():
+                return t.to(device=device)
             dt = torch.float32 if name in ("A_log", "dt_bias") else dtype
             return t.to(device=device, dtype=dt)
 
@@ -259,9 +266,6 @@ def load_checkpoint(path: str | Path, device: str | torch.device = "cpu", dtype:
     cfg = ModelConfig.from_pretrained(path)
     src = _TensorSource(path)
 
-    def put(w: Weights | LayerWeights):
-        return w
-
     layers = []
     for i, kind in enumerate(cfg.layer_types):
         lw = _load_layer(src, f"layers.{i}.", kind, cfg)
@@ -292,7 +296,7 @@ def _layer_to(lw: LayerWeights, device, dtype) -> LayerWeights:
     kw = dict(lw.__dict__)
     for k, v in lw.tensors():
         dt = torch.float32 if k in ("A_log", "dt_bias") else dtype
-        kw[k] = v.to(device=device, dtype=dt)
+        kw[k] = v.to(device=device, dtype=dt) if v.is_floating_point() else v.to(device=device)
     return LayerWeights(**kw)
 
 

@@ -70,7 +70,10 @@ class PackedBatch:
 
 class Model:
     def __init__(self, weights: Weights, num_pages: int, state_slots: int, ops=None,
-                 kv_dtype: torch.dtype | None = None) -> None:
+                 kv_dtype: torch.dtype | None = None, tp=None) -> None:
+        """``weights`` may be one rank's shard (``parallel.tp.shard_weights``); then ``tp`` names the rank
+        group and every mixer / MoE output is summed across it."""
+        self.tp = tp
         self.w = weights
         self.cfg: ModelConfig = weights.config
         self.ops = ops or torch_ops
@@ -123,6 +126,10 @@ class Model:
     # ------------------------------------------------------------------ blocks
     def _moe(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
         cfg, ops = self.cfg, self.ops
+        if self.tp is not None:  # expert parallel: local experts only, partial sums meet in the all-reduce
+            part = ops.moe_block(x, lw.router, lw.w_gate_up, lw.w_down, cfg.num_experts, cfg.num_experts_per_tok,
+                                 True, expert_map=lw.expert_map, partial_f32=True)
+            return self.tp.comm.allreduce(part, None, x.dtype)
         out = ops.moe_block(x, lw.router, lw.w_gate_up, lw.w_down, cfg.num_experts, cfg.num_experts_per_tok,
                             lw.shared_merged)
         if lw.shared_merged:
@@ -140,7 +147,7 @@ class Model:
             cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rotary_dim, cfg.rope_theta,
             cfg.rms_norm_eps, batch.G, batch.seg_starts, batch.seg_pos0,
         )
-        return ops.linear(core, lw.out_proj)
+        return self._out_proj(core, lw.out_proj)
 
     def _gdn(self, lw, gi: int, h: torch.Tensor, batch: PackedBatch, ring) -> torch.Tensor:
         cfg, ops = self.cfg, self.ops
@@ -155,7 +162,13 @@ class Model:
         else:
             r = None if ring is None else (ring[0][gi], ring[1][gi])
             core = ops.gdn_decode(mixed, batch.slots, conv, rec, *args, G=batch.G, ring=r)
-        return ops.linear(core, lw.out_proj)
+        return self._out_proj(core, lw.out_proj)
+
+    def _out_proj(self, core: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """Mixer output projection; under tensor parallelism the GEMM's epilogue is the all-reduce."""
+        if self.tp is None:
+            return self.ops.linear(core, w)
+        return self.tp.comm.gemm_allreduce(self.ops, core, w)
 
     def _layer(self, lw, x, res, batch, kv_layer=None, gi=None, ring=None):
         cfg, ops = self.cfg, self.ops
@@ -182,11 +195,25 @@ class Model:
         return h
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
-        return self.ops.linear(hidden, self.w.lm_head, out_dtype=torch.float32)
+        out = self.ops.linear(hidden, self.w.lm_head, out_dtype=torch.float32)
+        if self.tp is None:
+            return out
+        import torch.distributed as dist
+
+        V = self.w.full_vocab
+        per = (V + self.tp.world - 1) // self.tp.world
+        pad = torch.full((out.shape[0], per), float("-inf"), dtype=out.dtype, device=out.device)
+        pad[:, : out.shape[1]] = out
+        parts = [torch.empty_like(pad) for _ in range(self.tp.world)]
+        dist.all_gather(parts, pad, group=self.tp.comm.group)
+        return torch.cat(parts, dim=1)[:, :V]
 
     def greedy(self, hidden: torch.Tensor) -> torch.Tensor:
         """Greedy next token of each row (LM head with fused argmax on the CUDA path)."""
-        return self.ops.lm_head_argmax(hidden, self.w.lm_head)
+        if self.tp is None:
+            return self.ops.lm_head_argmax(hidden, self.w.lm_head)
+        idx, val = self.ops.lm_head_argmax(hidden, self.w.lm_head, return_value=True)
+        return self.tp.comm.argmax(val, idx + self.w.vocab_start)
 
     def mtp_forward(self, hidden: torch.Tensor, next_tokens: torch.Tensor, batch: PackedBatch) -> torch.Tensor:
         """The MTP block over packed rows: row ``t`` pairs base hidden ``H[t]`` with token ``x[t+1]``.

@@ -75,7 +75,7 @@ __global__ void add_rmsnorm_kernel(const bf16* x, const bf16* res, const bf16* w
 constexpr int MAX_PER_LANE = 16;  // E <= 512
 
 __global__ void route_kernel(const float* logits, int ldl, int T, int E, int top_k, int shared, float* wts, int* idx,
-                             int* counts) {
+                             int* counts, const int* expert_map) {
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp_global >= T) return;
@@ -121,15 +121,18 @@ __global__ void route_kernel(const float* logits, int ldl, int T, int E, int top
   }
   if (lane < top_k) {
     const float wv = __bfloat162float(__float2bfloat16(sel_w / tot));
+    // expert parallelism: experts hosted elsewhere map to -1 and are skipped by the later stages
+    const int le = expert_map ? expert_map[sel_e] : sel_e;
     wts[static_cast<size_t>(warp_global) * P + lane] = wv;
-    idx[static_cast<size_t>(warp_global) * P + lane] = sel_e;
-    atomicAdd(&counts[sel_e], 1);
+    idx[static_cast<size_t>(warp_global) * P + lane] = le;
+    if (le >= 0) atomicAdd(&counts[le], 1);
   }
   if (shared && lane == 0) {
     const float sg = sigmoid_f(row[E]);
+    const int le = expert_map ? expert_map[E] : E;
     wts[static_cast<size_t>(warp_global) * P + top_k] = __bfloat162float(__float2bfloat16(sg));
-    idx[static_cast<size_t>(warp_global) * P + top_k] = E;
-    atomicAdd(&counts[E], 1);
+    idx[static_cast<size_t>(warp_global) * P + top_k] = le;
+    if (le >= 0) atomicAdd(&counts[le], 1);
   }
 }
 
@@ -169,33 +172,43 @@ __global__ void moe_scatter_kernel(const int* idx, int n_pairs, int Et, const in
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_pairs) return;
   const int e = idx[i];
-  if (e < 0 || e >= Et) { atomicCAS(err, 0, ERR_BAD_INDEX); return; }
+  if (e < 0) { inv[i] = -1; return; }  // pair served by another rank
+  if (e >= Et) { atomicCAS(err, 0, ERR_BAD_INDEX); inv[i] = -1; return; }
   const int pos = offsets[e] + atomicAdd(&cursors[e], 1);
   perm[pos] = i;
   inv[i] = pos;
 }
 
 // x_sorted[pos] = x[perm[pos] / P]
-__global__ void moe_gather_kernel(const bf16* x, const int* perm, int P, int H, bf16* xs) {
+__global__ void moe_gather_kernel(const bf16* x, const int* perm, const int* n_valid, int T, int P, int H, bf16* xs) {
   const int pos = blockIdx.x;
+  if (pos >= *n_valid) return;  // with expert parallelism only the locally served pairs are laid out
   const int t = perm[pos] / P;
+  if (t < 0 || t >= T) return;
   const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H);
   uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(pos) * H);
   for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
 }
 
 // out[t] = bf16( sum_j w[t,j] * pair_out[inv[t,j]] ) in pair order, fp32 accumulation, rounded once.
-__global__ void moe_combine_kernel(const bf16* pair_out, const float* wts, const int* inv, int P, int H, bf16* out) {
+__global__ void moe_combine_kernel(const bf16* pair_out, const float* wts, const int* inv, int P, int H, bf16* out,
+                                   float* out_f32) {
   const int t = blockIdx.x;
   for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int j = 0; j < P; ++j) {
       const float wv = wts[static_cast<size_t>(t) * P + j];
       const int pos = inv[static_cast<size_t>(t) * P + j];
+      if (pos < 0) continue;
       uint4 pv = *reinterpret_cast<const uint4*>(pair_out + static_cast<size_t>(pos) * H + i);
       const bf16* pe = reinterpret_cast<const bf16*>(&pv);
 #pragma unroll
       for (int k = 0; k < 8; ++k) acc[k] += wv * __bfloat162float(pe[k]);
+    }
+    if (out_f32) {  // a partial sum that still has to be added across ranks
+#pragma unroll
+      for (int k = 0; k < 8; ++k) out_f32[static_cast<size_t>(t) * H + i + k] = acc[k];
+      continue;
     }
     uint4 ov;
     bf16* oe = reinterpret_cast<bf16*>(&ov);
@@ -230,11 +243,11 @@ extern "C" int b200_add_rmsnorm(const void* x, const void* res, const void* w, v
 }
 
 extern "C" int b200_moe_route(const float* logits, int ldl, int T, int E, int top_k, int shared, float* wts, int* idx,
-                              int* counts, cudaStream_t st) {
+                              int* counts, int n_counts, const int* expert_map, cudaStream_t st) {
   if (T <= 0) return 0;
   if (E > 32 * MAX_PER_LANE || top_k > 32) return -7;
-  cudaMemsetAsync(counts, 0, sizeof(int) * (E + 1), st);
-  route_kernel<<<(T + 3) / 4, 128, 0, st>>>(logits, ldl, T, E, top_k, shared, wts, idx, counts);
+  cudaMemsetAsync(counts, 0, sizeof(int) * n_counts, st);
+  route_kernel<<<(T + 3) / 4, 128, 0, st>>>(logits, ldl, T, E, top_k, shared, wts, idx, counts, expert_map);
   CHECK_LAUNCH();
 }
 
@@ -246,15 +259,18 @@ extern "C" int b200_moe_plan(const int* counts, const int* idx, int n_pairs, int
   CHECK_LAUNCH();
 }
 
-extern "C" int b200_moe_gather(const void* x, const int* perm, int n_pairs, int P, int H, void* xs, cudaStream_t st) {
+extern "C" int b200_moe_gather(const void* x, const int* perm, const int* n_valid, int n_pairs, int T, int P, int H,
+                               void* xs, cudaStream_t st) {
   if (n_pairs <= 0) return 0;
-  moe_gather_kernel<<<n_pairs, 128, 0, st>>>(static_cast<const bf16*>(x), perm, P, H, static_cast<bf16*>(xs));
+  moe_gather_kernel<<<n_pairs, 128, 0, st>>>(static_cast<const bf16*>(x), perm, n_valid, T, P, H,
+                                             static_cast<bf16*>(xs));
   CHECK_LAUNCH();
 }
 
 extern "C" int b200_moe_combine(const void* pair_out, const float* wts, const int* inv, int T, int P, int H, void* out,
-                                cudaStream_t st) {
+                                float* out_f32, cudaStream_t st) {
   if (T <= 0) return 0;
-  moe_combine_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(pair_out), wts, inv, P, H, static_cast<bf16*>(out));
+  moe_combine_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(pair_out), wts, inv, P, H, static_cast<bf16*>(out),
+                                        out_f32);
   CHECK_LAUNCH();
 }

@@ -19,7 +19,7 @@
 // names (expert, first row, row count) for each token tile of an expert-sorted activation
 // buffer (replaces the reference's Triton GEMV / grouped GEMM family: engine/fast/mfma.py:90-179,
 // engine/fast/moe_prefill.py:156-319, engine/fast/fused.py:581-692).
-#include "common.cuh"
+#include "comm.cuh"
 
 namespace b200 {
 
@@ -27,7 +27,7 @@ constexpr int BM = 128;  // weight rows per tile (TMEM lanes)
 constexpr int BK = 64;   // bf16 per operand row per stage (128 bytes)
 constexpr int UMMA_K = 16;
 
-enum Epilogue : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_ARGMAX = 3 };
+enum Epilogue : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_ARGMAX = 3, EPI_ALLREDUCE = 4 };
 
 struct GemmParams {
   int N;             // weight rows (per expert when grouped)
@@ -41,6 +41,8 @@ struct GemmParams {
   float* part_max;   // EPI_ARGMAX: [n_tiles_n, T]
   int* part_idx;     // EPI_ARGMAX: [n_tiles_n, T]
   int* err;          // error word (0 = ok)
+  const bf16* residual; // EPI_ALLREDUCE: optional [T, ldo] added after the cross-rank sum
+  CommCtx comm;      // EPI_ALLREDUCE: the rank group's symmetric buffers
 };
 
 template <int BT, int EPI>
@@ -148,6 +150,50 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     tc_fence_after();
     const int n = n0 + q * 32 + lane;
     const bool n_ok = n < p.N;
+    if (EPI == EPI_ALLREDUCE) {
+      // Fused GEMM -> one-shot all-reduce: this tile's fp32 partial goes straight from TMEM into every
+      // rank's receive slot over NVLink; when all R partials of the tile have arrived they are added in
+      // rank order (+ residual) and stored as bf16. No partial ever touches this rank's output buffer.
+      const CommCtx& cc = p.comm;
+      const int blk = blockIdx.y * gridDim.x + blockIdx.x;
+      __shared__ uint32_t s_epoch;
+      __shared__ int s_peer_ok;
+      const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
+      if (et == 0) { s_epoch = cc.epoch[blk] + 1; cc.epoch[blk] = s_epoch; s_peer_ok = 1; }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const uint32_t e = s_epoch;
+      if (ok) {
+#pragma unroll 1
+        for (int c = 0; c < nrows; c += 16) {
+          float v[16];
+          tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + c, v);  // warp-collective: never predicated
+          if (n_ok) {
+            for (int r = 0; r < cc.world; ++r) {
+              float* dst = comm_slot(cc, r, e, cc.rank);
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (c + j < nrows) dst[static_cast<size_t>(row0 + c + j) * p.ldo + n] = v[j];
+            }
+          }
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et < cc.world) {
+        __threadfence_system();
+        st_release_sys(cc.flags[et] + static_cast<size_t>(cc.rank) * cc.max_blocks + blk, e);
+        if (!wait_flag(cc.flags[cc.rank] + static_cast<size_t>(et) * cc.max_blocks + blk, e, cc.err)) s_peer_ok = 0;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ok && n_ok && s_peer_ok) {
+        for (int t = 0; t < nrows; ++t) {
+          const size_t o = static_cast<size_t>(row0 + t) * p.ldo + n;
+          float acc = comm_slot(cc, cc.rank, e, 0)[o];
+          for (int r = 1; r < cc.world; ++r) acc += comm_slot(cc, cc.rank, e, r)[o];
+          if (p.residual) acc = __bfloat162float(__float2bfloat16(acc)) + __bfloat162float(p.residual[o]);
+          reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16(acc);
+        }
+      }
+    } else
     if (ok) {
 #pragma unroll 1
       for (int c = 0; c < BT; c += 16) {
@@ -320,7 +366,7 @@ extern "C" int b200_gemm_dense(const void* X, const void* W, void* out, int T, i
   const int w_rows = (epi == EPI_SILU_MUL) ? up_offset + N : N;
   if (make_map(&tw, W, K, w_rows, 0, ldw, 0, BM)) return -1;
   if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
-  GemmParams p{N, K, T, ldo, out, nullptr, nullptr, up_offset, part_max, part_idx, err};
+  GemmParams p{N, K, T, ldo, out, nullptr, nullptr, up_offset, part_max, part_idx, err, nullptr, CommCtx{}};
   const int gy = (T + bt - 1) / bt;
   switch (epi) {
     case EPI_BF16: return dispatch_bt<EPI_BF16, false>(bt, tw, tx, p, gy, st);
@@ -340,12 +386,28 @@ extern "C" int b200_gemm_grouped(const void* X, const void* W, void* out, int ca
   CUtensorMap tw, tx;
   if (make_map(&tw, W, K, w_rows, E, K, static_cast<uint64_t>(w_rows) * K, BM)) return -1;
   if (make_map(&tx, X, K, cap, 0, K, 0, bt)) return -1;
-  GemmParams p{N, K, cap, ldo, out, reinterpret_cast<const int4*>(tiles), n_tiles, up_offset, nullptr, nullptr, err};
+  GemmParams p{N, K, cap, ldo, out, reinterpret_cast<const int4*>(tiles), n_tiles, up_offset, nullptr, nullptr, err, nullptr, CommCtx{}};
   switch (epi) {
     case EPI_BF16: return dispatch_bt<EPI_BF16, true>(bt, tw, tx, p, max_tiles, st);
     case EPI_SILU_MUL: return dispatch_bt<EPI_SILU_MUL, true>(bt, tw, tx, p, max_tiles, st);
   }
   return -6;
+}
+
+// Tensor-parallel output projection: out[T, N] = bf16(residual + sum over ranks of X_r[T, K_r] W_r[N, K_r]^T).
+// Every rank calls this with its K-shard; the all-reduce happens inside the GEMM epilogue over peer memory.
+// Needs T * N <= ctx->slot_elems and ceil(N/128) * ceil(T/bt) <= ctx->max_blocks.
+extern "C" int b200_gemm_allreduce(const CommCtx* ctx, const void* X, const void* W, const void* residual, void* out,
+                                   int T, int N, int K, int ldx, int ldw, int bt, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (bt <= 0) bt = b200_pick_bt(T);
+  const int gy = (T + bt - 1) / bt;
+  if (static_cast<unsigned long long>(T) * N > ctx->slot_elems || ((N + BM - 1) / BM) * gy > ctx->max_blocks) return -7;
+  CUtensorMap tw, tx;
+  if (make_map(&tw, W, K, N, 0, ldw, 0, BM)) return -1;
+  if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
+  GemmParams p{N, K, T, N, out, nullptr, nullptr, 0, nullptr, nullptr, ctx->err, static_cast<const bf16*>(residual), *ctx};
+  return dispatch_bt<EPI_ALLREDUCE, false>(bt, tw, tx, p, gy, st);
 }
 
 extern "C" int b200_argmax_finish(const float* part_max, const int* part_idx, int n_tiles, int T, int64_t* out,
@@ -395,7 +457,7 @@ extern "C" int b200_lm_head_argmax_noalloc(const void* X, const void* W, int64_t
   CUtensorMap tw, tx;
   if (make_map(&tw, W, K, V, 0, ldw, 0, BM)) return -1;
   if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
-  GemmParams p{V, K, T, 0, nullptr, nullptr, nullptr, 0, part_max, part_idx, err};
+  GemmParams p{V, K, T, 0, nullptr, nullptr, nullptr, 0, part_max, part_idx, err, nullptr, CommCtx{}};
   const int rc = dispatch_bt<EPI_ARGMAX, false>(bt, tw, tx, p, (T + bt - 1) / bt, st);
   if (rc) return rc;
   argmax_finish_kernel<<<T, 256, 0, st>>>(part_max, part_idx, n_tiles, T, out_idx, out_val);

@@ -55,10 +55,10 @@ class _Sig:
     b200_argmax_finish = [P, P, I, I, P, P, P]
     b200_embed = [P, P, P, I, I, I, P]
     b200_add_rmsnorm = [P, P, P, P, P, I, I, F, I, P]
-    b200_moe_route = [P, I, I, I, I, I, P, P, P, P]
+    b200_moe_route = [P, I, I, I, I, I, P, P, P, I, P, P]
     b200_moe_plan = [P, P, I, I, I, P, P, P, P, I, P, P, P, P]
-    b200_moe_gather = [P, P, I, I, I, P, P]
-    b200_moe_combine = [P, P, P, I, I, I, P, P]
+    b200_moe_gather = [P, P, P, I, I, I, I, P, P]
+    b200_moe_combine = [P, P, P, I, I, I, P, P, P]
     b200_gdn_decode = [P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P]
     b200_attn_prep = [P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P, P]
     b200_paged_attn = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
@@ -186,8 +186,12 @@ def moe_bt(T: int, pairs_per_row: int, n_experts: int) -> int:
 
 
 def moe_block(x: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, n_experts: int,
-              top_k: int, shared_merged: bool) -> torch.Tensor:
-    """Router GEMM, top-k, expert-sorted grouped gate/up + SiLU-mul, grouped down, weighted combine."""
+              top_k: int, shared_merged: bool, expert_map: torch.Tensor | None = None,
+              partial_f32: bool = False) -> torch.Tensor:
+    """Router GEMM, top-k, expert-sorted grouped gate/up + SiLU-mul, grouped down, weighted combine.
+
+    With ``expert_map`` (global expert id -> local slot or -1) only the pairs of locally hosted experts
+    are computed; ``partial_f32`` returns the fp32 partial sum that the caller adds across ranks."""
     T, H = x.shape
     dev = x.device
     Et = w_gate_up.shape[0]
@@ -206,14 +210,14 @@ def moe_block(x: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_
     perm = ints[3 * Et + 4 : 3 * Et + 4 + n_pairs]
     inv = ints[3 * Et + 4 + n_pairs :]
     _check(L.b200_moe_route(_ptr(logits), logits.stride(0), T, n_experts, top_k, int(shared_merged), _ptr(wts),
-                            _ptr(idx), _ptr(counts), st), "moe_route")
+                            _ptr(idx), _ptr(counts), Et + 1, _ptr(expert_map), st), "moe_route")
     bt = moe_bt(T, Pn, n_experts)
     max_tiles = min(Et, n_pairs) + n_pairs // bt + 1
     tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device=dev)
     _check(L.b200_moe_plan(_ptr(counts), _ptr(idx), n_pairs, Et, bt, _ptr(offsets), _ptr(cursors), _ptr(tiles),
                            _ptr(n_tiles), max_tiles, _ptr(perm), _ptr(inv), _ptr(err), st), "moe_plan")
     xs = torch.empty(n_pairs, H, dtype=x.dtype, device=dev)
-    _check(L.b200_moe_gather(_ptr(x), _ptr(perm), n_pairs, Pn, H, _ptr(xs), st), "moe_gather")
+    _check(L.b200_moe_gather(_ptr(x), _ptr(perm), _ptr(offsets[Et:]), n_pairs, T, Pn, H, _ptr(xs), st), "moe_gather")
     act = torch.empty(n_pairs, inter, dtype=x.dtype, device=dev)
     _check(L.b200_gemm_grouped(_ptr(xs), _ptr(w_gate_up), _ptr(act), n_pairs, Et, inter, 2 * inter, H, inter,
                                EPI_SILU_MUL, inter, bt, _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err), st),
@@ -221,8 +225,9 @@ def moe_block(x: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_
     pair_out = torch.empty(n_pairs, H, dtype=x.dtype, device=dev)
     _check(L.b200_gemm_grouped(_ptr(act), _ptr(w_down), _ptr(pair_out), n_pairs, Et, H, H, inter, H, EPI_BF16, 0, bt,
                                _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err), st), "gemm_grouped(down)")
-    out = torch.empty_like(x)
-    _check(L.b200_moe_combine(_ptr(pair_out), _ptr(wts), _ptr(inv), T, Pn, H, _ptr(out), st), "moe_combine")
+    out = torch.empty(T, H, dtype=torch.float32 if partial_f32 else x.dtype, device=dev)
+    _check(L.b200_moe_combine(_ptr(pair_out), _ptr(wts), _ptr(inv), T, Pn, H, None if partial_f32 else _ptr(out),
+                              _ptr(out) if partial_f32 else None, st), "moe_combine")
     return out
 
 

@@ -167,6 +167,7 @@ def moe_experts(
     idx: torch.Tensor,
     w_gate_up: torch.Tensor,
     w_down: torch.Tensor,
+    partial_f32: bool = False,
 ) -> torch.Tensor:
     """Sum over each row's selected experts of ``w * down(silu(gate(x)) * up(x))``.
 
@@ -180,13 +181,15 @@ def moe_experts(
     pair_out = torch.zeros(T, P, x.shape[1], dtype=x.dtype, device=x.device)
     flat = idx.reshape(-1).long()
     for e in torch.unique(flat).tolist():
+        if e < 0:
+            continue  # hosted by another rank
         sel = (flat == e).nonzero(as_tuple=True)[0]
         rows = sel // P
         gu = linear(x[rows], w_gate_up[e])
         act = F.silu(gu[:, :inter].float()).to(x.dtype) * gu[:, inter:]
         pair_out.view(T * P, -1)[sel] = linear(act, w_down[e])
     out = (pair_out.float() * weights.float()[:, :, None]).sum(1)
-    return out.to(x.dtype)
+    return out if partial_f32 else out.to(x.dtype)
 
 
 # --------------------------------------------------------------------------- Gated DeltaNet
@@ -470,15 +473,24 @@ def lm_head_argmax(x: torch.Tensor, w: torch.Tensor, return_value: bool = False)
     return idx
 
 
-def moe_block(x, router, w_gate_up, w_down, n_experts: int, top_k: int, shared_merged: bool) -> torch.Tensor:
+def moe_block(x, router, w_gate_up, w_down, n_experts: int, top_k: int, shared_merged: bool,
+              expert_map: torch.Tensor | None = None, partial_f32: bool = False) -> torch.Tensor:
     """Router, top-k and experts; with ``shared_merged`` router row ``E`` is the shared gate and
-    expert ``E`` the shared expert, selected for every row with weight ``sigmoid(logit_E)``."""
+    expert ``E`` the shared expert, selected for every row with weight ``sigmoid(logit_E)``.
+
+    ``expert_map`` (global id -> local slot or -1) restricts the work to locally hosted experts;
+    ``partial_f32`` returns the unrounded fp32 partial sum for a cross-rank reduction."""
     logits = linear(x, router, out_dtype=torch.float32)
     wts, idx = router_topk(logits[:, :n_experts], top_k)
     if shared_merged:
         wts = torch.cat([wts, torch.sigmoid(logits[:, n_experts : n_experts + 1])], dim=1)
         idx = torch.cat([idx, torch.full_like(idx[:, :1], n_experts)], dim=1)
-    return moe_experts(x, wts.to(x.dtype), idx, w_gate_up, w_down)
+    wts = wts.to(x.dtype)
+    if expert_map is not None:
+        local = expert_map.to(idx.device)[idx.long()]
+        wts = torch.where(local >= 0, wts, torch.zeros_like(wts))
+        idx = local
+    return moe_experts(x, wts, idx, w_gate_up, w_down, partial_f32=partial_f32)
 
 
 def attention(qkv, positions, seq_of_row, block_tables, kv_layer, q_norm, k_norm, n_q, n_kv, head_dim, rotary_dim,

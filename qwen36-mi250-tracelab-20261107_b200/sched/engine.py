@@ -43,8 +43,11 @@ def _select_ops(device: torch.device):
 
 
 class Engine:
-    def __init__(self, weights: Weights, cfg: EngineConfig | None = None, ops=None) -> None:
+    def __init__(self, weights: Weights, cfg: EngineConfig | None = None, ops=None, tp=None) -> None:
+        """``tp``: a ``parallel.tp.TPContext`` when ``weights`` is one rank's shard; all ranks of the group
+        then run the same engine on the same requests in lockstep."""
         self.cfg = cfg or EngineConfig()
+        self.tp = tp
         self.mcfg: ModelConfig = weights.config
         self.device = weights.device
         self.ops = ops or _select_ops(self.device)
@@ -54,7 +57,7 @@ class Engine:
         self.max_pages_per_seq = (self.max_model_len + PAGE_SIZE - 1) // PAGE_SIZE + 1
         n_slots = c.state_slots or (c.max_seqs * 2 + 2)
         n_pages = c.kv_pages or self._auto_pages(weights, n_slots)
-        self.model = Model(weights, n_pages, n_slots, ops=self.ops)
+        self.model = Model(weights, n_pages, n_slots, ops=self.ops, tp=tp)
         self.pages = PagePool(n_pages)
         self.slots = SlotPool(n_slots)
         page_bytes = self.model.kv[:, 0].numel() * self.model.kv.element_size()

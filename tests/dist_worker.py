@@ -32,11 +32,12 @@ def mode_allreduce(rank, world, dev):
 
     comm = SymmComm(dev, dist.group.WORLD, slot_elems=1 << 20, max_blocks=1024)
     g = torch.Generator(device=dev).manual_seed(100 + rank)
+    gc = torch.Generator(device=dev).manual_seed(7)  # replicated tensors: same on every rank
     for T, H in ((1, 2048), (16, 2048), (128, 2048), (7, 512)):
         for dtype in (torch.float32, torch.bfloat16):
             for rep in range(3):
                 x = torch.randn(T, H, device=dev, generator=g).to(dtype)
-                res = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+                res = torch.randn(T, H, device=dev, generator=gc).to(torch.bfloat16)
                 got = comm.allreduce(x, res)
                 ref = x.float().clone()
                 dist.all_reduce(ref)
@@ -76,7 +77,48 @@ def mode_allreduce(rank, world, dev):
     comm.close()
 
 
-MODES = {"allreduce": mode_allreduce}
+def mode_tp_model(rank, world, dev):
+    """Tensor + expert parallel engine against the unsharded engine on the same requests."""
+    from b200serve.config import EngineConfig, ModelConfig
+    from b200serve.models.checkpoint import random_weights
+    from b200serve.parallel.tp import DistComm, FusedComm, TPContext, shard_weights
+    from b200serve.sched.engine import Engine
+    from b200serve.sched.request import Sampling
+
+    cuda = dev.type == "cuda"
+    dtype = torch.bfloat16 if cuda else torch.float32
+    cfg = ModelConfig.tiny(num_experts=8)
+    full = random_weights(cfg, seed=0, device="cpu", dtype=torch.float32, std=0.05, lm_head_std=0.5).to(dev, dtype)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(3, 1024, (n,), generator=g).tolist() for n in (20, 70, 150, 33)]
+    s = Sampling(max_tokens=12, ignore_eos=True)
+    ecfg = EngineConfig(max_model_len=1024, prefill_chunk_tokens=64, max_seqs=4, mtp=False, kv_pages=128)
+    ref = [x.output for x in Engine(full, ecfg).generate(prompts, s)]
+    comms = {"library": DistComm(dist.group.WORLD)}
+    if cuda:
+        comms["fused"] = FusedComm(dev, dist.group.WORLD, slot_elems=1 << 20, max_blocks=1024)
+    for name, comm in comms.items():
+        shard = shard_weights(full, rank, world)
+        eng = Engine(shard, ecfg, tp=TPContext(rank, world, comm))
+        got = [x.output for x in eng.generate(prompts, s)]
+        # every rank produced the same tokens
+        mine = torch.tensor(got)
+        allr = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine.to(dev))
+        assert all(torch.equal(allr[0], t) for t in allr), name
+        same = sum(a == b for x, y in zip(got, ref) for a, b in zip(x, y))
+        total = sum(len(x) for x in ref)
+        if rank == 0:
+            print(f"tp_model[{name}] world={world}: {same}/{total} tokens equal the unsharded engine", flush=True)
+        # sharded sums are reordered: allow rare flips of near-tied tokens in bf16, none in fp32
+        assert same >= (0.9 if cuda else 1.0) * total, (name, same, total)
+        if cuda:
+            from b200serve.ops import cuda_ops
+
+            cuda_ops.check_errors(dev)
+
+
+MODES = {"allreduce": mode_allreduce, "tp_model": mode_tp_model}
 
 if __name__ == "__main__":
     mode = sys.argv[1]

@@ -117,7 +117,7 @@ def test_route_ties_pick_lower_id(C):
     idx = torch.empty(T, k + 1, dtype=torch.int32, device="cuda")
     counts = torch.empty(E + 1, dtype=torch.int32, device="cuda")
     rc = C.lib().b200_moe_route(logits.data_ptr(), E + 1, T, E, k, 1, wts.data_ptr(), idx.data_ptr(),
-                                counts.data_ptr(), torch.cuda.current_stream().cuda_stream)
+                                counts.data_ptr(), E + 1, None, torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     assert idx[0, :k].tolist() == list(range(8))
     assert idx[1, :k].tolist() == list(range(100, 108))

@@ -1,0 +1,54 @@
+"""Tensor + expert parallelism without a cluster: CPU ranks over gloo (and 2 GPUs when present)."""
+
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _launch(mode: str, nproc: int, port: int, env: dict | None = None, timeout: int = 600):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), str(ROOT / "tests/dist_worker.py"), mode]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env={**os.environ, **(env or {})})
+
+
+def test_shard_shapes():
+    from b200serve.config import ModelConfig
+    from b200serve.models.checkpoint import random_weights
+    from b200serve.parallel.tp import local_config, shard_weights
+
+    cfg = ModelConfig.tiny(num_attention_heads=4, num_key_value_heads=2)
+    w = random_weights(cfg, seed=0, dtype=torch.float32)
+    for world in (2,):
+        lc = local_config(cfg, world)
+        assert lc.linear_num_value_heads == cfg.linear_num_value_heads // world
+        for rank in range(world):
+            s = shard_weights(w, rank, world)
+            gdn, attn = s.layers[0], s.layers[3]
+            assert gdn.in_proj.shape[0] == lc.gdn_in_rows and gdn.out_proj.shape == (cfg.hidden_size, lc.gdn_value_dim)
+            assert gdn.conv_w.shape[0] == lc.gdn_conv_dim and gdn.A_log.shape[0] == lc.linear_num_value_heads
+            assert attn.in_proj.shape[0] == lc.attn_q_rows + 2 * lc.attn_kv_rows
+            hosted = [(i % world) == rank for i in range(4)]
+            for lw, h in zip(s.layers, hosted):
+                assert lw.w_gate_up.shape[0] == cfg.num_experts // world + int(h)
+                assert (lw.expert_map >= 0).sum().item() == lw.w_gate_up.shape[0]
+            assert s.lm_head.shape[0] == cfg.vocab_size // world and s.vocab_start == rank * cfg.vocab_size // world
+    with pytest.raises(ValueError):
+        local_config(cfg, 3)
+
+
+def test_two_cpu_ranks_match_the_unsharded_engine():
+    r = _launch("tp_model", 2, 29621, env={"CUDA_VISIBLE_DEVICES": ""})
+    assert r.returncode == 0 and "OK tp_model" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_ranks_fused_collectives_match_the_unsharded_engine():
+    r = _launch("tp_model", 2, 29622, env={"NCCL_NVLS_ENABLE": "0"})
+    assert r.returncode == 0 and "OK tp_model" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
