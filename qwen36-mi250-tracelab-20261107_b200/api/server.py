@@ -345,21 +345,35 @@ def load_service(args: argparse.Namespace) -> Service:
     from .tokenizer import TextCodec
 
     use_cuda = args.device == "cuda" or (args.device == "auto" and torch.cuda.is_available())
-    device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
-    dtype = torch.bfloat16 if use_cuda else torch.float32
     t0 = time.time()
-    weights = load_checkpoint(args.model, device=device, dtype=dtype)
     cfg = EngineConfig.from_env(
         model=args.model, max_model_len=args.max_model_len, prefill_chunk_tokens=args.prefill_chunk_tokens,
         prefix_cache_tokens=args.prefix_cache_tokens, prefix_cache_entries=args.prefix_cache_entries,
         prefix_cache_gib=args.prefix_cache_gib, max_seqs=args.max_seqs,
     )
-    engine = Engine(weights, cfg)
+    tp = int(args.gpus_per_replica or os.environ.get("ENGINE_TP", "1") or 1)
+    followers = []
+    if tp > 1:  # a tensor-parallel replica: this process is rank 0, the other ranks are child processes
+        from ..parallel import replica
+
+        passthrough = ["--max-model-len", str(args.max_model_len), "--prefill-chunk-tokens",
+                       str(args.prefill_chunk_tokens), "--prefix-cache-tokens", str(args.prefix_cache_tokens),
+                       "--prefix-cache-entries", str(args.prefix_cache_entries), "--prefix-cache-gib",
+                       str(args.prefix_cache_gib), "--max-seqs", str(args.max_seqs)]
+        engine, followers = replica.leader_engine(args.model, tp, use_cuda, cfg, passthrough)
+        device = engine.device
+    else:
+        device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
+        dtype = torch.bfloat16 if use_cuda else torch.float32
+        engine = Engine(load_checkpoint(args.model, device=device, dtype=dtype), cfg)
     codec = TextCodec(args.model)
     name = args.served_model_name or args.model
-    print(f"engine: loaded {args.model} on {device} ({weights.nbytes() / 1e9:.2f} GB) in {time.time() - t0:.1f} s; "
-          f"kv_pages={engine.pages.num_pages} slots={engine.slots.num_slots} mtp={engine.spec is not None}", flush=True)
-    return Service(engine, codec, name)
+    print(f"engine: loaded {args.model} on {device} tp={tp} ({engine.model.w.nbytes() / 1e9:.2f} GB per rank) in "
+          f"{time.time() - t0:.1f} s; kv_pages={engine.pages.num_pages} slots={engine.slots.num_slots} "
+          f"mtp={engine.spec is not None}", flush=True)
+    service = Service(engine, codec, name)
+    service.followers = followers
+    return service
 
 
 def main(argv: list[str] | None = None) -> None:
@@ -379,6 +393,11 @@ def main(argv: list[str] | None = None) -> None:
         pass
     finally:
         service.worker.stop()
+        if service.engine.coordinator is not None:
+            service.worker.join(timeout=5)
+            service.engine.coordinator.stop(service.engine)
+        for p in getattr(service, "followers", []):
+            p.terminate()
 
 
 if __name__ == "__main__":

@@ -260,19 +260,32 @@ def _pack_moe(router, gate_up, down, sh_gu, sh_down, sh_gate) -> dict[str, Any]:
     )
 
 
-def load_checkpoint(path: str | Path, device: str | torch.device = "cpu", dtype: torch.dtype | None = None) -> Weights:
-    """Read a HF-layout checkpoint directory into engine ``Weights`` on ``device``."""
+def load_checkpoint(path: str | Path, device: str | torch.device = "cpu", dtype: torch.dtype | None = None,
+                    shard: tuple[int, int] | None = None) -> Weights:
+    """Read a HF-layout checkpoint directory into engine ``Weights`` on ``device``.
+
+    ``shard = (rank, world)`` keeps only that rank's tensor/expert-parallel part: every layer is
+    cut on the host right after it is read, so a rank never holds more than one full layer."""
     path = Path(path)
     cfg = ModelConfig.from_pretrained(path)
     src = _TensorSource(path)
+    out_cfg = cfg
+    cut = lambda lw, i: lw  # noqa: E731
+    v0, v1 = 0, cfg.vocab_size
+    if shard is not None and shard[1] > 1:
+        from ..parallel.tp import local_config, shard_layer
 
+        rank, world = shard
+        out_cfg = local_config(cfg, world)
+        cut = lambda lw, i: shard_layer(lw, cfg, rank, world, i)  # noqa: E731
+        per = (cfg.vocab_size + world - 1) // world
+        v0, v1 = rank * per, min(cfg.vocab_size, (rank + 1) * per)
     layers = []
     for i, kind in enumerate(cfg.layer_types):
-        lw = _load_layer(src, f"layers.{i}.", kind, cfg)
-        layers.append(_layer_to(lw, device, dtype))
+        layers.append(_layer_to(cut(_load_layer(src, f"layers.{i}.", kind, cfg), i), device, dtype))
     mtp = None
     if cfg.mtp_num_hidden_layers and src.has("mtp.fc.weight"):
-        lw = _load_layer(src, "mtp.layers.0.", "full_attention", cfg)
+        lw = cut(_load_layer(src, "mtp.layers.0.", "full_attention", cfg), len(cfg.layer_types))
         mtp = MTPWeights(
             fc=src.get("mtp.fc.weight").to(device=device, dtype=dtype),
             pre_fc_norm_embedding=src.get("mtp.pre_fc_norm_embedding.weight").to(device=device, dtype=dtype),
@@ -282,13 +295,16 @@ def load_checkpoint(path: str | Path, device: str | torch.device = "cpu", dtype:
         )
     else:
         cfg.mtp_num_hidden_layers = 0
+        out_cfg.mtp_num_hidden_layers = 0
     return Weights(
-        cfg,
+        out_cfg,
         src.get("embed_tokens.weight").to(device=device, dtype=dtype),
-        src.get("lm_head.weight").to(device=device, dtype=dtype),
+        src.get("lm_head.weight")[v0:v1].to(device=device, dtype=dtype).contiguous(),
         src.get("norm.weight").to(device=device, dtype=dtype),
         layers,
         mtp,
+        vocab_start=v0,
+        full_vocab=cfg.vocab_size,
     )
 
 

@@ -1,0 +1,124 @@
+"""One tensor-parallel replica: a leader process (HTTP + scheduler) and follower rank processes.
+
+``python -m b200serve.api.server --gpus-per-replica N`` makes the calling process rank 0 and
+starts ranks 1..N-1 with ``python -m b200serve.parallel.replica``; every rank loads its shard of
+the checkpoint onto its own GPU (``LOCAL_RANK``), joins one ``torch.distributed`` group (NCCL for
+tensors, an extra gloo group for the lockstep messages) and runs the same engine
+(``parallel.lockstep``). On a machine without GPUs the ranks are CPU processes over gloo, which
+is how the plumbing is tested.
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+import signal
+import socket
+import subprocess
+import sys
+import time
+from datetime import timedelta
+
+import torch
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def init_rank(rank: int, world: int, port: int, cuda: bool):
+    import torch.distributed as dist
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ["MASTER_PORT"] = str(port)
+    if cuda:
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=timedelta(minutes=30))
+    else:
+        dev = torch.device("cpu")
+        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(days=7))
+    cpu_group = dist.new_group(backend="gloo", timeout=timedelta(days=7))
+    return dev, cpu_group
+
+
+def build_engine(model_dir: str, rank: int, world: int, dev: torch.device, cpu_group, engine_cfg):
+    import torch.distributed as dist
+
+    from ..models.checkpoint import load_checkpoint
+    from ..sched.engine import Engine
+    from .lockstep import Coordinator
+    from .tp import DistComm, FusedComm, TPContext
+
+    dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    weights = load_checkpoint(model_dir, device=dev, dtype=dtype, shard=(rank, world))
+    if dev.type == "cuda" and engine_cfg.fused_collectives:
+        comm = FusedComm(dev, dist.group.WORLD)
+    else:
+        comm = DistComm(dist.group.WORLD)
+    engine = Engine(weights, engine_cfg, tp=TPContext(rank, world, comm))
+    engine.coordinator = Coordinator(cpu_group, rank)
+    return engine
+
+
+def start_followers(model_dir: str, world: int, port: int, cuda: bool, cfg_args: list[str]) -> list[subprocess.Popen]:
+    procs = []
+    for r in range(1, world):
+        cmd = [sys.executable, "-m", "b200serve.parallel.replica", "--model", model_dir, "--rank", str(r), "--world",
+               str(world), "--port", str(port), "--device", "cuda" if cuda else "cpu", *cfg_args]
+        procs.append(subprocess.Popen(cmd, env=dict(os.environ)))
+    return procs
+
+
+def follower_main(argv: list[str] | None = None) -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", required=True)
+    ap.add_argument("--rank", type=int, required=True)
+    ap.add_argument("--world", type=int, required=True)
+    ap.add_argument("--port", type=int, required=True)
+    ap.add_argument("--device", default="cuda")
+    ap.add_argument("--max-model-len", type=int, default=262144)
+    ap.add_argument("--prefill-chunk-tokens", type=int, default=2048)
+    ap.add_argument("--prefix-cache-tokens", type=int, default=4194304)
+    ap.add_argument("--prefix-cache-entries", type=int, default=128)
+    ap.add_argument("--prefix-cache-gib", type=float, default=16.0)
+    ap.add_argument("--max-seqs", type=int, default=128)
+    args = ap.parse_args(argv)
+    try:  # leave with the leader
+        import ctypes
+
+        ctypes.CDLL("libc.so.6", use_errno=True).prctl(1, signal.SIGTERM)
+    except OSError:
+        pass
+    from ..config import EngineConfig
+
+    dev, cpu_group = init_rank(args.rank, args.world, args.port, args.device == "cuda")
+    cfg = EngineConfig.from_env(
+        model=args.model, max_model_len=args.max_model_len, prefill_chunk_tokens=args.prefill_chunk_tokens,
+        prefix_cache_tokens=args.prefix_cache_tokens, prefix_cache_entries=args.prefix_cache_entries,
+        prefix_cache_gib=args.prefix_cache_gib, max_seqs=args.max_seqs, mtp=False,
+    )
+    engine = build_engine(args.model, args.rank, args.world, dev, cpu_group, cfg)
+    print(f"engine: rank {args.rank}/{args.world} ready on {dev}", flush=True)
+    engine.coordinator.follow(engine)
+
+
+def leader_engine(model_dir: str, world: int, cuda: bool, engine_cfg, cfg_args: list[str]):
+    """Start the followers, build rank 0's engine; returns ``(engine, follower processes)``."""
+    port = _free_port()
+    followers = start_followers(model_dir, world, port, cuda, cfg_args)
+    try:
+        dev, cpu_group = init_rank(0, world, port, cuda)
+        engine_cfg.mtp = False  # speculation inside a TP replica is not wired yet
+        engine = build_engine(model_dir, 0, world, dev, cpu_group, engine_cfg)
+    except BaseException:
+        for p in followers:
+            p.terminate()
+        raise
+    return engine, followers
+
+
+if __name__ == "__main__":
+    follower_main()

@@ -48,6 +48,7 @@ class Engine:
         then run the same engine on the same requests in lockstep."""
         self.cfg = cfg or EngineConfig()
         self.tp = tp
+        self.coordinator = None  # parallel.lockstep.Coordinator in a multi-rank replica
         self.mcfg: ModelConfig = weights.config
         self.device = weights.device
         self.ops = ops or _select_ops(self.device)
@@ -176,18 +177,30 @@ class Engine:
             gen.sampling.max_tokens = self.max_model_len - L
         if gen.sampling.seed is not None or not gen.sampling.greedy:
             gen.rng = torch.Generator(device="cpu")
-            gen.rng.manual_seed(gen.sampling.seed if gen.sampling.seed is not None else gen.id * 7919 + int(time.time()))
+            gen.rng.manual_seed(gen.sampling.seed if gen.sampling.seed is not None else gen.id * 7919)
 
-    def _admit(self) -> None:
+    def _poll_local(self) -> None:
+        """Single-process mode: take new submissions and latch cancellations at the iteration boundary."""
         while True:
             try:
-                self.waiting.append(self._inbox.get_nowait())
+                g = self._inbox.get_nowait()
             except queue.Empty:
                 break
+            if g.sampling.seed is None and not g.sampling.greedy:
+                g.sampling.seed = (g.id * 7919 + int(time.time() * 1e3)) % (2**31)
+            self.waiting.append(g)
+        for g in self.waiting:
+            g.cancel_now = g.cancel_now or g.cancelled.is_set()
+        for g in self.prefilling:
+            g.cancel_now = g.cancel_now or g.cancelled.is_set()
+        for g in self.running:
+            g.cancel_now = g.cancel_now or g.cancelled.is_set()
+
+    def _admit(self) -> None:
         while self.waiting and len(self.prefilling) + len(self.running) < self.cfg.max_seqs:
             gen = self.waiting.pop(0)
             self.stats["requests"] += 1
-            if gen.cancelled.is_set():
+            if gen.cancel_now:
                 self._finish(gen, "cancelled", retire=False)
                 continue
             try:
@@ -221,7 +234,7 @@ class Engine:
         budget = self.cfg.prefill_pack_tokens
         picked: list[Generation] = []
         for gen in list(self.prefilling):
-            if gen.cancelled.is_set():
+            if gen.cancel_now:
                 self.prefilling.remove(gen)
                 self._finish(gen, "cancelled")
                 continue
@@ -292,7 +305,7 @@ class Engine:
     # ------------------------------------------------------------------ decode
     def _decode_step(self) -> bool:
         for gen in list(self.running):
-            if gen.cancelled.is_set():
+            if gen.cancel_now:
                 self.running.remove(gen)
                 self._finish(gen, "cancelled")
         if not self.running:
@@ -411,8 +424,15 @@ class Engine:
         g.emit(TokenEvent(None, "error", err))
 
     # ------------------------------------------------------------------ loop
-    def step(self) -> bool:
-        """One scheduler iteration. Returns False when there was nothing to do."""
+    def step(self, synced: bool = False) -> bool:
+        """One scheduler iteration. Returns False when there was nothing to do.
+
+        In a tensor-parallel replica the ranks first exchange the iteration's new requests and
+        cancellations (``parallel.lockstep``); ``synced`` says the caller has already done so."""
+        if self.coordinator is None:
+            self._poll_local()
+        elif not synced and not self.coordinator.sync(self):
+            return False
         self._admit()
         did = self._prefill_pass()
         did = self._decode_step() or did

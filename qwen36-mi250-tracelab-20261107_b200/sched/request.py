@@ -57,7 +57,8 @@ class Generation:
         self.on_event = on_event
         self.output: list[int] = []
         self.finish_reason: str | None = None
-        self.cancelled = threading.Event()
+        self.cancelled = threading.Event()  # set by any thread; the engine latches it into cancel_now
+        self.cancel_now = False
         # engine-owned
         self.slot: int = 0
         self.pages: list[int] = []

@@ -118,7 +118,51 @@ def mode_tp_model(rank, world, dev):
             cuda_ops.check_errors(dev)
 
 
-MODES = {"allreduce": mode_allreduce, "tp_model": mode_tp_model}
+def mode_lockstep(rank, world, dev):
+    """Leader/follower replica: only rank 0 sees the requests (and a cancellation); followers mirror it."""
+    from b200serve.config import EngineConfig, ModelConfig
+    from b200serve.models.checkpoint import random_weights
+    from b200serve.parallel.lockstep import Coordinator
+    from b200serve.parallel.tp import DistComm, TPContext, shard_weights
+    from b200serve.sched.engine import Engine
+    from b200serve.sched.request import Generation, Sampling
+
+    cuda = dev.type == "cuda"
+    dtype = torch.bfloat16 if cuda else torch.float32
+    cfg = ModelConfig.tiny()
+    full = random_weights(cfg, seed=0, device="cpu", dtype=torch.float32, std=0.05, lm_head_std=0.5).to(dev, dtype)
+    ecfg = EngineConfig(max_model_len=1024, prefill_chunk_tokens=64, max_seqs=4, mtp=False, kv_pages=128)
+    cpu_group = dist.new_group(backend="gloo")
+    eng = Engine(shard_weights(full, rank, world), ecfg, tp=TPContext(rank, world, DistComm(dist.group.WORLD)))
+    eng.coordinator = Coordinator(cpu_group, rank)
+    if rank != 0:
+        eng.coordinator.follow(eng)
+        assert not eng.running and not eng.prefilling
+        return
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(3, 1024, (n,), generator=g).tolist() for n in (40, 90, 25)]
+    samp = [Sampling(max_tokens=10, ignore_eos=True), Sampling(max_tokens=200, ignore_eos=True),
+            Sampling(max_tokens=8, temperature=0.8, seed=11, ignore_eos=True)]
+    gens = [eng.submit(Generation(p, s)) for p, s in zip(prompts, samp)]
+    steps = 0
+    while not (gens[0].done and gens[2].done):
+        eng.step()
+        steps += 1
+        if steps == 6:
+            gens[1].cancelled.set()  # a client went away mid-stream
+    late = eng.submit(Generation(prompts[0] + gens[0].output + [9, 9], Sampling(max_tokens=5, ignore_eos=True)))
+    while not (late.done and gens[1].done):
+        eng.step()
+    eng.coordinator.stop(eng)
+    ref_eng = Engine(full, ecfg)
+    ref = ref_eng.generate([prompts[0], prompts[2]], [samp[0], samp[2]])
+    assert gens[0].output == ref[0].output and gens[2].output == ref[1].output
+    assert gens[1].finish_reason == "cancelled" and 0 < len(gens[1].output) < 200
+    assert late.cached_tokens > 0 and len(late.output) == 5
+    print("lockstep: leader finished after", steps, "steps", flush=True)
+
+
+MODES = {"allreduce": mode_allreduce, "tp_model": mode_tp_model, "lockstep": mode_lockstep}
 
 if __name__ == "__main__":
     mode = sys.argv[1]

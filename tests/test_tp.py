@@ -52,3 +52,29 @@ def test_two_cpu_ranks_match_the_unsharded_engine():
 def test_two_gpu_ranks_fused_collectives_match_the_unsharded_engine():
     r = _launch("tp_model", 2, 29622, env={"NCCL_NVLS_ENABLE": "0"})
     assert r.returncode == 0 and "OK tp_model" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_lockstep_replica_on_two_cpu_ranks():
+    r = _launch("lockstep", 2, 29623, env={"CUDA_VISIBLE_DEVICES": ""})
+    assert r.returncode == 0 and "OK lockstep" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_served_tensor_parallel_replica_on_cpu_ranks(tmp_path):
+    """`--gpus-per-replica 2` on a machine without GPUs: leader + follower processes over gloo, over HTTP."""
+    from http_util import ServerProc, ids_of
+
+    from b200serve.models.tiny import write_tiny_checkpoint
+
+    write_tiny_checkpoint(tmp_path, lm_head_std=0.5)
+    tp = ServerProc(tmp_path, extra=["--gpus-per-replica", "2"], env={"CUDA_VISIBLE_DEVICES": "", "ENGINE_MTP": "0"})
+    one = ServerProc(tmp_path, env={"CUDA_VISIBLE_DEVICES": "", "ENGINE_MTP": "0"})
+    try:
+        prompt = [5 + (i * 11) % 300 for i in range(100)]
+        a, ua = tp.completion(prompt, 12)
+        b, _ = one.completion(prompt, 12)
+        assert ids_of(a) == ids_of(b)
+        again, u2 = tp.completion(prompt, 12)
+        assert u2["prompt_tokens_details"]["cached_tokens"] > 0 and ids_of(again) == ids_of(a)
+    finally:
+        tp.stop()
+        one.stop()
