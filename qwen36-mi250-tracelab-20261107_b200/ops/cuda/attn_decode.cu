@@ -224,16 +224,22 @@ extern "C" int b200_paged_attn(const void* q, const void* gate, const void* kv, 
   paged_attn_kernel<DD, GG><<<grid, 32 * GG, 0, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(kv),    \
                                                       tables, max_pages, positions, part_acc, part_ml, n_q, n_kv, G, \
                                                       Z, scale, num_pages)
-  if (D == 256 && group == 8) ATT(256, 8);
-  else if (D == 256 && group == 4) ATT(256, 4);
-  else if (D == 256 && group == 2) ATT(256, 2);
-  else if (D == 256 && group == 1) ATT(256, 1);
-  else if (D == 32 && group == 4) ATT(32, 4);
-  else if (D == 64 && group == 4) ATT(64, 4);
+#define ATT_GROUPS(DD)                         \
+  if (group == 8) ATT(DD, 8);                  \
+  else if (group == 4) ATT(DD, 4);             \
+  else if (group == 2) ATT(DD, 2);             \
+  else if (group == 1) ATT(DD, 1);             \
+  else return -7
+  if (D == 256) { ATT_GROUPS(256); }
+  else if (D == 128) { ATT_GROUPS(128); }
+  else if (D == 64) { ATT_GROUPS(64); }
+  else if (D == 32) { ATT_GROUPS(32); }
   else return -7;
+#undef ATT_GROUPS
 #undef ATT
   dim3 cgrid(B * G, n_q);
   if (D == 256) attn_combine_kernel<256><<<cgrid, 256, 0, st>>>(part_acc, part_ml, static_cast<const bf16*>(gate), static_cast<bf16*>(out), n_q, Z);
+  else if (D == 128) attn_combine_kernel<128><<<cgrid, 128, 0, st>>>(part_acc, part_ml, static_cast<const bf16*>(gate), static_cast<bf16*>(out), n_q, Z);
   else if (D == 64) attn_combine_kernel<64><<<cgrid, 64, 0, st>>>(part_acc, part_ml, static_cast<const bf16*>(gate), static_cast<bf16*>(out), n_q, Z);
   else if (D == 32) attn_combine_kernel<32><<<cgrid, 32, 0, st>>>(part_acc, part_ml, static_cast<const bf16*>(gate), static_cast<bf16*>(out), n_q, Z);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

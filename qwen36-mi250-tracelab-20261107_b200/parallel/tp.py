@@ -91,6 +91,24 @@ class FusedComm(DistComm):
             return self.symm.allreduce(partial.contiguous(), residual)
         return super().allreduce(partial, residual, out_dtype)
 
+    def argmax(self, val: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+        """Cross-rank greedy pick without a library collective (so that it can live inside a CUDA graph):
+        every rank fills its own row of a ``[world, T, 2]`` fp32 table (value, index; indices below 2^24
+        are exact in fp32), the one-shot all-reduce adds the disjoint rows, then each rank picks."""
+        if not val.is_cuda:
+            return super().argmax(val, idx)
+        T = val.shape[0]
+        table = torch.zeros(self.world, T, 2, dtype=torch.float32, device=val.device)
+        table[self.rank, :, 0] = val
+        table[self.rank, :, 1] = idx.float()
+        table = self.symm.allreduce(table, out_dtype=torch.float32)
+        best_v, best_i = table[0, :, 0], table[0, :, 1]
+        for r in range(1, self.world):
+            v, i = table[r, :, 0], table[r, :, 1]
+            take = (v > best_v) | ((v == best_v) & (i < best_i))
+            best_v, best_i = torch.where(take, v, best_v), torch.where(take, i, best_i)
+        return best_i.long()
+
     def gemm_allreduce(self, ops, x, w, residual=None):
         from ..ops import cuda_ops
         from .symm import _lib

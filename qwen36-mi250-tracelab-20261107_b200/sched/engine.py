@@ -80,7 +80,8 @@ class Engine:
             mtp_verify_steps=0, mtp_proposed=0, mtp_accepted=0,
         )
         self._graphs = None
-        if self.device.type == "cuda" and c.cuda_graphs:
+        # library collectives (the NCCL baseline path) stay out of CUDA graphs; the fused NVLink kernels go in
+        if self.device.type == "cuda" and c.cuda_graphs and (tp is None or tp.comm.fused):
             from .graphs import DecodeGraphs
 
             self._graphs = DecodeGraphs(self)

@@ -97,10 +97,16 @@ def mode_tp_model(rank, world, dev):
     comms = {"library": DistComm(dist.group.WORLD)}
     if cuda:
         comms["fused"] = FusedComm(dev, dist.group.WORLD, slot_elems=1 << 20, max_blocks=1024)
+    def note(msg):
+        print(f"[rank {rank}] {msg}", file=sys.stderr, flush=True)
+
+    note("reference engine done")
     for name, comm in comms.items():
         shard = shard_weights(full, rank, world)
         eng = Engine(shard, ecfg, tp=TPContext(rank, world, comm))
+        note(f"{name}: engine built, graphs={'on' if eng._graphs is not None else 'off'}")
         got = [x.output for x in eng.generate(prompts, s)]
+        note(f"{name}: generated")
         # every rank produced the same tokens
         mine = torch.tensor(got)
         allr = [torch.empty_like(mine) for _ in range(world)]
