@@ -108,9 +108,9 @@ def mode_tp_model(rank, world, dev):
         got = [x.output for x in eng.generate(prompts, s)]
         note(f"{name}: generated")
         # every rank produced the same tokens
-        mine = torch.tensor(got)
+        mine = torch.tensor(got, device=dev)
         allr = [torch.empty_like(mine) for _ in range(world)]
-        dist.all_gather(allr, mine.to(dev))
+        dist.all_gather(allr, mine)
         assert all(torch.equal(allr[0], t) for t in allr), name
         same = sum(a == b for x, y in zip(got, ref) for a, b in zip(x, y))
         total = sum(len(x) for x in ref)
