@@ -1,0 +1,186 @@
+"""Per-kernel timing against the measured roofline.
+
+    python bench/kernel_bench.py [case ...] [--small]
+
+Each case runs one kernel (or one fused op) of the decode / prefill path at the shapes of
+Qwen3.6-35B-A3B, timed with CUDA events after warm-up, with an L2 flush (a 256 MB write) between
+timed launches, and prints one JSON line: algorithmic bytes and FLOPs, microseconds, achieved
+GB/s and TFLOP/s, and the fraction of the measured copy bandwidth / cuBLAS bf16 throughput from
+``MEASURED_PEAKS.json`` (fallback 6650 GB/s and 1590 TFLOP/s when the file is absent).
+``--small`` shrinks every case to a few hundred MB so that a profiler capture ends quickly.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+
+from b200serve.ops import cuda_ops as C  # noqa: E402
+
+
+def peaks() -> tuple[float, float, str]:
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        p = json.loads(f.read_text())
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def bf(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+_flush = None
+
+
+def timed(fn, iters=10, warm=3):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        _flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    return total / iters * 1e3  # microseconds
+
+
+def report(name, us, nbytes, flops, **extra):
+    hbm, tf, kind = peaks()
+    gbs, tfl = nbytes / us / 1e3, flops / us / 1e6
+    line = {"case": name, "us": round(us, 2), "bytes": nbytes, "flops": flops, "GBps": round(gbs, 1),
+            "TFLOPs": round(tfl, 2), f"frac_of_{kind}_hbm": round(gbs / hbm, 3),
+            f"frac_of_{kind}_bf16": round(tfl / tf, 3), **extra}
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- cases
+def case_moe_decode(small):
+    """MoE block of one decode step: 128 rows, 256 experts top-8 + shared (weight streaming)."""
+    T, E, H, I = 128, (64 if small else 256), 2048, 512
+    x, router = bf(T, H), bf(E + 1, H, scale=0.3)
+    wgu, wd = bf(E + 1, 2 * I, H, scale=0.02), bf(E + 1, H, I, scale=0.02)
+    us = timed(lambda: C.moe_block(x, router, wgu, wd, E, 8, True))
+    w_bytes = (wgu.numel() + wd.numel() + router.numel()) * 2
+    report("moe_decode_b128", us, w_bytes, 2 * T * 9 * 3 * H * I, experts=E)
+
+
+def case_gemm_grouped(small):
+    """The two grouped GEMMs alone on a fixed routing (gate/up + SiLU-mul, then down)."""
+    T, E, H, I, P = 128, (64 if small else 256), 2048, 512, 9
+    wgu, wd = bf(E + 1, 2 * I, H, scale=0.02), bf(E + 1, H, I, scale=0.02)
+    n_pairs = T * P
+    idx = torch.cat([torch.stack([torch.randperm(E, device="cuda")[:8] for _ in range(T)]),
+                     torch.full((T, 1), E, device="cuda")], 1).to(torch.int32)
+    counts = torch.bincount(idx.flatten().long(), minlength=E + 1).to(torch.int32)
+    ints = torch.zeros(2 * (E + 2) + 1 + 2 * n_pairs, dtype=torch.int32, device="cuda")
+    offsets, cursors = ints[: E + 2], ints[E + 2 : 2 * E + 4]
+    n_tiles, perm, inv = ints[2 * E + 4 : 2 * E + 5], ints[2 * E + 5 : 2 * E + 5 + n_pairs], ints[2 * E + 5 + n_pairs :]
+    bt = 16
+    max_tiles = E + 1 + n_pairs // bt + 1
+    tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device="cuda")
+    L, st = C.lib(), torch.cuda.current_stream().cuda_stream
+    err = C.err_word(torch.device("cuda"))
+    assert L.b200_moe_plan(counts.data_ptr(), idx.data_ptr(), n_pairs, E + 1, bt, offsets.data_ptr(), cursors.data_ptr(),
+                           tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, perm.data_ptr(), inv.data_ptr(),
+                           err.data_ptr(), st) == 0
+    xs, act, out = bf(n_pairs, H), torch.empty(n_pairs, I, dtype=torch.bfloat16, device="cuda"), torch.empty(
+        n_pairs, H, dtype=torch.bfloat16, device="cuda")
+
+    def up():
+        L.b200_gemm_grouped(xs.data_ptr(), wgu.data_ptr(), act.data_ptr(), n_pairs, E + 1, I, 2 * I, H, I, 2, I, bt,
+                            tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), st)
+
+    def down():
+        L.b200_gemm_grouped(act.data_ptr(), wd.data_ptr(), out.data_ptr(), n_pairs, E + 1, H, H, I, H, 0, 0, bt,
+                            tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), st)
+
+    report("grouped_gate_up_silu", timed(up), wgu.numel() * 2, 2 * n_pairs * 2 * I * H, experts=E)
+    report("grouped_down", timed(down), wd.numel() * 2, 2 * n_pairs * I * H, experts=E)
+
+
+def case_gdn_decode(small):
+    """Recurrent Gated-DeltaNet step of one layer: 128 sequences x 32 heads x 64 KB of fp32 state."""
+    B = 32 if small else 128
+    n_k, n_v, dk, dv = 16, 32, 128, 128
+    Cd = 2 * n_k * dk + n_v * dv
+    mixed = bf(B, Cd + n_v * dv + 2 * n_v)
+    conv, rec = bf(B + 1, Cd, 3), torch.randn(B + 1, n_v, dk, dv, device="cuda") * 0.1
+    args = (bf(Cd, 4, scale=0.3), torch.rand(n_v, device="cuda"), torch.randn(n_v, device="cuda"), bf(dv), n_k, n_v, dk, dv, 1e-6)
+    slots = torch.arange(1, B + 1, dtype=torch.int32, device="cuda")
+    us = timed(lambda: C.gdn_decode(mixed, slots, conv, rec, *args))
+    report(f"gdn_decode_b{B}", us, 2 * B * n_v * dk * dv * 4, 6 * B * n_v * dk * dv)
+
+
+def case_attn_decode(small):
+    """Paged decode attention of one layer: 128 sequences, 1024-token context, 16 Q / 2 KV heads, D=256."""
+    B, ctx = (32 if small else 128), 1024
+    n_q, n_kv, D = 16, 2, 256
+    pages_per = ctx // 64 + 1
+    kv = bf(B * pages_per + 1, 2, n_kv, 64, D)
+    tables = (torch.arange(B * pages_per, dtype=torch.int32, device="cuda").view(B, pages_per) + 1)
+    qkv = bf(B, n_q * 2 * D + 2 * n_kv * D)
+    pos = torch.full((B,), ctx, dtype=torch.int64, device="cuda")
+    seq = torch.arange(B, dtype=torch.int32, device="cuda")
+    qn, kn = bf(D, scale=0.1), bf(D, scale=0.1)
+    us = timed(lambda: C.attention(qkv, pos, seq, tables, kv, qn, kn, n_q, n_kv, D, 64, 1e7, 1e-6, 1))
+    report(f"attn_decode_b{B}_ctx{ctx}", us, B * (ctx + 1) * 2 * n_kv * D * 2, 4 * B * n_q * (ctx + 1) * D)
+
+
+def case_lm_head(small):
+    """LM head with fused argmax: 248320 x 2048 weights, 128 rows."""
+    V = 65536 if small else 248320
+    x, w = bf(128, 2048), bf(V, 2048, scale=0.02)
+    us = timed(lambda: C.lm_head_argmax(x, w))
+    report("lm_head_argmax_b128", us, w.numel() * 2, 2 * 128 * V * 2048, vocab=V)
+
+
+def case_gemm_decode(small):
+    """Dense projections at decode size (128 rows): GDN in_proj 12352 x 2048 and out_proj 2048 x 4096."""
+    for name, N, K in (("in_proj", 12352, 2048), ("out_proj", 2048, 4096)):
+        x, w = bf(128, K), bf(N, K, scale=0.02)
+        us = timed(lambda: C.linear(x, w))
+        report(f"gemm_decode_{name}_b128", us, w.numel() * 2, 2 * 128 * N * K)
+
+
+def case_gemm_prefill(small):
+    """Dense projection at prefill size: 8192 rows x (12352 x 2048), compute bound."""
+    T = 2048 if small else 8192
+    x, w = bf(T, 2048), bf(12352, 2048, scale=0.02)
+    us = timed(lambda: C.linear(x, w), iters=5)
+    report(f"gemm_prefill_in_proj_T{T}", us, (w.numel() + x.numel() + T * 12352) * 2, 2 * T * 12352 * 2048)
+
+
+def case_moe_prefill(small):
+    """MoE block at prefill size: 8192 rows (grouped GEMMs with 128-row token tiles)."""
+    T, E, H, I = (1024 if small else 8192), (64 if small else 256), 2048, 512
+    x, router = bf(T, H), bf(E + 1, H, scale=0.3)
+    wgu, wd = bf(E + 1, 2 * I, H, scale=0.02), bf(E + 1, H, I, scale=0.02)
+    us = timed(lambda: C.moe_block(x, router, wgu, wd, E, 8, True), iters=5)
+    report(f"moe_prefill_T{T}", us, (wgu.numel() + wd.numel()) * 2, 2 * T * 9 * 3 * H * I, experts=E)
+
+
+CASES = {k[5:]: v for k, v in globals().items() if k.startswith("case_")}
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("cases", nargs="*", default=list(CASES))
+    ap.add_argument("--small", action="store_true")
+    a = ap.parse_args()
+    for name in a.cases:
+        CASES[name](a.small)
+    C.check_errors(torch.device("cuda"))

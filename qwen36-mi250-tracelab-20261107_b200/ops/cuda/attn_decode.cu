@@ -111,22 +111,45 @@ __global__ void attn_prep_kernel(const bf16* qkv, int ld, const int64_t* positio
 }
 
 // Partials: part_acc [B*G, n_q, Z, D] fp32, part_ml [B*G, n_q, Z, 2] (running max, running sum).
+//
+// One CTA per (sequence, kv head, lane z); warp w serves query head w of the GQA group. A page's
+// K and V tiles (64 tokens x D) are staged in shared memory once with coalesced 16-byte loads
+// and shared by all heads of the group, so HBM sees every KV byte once per layer. K rows are
+// padded by 16 bytes: lane t reads row t, and the pad spreads rows over the banks. Scores: lane
+// owns tokens `lane` and `lane + 32`; softmax statistics by warp reductions once per page;
+// P.V: lane owns D/32 consecutive output dims.
+template <int D>
+struct AttnSmem {
+  static constexpr int KSTRIDE = D + 8;  // bf16 elements per padded K row
+  static constexpr size_t bytes(int group) {
+    return static_cast<size_t>(PAGE) * KSTRIDE * 2 + static_cast<size_t>(PAGE) * D * 2 +
+           static_cast<size_t>(group) * D * 4 + static_cast<size_t>(group) * PAGE * 4;
+  }
+};
+
 template <int D, int GROUP>
 __global__ void __launch_bounds__(32 * GROUP)
 paged_attn_kernel(const bf16* q, const bf16* kv, const int* tables, int max_pages, const int64_t* positions,
                   float* part_acc, float* part_ml, int n_q, int n_kv, int G, int Z, float scale, int num_pages) {
+  constexpr int KS = AttnSmem<D>::KSTRIDE;
+  constexpr int PER = D / 32;
+  constexpr int NT = 32 * GROUP;
+  constexpr int CHUNKS = D / 8;  // 16-byte chunks per row
+  extern __shared__ __align__(16) uint8_t smem_attn[];
+  bf16* sK = reinterpret_cast<bf16*>(smem_attn);
+  bf16* sV = sK + PAGE * KS;
+  float* sQ = reinterpret_cast<float*>(sV + PAGE * D);
+  float* sP = sQ + GROUP * D;
   const int b = blockIdx.x, kh = blockIdx.y, z = blockIdx.z;
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qh = kh * GROUP + w;
-  constexpr int PER = D / 32;  // dims per lane, contiguous: lane*PER .. lane*PER+PER-1
   for (int g = 0; g < G; ++g) {
     const int row = b * G + g;
     const int len = static_cast<int>(positions[row]) + 1;  // keys 0..pos inclusive
-    float qv[PER];
     {
-      const bf16* qp = q + (static_cast<size_t>(row) * n_q + qh) * D + lane * PER;
+      const bf16* qp = q + (static_cast<size_t>(row) * n_q + qh) * D;
 #pragma unroll
-      for (int i = 0; i < PER; ++i) qv[i] = __bfloat162float(qp[i]) * scale;
+      for (int i = 0; i < PER; ++i) sQ[w * D + lane + 32 * i] = __bfloat162float(qp[lane + 32 * i]) * scale;
     }
     float m = -INFINITY, l = 0.f;
     float acc[PER];
@@ -139,22 +162,57 @@ paged_attn_kernel(const bf16* q, const bf16* kv, const int* tables, int max_page
       const bf16* kp = kv + ((static_cast<size_t>(page) * 2 + 0) * n_kv + kh) * PAGE * D;
       const bf16* vp = kv + ((static_cast<size_t>(page) * 2 + 1) * n_kv + kh) * PAGE * D;
       const int n_tok = min(PAGE, len - pg * PAGE);
-      for (int t = 0; t < n_tok; ++t) {
-        float ke[PER], ve[PER];
-        load_bf16_vec<PER>(kp + static_cast<size_t>(t) * D + lane * PER, ke);
-        load_bf16_vec<PER>(vp + static_cast<size_t>(t) * D + lane * PER, ve);
-        float s = 0.f;
-#pragma unroll
-        for (int i = 0; i < PER; ++i) s += qv[i] * ke[i];
-        s = warp_sum(s);
-        const float mn = fmaxf(m, s);
-        const float corr = __expf(m - mn);
-        const float pexp = __expf(s - mn);
-        l = l * corr + pexp;
-#pragma unroll
-        for (int i = 0; i < PER; ++i) acc[i] = acc[i] * corr + pexp * ve[i];
-        m = mn;
+      __syncthreads();  // previous page (and the q of a previous row) fully consumed
+      for (int c = threadIdx.x; c < n_tok * CHUNKS; c += NT) {
+        const int t = c / CHUNKS, j = c % CHUNKS;
+        *reinterpret_cast<uint4*>(sK + t * KS + j * 8) = *reinterpret_cast<const uint4*>(kp + static_cast<size_t>(t) * D + j * 8);
+        *reinterpret_cast<uint4*>(sV + t * D + j * 8) = *reinterpret_cast<const uint4*>(vp + static_cast<size_t>(t) * D + j * 8);
       }
+      __syncthreads();
+      // scores of this head against tokens lane and lane + 32
+      float s0 = 0.f, s1 = 0.f;
+      const bool v0 = lane < n_tok, v1 = lane + 32 < n_tok;
+      const bf16* k0 = sK + lane * KS;
+      const bf16* k1 = sK + (lane + 32) * KS;
+      const float* qv = sQ + w * D;
+#pragma unroll 4
+      for (int j = 0; j < CHUNKS; ++j) {
+        const float4 qa = *reinterpret_cast<const float4*>(qv + j * 8);
+        const float4 qb = *reinterpret_cast<const float4*>(qv + j * 8 + 4);
+        if (v0) {
+          uint4 raw = *reinterpret_cast<const uint4*>(k0 + j * 8);
+          const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&raw);
+          const float2 a = __bfloat1622float2(e[0]), bb = __bfloat1622float2(e[1]), c2 = __bfloat1622float2(e[2]), d2 = __bfloat1622float2(e[3]);
+          s0 += qa.x * a.x + qa.y * a.y + qa.z * bb.x + qa.w * bb.y + qb.x * c2.x + qb.y * c2.y + qb.z * d2.x + qb.w * d2.y;
+        }
+        if (v1) {
+          uint4 raw = *reinterpret_cast<const uint4*>(k1 + j * 8);
+          const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&raw);
+          const float2 a = __bfloat1622float2(e[0]), bb = __bfloat1622float2(e[1]), c2 = __bfloat1622float2(e[2]), d2 = __bfloat1622float2(e[3]);
+          s1 += qa.x * a.x + qa.y * a.y + qa.z * bb.x + qa.w * bb.y + qb.x * c2.x + qb.y * c2.y + qb.z * d2.x + qb.w * d2.y;
+        }
+      }
+      if (!v0) s0 = -INFINITY;
+      if (!v1) s1 = -INFINITY;
+      const float mn = fmaxf(m, warp_max(fmaxf(s0, s1)));
+      const float corr = __expf(m - mn);
+      const float p0 = v0 ? __expf(s0 - mn) : 0.f, p1 = v1 ? __expf(s1 - mn) : 0.f;
+      sP[w * PAGE + lane] = p0;
+      sP[w * PAGE + lane + 32] = p1;
+      l = l * corr + warp_sum(p0 + p1);
+      m = mn;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) acc[i] *= corr;
+      __syncwarp();
+      const float* pw = sP + w * PAGE;
+      for (int t = 0; t < n_tok; ++t) {
+        const float pt = pw[t];
+        float ve[PER];
+        load_bf16_vec<PER>(sV + t * D + lane * PER, ve);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) acc[i] += pt * ve[i];
+      }
+      __syncwarp();
     }
     float* pa = part_acc + ((static_cast<size_t>(row) * n_q + qh) * Z + z) * D + lane * PER;
 #pragma unroll
@@ -163,6 +221,7 @@ paged_attn_kernel(const bf16* q, const bf16* kv, const int* tables, int max_page
       float* pm = part_ml + ((static_cast<size_t>(row) * n_q + qh) * Z + z) * 2;
       pm[0] = m; pm[1] = l;
     }
+    __syncthreads();  // sQ is rewritten for the next row
   }
 }
 
@@ -221,9 +280,17 @@ extern "C" int b200_paged_attn(const void* q, const void* gate, const void* kv, 
   const float scale = 1.0f / sqrtf(static_cast<float>(D));
   dim3 grid(B, n_kv, Z);
 #define ATT(DD, GG)                                                                                                  \
-  paged_attn_kernel<DD, GG><<<grid, 32 * GG, 0, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(kv),    \
-                                                      tables, max_pages, positions, part_acc, part_ml, n_q, n_kv, G, \
-                                                      Z, scale, num_pages)
+  do {                                                                                                                \
+    auto kern = paged_attn_kernel<DD, GG>;                                                                           \
+    const size_t smem = AttnSmem<DD>::bytes(GG);                                                                     \
+    static bool configured = false;                                                                                  \
+    if (!configured) {                                                                                               \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) return -3; \
+      configured = true;                                                                                             \
+    }                                                                                                                \
+    kern<<<grid, 32 * GG, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(kv), tables, max_pages, \
+                                      positions, part_acc, part_ml, n_q, n_kv, G, Z, scale, num_pages);              \
+  } while (0)
 #define ATT_GROUPS(DD)                         \
   if (group == 8) ATT(DD, 8);                  \
   else if (group == 4) ATT(DD, 4);             \

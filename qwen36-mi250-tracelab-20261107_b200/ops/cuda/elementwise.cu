@@ -138,30 +138,44 @@ __global__ void route_kernel(const float* logits, int ldl, int T, int E, int top
 
 // One CTA: exclusive offsets per expert, the token-tile table (expert, row0, nrows) and its length;
 // clears the scatter cursors. Experts are laid out in id order, rows of one expert contiguous.
-__global__ void moe_plan_kernel(const int* counts, int Et, int bt, int* offsets, int* cursors, int4* tiles,
-                                int* n_tiles, int max_tiles) {
-  __shared__ int s_off[1025];
-  __shared__ int s_tile[1025];
-  const int tid = threadIdx.x;
-  if (tid == 0) {
-    int acc = 0, tacc = 0;
-    for (int e = 0; e < Et; ++e) {
-      s_off[e] = acc; s_tile[e] = tacc;
-      acc += counts[e];
-      tacc += (counts[e] + bt - 1) / bt;
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* counts, int Et, int bt, int* offsets, int* cursors, int4* tiles, int* n_tiles,
+                int max_tiles) {
+  // block-wide exclusive scan of (rows, tiles) per expert: one expert per thread, Et <= 1024
+  __shared__ int w_rows[32], w_tiles[32];
+  const int e = threadIdx.x, lane = e & 31, w = e >> 5;
+  const int c = e < Et ? counts[e] : 0;
+  const int t = (c + bt - 1) / bt;
+  int sc = c, stl = t;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, sc, o), b2 = __shfl_up_sync(0xffffffffu, stl, o);
+    if (lane >= o) { sc += a; stl += b2; }
+  }
+  if (lane == 31) { w_rows[w] = sc; w_tiles[w] = stl; }
+  __syncthreads();
+  if (w == 0) {
+    int a = w_rows[lane], b2 = w_tiles[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int x = __shfl_up_sync(0xffffffffu, a, o), y = __shfl_up_sync(0xffffffffu, b2, o);
+      if (lane >= o) { a += x; b2 += y; }
     }
-    s_off[Et] = acc; s_tile[Et] = tacc;
-    *n_tiles = tacc < max_tiles ? tacc : max_tiles;
+    w_rows[lane] = a; w_tiles[lane] = b2;
   }
   __syncthreads();
-  for (int e = tid; e <= Et; e += blockDim.x) {
-    offsets[e] = s_off[e];
-    if (e < Et) {
-      cursors[e] = 0;
-      const int c = counts[e];
-      for (int i = 0, t = s_tile[e]; i * bt < c && t < max_tiles; ++i, ++t)
-        tiles[t] = make_int4(e, s_off[e] + i * bt, min(bt, c - i * bt), 0);
-    }
+  const int row0 = sc - c + (w ? w_rows[w - 1] : 0);    // exclusive prefix
+  const int tile0 = stl - t + (w ? w_tiles[w - 1] : 0);
+  if (e < Et) {
+    offsets[e] = row0;
+    cursors[e] = 0;
+    for (int i = 0, ti = tile0; i * bt < c && ti < max_tiles; ++i, ++ti)
+      tiles[ti] = make_int4(e, row0 + i * bt, min(bt, c - i * bt), 0);
+  }
+  if (e == Et - 1) {
+    offsets[Et] = row0 + c;
+    const int total = tile0 + t;
+    *n_tiles = total < max_tiles ? total : max_tiles;
   }
 }
 
@@ -254,7 +268,7 @@ extern "C" int b200_moe_route(const float* logits, int ldl, int T, int E, int to
 extern "C" int b200_moe_plan(const int* counts, const int* idx, int n_pairs, int Et, int bt, int* offsets, int* cursors,
                              void* tiles, int* n_tiles, int max_tiles, int* perm, int* inv, int* err, cudaStream_t st) {
   if (Et > 1024) return -7;
-  moe_plan_kernel<<<1, 256, 0, st>>>(counts, Et, bt, offsets, cursors, static_cast<int4*>(tiles), n_tiles, max_tiles);
+  moe_plan_kernel<<<1, 1024, 0, st>>>(counts, Et, bt, offsets, cursors, static_cast<int4*>(tiles), n_tiles, max_tiles);
   moe_scatter_kernel<<<(n_pairs + 255) / 256, 256, 0, st>>>(idx, n_pairs, Et, offsets, cursors, perm, inv, err);
   CHECK_LAUNCH();
 }

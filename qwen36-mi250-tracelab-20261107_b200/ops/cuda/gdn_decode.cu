@@ -54,7 +54,7 @@ __global__ void gdn_conv_step_kernel(const bf16* mixed, int ld, const int* slots
 
 // ------------------------------------------------------------------ delta-rule step
 template <int DK, int DV>
-__global__ void __launch_bounds__(4 * DV)
+__global__ void __launch_bounds__(4 * DV, 2)
 gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
                 const bf16* mixed,      // [B*G, ld] z at column z_off, b at b_off, a at a_off
                 int ld, int z_off, int b_off, int a_off,

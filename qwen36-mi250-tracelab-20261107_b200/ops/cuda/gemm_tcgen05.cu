@@ -51,7 +51,10 @@ struct Cfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BT * BK * 2;
   static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
-  static constexpr int BUDGET = 200 * 1024;
+  // small token tiles (decode) leave room for two CTAs per SM: one CTA's pipeline fill and epilogue
+  // overlap the other's main loop, which matters when K is short (the MoE down projection has 8 k-blocks)
+  static constexpr int CTAS_PER_SM = BT <= 64 ? 2 : 1;
+  static constexpr int BUDGET = BT <= 64 ? 108 * 1024 : 200 * 1024;
   static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int TMEM_COLS_RAW = A_TILES * BT;
@@ -60,7 +63,7 @@ struct Cfg {
 };
 
 template <int BT, int EPI, bool GROUPED>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, Cfg<BT, EPI>::CTAS_PER_SM)
 gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmParams p) {
   using C = Cfg<BT, EPI>;
   extern __shared__ uint8_t smem_raw[];
