@@ -1,0 +1,347 @@
+// Causal gated flash attention for prefill spans over the paged KV cache, on tcgen05.
+//
+// One CTA per (query tile, kv head). A tile is 128 MMA rows = (128 / GROUP) consecutive query
+// positions x the GROUP query heads that share the kv head, so every K/V page fetched by TMA is
+// used by all heads of the group (reference: engine/fast/flash_prefill.py:97-186 tiles
+// M = BLOCK_R x GROUP rows the same way on MFMA). Per 64-key page:
+//
+//   S[128 x 64]  = Q[128 x D] K[64 x D]^T      tcgen05.mma, both operands K-major, S in TMEM
+//   softmax      : each of 128 threads owns one TMEM lane = one row, so row max / sum need no
+//                  shuffles; P = exp2(S - m) goes to shared memory as bf16 in the swizzled K-major
+//                  layout the next MMA reads; the O accumulator in TMEM is rescaled only when a
+//                  row maximum grew by more than 2^8 (exact: the final division uses the same m)
+//   O[128 x D]  += P[128 x 64] V[64 x D]       V is read straight from its page layout as an
+//                                              MN-major B operand (no transpose)
+//
+// Warp 4 lane 0 drives TMA (Q once, K/V pages double-buffered) and issues all MMAs; warps 0..3
+// do the softmax and the epilogue (divide by the row sum, multiply by sigmoid(gate), store bf16).
+// Chunked prefill: queries sit at positions pos0.. of their sequence, keys are 0..pos.
+// All waits are bounded (common.cuh). No cluster multicast.
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int FP_PAGE = 64;
+
+struct FlashParams {
+  const int4* tiles;      // (segment, first local position, segment start row, segment length)
+  const int* seg_pos0;    // position of each segment's first row
+  const int* tables;      // [segments, max_pages]
+  int max_pages;
+  int num_pages;
+  const bf16* gate;       // [T, n_q * D]
+  bf16* out;              // [T, n_q * D]
+  int n_q, n_kv;
+  float scale_log2;       // D^-0.5 * log2(e)
+  int* err;
+};
+
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t addr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+      : "memory");
+}
+// MN-major B operand tile written by TMA with the 128-byte swizzle: rows = K index (keys), 128 bytes
+// (64 elements of N) per row, 8-row groups 1024 bytes apart (stride offset), next 64 elements of N
+// `lbo` bytes further (leading offset).
+__device__ __forceinline__ uint64_t umma_smem_desc_mn(uint32_t smem_addr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(lbo_bytes >> 4) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+template <int D>
+struct FlashCfg {
+  static constexpr int DB = D / 64;             // 64-element (128-byte) blocks along the head dim
+  static constexpr int Q_BYTES = DB * 128 * 128;
+  static constexpr int KV_BYTES = DB * FP_PAGE * 128;  // one of K or V, one stage
+  static constexpr int P_BYTES = 128 * 128;
+  static constexpr int SMEM = Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = (64 + D) <= 128 ? 128 : (64 + D) <= 256 ? 256 : 512;
+};
+
+template <int D, int GROUP>
+__global__ void __launch_bounds__(160, 1)
+flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKV, FlashParams p) {
+  using C = FlashCfg<D>;
+  constexpr int DB = C::DB;
+  constexpr int R = 128 / GROUP;  // query positions per tile
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + C::Q_BYTES;               // [2 stages][DB][64 x 128 B]
+  uint8_t* sV = sK + 2 * C::KV_BYTES;
+  uint8_t* sP = sV + 2 * C::KV_BYTES;          // [128 x 128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::P_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;                // [2]
+  uint64_t* kv_empty = bars + 3;               // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_full = bars + 6;
+  uint64_t* acc_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int4 tile = p.tiles[blockIdx.x];
+  const int seg = tile.x, p0 = tile.y, seg_row0 = tile.z, seg_len = tile.w;
+  const int kh = blockIdx.y;
+  const int pos0 = p.seg_pos0[seg];
+  const int n_pos = min(R, seg_len - p0);
+  const int np = (pos0 + p0 + n_pos - 1) / FP_PAGE + 1;  // pages that hold visible keys
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmKV);
+  }
+  if (warp == 4) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_S = tmem, tmem_O = tmem + 64;
+
+  if (warp == 4) {
+    if (elect_one()) {
+      auto load_page = [&](int i) {
+        const int s = i & 1;
+        int page = p.tables[static_cast<size_t>(seg) * p.max_pages + i];
+        if (page < 0 || page >= p.num_pages) { atomicCAS(p.err, 0, ERR_BAD_INDEX); page = 0; }
+        const int krow = ((page * 2 + 0) * p.n_kv + kh) * FP_PAGE;
+        const int vrow = ((page * 2 + 1) * p.n_kv + kh) * FP_PAGE;
+        mbar_expect_tx(&kv_full[s], 2 * C::KV_BYTES);
+        for (int a = 0; a < DB; ++a) {
+          tma_load_2d(sK + s * C::KV_BYTES + a * FP_PAGE * 128, &tmKV, &kv_full[s], a * 64, krow);
+          tma_load_2d(sV + s * C::KV_BYTES + a * FP_PAGE * 128, &tmKV, &kv_full[s], a * 64, vrow);
+        }
+      };
+      mbar_expect_tx(q_full, C::Q_BYTES);
+      for (int a = 0; a < DB; ++a) tma_load_4d(sQ + a * 128 * 128, &tmQ, q_full, a * 64, 0, kh, seg_row0 + p0);
+      load_page(0);
+      if (np > 1) load_page(1);
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 64);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, D) | (1u << 16);  // B operand MN-major
+      bool ok = mbar_wait(q_full, 0, p.err, ERR_WAIT_FULL, abort_flag);
+      for (int i = 0; i < np && ok; ++i) {
+        const int s = i & 1;
+        ok = mbar_wait(&kv_full[s], (i >> 1) & 1, p.err, ERR_WAIT_FULL, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * C::KV_BYTES), va = smem_u32(sV + s * C::KV_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t blk = kk >> 2, koff = (kk & 3) * 32;
+          umma_bf16(tmem_S, umma_smem_desc(qa + blk * 128 * 128 + koff), umma_smem_desc(ka + blk * FP_PAGE * 128 + koff),
+                    idesc_qk, kk != 0);
+        }
+        umma_commit(s_full);
+        if (i >= 1 && i + 1 < np) {  // the stage of page i-1 is free once its P.V has finished
+          ok = mbar_wait(&kv_empty[(i - 1) & 1], ((i - 1) >> 1) & 1, p.err, ERR_WAIT_EMPTY, abort_flag);
+          if (!ok) break;
+          load_page(i + 1);
+        }
+        ok = mbar_wait(p_full, i & 1, p.err, ERR_WAIT_FULL, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t pa = smem_u32(sP);
+#pragma unroll
+        for (int kk = 0; kk < FP_PAGE / 16; ++kk)
+          umma_bf16(tmem_O, umma_smem_desc(pa + kk * 32), umma_smem_desc_mn(va + kk * 2048, FP_PAGE * 128), idesc_pv,
+                    (i | kk) != 0);
+        umma_commit(&kv_empty[s]);
+      }
+      umma_commit(acc_done);
+    }
+  } else {
+    // ---------------- softmax + epilogue: thread r owns TMEM lane r = one (position, head) row
+    const int r = threadIdx.x;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const int lp = r / GROUP, head = r % GROUP;
+    const int qpos = pos0 + p0 + lp;
+    const bool row_valid = lp < n_pos;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int i = 0; i < np && ok; ++i) {
+      ok = mbar_wait(s_full, i & 1, p.err, ERR_WAIT_TMEM, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      float sc[64];
+#pragma unroll
+      for (int c = 0; c < 64; c += 16) tmem_ld16(tmem_S + lane_base + c, sc + c);
+      float mx = -INFINITY;
+      const int kbase = i * FP_PAGE;
+#pragma unroll
+      for (int j = 0; j < 64; ++j) {
+        sc[j] = (kbase + j <= qpos) ? sc[j] * p.scale_log2 : -INFINITY;
+        mx = fmaxf(mx, sc[j]);
+      }
+      const bool need = mx > m_used + 8.0f;
+      if (__any_sync(0xffffffffu, need)) {  // warp-uniform: TMEM loads/stores are warp-collective
+        const float factor = need ? exp2f(m_used - mx) : 1.0f;  // exp2(-inf) = 0 on the first page
+        if (need) { m_used = mx; l *= factor; }
+        if (i > 0) {
+#pragma unroll 1
+          for (int c = 0; c < D; c += 16) {
+            float o[16];
+            tmem_ld16(tmem_O + lane_base + c, o);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) o[j] *= factor;
+            tmem_st16(tmem_O + lane_base + c, o);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+      }
+      float sum = 0.f;
+      uint8_t* prow = sP + r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4 packed;
+        __nv_bfloat162* pe = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float a = exp2f(sc[c * 8 + 2 * j] - m_used), b2 = exp2f(sc[c * 8 + 2 * j + 1] - m_used);
+          sum += a + b2;
+          pe[j] = __floats2bfloat162_rn(a, b2);
+        }
+        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) * 16)) = packed;  // 128-byte swizzle of the K-major tile
+      }
+      l += sum;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    ok = ok && mbar_wait(acc_done, 0, p.err, ERR_WAIT_TMEM, abort_flag) && !*abort_flag;
+    tc_fence_after();
+    if (ok) {
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      const size_t row = static_cast<size_t>(seg_row0 + p0 + lp);
+      const size_t base = row * (static_cast<size_t>(p.n_q) * D) + static_cast<size_t>(kh * GROUP + head) * D;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 16) {
+        float o[16];
+        tmem_ld16(tmem_O + lane_base + c, o);  // warp-collective: never predicated
+        if (row_valid) {
+          uint4 g0 = *reinterpret_cast<const uint4*>(p.gate + base + c), g1 = *reinterpret_cast<const uint4*>(p.gate + base + c + 8);
+          const bf16* ge0 = reinterpret_cast<const bf16*>(&g0);
+          const bf16* ge1 = reinterpret_cast<const bf16*>(&g1);
+          uint4 o0, o1;
+          bf16* oe0 = reinterpret_cast<bf16*>(&o0);
+          bf16* oe1 = reinterpret_cast<bf16*>(&o1);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            oe0[j] = __float2bfloat16(__bfloat162float(__float2bfloat16(o[j] * inv)) * sigmoid_f(__bfloat162float(ge0[j])));
+            oe1[j] = __float2bfloat16(__bfloat162float(__float2bfloat16(o[8 + j] * inv)) * sigmoid_f(__bfloat162float(ge1[j])));
+          }
+          *reinterpret_cast<uint4*>(p.out + base + c) = o0;
+          *reinterpret_cast<uint4*>(p.out + base + c + 8) = o1;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) { tc_fence_after(); tmem_dealloc(tmem, C::TMEM_COLS); }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+namespace {
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn fp_encode_fn() {
+  static EncodeFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess) fn = reinterpret_cast<EncodeFn>(ptr);
+  }
+  return fn;
+}
+int fp_make_map(CUtensorMap* m, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
+                const cuuint32_t* box) {
+  EncodeFn fn = fp_encode_fn();
+  if (!fn) return -1;
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides_bytes, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+template <int D, int GROUP>
+int fp_launch(const CUtensorMap& tq, const CUtensorMap& tkv, const FlashParams& p, int n_tiles, cudaStream_t st) {
+  auto kern = flash_prefill_kernel<D, GROUP>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashCfg<D>::SMEM) != cudaSuccess) return -3;
+    configured = true;
+  }
+  kern<<<dim3(n_tiles, p.n_kv), 160, FlashCfg<D>::SMEM, st>>>(tq, tkv, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+}  // namespace
+
+// q: [T, n_q, D] bf16 (already normed and rotated), gate/out: [T, n_q * D], kv: one layer of the paged pool
+// [num_pages, 2, n_kv, 64, D]; tiles: int4 (segment, first local position, segment start row, segment length) with
+// 128 / (n_q / n_kv) positions per tile; seg_pos0 / tables per segment. The span's K/V must already be in the pages.
+extern "C" int b200_flash_prefill(const void* q, const void* gate, const void* kv, void* out, const void* tiles,
+                                  int n_tiles, const int* seg_pos0, const int* tables, int max_pages, int num_pages,
+                                  int T, int n_q, int n_kv, int D, int* err, cudaStream_t st) {
+  if (n_tiles <= 0) return 0;
+  const int group = n_q / n_kv;
+  if (group * n_kv != n_q || (D != 64 && D != 128 && D != 256) || 128 % group) return -7;
+  CUtensorMap tq, tkv;
+  {
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(group), static_cast<cuuint64_t>(n_kv),
+                          static_cast<cuuint64_t>(T)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(group) * D * 2,
+                             static_cast<cuuint64_t>(n_q) * D * 2};
+    cuuint32_t box[4] = {64, static_cast<cuuint32_t>(group), 1, static_cast<cuuint32_t>(128 / group)};
+    if (fp_make_map(&tq, q, 4, dims, strides, box)) return -1;
+  }
+  {
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(num_pages) * 2 * n_kv * FP_PAGE};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(D) * 2};
+    cuuint32_t box[2] = {64, FP_PAGE};
+    if (fp_make_map(&tkv, kv, 2, dims, strides, box)) return -1;
+  }
+  FlashParams p{static_cast<const int4*>(tiles), seg_pos0, tables, max_pages, num_pages, static_cast<const bf16*>(gate),
+                static_cast<bf16*>(out), n_q, n_kv, 1.4426950408889634f / sqrtf(static_cast<float>(D)), err};
+#define FP_GROUPS(DD)                                              \
+  switch (group) {                                                 \
+    case 1: return fp_launch<DD, 1>(tq, tkv, p, n_tiles, st);      \
+    case 2: return fp_launch<DD, 2>(tq, tkv, p, n_tiles, st);      \
+    case 4: return fp_launch<DD, 4>(tq, tkv, p, n_tiles, st);      \
+    case 8: return fp_launch<DD, 8>(tq, tkv, p, n_tiles, st);      \
+    default: return -7;                                            \
+  }
+  if (D == 256) { FP_GROUPS(256) }
+  if (D == 128) { FP_GROUPS(128) }
+  FP_GROUPS(64)
+#undef FP_GROUPS
+}

@@ -62,6 +62,7 @@ class _Sig:
     b200_gdn_decode = [P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P]
     b200_attn_prep = [P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P, P]
     b200_paged_attn = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
+    b200_flash_prefill = [P, P, P, P, P, I, P, P, I, I, I, I, I, I, P, P]
 
 
 def _ptr(t: torch.Tensor | None):
@@ -279,6 +280,9 @@ def attention(qkv, positions, seq_of_row, block_tables, kv_layer, q_norm, k_norm
     )
     _check(rc, "attn_prep")
     if G == 0:
+        group = n_q // n_kv
+        if head_dim in (64, 128, 256) and group in (1, 2, 4, 8):
+            return flash_prefill(q, gate, kv_layer, block_tables, seg_starts, seg_pos0)
         return torch_ops.paged_attention(q, gate, kv_layer, block_tables, seg_starts, seg_pos0)
     B = rows // G
     part_acc = torch.empty(rows, n_q, ATTN_Z, head_dim, dtype=torch.float32, device=dev)
@@ -289,6 +293,30 @@ def attention(qkv, positions, seq_of_row, block_tables, kv_layer, q_norm, k_norm
         _ptr(part_acc), _ptr(part_ml), _ptr(out), B, G, n_q, n_kv, head_dim, ATTN_Z, num_pages, _stream(),
     )
     _check(rc, "paged_attn")
+    return out
+
+
+def flash_prefill(q: torch.Tensor, gate: torch.Tensor, kv_layer: torch.Tensor, block_tables: torch.Tensor,
+                  seg_starts: list[int], seg_pos0: list[int]) -> torch.Tensor:
+    """Causal gated attention of ragged prefill spans over the paged cache (tcgen05 flash kernel).
+
+    ``q [T, n_q, D]`` normed and rotated; the spans' K/V are already in their pages."""
+    T, n_q, D = q.shape
+    n_kv = kv_layer.shape[2]
+    R = 128 // (n_q // n_kv)
+    tiles = []
+    for i in range(len(seg_starts) - 1):
+        n = seg_starts[i + 1] - seg_starts[i]
+        tiles.extend((i, p0, seg_starts[i], n) for p0 in range(0, n, R))
+    dev = q.device
+    tiles_t = torch.tensor(tiles, dtype=torch.int32).reshape(-1, 4).to(dev, non_blocking=True)
+    pos0_t = torch.tensor(seg_pos0, dtype=torch.int32).to(dev, non_blocking=True)
+    out = torch.empty(T, n_q * D, dtype=q.dtype, device=dev)
+    rc = lib().b200_flash_prefill(
+        _ptr(q), _ptr(gate), _ptr(kv_layer), _ptr(out), _ptr(tiles_t), len(tiles), _ptr(pos0_t), _ptr(block_tables),
+        block_tables.stride(0), kv_layer.shape[0], T, n_q, n_kv, D, _ptr(err_word(dev)), _stream(),
+    )
+    _check(rc, "flash_prefill")
     return out
 
 

@@ -224,3 +224,28 @@ def test_tiny_model_cuda_matches_fp32_oracle(C, O):
     cos = torch.nn.functional.cosine_similarity(ref, got, dim=-1)
     # a near-tied expert choice may flip in bf16 for a single row: bound the mean tightly, the minimum loosely
     assert cos.mean().item() > 0.995 and cos.min().item() > 0.95, cos
+
+
+@pytest.mark.parametrize("n_q,n_kv,D,lens,pos0", [
+    (8, 1, 64, [40], [0]),
+    (16, 2, 256, [70, 16, 200], [0, 130, 64]),
+    (4, 2, 128, [129, 5], [3, 500]),
+    (16, 2, 256, [1024], [0]),
+])
+def test_flash_prefill_matches_reference(C, O, n_q, n_kv, D, lens, pos0):
+    g = torch.Generator(device="cuda").manual_seed(50)
+    nseg = len(lens)
+    maxp = max((p + n + 63) // 64 for p, n in zip(pos0, lens)) + 1
+    pages = nseg * maxp + 1
+    kv = (torch.randn(pages, 2, n_kv, 64, D, device="cuda", generator=g)).to(torch.bfloat16)
+    tables = (torch.randperm(pages - 1, device="cuda", generator=g)[: nseg * maxp] + 1).to(torch.int32).view(nseg, maxp)
+    starts = [0]
+    for n in lens:
+        starts.append(starts[-1] + n)
+    T = starts[-1]
+    q = _bf(T, n_q, D, seed=51)
+    gate = _bf(T, n_q * D, seed=52)
+    ref = O.paged_attention(q.float(), gate.float(), kv.float(), tables, starts, pos0)
+    got = C.flash_prefill(q, gate, kv, tables, starts, pos0)
+    C.check_errors(q.device)
+    _close(got, ref, 3e-2, 3e-2, "flash prefill")
