@@ -175,7 +175,7 @@ def main() -> None:
             for _ in range(timed_steps):
                 engine.step()
         else:
-            bucket = engine._graphs.buckets[B]
+            bucket = next(b for b in engine._graphs.buckets.values() if b.size == B)
             for _ in range(timed_steps):
                 bucket.graph.replay()
                 bucket.tokens.copy_(bucket.picks)  # feed the picks back on the device
@@ -213,7 +213,7 @@ def main() -> None:
     e2e_s = reduce_max(max(e2e_wall, e2e_ms / 1e3))
     value = world * tokens / (ms / 1e3)
     e2e_value = world * e2e_tokens / e2e_s
-    bucket = engine._graphs.buckets[B]
+    bucket = next(b for b in engine._graphs.buckets.values() if b.size == B)
     h2d = (bucket.h_tokens.numel() * 8 + bucket.h_positions.numel() * 8 + bucket.h_slots.numel() * 4
            + bucket.h_tables.numel() * 4)
     d2h = bucket.h_picks.numel() * 8

@@ -311,3 +311,15 @@ extern "C" int b200_paged_attn(const void* q, const void* gate, const void* kv, 
   else if (D == 32) attn_combine_kernel<32><<<cgrid, 32, 0, st>>>(part_acc, part_ml, static_cast<const bf16*>(gate), static_cast<bf16*>(out), n_q, Z);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// Merge split partials [rows, n_q, Z, D] / [rows, n_q, Z, 2] in split order, apply sigmoid(gate), store bf16.
+extern "C" int b200_attn_combine(const float* part_acc, const float* part_ml, const void* gate, void* out, int rows,
+                                 int n_q, int D, int Z, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  dim3 cgrid(rows, n_q);
+  if (D == 256) attn_combine_kernel<256><<<cgrid, 256, 0, st>>>(part_acc, part_ml, static_cast<const bf16*>(gate), static_cast<bf16*>(out), n_q, Z);
+  else if (D == 128) attn_combine_kernel<128><<<cgrid, 128, 0, st>>>(part_acc, part_ml, static_cast<const bf16*>(gate), static_cast<bf16*>(out), n_q, Z);
+  else if (D == 64) attn_combine_kernel<64><<<cgrid, 64, 0, st>>>(part_acc, part_ml, static_cast<const bf16*>(gate), static_cast<bf16*>(out), n_q, Z);
+  else return -7;
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

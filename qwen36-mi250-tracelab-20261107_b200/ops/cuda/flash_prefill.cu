@@ -34,6 +34,9 @@ struct FlashParams {
   int n_q, n_kv;
   float scale_log2;       // D^-0.5 * log2(e)
   int* err;
+  int split_pages;        // > 0: blockIdx.z handles pages [z*split, (z+1)*split) and writes partials
+  float* part_acc;        // [T, n_q, gridDim.z, D] unnormalised partial outputs
+  float* part_ml;         // [T, n_q, gridDim.z, 2] (row maximum in natural-log units, row sum)
 };
 
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z, int w) {
@@ -103,7 +106,20 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int kh = blockIdx.y;
   const int pos0 = p.seg_pos0[seg];
   const int n_pos = min(R, seg_len - p0);
-  const int np = (pos0 + p0 + n_pos - 1) / FP_PAGE + 1;  // pages that hold visible keys
+  const int np_all = (pos0 + p0 + n_pos - 1) / FP_PAGE + 1;  // pages that hold visible keys
+  // split mode: a fixed number of consecutive pages per CTA, so the partition of a sequence's context
+  // depends on its own length only, never on what else is in the batch
+  const int first = p.split_pages > 0 ? static_cast<int>(blockIdx.z) * p.split_pages : 0;
+  const int np = p.split_pages > 0 ? max(0, min(np_all, first + p.split_pages) - first) : np_all;
+  if (np == 0) {  // nothing for this split: publish an empty partial and leave before any barrier / TMEM use
+    const int r = threadIdx.x;
+    if (r < 128 && r / GROUP < n_pos) {
+      const size_t row = static_cast<size_t>(seg_row0 + p0 + r / GROUP);
+      float* pm = p.part_ml + ((row * p.n_q + kh * GROUP + r % GROUP) * gridDim.z + blockIdx.z) * 2;
+      pm[0] = -INFINITY; pm[1] = 0.f;
+    }
+    return;
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -127,7 +143,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (elect_one()) {
       auto load_page = [&](int i) {
         const int s = i & 1;
-        int page = p.tables[static_cast<size_t>(seg) * p.max_pages + i];
+        int page = p.tables[static_cast<size_t>(seg) * p.max_pages + first + i];
         if (page < 0 || page >= p.num_pages) { atomicCAS(p.err, 0, ERR_BAD_INDEX); page = 0; }
         const int krow = ((page * 2 + 0) * p.n_kv + kh) * FP_PAGE;
         const int vrow = ((page * 2 + 1) * p.n_kv + kh) * FP_PAGE;
@@ -191,7 +207,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
       for (int c = 0; c < 64; c += 16) tmem_ld16(tmem_S + lane_base + c, sc + c);
       float mx = -INFINITY;
-      const int kbase = i * FP_PAGE;
+      const int kbase = (first + i) * FP_PAGE;
 #pragma unroll
       for (int j = 0; j < 64; ++j) {
         sc[j] = (kbase + j <= qpos) ? sc[j] * p.scale_log2 : -INFINITY;
@@ -234,6 +250,24 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     ok = ok && mbar_wait(acc_done, 0, p.err, ERR_WAIT_TMEM, abort_flag) && !*abort_flag;
     tc_fence_after();
+    if (ok && p.split_pages > 0) {
+      const size_t row = static_cast<size_t>(seg_row0 + p0 + lp);
+      const size_t slot = (row * p.n_q + kh * GROUP + head) * gridDim.z + blockIdx.z;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 16) {
+        float o[16];
+        tmem_ld16(tmem_O + lane_base + c, o);  // warp-collective: never predicated
+        if (row_valid) {
+          float4* dst = reinterpret_cast<float4*>(p.part_acc + slot * D + c);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+        }
+      }
+      if (row_valid) {
+        p.part_ml[slot * 2] = m_used * 0.6931471805599453f;  // log2 units -> natural log, as the combine expects
+        p.part_ml[slot * 2 + 1] = l;
+      }
+    } else
     if (ok) {
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       const size_t row = static_cast<size_t>(seg_row0 + p0 + lp);
@@ -294,14 +328,14 @@ int fp_make_map(CUtensorMap* m, const void* base, int rank, const cuuint64_t* di
 }
 
 template <int D, int GROUP>
-int fp_launch(const CUtensorMap& tq, const CUtensorMap& tkv, const FlashParams& p, int n_tiles, cudaStream_t st) {
+int fp_launch(const CUtensorMap& tq, const CUtensorMap& tkv, const FlashParams& p, int n_tiles, int gz, cudaStream_t st) {
   auto kern = flash_prefill_kernel<D, GROUP>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashCfg<D>::SMEM) != cudaSuccess) return -3;
     configured = true;
   }
-  kern<<<dim3(n_tiles, p.n_kv), 160, FlashCfg<D>::SMEM, st>>>(tq, tkv, p);
+  kern<<<dim3(n_tiles, p.n_kv, gz), 160, FlashCfg<D>::SMEM, st>>>(tq, tkv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 }  // namespace
@@ -311,7 +345,8 @@ int fp_launch(const CUtensorMap& tq, const CUtensorMap& tkv, const FlashParams& 
 // 128 / (n_q / n_kv) positions per tile; seg_pos0 / tables per segment. The span's K/V must already be in the pages.
 extern "C" int b200_flash_prefill(const void* q, const void* gate, const void* kv, void* out, const void* tiles,
                                   int n_tiles, const int* seg_pos0, const int* tables, int max_pages, int num_pages,
-                                  int T, int n_q, int n_kv, int D, int* err, cudaStream_t st) {
+                                  int T, int n_q, int n_kv, int D, int split_pages, int n_splits, float* part_acc,
+                                  float* part_ml, int* err, cudaStream_t st) {
   if (n_tiles <= 0) return 0;
   const int group = n_q / n_kv;
   if (group * n_kv != n_q || (D != 64 && D != 128 && D != 256) || 128 % group) return -7;
@@ -331,13 +366,15 @@ extern "C" int b200_flash_prefill(const void* q, const void* gate, const void* k
     if (fp_make_map(&tkv, kv, 2, dims, strides, box)) return -1;
   }
   FlashParams p{static_cast<const int4*>(tiles), seg_pos0, tables, max_pages, num_pages, static_cast<const bf16*>(gate),
-                static_cast<bf16*>(out), n_q, n_kv, 1.4426950408889634f / sqrtf(static_cast<float>(D)), err};
+                static_cast<bf16*>(out), n_q, n_kv, 1.4426950408889634f / sqrtf(static_cast<float>(D)), err,
+                split_pages, part_acc, part_ml};
+  const int gz = split_pages > 0 ? n_splits : 1;
 #define FP_GROUPS(DD)                                              \
   switch (group) {                                                 \
-    case 1: return fp_launch<DD, 1>(tq, tkv, p, n_tiles, st);      \
-    case 2: return fp_launch<DD, 2>(tq, tkv, p, n_tiles, st);      \
-    case 4: return fp_launch<DD, 4>(tq, tkv, p, n_tiles, st);      \
-    case 8: return fp_launch<DD, 8>(tq, tkv, p, n_tiles, st);      \
+    case 1: return fp_launch<DD, 1>(tq, tkv, p, n_tiles, gz, st);      \
+    case 2: return fp_launch<DD, 2>(tq, tkv, p, n_tiles, gz, st);      \
+    case 4: return fp_launch<DD, 4>(tq, tkv, p, n_tiles, gz, st);      \
+    case 8: return fp_launch<DD, 8>(tq, tkv, p, n_tiles, gz, st);      \
     default: return -7;                                            \
   }
   if (D == 256) { FP_GROUPS(256) }

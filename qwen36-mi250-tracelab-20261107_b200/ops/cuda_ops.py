@@ -62,7 +62,8 @@ class _Sig:
     b200_gdn_decode = [P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P]
     b200_attn_prep = [P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P, P]
     b200_paged_attn = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
-    b200_flash_prefill = [P, P, P, P, P, I, P, P, I, I, I, I, I, I, P, P]
+    b200_flash_prefill = [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, P, P, P]
+    b200_attn_combine = [P, P, P, P, I, I, I, I, P]
 
 
 def _ptr(t: torch.Tensor | None):
@@ -285,6 +286,8 @@ def attention(qkv, positions, seq_of_row, block_tables, kv_layer, q_norm, k_norm
             return flash_prefill(q, gate, kv_layer, block_tables, seg_starts, seg_pos0)
         return torch_ops.paged_attention(q, gate, kv_layer, block_tables, seg_starts, seg_pos0)
     B = rows // G
+    if head_dim in (64, 128, 256) and (n_q // n_kv) in (1, 2, 4, 8):
+        return flash_decode(q, gate, kv_layer, block_tables, positions, G)
     part_acc = torch.empty(rows, n_q, ATTN_Z, head_dim, dtype=torch.float32, device=dev)
     part_ml = torch.empty(rows, n_q, ATTN_Z, 2, dtype=torch.float32, device=dev)
     out = torch.empty(rows, n_q * head_dim, dtype=qkv.dtype, device=dev)
@@ -314,9 +317,46 @@ def flash_prefill(q: torch.Tensor, gate: torch.Tensor, kv_layer: torch.Tensor, b
     out = torch.empty(T, n_q * D, dtype=q.dtype, device=dev)
     rc = lib().b200_flash_prefill(
         _ptr(q), _ptr(gate), _ptr(kv_layer), _ptr(out), _ptr(tiles_t), len(tiles), _ptr(pos0_t), _ptr(block_tables),
-        block_tables.stride(0), kv_layer.shape[0], T, n_q, n_kv, D, _ptr(err_word(dev)), _stream(),
+        block_tables.stride(0), kv_layer.shape[0], T, n_q, n_kv, D, 0, 1, None, None, _ptr(err_word(dev)), _stream(),
     )
     _check(rc, "flash_prefill")
+    return out
+
+
+SPLIT_PAGES = 8  # pages (512 tokens) of context per decode-attention CTA: fixed, part of the numerics contract
+_decode_tiles: dict = {}
+
+
+def flash_decode(q: torch.Tensor, gate: torch.Tensor, kv_layer: torch.Tensor, block_tables: torch.Tensor,
+                 positions: torch.Tensor, G: int) -> torch.Tensor:
+    """Decode / verify attention (``G`` rows per sequence) on the tcgen05 flash kernel with split context.
+
+    Each sequence is one query tile (its ``G`` positions x the GQA group fill the first rows of the 128-row
+    MMA tile); the context is cut into runs of ``SPLIT_PAGES`` pages handled by separate CTAs whose partial
+    results are merged in order. Only device tensors are touched, so the call can be captured in a CUDA graph."""
+    rows, n_q, D = q.shape
+    n_kv = kv_layer.shape[2]
+    B = rows // G
+    dev = q.device
+    key = (B, G, dev.index)
+    if key not in _decode_tiles:
+        b = torch.arange(B, dtype=torch.int32)
+        _decode_tiles[key] = torch.stack([b, torch.zeros_like(b), b * G, torch.full_like(b, G)], 1).contiguous().to(dev)
+    tiles = _decode_tiles[key]
+    n_splits = max(1, (block_tables.shape[1] + SPLIT_PAGES - 1) // SPLIT_PAGES)
+    pos0 = positions[::G].to(torch.int32)
+    part_acc = torch.empty(rows, n_q, n_splits, D, dtype=torch.float32, device=dev)
+    part_ml = torch.empty(rows, n_q, n_splits, 2, dtype=torch.float32, device=dev)
+    out = torch.empty(rows, n_q * D, dtype=q.dtype, device=dev)
+    L = lib()
+    rc = L.b200_flash_prefill(
+        _ptr(q), _ptr(gate), _ptr(kv_layer), None, _ptr(tiles), B, _ptr(pos0), _ptr(block_tables),
+        block_tables.stride(0), kv_layer.shape[0], rows, n_q, n_kv, D, SPLIT_PAGES, n_splits, _ptr(part_acc),
+        _ptr(part_ml), _ptr(err_word(dev)), _stream(),
+    )
+    _check(rc, "flash_decode")
+    _check(L.b200_attn_combine(_ptr(part_acc), _ptr(part_ml), _ptr(gate), _ptr(out), rows, n_q, D, n_splits, _stream()),
+           "attn_combine")
     return out
 
 

@@ -58,27 +58,32 @@ class DecodeGraphs:
         self.sizes = sorted(b for b in engine.cfg.decode_buckets if b <= max(engine.cfg.max_seqs, 1)) or [engine.cfg.max_seqs]
         if self.sizes[-1] < engine.cfg.max_seqs:
             self.sizes.append(engine.cfg.max_seqs)
-        # page-table width of the graphs: enough for the configured context, bounded to keep the buffers small
-        self.width = min(engine.max_pages_per_seq, 4096)
-        self.buckets: dict[int, _Bucket] = {}
-        self.errors: dict[int, str] = {}
+        # page-table widths of the graphs (context classes of 4k / 32k / 256k tokens): the decode attention
+        # launches one CTA per 8 pages of table width, so short contexts should not pay for long tables
+        cap = engine.max_pages_per_seq
+        self.widths = sorted({min(w, cap) for w in (64, 512, 4096)} | ({cap} if cap <= 4096 else set()))
+        self.width = self.widths[-1]
+        self.buckets: dict = {}
+        self.errors: dict = {}
 
     def usable(self, gens) -> bool:
         if len(gens) > self.sizes[-1]:
             return False
         return all(len(g.pages) <= self.width for g in gens)
 
-    def _bucket(self, n: int) -> _Bucket | None:
+    def _bucket(self, n: int, pages: int = 0) -> _Bucket | None:
         size = next(s for s in self.sizes if s >= n)
-        b = self.buckets.get(size)
-        if b is None and size not in self.errors:
-            b = _Bucket(self.engine, size, self.width)
+        width = next(w for w in self.widths if w >= pages)
+        key = (size, width)
+        b = self.buckets.get(key)
+        if b is None and key not in self.errors:
+            b = _Bucket(self.engine, size, width)
             try:
                 b.capture(self.engine)
             except Exception as e:  # capture failure: remember it, run eagerly (reference: model.py:2009-2029)
-                self.errors[size] = repr(e)
+                self.errors[key] = repr(e)
                 return None
-            self.buckets[size] = b
+            self.buckets[key] = b
         return b
 
     def warm(self) -> None:
@@ -87,7 +92,7 @@ class DecodeGraphs:
 
     def run(self, gens, tokens, positions):
         n = len(gens)
-        b = self._bucket(n)
+        b = self._bucket(n, max(len(g.pages) for g in gens))
         if b is None:
             eng = self.engine
             batch = PackedBatch.uniform(tokens, positions, [g.slot for g in gens], eng._table(gens), 1, eng.device)
