@@ -53,8 +53,25 @@ __global__ void gdn_conv_step_kernel(const bf16* mixed, int ld, const int* slots
 }
 
 // ------------------------------------------------------------------ delta-rule step
+// The DK x DV fp32 state tile of one (sequence, value head) is brought into shared memory by one bulk
+// async copy (TMA, no registers held while it is in flight), updated in place for the G rows of the step,
+// and written back by one bulk store; with 64 KB per CTA three CTAs fit an SM, so loads, updates and
+// stores of different tiles overlap. Thread (p, c) owns column c for key rows [p*DK/4, (p+1)*DK/4).
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
 template <int DK, int DV>
-__global__ void __launch_bounds__(4 * DV, 2)
+__global__ void __launch_bounds__(4 * DV, 3)
 gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
                 const bf16* mixed,      // [B*G, ld] z at column z_off, b at b_off, a at a_off
                 int ld, int z_off, int b_off, int a_off,
@@ -62,8 +79,10 @@ gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
                 const float* A_log, const float* dt_bias, const bf16* gnorm_w,
                 bf16* out,              // [B*G, HV*DV]
                 float* ring_rec,        // optional [B, G, HV, DK, DV]
-                int HK, int HV, int G, float eps) {
+                int HK, int HV, int G, float eps, int* err) {
   constexpr int KP = DK / 4;  // key rows per partition
+  constexpr uint32_t TILE_BYTES = DK * DV * sizeof(float);
+  extern __shared__ __align__(128) float sS[];
   const int b = blockIdx.y, h = blockIdx.x;
   const int c = threadIdx.x % DV, p = threadIdx.x / DV;
   const int hk = h / (HV / HK);
@@ -76,10 +95,18 @@ gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
   __shared__ float red[4][DV][2];
   __shared__ float nred[4][3];
   __shared__ float wred[4 * DV / 32];
+  __shared__ uint64_t bar;
+  __shared__ int s_abort;
 
-  float s[KP];
-#pragma unroll
-  for (int i = 0; i < KP; ++i) s[i] = S[static_cast<size_t>(p * KP + i) * DV + c];
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    s_abort = 0;
+    mbar_fence_init();
+    mbar_expect_tx(&bar, TILE_BYTES);
+    bulk_load(sS, S, TILE_BYTES, &bar);
+  }
+  __syncthreads();
+  if (!mbar_wait(&bar, 0, err, ERR_WAIT_FULL, &s_abort)) return;  // status recorded; the state is left as it was
 
   for (int j = 0; j < G; ++j) {
     const size_t row = static_cast<size_t>(b) * G + j;
@@ -109,13 +136,14 @@ gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
     const float decay = __expf(-__expf(A_log[h]) * softplus_f(a + dt_bias[h]));
     const float beta = sigmoid_f(bb);
 
-    // partial S^T k and S^T q over this thread's key rows (state decayed first)
+    // pass 1: partial S^T k and S^T q over this thread's key rows (state decayed first)
     float pk = 0.f, pq = 0.f;
-#pragma unroll
+    float* col = sS + static_cast<size_t>(p * KP) * DV + c;
+#pragma unroll 8
     for (int i = 0; i < KP; ++i) {
-      s[i] *= decay;
-      pk += s[i] * (sk[p * KP + i] * ks);
-      pq += s[i] * (sq[p * KP + i] * qs);
+      const float v = col[i * DV] * decay;
+      pk += v * (sk[p * KP + i] * ks);
+      pq += v * (sq[p * KP + i] * qs);
     }
     red[p][c][0] = pk; red[p][c][1] = pq;
     __syncthreads();
@@ -123,8 +151,9 @@ gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
     const float sq_mem = (red[0][c][1] + red[1][c][1]) + (red[2][c][1] + red[3][c][1]);
     const float v = __bfloat162float(co[2 * key_dim + h * DV + c]);
     const float delta = (v - kv_mem) * beta;
-#pragma unroll
-    for (int i = 0; i < KP; ++i) s[i] += (sk[p * KP + i] * ks) * delta;
+    // pass 2: S = decay * S + k delta^T, in place
+#pragma unroll 8
+    for (int i = 0; i < KP; ++i) col[i * DV] = col[i * DV] * decay + (sk[p * KP + i] * ks) * delta;
     const float o = sq_mem + delta * kq;  // = S_new^T q
 
     // gated RMSNorm over the head's DV outputs
@@ -133,6 +162,7 @@ gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
     float ss = (p == 0) ? of * of : 0.f;
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) wred[threadIdx.x >> 5] = ss;
+    if (ring_rec) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
     float tot = 0.f;
 #pragma unroll
@@ -143,14 +173,20 @@ gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
       const float nb = __bfloat162float(__float2bfloat16(of * inv));
       out[row * (HV * DV) + h * DV + c] = __float2bfloat16(__bfloat162float(gnorm_w[c]) * nb * silu_f(z));
     }
-    if (ring_rec) {
-      float* R = ring_rec + (((static_cast<size_t>(b) * G + j) * HV + h) * DK) * DV;
-#pragma unroll
-      for (int i = 0; i < KP; ++i) R[static_cast<size_t>(p * KP + i) * DV + c] = s[i];
+    if (ring_rec) {  // keep the state after this row; the tile may only change again once the store has read it
+      if (threadIdx.x == 0) {
+        bulk_store(ring_rec + (((static_cast<size_t>(b) * G + j) * HV + h) * DK) * DV, sS, TILE_BYTES);
+        bulk_store_wait_read();
+      }
+      __syncthreads();
     }
   }
-#pragma unroll
-  for (int i = 0; i < KP; ++i) S[static_cast<size_t>(p * KP + i) * DV + c] = s[i];
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    bulk_store(S, sS, TILE_BYTES);
+    bulk_store_wait_read();
+  }
 }
 
 }  // namespace b200
@@ -160,7 +196,7 @@ using namespace b200;
 extern "C" int b200_gdn_decode(const void* mixed, int ld, const int* slots, void* conv_state, void* rec_state,
                                const void* conv_w, const float* A_log, const float* dt_bias, const void* gnorm_w,
                                void* conv_out, void* out, void* ring_conv, float* ring_rec, int B, int G, int HK, int HV,
-                               int DK, int DV, int KW, float eps, cudaStream_t st) {
+                               int DK, int DV, int KW, float eps, int* err, cudaStream_t st) {
   if (B <= 0) return 0;
   const int key_dim = HK * DK, value_dim = HV * DV, C = 2 * key_dim + value_dim;
   if (KW != 4) return -7;
@@ -171,10 +207,19 @@ extern "C" int b200_gdn_decode(const void* mixed, int ld, const int* slots, void
   dim3 grid(HV, B);
   const int z_off = C, b_off = C + value_dim, a_off = C + value_dim + HV;
 #define LAUNCH_STEP(DKV)                                                                                           \
-  gdn_step_kernel<DKV, DKV><<<grid, 4 * DKV, 0, st>>>(                                                             \
-      static_cast<const bf16*>(conv_out), static_cast<const bf16*>(mixed), ld, z_off, b_off, a_off, slots,         \
-      static_cast<float*>(rec_state), A_log, dt_bias, static_cast<const bf16*>(gnorm_w), static_cast<bf16*>(out), \
-      ring_rec, HK, HV, G, eps)
+  do {                                                                                                             \
+    auto kern = gdn_step_kernel<DKV, DKV>;                                                                         \
+    constexpr int smem = DKV * DKV * 4;                                                                            \
+    static bool configured = false;                                                                                \
+    if (!configured) {                                                                                             \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3; \
+      configured = true;                                                                                           \
+    }                                                                                                              \
+    kern<<<grid, 4 * DKV, smem, st>>>(                                                                             \
+        static_cast<const bf16*>(conv_out), static_cast<const bf16*>(mixed), ld, z_off, b_off, a_off, slots,       \
+        static_cast<float*>(rec_state), A_log, dt_bias, static_cast<const bf16*>(gnorm_w),                         \
+        static_cast<bf16*>(out), ring_rec, HK, HV, G, eps, err);                                                   \
+  } while (0)
   if (DK == 128 && DV == 128) LAUNCH_STEP(128);
   else if (DK == 32 && DV == 32) LAUNCH_STEP(32);
   else if (DK == 64 && DV == 64) LAUNCH_STEP(64);

@@ -59,7 +59,7 @@ class _Sig:
     b200_moe_plan = [P, P, I, I, I, P, P, P, P, I, P, P, P, P]
     b200_moe_gather = [P, P, P, I, I, I, I, P, P]
     b200_moe_combine = [P, P, P, I, I, I, P, P, P]
-    b200_gdn_decode = [P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P]
+    b200_gdn_decode = [P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P]
     b200_attn_prep = [P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P, P]
     b200_paged_attn = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
     b200_flash_prefill = [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, P, P, P]
@@ -246,7 +246,8 @@ def gdn_decode(mixed, slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnor
     rc = lib().b200_gdn_decode(
         _ptr(mixed), mixed.stride(0), _ptr(slots32), _ptr(conv_state), _ptr(rec_state), _ptr(conv_w), _ptr(A_log),
         _ptr(dt_bias), _ptr(gnorm_w), _ptr(conv_out), _ptr(out), _ptr(ring[0]) if ring else None,
-        _ptr(ring[1]) if ring else None, B, G, n_k, n_v, dk, dv, conv_w.shape[1], eps, _stream(),
+        _ptr(ring[1]) if ring else None, B, G, n_k, n_v, dk, dv, conv_w.shape[1], eps, _ptr(err_word(mixed.device)),
+        _stream(),
     )
     _check(rc, "gdn_decode")
     return out

@@ -53,3 +53,34 @@ def test_gpu_session_tail_reuse_matches_cold():
     c = eng.generate([nxt], s)[0]
     assert c.cached_tokens >= len(p)
     assert len(c.output) == 9
+
+
+def test_gpu_mtp_speculation_keeps_outputs():
+    """Chained MTP verify steps on the CUDA kernels (G rows per sequence, GDN state ring) never change tokens."""
+    from b200serve.config import EngineConfig, ModelConfig
+    from b200serve.models.checkpoint import random_weights
+    from b200serve.ops import cuda_ops
+    from b200serve.sched.engine import Engine
+    from b200serve.sched.request import Sampling
+
+    cfg = ModelConfig.tiny(head_dim=64, num_attention_heads=4, num_key_value_heads=1)
+    w = random_weights(cfg, seed=0, device="cuda", dtype=torch.bfloat16, std=0.05, lm_head_std=0.5)
+    prompts = _prompts(4, seed=21)
+    s = Sampling(max_tokens=20, ignore_eos=True)
+
+    def run(mtp, k=0):
+        ecfg = EngineConfig(max_model_len=1024, prefill_chunk_tokens=64, max_seqs=8, mtp=mtp, spec_k=k, kv_pages=256,
+                            decode_buckets=(4, 8))
+        eng = Engine(w, ecfg)
+        return eng, [g.output for g in eng.generate(prompts, s)]
+
+    _, plain = run(False)
+    eng, spec = run(True, 2)
+    truth = {tuple(p): o for p, o in zip(prompts, plain)}
+    assert spec == plain
+    assert eng.stats["mtp_verify_steps"] > 0
+    eng2 = Engine(w, EngineConfig(max_model_len=1024, prefill_chunk_tokens=64, max_seqs=8, mtp=True, spec_k=3, kv_pages=256))
+    eng2.spec.draft_override = lambda g, k: truth[tuple(g.prompt)][len(g.output):len(g.output) + k]
+    forced = [g.output for g in eng2.generate(prompts, s)]
+    assert forced == plain and eng2.stats["mtp_accepted"] == eng2.stats["mtp_proposed"] > 0
+    cuda_ops.check_errors(torch.device("cuda"))
