@@ -27,7 +27,7 @@ constexpr int BM = 128;  // weight rows per tile (TMEM lanes)
 constexpr int BK = 64;   // bf16 per operand row per stage (128 bytes)
 constexpr int UMMA_K = 16;
 
-enum Epilogue : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_ARGMAX = 3, EPI_ALLREDUCE = 4 };
+enum Epilogue : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_ARGMAX = 3, EPI_ALLREDUCE = 4, EPI_SCATTER = 5 };
 
 struct GemmParams {
   int N;             // weight rows (per expert when grouped)
@@ -43,6 +43,8 @@ struct GemmParams {
   int* err;          // error word (0 = ok)
   const bf16* residual; // EPI_ALLREDUCE: optional [T, ldo] added after the cross-rank sum
   CommCtx comm;      // EPI_ALLREDUCE: the rank group's symmetric buffers
+  const int2* meta;  // EPI_SCATTER: (source rank, pair slot) of every sorted row
+  bf16* pair_out[MAX_RANKS];  // EPI_SCATTER: every rank's pair-output buffer [pairs, ldo] as mapped here
 };
 
 template <int BT, int EPI>
@@ -227,6 +229,18 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             }
             if (lane == 0) { red_max[q][c + j] = m; red_idx[q][c + j] = idx; }
           }
+        } else if (EPI == EPI_SCATTER) {
+          // expert-parallel combine: each output row goes straight to the rank that owns the token,
+          // into the slot of its (token, pair) - a peer store over NVLink when that rank is not this one
+          if (n_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (c + j < nrows) {
+                const int2 m = p.meta[row0 + c + j];
+                p.pair_out[m.x][static_cast<size_t>(m.y) * p.ldo + n] = __float2bfloat16(v[j]);
+              }
+            }
+          }
         } else if (n_ok) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -369,7 +383,7 @@ extern "C" int b200_gemm_dense(const void* X, const void* W, void* out, int T, i
   const int w_rows = (epi == EPI_SILU_MUL) ? up_offset + N : N;
   if (make_map(&tw, W, K, w_rows, 0, ldw, 0, BM)) return -1;
   if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
-  GemmParams p{N, K, T, ldo, out, nullptr, nullptr, up_offset, part_max, part_idx, err, nullptr, CommCtx{}};
+  GemmParams p{N, K, T, ldo, out, nullptr, nullptr, up_offset, part_max, part_idx, err, nullptr, CommCtx{}, nullptr, {}};
   const int gy = (T + bt - 1) / bt;
   switch (epi) {
     case EPI_BF16: return dispatch_bt<EPI_BF16, false>(bt, tw, tx, p, gy, st);
@@ -389,7 +403,7 @@ extern "C" int b200_gemm_grouped(const void* X, const void* W, void* out, int ca
   CUtensorMap tw, tx;
   if (make_map(&tw, W, K, w_rows, E, K, static_cast<uint64_t>(w_rows) * K, BM)) return -1;
   if (make_map(&tx, X, K, cap, 0, K, 0, bt)) return -1;
-  GemmParams p{N, K, cap, ldo, out, reinterpret_cast<const int4*>(tiles), n_tiles, up_offset, nullptr, nullptr, err, nullptr, CommCtx{}};
+  GemmParams p{N, K, cap, ldo, out, reinterpret_cast<const int4*>(tiles), n_tiles, up_offset, nullptr, nullptr, err, nullptr, CommCtx{}, nullptr, {}};
   switch (epi) {
     case EPI_BF16: return dispatch_bt<EPI_BF16, true>(bt, tw, tx, p, max_tiles, st);
     case EPI_SILU_MUL: return dispatch_bt<EPI_SILU_MUL, true>(bt, tw, tx, p, max_tiles, st);
@@ -409,8 +423,23 @@ extern "C" int b200_gemm_allreduce(const CommCtx* ctx, const void* X, const void
   CUtensorMap tw, tx;
   if (make_map(&tw, W, K, N, 0, ldw, 0, BM)) return -1;
   if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
-  GemmParams p{N, K, T, N, out, nullptr, nullptr, 0, nullptr, nullptr, ctx->err, static_cast<const bf16*>(residual), *ctx};
+  GemmParams p{N, K, T, N, out, nullptr, nullptr, 0, nullptr, nullptr, ctx->err, static_cast<const bf16*>(residual), *ctx, nullptr, {}};
   return dispatch_bt<EPI_ALLREDUCE, false>(bt, tw, tx, p, gy, st);
+}
+
+// Expert-parallel down projection: grouped GEMM whose epilogue scatters every output row to the owner of its
+// token (`meta[row] = (rank, pair slot)`, `pair_out[rank]` = that rank's [pairs, N] buffer as mapped in this process).
+extern "C" int b200_gemm_grouped_scatter(const void* X, const void* W, int cap, int E, int N, int K, int bt,
+                                         const void* tiles, const int* n_tiles, int max_tiles, const void* meta,
+                                         void* const* pair_out, int world, int* err, cudaStream_t st) {
+  if (max_tiles <= 0) return 0;
+  CUtensorMap tw, tx;
+  if (make_map(&tw, W, K, N, E, K, static_cast<uint64_t>(N) * K, BM)) return -1;
+  if (make_map(&tx, X, K, cap, 0, K, 0, bt)) return -1;
+  GemmParams p{N, K, cap, N, nullptr, reinterpret_cast<const int4*>(tiles), n_tiles, 0, nullptr, nullptr, err, nullptr,
+               CommCtx{}, static_cast<const int2*>(meta), {}};
+  for (int r = 0; r < world && r < MAX_RANKS; ++r) p.pair_out[r] = static_cast<bf16*>(pair_out[r]);
+  return dispatch_bt<EPI_SCATTER, true>(bt, tw, tx, p, max_tiles, st);
 }
 
 extern "C" int b200_argmax_finish(const float* part_max, const int* part_idx, int n_tiles, int T, int64_t* out,
@@ -460,7 +489,7 @@ extern "C" int b200_lm_head_argmax_noalloc(const void* X, const void* W, int64_t
   CUtensorMap tw, tx;
   if (make_map(&tw, W, K, V, 0, ldw, 0, BM)) return -1;
   if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
-  GemmParams p{V, K, T, 0, nullptr, nullptr, nullptr, 0, part_max, part_idx, err, nullptr, CommCtx{}};
+  GemmParams p{V, K, T, 0, nullptr, nullptr, nullptr, 0, part_max, part_idx, err, nullptr, CommCtx{}, nullptr, {}};
   const int rc = dispatch_bt<EPI_ARGMAX, false>(bt, tw, tx, p, (T + bt - 1) / bt, st);
   if (rc) return rc;
   argmax_finish_kernel<<<T, 256, 0, st>>>(part_max, part_idx, n_tiles, T, out_idx, out_val);

@@ -1,0 +1,177 @@
+"""Expert-parallel MoE block for token-sharded activations (each rank owns different rows).
+
+``EpMoE.forward`` runs, on every rank of the group and in the same order: router GEMM + top-k on the
+rank's own rows, a count exchange, the dispatch all-to-all (rows stored straight into the hosting
+rank's expert-sorted buffer over NVLink), the grouped gate/up GEMM, the grouped down GEMM whose
+epilogue scatters every output row back to its owner (the combine all-to-all), and the top-k
+weighted sum. Kernels: ``ops/cuda/ep_moe.cu`` and the ``EPI_SCATTER`` epilogue of
+``ops/cuda/gemm_tcgen05.cu``; buffers are CUDA IPC symmetric memory as in ``parallel/symm.py``.
+The reference has no expert parallelism; this is the BASELINE configuration's EP path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..ops import cuda_ops
+from .symm import MAX_RANKS, _lib as _symm_lib
+
+
+class EpCtx(ctypes.Structure):
+    _fields_ = [
+        ("xs", ctypes.c_void_p * MAX_RANKS),
+        ("meta", ctypes.c_void_p * MAX_RANKS),
+        ("pair_out", ctypes.c_void_p * MAX_RANKS),
+        ("counts_all", ctypes.c_void_p * MAX_RANKS),
+        ("flags", ctypes.c_void_p * MAX_RANKS),
+        ("epoch", ctypes.c_void_p),
+        ("err", ctypes.c_void_p),
+        ("rank", ctypes.c_int),
+        ("world", ctypes.c_int),
+        ("E", ctypes.c_int),
+        ("per", ctypes.c_int),
+        ("cap_rows", ctypes.c_int),
+        ("max_pairs", ctypes.c_int),
+    ]
+
+
+def _lib():
+    L = _symm_lib()
+    if not getattr(L, "_ep_ready", False):
+        P, I = ctypes.c_void_p, ctypes.c_int
+        C = ctypes.POINTER(EpCtx)
+        L.b200_ep_counts.argtypes = [C, P, P]
+        L.b200_ep_plan.argtypes = [C, I, P, P, P, P, I, P, P]
+        L.b200_ep_dispatch.argtypes = [C, P, P, P, P, I, I, I, P]
+        L.b200_ep_combine.argtypes = [C, P, I, I, I, P, P]
+        L.b200_gemm_grouped_scatter.argtypes = [P, P, I, I, I, I, I, P, P, I, P, P, I, P, P]
+        for n in ("b200_ep_counts", "b200_ep_plan", "b200_ep_dispatch", "b200_ep_combine", "b200_gemm_grouped_scatter",
+                  "b200_ep_ctx_size"):
+            getattr(L, n).restype = I
+        assert L.b200_ep_ctx_size() == ctypes.sizeof(EpCtx), "EpCtx layout mismatch"
+        L._ep_ready = True
+    return L
+
+
+class EpMoE:
+    def __init__(self, device: torch.device, group, n_experts: int, hidden: int, top_k: int, max_rows: int) -> None:
+        """``max_rows``: most rows any rank brings to one call; buffers are sized for the worst case in which
+        every pair of every rank lands on one host."""
+        import torch.distributed as dist
+
+        self.device, self.group = device, group
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.E, self.H, self.top_k = n_experts, hidden, top_k
+        self.P = top_k + 1
+        self.per = n_experts // self.world
+        self.max_pairs = max_rows * self.P
+        self.cap_rows = self.max_pairs * self.world
+        L = _lib()
+        Etot = n_experts + 1
+        sizes = {
+            "xs": self.cap_rows * hidden * 2,
+            "meta": self.cap_rows * 8,
+            "pair_out": self.max_pairs * hidden * 2,
+            "counts_all": self.world * Etot * 4,
+            "flags": 3 * MAX_RANKS * 4,
+            "epoch": 16,
+        }
+        self._own, self._opened = {}, []
+        with torch.cuda.device(device):
+            for name, nbytes in sizes.items():
+                p = ctypes.c_void_p()
+                if L.b200_symm_alloc(ctypes.byref(p), nbytes):
+                    raise RuntimeError(f"symmetric allocation of {nbytes} bytes failed")
+                self._own[name] = p.value
+            torch.cuda.synchronize(device)
+            peers = {k: [self._own[k]] * 1 for k in ("xs", "meta", "pair_out", "counts_all", "flags")}
+            if self.world > 1:
+                handles = {}
+                for name in peers:
+                    buf = ctypes.create_string_buffer(64)
+                    if L.b200_symm_export(self._own[name], buf):
+                        raise RuntimeError("cudaIpcGetMemHandle failed")
+                    handles[name] = buf.raw
+                gathered: list = [None] * self.world
+                dist.all_gather_object(gathered, handles, group=group)
+                peers = {k: [] for k in peers}
+                for r in range(self.world):
+                    for name in peers:
+                        if r == self.rank:
+                            peers[name].append(self._own[name])
+                            continue
+                        p = ctypes.c_void_p()
+                        if L.b200_symm_import(gathered[r][name], ctypes.byref(p)):
+                            raise RuntimeError(f"cudaIpcOpenMemHandle failed for rank {r}")
+                        peers[name].append(p.value)
+                        self._opened.append(p.value)
+                dist.barrier(group=group)
+        ctx = EpCtx()
+        for r in range(self.world):
+            for name in peers:
+                getattr(ctx, name)[r] = peers[name][r]
+        ctx.epoch = self._own["epoch"]
+        ctx.err = cuda_ops.err_word(device).data_ptr()
+        ctx.rank, ctx.world, ctx.E, ctx.per = self.rank, self.world, n_experts, self.per
+        ctx.cap_rows, ctx.max_pairs = self.cap_rows, self.max_pairs
+        self.ctx = ctx
+        self._pair_out_ptrs = (ctypes.c_void_p * MAX_RANKS)(*[peers["pair_out"][r] if r < self.world else None
+                                                             for r in range(MAX_RANKS)])
+
+    def local_experts(self, w_gate_up: torch.Tensor, w_down: torch.Tensor):
+        """This rank's slice of full stacked expert weights ``[E + 1, ...]``: its routed experts, then the shared one."""
+        ids = list(range(self.rank * self.per, (self.rank + 1) * self.per)) + [self.E]
+        sel = torch.tensor(ids, device=w_gate_up.device)
+        return w_gate_up[sel].contiguous(), w_down[sel].contiguous()
+
+    def forward(self, x: torch.Tensor, router: torch.Tensor, w_gate_up_local: torch.Tensor,
+                w_down_local: torch.Tensor) -> torch.Tensor:
+        T, H = x.shape
+        assert T * self.P <= self.max_pairs and H == self.H
+        dev, L, st = x.device, _lib(), torch.cuda.current_stream().cuda_stream
+        K = cuda_ops.lib()
+        E, Pn, Etot = self.E, self.P, self.E + 1
+        inter = w_down_local.shape[2]
+        n_pairs = T * Pn
+        logits = cuda_ops.linear(x, router, out_dtype=torch.float32)
+        wts = torch.empty(T, Pn, dtype=torch.float32, device=dev)
+        idx = torch.empty(T, Pn, dtype=torch.int32, device=dev)
+        ints = torch.zeros(3 * Etot + 2, dtype=torch.int32, device=dev)
+        counts, send_base, cursors = ints[:Etot], ints[Etot : 2 * Etot], ints[2 * Etot : 3 * Etot]
+        n_tiles, n_rows = ints[3 * Etot : 3 * Etot + 1], ints[3 * Etot + 1 :]
+        rc = K.b200_moe_route(logits.data_ptr(), logits.stride(0), T, E, self.top_k, 1, wts.data_ptr(), idx.data_ptr(),
+                              counts.data_ptr(), Etot, None, st)
+        bt = cuda_ops.moe_bt(T * self.world, Pn, E)
+        max_tiles = self.per + 1 + self.cap_rows // bt + 1
+        tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device=dev)
+        C = ctypes.byref(self.ctx)
+        rc |= L.b200_ep_counts(C, counts.data_ptr(), st)
+        rc |= L.b200_ep_plan(C, bt, send_base.data_ptr(), cursors.data_ptr(), tiles.data_ptr(), n_tiles.data_ptr(),
+                             max_tiles, n_rows.data_ptr(), st)
+        rc |= L.b200_ep_dispatch(C, x.data_ptr(), idx.data_ptr(), send_base.data_ptr(), cursors.data_ptr(), n_pairs, Pn,
+                                 H, st)
+        act = torch.empty(self.cap_rows, inter, dtype=x.dtype, device=dev)
+        err = cuda_ops.err_word(dev)
+        rc |= K.b200_gemm_grouped(self._own["xs"], w_gate_up_local.data_ptr(), act.data_ptr(), self.cap_rows,
+                                  self.per + 1, inter, 2 * inter, H, inter, cuda_ops.EPI_SILU_MUL, inter, bt,
+                                  tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), st)
+        rc |= L.b200_gemm_grouped_scatter(act.data_ptr(), w_down_local.data_ptr(), self.cap_rows, self.per + 1, H,
+                                          inter, bt, tiles.data_ptr(), n_tiles.data_ptr(), max_tiles,
+                                          self._own["meta"], self._pair_out_ptrs, self.world, err.data_ptr(), st)
+        out = torch.empty_like(x)
+        rc |= L.b200_ep_combine(C, wts.data_ptr(), T, Pn, H, out.data_ptr(), st)
+        if rc:
+            raise cuda_ops.KernelError(f"expert-parallel MoE failed with code {rc}")
+        return out
+
+    def close(self) -> None:
+        L = _lib()
+        torch.cuda.synchronize(self.device)
+        for p in self._opened:
+            L.b200_symm_close(p)
+        for p in self._own.values():
+            L.b200_symm_free(p)
+        self._opened, self._own = [], {}

@@ -168,7 +168,51 @@ def mode_lockstep(rank, world, dev):
     print("lockstep: leader finished after", steps, "steps", flush=True)
 
 
-MODES = {"allreduce": mode_allreduce, "tp_model": mode_tp_model, "lockstep": mode_lockstep}
+def mode_ep_moe(rank, world, dev):
+    """Expert-parallel MoE on token-sharded rows: dispatch / combine over peer memory vs the PyTorch block."""
+    from b200serve.ops import cuda_ops, torch_ops
+    from b200serve.parallel.ep import EpMoE
+
+    E, H, I, k = 64, 512, 256, 4
+    g = torch.Generator(device=dev).manual_seed(11)  # weights: same on every rank
+    router = (torch.randn(E + 1, H, device=dev, generator=g) * 0.3).to(torch.bfloat16)
+    wgu = (torch.randn(E + 1, 2 * I, H, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    wd = (torch.randn(E + 1, H, I, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    ep = EpMoE(dev, dist.group.WORLD, E, H, k, max_rows=300)
+    lgu, ld = ep.local_experts(wgu, wd)
+    gx = torch.Generator(device=dev).manual_seed(100 + rank)  # rows: different on every rank
+    for T in (1, 37 + 5 * rank, 256, 0 if rank == 0 else 9):
+        x = torch.randn(T, H, device=dev, generator=gx).to(torch.bfloat16)
+        got = ep.forward(x, router, lgu, ld)
+        cuda_ops.check_errors(dev)
+        if T:
+            logits = cuda_ops.linear(x, router, out_dtype=torch.float32)
+            wts, idx = torch_ops.router_topk(logits[:, :E], k)
+            wts = torch.cat([wts, torch.sigmoid(logits[:, E:E + 1])], 1).to(torch.bfloat16)
+            idx = torch.cat([idx, torch.full_like(idx[:, :1], E)], 1)
+            ref = torch_ops.moe_experts(x.float(), wts.float(), idx, wgu.float(), wd.float())
+            err = (got.float() - ref).abs().max().item()
+            assert err <= 3e-2 * max(1.0, ref.abs().max().item()), (T, err)
+    # device-timed, max over ranks
+    x = torch.randn(128, H, device=dev, generator=gx).to(torch.bfloat16)
+    for _ in range(3):
+        ep.forward(x, router, lgu, ld)
+    torch.cuda.synchronize(); dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(20):
+        ep.forward(x, router, lgu, ld)
+    b.record(); torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / 20 * 1e3], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print(f"ep_moe world={world} 128 rows/rank E={E}: {t.item():.1f} us per block", flush=True)
+    cuda_ops.check_errors(dev)
+    dist.barrier()
+    ep.close()
+
+
+MODES = {"allreduce": mode_allreduce, "ep_moe": mode_ep_moe, "tp_model": mode_tp_model, "lockstep": mode_lockstep}
 
 if __name__ == "__main__":
     mode = sys.argv[1]

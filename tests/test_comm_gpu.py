@@ -72,3 +72,36 @@ def test_two_rank_allreduce_over_nvlink():
                         "--master-addr", "127.0.0.1", "--master-port", "29611", str(ROOT / "tests/dist_worker.py"),
                         "allreduce"], capture_output=True, text=True, timeout=600, env={**os.environ, **env})
     assert r.returncode == 0 and "OK allreduce" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_expert_parallel_moe_loopback_matches_the_local_block():
+    """One-rank group: dispatch, scatter epilogue and combine run against this GPU's own buffers."""
+    from b200serve.ops import cuda_ops
+    from b200serve.parallel.ep import EpMoE
+
+    dev = torch.device("cuda")
+    E, H, I, k = 16, 256, 128, 2
+    g = torch.Generator(device=dev).manual_seed(3)
+    router = (torch.randn(E + 1, H, device=dev, generator=g) * 0.3).to(torch.bfloat16)
+    wgu = (torch.randn(E + 1, 2 * I, H, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    wd = (torch.randn(E + 1, H, I, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    ep = EpMoE(dev, None, E, H, k, max_rows=200)
+    lgu, ld = ep.local_experts(wgu, wd)
+    for T in (1, 50, 200):
+        x = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+        got = ep.forward(x, router, lgu, ld)
+        ref = cuda_ops.moe_block(x, router, wgu, wd, E, k, True)
+        cuda_ops.check_errors(dev)
+        assert torch.equal(got, ref), (T, (got.float() - ref.float()).abs().max().item())
+    ep.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_rank_expert_parallel_moe():
+    import os
+
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29631", str(ROOT / "tests/dist_worker.py"),
+                        "ep_moe"], capture_output=True, text=True, timeout=600,
+                       env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
+    assert r.returncode == 0 and "OK ep_moe" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
