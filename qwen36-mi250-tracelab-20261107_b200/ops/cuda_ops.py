@@ -62,6 +62,8 @@ class _Sig:
     b200_gdn_decode = [P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P]
     b200_attn_prep = [P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P, P]
     b200_paged_attn = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
+    b200_gdn_prefill = [P, I, P, P, P, P, P, P, P, P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, F, P]
+    b200_gdn_prefill_work_stride = [I]
     b200_flash_prefill = [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, P, P, P]
     b200_attn_combine = [P, P, P, P, I, I, I, I, P]
 
@@ -255,10 +257,43 @@ def gdn_decode(mixed, slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnor
 
 def gdn_prefill(mixed, seg_starts, seg_slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnorm_w, n_k, n_v, dk,
                 dv, eps) -> torch.Tensor:
-    """Chunked prefill of the delta rule. Batched PyTorch over equal-length groups for now."""
-    return torch_ops.gdn_prefill_batched(
-        mixed, seg_starts, seg_slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnorm_w, n_k, n_v, dk, dv, eps
+    """Chunked prefill of the gated delta rule over packed spans (conv, WY transform, state scan, gated norm)."""
+    if dk != dv or dk not in (32, 64, 128) or conv_w.shape[1] != 4:
+        return torch_ops.gdn_prefill_batched(
+            mixed, seg_starts, seg_slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnorm_w, n_k, n_v, dk, dv, eps
+        )
+    T = mixed.shape[0]
+    dev = mixed.device
+    nseg = len(seg_slots)
+    chunks, seg_chunks, seq_of_row = [], [], []
+    for i in range(nseg):
+        a, b = seg_starts[i], seg_starts[i + 1]
+        first = len(chunks)
+        for r0 in range(a, b, 64):
+            chunks.append((i, r0, min(64, b - r0), int(r0 == a)))
+        seg_chunks.append((first, len(chunks) - first))
+        seq_of_row.extend([i] * (b - a))
+    meta = torch.tensor([c for ch in chunks for c in ch] + [c for sc in seg_chunks for c in sc] + seq_of_row
+                        + list(seg_starts) + list(seg_slots), dtype=torch.int32).to(dev, non_blocking=True)
+    o = 0
+    chunks_t = meta[o : o + 4 * len(chunks)]; o += 4 * len(chunks)
+    segc_t = meta[o : o + 2 * nseg]; o += 2 * nseg
+    sor_t = meta[o : o + T]; o += T
+    start_t = meta[o : o + nseg + 1]; o += nseg + 1
+    slots_t = meta[o : o + nseg]
+    C = 2 * n_k * dk + n_v * dv
+    stride = lib().b200_gdn_prefill_work_stride(dk)
+    work = torch.empty(len(chunks) * n_v * stride, dtype=torch.float32, device=dev)
+    conv_out = torch.empty(T, C, dtype=mixed.dtype, device=dev)
+    o_tmp = torch.empty(T, n_v * dv, dtype=mixed.dtype, device=dev)
+    out = torch.empty(T, n_v * dv, dtype=mixed.dtype, device=dev)
+    rc = lib().b200_gdn_prefill(
+        _ptr(mixed), mixed.stride(0), _ptr(sor_t), _ptr(start_t), _ptr(slots_t), _ptr(conv_state), _ptr(rec_state),
+        _ptr(conv_w), _ptr(A_log), _ptr(dt_bias), _ptr(gnorm_w), _ptr(conv_out), _ptr(chunks_t), len(chunks),
+        _ptr(segc_t), nseg, _ptr(work), _ptr(o_tmp), _ptr(out), T, n_k, n_v, dk, dv, eps, _stream(),
     )
+    _check(rc, "gdn_prefill")
+    return out
 
 
 # --------------------------------------------------------------------------- attention

@@ -274,3 +274,32 @@ def test_flash_decode_split_context(C, O, n_q, n_kv, D, B, G, lens):
     one = C.attention(qkv[:G].contiguous(), positions[:G].contiguous(), seq[:G].contiguous(), tables[:1].contiguous(), kv,
                       qn, kn, n_q, n_kv, D, D // 4, 1e7, 1e-6, G)
     assert torch.equal(one, got[:G])
+
+
+@pytest.mark.parametrize("dims,lens", [((2, 4, 32, 32), [5, 130, 64]), ((16, 32, 128, 128), [200, 1, 63, 65]),
+                                       ((4, 8, 128, 128), [700])])
+def test_gdn_prefill_kernels_match_reference(C, O, dims, lens):
+    n_k, n_v, dk, dv = dims
+    nseg = len(lens)
+    starts = [0]
+    for n in lens:
+        starts.append(starts[-1] + n)
+    T = starts[-1]
+    mixed, _, conv, rec, args = _gdn_setup(dims, nseg, 1, seed=70)
+    mixed = _bf(T, mixed.shape[1], seed=71)
+    slots = list(range(1, nseg + 1))
+    conv_r, rec_r = conv.float().clone(), rec.clone()
+    a = list(args)
+    ref_args = (a[0].float(), a[1], a[2], a[3].float(), *a[4:])
+    ref = O.gdn_prefill(mixed.float(), starts, slots, conv_r, rec_r, *ref_args)
+    got = C.gdn_prefill(mixed, starts, slots, conv, rec, *args)
+    C.check_errors(mixed.device)
+    _close(conv, conv_r, 1e-6, 0, "conv state")
+    _close(got, ref, 1e-2 * max(1.0, ref.abs().max().item()), 4e-2, "prefill out")  # conv output and o pass through bf16
+    _close(rec, rec_r, 1e-2, 3e-2, "final state")
+    # decode continues from the prefill state
+    more = _bf(nseg, mixed.shape[1], seed=72)
+    st = torch.tensor(slots, dtype=torch.int32, device="cuda")
+    d_ref = O.gdn_decode(more.float(), st, conv_r, rec_r, *ref_args)
+    d_got = C.gdn_decode(more, st, conv, rec, *args)
+    _close(d_got, d_ref, 1e-2 * max(1.0, d_ref.abs().max().item()), 4e-2, "decode after prefill")
