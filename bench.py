@@ -138,19 +138,31 @@ def main() -> None:
     B, P, K, W = args.batch, args.prompt_len, args.steps, args.warmup
 
     mcfg = ModelConfig.qwen36_35b_a3b() if not args.layers else ModelConfig(num_hidden_layers=args.layers)
-    weights = random_weights(mcfg, seed=1234 + rank, device=dev, dtype=torch.bfloat16)
+    tp_mode = args.parallelism == "tp_ep" and world > 1
+    tp_ctx = None
+    if tp_mode:  # one replica over all ranks: same weights and the same requests everywhere, sharded TP + EP
+        from b200serve.parallel.tp import FusedComm, TPContext, shard_weights
+
+        full = random_weights(mcfg, seed=1234, device=dev, dtype=torch.bfloat16)
+        weights = shard_weights(full, rank, world)
+        del full
+        torch.cuda.empty_cache()
+        tp_ctx = TPContext(rank, world, FusedComm(dev, dist.group.WORLD, slot_elems=1 << 21, max_blocks=4096))
+    else:
+        weights = random_weights(mcfg, seed=1234 + rank, device=dev, dtype=torch.bfloat16)
     total_out = K + max(W, 3) + 64 + (B * P) // 4096  # room for the tokens decoded while later prompts prefill
     ecfg = EngineConfig(
         max_model_len=P + 2 * total_out + 64, max_seqs=B, state_slots=B + 2, prefill_chunk_tokens=2048,
         prefill_pack_tokens=8192, kv_pages=B * ((P + 2 * total_out) // 64 + 2) + 2, mtp=bool(args.mtp),
         spec_k=args.mtp, decode_buckets=(B,),
     )
-    engine = Engine(weights, ecfg)
+    engine = Engine(weights, ecfg, tp=tp_ctx)
+    replicas = 1 if tp_mode else world  # independent request streams in the job
 
     def run_phase(timed_steps: int, warm: int, e2e: bool):
         """Prefill B fresh requests, run `warm` untimed decode steps, then time `timed_steps` steps."""
         engine.cache.clear()
-        g = torch.Generator().manual_seed(99 + rank + (1000 if e2e else 0))
+        g = torch.Generator().manual_seed(99 + (0 if tp_mode else rank) + (1000 if e2e else 0))
         gens = [
             engine.submit(Generation(torch.randint(0, mcfg.vocab_size, (P,), generator=g).tolist(),
                                      Sampling(max_tokens=total_out, ignore_eos=True)))
@@ -211,8 +223,8 @@ def main() -> None:
 
     ms = reduce_max(ms)
     e2e_s = reduce_max(max(e2e_wall, e2e_ms / 1e3))
-    value = world * tokens / (ms / 1e3)
-    e2e_value = world * e2e_tokens / e2e_s
+    value = replicas * tokens / (ms / 1e3)
+    e2e_value = replicas * e2e_tokens / e2e_s
     bucket = next(b for b in engine._graphs.buckets.values() if b.size == B)
     h2d = (bucket.h_tokens.numel() * 8 + bucket.h_positions.numel() * 8 + bucket.h_slots.numel() * 4
            + bucket.h_tables.numel() * 4)
@@ -225,12 +237,12 @@ def main() -> None:
         line = {
             "metric": "output tok/s (whole box, max over ranks), decode", "value": round(value, 1), "unit": "tok/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None if BASELINE_TOK_S is None else value / BASELINE_TOK_S,
+            "scaling": "strong" if tp_mode else "weak", "vs_baseline": None if BASELINE_TOK_S is None else value / BASELINE_TOK_S,
             "dtype": "bf16", "data": "synthetic (uniform-random prompt tokens, random-init weights)",
             "impl": "ours",
             "config": {
                 "model": "Qwen3.6-35B-A3B" + (f"[{args.layers} layers: INVALID]" if args.layers else ""),
-                "global_batch": B * world, "seq_len": P, "parallelism": f"{args.parallelism}{world}",
+                "global_batch": B * replicas, "seq_len": P, "parallelism": f"{args.parallelism}{world}",
                 "batch_per_gpu": B, "l2": "working set per step (weights + KV + GDN state) far exceeds the 126 MB L2",
                 "mtp_depth": args.mtp,
             },
