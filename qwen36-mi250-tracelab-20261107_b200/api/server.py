@@ -362,11 +362,26 @@ def load_service(args: argparse.Namespace) -> Service:
                        str(args.prefix_cache_gib), "--max-seqs", str(args.max_seqs)]
         engine, followers = replica.leader_engine(args.model, tp, use_cuda, cfg, passthrough)
         device = engine.device
+    elif args.model.startswith("random:"):
+        # benchmark mode: random-init weights of a named architecture created on the device, no checkpoint on disk
+        import tempfile
+
+        from ..config import ModelConfig
+        from ..models.checkpoint import random_weights
+        from ..models.tiny import build_tokenizer
+
+        device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
+        dtype = torch.bfloat16 if use_cuda else torch.float32
+        mcfg = ModelConfig.tiny() if args.model == "random:tiny" else ModelConfig.qwen36_35b_a3b()
+        engine = Engine(random_weights(mcfg, seed=0, device=device, dtype=dtype), cfg)
+        tok_dir = tempfile.mkdtemp(prefix="b200serve-tok-")
+        build_tokenizer(512).save_pretrained(tok_dir)
+        args.model_dir_for_tokenizer = tok_dir
     else:
         device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
         dtype = torch.bfloat16 if use_cuda else torch.float32
         engine = Engine(load_checkpoint(args.model, device=device, dtype=dtype), cfg)
-    codec = TextCodec(args.model)
+    codec = TextCodec(getattr(args, "model_dir_for_tokenizer", args.model))
     name = args.served_model_name or args.model
     print(f"engine: loaded {args.model} on {device} tp={tp} ({engine.model.w.nbytes() / 1e9:.2f} GB per rank) in "
           f"{time.time() - t0:.1f} s; kv_pages={engine.pages.num_pages} slots={engine.slots.num_slots} "
