@@ -381,6 +381,8 @@ def load_service(args: argparse.Namespace) -> Service:
         device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
         dtype = torch.bfloat16 if use_cuda else torch.float32
         engine = Engine(load_checkpoint(args.model, device=device, dtype=dtype), cfg)
+    if tp == 1 and os.environ.get("ENGINE_WARMUP", "1") == "1":
+        engine.warmup()
     codec = TextCodec(getattr(args, "model_dir_for_tokenizer", args.model))
     name = args.served_model_name or args.model
     print(f"engine: loaded {args.model} on {device} tp={tp} ({engine.model.w.nbytes() / 1e9:.2f} GB per rank) in "

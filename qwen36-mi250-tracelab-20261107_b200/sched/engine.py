@@ -439,6 +439,22 @@ class Engine:
         did = self._decode_step() or did
         return did
 
+    def warmup(self) -> None:
+        """Run one short request and capture every decode graph before serving, so that no request pays for
+        first-use work (the reference warms its kernels and captures its graphs before ``/health`` answers,
+        ``engine/generator.py:706-728``). Counters and caches are reset afterwards."""
+        n = min(self.chunk + 8, self.max_model_len - 8)
+        g = self.generate([[1 + (i % 7) for i in range(n)]], Sampling(max_tokens=3, ignore_eos=True))[0]
+        assert g.done
+        if self._graphs is not None:
+            self._graphs.warm()
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+        self.cache.clear()
+        for k in self.stats:
+            self.stats[k] = 0
+        self.cache.stats = type(self.cache.stats)()
+
     def health(self) -> dict:
         out = dict(self.stats)
         cs = self.cache.stats
