@@ -103,11 +103,11 @@ def case_gemm_grouped(small):
 
     def up():
         L.b200_gemm_grouped(xs.data_ptr(), wgu.data_ptr(), act.data_ptr(), n_pairs, E + 1, I, 2 * I, H, I, 2, I, bt,
-                            tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), st)
+                            tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), 1, st)
 
     def down():
         L.b200_gemm_grouped(act.data_ptr(), wd.data_ptr(), out.data_ptr(), n_pairs, E + 1, H, H, I, H, 0, 0, bt,
-                            tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), st)
+                            tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), 1, st)
 
     report("grouped_gate_up_silu", timed(up), wgu.numel() * 2, 2 * n_pairs * 2 * I * H, experts=E)
     report("grouped_down", timed(down), wd.numel() * 2, 2 * n_pairs * I * H, experts=E)

@@ -184,6 +184,7 @@ class Model:
     def forward(self, batch: PackedBatch, ring=None) -> torch.Tensor:
         """Run the layer stack; returns the final-normed hidden state of every row ``[T, H]``."""
         cfg, ops = self.cfg, self.ops
+        ops.DECODE_MODE = batch.G > 0  # decode / verify passes may split K across clusters; prefill never does
         x = ops.embed(batch.tokens, self.w.embed)
         res = None
         for i, lw in enumerate(self.w.layers):

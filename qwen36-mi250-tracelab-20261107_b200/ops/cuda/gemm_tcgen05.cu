@@ -43,6 +43,7 @@ struct GemmParams {
   int* err;          // error word (0 = ok)
   const bf16* residual; // EPI_ALLREDUCE: optional [T, ldo] added after the cross-rank sum
   CommCtx comm;      // EPI_ALLREDUCE: the rank group's symmetric buffers
+  int splits;        // split-K: CTAs of one cluster share an output tile, each taking 1/splits of the k-blocks
   const int2* meta;  // EPI_SCATTER: (source rank, pair slot) of every sorted row
   bf16* pair_out[MAX_RANKS];  // EPI_SCATTER: every rank's pair-output buffer [pairs, ldo] as mapped here
 };
@@ -64,7 +65,7 @@ struct Cfg {
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-template <int BT, int EPI, bool GROUPED>
+template <int BT, int EPI, bool GROUPED, bool SPLIT = false>
 __global__ void __launch_bounds__(192, Cfg<BT, EPI>::CTAS_PER_SM)
 gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmParams p) {
   using C = Cfg<BT, EPI>;
@@ -90,7 +91,12 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   } else {
     nrows = min(BT, p.T - row0);
   }
-  const int num_k = (p.K + BK - 1) / BK;
+  const int num_k_all = (p.K + BK - 1) / BK;
+  // split-K: the cluster's CTAs (blockIdx.z = rank in the cluster) take consecutive runs of k-blocks; their fp32
+  // partial tiles meet in the leader through distributed shared memory, added in rank order
+  const int k_per = SPLIT ? (num_k_all + p.splits - 1) / p.splits : num_k_all;
+  const int kb0 = SPLIT ? static_cast<int>(blockIdx.z) * k_per : 0;
+  const int num_k = SPLIT ? max(0, min(num_k_all, kb0 + k_per) - kb0) : num_k_all;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -115,15 +121,16 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         uint8_t* st = smem + s * C::STAGE_BYTES;
         mbar_expect_tx(&full[s], C::STAGE_BYTES);
         if (GROUPED) {
-          tma_load_3d(st, &tmW, &full[s], kb * BK, n0, expert);
-          if (EPI == EPI_SILU_MUL) tma_load_3d(st + C::A_BYTES, &tmW, &full[s], kb * BK, p.up_offset + n0, expert);
+          tma_load_3d(st, &tmW, &full[s], (kb0 + kb) * BK, n0, expert);
+          if (EPI == EPI_SILU_MUL) tma_load_3d(st + C::A_BYTES, &tmW, &full[s], (kb0 + kb) * BK, p.up_offset + n0, expert);
         } else {
-          tma_load_2d(st, &tmW, &full[s], kb * BK, n0);
-          if (EPI == EPI_SILU_MUL) tma_load_2d(st + C::A_BYTES, &tmW, &full[s], kb * BK, p.up_offset + n0);
+          tma_load_2d(st, &tmW, &full[s], (kb0 + kb) * BK, n0);
+          if (EPI == EPI_SILU_MUL) tma_load_2d(st + C::A_BYTES, &tmW, &full[s], (kb0 + kb) * BK, p.up_offset + n0);
         }
-        tma_load_2d(st + C::A_TILES * C::A_BYTES, &tmX, &full[s], kb * BK, row0);
+        tma_load_2d(st + C::A_TILES * C::A_BYTES, &tmX, &full[s], (kb0 + kb) * BK, row0);
       }
     }
+    if (SPLIT) { __syncwarp(); cluster_sync(); }
   } else if (warp == 1) {
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BT);
@@ -148,6 +155,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
       umma_commit(acc_full);     // always arrive so that the epilogue is released
     }
+    if (SPLIT) { __syncwarp(); cluster_sync(); }
   } else {
     // ---------------- epilogue: warp q owns TMEM lanes [32q, 32q+32)
     const int q = warp & 3;
@@ -199,15 +207,50 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
       }
     } else
+    if (SPLIT && blockIdx.z != 0) {
+      // split-K follower: park the partial tile in shared memory (the pipeline stages are idle now) as
+      // red[column][weight row]; a CTA without k-blocks contributes zeros
+      float* red = reinterpret_cast<float*>(smem);
+#pragma unroll 1
+      for (int c = 0; c < nrows; c += 16) {
+        float v[16];
+        if (num_k > 0 && ok) tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + c, v);
+        else { for (int j = 0; j < 16; ++j) v[j] = 0.f; }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) red[(c + j) * BM + q * 32 + lane] = v[j];
+        if (EPI == EPI_SILU_MUL) {
+          if (num_k > 0 && ok) tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + BT + c, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) red[(BT + c + j) * BM + q * 32 + lane] = v[j];
+        }
+      }
+      cluster_sync();  // first cluster barrier (every thread of the cluster takes part exactly once)
+    } else {
+    if (SPLIT) cluster_sync();  // first cluster barrier: the followers' partial tiles are in place
     if (ok) {
+      const uint32_t red_local = smem_u32(smem);
 #pragma unroll 1
       for (int c = 0; c < BT; c += 16) {
         if (c >= nrows && EPI != EPI_ARGMAX) break;  // warp-uniform
         float v[16];
         tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + c, v);
+        if (SPLIT) {
+          for (int r = 1; r < p.splits; ++r) {
+            const uint32_t remote = dsmem_addr(red_local, r);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] += ld_dsmem_f32(remote + ((c + j) * BM + q * 32 + lane) * 4);
+          }
+        }
         if (EPI == EPI_SILU_MUL) {
           float u[16];
           tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + BT + c, u);
+          if (SPLIT) {
+            for (int r = 1; r < p.splits; ++r) {
+              const uint32_t remote = dsmem_addr(red_local, r);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) u[j] += ld_dsmem_f32(remote + ((BT + c + j) * BM + q * 32 + lane) * 4);
+            }
+          }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             // round gate and up to bf16 first, as the unfused sequence of ops does
@@ -253,6 +296,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
       }
     }
+    }
     if (EPI == EPI_ARGMAX) {
       asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
       const int t = (warp - 2) * 32 + lane;
@@ -270,6 +314,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     }
   }
+  if (SPLIT) cluster_sync();  // second cluster barrier: the leader has read every partial tile
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, C::TMEM_COLS); }
@@ -332,9 +377,36 @@ static int make_map(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, 
 }
 
 template <int BT, int EPI, bool GROUPED>
+static int launch_split(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int grid_y, cudaStream_t st) {
+  using C = Cfg<BT, EPI>;
+  auto kern = gemm_swapab_kernel<BT, EPI, GROUPED, true>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess) return -3;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((p.N + BM - 1) / BM, grid_y, p.splits);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = C::SMEM;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = p.splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tw, tx, p) == cudaSuccess ? 0 : -4;
+}
+
+template <int BT, int EPI, bool GROUPED>
 static int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int grid_y, cudaStream_t st) {
   using C = Cfg<BT, EPI>;
-  auto kern = gemm_swapab_kernel<BT, EPI, GROUPED>;
+  if constexpr (EPI == EPI_BF16 || EPI == EPI_F32 || EPI == EPI_SILU_MUL) {
+    if (p.splits > 1) return launch_split<BT, EPI, GROUPED>(tw, tx, p, grid_y, st);
+  }
+  auto kern = gemm_swapab_kernel<BT, EPI, GROUPED, false>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess) return -3;
@@ -375,15 +447,16 @@ extern "C" int b200_pick_bt(int T) {
 // with the up half at row `up_offset`), 3 argmax partials (part_max/part_idx sized [ceil(N/128), T]).
 extern "C" int b200_gemm_dense(const void* X, const void* W, void* out, int T, int N, int K, int ldx, int ldw, int ldo,
                                int epi, int up_offset, int bt, float* part_max, int* part_idx, int* err,
-                               cudaStream_t st) {
+                               int splits, cudaStream_t st) {
   if (T <= 0) return 0;
+  if (splits < 1 || splits > 8 || splits > (K + BK - 1) / BK) splits = 1;
   if (bt <= 0) bt = b200_pick_bt(T);
   if (epi == EPI_SILU_MUL && bt > 128) bt = 128;
   CUtensorMap tw, tx;
   const int w_rows = (epi == EPI_SILU_MUL) ? up_offset + N : N;
   if (make_map(&tw, W, K, w_rows, 0, ldw, 0, BM)) return -1;
   if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
-  GemmParams p{N, K, T, ldo, out, nullptr, nullptr, up_offset, part_max, part_idx, err, nullptr, CommCtx{}, nullptr, {}};
+  GemmParams p{N, K, T, ldo, out, nullptr, nullptr, up_offset, part_max, part_idx, err, nullptr, CommCtx{}, splits, nullptr, {}};
   const int gy = (T + bt - 1) / bt;
   switch (epi) {
     case EPI_BF16: return dispatch_bt<EPI_BF16, false>(bt, tw, tx, p, gy, st);
@@ -398,12 +471,13 @@ extern "C" int b200_gemm_dense(const void* X, const void* W, void* out, int T, i
 // [tiles[i].y, +tiles[i].z) of expert tiles[i].x; W is [E, rows, K]. `max_tiles` bounds the grid.
 extern "C" int b200_gemm_grouped(const void* X, const void* W, void* out, int cap, int E, int N, int w_rows, int K,
                                  int ldo, int epi, int up_offset, int bt, const void* tiles, const int* n_tiles,
-                                 int max_tiles, int* err, cudaStream_t st) {
+                                 int max_tiles, int* err, int splits, cudaStream_t st) {
   if (max_tiles <= 0) return 0;
+  if (splits < 1 || splits > 8 || splits > (K + BK - 1) / BK) splits = 1;
   CUtensorMap tw, tx;
   if (make_map(&tw, W, K, w_rows, E, K, static_cast<uint64_t>(w_rows) * K, BM)) return -1;
   if (make_map(&tx, X, K, cap, 0, K, 0, bt)) return -1;
-  GemmParams p{N, K, cap, ldo, out, reinterpret_cast<const int4*>(tiles), n_tiles, up_offset, nullptr, nullptr, err, nullptr, CommCtx{}, nullptr, {}};
+  GemmParams p{N, K, cap, ldo, out, reinterpret_cast<const int4*>(tiles), n_tiles, up_offset, nullptr, nullptr, err, nullptr, CommCtx{}, splits, nullptr, {}};
   switch (epi) {
     case EPI_BF16: return dispatch_bt<EPI_BF16, true>(bt, tw, tx, p, max_tiles, st);
     case EPI_SILU_MUL: return dispatch_bt<EPI_SILU_MUL, true>(bt, tw, tx, p, max_tiles, st);
@@ -423,7 +497,7 @@ extern "C" int b200_gemm_allreduce(const CommCtx* ctx, const void* X, const void
   CUtensorMap tw, tx;
   if (make_map(&tw, W, K, N, 0, ldw, 0, BM)) return -1;
   if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
-  GemmParams p{N, K, T, N, out, nullptr, nullptr, 0, nullptr, nullptr, ctx->err, static_cast<const bf16*>(residual), *ctx, nullptr, {}};
+  GemmParams p{N, K, T, N, out, nullptr, nullptr, 0, nullptr, nullptr, ctx->err, static_cast<const bf16*>(residual), *ctx, 1, nullptr, {}};
   return dispatch_bt<EPI_ALLREDUCE, false>(bt, tw, tx, p, gy, st);
 }
 
@@ -437,7 +511,7 @@ extern "C" int b200_gemm_grouped_scatter(const void* X, const void* W, int cap, 
   if (make_map(&tw, W, K, N, E, K, static_cast<uint64_t>(N) * K, BM)) return -1;
   if (make_map(&tx, X, K, cap, 0, K, 0, bt)) return -1;
   GemmParams p{N, K, cap, N, nullptr, reinterpret_cast<const int4*>(tiles), n_tiles, 0, nullptr, nullptr, err, nullptr,
-               CommCtx{}, static_cast<const int2*>(meta), {}};
+               CommCtx{}, 1, static_cast<const int2*>(meta), {}};
   for (int r = 0; r < world && r < MAX_RANKS; ++r) p.pair_out[r] = static_cast<bf16*>(pair_out[r]);
   return dispatch_bt<EPI_SCATTER, true>(bt, tw, tx, p, max_tiles, st);
 }
@@ -489,7 +563,7 @@ extern "C" int b200_lm_head_argmax_noalloc(const void* X, const void* W, int64_t
   CUtensorMap tw, tx;
   if (make_map(&tw, W, K, V, 0, ldw, 0, BM)) return -1;
   if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
-  GemmParams p{V, K, T, 0, nullptr, nullptr, nullptr, 0, part_max, part_idx, err, nullptr, CommCtx{}, nullptr, {}};
+  GemmParams p{V, K, T, 0, nullptr, nullptr, nullptr, 0, part_max, part_idx, err, nullptr, CommCtx{}, 1, nullptr, {}};
   const int rc = dispatch_bt<EPI_ARGMAX, false>(bt, tw, tx, p, (T + bt - 1) / bt, st);
   if (rc) return rc;
   argmax_finish_kernel<<<T, 256, 0, st>>>(part_max, part_idx, n_tiles, T, out_idx, out_val);

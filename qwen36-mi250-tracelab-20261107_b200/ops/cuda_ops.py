@@ -50,8 +50,8 @@ P, I, F = c_void_p, c_int, c_float
 
 class _Sig:
     b200_pick_bt = [I]
-    b200_gemm_dense = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, P, P]
-    b200_gemm_grouped = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, I, P, P]
+    b200_gemm_dense = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, P, I, P]
+    b200_gemm_grouped = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, I, P, I, P]
     b200_argmax_finish = [P, P, I, I, P, P, P]
     b200_embed = [P, P, P, I, I, I, P]
     b200_add_rmsnorm = [P, P, P, P, P, I, I, F, I, P]
@@ -103,6 +103,23 @@ def check_errors(device: torch.device) -> None:
 
 
 # --------------------------------------------------------------------------- GEMM family
+DECODE_MODE = False  # set by Model.forward: decode / verify passes split K across a thread-block cluster
+
+
+def split_k(N: int, K: int, grouped: bool = False) -> int:
+    """CTAs per cluster that share one output tile along K. A function of the weight shape and of the kind
+    of pass only (never of the number of rows), so a row's bits do not depend on its batch."""
+    if not DECODE_MODE:
+        return 1
+    nk = K // 64
+    if grouped:
+        return 4 if nk >= 32 else 1
+    tiles, s = (N + 127) // 128, 1
+    while s < 8 and tiles * s * 2 <= 160 and nk // (s * 2) >= 4:
+        s *= 2
+    return s
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None, bt: int = 0) -> torch.Tensor:
     """``x [T, K] @ w[N, K].T`` on tcgen05; bf16 in, bf16 (default) or fp32 out."""
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
@@ -115,7 +132,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     assert x.stride(1) == 1 and w.stride(1) == 1 and K % 8 == 0
     rc = lib().b200_gemm_dense(
         _ptr(x), _ptr(w), _ptr(out), T, N, K, x.stride(0), w.stride(0), N, EPI_F32 if f32 else EPI_BF16, 0, bt,
-        None, None, _ptr(err_word(x.device)), _stream(),
+        None, None, _ptr(err_word(x.device)), split_k(N, K), _stream(),
     )
     _check(rc, "gemm_dense")
     return out
@@ -128,7 +145,7 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     out = torch.empty(T, inter, dtype=torch.bfloat16, device=x.device)
     rc = lib().b200_gemm_dense(
         _ptr(x), _ptr(w_gate_up), _ptr(out), T, inter, K, x.stride(0), w_gate_up.stride(0), inter, EPI_SILU_MUL,
-        inter, 0, None, None, _ptr(err_word(x.device)), _stream(),
+        inter, 0, None, None, _ptr(err_word(x.device)), split_k(inter, K), _stream(),
     )
     _check(rc, "gemm_dense(silu_mul)")
     return out
@@ -145,7 +162,7 @@ def lm_head_argmax(x: torch.Tensor, w: torch.Tensor, return_value: bool = False)
     val = torch.empty(T, dtype=torch.float32, device=x.device) if return_value else None
     rc = lib().b200_gemm_dense(
         _ptr(x), _ptr(w), None, T, V, K, x.stride(0), w.stride(0), 0, EPI_ARGMAX, 0, 0, _ptr(pmax), _ptr(pidx),
-        _ptr(err_word(x.device)), _stream(),
+        _ptr(err_word(x.device)), 1, _stream(),
     )
     _check(rc, "gemm_dense(argmax)")
     _check(lib().b200_argmax_finish(_ptr(pmax), _ptr(pidx), n_tiles, T, _ptr(out), _ptr(val), _stream()), "argmax_finish")
@@ -224,11 +241,13 @@ def moe_block(x: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_
     _check(L.b200_moe_gather(_ptr(x), _ptr(perm), _ptr(offsets[Et:]), n_pairs, T, Pn, H, _ptr(xs), st), "moe_gather")
     act = torch.empty(n_pairs, inter, dtype=x.dtype, device=dev)
     _check(L.b200_gemm_grouped(_ptr(xs), _ptr(w_gate_up), _ptr(act), n_pairs, Et, inter, 2 * inter, H, inter,
-                               EPI_SILU_MUL, inter, bt, _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err), st),
+                               EPI_SILU_MUL, inter, bt, _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err),
+                               split_k(inter, H, grouped=True), st),
            "gemm_grouped(gate_up)")
     pair_out = torch.empty(n_pairs, H, dtype=x.dtype, device=dev)
     _check(L.b200_gemm_grouped(_ptr(act), _ptr(w_down), _ptr(pair_out), n_pairs, Et, H, H, inter, H, EPI_BF16, 0, bt,
-                               _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err), st), "gemm_grouped(down)")
+                               _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err), split_k(H, inter, grouped=True), st),
+           "gemm_grouped(down)")
     out = torch.empty(T, H, dtype=torch.float32 if partial_f32 else x.dtype, device=dev)
     _check(L.b200_moe_combine(_ptr(pair_out), _ptr(wts), _ptr(inv), T, Pn, H, None if partial_f32 else _ptr(out),
                               _ptr(out) if partial_f32 else None, st), "moe_combine")

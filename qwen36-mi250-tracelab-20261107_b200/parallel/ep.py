@@ -157,7 +157,7 @@ class EpMoE:
         err = cuda_ops.err_word(dev)
         rc |= K.b200_gemm_grouped(self._own["xs"], w_gate_up_local.data_ptr(), act.data_ptr(), self.cap_rows,
                                   self.per + 1, inter, 2 * inter, H, inter, cuda_ops.EPI_SILU_MUL, inter, bt,
-                                  tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), st)
+                                  tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), 1, st)
         rc |= L.b200_gemm_grouped_scatter(act.data_ptr(), w_down_local.data_ptr(), self.cap_rows, self.per + 1, H,
                                           inter, bt, tiles.data_ptr(), n_tiles.data_ptr(), max_tiles,
                                           self._own["meta"], self._pair_out_ptrs, self.world, err.data_ptr(), st)

@@ -303,3 +303,36 @@ def test_gdn_prefill_kernels_match_reference(C, O, dims, lens):
     d_ref = O.gdn_decode(more.float(), st, conv_r, rec_r, *ref_args)
     d_got = C.gdn_decode(more, st, conv, rec, *args)
     _close(d_got, d_ref, 1e-2 * max(1.0, d_ref.abs().max().item()), 4e-2, "decode after prefill")
+
+
+def test_split_k_cluster_gemm(C, O):
+    """Decode-mode GEMMs split K over a thread-block cluster and add the partial tiles through distributed
+    shared memory in rank order: correct, and still independent of the number of rows."""
+    C.DECODE_MODE = True
+    try:
+        for T, N, K in ((1, 2048, 4096), (5, 257, 2048), (128, 2048, 4096), (40, 9216, 2048), (300, 2048, 4096)):
+            assert C.split_k(N, K) > 1
+            x, w = _bf(T, K, seed=80), _bf(N, K, scale=0.05, seed=81)
+            ref = x.float() @ w.float().t()
+            _close(C.linear(x, w), ref, 3e-2, 1e-2, f"bf16 {T}x{N}x{K}")
+            _close(C.linear(x, w, out_dtype=torch.float32), ref, 2e-3, 1e-3, f"fp32 {T}x{N}x{K}")
+        x, w = _bf(256, 4096, seed=82), _bf(2048, 4096, scale=0.05, seed=83)
+        full = C.linear(x, w, out_dtype=torch.float32)
+        for rows in (1, 7, 16, 100):
+            assert torch.equal(C.linear(x[:rows].contiguous(), w, out_dtype=torch.float32), full[:rows]), rows
+        # fused SiLU-mul over both accumulators, dense and grouped (the MoE block)
+        x, w = _bf(9, 2048, seed=84), _bf(1024, 2048, scale=0.05, seed=85)
+        _close(C.linear_silu_mul(x, w), O.linear_silu_mul(x.float(), w.float()), 2e-2, 2e-2, "silu split")
+        E, H, I, k = 32, 2048, 512, 4
+        xx, router = _bf(6, H, seed=86), _bf(E + 1, H, scale=0.3, seed=87)
+        wgu, wd = _bf(E + 1, 2 * I, H, scale=0.05, seed=88), _bf(E + 1, H, I, scale=0.05, seed=89)
+        got = C.moe_block(xx, router, wgu, wd, E, k, True)
+        logits = C.linear(xx, router, out_dtype=torch.float32)
+        wts, idx = O.router_topk(logits[:, :E], k)
+        wts = torch.cat([wts, torch.sigmoid(logits[:, E:E + 1])], 1).to(torch.bfloat16)
+        idx = torch.cat([idx, torch.full_like(idx[:, :1], E)], 1)
+        ref = O.moe_experts(xx.float(), wts.float(), idx, wgu.float(), wd.float())
+        _close(got, ref, 3e-2 * ref.abs().max().item(), 3e-2, "moe split")
+        C.check_errors(x.device)
+    finally:
+        C.DECODE_MODE = False
