@@ -103,17 +103,21 @@ def check_errors(device: torch.device) -> None:
 
 
 # --------------------------------------------------------------------------- GEMM family
-DECODE_MODE = False  # set by Model.forward: decode / verify passes split K across a thread-block cluster
+DECODE_MODE = False  # set by Model.forward: True for decode / verify passes
+# Split-K over thread-block clusters for decode passes. Measured on B200 (batch 1: 4.34 -> 3.94 ms per step;
+# batch 128: 18.1 -> 19.3 ms, the leader CTA's DSMEM reads of seven partial tiles cost more than the extra
+# CTAs save), so it is off unless ENGINE_SPLIT_K=1; the split factor must not depend on the batch size.
+SPLIT_K_ENABLED = __import__("os").environ.get("ENGINE_SPLIT_K", "0") == "1"
 
 
 def split_k(N: int, K: int, grouped: bool = False) -> int:
     """CTAs per cluster that share one output tile along K. A function of the weight shape and of the kind
     of pass only (never of the number of rows), so a row's bits do not depend on its batch."""
-    if not DECODE_MODE:
+    if not (DECODE_MODE and SPLIT_K_ENABLED):
         return 1
     nk = K // 64
-    if grouped:
-        return 4 if nk >= 32 else 1
+    if grouped:  # expert tiles already give hundreds of CTAs at batch sizes where the MoE dominates the step
+        return 2 if nk >= 32 else 1
     tiles, s = (N + 127) // 128, 1
     while s < 8 and tiles * s * 2 <= 160 and nk // (s * 2) >= 4:
         s *= 2

@@ -308,7 +308,7 @@ def test_gdn_prefill_kernels_match_reference(C, O, dims, lens):
 def test_split_k_cluster_gemm(C, O):
     """Decode-mode GEMMs split K over a thread-block cluster and add the partial tiles through distributed
     shared memory in rank order: correct, and still independent of the number of rows."""
-    C.DECODE_MODE = True
+    C.DECODE_MODE = C.SPLIT_K_ENABLED = True
     try:
         for T, N, K in ((1, 2048, 4096), (5, 257, 2048), (128, 2048, 4096), (40, 9216, 2048), (300, 2048, 4096)):
             assert C.split_k(N, K) > 1
@@ -335,4 +335,4 @@ def test_split_k_cluster_gemm(C, O):
         _close(got, ref, 3e-2 * ref.abs().max().item(), 3e-2, "moe split")
         C.check_errors(x.device)
     finally:
-        C.DECODE_MODE = False
+        C.DECODE_MODE = C.SPLIT_K_ENABLED = False
