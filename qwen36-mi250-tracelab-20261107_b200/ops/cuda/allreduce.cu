@@ -102,6 +102,80 @@ extern "C" int b200_allreduce_push(const CommCtx* ctx, const void* in, int in_is
 }
 
 // ------------------------------------------------------------------ symmetric memory (CUDA IPC)
+// ------------------------------------------------------------------ RMSNorm + all-gather push
+// Sequence-parallel half of a tensor-parallel layer: after a GEMM -> reduce-scatter each rank owns `rows` token
+// rows of the residual stream. This kernel normalises the rank's rows and stores every normalised row straight
+// into the full activation buffer of EVERY rank (peer stores over NVLink; `xfull[r]` is rank r's [R * rows, H]
+// buffer), so the all-gather needs no separate pass. The last CTA to finish publishes the arrival epoch of this
+// rank's shard on every rank; the consuming GEMM (b200_gemm_gathered) waits for exactly the shards its tile reads.
+struct AgCtx {
+  bf16* xfull[MAX_RANKS];
+  uint32_t* flags[MAX_RANKS];  // rank r's arrival epochs, uint32 [R sources]
+  uint32_t* epoch;             // this rank's call counter (device-resident: graph-capturable)
+  uint32_t* counter;           // CTAs of the current call that have finished
+  int rank, world;
+};
+
+template <bool ZERO_CENTRED>
+__global__ void norm_allgather_kernel(AgCtx c, const bf16* x, const bf16* w, int rows, int H, float eps) {
+  extern __shared__ float vals[];  // H floats
+  const size_t row = static_cast<size_t>(blockIdx.x) * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 xv = *reinterpret_cast<const uint4*>(x + row + i);
+    const bf16* xe = reinterpret_cast<const bf16*>(&xv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float f = __bfloat162float(xe[j]);
+      vals[i + j] = f;
+      ss += f * f;
+    }
+  }
+  __shared__ float part[32];
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < static_cast<int>(blockDim.x >> 5); ++i) tot += part[i];  // fixed order
+  const float inv = rsqrtf(tot / H + eps);
+  const size_t grow = (static_cast<size_t>(c.rank) * rows + blockIdx.x) * H;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 wv = *reinterpret_cast<const uint4*>(w + i);
+    const bf16* we = reinterpret_cast<const bf16*>(&wv);
+    uint4 ov;
+    bf16* oe = reinterpret_cast<bf16*>(&ov);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float g = ZERO_CENTRED ? 1.0f + __bfloat162float(we[j]) : __bfloat162float(we[j]);
+      oe[j] = __float2bfloat16(vals[i + j] * inv * g);
+    }
+    for (int r = 0; r < c.world; ++r) *reinterpret_cast<uint4*>(c.xfull[r] + grow + i) = ov;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t done = atomicAdd(c.counter, 1u);
+    if (done == gridDim.x - 1) {
+      __threadfence_system();
+      *c.counter = 0;
+      const uint32_t e = *c.epoch + 1;
+      *c.epoch = e;
+      for (int r = 0; r < c.world; ++r) st_release_sys(c.flags[r] + c.rank, e);
+    }
+  }
+}
+
+extern "C" int b200_norm_allgather(const AgCtx* ctx, const void* x, const void* w, int rows, int H, float eps,
+                                   int zero_centred, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (H % 8) return -7;
+  auto k = zero_centred ? norm_allgather_kernel<true> : norm_allgather_kernel<false>;
+  k<<<rows, H >= 2048 ? 256 : 128, H * sizeof(float), st>>>(*ctx, static_cast<const bf16*>(x),
+                                                            static_cast<const bf16*>(w), rows, H, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+extern "C" int b200_ag_ctx_size() { return static_cast<int>(sizeof(AgCtx)); }
+
 extern "C" int b200_symm_alloc(void** ptr, unsigned long long bytes) {
   if (cudaMalloc(ptr, bytes) != cudaSuccess) return -1;
   return cudaMemset(*ptr, 0, bytes) == cudaSuccess ? 0 : -2;

@@ -27,7 +27,7 @@ constexpr int BM = 128;  // weight rows per tile (TMEM lanes)
 constexpr int BK = 64;   // bf16 per operand row per stage (128 bytes)
 constexpr int UMMA_K = 16;
 
-enum Epilogue : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_ARGMAX = 3, EPI_ALLREDUCE = 4, EPI_SCATTER = 5 };
+enum Epilogue : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_ARGMAX = 3, EPI_ALLREDUCE = 4, EPI_SCATTER = 5, EPI_REDUCE_SCATTER = 6 };
 
 struct GemmParams {
   int N;             // weight rows (per expert when grouped)
@@ -43,9 +43,14 @@ struct GemmParams {
   int* err;          // error word (0 = ok)
   const bf16* residual; // EPI_ALLREDUCE: optional [T, ldo] added after the cross-rank sum
   CommCtx comm;      // EPI_ALLREDUCE: the rank group's symmetric buffers
+  int rows_per_rank; // EPI_REDUCE_SCATTER / gathered X: token rows owned by each rank (a multiple of the token tile)
+  const uint32_t* x_flags;  // gathered X: per-owner arrival epochs of this rank's full activation buffer (or null)
+  const uint32_t* x_epoch;  // gathered X: the epoch the current call waits for
   int splits;        // split-K: CTAs of one cluster share an output tile, each taking 1/splits of the k-blocks
   const int2* meta;  // EPI_SCATTER: (source rank, pair slot) of every sorted row
   bf16* pair_out[MAX_RANKS];  // EPI_SCATTER: every rank's pair-output buffer [pairs, ldo] as mapped here
+  int y_rot;         // dense sequence-parallel GEMMs: token tile = (blockIdx.y + y_rot) % gridDim.y, so that each rank
+                     // starts with the tiles whose data (or whose consumer) is furthest from being the bottleneck
 };
 
 template <int BT, int EPI>
@@ -82,7 +87,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM;
-  int expert = 0, row0 = blockIdx.y * BT, nrows = BT;
+  const int by = (!GROUPED && p.y_rot) ? static_cast<int>((blockIdx.y + p.y_rot) % gridDim.y) : static_cast<int>(blockIdx.y);
+  int expert = 0, row0 = by * BT, nrows = BT;
   if (GROUPED) {
     const int nt = *p.n_tiles;
     if (static_cast<int>(blockIdx.y) >= nt) return;  // whole CTA leaves before any barrier or TMEM use
@@ -114,6 +120,9 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
   if (warp == 0) {
     if (elect_one()) {
+      // all-gather -> GEMM: the activation rows of this tile were pushed here by their owner rank; wait for that
+      // shard only, so tiles of shards that have already arrived run while the others are still in flight
+      if (p.x_flags != nullptr && !wait_flag(p.x_flags + row0 / p.rows_per_rank, *p.x_epoch, p.err)) *abort_flag = 1;
       for (int kb = 0; kb < num_k; ++kb) {
         const int s = kb % C::STAGES;
         const uint32_t ph = (kb / C::STAGES) & 1;
@@ -204,6 +213,52 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           for (int r = 1; r < cc.world; ++r) acc += comm_slot(cc, cc.rank, e, r)[o];
           if (p.residual) acc = __bfloat162float(__float2bfloat16(acc)) + __bfloat162float(p.residual[o]);
           reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16(acc);
+        }
+      }
+    } else if (EPI == EPI_REDUCE_SCATTER) {
+      // Fused GEMM -> reduce-scatter: the tile's token rows belong to one owner rank. Every rank stores its fp32
+      // partial straight into the owner's receive slot (a peer store over NVLink unless it is the owner); the
+      // owner's CTA of the same tile adds the R partials in rank order (+ residual) into its row shard.
+      const CommCtx& cc = p.comm;
+      const int blk = by * gridDim.x + blockIdx.x;
+      const int owner = row0 / p.rows_per_rank;
+      const int lrow0 = row0 - owner * p.rows_per_rank;
+      __shared__ uint32_t s_epoch_rs;
+      __shared__ int s_peer_ok_rs;
+      const int et = threadIdx.x - 64;
+      if (et == 0) { s_epoch_rs = cc.epoch[blk] + 1; cc.epoch[blk] = s_epoch_rs; s_peer_ok_rs = 1; }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const uint32_t e = s_epoch_rs;
+      if (ok) {
+        float* dst = comm_slot(cc, owner, e, cc.rank);
+#pragma unroll 1
+        for (int c = 0; c < nrows; c += 16) {
+          float v[16];
+          tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + c, v);  // warp-collective: never predicated
+          if (n_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (c + j < nrows) dst[static_cast<size_t>(lrow0 + c + j) * p.ldo + n] = v[j];
+          }
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et == 0) {
+        __threadfence_system();
+        st_release_sys(cc.flags[owner] + static_cast<size_t>(cc.rank) * cc.max_blocks + blk, e);
+      }
+      if (owner == cc.rank) {
+        if (et < cc.world && !wait_flag(cc.flags[cc.rank] + static_cast<size_t>(et) * cc.max_blocks + blk, e, cc.err))
+          s_peer_ok_rs = 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ok && n_ok && s_peer_ok_rs) {
+          for (int t = 0; t < nrows; ++t) {
+            const size_t o = static_cast<size_t>(lrow0 + t) * p.ldo + n;
+            float acc = comm_slot(cc, cc.rank, e, 0)[o];
+            for (int r = 1; r < cc.world; ++r) acc += comm_slot(cc, cc.rank, e, r)[o];
+            if (p.residual) acc = __bfloat162float(__float2bfloat16(acc)) + __bfloat162float(p.residual[o]);
+            reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16(acc);
+          }
         }
       }
     } else
@@ -456,7 +511,7 @@ extern "C" int b200_gemm_dense(const void* X, const void* W, void* out, int T, i
   const int w_rows = (epi == EPI_SILU_MUL) ? up_offset + N : N;
   if (make_map(&tw, W, K, w_rows, 0, ldw, 0, BM)) return -1;
   if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
-  GemmParams p{N, K, T, ldo, out, nullptr, nullptr, up_offset, part_max, part_idx, err, nullptr, CommCtx{}, splits, nullptr, {}};
+  GemmParams p{N, K, T, ldo, out, nullptr, nullptr, up_offset, part_max, part_idx, err, nullptr, CommCtx{}, 0, nullptr, nullptr, splits, nullptr, {}};
   const int gy = (T + bt - 1) / bt;
   switch (epi) {
     case EPI_BF16: return dispatch_bt<EPI_BF16, false>(bt, tw, tx, p, gy, st);
@@ -477,7 +532,7 @@ extern "C" int b200_gemm_grouped(const void* X, const void* W, void* out, int ca
   CUtensorMap tw, tx;
   if (make_map(&tw, W, K, w_rows, E, K, static_cast<uint64_t>(w_rows) * K, BM)) return -1;
   if (make_map(&tx, X, K, cap, 0, K, 0, bt)) return -1;
-  GemmParams p{N, K, cap, ldo, out, reinterpret_cast<const int4*>(tiles), n_tiles, up_offset, nullptr, nullptr, err, nullptr, CommCtx{}, splits, nullptr, {}};
+  GemmParams p{N, K, cap, ldo, out, reinterpret_cast<const int4*>(tiles), n_tiles, up_offset, nullptr, nullptr, err, nullptr, CommCtx{}, 0, nullptr, nullptr, splits, nullptr, {}};
   switch (epi) {
     case EPI_BF16: return dispatch_bt<EPI_BF16, true>(bt, tw, tx, p, max_tiles, st);
     case EPI_SILU_MUL: return dispatch_bt<EPI_SILU_MUL, true>(bt, tw, tx, p, max_tiles, st);
@@ -497,7 +552,7 @@ extern "C" int b200_gemm_allreduce(const CommCtx* ctx, const void* X, const void
   CUtensorMap tw, tx;
   if (make_map(&tw, W, K, N, 0, ldw, 0, BM)) return -1;
   if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
-  GemmParams p{N, K, T, N, out, nullptr, nullptr, 0, nullptr, nullptr, ctx->err, static_cast<const bf16*>(residual), *ctx, 1, nullptr, {}};
+  GemmParams p{N, K, T, N, out, nullptr, nullptr, 0, nullptr, nullptr, ctx->err, static_cast<const bf16*>(residual), *ctx, 0, nullptr, nullptr, 1, nullptr, {}};
   return dispatch_bt<EPI_ALLREDUCE, false>(bt, tw, tx, p, gy, st);
 }
 
@@ -511,9 +566,50 @@ extern "C" int b200_gemm_grouped_scatter(const void* X, const void* W, int cap, 
   if (make_map(&tw, W, K, N, E, K, static_cast<uint64_t>(N) * K, BM)) return -1;
   if (make_map(&tx, X, K, cap, 0, K, 0, bt)) return -1;
   GemmParams p{N, K, cap, N, nullptr, reinterpret_cast<const int4*>(tiles), n_tiles, 0, nullptr, nullptr, err, nullptr,
-               CommCtx{}, 1, static_cast<const int2*>(meta), {}};
+               CommCtx{}, 0, nullptr, nullptr, 1, static_cast<const int2*>(meta), {}};
   for (int r = 0; r < world && r < MAX_RANKS; ++r) p.pair_out[r] = static_cast<bf16*>(pair_out[r]);
   return dispatch_bt<EPI_SCATTER, true>(bt, tw, tx, p, max_tiles, st);
+}
+
+// Tensor-parallel output projection with a reduce-scatter epilogue: every rank calls it with its K-shard of X and
+// W; rank r ends up with out[T / R, N] = bf16(residual + sum over ranks) for its rows [r * T / R, (r + 1) * T / R).
+// T must be a multiple of world * bt. Needs (T / R) * N <= ctx->slot_elems and the tile count <= ctx->max_blocks.
+extern "C" int b200_gemm_reduce_scatter(const CommCtx* ctx, const void* X, const void* W, const void* residual,
+                                        void* out, int T, int N, int K, int ldx, int ldw, int bt, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (bt <= 0) bt = b200_pick_bt(T / ctx->world);
+  if (T % (ctx->world * bt)) return -7;
+  const int rpr = T / ctx->world, gy = T / bt;
+  if (static_cast<unsigned long long>(rpr) * N > ctx->slot_elems || ((N + BM - 1) / BM) * gy > ctx->max_blocks) return -7;
+  CUtensorMap tw, tx;
+  if (make_map(&tw, W, K, N, 0, ldw, 0, BM)) return -1;
+  if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
+  GemmParams p{N, K, T, N, out, nullptr, nullptr, 0, nullptr, nullptr, ctx->err, static_cast<const bf16*>(residual), *ctx,
+               rpr, nullptr, nullptr, 1, nullptr, {}};
+  // each rank runs the tiles of the next rank first and its own last: partials reach their owners early, and an
+  // owner's waits fall at the end of its grid, on tiles every peer has already pushed
+  p.y_rot = ((ctx->rank + 1) % ctx->world) * (rpr / bt);
+  return dispatch_bt<EPI_REDUCE_SCATTER, false>(bt, tw, tx, p, gy, st);
+}
+
+// All-gather -> GEMM: X [T, K] is this rank's full activation buffer into which every owner rank pushes its row
+// shard (allreduce.cu: norm_allgather); a tile starts as soon as its owner's shard has arrived (x_flags[owner] >=
+// *x_epoch). out[T, N] = X W^T, bf16 or fp32. `y_rot` = rank * (rows_per_rank / bt) makes each rank start with its
+// own shard, which is already there.
+extern "C" int b200_gemm_gathered(const void* X, const void* W, void* out, int T, int N, int K, int ldx, int ldw,
+                                  int out_f32, int bt, int rows_per_rank, int y_rot, const uint32_t* x_flags,
+                                  const uint32_t* x_epoch, int* err, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (bt <= 0) bt = b200_pick_bt(rows_per_rank);
+  if (rows_per_rank % bt) return -7;
+  CUtensorMap tw, tx;
+  if (make_map(&tw, W, K, N, 0, ldw, 0, BM)) return -1;
+  if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
+  GemmParams p{N, K, T, N, out, nullptr, nullptr, 0, nullptr, nullptr, err, nullptr, CommCtx{}, rows_per_rank, x_flags,
+               x_epoch, 1, nullptr, {}};
+  p.y_rot = y_rot;
+  const int gy = (T + bt - 1) / bt;
+  return out_f32 ? dispatch_bt<EPI_F32, false>(bt, tw, tx, p, gy, st) : dispatch_bt<EPI_BF16, false>(bt, tw, tx, p, gy, st);
 }
 
 extern "C" int b200_argmax_finish(const float* part_max, const int* part_idx, int n_tiles, int T, int64_t* out,
@@ -563,7 +659,7 @@ extern "C" int b200_lm_head_argmax_noalloc(const void* X, const void* W, int64_t
   CUtensorMap tw, tx;
   if (make_map(&tw, W, K, V, 0, ldw, 0, BM)) return -1;
   if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
-  GemmParams p{V, K, T, 0, nullptr, nullptr, nullptr, 0, part_max, part_idx, err, nullptr, CommCtx{}, 1, nullptr, {}};
+  GemmParams p{V, K, T, 0, nullptr, nullptr, nullptr, 0, part_max, part_idx, err, nullptr, CommCtx{}, 0, nullptr, nullptr, 1, nullptr, {}};
   const int rc = dispatch_bt<EPI_ARGMAX, false>(bt, tw, tx, p, (T + bt - 1) / bt, st);
   if (rc) return rc;
   argmax_finish_kernel<<<T, 256, 0, st>>>(part_max, part_idx, n_tiles, T, out_idx, out_val);

@@ -1,0 +1,176 @@
+"""Sequence-parallel tensor parallelism for prefill-size passes: fused GEMM -> reduce-scatter and
+all-gather -> GEMM over NVLink peer memory.
+
+With T token rows replicated on R ranks, a one-shot all-reduce after every row-parallel projection moves
+``T * N * 4 * (R - 1)`` bytes out of each GPU. For large T this class keeps the residual stream row-sharded
+instead (rank r owns rows ``[r * T / R, (r + 1) * T / R)``) and runs three kernels per half-layer:
+
+* ``gemm_reduce_scatter``: the row-parallel GEMM (``ops/cuda/gemm_tcgen05.cu``, ``EPI_REDUCE_SCATTER``)
+  stores each fp32 partial tile straight from TMEM into the owner rank's receive slot; the owner's CTA of
+  the same tile adds the partials in rank order plus the residual. ``(R - 1) / R`` of the all-reduce bytes.
+* ``norm_allgather``: RMSNorm of the rank's rows, each normalised row stored into every rank's full
+  activation buffer (``ops/cuda/allreduce.cu``), then one arrival epoch per shard.
+* ``gemm_gathered``: the following column-parallel GEMM reads the full buffer locally; its TMA producer
+  waits only for the shard that owns the tile's rows, so tiles of early shards overlap the rest of the gather.
+
+Calls must be made in the same order on every rank. Two ``gemm_reduce_scatter`` calls must be separated by a
+``norm_allgather`` + ``gemm_gathered`` pair (as in a transformer layer): that pair is what guarantees that an
+owner has finished reading a receive slot before a peer writes it again. The reference has no counterpart
+(its tensor parallelism is a 2-GPU all-reduce, ``engine/fast/tp.py:132-162``).
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..ops import cuda_ops
+from .symm import MAX_RANKS, CommCtx, SymmComm, _lib as _symm_lib
+
+
+class AgCtx(ctypes.Structure):
+    _fields_ = [
+        ("xfull", ctypes.c_void_p * MAX_RANKS),
+        ("flags", ctypes.c_void_p * MAX_RANKS),
+        ("epoch", ctypes.c_void_p),
+        ("counter", ctypes.c_void_p),
+        ("rank", ctypes.c_int),
+        ("world", ctypes.c_int),
+    ]
+
+
+def _lib():
+    L = _symm_lib()
+    if not getattr(L, "_sp_ready", False):
+        P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+        L.b200_gemm_reduce_scatter.argtypes = [ctypes.POINTER(CommCtx), P, P, P, P, I, I, I, I, I, I, P]
+        L.b200_gemm_gathered.argtypes = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, P, P]
+        L.b200_norm_allgather.argtypes = [ctypes.POINTER(AgCtx), P, P, I, I, F, I, P]
+        for n in ("b200_gemm_reduce_scatter", "b200_gemm_gathered", "b200_norm_allgather", "b200_ag_ctx_size"):
+            getattr(L, n).restype = I
+        assert L.b200_ag_ctx_size() == ctypes.sizeof(AgCtx), "AgCtx layout mismatch"
+        L._sp_ready = True
+    return L
+
+
+class _DevMem:
+    """A raw device allocation seen through ``__cuda_array_interface__`` so that torch can view it."""
+
+    def __init__(self, ptr: int, n_u16: int) -> None:
+        self.__cuda_array_interface__ = {"shape": (n_u16,), "typestr": "<u2", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+class SeqParallel:
+    def __init__(self, device: torch.device, group, max_rows: int, hidden: int, max_n: int | None = None) -> None:
+        """``max_rows``: most token rows of one pass (all ranks together); ``max_n``: widest reduce-scattered output."""
+        import torch.distributed as dist
+
+        self.device, self.group = device, group
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.max_rows, self.H = max_rows, hidden
+        n = max_n or hidden
+        rpr = (max_rows + self.world - 1) // self.world
+        self.comm = SymmComm(device, group, slot_elems=rpr * n, max_blocks=max(4096, ((n + 127) // 128) * (max_rows // 16 + 1)))
+        L = _lib()
+        sizes = {"xfull": max_rows * hidden * 2, "flags": MAX_RANKS * 4, "epoch": 16, "counter": 16}
+        self._own, self._opened = {}, []
+        with torch.cuda.device(device):
+            for name, nbytes in sizes.items():
+                p = ctypes.c_void_p()
+                if L.b200_symm_alloc(ctypes.byref(p), nbytes):
+                    raise RuntimeError(f"symmetric allocation of {nbytes} bytes failed")
+                self._own[name] = p.value
+            torch.cuda.synchronize(device)
+            peers = {k: [self._own[k]] for k in ("xfull", "flags")}
+            if self.world > 1:
+                handles = {}
+                for name in peers:
+                    buf = ctypes.create_string_buffer(64)
+                    if L.b200_symm_export(self._own[name], buf):
+                        raise RuntimeError("cudaIpcGetMemHandle failed")
+                    handles[name] = buf.raw
+                gathered: list = [None] * self.world
+                dist.all_gather_object(gathered, handles, group=group)
+                peers = {k: [] for k in peers}
+                for r in range(self.world):
+                    for name in peers:
+                        if r == self.rank:
+                            peers[name].append(self._own[name])
+                            continue
+                        p = ctypes.c_void_p()
+                        if L.b200_symm_import(gathered[r][name], ctypes.byref(p)):
+                            raise RuntimeError(f"cudaIpcOpenMemHandle failed for rank {r}")
+                        peers[name].append(p.value)
+                        self._opened.append(p.value)
+                dist.barrier(group=group)
+        ctx = AgCtx()
+        for r in range(self.world):
+            ctx.xfull[r], ctx.flags[r] = peers["xfull"][r], peers["flags"][r]
+        ctx.epoch, ctx.counter = self._own["epoch"], self._own["counter"]
+        ctx.rank, ctx.world = self.rank, self.world
+        self.ctx = ctx
+        self._xfull = torch.as_tensor(_DevMem(self._own["xfull"], max_rows * hidden), device=device).view(torch.bfloat16)
+
+    def rows_per_rank(self, T: int) -> int:
+        if T % self.world:
+            raise ValueError(f"{T} rows do not split over {self.world} ranks")
+        return T // self.world
+
+    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``x [T, K/R] @ w [N, K/R]^T`` summed over ranks (+ ``residual [T/R, N]``) -> this rank's rows ``[T/R, N]``."""
+        T, K = x.shape
+        N = w.shape[0]
+        rpr = self.rows_per_rank(T)
+        bt = cuda_ops.lib().b200_pick_bt(rpr)
+        while rpr % bt:
+            bt //= 2
+        if bt < 16:
+            raise ValueError(f"{rpr} rows per rank are not a multiple of 16")
+        out = torch.empty(rpr, N, dtype=torch.bfloat16, device=x.device)
+        rc = _lib().b200_gemm_reduce_scatter(ctypes.byref(self.comm.ctx), x.data_ptr(), w.data_ptr(),
+                                             None if residual is None else residual.data_ptr(), out.data_ptr(), T, N, K,
+                                             x.stride(0), w.stride(0), bt, torch.cuda.current_stream().cuda_stream)
+        if rc:
+            raise cuda_ops.KernelError(f"gemm_reduce_scatter failed with code {rc}")
+        return out
+
+    def norm_allgather(self, x: torch.Tensor, w: torch.Tensor, eps: float, zero_centred: bool = True) -> torch.Tensor:
+        """RMSNorm of this rank's rows, pushed into every rank's full buffer; returns the (not yet complete) view."""
+        rows, H = x.shape
+        assert H == self.H and rows * self.world <= self.max_rows and x.is_contiguous()
+        rc = _lib().b200_norm_allgather(ctypes.byref(self.ctx), x.data_ptr(), w.data_ptr(), rows, H, eps,
+                                        int(zero_centred), torch.cuda.current_stream().cuda_stream)
+        if rc:
+            raise cuda_ops.KernelError(f"norm_allgather failed with code {rc}")
+        return self._xfull[: rows * self.world * H].view(rows * self.world, H)
+
+    def gemm_gathered(self, xfull: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        """``xfull @ w^T`` where ``xfull`` is the view ``norm_allgather`` returned: tiles wait for their shard only."""
+        T, K = xfull.shape
+        N = w.shape[0]
+        rpr = self.rows_per_rank(T)
+        bt = cuda_ops.lib().b200_pick_bt(rpr)
+        while rpr % bt:
+            bt //= 2
+        out = torch.empty(T, N, dtype=out_dtype, device=xfull.device)
+        rc = _lib().b200_gemm_gathered(xfull.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, xfull.stride(0),
+                                       w.stride(0), int(out_dtype == torch.float32), bt, rpr, self.rank * (rpr // bt), self._own["flags"],
+                                       self._own["epoch"], cuda_ops.err_word(xfull.device).data_ptr(),
+                                       torch.cuda.current_stream().cuda_stream)
+        if rc:
+            raise cuda_ops.KernelError(f"gemm_gathered failed with code {rc}")
+        return out
+
+    def close(self) -> None:
+        L = _lib()
+        torch.cuda.synchronize(self.device)
+        self._xfull = None
+        for p in self._opened:
+            L.b200_symm_close(p)
+        for p in self._own.values():
+            L.b200_symm_free(p)
+        self._opened, self._own = [], {}
+        self.comm.close()

@@ -212,7 +212,97 @@ def mode_ep_moe(rank, world, dev):
     ep.close()
 
 
-MODES = {"allreduce": mode_allreduce, "ep_moe": mode_ep_moe, "tp_model": mode_tp_model, "lockstep": mode_lockstep}
+def mode_seq_parallel(rank, world, dev):
+    """GEMM -> reduce-scatter, norm + all-gather push, gathered GEMM: numerics against NCCL + fp32, then timing
+    of the fused pipeline against reduce_scatter / all_gather / torch.matmul."""
+    from b200serve.ops import cuda_ops, torch_ops
+    from b200serve.parallel.sp import SeqParallel
+
+    H, eps = 2048, 1e-6
+    sp = SeqParallel(dev, dist.group.WORLD, max_rows=8192, hidden=H)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    gc = torch.Generator(device=dev).manual_seed(7)
+    for T, Ks, N2 in ((32 * world, 512, 1024), (128 * world, 2048, 4096), (1024, 1024, 12352 // world // 8 * 8)):
+        rpr = T // world
+        x = (torch.randn(T, Ks, device=dev, generator=g) * 0.5).to(torch.bfloat16)          # K-shard of the input
+        w_o = (torch.randn(H, Ks, device=dev, generator=g) * 0.05).to(torch.bfloat16)       # K-shard of out_proj
+        res = torch.randn(T, H, device=dev, generator=gc).to(torch.bfloat16)                # replicated residual
+        w_n = (torch.randn(H, device=dev, generator=gc) * 0.1).to(torch.bfloat16)
+        w_i = (torch.randn(N2, H, device=dev, generator=g) * 0.05).to(torch.bfloat16)       # column shard of in_proj
+        for rep in range(3):
+            mine = sp.gemm_reduce_scatter(x, w_o, res[rank * rpr:(rank + 1) * rpr].contiguous())
+            full = sp.norm_allgather(mine, w_n, eps)
+            y = sp.gemm_gathered(full, w_i)
+            torch.cuda.synchronize()
+            cuda_ops.check_errors(dev)
+            part = x.float() @ w_o.float().t()
+            dist.all_reduce(part)
+            want_res = (part.to(torch.bfloat16).float() + res.float()).to(torch.bfloat16)
+            got_res = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(got_res, mine)
+            got_res = torch.cat(got_res)
+            err = (got_res.float() - want_res.float()).abs().max().item()
+            assert err <= 0.02 * want_res.float().abs().max().item() + 1e-3, ("reduce_scatter", T, rep, err)
+            want_full = torch_ops.rmsnorm(got_res, w_n, eps)
+            assert torch.equal(full, want_full.to(torch.bfloat16)) or \
+                (full.float() - want_full.float()).abs().max().item() < 0.05, ("allgather", T, rep)
+            want_y = full.float() @ w_i.float().t()
+            e2 = (y.float() - want_y).abs().max().item()
+            assert e2 <= 0.02 * want_y.abs().max().item() + 1e-3, ("gathered", T, rep, e2)
+            dist.barrier()
+    # timing at a prefill size: T = 8192 rows, out_proj K-shard 4096 / world, in_proj 12352 / world columns
+    T, Ks, N2 = 8192, 4096 // world, 12352 // world // 8 * 8
+    rpr = T // world
+    x = (torch.randn(T, Ks, device=dev) * 0.5).to(torch.bfloat16)
+    w_o = (torch.randn(H, Ks, device=dev) * 0.05).to(torch.bfloat16)
+    w_n = torch.zeros(H, device=dev, dtype=torch.bfloat16)
+    w_i = (torch.randn(N2, H, device=dev) * 0.05).to(torch.bfloat16)
+    res = torch.randn(rpr, H, device=dev).to(torch.bfloat16)
+
+    def fused():
+        mine = sp.gemm_reduce_scatter(x, w_o, res)
+        return sp.gemm_gathered(sp.norm_allgather(mine, w_n, eps), w_i)
+
+    rs_out = torch.empty(rpr, H, device=dev, dtype=torch.bfloat16)
+    ag_out = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+
+    def library():
+        part = x @ w_o.t()
+        dist.reduce_scatter_tensor(rs_out, part)
+        mine = torch_ops.rmsnorm(rs_out + res, w_n, eps)
+        dist.all_gather_into_tensor(ag_out, mine)
+        return ag_out @ w_i.t()
+
+    def allreduce_path():
+        h = cuda_ops.linear(x, w_o, out_dtype=torch.float32)
+        dist.all_reduce(h)
+        return cuda_ops.linear(cuda_ops.rmsnorm(h.to(torch.bfloat16), w_n, eps), w_i)
+
+    names = {}
+    for name, fn in (("fused", fused), ("nccl_rs_ag_cublas", library), ("gemm_nccl_allreduce", allreduce_path)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(); dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(10):
+            fn()
+        b.record(); torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / 10 * 1e3], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        names[name] = t.item()
+    if rank == 0:
+        flops = 2 * T * H * Ks + 2 * T * N2 * H
+        nv = (world - 1) / world * T * H * (4 + 2)
+        print(f"seq_parallel world={world} T={T}: " + ", ".join(f"{k} {v:.1f} us" for k, v in names.items()) +
+              f"; {flops / names['fused'] / 1e6:.0f} TFLOP/s per GPU, NVLink bytes out per GPU {nv / 1e6:.1f} MB", flush=True)
+    cuda_ops.check_errors(dev)
+    dist.barrier()
+    sp.close()
+
+
+MODES = {"allreduce": mode_allreduce, "ep_moe": mode_ep_moe, "tp_model": mode_tp_model, "lockstep": mode_lockstep,
+         "seq_parallel": mode_seq_parallel}
 
 if __name__ == "__main__":
     mode = sys.argv[1]

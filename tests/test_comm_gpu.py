@@ -105,3 +105,43 @@ def test_two_rank_expert_parallel_moe():
                         "ep_moe"], capture_output=True, text=True, timeout=600,
                        env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
     assert r.returncode == 0 and "OK ep_moe" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_sequence_parallel_kernels_loopback():
+    """One-rank group: GEMM -> reduce-scatter, norm + all-gather push and the gathered GEMM against fp32."""
+    from b200serve.ops import cuda_ops, torch_ops
+    from b200serve.parallel.sp import SeqParallel
+
+    dev = torch.device("cuda")
+    H = 512
+    sp = SeqParallel(dev, None, max_rows=512, hidden=H)
+    g = torch.Generator(device=dev).manual_seed(5)
+    for T in (16, 48, 512):
+        x = (torch.randn(T, 256, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+        w_o = (torch.randn(H, 256, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+        res = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+        w_n = (torch.randn(H, device=dev, generator=g) * 0.1).to(torch.bfloat16)
+        w_i = (torch.randn(384, H, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+        for _ in range(3):
+            mine = sp.gemm_reduce_scatter(x, w_o, res)
+            full = sp.norm_allgather(mine, w_n, 1e-6)
+            y = sp.gemm_gathered(full, w_i)
+            torch.cuda.synchronize()
+            cuda_ops.check_errors(dev)
+            want = ((x.float() @ w_o.float().t()).to(torch.bfloat16).float() + res.float()).to(torch.bfloat16)
+            assert (mine.float() - want.float()).abs().max().item() <= 0.02 * want.float().abs().max().item()
+            assert (full.float() - torch_ops.rmsnorm(mine, w_n, 1e-6).float()).abs().max().item() < 0.05
+            want_y = full.float() @ w_i.float().t()
+            assert (y.float() - want_y).abs().max().item() <= 0.02 * want_y.abs().max().item() + 1e-3
+    sp.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_rank_sequence_parallel_gemms():
+    import os
+
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29641", str(ROOT / "tests/dist_worker.py"),
+                        "seq_parallel"], capture_output=True, text=True, timeout=600,
+                       env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
+    assert r.returncode == 0 and "OK seq_parallel" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
