@@ -116,19 +116,65 @@ struct AgCtx {
   int rank, world;
 };
 
-template <bool ZERO_CENTRED>
-__global__ void norm_allgather_kernel(AgCtx c, const bf16* x, const bf16* w, int rows, int H, float eps) {
+// REDUCE: the rows come from a GEMM -> reduce-scatter (gemm_tcgen05.cu, EPI_REDUCE_SCATTER): wait for the arrival
+// flags of the row's tiles (gx tiles of 128 columns x R sources), add the R fp32 partials in rank order, round to
+// bf16, add the residual, store the new residual row, then normalise. Otherwise x is the row itself.
+template <bool ZERO_CENTRED, bool REDUCE>
+__global__ void reduce_norm_allgather_kernel(AgCtx c, CommCtx cc, const bf16* x, const bf16* res, bf16* res_out,
+                                             const bf16* w, int rows, int H, float eps, int bt) {
   extern __shared__ float vals[];  // H floats
   const size_t row = static_cast<size_t>(blockIdx.x) * H;
+  __shared__ int s_ok;
+  if (REDUCE) {
+    const int gx = (H + 127) / 128;
+    const int by = (cc.rank * rows + blockIdx.x) / bt;  // token tile of this row in the GEMM's grid
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < gx * cc.world; i += blockDim.x) {
+      const int nx = i % gx, src = i / gx;
+      const int blk = by * gx + nx;
+      if (!wait_flag(cc.flags[cc.rank] + static_cast<size_t>(src) * cc.max_blocks + blk, cc.epoch[blk], cc.err)) s_ok = 0;
+    }
+    __syncthreads();
+    if (!s_ok) return;  // the error word is set; the shard's epoch is never published, consumers time out the same way
+  }
   float ss = 0.f;
   for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
-    uint4 xv = *reinterpret_cast<const uint4*>(x + row + i);
-    const bf16* xe = reinterpret_cast<const bf16*>(&xv);
+    float f[8];
+    if (REDUCE) {
+      const uint32_t ei = cc.epoch[((cc.rank * rows + blockIdx.x) / bt) * ((H + 127) / 128) + i / 128];
+      const float4* s0 = reinterpret_cast<const float4*>(comm_slot(cc, cc.rank, ei, 0) + row + i);
+      float4 a = s0[0], b = s0[1];
+      for (int r = 1; r < cc.world; ++r) {
+        const float4* sr = reinterpret_cast<const float4*>(comm_slot(cc, cc.rank, ei, r) + row + i);
+        const float4 a2 = sr[0], b2 = sr[1];
+        a.x += a2.x; a.y += a2.y; a.z += a2.z; a.w += a2.w;
+        b.x += b2.x; b.y += b2.y; b.z += b2.z; b.w += b2.w;
+      }
+      f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+      uint4 rv;
+      const bf16* re = reinterpret_cast<const bf16*>(&rv);
+      if (res) rv = *reinterpret_cast<const uint4*>(res + row + i);
+      uint4 ov;
+      bf16* oe = reinterpret_cast<bf16*>(&ov);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        bf16 s = __float2bfloat16(f[j]);
+        if (res) s = __float2bfloat16(__bfloat162float(s) + __bfloat162float(re[j]));
+        oe[j] = s;
+        f[j] = __bfloat162float(s);
+      }
+      if (res_out) *reinterpret_cast<uint4*>(res_out + row + i) = ov;
+    } else {
+      uint4 xv = *reinterpret_cast<const uint4*>(x + row + i);
+      const bf16* xe = reinterpret_cast<const bf16*>(&xv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(xe[j]);
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float f = __bfloat162float(xe[j]);
-      vals[i + j] = f;
-      ss += f * f;
+      vals[i + j] = f[j];
+      ss += f[j] * f[j];
     }
   }
   __shared__ float part[32];
@@ -158,20 +204,33 @@ __global__ void norm_allgather_kernel(AgCtx c, const bf16* x, const bf16* w, int
     if (done == gridDim.x - 1) {
       __threadfence_system();
       *c.counter = 0;
-      const uint32_t e = *c.epoch + 1;
-      *c.epoch = e;
-      for (int r = 0; r < c.world; ++r) st_release_sys(c.flags[r] + c.rank, e);
+      const uint32_t en = *c.epoch + 1;
+      *c.epoch = en;
+      for (int r = 0; r < c.world; ++r) st_release_sys(c.flags[r] + c.rank, en);
     }
   }
 }
 
-extern "C" int b200_norm_allgather(const AgCtx* ctx, const void* x, const void* w, int rows, int H, float eps,
-                                   int zero_centred, cudaStream_t st) {
+// comm == nullptr: plain rows `x` [rows, H]. Otherwise the rows are reduced from the receive slots that a preceding
+// b200_gemm_reduce_scatter with token tile `bt` filled; `res` (may be null) is added, `res_out` (may be null, may
+// alias `res`) receives the new residual rows.
+extern "C" int b200_reduce_norm_allgather(const AgCtx* ctx, const CommCtx* comm, const void* x, const void* res,
+                                          void* res_out, const void* w, int rows, int H, float eps, int zero_centred,
+                                          int bt, cudaStream_t st) {
   if (rows <= 0) return 0;
   if (H % 8) return -7;
-  auto k = zero_centred ? norm_allgather_kernel<true> : norm_allgather_kernel<false>;
-  k<<<rows, H >= 2048 ? 256 : 128, H * sizeof(float), st>>>(*ctx, static_cast<const bf16*>(x),
-                                                            static_cast<const bf16*>(w), rows, H, eps);
+  const int threads = H >= 2048 ? 256 : 128;
+  const size_t sm = H * sizeof(float);
+  const bf16 *xb = static_cast<const bf16*>(x), *rb = static_cast<const bf16*>(res), *wb = static_cast<const bf16*>(w);
+  bf16* ro = static_cast<bf16*>(res_out);
+  if (comm) {
+    if (bt <= 0 || rows % bt || static_cast<unsigned long long>(rows) * H > comm->slot_elems) return -7;
+    if (zero_centred) reduce_norm_allgather_kernel<true, true><<<rows, threads, sm, st>>>(*ctx, *comm, xb, rb, ro, wb, rows, H, eps, bt);
+    else reduce_norm_allgather_kernel<false, true><<<rows, threads, sm, st>>>(*ctx, *comm, xb, rb, ro, wb, rows, H, eps, bt);
+  } else {
+    if (zero_centred) reduce_norm_allgather_kernel<true, false><<<rows, threads, sm, st>>>(*ctx, CommCtx{}, xb, rb, ro, wb, rows, H, eps, bt);
+    else reduce_norm_allgather_kernel<false, false><<<rows, threads, sm, st>>>(*ctx, CommCtx{}, xb, rb, ro, wb, rows, H, eps, bt);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 extern "C" int b200_ag_ctx_size() { return static_cast<int>(sizeof(AgCtx)); }

@@ -217,16 +217,16 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     } else if (EPI == EPI_REDUCE_SCATTER) {
       // Fused GEMM -> reduce-scatter: the tile's token rows belong to one owner rank. Every rank stores its fp32
-      // partial straight into the owner's receive slot (a peer store over NVLink unless it is the owner); the
-      // owner's CTA of the same tile adds the R partials in rank order (+ residual) into its row shard.
+      // partial straight from TMEM into the owner's receive slot (a peer store over NVLink unless it is the
+      // owner) and releases the tile's arrival flag there. Nothing waits here: the owner adds the R partials in
+      // rank order inside the following norm kernel (allreduce.cu, reduce_norm_allgather_kernel), at full occupancy.
       const CommCtx& cc = p.comm;
       const int blk = by * gridDim.x + blockIdx.x;
       const int owner = row0 / p.rows_per_rank;
       const int lrow0 = row0 - owner * p.rows_per_rank;
       __shared__ uint32_t s_epoch_rs;
-      __shared__ int s_peer_ok_rs;
       const int et = threadIdx.x - 64;
-      if (et == 0) { s_epoch_rs = cc.epoch[blk] + 1; cc.epoch[blk] = s_epoch_rs; s_peer_ok_rs = 1; }
+      if (et == 0) { s_epoch_rs = cc.epoch[blk] + 1; cc.epoch[blk] = s_epoch_rs; }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       const uint32_t e = s_epoch_rs;
       if (ok) {
@@ -246,20 +246,6 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       if (et == 0) {
         __threadfence_system();
         st_release_sys(cc.flags[owner] + static_cast<size_t>(cc.rank) * cc.max_blocks + blk, e);
-      }
-      if (owner == cc.rank) {
-        if (et < cc.world && !wait_flag(cc.flags[cc.rank] + static_cast<size_t>(et) * cc.max_blocks + blk, e, cc.err))
-          s_peer_ok_rs = 0;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (ok && n_ok && s_peer_ok_rs) {
-          for (int t = 0; t < nrows; ++t) {
-            const size_t o = static_cast<size_t>(lrow0 + t) * p.ldo + n;
-            float acc = comm_slot(cc, cc.rank, e, 0)[o];
-            for (int r = 1; r < cc.world; ++r) acc += comm_slot(cc, cc.rank, e, r)[o];
-            if (p.residual) acc = __bfloat162float(__float2bfloat16(acc)) + __bfloat162float(p.residual[o]);
-            reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16(acc);
-          }
-        }
       }
     } else
     if (SPLIT && blockIdx.z != 0) {
@@ -572,10 +558,11 @@ extern "C" int b200_gemm_grouped_scatter(const void* X, const void* W, int cap, 
 }
 
 // Tensor-parallel output projection with a reduce-scatter epilogue: every rank calls it with its K-shard of X and
-// W; rank r ends up with out[T / R, N] = bf16(residual + sum over ranks) for its rows [r * T / R, (r + 1) * T / R).
+// W [N, K]; afterwards the fp32 partials of rank r's rows [r * T / R, (r + 1) * T / R) sit in rank r's receive
+// slots, one per source rank, with one arrival flag per (source, tile). b200_reduce_norm_allgather consumes them.
 // T must be a multiple of world * bt. Needs (T / R) * N <= ctx->slot_elems and the tile count <= ctx->max_blocks.
-extern "C" int b200_gemm_reduce_scatter(const CommCtx* ctx, const void* X, const void* W, const void* residual,
-                                        void* out, int T, int N, int K, int ldx, int ldw, int bt, cudaStream_t st) {
+extern "C" int b200_gemm_reduce_scatter(const CommCtx* ctx, const void* X, const void* W, int T, int N, int K, int ldx,
+                                        int ldw, int bt, cudaStream_t st) {
   if (T <= 0) return 0;
   if (bt <= 0) bt = b200_pick_bt(T / ctx->world);
   if (T % (ctx->world * bt)) return -7;
@@ -584,7 +571,7 @@ extern "C" int b200_gemm_reduce_scatter(const CommCtx* ctx, const void* X, const
   CUtensorMap tw, tx;
   if (make_map(&tw, W, K, N, 0, ldw, 0, BM)) return -1;
   if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
-  GemmParams p{N, K, T, N, out, nullptr, nullptr, 0, nullptr, nullptr, ctx->err, static_cast<const bf16*>(residual), *ctx,
+  GemmParams p{N, K, T, N, nullptr, nullptr, nullptr, 0, nullptr, nullptr, ctx->err, nullptr, *ctx,
                rpr, nullptr, nullptr, 1, nullptr, {}};
   // each rank runs the tiles of the next rank first and its own last: partials reach their owners early, and an
   // owner's waits fall at the end of its grid, on tiles every peer has already pushed

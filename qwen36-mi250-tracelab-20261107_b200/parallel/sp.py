@@ -6,15 +6,16 @@ With T token rows replicated on R ranks, a one-shot all-reduce after every row-p
 instead (rank r owns rows ``[r * T / R, (r + 1) * T / R)``) and runs three kernels per half-layer:
 
 * ``gemm_reduce_scatter``: the row-parallel GEMM (``ops/cuda/gemm_tcgen05.cu``, ``EPI_REDUCE_SCATTER``)
-  stores each fp32 partial tile straight from TMEM into the owner rank's receive slot; the owner's CTA of
-  the same tile adds the partials in rank order plus the residual. ``(R - 1) / R`` of the all-reduce bytes.
-* ``norm_allgather``: RMSNorm of the rank's rows, each normalised row stored into every rank's full
-  activation buffer (``ops/cuda/allreduce.cu``), then one arrival epoch per shard.
+  stores each fp32 partial tile straight from TMEM into the owner rank's receive slot and releases the tile's
+  arrival flag; it never waits. ``(R - 1) / R`` of the all-reduce bytes.
+* ``reduce_norm_allgather`` (``ops/cuda/allreduce.cu``): the owner waits for the flags of a row's tiles, adds
+  the partials in rank order plus the residual, stores the new residual row, and pushes the RMSNorm of the row
+  into every rank's full activation buffer; the last CTA publishes one arrival epoch for the shard.
 * ``gemm_gathered``: the following column-parallel GEMM reads the full buffer locally; its TMA producer
   waits only for the shard that owns the tile's rows, so tiles of early shards overlap the rest of the gather.
 
 Calls must be made in the same order on every rank. Two ``gemm_reduce_scatter`` calls must be separated by a
-``norm_allgather`` + ``gemm_gathered`` pair (as in a transformer layer): that pair is what guarantees that an
+``reduce_norm_allgather`` + ``gemm_gathered`` pair (as in a transformer layer): that pair is what guarantees that an
 owner has finished reading a receive slot before a peer writes it again. The reference has no counterpart
 (its tensor parallelism is a 2-GPU all-reduce, ``engine/fast/tp.py:132-162``).
 """
@@ -44,10 +45,10 @@ def _lib():
     L = _symm_lib()
     if not getattr(L, "_sp_ready", False):
         P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
-        L.b200_gemm_reduce_scatter.argtypes = [ctypes.POINTER(CommCtx), P, P, P, P, I, I, I, I, I, I, P]
+        L.b200_gemm_reduce_scatter.argtypes = [ctypes.POINTER(CommCtx), P, P, I, I, I, I, I, I, P]
         L.b200_gemm_gathered.argtypes = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, P, P]
-        L.b200_norm_allgather.argtypes = [ctypes.POINTER(AgCtx), P, P, I, I, F, I, P]
-        for n in ("b200_gemm_reduce_scatter", "b200_gemm_gathered", "b200_norm_allgather", "b200_ag_ctx_size"):
+        L.b200_reduce_norm_allgather.argtypes = [ctypes.POINTER(AgCtx), ctypes.POINTER(CommCtx), P, P, P, P, I, I, F, I, I, P]
+        for n in ("b200_gemm_reduce_scatter", "b200_gemm_gathered", "b200_reduce_norm_allgather", "b200_ag_ctx_size"):
             getattr(L, n).restype = I
         assert L.b200_ag_ctx_size() == ctypes.sizeof(AgCtx), "AgCtx layout mismatch"
         L._sp_ready = True
@@ -71,6 +72,7 @@ class SeqParallel:
         self.rank = dist.get_rank(group) if group is not None else 0
         self.world = dist.get_world_size(group) if group is not None else 1
         self.max_rows, self.H = max_rows, hidden
+        self.bt_cap = 256  # widest token tile of the three kernels
         n = max_n or hidden
         rpr = (max_rows + self.world - 1) // self.world
         self.comm = SymmComm(device, group, slot_elems=rpr * n, max_blocks=max(4096, ((n + 127) // 128) * (max_rows // 16 + 1)))
@@ -119,30 +121,47 @@ class SeqParallel:
             raise ValueError(f"{T} rows do not split over {self.world} ranks")
         return T // self.world
 
-    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
-        """``x [T, K/R] @ w [N, K/R]^T`` summed over ranks (+ ``residual [T/R, N]``) -> this rank's rows ``[T/R, N]``."""
-        T, K = x.shape
-        N = w.shape[0]
-        rpr = self.rows_per_rank(T)
-        bt = cuda_ops.lib().b200_pick_bt(rpr)
+    def _bt(self, rpr: int) -> int:
+        bt = min(cuda_ops.lib().b200_pick_bt(rpr), self.bt_cap)
         while rpr % bt:
             bt //= 2
         if bt < 16:
             raise ValueError(f"{rpr} rows per rank are not a multiple of 16")
-        out = torch.empty(rpr, N, dtype=torch.bfloat16, device=x.device)
-        rc = _lib().b200_gemm_reduce_scatter(ctypes.byref(self.comm.ctx), x.data_ptr(), w.data_ptr(),
-                                             None if residual is None else residual.data_ptr(), out.data_ptr(), T, N, K,
-                                             x.stride(0), w.stride(0), bt, torch.cuda.current_stream().cuda_stream)
+        return bt
+
+    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor) -> int:
+        """``x [T, K/R] @ w [N, K/R]^T``: every rank's fp32 partial of rank r's rows lands in rank r's receive
+        slots. Returns the rows per rank; ``reduce_norm_allgather`` must follow on every rank."""
+        T, K = x.shape
+        N = w.shape[0]
+        assert N == self.H
+        rpr = self.rows_per_rank(T)
+        rc = _lib().b200_gemm_reduce_scatter(ctypes.byref(self.comm.ctx), x.data_ptr(), w.data_ptr(), T, N, K,
+                                             x.stride(0), w.stride(0), self._bt(rpr),
+                                             torch.cuda.current_stream().cuda_stream)
         if rc:
             raise cuda_ops.KernelError(f"gemm_reduce_scatter failed with code {rc}")
-        return out
+        return rpr
+
+    def reduce_norm_allgather(self, rows: int, residual: torch.Tensor | None, w: torch.Tensor, eps: float,
+                              zero_centred: bool = True) -> tuple[torch.Tensor, torch.Tensor]:
+        """Finish the reduce-scatter: new residual rows ``[rows, H]`` of this rank = bf16(sum of partials) +
+        ``residual``; their RMSNorm is pushed into every rank's full buffer. Returns (new residual, full view)."""
+        new_res = torch.empty(rows, self.H, dtype=torch.bfloat16, device=self.device)
+        rc = _lib().b200_reduce_norm_allgather(ctypes.byref(self.ctx), ctypes.byref(self.comm.ctx), None,
+                                               None if residual is None else residual.data_ptr(), new_res.data_ptr(),
+                                               w.data_ptr(), rows, self.H, eps, int(zero_centred), self._bt(rows),
+                                               torch.cuda.current_stream().cuda_stream)
+        if rc:
+            raise cuda_ops.KernelError(f"reduce_norm_allgather failed with code {rc}")
+        return new_res, self._xfull[: rows * self.world * self.H].view(rows * self.world, self.H)
 
     def norm_allgather(self, x: torch.Tensor, w: torch.Tensor, eps: float, zero_centred: bool = True) -> torch.Tensor:
         """RMSNorm of this rank's rows, pushed into every rank's full buffer; returns the (not yet complete) view."""
         rows, H = x.shape
         assert H == self.H and rows * self.world <= self.max_rows and x.is_contiguous()
-        rc = _lib().b200_norm_allgather(ctypes.byref(self.ctx), x.data_ptr(), w.data_ptr(), rows, H, eps,
-                                        int(zero_centred), torch.cuda.current_stream().cuda_stream)
+        rc = _lib().b200_reduce_norm_allgather(ctypes.byref(self.ctx), None, x.data_ptr(), None, None, w.data_ptr(), rows,
+                                               H, eps, int(zero_centred), 0, torch.cuda.current_stream().cuda_stream)
         if rc:
             raise cuda_ops.KernelError(f"norm_allgather failed with code {rc}")
         return self._xfull[: rows * self.world * H].view(rows * self.world, H)
@@ -152,9 +171,7 @@ class SeqParallel:
         T, K = xfull.shape
         N = w.shape[0]
         rpr = self.rows_per_rank(T)
-        bt = cuda_ops.lib().b200_pick_bt(rpr)
-        while rpr % bt:
-            bt //= 2
+        bt = self._bt(rpr)
         out = torch.empty(T, N, dtype=out_dtype, device=xfull.device)
         rc = _lib().b200_gemm_gathered(xfull.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, xfull.stride(0),
                                        w.stride(0), int(out_dtype == torch.float32), bt, rpr, self.rank * (rpr // bt), self._own["flags"],

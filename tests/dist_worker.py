@@ -230,8 +230,8 @@ def mode_seq_parallel(rank, world, dev):
         w_n = (torch.randn(H, device=dev, generator=gc) * 0.1).to(torch.bfloat16)
         w_i = (torch.randn(N2, H, device=dev, generator=g) * 0.05).to(torch.bfloat16)       # column shard of in_proj
         for rep in range(3):
-            mine = sp.gemm_reduce_scatter(x, w_o, res[rank * rpr:(rank + 1) * rpr].contiguous())
-            full = sp.norm_allgather(mine, w_n, eps)
+            rows = sp.gemm_reduce_scatter(x, w_o)
+            mine, full = sp.reduce_norm_allgather(rows, res[rank * rpr:(rank + 1) * rpr].contiguous(), w_n, eps)
             y = sp.gemm_gathered(full, w_i)
             torch.cuda.synchronize()
             cuda_ops.check_errors(dev)
@@ -260,8 +260,8 @@ def mode_seq_parallel(rank, world, dev):
     res = torch.randn(rpr, H, device=dev).to(torch.bfloat16)
 
     def fused():
-        mine = sp.gemm_reduce_scatter(x, w_o, res)
-        return sp.gemm_gathered(sp.norm_allgather(mine, w_n, eps), w_i)
+        rows = sp.gemm_reduce_scatter(x, w_o)
+        return sp.gemm_gathered(sp.reduce_norm_allgather(rows, res, w_n, eps)[1], w_i)
 
     rs_out = torch.empty(rpr, H, device=dev, dtype=torch.bfloat16)
     ag_out = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
@@ -291,7 +291,26 @@ def mode_seq_parallel(rank, world, dev):
         t = torch.tensor([a.elapsed_time(b) / 10 * 1e3], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         names[name] = t.item()
+    # where the fused pipeline spends its time (events between the three kernels, summed over 10 iterations)
+    stage_lines = []
+    for cap in (64, 128, 256):
+        sp.bt_cap = cap
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(10)]
+        torch.cuda.synchronize(); dist.barrier()
+        for it in range(10):
+            ev[it][0].record()
+            rows = sp.gemm_reduce_scatter(x, w_o)
+            ev[it][1].record()
+            full = sp.reduce_norm_allgather(rows, res, w_n, eps)[1]
+            ev[it][2].record()
+            sp.gemm_gathered(full, w_i)
+            ev[it][3].record()
+        torch.cuda.synchronize()
+        parts = [sum(ev[it][i].elapsed_time(ev[it][i + 1]) for it in range(10)) * 100 for i in range(3)]
+        stage_lines.append(f"  token tile <= {cap}, rank 0: gemm+push {parts[0]:.1f} us, reduce+norm+gather {parts[1]:.1f} us, "
+                           f"gathered gemm {parts[2]:.1f} us")
     if rank == 0:
+        print("\n".join(stage_lines), flush=True)
         flops = 2 * T * H * Ks + 2 * T * N2 * H
         nv = (world - 1) / world * T * H * (4 + 2)
         print(f"seq_parallel world={world} T={T}: " + ", ".join(f"{k} {v:.1f} us" for k, v in names.items()) +

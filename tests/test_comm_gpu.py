@@ -123,8 +123,9 @@ def test_sequence_parallel_kernels_loopback():
         w_n = (torch.randn(H, device=dev, generator=g) * 0.1).to(torch.bfloat16)
         w_i = (torch.randn(384, H, device=dev, generator=g) * 0.05).to(torch.bfloat16)
         for _ in range(3):
-            mine = sp.gemm_reduce_scatter(x, w_o, res)
-            full = sp.norm_allgather(mine, w_n, 1e-6)
+            rows = sp.gemm_reduce_scatter(x, w_o)
+            mine, full = sp.reduce_norm_allgather(rows, res, w_n, 1e-6)
+            assert torch.equal(sp.norm_allgather(mine, w_n, 1e-6), full)
             y = sp.gemm_gathered(full, w_i)
             torch.cuda.synchronize()
             cuda_ops.check_errors(dev)
