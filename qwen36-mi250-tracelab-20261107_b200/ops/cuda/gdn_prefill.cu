@@ -388,17 +388,24 @@ int gdn_prefill_launch(const bf16* mixed, int ld, const bf16* conv_out, const Ch
 }
 }  // namespace
 
+extern "C" int b200_gdn_prefill_tc(const void* mixed, int ld, const void* conv_out, const void* chunks, int n_chunks,
+                                   const void* seg_chunks, int n_seg, const int* slots, float* rec_state,
+                                   const float* A_log, const float* dt_bias, void* work, void* o_tmp, int T, int HK,
+                                   int HV, int* err, cudaStream_t st);
+
 // Workspace floats needed per (chunk, head).
 extern "C" int b200_gdn_prefill_work_stride(int DK) { return 64 * (4 * DK + 64) + 64; }
 
 // mixed: [T, ld] in_proj output (qkv | z | b | a); conv_out: [T, C] scratch; chunks: ChunkInfo[n_chunks] in sequence
 // order; seg_chunks: int2[n_seg]; seq_of_row / seg_start: row -> sequence, sequence -> first row (n_seg + 1 entries);
-// work: fp32 [n_chunks * HV * stride]; o_tmp: bf16 [T, HV * DV]; out: bf16 [T, HV * DV].
+// work: fp32 [n_chunks * HV * stride]; o_tmp: bf16 [T, HV * DV]; out: bf16 [T, HV * DV]. use_tc: head dims of 128
+// take the tcgen05 kernels of gdn_prefill_tc.cu (other head dims always run the fp32 kernels).
 extern "C" int b200_gdn_prefill(const void* mixed, int ld, const int* seq_of_row, const int* seg_start, const int* slots,
                                 void* conv_state, float* rec_state, const void* conv_w, const float* A_log,
                                 const float* dt_bias, const void* gnorm_w, void* conv_out, const void* chunks,
                                 int n_chunks, const void* seg_chunks, int n_seg, float* work, void* o_tmp, void* out,
-                                int T, int HK, int HV, int DK, int DV, float eps, cudaStream_t st) {
+                                int T, int HK, int HV, int DK, int DV, float eps, int use_tc, int* err,
+                                cudaStream_t st) {
   if (T <= 0) return 0;
   if (DK != DV) return -7;
   const int C = 2 * HK * DK + HV * DV;
@@ -412,6 +419,17 @@ extern "C" int b200_gdn_prefill(const void* mixed, int ld, const int* seq_of_row
                                  static_cast<const ChunkInfo*>(chunks), n_chunks, static_cast<const int2*>(seg_chunks), \
                                  n_seg, slots, rec_state, A_log, dt_bias, static_cast<const bf16*>(gnorm_w), work,   \
                                  static_cast<bf16*>(o_tmp), static_cast<bf16*>(out), T, HK, HV, eps, st)
+  if (DK == 128 && use_tc) {
+    // tensor-core WY transform and state pass (gdn_prefill_tc.cu), then the same gated norm
+    const int rc = b200_gdn_prefill_tc(mixed, ld, conv_out, chunks, n_chunks, seg_chunks, n_seg, slots, rec_state, A_log,
+                                       dt_bias, work, o_tmp, T, HK, HV, err, st);
+    if (rc) return rc;
+    const int warps = T * HV;
+    gdn_gated_norm_kernel<128><<<(warps + 7) / 8, 256, 0, st>>>(static_cast<const bf16*>(o_tmp), static_cast<const bf16*>(mixed),
+                                                                ld, C, static_cast<const bf16*>(gnorm_w),
+                                                                static_cast<bf16*>(out), T, HV, eps);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
   if (DK == 128) GP(128);
   if (DK == 64) GP(64);
   if (DK == 32) GP(32);

@@ -62,7 +62,7 @@ class _Sig:
     b200_gdn_decode = [P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P]
     b200_attn_prep = [P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P, P]
     b200_paged_attn = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
-    b200_gdn_prefill = [P, I, P, P, P, P, P, P, P, P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, F, P]
+    b200_gdn_prefill = [P, I, P, P, P, P, P, P, P, P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, F, I, P, P]
     b200_gdn_prefill_work_stride = [I]
     b200_flash_prefill = [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, P, P, P]
     b200_attn_combine = [P, P, P, P, I, I, I, I, P]
@@ -108,6 +108,9 @@ DECODE_MODE = False  # set by Model.forward: True for decode / verify passes
 # batch 128: 18.1 -> 19.3 ms, the leader CTA's DSMEM reads of seven partial tiles cost more than the extra
 # CTAs save), so it is off unless ENGINE_SPLIT_K=1; the split factor must not depend on the batch size.
 SPLIT_K_ENABLED = __import__("os").environ.get("ENGINE_SPLIT_K", "0") == "1"
+# Gated DeltaNet prefill with head dims of 128: tcgen05 WY transform and state pass (ENGINE_GDN_TC=0 selects the fp32
+# CUDA-core kernels, which other head dims always use)
+GDN_PREFILL_TC = __import__("os").environ.get("ENGINE_GDN_TC", "1") == "1"
 
 
 def split_k(N: int, K: int, grouped: bool = False) -> int:
@@ -313,7 +316,8 @@ def gdn_prefill(mixed, seg_starts, seg_slots, conv_state, rec_state, conv_w, A_l
     rc = lib().b200_gdn_prefill(
         _ptr(mixed), mixed.stride(0), _ptr(sor_t), _ptr(start_t), _ptr(slots_t), _ptr(conv_state), _ptr(rec_state),
         _ptr(conv_w), _ptr(A_log), _ptr(dt_bias), _ptr(gnorm_w), _ptr(conv_out), _ptr(chunks_t), len(chunks),
-        _ptr(segc_t), nseg, _ptr(work), _ptr(o_tmp), _ptr(out), T, n_k, n_v, dk, dv, eps, _stream(),
+        _ptr(segc_t), nseg, _ptr(work), _ptr(o_tmp), _ptr(out), T, n_k, n_v, dk, dv, eps, int(GDN_PREFILL_TC),
+        _ptr(err_word(dev)), _stream(),
     )
     _check(rc, "gdn_prefill")
     return out
