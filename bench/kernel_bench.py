@@ -174,6 +174,24 @@ def case_moe_prefill(small):
     report(f"moe_prefill_T{T}", us, (wgu.numel() + wd.numel()) * 2, 2 * T * 9 * 3 * H * I, experts=E)
 
 
+def case_gdn_prefill(small):
+    """Gated DeltaNet chunked prefill of one layer: 8 sequences x 1024 tokens, 32 value heads of 128 x 128
+    (conv + WY transform + state pass + gated norm; tensor-core path unless ENGINE_GDN_TC=0)."""
+    nseg, L = (2, 512) if small else (8, 1024)
+    n_k, n_v, dk, dv = 16, 32, 128, 128
+    Cd = 2 * n_k * dk + n_v * dv
+    T = nseg * L
+    mixed = bf(T, Cd + n_v * dv + 2 * n_v)
+    conv, rec = bf(nseg + 1, Cd, 3), torch.randn(nseg + 1, n_v, dk, dv, device="cuda") * 0.1
+    args = (bf(Cd, 4, scale=0.3), torch.rand(n_v, device="cuda"), torch.randn(n_v, device="cuda"), bf(dv), n_k, n_v, dk, dv, 1e-6)
+    starts = [i * L for i in range(nseg + 1)]
+    slots = list(range(1, nseg + 1))
+    us = timed(lambda: C.gdn_prefill(mixed, starts, slots, conv, rec, *args), iters=5)
+    # per (chunk, head): K K^T, Q K^T, T k, T v (64x64x128 each, 2 flops/mac), S w, S q, scores v, k^T v
+    flops = (T // 64) * n_v * 2 * (4 * 64 * 64 * 128 + 2 * 64 * 128 * 128 + 64 * 64 * 128 + 128 * 64 * 128)
+    report(f"gdn_prefill_{nseg}x{L}", us, mixed.numel() * 2 + T * n_v * dv * 2, flops, tensor_cores=C.GDN_PREFILL_TC)
+
+
 CASES = {k[5:]: v for k, v in globals().items() if k.startswith("case_")}
 
 if __name__ == "__main__":

@@ -31,28 +31,63 @@ struct ChunkInfo {  // one per (sequence chunk)
 
 // ------------------------------------------------------------------ conv
 // x: [T, ld] (conv input at columns [0, C)); seg_start[seg] = first row of the span; out: [T, C] bf16.
-__global__ void gdn_conv_prefill_kernel(const bf16* x, int ld, const int* seq_of_row, const int* seg_start,
-                                        const int* slots, const bf16* conv_state, const bf16* conv_w, bf16* out, int T,
-                                        int C) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+// A thread owns 8 consecutive channels (16-byte loads) over 32 rows and slides a 3-row window down them, so each
+// input element is read once; the window is rebuilt from the slot's conv state wherever a span starts.
+__global__ void __launch_bounds__(128)
+gdn_conv_prefill_kernel(const bf16* x, int ld, const int* seq_of_row, const int* seg_start, const int* slots,
+                        const bf16* conv_state, const bf16* conv_w, bf16* out, int T, int C) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   const int r0 = blockIdx.y * 32;
   if (c >= C) return;
-  float w[4];
+  float w[8][4];
+  {
+    uint4 wv[4];
 #pragma unroll
-  for (int k = 0; k < 4; ++k) w[k] = __bfloat162float(conv_w[c * 4 + k]);
-  for (int r = r0; r < min(T, r0 + 32); ++r) {
+    for (int i = 0; i < 4; ++i) wv[i] = reinterpret_cast<const uint4*>(conv_w + static_cast<size_t>(c) * 4)[i];
+    const bf16* we = reinterpret_cast<const bf16*>(wv);
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) w[ch][k] = __bfloat162float(we[ch * 4 + k]);
+  }
+  float win[3][8];  // inputs of rows r-3, r-2, r-1
+  const int r1 = min(T, r0 + 32);
+  for (int r = r0; r < r1; ++r) {
     const int seg = seq_of_row[r];
     const int s0 = seg_start[seg];
-    const bf16* st = conv_state + (static_cast<size_t>(slots[seg]) * C + c) * 3;
-    float acc = 0.f;
+    if (r == r0 || r == s0) {
+      uint4 sv[3];
+      const uint4* sp = reinterpret_cast<const uint4*>(conv_state + (static_cast<size_t>(slots[seg]) * C + c) * 3);
+      if (r - 3 < s0) { sv[0] = sp[0]; sv[1] = sp[1]; sv[2] = sp[2]; }
+      const bf16* se = reinterpret_cast<const bf16*>(sv);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int rr = r - 3 + k;  // input row of tap k
-      const float v = rr >= s0 ? __bfloat162float(x[static_cast<size_t>(rr) * ld + c])
-                               : __bfloat162float(st[3 - (s0 - rr)]);  // s0 - rr in 1..3 -> state[2], [1], [0]
-      acc += w[k] * v;
+      for (int back = 3; back >= 1; --back) {
+        const int rr = r - back;
+        if (rr >= s0) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(rr) * ld + c);
+          const bf16* xe = reinterpret_cast<const bf16*>(&xv);
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) win[3 - back][ch] = __bfloat162float(xe[ch]);
+        } else {
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) win[3 - back][ch] = __bfloat162float(se[ch * 3 + 3 - (s0 - rr)]);  // s0 - rr in 1..3
+        }
+      }
     }
-    out[static_cast<size_t>(r) * C + c] = __float2bfloat16(silu_f(acc));
+    const uint4 xv = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * ld + c);
+    const bf16* xe = reinterpret_cast<const bf16*>(&xv);
+    uint4 ov;
+    bf16* oe = reinterpret_cast<bf16*>(&ov);
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+      const float cur = __bfloat162float(xe[ch]);
+      const float acc = w[ch][0] * win[0][ch] + w[ch][1] * win[1][ch] + w[ch][2] * win[2][ch] + w[ch][3] * cur;
+      oe[ch] = __float2bfloat16(silu_f(acc));
+      win[0][ch] = win[1][ch];
+      win[1][ch] = win[2][ch];
+      win[2][ch] = cur;
+    }
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * C + c) = ov;
   }
 }
 
@@ -409,7 +444,8 @@ extern "C" int b200_gdn_prefill(const void* mixed, int ld, const int* seq_of_row
   if (T <= 0) return 0;
   if (DK != DV) return -7;
   const int C = 2 * HK * DK + HV * DV;
-  gdn_conv_prefill_kernel<<<dim3((C + 127) / 128, (T + 31) / 32), 128, 0, st>>>(
+  if (C % 8 || ld % 8) return -7;
+  gdn_conv_prefill_kernel<<<dim3((C / 8 + 127) / 128, (T + 31) / 32), 128, 0, st>>>(
       static_cast<const bf16*>(mixed), ld, seq_of_row, seg_start, slots, static_cast<const bf16*>(conv_state),
       static_cast<const bf16*>(conv_w), static_cast<bf16*>(conv_out), T, C);
   gdn_conv_state_update_kernel<<<dim3((C + 127) / 128, n_seg), 128, 0, st>>>(

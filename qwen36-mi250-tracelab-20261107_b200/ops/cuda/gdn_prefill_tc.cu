@@ -6,8 +6,8 @@
 //                TMA brings the raw q / k / v rows of both chunks into 128B-swizzled tiles. tcgen05.mma forms the
 //                128 x 128 Gram matrices K K^T and Q K^T (only the two 64 x 64 diagonal blocks are used), threads
 //                turn them into A = (k beta) k^T decay (strictly lower) and the causal scores, each thread then
-//                solves its own column of T = (I + A)^-1 by forward substitution in registers, and a second pair
-//                of MMAs with the block-diagonal T forms w = T (k beta e^g) and u = T (v beta). Everything the state
+//                solves its own column of T = (I + A)^-1 by forward substitution, and a second pair of MMAs with
+//                the block-diagonal T diag(beta) forms w = T (k beta e^g) and u = T (v beta). Everything the state
 //                pass needs is written as bf16: w, u, q e^g, k e^{g_last - g}, scores, and g_last in fp32
 //                (reference: engine/fast/gdn_chunk.py:203-471).
 //  gdn_scan_tc : one CTA per (sequence, value head), chunks in order. The transposed fp32 state S^T [dv, dk] lives
@@ -56,8 +56,8 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;            // raw q, later the fp32 A blocks, later the bf16 block-diagonal T
-  uint8_t* sK = smem + 32768;    // raw k, later k beta e^g
-  uint8_t* sV = smem + 65536;    // raw v, later v beta
+  uint8_t* sK = smem + 32768;    // raw k, later k e^g / |k|
+  uint8_t* sV = smem + 65536;    // the substitution's private columns (fp32), later raw v
   float* sG = reinterpret_cast<float*>(smem + 98304);  // [128] cumulative log decay
   float* sRk = sG + 128;                               // [128] 1 / |k|
   float* sTot = sRk + 128;                             // [4] warp totals of the scan
@@ -92,14 +92,13 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
 
   if (i == 0) {
     // rows of both chunks (a missing second chunk re-reads the first: finite data, never written out)
-    mbar_expect_tx(tma_bar, 3 * 32768);
+    mbar_expect_tx(tma_bar, 2 * 32768);  // v arrives later: its region is scratch for the substitution first
     for (int cc = 0; cc < 2; ++cc) {
       const int idx = 2 * blockIdx.x + cc;
       const int row0 = p.chunks[idx < p.n_chunks ? idx : 2 * blockIdx.x].row0;
       for (int a = 0; a < 2; ++a) {
         tma_load_2d(sQ + a * 16384 + cc * 8192, &tmConv, tma_bar, hk * 128 + a * 64, row0);
         tma_load_2d(sK + a * 16384 + cc * 8192, &tmConv, tma_bar, key_dim + hk * 128 + a * 64, row0);
-        tma_load_2d(sV + a * 16384 + cc * 8192, &tmConv, tma_bar, 2 * key_dim + h * 128 + a * 64, row0);
       }
     }
   }
@@ -220,62 +219,59 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
       reinterpret_cast<uint4*>(regB + r * 64 + j0)[1] = so[1];
     }
   }
-  // k <- k beta e^g / |k| and v <- v beta, in place (the first pair of MMAs has finished reading them)
+  // k <- k e^g / |k| in place (the first pair of MMAs has finished reading it); beta is folded into T below
   {
-    const float fk = rk * beta * __expf(gs);
+    const float fk = rk * __expf(gs);
 #pragma unroll
     for (int a = 0; a < 2; ++a)
 #pragma unroll
       for (int c16 = 0; c16 < 8; ++c16) {
         uint4* kp = reinterpret_cast<uint4*>(sK + a * 16384 + swz(tile_row, c16));
-        uint4* vp = reinterpret_cast<uint4*>(sV + a * 16384 + swz(tile_row, c16));
-        uint4 kv = *kp, vv = *vp;
+        uint4 kv = *kp;
         bf16* ke = reinterpret_cast<bf16*>(&kv);
-        bf16* ve = reinterpret_cast<bf16*>(&vv);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          ke[j] = __float2bfloat16(__bfloat162float(ke[j]) * fk);
-          ve[j] = __float2bfloat16(__bfloat162float(ve[j]) * beta);
-        }
+        for (int j = 0; j < 8; ++j) ke[j] = __float2bfloat16(__bfloat162float(ke[j]) * fk);
         *kp = kv;
-        *vp = vv;
       }
   }
   __syncthreads();
-  // T = (I + A)^-1: thread (c, r) solves column r of its chunk's T in registers; the column is private to it, and
-  // the reads of A are the same address across the warp (broadcast), so no barrier is needed inside
-  float tc[64];
-#pragma unroll
-  for (int ii = 0; ii < 64; ++ii) tc[ii] = 0.f;
-#pragma unroll
-  for (int ii = 1; ii < 64; ++ii) {
-    float acc = 0.f;
-#pragma unroll
-    for (int j4 = 0; j4 < (ii + 3) / 4; ++j4) {
-      const float4 a4 = *reinterpret_cast<const float4*>(sA + ii * 64 + (((j4 + ii) & 15) << 2));
-      const float av[4] = {a4.x, a4.y, a4.z, a4.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int j = 4 * j4 + e;
-        if (j < ii) {
-          // column r of T: T[j][r] = 1 at j == r, 0 above, tc[j] below
-          const float t = j == r ? 1.f : (j > r ? tc[j] : 0.f);
-          acc += av[e] * t;
-        }
-      }
+  // T = (I + A)^-1: thread (c, r) solves column r of its chunk's T by forward substitution. The column is private
+  // to the thread (sC[j * 128 + i], the v region, free until v is loaded), the reads of A are the same address
+  // across the warp (broadcast), so the loop needs no barrier; it stays rolled to keep the code small.
+  // Column entry j of thread i lives at sC[(j >> 2) * 512 + i * 4 + (j & 3)]: four consecutive entries are one
+  // 16-byte load, and a warp's loads are contiguous.
+  float* sC = reinterpret_cast<float*>(sV);
+#pragma unroll 4
+  for (int j4 = 0; j4 < 16; ++j4)
+    *reinterpret_cast<float4*>(sC + j4 * 512 + i * 4) =
+        make_float4(4 * j4 == r ? 1.f : 0.f, 4 * j4 + 1 == r ? 1.f : 0.f, 4 * j4 + 2 == r ? 1.f : 0.f, 4 * j4 + 3 == r ? 1.f : 0.f);
+  // the odd warp of a chunk owns columns 32..63: their entries above row 32 are zero, so it starts further down
+  const int j4_lo = (warp & 1) ? 8 : 0;
+#pragma unroll 1
+  for (int ii = (warp & 1) ? 33 : 1; ii < 64; ++ii) {
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    const int ng = (ii + 3) >> 2;  // entries at or right of the diagonal are zero in A
+    const float* arow = sA + ii * 64;
+#pragma unroll 4
+    for (int j4 = j4_lo; j4 < ng; ++j4) {
+      const float4 a4 = *reinterpret_cast<const float4*>(arow + (((j4 + ii) & 15) << 2));
+      const float4 c4 = *reinterpret_cast<const float4*>(sC + j4 * 512 + i * 4);
+      a0 += a4.x * c4.x;
+      a1 += a4.y * c4.y;
+      a2 += a4.z * c4.z;
+      a3 += a4.w * c4.w;
     }
-    tc[ii] = ii > r ? -acc : 0.f;
+    if (ii > r) sC[(ii >> 2) * 512 + i * 4 + (ii & 3)] = -((a0 + a1) + (a2 + a3));
   }
-  __syncthreads();  // every thread has finished reading A: the region becomes the bf16 T tile
-  // block-diagonal T as a K-major A operand: row (c * 64 + ii), K index (c * 64 + r) -> atom c; the other atom's
-  // rows of this chunk are zero
+  __syncthreads();  // every thread has finished reading A: the region becomes the bf16 operand tile
+  // T diag(beta), block-diagonal, as a K-major A operand: row (c * 64 + ii), K index (c * 64 + r) -> atom c; the
+  // other atom's rows of this chunk are zero. w = (T diag(beta)) (k e^g), u = (T diag(beta)) v.
   {
     uint8_t* tile = sQ + c * 16384;
-#pragma unroll
-    for (int ii = 0; ii < 64; ++ii) {
-      const float t = ii == r ? 1.f : tc[ii];
-      *reinterpret_cast<bf16*>(tile + swz(c * 64 + ii, r >> 3) + (r & 7) * 2) = __float2bfloat16(t);
-    }
+#pragma unroll 8
+    for (int ii = 0; ii < 64; ++ii)
+      *reinterpret_cast<bf16*>(tile + swz(c * 64 + ii, r >> 3) + (r & 7) * 2) =
+          __float2bfloat16(sC[(ii >> 2) * 512 + i * 4 + (ii & 3)] * beta);
     uint8_t* other = sQ + (1 - c) * 16384;
 #pragma unroll
     for (int c16 = 0; c16 < 8; ++c16) *reinterpret_cast<uint4*>(other + swz(tile_row, c16)) = make_uint4(0, 0, 0, 0);
@@ -285,6 +281,14 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
   __syncthreads();
   if (i == 0 && ok) {
     tc_fence_after();
+    // the v rows of both chunks replace the scratch columns while the first MMA runs
+    mbar_expect_tx(tma_bar, 32768);
+    for (int cc = 0; cc < 2; ++cc) {
+      const int idx = 2 * blockIdx.x + cc;
+      const int row0 = p.chunks[idx < p.n_chunks ? idx : 2 * blockIdx.x].row0;
+      for (int a = 0; a < 2; ++a)
+        tma_load_2d(sV + a * 16384 + cc * 8192, &tmConv, tma_bar, 2 * key_dim + h * 128 + a * 64, row0);
+    }
     constexpr uint32_t idesc = umma_idesc_bf16(128, 128) | (1u << 16);  // B operand MN-major: [token][feature]
     const uint32_t ta = smem_u32(sQ), ka = smem_u32(sK), va = smem_u32(sV);
 #pragma unroll
@@ -292,10 +296,14 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
       const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
       umma_bf16(tmem, umma_smem_desc(ta + aoff), umma_smem_desc_mn(ka + kk * 2048, 16384), idesc, kk != 0);        // w
     }
+    if (!mbar_wait(tma_bar, 1, p.err, ERR_WAIT_FULL, abort_flag)) ok = false;
+    tc_fence_after();
+    if (ok) {
 #pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {
-      const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
-      umma_bf16(tmem + 128, umma_smem_desc(ta + aoff), umma_smem_desc_mn(va + kk * 2048, 16384), idesc, kk != 0);  // u
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
+        umma_bf16(tmem + 128, umma_smem_desc(ta + aoff), umma_smem_desc_mn(va + kk * 2048, 16384), idesc, kk != 0);  // u
+      }
     }
     umma_commit(mma_bar);
   }

@@ -51,6 +51,7 @@ struct GemmParams {
   bf16* pair_out[MAX_RANKS];  // EPI_SCATTER: every rank's pair-output buffer [pairs, ldo] as mapped here
   int y_rot;         // dense sequence-parallel GEMMs: token tile = (blockIdx.y + y_rot) % gridDim.y, so that each rank
                      // starts with the tiles whose data (or whose consumer) is furthest from being the bottleneck
+  int grid_y;        // dense: number of token tiles (set by the launcher)
 };
 
 template <int BT, int EPI>
@@ -65,7 +66,11 @@ struct Cfg {
   static constexpr int BUDGET = BT <= 64 ? 108 * 1024 : 200 * 1024;
   static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int TMEM_COLS_RAW = A_TILES * BT;
+  static constexpr int ACC_COLS = A_TILES * BT;  // one accumulator stage
+  // two accumulator stages whenever they fit (512 columns per SM shared by the resident CTAs): the epilogue of
+  // one tile then overlaps the main loop of the CTA's next tile
+  static constexpr int ACC_STAGES = (2 * ACC_COLS * CTAS_PER_SM <= 512) ? 2 : 1;
+  static constexpr int TMEM_COLS_RAW = ACC_COLS * ACC_STAGES;
   static constexpr int TMEM_COLS = TMEM_COLS_RAW <= 32 ? 32 : TMEM_COLS_RAW <= 64 ? 64 : TMEM_COLS_RAW <= 128 ? 128 : TMEM_COLS_RAW <= 256 ? 256 : 512;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
@@ -79,24 +84,23 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + C::STAGES;
-  uint64_t* acc_full = bars + 2 * C::STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 1);
+  uint64_t* acc_full = bars + 2 * C::STAGES;   // [2]
+  uint64_t* acc_empty = bars + 2 * C::STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   __shared__ float red_max[4][BT > 0 ? BT : 1];
   __shared__ int red_idx[4][BT > 0 ? BT : 1];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BM;
-  const int by = (!GROUPED && p.y_rot) ? static_cast<int>((blockIdx.y + p.y_rot) % gridDim.y) : static_cast<int>(blockIdx.y);
-  int expert = 0, row0 = by * BT, nrows = BT;
-  if (GROUPED) {
-    const int nt = *p.n_tiles;
-    if (static_cast<int>(blockIdx.y) >= nt) return;  // whole CTA leaves before any barrier or TMEM use
-    const int4 t = p.tiles[blockIdx.y];
-    expert = t.x; row0 = t.y; nrows = t.z;
-  } else {
-    nrows = min(BT, p.T - row0);
-  }
+  // Persistent tile loop: CTA b takes output tiles b, b + gridDim.x, ... (weight tile fastest, so CTAs that run
+  // together share the activation tile). A split-K cluster takes the single tile its grid position names.
+  const int tiles_n = (p.N + BM - 1) / BM;
+  const int tiles_y = GROUPED ? *p.n_tiles : p.grid_y;
+  const int total = tiles_n * tiles_y;
+  const int tile0 = SPLIT ? static_cast<int>(blockIdx.y) * tiles_n + static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
+  const int tstep = SPLIT ? (1 << 30) : static_cast<int>(gridDim.x);
+  constexpr int ACC = SPLIT ? 1 : C::ACC_STAGES;
+  if (SPLIT && tile0 >= total) return;  // the whole cluster leaves together, before any barrier or TMEM use
   const int num_k_all = (p.K + BK - 1) / BK;
   // split-K: the cluster's CTAs (blockIdx.z = rank in the cluster) take consecutive runs of k-blocks; their fp32
   // partial tiles meet in the leader through distributed shared memory, added in rank order
@@ -106,7 +110,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    mbar_init(acc_full, 1);
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmW);
@@ -116,17 +120,37 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_base = *tmem_slot;
+
+  // geometry of output tile `tile`
+  auto tile_geom = [&](int tile, int& n0, int& by, int& expert, int& row0, int& nrows) {
+    const int nx = tile % tiles_n, byr = tile / tiles_n;
+    n0 = nx * BM;
+    by = (!GROUPED && p.y_rot) ? (byr + p.y_rot) % tiles_y : byr;
+    expert = 0;
+    if (GROUPED) {
+      const int4 t = p.tiles[by];
+      expert = t.x; row0 = t.y; nrows = t.z;
+    } else {
+      row0 = by * BT;
+      nrows = min(BT, p.T - row0);
+    }
+  };
 
   if (warp == 0) {
     if (elect_one()) {
+      int it = 0;  // k-blocks issued so far, over all tiles of this CTA
+      bool live = true;
+      for (int tile = tile0; tile < total && live; tile += tstep) {
+      int n0, by, expert, row0, nrows;
+      tile_geom(tile, n0, by, expert, row0, nrows);
       // all-gather -> GEMM: the activation rows of this tile were pushed here by their owner rank; wait for that
       // shard only, so tiles of shards that have already arrived run while the others are still in flight
       if (p.x_flags != nullptr && !wait_flag(p.x_flags + row0 / p.rows_per_rank, *p.x_epoch, p.err)) *abort_flag = 1;
-      for (int kb = 0; kb < num_k; ++kb) {
-        const int s = kb % C::STAGES;
-        const uint32_t ph = (kb / C::STAGES) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1, p.err, ERR_WAIT_EMPTY, abort_flag)) break;
+      for (int kb = 0; kb < num_k; ++kb, ++it) {
+        const int s = it % C::STAGES;
+        const uint32_t ph = (it / C::STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, p.err, ERR_WAIT_EMPTY, abort_flag)) { live = false; break; }
         uint8_t* st = smem + s * C::STAGE_BYTES;
         mbar_expect_tx(&full[s], C::STAGE_BYTES);
         if (GROUPED) {
@@ -138,15 +162,23 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
         tma_load_2d(st + C::A_TILES * C::A_BYTES, &tmX, &full[s], (kb0 + kb) * BK, row0);
       }
+      }
     }
     if (SPLIT) { __syncwarp(); cluster_sync(); }
   } else if (warp == 1) {
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BT);
       bool ok = true;
-      for (int kb = 0; kb < num_k && ok; ++kb) {
-        const int s = kb % C::STAGES;
-        const uint32_t ph = (kb / C::STAGES) & 1;
+      int it = 0, lt = 0;  // k-blocks and tiles consumed so far
+      for (int tile = tile0; tile < total && ok; tile += tstep, ++lt) {
+      const int acc = lt % ACC;
+      const uint32_t tmem = tmem_base + acc * C::ACC_COLS;
+      // the epilogue must have drained this accumulator stage (two tiles ago) before it is overwritten
+      ok = mbar_wait(&acc_empty[acc], ((lt / ACC) & 1) ^ 1, p.err, ERR_WAIT_TMEM, abort_flag);
+      if (ok) tc_fence_after();
+      for (int kb = 0; kb < num_k && ok; ++kb, ++it) {
+        const int s = it % C::STAGES;
+        const uint32_t ph = (it / C::STAGES) & 1;
         ok = mbar_wait(&full[s], ph, p.err, ERR_WAIT_FULL, abort_flag);
         if (!ok) break;
         tc_fence_after();
@@ -162,13 +194,22 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
         umma_commit(&empty[s]);  // stage reusable once these MMAs have read it
       }
-      umma_commit(acc_full);     // always arrive so that the epilogue is released
+      umma_commit(&acc_full[acc]);  // always arrive so that the epilogue is released
+      }
     }
     if (SPLIT) { __syncwarp(); cluster_sync(); }
   } else {
     // ---------------- epilogue: warp q owns TMEM lanes [32q, 32q+32)
     const int q = warp & 3;
-    const bool ok = mbar_wait(acc_full, 0, p.err, ERR_WAIT_TMEM, abort_flag) && !*abort_flag;
+    int lt = 0;
+    for (int tile = tile0; tile < total; tile += tstep, ++lt) {
+    int n0, by, expert, row0, nrows;
+    tile_geom(tile, n0, by, expert, row0, nrows);
+    (void)expert;
+    const int nx = n0 / BM;
+    const int acc = lt % ACC;
+    const uint32_t tmem = tmem_base + acc * C::ACC_COLS;
+    const bool ok = mbar_wait(&acc_full[acc], (lt / ACC) & 1, p.err, ERR_WAIT_TMEM, abort_flag) && !*abort_flag;
     tc_fence_after();
     const int n = n0 + q * 32 + lane;
     const bool n_ok = n < p.N;
@@ -177,7 +218,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       // rank's receive slot over NVLink; when all R partials of the tile have arrived they are added in
       // rank order (+ residual) and stored as bf16. No partial ever touches this rank's output buffer.
       const CommCtx& cc = p.comm;
-      const int blk = blockIdx.y * gridDim.x + blockIdx.x;
+      const int blk = by * tiles_n + nx;
       __shared__ uint32_t s_epoch;
       __shared__ int s_peer_ok;
       const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
@@ -221,7 +262,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       // owner) and releases the tile's arrival flag there. Nothing waits here: the owner adds the R partials in
       // rank order inside the following norm kernel (allreduce.cu, reduce_norm_allgather_kernel), at full occupancy.
       const CommCtx& cc = p.comm;
-      const int blk = by * gridDim.x + blockIdx.x;
+      const int blk = by * tiles_n + nx;
       const int owner = row0 / p.rows_per_rank;
       const int lrow0 = row0 - owner * p.rows_per_rank;
       __shared__ uint32_t s_epoch_rs;
@@ -349,16 +390,23 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             const float om = red_max[w][c]; const int oi = red_idx[w][c];
             if (om > m || (om == m && oi < idx)) { m = om; idx = oi; }
           }
-          const size_t o = static_cast<size_t>(blockIdx.x) * p.T + row0 + c;
+          const size_t o = static_cast<size_t>(nx) * p.T + row0 + c;
           p.part_max[o] = m; p.part_idx[o] = idx;
         }
       }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // red_max / red_idx are reused by the next tile
+    }
+    // this accumulator stage may be overwritten: every tcgen05.ld of the warp has completed (wait::ld)
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    if (!ok) break;
     }
   }
   if (SPLIT) cluster_sync();  // second cluster barrier: the leader has read every partial tile
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, C::TMEM_COLS); }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, C::TMEM_COLS); }
 }
 
 // Reduce the LM-head partials of each row over the vocabulary tiles, first maximum wins.
@@ -438,7 +486,9 @@ static int launch_split(const CUtensorMap& tw, const CUtensorMap& tx, const Gemm
   attr[0].val.clusterDim.z = p.splits;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, tw, tx, p) == cudaSuccess ? 0 : -4;
+  GemmParams q = p;
+  q.grid_y = grid_y;
+  return cudaLaunchKernelEx(&cfg, kern, tw, tx, q) == cudaSuccess ? 0 : -4;
 }
 
 template <int BT, int EPI, bool GROUPED>
@@ -453,8 +503,16 @@ static int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess) return -3;
     configured = true;
   }
-  dim3 grid((p.N + BM - 1) / BM, grid_y);
-  kern<<<grid, 192, C::SMEM, st>>>(tw, tx, p);
+  static int resident = 0;  // CTAs the device holds at once: the persistent grid is never larger
+  if (!resident) {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -3;
+    resident = sms * C::CTAS_PER_SM;
+  }
+  GemmParams q = p;
+  q.grid_y = grid_y;
+  const long long tiles = static_cast<long long>((p.N + BM - 1) / BM) * grid_y;
+  kern<<<static_cast<unsigned>(tiles < resident ? tiles : resident), 192, C::SMEM, st>>>(tw, tx, q);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

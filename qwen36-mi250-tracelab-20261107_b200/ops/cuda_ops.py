@@ -284,7 +284,7 @@ def gdn_decode(mixed, slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnor
 def gdn_prefill(mixed, seg_starts, seg_slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnorm_w, n_k, n_v, dk,
                 dv, eps) -> torch.Tensor:
     """Chunked prefill of the gated delta rule over packed spans (conv, WY transform, state scan, gated norm)."""
-    if dk != dv or dk not in (32, 64, 128) or conv_w.shape[1] != 4:
+    if dk != dv or dk not in (32, 64, 128) or conv_w.shape[1] != 4 or mixed.stride(0) % 8 or (n_k * dk) % 4:
         return torch_ops.gdn_prefill_batched(
             mixed, seg_starts, seg_slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnorm_w, n_k, n_v, dk, dv, eps
         )
