@@ -11,6 +11,14 @@ every token's arrival time is recorded on the client. Definitions (same as the r
 time) / (n - 1); output tok/s = all output tokens / wall time of the run. A session's round r+1 prompt is
 round r's prompt + its output ids + new random tokens, so the server's session-tail cache is exercised;
 ``cached_tokens`` from the usage chunk is summed.
+
+    python bench/serve_bench.py ... --trace bench/sample_trace.csv --concurrency 8    # recorded-trace replay
+
+``--trace`` replays a CSV of ``session_id,round_idx,input_len,output_len,prefix_len,tool_wait_after_ms`` rows
+(the column layout of the reference's recorded sample, ``.vibesys/shared/tracelab/recorded_sessions.csv``):
+round r of a session sends the first ``prefix_len`` tokens of what the session has seen so far (its previous
+prompt plus the ids the server generated) followed by ``input_len`` new random tokens, asks for exactly
+``output_len`` tokens, then sleeps ``tool_wait_after_ms``. ``--concurrency`` is the number of session slots.
 """
 
 from __future__ import annotations
@@ -74,6 +82,7 @@ def main() -> None:
     ap.add_argument("--max-first-len", type=int, default=65536)
     ap.add_argument("--grow", default="100-2000")
     ap.add_argument("--rate", type=float, default=0.0, help="Poisson arrivals per second (0 = all at once)")
+    ap.add_argument("--trace", default="", help="CSV of recorded sessions to replay")
     ap.add_argument("--seed", type=int, default=0)
     a = ap.parse_args()
     rng = random.Random(a.seed)
@@ -93,9 +102,33 @@ def main() -> None:
                 results.append(res)
             prompt = prompt + res["ids"] + [srng.randint(lo_v, hi_v) for _ in range(srng.randint(*grow))]
 
+    def run_trace(rows: list[dict], srng: random.Random) -> None:
+        seen: list[int] = []
+        with gate:  # a session holds its slot through tool waits, as the recorded runner does
+            for row in rows:
+                keep = min(int(row["prefix_len"]), len(seen))
+                pad = int(row["prefix_len"]) - keep
+                prompt = seen[:keep] + [srng.randint(lo_v, hi_v) for _ in range(pad + int(row["input_len"]))]
+                res = stream_once(a.url, a.model, prompt, int(row["output_len"]))
+                res["round"] = int(row["round_idx"])
+                with lock:
+                    results.append(res)
+                seen = prompt + res["ids"]
+                time.sleep(int(row.get("tool_wait_after_ms") or 0) / 1e3)
+
     threads = []
     t_arrive = 0.0
-    if a.sessions:
+    if a.trace:
+        import csv
+
+        by_session: dict[str, list[dict]] = {}
+        with open(a.trace, newline="") as f:
+            for row in csv.DictReader(f):
+                by_session.setdefault(row["session_id"], []).append(row)
+        for rows in by_session.values():
+            rows.sort(key=lambda r: int(r["round_idx"]))
+            threads.append(threading.Thread(target=run_trace, args=(rows, random.Random(rng.random()))))
+    elif a.sessions:
         r_lo, r_hi = _range(a.rounds)
         for _ in range(a.sessions):
             n = int(min(a.max_first_len, max(16, rng.lognormvariate(0, 0.8) * a.first_len)))

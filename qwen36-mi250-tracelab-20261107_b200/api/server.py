@@ -21,7 +21,7 @@ from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 from typing import Any, Iterator
 
 from ..config import EngineConfig
-from ..obs import looptimers, reqstamps
+from ..obs import buildlog, looptimers, reqstamps
 from ..sched.request import EngineError, Generation, TokenEvent
 from . import protocol
 from .protocol import ChatRequest, CompletionRequest, Envelope, RequestError, Usage
@@ -210,6 +210,8 @@ class Service:
             body["loop_timers"] = looptimers.summary()
         if reqstamps.ENABLED:
             body["request_stamps"] = reqstamps.summary()
+        body["native_loads"] = len(buildlog.events())
+        body["native_loads_while_serving"] = len(buildlog.events(serving_only=True))
         return body
 
 
@@ -403,6 +405,7 @@ def main(argv: list[str] | None = None) -> None:
         return
     service = load_service(args)
     server = Server((args.host, args.port), service)
+    buildlog.mark_serving()  # any native load from here on is a stall a request can see
     print(f"engine: serving {service.model_name} on http://{args.host}:{args.port}", flush=True)
     try:
         server.serve_forever()

@@ -12,11 +12,13 @@ current stream, ``engine/fast/hipmega_rtc.py:150-215``).
 from __future__ import annotations
 
 import ctypes
+import time
 from ctypes import c_float, c_int, c_void_p
 
 import torch
 
 from ..config import PAGE_SIZE
+from ..obs import buildlog
 from . import torch_ops
 from .build import lib_path
 
@@ -36,7 +38,9 @@ def lib() -> ctypes.CDLL:
         path = lib_path()
         if not path.exists():
             raise KernelError(f"{path} is missing: run `python -m b200serve.ops.build` (or __graft_entry__.build())")
+        t0 = time.perf_counter()
         _lib = ctypes.CDLL(str(path))
+        buildlog.record("load", path.name, time.perf_counter() - t0)
         for name in dir(_Sig):
             if name.startswith("b200_"):
                 fn = getattr(_lib, name)

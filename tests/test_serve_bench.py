@@ -22,5 +22,12 @@ def test_serve_bench_single_round_and_sessions(tmp_path):
         assert r.returncode == 0, r.stderr[-2000:]
         out = json.loads(r.stdout.strip().splitlines()[-1])
         assert out["requests"] >= 6 and out["cached_tokens"] > 0  # later rounds reuse their session tails
+        trace = tmp_path / "trace.csv"
+        trace.write_text("session_id,round_idx,input_len,output_len,prefix_len,tool_wait_after_ms\n"
+                         "0,0,70,5,0,10\n0,1,20,6,75,0\n1,0,90,4,0,0\n1,1,10,3,94,5\n1,2,15,2,107,0\n")
+        r = subprocess.run(base + ["--concurrency", "2", "--trace", str(trace)], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        out = json.loads(r.stdout.strip().splitlines()[-1])
+        assert out["requests"] == 5 and out["output_tokens"] == 20 and out["cached_tokens"] > 0
     finally:
         s.stop()
