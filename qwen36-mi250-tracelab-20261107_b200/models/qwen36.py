@@ -181,9 +181,78 @@ class Model:
         return self._moe(lw, h), res
 
     # ------------------------------------------------------------------ passes
+    SP_MIN_ROWS = 512  # prefill passes at least this long take the sequence-parallel collectives under TP
+
+    def _sp(self, T: int):
+        """The rank group's sequence-parallel kernels when this prefill pass should use them, else None."""
+        tp = self.tp
+        if tp is None or not getattr(tp.comm, "fused", False) or T < self.SP_MIN_ROWS or not self.device.type == "cuda":
+            return None
+        sp = getattr(tp, "sp", None)
+        if sp is None:
+            from ..parallel.sp import SeqParallel
+
+            sp = tp.sp = SeqParallel(self.device, tp.comm.group, max_rows=self.SP_MAX_ROWS, hidden=self.cfg.hidden_size)
+        unit = tp.world * 128
+        return sp if (T + unit - 1) // unit * unit <= sp.max_rows else None
+
+    SP_MAX_ROWS = 16384
+
+    def _forward_sp(self, batch: PackedBatch, sp) -> torch.Tensor:
+        """Prefill pass under tensor parallelism with a row-sharded residual stream: every all-reduce becomes a
+        reduce-scatter into the owner's rows, RMSNorm runs on the owned rows only, and the all-gather is the
+        norm kernel's stores into every rank's activation buffer, which the next GEMM consumes shard by shard
+        (``parallel/sp.py``). Rows are padded to a multiple of ``world * 128``; padding rows belong to no
+        sequence, feed only the GEMMs, and are dropped at the end."""
+        cfg, ops, R = self.cfg, self.ops, self.tp.world
+        ops.DECODE_MODE = False
+        T = batch.tokens.shape[0]
+        unit = R * 128
+        Tp = (T + unit - 1) // unit * unit
+        rpr = Tp // R
+        eps = cfg.rms_norm_eps
+        x = ops.embed(batch.tokens, self.w.embed)
+        if Tp != T:
+            x = torch.cat([x, x.new_zeros(Tp - T, x.shape[1])])
+        res = x[self.tp.rank * rpr:(self.tp.rank + 1) * rpr].contiguous()      # this rank's rows of the residual
+        sp.barrier()  # no peer is still reading its activation buffer from an earlier pass
+        full = sp.norm_allgather(res, self.w.layers[0].input_norm, eps)         # first norm: no reduction yet
+
+        def pad(t: torch.Tensor) -> torch.Tensor:
+            return t if Tp == T else torch.cat([t, t.new_zeros(Tp - T, t.shape[1])])
+
+        for i, lw in enumerate(self.w.layers):
+            mixed = sp.gemm_gathered(full, lw.in_proj)
+            if lw.kind == "linear_attention":
+                gi = self._gdn_index[i]
+                core = ops.gdn_prefill(mixed[:T], batch.seg_starts, batch.seg_slots, self.conv_state[gi], self.rec_state[gi],
+                                       lw.conv_w, lw.A_log, lw.dt_bias, lw.gnorm_w, cfg.linear_num_key_heads,
+                                       cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim, eps)
+            else:
+                core = ops.attention(mixed[:T], batch.positions, batch.seq_of_row, batch.block_tables,
+                                     self.kv[self._kv_index[i]], lw.q_norm, lw.k_norm, cfg.num_attention_heads,
+                                     cfg.num_key_value_heads, cfg.head_dim, cfg.rotary_dim, cfg.rope_theta, eps, 0,
+                                     batch.seg_starts, batch.seg_pos0)
+            sp.gemm_reduce_scatter(pad(core), lw.out_proj)
+            res, full = sp.reduce_norm_allgather(rpr, res, lw.post_norm, eps)
+            logits = sp.gemm_gathered(full, lw.router, out_dtype=torch.float32)
+            part = ops.moe_block(full, lw.router, lw.w_gate_up, lw.w_down, cfg.num_experts, cfg.num_experts_per_tok,
+                                 True, expert_map=lw.expert_map, partial_f32=True, logits=logits)
+            sp.push_reduce_scatter(part)
+            nxt = self.w.layers[i + 1].input_norm if i + 1 < len(self.w.layers) else self.w.final_norm
+            res, full = sp.reduce_norm_allgather(rpr, res, nxt, eps)
+        # the last all-gather has no GEMM behind it to wait for the shards: a one-row gathered GEMM would do, but the
+        # final hidden state is consumed by the LM head on the host's schedule, so wait for every shard here
+        sp.wait_all(full)
+        return full[:T].clone()
+
     def forward(self, batch: PackedBatch, ring=None) -> torch.Tensor:
         """Run the layer stack; returns the final-normed hidden state of every row ``[T, H]``."""
         cfg, ops = self.cfg, self.ops
+        if batch.G == 0:
+            sp = self._sp(batch.tokens.shape[0])
+            if sp is not None:
+                return self._forward_sp(batch, sp)
         ops.DECODE_MODE = batch.G > 0  # decode / verify passes may split K across clusters; prefill never does
         x = ops.embed(batch.tokens, self.w.embed)
         res = None

@@ -233,6 +233,50 @@ extern "C" int b200_reduce_norm_allgather(const AgCtx* ctx, const CommCtx* comm,
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
+// Reduce-scatter push of an fp32 partial [T, N] that no GEMM epilogue produced (the expert-parallel MoE block's
+// partial sums): tile (by, nx) of bt rows x 128 columns goes to the receive slot of the rank that owns its rows,
+// with the same flags and epochs as the EPI_REDUCE_SCATTER epilogue, so b200_reduce_norm_allgather consumes
+// either. T must be a multiple of world * bt.
+__global__ void __launch_bounds__(256)
+rs_push_kernel(CommCtx cc, const float* part, int N, int bt, int rows_per_rank) {
+  const int nx = blockIdx.x, by = blockIdx.y;
+  const int blk = by * gridDim.x + nx;
+  const int row0 = by * bt, owner = row0 / rows_per_rank, lrow0 = row0 - owner * rows_per_rank;
+  __shared__ uint32_t s_e;
+  if (threadIdx.x == 0) { s_e = cc.epoch[blk] + 1; cc.epoch[blk] = s_e; }
+  __syncthreads();
+  const uint32_t e = s_e;
+  float* dst = comm_slot(cc, owner, e, cc.rank);
+  const int cols = min(128, N - nx * 128);  // N is a multiple of 4
+  for (int idx = threadIdx.x; idx < bt * 32; idx += blockDim.x) {
+    const int r = idx >> 5, c4 = (idx & 31) * 4;
+    if (c4 < cols)
+      *reinterpret_cast<float4*>(dst + static_cast<size_t>(lrow0 + r) * N + nx * 128 + c4) =
+          *reinterpret_cast<const float4*>(part + static_cast<size_t>(row0 + r) * N + nx * 128 + c4);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) st_release_sys(cc.flags[owner] + static_cast<size_t>(cc.rank) * cc.max_blocks + blk, e);
+}
+
+extern "C" int b200_rs_push(const CommCtx* ctx, const float* part, int T, int N, int bt, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (bt <= 0 || T % (ctx->world * bt) || N % 4) return -7;
+  const int rpr = T / ctx->world, gx = (N + 127) / 128, gy = T / bt;
+  if (static_cast<unsigned long long>(rpr) * N > ctx->slot_elems || gx * gy > ctx->max_blocks) return -7;
+  rs_push_kernel<<<dim3(gx, gy), 256, 0, st>>>(*ctx, part, N, bt, rpr);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// Wait until every rank's shard of the current all-gather has arrived (for a consumer that is not a gathered GEMM).
+__global__ void ag_wait_kernel(const uint32_t* flags, const uint32_t* epoch, int world, int* err) {
+  if (static_cast<int>(threadIdx.x) < world) wait_flag(flags + threadIdx.x, *epoch, err);
+}
+extern "C" int b200_ag_wait(const AgCtx* ctx, int* err, cudaStream_t st) {
+  ag_wait_kernel<<<1, 32, 0, st>>>(ctx->flags[ctx->rank], ctx->epoch, ctx->world, err);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
 extern "C" int b200_ag_ctx_size() { return static_cast<int>(sizeof(AgCtx)); }
 
 extern "C" int b200_symm_alloc(void** ptr, unsigned long long bytes) {

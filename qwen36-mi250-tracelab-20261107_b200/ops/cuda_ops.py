@@ -219,11 +219,12 @@ def moe_bt(T: int, pairs_per_row: int, n_experts: int) -> int:
 
 def moe_block(x: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, n_experts: int,
               top_k: int, shared_merged: bool, expert_map: torch.Tensor | None = None,
-              partial_f32: bool = False) -> torch.Tensor:
+              partial_f32: bool = False, logits: torch.Tensor | None = None) -> torch.Tensor:
     """Router GEMM, top-k, expert-sorted grouped gate/up + SiLU-mul, grouped down, weighted combine.
 
     With ``expert_map`` (global expert id -> local slot or -1) only the pairs of locally hosted experts
-    are computed; ``partial_f32`` returns the fp32 partial sum that the caller adds across ranks."""
+    are computed; ``partial_f32`` returns the fp32 partial sum that the caller adds across ranks. ``logits``
+    (fp32 ``[T, rows of router]``) skips the router GEMM when the caller has already run it."""
     T, H = x.shape
     dev = x.device
     Et = w_gate_up.shape[0]
@@ -233,7 +234,8 @@ def moe_block(x: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_
     L = lib()
     st = _stream()
     err = err_word(dev)
-    logits = linear(x, router, out_dtype=torch.float32)
+    if logits is None:
+        logits = linear(x, router, out_dtype=torch.float32)
     wts = torch.empty(T, Pn, dtype=torch.float32, device=dev)
     idx = torch.empty(T, Pn, dtype=torch.int32, device=dev)
     ints = torch.empty(3 * (Et + 1) + 1 + 2 * n_pairs, dtype=torch.int32, device=dev)

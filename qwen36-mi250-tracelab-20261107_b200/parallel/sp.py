@@ -48,7 +48,11 @@ def _lib():
         L.b200_gemm_reduce_scatter.argtypes = [ctypes.POINTER(CommCtx), P, P, I, I, I, I, I, I, P]
         L.b200_gemm_gathered.argtypes = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, P, P]
         L.b200_reduce_norm_allgather.argtypes = [ctypes.POINTER(AgCtx), ctypes.POINTER(CommCtx), P, P, P, P, I, I, F, I, I, P]
-        for n in ("b200_gemm_reduce_scatter", "b200_gemm_gathered", "b200_reduce_norm_allgather", "b200_ag_ctx_size"):
+        L.b200_rs_push.argtypes = [ctypes.POINTER(CommCtx), P, I, I, I, P]
+        L.b200_ag_wait.argtypes = [ctypes.POINTER(AgCtx), P, P]
+        L.b200_ag_wait.restype = I
+        for n in ("b200_gemm_reduce_scatter", "b200_gemm_gathered", "b200_reduce_norm_allgather", "b200_ag_ctx_size",
+                  "b200_rs_push"):
             getattr(L, n).restype = I
         assert L.b200_ag_ctx_size() == ctypes.sizeof(AgCtx), "AgCtx layout mismatch"
         L._sp_ready = True
@@ -143,6 +147,18 @@ class SeqParallel:
             raise cuda_ops.KernelError(f"gemm_reduce_scatter failed with code {rc}")
         return rpr
 
+    def push_reduce_scatter(self, partial: torch.Tensor) -> int:
+        """Reduce-scatter of an fp32 partial ``[T, H]`` that no GEMM produced (the expert-parallel MoE output):
+        same receive slots and flags as ``gemm_reduce_scatter``; ``reduce_norm_allgather`` must follow."""
+        T, N = partial.shape
+        assert N == self.H and partial.dtype == torch.float32 and partial.is_contiguous()
+        rpr = self.rows_per_rank(T)
+        rc = _lib().b200_rs_push(ctypes.byref(self.comm.ctx), partial.data_ptr(), T, N, self._bt(rpr),
+                                 torch.cuda.current_stream().cuda_stream)
+        if rc:
+            raise cuda_ops.KernelError(f"rs_push failed with code {rc}")
+        return rpr
+
     def reduce_norm_allgather(self, rows: int, residual: torch.Tensor | None, w: torch.Tensor, eps: float,
                               zero_centred: bool = True) -> tuple[torch.Tensor, torch.Tensor]:
         """Finish the reduce-scatter: new residual rows ``[rows, H]`` of this rank = bf16(sum of partials) +
@@ -165,6 +181,20 @@ class SeqParallel:
         if rc:
             raise cuda_ops.KernelError(f"norm_allgather failed with code {rc}")
         return self._xfull[: rows * self.world * H].view(rows * self.world, H)
+
+    def wait_all(self, xfull: torch.Tensor) -> torch.Tensor:
+        """Make the stream wait until every shard of the last all-gather is in ``xfull`` (for consumers other than
+        ``gemm_gathered``)."""
+        rc = _lib().b200_ag_wait(ctypes.byref(self.ctx), cuda_ops.err_word(self.device).data_ptr(),
+                                 torch.cuda.current_stream().cuda_stream)
+        if rc:
+            raise cuda_ops.KernelError(f"ag_wait failed with code {rc}")
+        return xfull
+
+    def barrier(self) -> None:
+        """Order this rank's stream after everything every rank has enqueued so far (a 4-float one-shot all-reduce):
+        the first push of a pass must not land in a buffer a peer is still reading from the previous pass."""
+        self.comm.allreduce(torch.zeros(4, dtype=torch.float32, device=self.device), out_dtype=torch.float32)
 
     def gemm_gathered(self, xfull: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
         """``xfull @ w^T`` where ``xfull`` is the view ``norm_allgather`` returned: tiles wait for their shard only."""

@@ -122,6 +122,33 @@ def mode_tp_model(rank, world, dev):
             from b200serve.ops import cuda_ops
 
             cuda_ops.check_errors(dev)
+    if cuda:
+        # prefill passes of >= 512 rows take the sequence-parallel kernels (GEMM -> reduce-scatter, norm + all-gather
+        # push, shard-gated GEMM): same hidden states as the all-reduce path of the same sharded model
+        from b200serve.models.qwen36 import Model, PackedBatch
+        from b200serve.ops import cuda_ops
+
+        shard = shard_weights(full, rank, world)
+        tp = TPContext(rank, world, comms["fused"])
+        model = Model(shard, num_pages=64, state_slots=4, ops=cuda_ops, tp=tp)
+        lens = (300, 417)   # 717 rows: padded to a multiple of world * 128
+        toks = [torch.randint(3, 1024, (n,), generator=g).tolist() for n in lens]
+        tables = torch.arange(1, 17, dtype=torch.int32).view(2, 8)
+        batch = PackedBatch.prefill(toks, [1, 2], [0, 0], tables, dev)
+        assert model._sp(sum(lens)) is not None
+        h_sp = model.forward(batch)
+        state_sp = model.rec_state.clone()
+        model.SP_MIN_ROWS = 1 << 30
+        model.rec_state.zero_(); model.conv_state.zero_()
+        h_ar = model.forward(batch)
+        torch.cuda.synchronize()
+        cuda_ops.check_errors(dev)
+        err = (h_sp.float() - h_ar.float()).abs().max().item()
+        note(f"sequence-parallel prefill vs all-reduce prefill: max err {err:.4g} (max {h_ar.float().abs().max().item():.3g})")
+        assert err <= 0.05 * h_ar.float().abs().max().item() + 0.05, err
+        assert (state_sp - model.rec_state).abs().max().item() < 0.05
+        if rank == 0:
+            print(f"tp_model[seq_parallel prefill] world={world}: max err {err:.4g}", flush=True)
 
 
 def mode_lockstep(rank, world, dev):
