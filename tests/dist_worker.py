@@ -87,7 +87,9 @@ def mode_tp_model(rank, world, dev):
 
     cuda = dev.type == "cuda"
     dtype = torch.bfloat16 if cuda else torch.float32
-    cfg = ModelConfig.tiny(num_experts=8)
+    # more than 2 ranks need more heads than the default tiny model has (and share KV heads between ranks)
+    wide = dict(linear_num_key_heads=4, linear_num_value_heads=8, num_attention_heads=8, num_key_value_heads=2) if world > 2 else {}
+    cfg = ModelConfig.tiny(num_experts=8, **wide)
     full = random_weights(cfg, seed=0, device="cpu", dtype=torch.float32, std=0.05, lm_head_std=0.5).to(dev, dtype)
     g = torch.Generator().manual_seed(3)
     prompts = [torch.randint(3, 1024, (n,), generator=g).tolist() for n in (20, 70, 150, 33)]

@@ -47,6 +47,12 @@ def test_two_cpu_ranks_match_the_unsharded_engine():
     assert r.returncode == 0 and "OK tp_model" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
+def test_four_cpu_ranks_share_kv_heads_and_match_the_unsharded_engine():
+    """More ranks than KV heads: ranks of a group hold copies of the same KV head."""
+    r = _launch("tp_model", 4, 29624, env={"CUDA_VISIBLE_DEVICES": ""})
+    assert r.returncode == 0 and "OK tp_model" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
 @pytest.mark.gpu
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_two_gpu_ranks_fused_collectives_match_the_unsharded_engine():
