@@ -11,7 +11,11 @@
 //
 // G rows per sequence (speculative verify) are processed in order on the same register tile;
 // the state after row j can be stored to `ring` so that the host can commit the accepted prefix.
+#ifdef B200_EMU  // host build of the kernel bodies for tests/emu (threads, barriers and copies come from the shim)
+#include "emu_shim.h"
+#else
 #include "common.cuh"
+#endif
 
 namespace b200 {
 
@@ -57,6 +61,7 @@ __global__ void gdn_conv_step_kernel(const bf16* mixed, int ld, const int* slots
 // async copy (TMA, no registers held while it is in flight), updated in place for the G rows of the step,
 // and written back by one bulk store; with 64 KB per CTA three CTAs fit an SM, so loads, updates and
 // stores of different tiles overlap. Thread (p, c) owns column c for key rows [p*DK/4, (p+1)*DK/4).
+#ifndef B200_EMU
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
@@ -70,6 +75,9 @@ __device__ __forceinline__ void bulk_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
+__device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+#endif
+
 template <int DK, int DV>
 __global__ void __launch_bounds__(4 * DV, 3)
 gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
@@ -82,7 +90,11 @@ gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
                 int HK, int HV, int G, float eps, int* err) {
   constexpr int KP = DK / 4;  // key rows per partition
   constexpr uint32_t TILE_BYTES = DK * DV * sizeof(float);
+#ifdef B200_EMU
+  float* sS = EMU_DYNAMIC_SMEM;
+#else
   extern __shared__ __align__(128) float sS[];
+#endif
   const int b = blockIdx.y, h = blockIdx.x;
   const int c = threadIdx.x % DV, p = threadIdx.x / DV;
   const int hk = h / (HV / HK);
@@ -162,7 +174,7 @@ gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
     float ss = (p == 0) ? of * of : 0.f;
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) wred[threadIdx.x >> 5] = ss;
-    if (ring_rec) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (ring_rec) proxy_fence();
     __syncthreads();
     float tot = 0.f;
 #pragma unroll
@@ -181,7 +193,7 @@ gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
       __syncthreads();
     }
   }
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  proxy_fence();
   __syncthreads();
   if (threadIdx.x == 0) {
     bulk_store(S, sS, TILE_BYTES);
@@ -191,6 +203,7 @@ gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
 
 }  // namespace b200
 
+#ifndef B200_EMU
 using namespace b200;
 
 extern "C" int b200_gdn_decode(const void* mixed, int ld, const int* slots, void* conv_state, void* rec_state,
@@ -227,3 +240,4 @@ extern "C" int b200_gdn_decode(const void* mixed, int ld, const int* slots, void
 #undef LAUNCH_STEP
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+#endif  // B200_EMU

@@ -1,0 +1,102 @@
+// Host shim that lets a CUDA kernel source compile and run as plain C++20: every CUDA thread of one CTA is a
+// std::thread, __syncthreads() is a std::barrier, __shared__ variables become function statics (one CTA runs at a
+// time), warp shuffles go through a per-CTA exchange array. Bulk copies are memcpy and mbarrier waits succeed at
+// once, so only the kernel's arithmetic, indexing and barrier placement are under test: a missing barrier shows up
+// as a wrong result (or a data race under -fsanitize=thread), without a GPU.
+// (The reference checks its HIP kernel the same way: tools/emu/gdn_hip_emu.cpp, tools/emu/gdn_hip_emu_shim.h.)
+#pragma once
+
+#include <barrier>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <functional>
+#include <thread>
+#include <vector>
+
+#define __global__
+#define __device__
+#define __host__
+#define __forceinline__ inline
+#define __shared__ static
+#define __align__(n) alignas(n)
+#define __launch_bounds__(...)
+
+namespace b200 {
+
+struct Dim3 { unsigned x = 1, y = 1, z = 1; };
+inline thread_local Dim3 threadIdx, blockIdx;
+inline Dim3 blockDim, gridDim;
+inline std::barrier<>* cta_barrier = nullptr;
+inline float* shfl_buf = nullptr;            // one float per thread of the CTA
+alignas(128) inline float sS_storage[128 * 128];  // dynamic shared memory of the CTA under test
+#define EMU_DYNAMIC_SMEM sS_storage
+
+inline void __syncthreads() { cta_barrier->arrive_and_wait(); }
+
+// bf16 with round-to-nearest-even conversion, as the device intrinsics do
+struct bf16 { uint16_t bits; };
+inline bf16 __float2bfloat16(float f) {
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return bf16{static_cast<uint16_t>((u >> 16) | 0x40)};
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return bf16{static_cast<uint16_t>(u >> 16)};
+}
+inline float __bfloat162float(bf16 b) {
+  const uint32_t u = static_cast<uint32_t>(b.bits) << 16;
+  float f;
+  std::memcpy(&f, &u, 4);
+  return f;
+}
+
+inline float __expf(float x) { return std::exp(x); }
+inline float rsqrtf(float x) { return 1.0f / std::sqrt(x); }
+inline float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+inline float sigmoid_f(float x) { return 1.0f / (1.0f + __expf(-x)); }
+inline float softplus_f(float x) { return x > 20.0f ? x : std::log1p(__expf(x)); }
+
+// Every thread of the CTA calls the shuffle at the same point (the kernels under test have no divergent shuffles),
+// so a CTA-wide exchange is equivalent to the warp-level one.
+inline float shfl_xor(float v, int mask) {
+  shfl_buf[threadIdx.x] = v;
+  __syncthreads();
+  const float o = shfl_buf[threadIdx.x ^ static_cast<unsigned>(mask)];
+  __syncthreads();
+  return o;
+}
+inline float warp_sum(float v) {
+  for (int o = 16; o > 0; o >>= 1) v += shfl_xor(v, o);
+  return v;
+}
+
+enum ErrCode : int { ERR_NONE = 0, ERR_WAIT_FULL = 1 };
+inline void mbar_init(uint64_t*, uint32_t) {}
+inline void mbar_fence_init() {}
+inline void mbar_expect_tx(uint64_t*, uint32_t) {}
+inline bool mbar_wait(uint64_t*, uint32_t, int*, int, volatile int*) { return true; }
+inline void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t*) { std::memcpy(dst, src, bytes); }
+inline void bulk_store(void* dst, const void* src, uint32_t bytes) { std::memcpy(dst, src, bytes); }
+inline void bulk_store_wait_read() {}
+inline void proxy_fence() {}
+
+// Run `body` as one CTA of `threads` threads at block index (bx, by).
+inline void run_cta(unsigned threads, unsigned bx, unsigned by, const std::function<void()>& body) {
+  std::barrier<> bar(static_cast<std::ptrdiff_t>(threads));
+  std::vector<float> buf(threads);
+  cta_barrier = &bar;
+  shfl_buf = buf.data();
+  blockDim.x = threads;
+  std::vector<std::thread> pool;
+  pool.reserve(threads);
+  for (unsigned t = 0; t < threads; ++t)
+    pool.emplace_back([&, t] {
+      threadIdx = Dim3{t, 0, 0};
+      blockIdx = Dim3{bx, by, 0};
+      body();
+      bar.arrive_and_drop();
+    });
+  for (auto& th : pool) th.join();
+}
+
+}  // namespace b200
