@@ -74,6 +74,7 @@ class Engine:
         self.waiting: list[Generation] = []
         self.prefilling: list[Generation] = []
         self.running: list[Generation] = []
+        self._deferred: list = []
         self.stats = dict(
             decode_steps=0, decoded_tokens=0, largest_batch=0, prefill_passes=0, prefill_segments=0,
             prefilled_tokens=0, cached_tokens=0, requests=0, finished=0, failed=0,
@@ -387,10 +388,10 @@ class Engine:
         g.output.append(tok)
         g.next_token = tok
         if len(g.output) >= g.sampling.max_tokens:
-            g.emit(TokenEvent(tok, "length"))
+            self._emit(g, TokenEvent(tok, "length"))
             self._finish(g, "length", emit=False)
         else:
-            g.emit(TokenEvent(tok, None))
+            self._emit(g, TokenEvent(tok, None))
 
     # ------------------------------------------------------------------ retirement
     def _finish(self, g: Generation, reason: str, retire: bool = True, emit: bool = True) -> None:
@@ -413,7 +414,7 @@ class Engine:
                 self.slots.release(g.slot)
             g.slot, g.pages = 0, []
         if emit:
-            g.emit(TokenEvent(None, reason))
+            self._emit(g, TokenEvent(None, reason))
 
     def _fail(self, g: Generation, err: EngineError) -> None:
         self.stats["failed"] += 1
@@ -422,7 +423,22 @@ class Engine:
             self.slots.release(g.slot)
             g.slot, g.pages = 0, []
         g.finish_reason = "error"
-        g.emit(TokenEvent(None, "error", err))
+        self._emit(g, TokenEvent(None, "error", err))
+
+    # ------------------------------------------------------------------ event delivery
+    def _emit(self, g: Generation, ev: TokenEvent) -> None:
+        """Token events are handed to their consumers (the HTTP handler threads) only at points where this thread
+        is about to wait for the GPU: right after the next decode step has been launched, or when the engine goes
+        idle. Waking a hundred handler threads any earlier makes this thread queue behind them for the interpreter
+        lock while the GPU has nothing to do (the reference launches step n+1 before it reads step n for the same
+        reason, ``engine/speculative.py`` run-ahead)."""
+        self._deferred.append((g, ev))
+
+    def flush_events(self) -> None:
+        if self._deferred:
+            pending, self._deferred = self._deferred, []
+            for g, ev in pending:
+                g.emit(ev)
 
     # ------------------------------------------------------------------ loop
     def step(self, synced: bool = False) -> bool:
@@ -435,8 +451,12 @@ class Engine:
         elif not synced and not self.coordinator.sync(self):
             return False
         self._admit()
+        if self.prefilling:
+            self.flush_events()  # a prefill pass is long: do not hold decode tokens behind it
         did = self._prefill_pass()
         did = self._decode_step() or did
+        if not self.running or self.spec is not None or self._graphs is None:
+            self.flush_events()  # no graph launch is coming that would deliver them
         return did
 
     def warmup(self) -> None:

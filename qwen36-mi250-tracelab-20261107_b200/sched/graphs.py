@@ -16,23 +16,61 @@ from ..models.qwen36 import PackedBatch
 
 
 class _Bucket:
+    """Fixed-shape inputs of one graph. Tokens, positions, slots and page tables live in ONE device buffer mirrored
+    by ONE pinned host buffer, so a step costs a single host-to-device copy; the host side is written through
+    numpy views, and a page-table row is rewritten only when its request or its page count changed."""
+
     def __init__(self, engine, size: int, width: int) -> None:
         dev = engine.device
         self.size, self.width = size, width
-        self.tokens = torch.zeros(size, dtype=torch.int64, device=dev)
-        self.positions = torch.zeros(size, dtype=torch.int64, device=dev)
-        self.slots = torch.zeros(size, dtype=torch.int32, device=dev)
-        self.tables = torch.zeros(size, width, dtype=torch.int32, device=dev)
+        n_tok, n_pos, n_slot, n_tab = size * 8, size * 8, size * 4, size * width * 4
+        offs = [0, n_tok, n_tok + n_pos, n_tok + n_pos + ((n_slot + 15) // 16) * 16]
+        total = offs[3] + n_tab
+        self.dev_buf = torch.zeros(total, dtype=torch.uint8, device=dev)
+        self.host_buf = torch.zeros(total, dtype=torch.uint8)
+        if dev.type == "cuda":
+            self.host_buf = self.host_buf.pin_memory()
+
+        def views(buf):
+            return (buf[offs[0] : offs[0] + n_tok].view(torch.int64), buf[offs[1] : offs[1] + n_pos].view(torch.int64),
+                    buf[offs[2] : offs[2] + n_slot].view(torch.int32), buf[offs[3] : offs[3] + n_tab].view(torch.int32).view(size, width))
+
+        self.tokens, self.positions, self.slots, self.tables = views(self.dev_buf)
+        h = views(self.host_buf)
+        self.np_tokens, self.np_positions, self.np_slots, self.np_tables = (t.numpy() for t in h)
         self.seq = torch.arange(size, dtype=torch.int32, device=dev)
-        self.h_tokens = torch.zeros(size, dtype=torch.int64).pin_memory()
-        self.h_positions = torch.zeros(size, dtype=torch.int64).pin_memory()
-        self.h_slots = torch.zeros(size, dtype=torch.int32).pin_memory()
-        self.h_tables = torch.zeros(size, width, dtype=torch.int32).pin_memory()
-        self.h_picks = torch.zeros(size, dtype=torch.int64).pin_memory()
+        self.h_picks = torch.zeros(size, dtype=torch.int64)
+        if dev.type == "cuda":
+            self.h_picks = self.h_picks.pin_memory()
+        self.rows: list = [None] * size  # (request id, page count, last page) whose table each row currently holds
+        self.live = 0
         self.batch = PackedBatch(self.tokens, self.positions, self.seq, self.slots, self.tables, 1)
         self.graph: torch.cuda.CUDAGraph | None = None
         self.hidden = None
         self.picks = None
+
+    def fill(self, gens, tokens, positions) -> None:
+        n = len(gens)
+        self.np_tokens[:n] = tokens
+        self.np_positions[:n] = positions
+        self.np_slots[:n] = [g.slot for g in gens]
+        if n < self.live:  # rows that fell out of the batch go back to the scratch slot and page
+            self.np_tokens[n : self.live] = 0
+            self.np_positions[n : self.live] = 0
+            self.np_slots[n : self.live] = 0
+            self.np_tables[n : self.live] = 0
+            for i in range(n, self.live):
+                self.rows[i] = None
+        self.live = n
+        rows, tab = self.rows, self.np_tables
+        for i, g in enumerate(gens):
+            sig = (g.id, len(g.pages), g.pages[-1] if g.pages else 0)
+            if rows[i] != sig:
+                rows[i] = sig
+                k = len(g.pages)
+                tab[i, :k] = g.pages
+                tab[i, k:] = 0
+        self.dev_buf.copy_(self.host_buf, non_blocking=True)
 
     def capture(self, engine) -> None:
         model = engine.model
@@ -97,17 +135,9 @@ class DecodeGraphs:
             eng = self.engine
             batch = PackedBatch.uniform(tokens, positions, [g.slot for g in gens], eng._table(gens), 1, eng.device)
             return eng.model.forward(batch), None
-        b.h_tokens.zero_(); b.h_positions.zero_(); b.h_slots.zero_(); b.h_tables.zero_()
-        b.h_tokens[:n] = torch.tensor(tokens, dtype=torch.int64)
-        b.h_positions[:n] = torch.tensor(positions, dtype=torch.int64)
-        b.h_slots[:n] = torch.tensor([g.slot for g in gens], dtype=torch.int32)
-        for i, g in enumerate(gens):
-            b.h_tables[i, : len(g.pages)] = torch.tensor(g.pages, dtype=torch.int32)
-        b.tokens.copy_(b.h_tokens, non_blocking=True)
-        b.positions.copy_(b.h_positions, non_blocking=True)
-        b.slots.copy_(b.h_slots, non_blocking=True)
-        b.tables.copy_(b.h_tables, non_blocking=True)
+        b.fill(gens, tokens, positions)
         b.graph.replay()
+        self.engine.flush_events()  # the previous step's tokens go out while the GPU runs this one
         b.h_picks.copy_(b.picks, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return b.hidden[:n], b.h_picks[:n]
