@@ -226,8 +226,7 @@ def main() -> None:
     value = replicas * tokens / (ms / 1e3)
     e2e_value = replicas * e2e_tokens / e2e_s
     bucket = next(b for b in engine._graphs.buckets.values() if b.size == B)
-    h2d = (bucket.h_tokens.numel() * 8 + bucket.h_positions.numel() * 8 + bucket.h_slots.numel() * 4
-           + bucket.h_tables.numel() * 4)
+    h2d = bucket.host_buf.numel()  # tokens, positions, slots and page tables: one pinned buffer, one copy per step
     d2h = bucket.h_picks.numel() * 8
     n_gdn, n_attn = len(mcfg.gdn_layers), len(mcfg.attention_layers)
     # kernels per decode step: 2 norms + 2 projections + router + 7 MoE kernels per layer, 2 (GDN) or 3 (attention)

@@ -120,17 +120,9 @@ GDN_PREFILL_TC = __import__("os").environ.get("ENGINE_GDN_TC", "1") == "1"
 def split_k(N: int, K: int, grouped: bool = False) -> int:
     """CTAs per cluster that share one output tile along K. A function of the weight shape and of the kind
     of pass only (never of the number of rows), so a row's bits do not depend on its batch."""
-    if not DECODE_MODE:
+    if not (DECODE_MODE and SPLIT_K_ENABLED):  # opt-in: measured slower at batch 128 even for the 3-tile router GEMM
         return 1
     nk = K // 64
-    if not SPLIT_K_ENABLED:
-        # default policy: only GEMMs with a handful of output tiles (the router: 3 tiles, 32 k-blocks in a row on 3 SMs)
-        if grouped or N > 512:
-            return 1
-        s = 1
-        while s < 8 and nk // (s * 2) >= 4:
-            s *= 2
-        return s
     if grouped:  # expert tiles already give hundreds of CTAs at batch sizes where the MoE dominates the step
         return 2 if nk >= 32 else 1
     tiles, s = (N + 127) // 128, 1
