@@ -99,7 +99,8 @@ class Engine:
         if self.device.type != "cuda":
             return min(4096, c.max_seqs * (min(self.max_model_len, 8192) // PAGE_SIZE + 2) + 64)
         free, _total = torch.cuda.mem_get_info(self.device)
-        budget = free * c.kv_fraction - c.reserve_gb * (1 << 30) - n_slots * m.gdn_state_bytes()
+        ring_rows = c.max_seqs * (max(1, c.spec_kmax) + 1) if (c.mtp and m.mtp_num_hidden_layers) else 0  # verify ring
+        budget = free * c.kv_fraction - c.reserve_gb * (1 << 30) - (n_slots + ring_rows) * m.gdn_state_bytes()
         pages = int(budget // per_page)
         need = self.max_pages_per_seq + 8  # at least one full-length sequence (reference: model.py:492-521)
         if pages < min(need, 64):
@@ -455,7 +456,7 @@ class Engine:
             self.flush_events()  # a prefill pass is long: do not hold decode tokens behind it
         did = self._prefill_pass()
         did = self._decode_step() or did
-        if not self.running or self.spec is not None or self._graphs is None:
+        if not self.running or self._graphs is None:
             self.flush_events()  # no graph launch is coming that would deliver them
         return did
 

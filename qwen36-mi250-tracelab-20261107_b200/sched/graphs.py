@@ -141,3 +141,145 @@ class DecodeGraphs:
         b.h_picks.copy_(b.picks, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return b.hidden[:n], b.h_picks[:n]
+
+
+class _VerifyBucket:
+    """One captured speculative step: verify pass over ``G = k + 1`` rows per sequence, greedy picks, the accepted
+    prefix length of every sequence, the MTP block over all rows and the ``kmax`` draft links that start at each
+    sequence's last accepted row, all on the device; the host reads one ``[picks | accepted | drafts]`` vector back
+    (the reference captures verify + accept + draft chain the same way and reads one packed row,
+    ``engine/fast/kernels.py:544-571``, ``engine/fast/model.py:2009-2120``)."""
+
+    def __init__(self, engine, size: int, width: int, k: int, kmax: int, ring) -> None:
+        dev = engine.device
+        G = k + 1
+        self.size, self.width, self.k, self.G, self.kmax = size, width, k, G, kmax
+        n_tok, n_slot, n_tab = size * G * 8, size * 4, size * width * 4
+        offs = [0, n_tok, 2 * n_tok, 2 * n_tok + ((n_slot + 15) // 16) * 16, 2 * n_tok + 2 * (((n_slot + 15) // 16) * 16)]
+        total = offs[4] + n_tab
+        self.dev_buf = torch.zeros(total, dtype=torch.uint8, device=dev)
+        self.host_buf = torch.zeros(total, dtype=torch.uint8).pin_memory()
+
+        def views(buf):
+            return (buf[offs[0] : offs[0] + n_tok].view(torch.int64), buf[offs[1] : offs[1] + n_tok].view(torch.int64),
+                    buf[offs[2] : offs[2] + n_slot].view(torch.int32), buf[offs[3] : offs[3] + n_slot].view(torch.int32),
+                    buf[offs[4] : offs[4] + n_tab].view(torch.int32).view(size, width))
+
+        self.tokens, self.positions, self.slots, self.n_valid, self.tables = views(self.dev_buf)
+        self.np_tokens, self.np_positions, self.np_slots, self.np_valid, self.np_tables = (t.numpy() for t in views(self.host_buf))
+        self.seq = torch.repeat_interleave(torch.arange(size, dtype=torch.int32, device=dev), G)
+        self.seq1 = torch.arange(size, dtype=torch.int32, device=dev)
+        self.batch = PackedBatch(self.tokens, self.positions, self.seq, self.slots, self.tables, G)
+        self.ring = ring
+        self.h_out = torch.zeros(size * G + size + size * kmax, dtype=torch.int64).pin_memory()
+        self.rows: list = [None] * size
+        self.live = 0
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.out = None
+
+    def _body(self, model):
+        size, G, k = self.size, self.G, self.k
+        dev = self.tokens.device
+        hidden = model.forward(self.batch, ring=self.ring)
+        picks = model.greedy(hidden)
+        pk = picks.view(size, G)
+        if k > 0:
+            tok = self.tokens.view(size, G)
+            valid = torch.arange(k, device=dev)[None, :] < self.n_valid[:, None]
+            match = ((tok[:, 1:] == pk[:, :-1]) & valid).long()
+            acc = torch.cumprod(match, dim=1).sum(dim=1)
+        else:
+            acc = torch.zeros(size, dtype=torch.long, device=dev)
+        y = model.mtp_forward(hidden, picks, self.batch)
+        h = y[torch.arange(size, device=dev) * G + acc]
+        d = model.greedy(h)
+        drafts = [d]
+        base = self.positions.view(size, G)[:, 0] + acc + 1
+        for j in range(1, self.kmax):
+            link = PackedBatch(d, base + (j - 1), self.seq1, self.slots, self.tables, 1)
+            h = model.mtp_forward(h, d, link)
+            d = model.greedy(h)
+            drafts.append(d)
+        return torch.cat([picks, acc, torch.stack(drafts, dim=1).reshape(-1)])
+
+    def capture(self, engine, pool) -> None:
+        s = torch.cuda.Stream(device=engine.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._body(engine.model)
+        torch.cuda.current_stream().wait_stream(s)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool=pool):
+            self.out = self._body(engine.model)
+        self.graph = g
+
+    def fill(self, gens, tokens, positions, n_valid) -> None:
+        n, G = len(gens), self.G
+        self.np_tokens[: n * G] = tokens
+        self.np_positions[: n * G] = positions
+        self.np_slots[:n] = [g.slot for g in gens]
+        self.np_valid[:n] = n_valid
+        if n < self.live:
+            self.np_tokens[n * G : self.live * G] = 0
+            self.np_positions[n * G : self.live * G] = 0
+            self.np_slots[n : self.live] = 0
+            self.np_valid[n : self.live] = 0
+            self.np_tables[n : self.live] = 0
+            for i in range(n, self.live):
+                self.rows[i] = None
+        self.live = n
+        rows, tab = self.rows, self.np_tables
+        for i, g in enumerate(gens):
+            sig = (g.id, len(g.pages), g.pages[-1] if g.pages else 0)
+            if rows[i] != sig:
+                rows[i] = sig
+                m = len(g.pages)
+                tab[i, :m] = g.pages
+                tab[i, m:] = 0
+        self.dev_buf.copy_(self.host_buf, non_blocking=True)
+
+
+class VerifyGraphs:
+    """Captured speculative steps per (batch bucket, context class, draft depth); shares the decode graphs' buckets'
+    sizes and memory pool. ``run`` returns None when a capture failed (the caller runs the step eagerly)."""
+
+    def __init__(self, engine, decode: DecodeGraphs, kmax: int, ring_of) -> None:
+        self.engine, self.decode, self.kmax, self.ring_of = engine, decode, kmax, ring_of
+        self.pool = torch.cuda.graph_pool_handle()
+        self.buckets: dict = {}
+        self.errors: dict = {}
+
+    def usable(self, gens) -> bool:
+        return self.decode.usable(gens)
+
+    def _bucket(self, n: int, pages: int, k: int):
+        size = next(s for s in self.decode.sizes if s >= n)
+        width = next(w for w in self.decode.widths if w >= pages)
+        key = (size, width, k)
+        b = self.buckets.get(key)
+        if b is None and key not in self.errors:
+            try:
+                b = _VerifyBucket(self.engine, size, width, k, self.kmax, self.ring_of(size, k + 1))
+                b.capture(self.engine, self.pool)
+            except Exception as e:  # noqa: BLE001 - remember the failure, run eagerly
+                self.errors[key] = repr(e)
+                return None
+            self.buckets[key] = b
+        return b
+
+    def run(self, gens, tokens, positions, n_valid, k: int):
+        n = len(gens)
+        b = self._bucket(n, max(len(g.pages) for g in gens), k)
+        if b is None:
+            return None
+        b.fill(gens, tokens, positions, n_valid)
+        b.graph.replay()
+        self.engine.flush_events()
+        b.h_out.copy_(b.out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        G, size = b.G, b.size
+        out = b.h_out
+        picks = out[: size * G].view(size, G)[:n].tolist()
+        acc = out[size * G : size * G + size][:n].tolist()
+        drafts = out[size * G + size :].view(size, self.kmax)[:n].tolist()
+        return picks, acc, drafts, b.ring, b.slots[:n]

@@ -86,19 +86,32 @@ class SpecController:
         self.policy = DepthPolicy(kmax=max(1, c.spec_kmax), fixed=c.spec_k)
         self.k_hist: dict[int, int] = {}
         self.draft_override = None  # tests: callable(gen, k) -> list[int] forcing the drafts of a step
-        self._rings: dict[tuple[int, int], tuple] = {}
+        self._ring_store = None
+        self._ring_cap = 0
+        self._vgraphs = None
 
     # ------------------------------------------------------------------ helpers
     def eligible(self, g) -> bool:
         return g.sampling.greedy and len(g.output) >= g.sampling.min_tokens
 
     def _ring(self, B: int, G: int):
-        key = (B, G)
-        if key not in self._rings:
-            if len(self._rings) > 8:
-                self._rings.clear()
-            self._rings[key] = self.engine.model.new_ring(B, G)
-        return self._rings[key]
+        """State-after-row buffers ``[layers, B, G, ...]`` of a verify pass: contiguous views of ONE storage sized for
+        the largest batch and depth, shared by every step shape (only one step runs at a time, and its accepted rows
+        are committed before the next). Captured graphs keep pointers into it, so it never moves once graphs exist."""
+        model = self.engine.model
+        n_gdn = model.conv_state.shape[0]
+        conv_row = model.conv_state[0, 0].numel()
+        rec_row = model.rec_state[0, 0].numel()
+        if self._ring_store is None or B * G > self._ring_cap:
+            if self._ring_store is not None and self._vgraphs is not None and self._vgraphs.buckets:
+                raise RuntimeError("the verify ring cannot grow after graphs were captured")
+            cap = max(B * G, self.engine.cfg.max_seqs * (self.policy.kmax + 1)) if self.engine._graphs is not None else B * G
+            self._ring_cap = cap
+            self._ring_store = (torch.empty(n_gdn * cap * conv_row, dtype=model.dtype, device=model.device),
+                                torch.empty(n_gdn * cap * rec_row, dtype=torch.float32, device=model.device))
+        conv, rec = self._ring_store
+        return (conv[: n_gdn * B * G * conv_row].view(n_gdn, B, G, *model.conv_state.shape[2:]),
+                rec[: n_gdn * B * G * rec_row].view(n_gdn, B, G, *model.rec_state.shape[2:]))
 
     # ------------------------------------------------------------------ prefill hooks
     def after_prefill(self, gens, spans, batch: PackedBatch, hidden: torch.Tensor) -> None:
@@ -176,6 +189,24 @@ class SpecController:
             ds = ds + [0] * (k - len(ds))
             tokens.extend([g.next_token] + ds)
             positions.extend(range(g.computed, g.computed + G))
+        res = None
+        if eng._graphs is not None and eng._graphs.usable(gens) and not any(eng._needs_logits(g) for g in gens):
+            if self._vgraphs is None:
+                from ..sched.graphs import VerifyGraphs
+
+                self._vgraphs = VerifyGraphs(eng, eng._graphs, self.policy.kmax, self._ring)
+            res = self._vgraphs.run(gens, tokens, positions, n_valid, k)
+        if res is not None:
+            picks_h, acc_h, drafts_h, ring, slots_t = res
+        else:
+            picks_h, acc_h, drafts_h, ring, slots_t = self._eager_step(gens, elig, tokens, positions, n_valid, k)
+        self._book(gens, elig, n_valid, k, picks_h, acc_h, drafts_h, ring, slots_t)
+        return True
+
+    def _eager_step(self, gens, elig, tokens, positions, n_valid, k):
+        """The same step launched kernel by kernel (CPU, sampled rows, or a shape without a captured graph)."""
+        eng = self.engine
+        B, G = len(gens), k + 1
         batch = PackedBatch.uniform(tokens, positions, [g.slot for g in gens], eng._table(gens), G, eng.device)
         ring = self._ring(B, G)
         hidden = eng.model.forward(batch, ring=ring)
@@ -206,9 +237,12 @@ class SpecController:
         drafts = [d]
         base_pos = batch.positions.view(B, G)[:, 0] + acc + 1
         self._chain_links(gens, h, d, base_pos, drafts)
-        picks_h = picks.view(B, G).tolist()
-        acc_h = acc.tolist()
-        drafts_h = torch.stack(drafts, dim=1).tolist()
+        eng.flush_events()
+        return picks.view(B, G).tolist(), acc.tolist(), torch.stack(drafts, dim=1).tolist(), ring, batch.slots
+
+    def _book(self, gens, elig, n_valid, k, picks_h, acc_h, drafts_h, ring, slots_t) -> None:
+        eng = self.engine
+        B = len(gens)
         # Phase 1: how many picks each request can book (EOS and the token budget end the run early),
         # hence which row's state to keep. The cache must be settled before any request retires.
         keep, book = [], []
@@ -225,7 +259,7 @@ class SpecController:
             used = n + 1 if eos else n  # rows whose tokens are confirmed: the EOS pick confirms its row too
             keep.append(used - 1)
             book.append((n, eos, used, a))
-        eng.model.commit_ring(ring, batch.slots, torch.tensor(keep, device=eng.device))
+        eng.model.commit_ring(ring, slots_t, torch.tensor(keep, device=eng.device))
         # Phase 2: book the tokens (this may finish requests and park their state as session tails)
         for i, g in enumerate(gens):
             n, eos, used, a = book[i]
@@ -248,7 +282,6 @@ class SpecController:
             st["mtp_verify_steps"] += 1
             st["mtp_proposed"] += sum(n_valid)
             st["mtp_accepted"] += sum(min(a, n) for a, n, e in zip(acc_h, n_valid, elig) if e)
-        return True
 
     def settle(self, gen) -> None:
         """Nothing to undo: a verify step commits exactly the rows whose tokens were booked."""
