@@ -13,6 +13,7 @@ One JSON line per (depth, batch): wall-clock around ``Engine.generate`` after a 
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import sys
 import time
@@ -64,6 +65,7 @@ def main() -> None:
                               "acceptance": round(st["mtp_accepted"] / st["mtp_proposed"], 4) if st.get("mtp_proposed") else None}),
                   flush=True)
         del eng
+        gc.collect()  # engine, controller and captured graphs reference each other
         if cuda:
             torch.cuda.empty_cache()
 
