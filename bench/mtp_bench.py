@@ -49,7 +49,7 @@ def main() -> None:
         eng = Engine(w, ecfg)
         for B in batches:
             prompts = [torch.randint(3, cfg.vocab_size, (a.prompt_len,), generator=g).tolist() for _ in range(B)]
-            eng.generate(prompts[:1], Sampling(max_tokens=8, ignore_eos=True))  # warm-up
+            eng.generate(prompts, Sampling(max_tokens=6, ignore_eos=True))  # warm-up: captures this batch size's graphs
             if cuda:
                 torch.cuda.synchronize()
             before = dict(eng.stats)
