@@ -118,6 +118,10 @@ class Model:
 
     def commit_ring(self, ring, slots: torch.Tensor, keep_rows: torch.Tensor) -> None:
         """Set each slot's GDN state to the state after row ``keep_rows[i]`` of its verify rows."""
+        if hasattr(self.ops, "ring_commit") and self.device.type == "cuda" \
+                and ring[0][0, 0, 0].numel() * ring[0].element_size() % 16 == 0:
+            self.ops.ring_commit(self.conv_state, self.rec_state, ring, slots, keep_rows)
+            return
         b = torch.arange(slots.shape[0], device=self.device)
         sl, kr = slots.long(), keep_rows.long()
         self.conv_state[:, sl] = ring[0][:, b, kr]

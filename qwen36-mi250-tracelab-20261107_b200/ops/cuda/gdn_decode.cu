@@ -204,7 +204,43 @@ gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
 }  // namespace b200
 
 #ifndef B200_EMU
+namespace b200 {
+// After a verify pass: slot state <- state after row keep[b] of sequence b, for every GDN layer. The step kernel
+// leaves the state after the LAST row in the slot, so sequences that keep every row need no copy; the others copy
+// one contiguous row of the ring (conv: C x 3 bf16, recurrent: HV x DK x DV fp32). Grid (chunks, B, layers).
+__global__ void ring_commit_kernel(uint4* conv_state, uint4* rec_state, const uint4* ring_conv, const uint4* ring_rec,
+                                   const int* slots, const int64_t* keep, int B, int G, int n_slots, size_t conv_row,
+                                   size_t rec_row) {
+  const int b = blockIdx.y, layer = blockIdx.z;
+  const int k = static_cast<int>(keep[b]);
+  if (k >= G - 1 || k < 0) return;
+  const size_t slot = static_cast<size_t>(slots[b]);
+  const uint4* src_r = ring_rec + ((static_cast<size_t>(layer) * B + b) * G + k) * rec_row;
+  uint4* dst_r = rec_state + (static_cast<size_t>(layer) * n_slots + slot) * rec_row;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < rec_row; i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    dst_r[i] = src_r[i];
+  const uint4* src_c = ring_conv + ((static_cast<size_t>(layer) * B + b) * G + k) * conv_row;
+  uint4* dst_c = conv_state + (static_cast<size_t>(layer) * n_slots + slot) * conv_row;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < conv_row; i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    dst_c[i] = src_c[i];
+}
+}  // namespace b200
+
 using namespace b200;
+
+// conv_state [layers, n_slots, conv_bytes], rec_state [layers, n_slots, rec_bytes], rings [layers, B, G, row bytes];
+// the first n <= B sequences are committed; row sizes in bytes, multiples of 16.
+extern "C" int b200_ring_commit(void* conv_state, void* rec_state, const void* ring_conv, const void* ring_rec,
+                                const int* slots, const int64_t* keep, int layers, int B, int n, int G, int n_slots,
+                                unsigned long long conv_bytes, unsigned long long rec_bytes, cudaStream_t st) {
+  if (n <= 0 || layers <= 0) return 0;
+  if (n > B) return -7;
+  if (conv_bytes % 16 || rec_bytes % 16) return -7;
+  ring_commit_kernel<<<dim3(32, n, layers), 256, 0, st>>>(
+      static_cast<uint4*>(conv_state), static_cast<uint4*>(rec_state), static_cast<const uint4*>(ring_conv),
+      static_cast<const uint4*>(ring_rec), slots, keep, B, G, n_slots, conv_bytes / 16, rec_bytes / 16);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
 
 extern "C" int b200_gdn_decode(const void* mixed, int ld, const int* slots, void* conv_state, void* rec_state,
                                const void* conv_w, const float* A_log, const float* dt_bias, const void* gnorm_w,

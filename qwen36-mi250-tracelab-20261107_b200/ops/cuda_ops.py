@@ -68,6 +68,7 @@ class _Sig:
     b200_paged_attn = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
     b200_gdn_prefill = [P, I, P, P, P, P, P, P, P, P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, F, I, P, P]
     b200_gdn_prefill_work_stride = [I]
+    b200_ring_commit = [P, P, P, P, P, P, I, I, I, I, I, ctypes.c_ulonglong, ctypes.c_ulonglong, P]
     b200_flash_prefill = [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, P, P, P]
     b200_attn_combine = [P, P, P, P, I, I, I, I, P]
 
@@ -285,6 +286,22 @@ def gdn_decode(mixed, slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnor
     )
     _check(rc, "gdn_decode")
     return out
+
+
+def ring_commit(conv_state, rec_state, ring, slots: torch.Tensor, keep_rows: torch.Tensor) -> None:
+    """Slot state <- state after row ``keep_rows[b]`` of a verify pass, all GDN layers in one launch; sequences that
+    keep every row are skipped (the step kernel already left that state in the slot)."""
+    ring_conv, ring_rec = ring
+    layers, G = ring_rec.shape[0], ring_rec.shape[2]
+    assert ring_rec.is_contiguous() and ring_conv.is_contiguous() and slots.shape[0] <= ring_rec.shape[1]
+    conv_bytes = conv_state[0, 0].numel() * conv_state.element_size()
+    rec_bytes = rec_state[0, 0].numel() * rec_state.element_size()
+    slots32 = slots if slots.dtype == torch.int32 else slots.to(torch.int32)
+    keep64 = keep_rows if keep_rows.dtype == torch.int64 else keep_rows.to(torch.int64)
+    rc = lib().b200_ring_commit(_ptr(conv_state), _ptr(rec_state), _ptr(ring_conv), _ptr(ring_rec), _ptr(slots32),
+                                _ptr(keep64), layers, ring_rec.shape[1], slots.shape[0], G, conv_state.shape[1], conv_bytes, rec_bytes,
+                                _stream())
+    _check(rc, "ring_commit")
 
 
 def gdn_prefill(mixed, seg_starts, seg_slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnorm_w, n_k, n_v, dk,

@@ -336,3 +336,20 @@ def test_split_k_cluster_gemm(C, O):
         C.check_errors(x.device)
     finally:
         C.DECODE_MODE = C.SPLIT_K_ENABLED = False
+
+
+def test_ring_commit_copies_only_sequences_that_dropped_rows(C):
+    """Verify-ring commit: slot <- ring[b, keep[b]] per layer, except where every row is kept."""
+    layers, n_slots, B, G, n = 3, 9, 6, 4, 4
+    conv = _bf(layers, n_slots, 64, 3, seed=90)
+    rec = torch.randn(layers, n_slots, 2, 16, 16, device="cuda")
+    ring = (_bf(layers, B, G, 64, 3, seed=91), torch.randn(layers, B, G, 2, 16, 16, device="cuda"))
+    slots = torch.tensor([5, 2, 7, 1], dtype=torch.int32, device="cuda")
+    keep = torch.tensor([0, 3, 2, 1], device="cuda")
+    want_c, want_r = conv.clone(), rec.clone()
+    for b in range(n):
+        if keep[b] < G - 1:
+            want_c[:, slots[b]] = ring[0][:, b, keep[b]]
+            want_r[:, slots[b]] = ring[1][:, b, keep[b]]
+    C.ring_commit(conv, rec, ring, slots, keep)
+    assert torch.equal(conv, want_c) and torch.equal(rec, want_r)
