@@ -38,16 +38,25 @@ def add(name: str, seconds: float) -> None:
         _cur[name] = _cur.get(name, 0.0) + seconds
 
 
+NVTX = os.environ.get("ENGINE_NVTX") == "1"  # also open an NVTX range per stage (visible to nsys / ncu --nvtx)
+
+
 @contextmanager
 def stage(name: str):
-    if not ENABLED:
+    if not (ENABLED or NVTX):
         yield
         return
+    if NVTX:
+        import torch
+
+        torch.cuda.nvtx.range_push(name)
     t = now()
     try:
         yield
     finally:
         add(name, now() - t)
+        if NVTX:
+            torch.cuda.nvtx.range_pop()
 
 
 def gpu_span(name: str):

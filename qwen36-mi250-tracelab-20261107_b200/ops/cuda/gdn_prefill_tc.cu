@@ -51,23 +51,29 @@ struct WyParams {
 
 constexpr int WY_SMEM = 3 * 32768 + 1024 /*align*/ + 4096 /*small arrays + barriers*/;
 
-__global__ void __launch_bounds__(128, 2)
+// 256 threads. Row phases: thread (i = tid & 127, half = tid >> 7) works on token row i = TMEM lane i and on one
+// 64-column half of it. Substitution phase: thread (col = tid >> 1, part = tid & 1) owns column col of T together with
+// its neighbour lane; the pair splits every dot product and meets in one shuffle.
+__global__ void __launch_bounds__(256, 2)
 gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;            // raw q, later the fp32 A blocks, later the bf16 block-diagonal T
+  uint8_t* sQ = smem;            // raw q, later the fp32 A blocks, later the bf16 block-diagonal T diag(beta)
   uint8_t* sK = smem + 32768;    // raw k, later k e^g / |k|
-  uint8_t* sV = smem + 65536;    // the substitution's private columns (fp32), later raw v
+  uint8_t* sV = smem + 65536;    // the substitution's columns (fp32), later raw v
   float* sG = reinterpret_cast<float*>(smem + 98304);  // [128] cumulative log decay
   float* sRk = sG + 128;                               // [128] 1 / |k|
-  float* sTot = sRk + 128;                             // [4] warp totals of the scan
+  float* sBeta = sRk + 128;                            // [128]
+  float* sPart = sBeta + 128;                          // [2][128][2] partial squared norms of the two row halves
+  float* sTot = sPart + 512;                           // [4] warp totals of the scan
   uint64_t* bars = reinterpret_cast<uint64_t*>(sTot + 8);
   uint64_t* tma_bar = bars;
   uint64_t* mma_bar = bars + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int i = threadIdx.x, warp = i >> 5, lane = i & 31;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int i = tid & 127, half = tid >> 7;
   const int c = i >> 6, r = i & 63;  // chunk of the pair, row inside it
   const int h = blockIdx.y, hk = h / (p.HV / p.HK);
   const int key_dim = p.HK * 128;
@@ -76,7 +82,7 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
   const ChunkInfoTc ci = p.chunks[present ? chunk_idx : 2 * blockIdx.x];
   const bool valid = present && r < ci.nrows;
 
-  if (i == 0) {
+  if (tid == 0) {
     mbar_init(tma_bar, 1);
     mbar_init(mma_bar, 1);
     *abort_flag = 0;
@@ -88,11 +94,12 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
 
-  if (i == 0) {
-    // rows of both chunks (a missing second chunk re-reads the first: finite data, never written out)
-    mbar_expect_tx(tma_bar, 2 * 32768);  // v arrives later: its region is scratch for the substitution first
+  if (tid == 0) {
+    // q and k rows of both chunks (a missing second chunk re-reads the first: finite data, never written out);
+    // v arrives later: its region is scratch for the substitution first
+    mbar_expect_tx(tma_bar, 2 * 32768);
     for (int cc = 0; cc < 2; ++cc) {
       const int idx = 2 * blockIdx.x + cc;
       const int row0 = p.chunks[idx < p.n_chunks ? idx : 2 * blockIdx.x].row0;
@@ -102,7 +109,7 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
       }
     }
   }
-  // gates and their inclusive scan inside each chunk (two warps per chunk)
+  // gates and their inclusive scan inside each chunk (two warps per chunk; both halves compute the same values)
   float g = 0.f, beta = 0.f;
   if (valid) {
     const size_t row = static_cast<size_t>(ci.row0 + r);
@@ -115,17 +122,17 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
     const float x = __shfl_up_sync(0xffffffffu, gs, o);
     if (lane >= o) gs += x;
   }
-  if (lane == 31) sTot[warp] = gs;
+  if (half == 0 && lane == 31) sTot[warp] = gs;
   __syncthreads();
-  if (warp & 1) gs += sTot[warp - 1];
-  sG[i] = gs;
+  if (warp & 1) gs += sTot[(warp & 3) - 1];
+  if (half == 0) { sG[i] = gs; sBeta[i] = beta; }
   __syncthreads();
   const float glast = sG[c * 64 + 63];
 
   bool ok = mbar_wait(tma_bar, 0, p.err, ERR_WAIT_FULL, abort_flag);
   tc_fence_after();
   __syncthreads();
-  if (i == 0 && ok) {
+  if (tid == 0 && ok) {
     constexpr uint32_t idesc = umma_idesc_bf16(128, 128);
     const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK);
 #pragma unroll
@@ -140,15 +147,14 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
     }
     umma_commit(mma_bar);
   }
-  // own q / k rows: norms, then the decayed copies the state pass consumes
-  float sq = 0.f, sk = 0.f;
-  const uint32_t tile_row = c * 64 + r;  // = i: row inside each 128-row atom
-#pragma unroll
-  for (int a = 0; a < 2; ++a)
+  // squared norms: each half sums its 64 columns of the q and k rows
+  const uint32_t tile_row = i;  // row inside each 128-row atom
+  {
+    float sq = 0.f, sk = 0.f;
 #pragma unroll
     for (int c16 = 0; c16 < 8; ++c16) {
-      const uint4 qv = *reinterpret_cast<const uint4*>(sQ + a * 16384 + swz(tile_row, c16));
-      const uint4 kv = *reinterpret_cast<const uint4*>(sK + a * 16384 + swz(tile_row, c16));
+      const uint4 qv = *reinterpret_cast<const uint4*>(sQ + half * 16384 + swz(tile_row, c16));
+      const uint4 kv = *reinterpret_cast<const uint4*>(sK + half * 16384 + swz(tile_row, c16));
       const bf16* qe = reinterpret_cast<const bf16*>(&qv);
       const bf16* ke = reinterpret_cast<const bf16*>(&kv);
 #pragma unroll
@@ -158,46 +164,51 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
         sk += y * y;
       }
     }
-  const float rq = rsqrtf(sq + 1e-6f) * 0.08838834764831845f;  // 1 / |q| / sqrt(128)
-  const float rk = rsqrtf(sk + 1e-6f);
-  sRk[i] = rk;
+    sPart[(half * 128 + i) * 2] = sq;
+    sPart[(half * 128 + i) * 2 + 1] = sk;
+  }
+  __syncthreads();
+  const float rq = rsqrtf(sPart[i * 2] + sPart[(128 + i) * 2] + 1e-6f) * 0.08838834764831845f;  // 1 / |q| / sqrt(128)
+  const float rk = rsqrtf(sPart[i * 2 + 1] + sPart[(128 + i) * 2 + 1] + 1e-6f);
+  if (half == 0) sRk[i] = rk;
   const size_t ch = static_cast<size_t>(present ? chunk_idx : 0) * p.HV + h;
   bf16* regA = reinterpret_cast<bf16*>(p.work) + ch * 256 * 128;
-  if (present) {
+  if (present) {  // the decayed copies the state pass consumes: this thread's 64 columns of row r
     const float fq = rq * __expf(gs), fk = rk * __expf(glast - gs);
-    uint4* qg = reinterpret_cast<uint4*>(regA + (128 + r) * 128);
-    uint4* kg = reinterpret_cast<uint4*>(regA + (192 + r) * 128);
+    uint4* qg = reinterpret_cast<uint4*>(regA + (128 + r) * 128) + half * 8;
+    uint4* kg = reinterpret_cast<uint4*>(regA + (192 + r) * 128) + half * 8;
 #pragma unroll
-    for (int a = 0; a < 2; ++a)
+    for (int c16 = 0; c16 < 8; ++c16) {
+      const uint4 qv = *reinterpret_cast<const uint4*>(sQ + half * 16384 + swz(tile_row, c16));
+      const uint4 kv = *reinterpret_cast<const uint4*>(sK + half * 16384 + swz(tile_row, c16));
+      const bf16* qe = reinterpret_cast<const bf16*>(&qv);
+      const bf16* ke = reinterpret_cast<const bf16*>(&kv);
+      uint4 qo, ko;
+      bf16* qoe = reinterpret_cast<bf16*>(&qo);
+      bf16* koe = reinterpret_cast<bf16*>(&ko);
 #pragma unroll
-      for (int c16 = 0; c16 < 8; ++c16) {
-        const uint4 qv = *reinterpret_cast<const uint4*>(sQ + a * 16384 + swz(tile_row, c16));
-        const uint4 kv = *reinterpret_cast<const uint4*>(sK + a * 16384 + swz(tile_row, c16));
-        const bf16* qe = reinterpret_cast<const bf16*>(&qv);
-        const bf16* ke = reinterpret_cast<const bf16*>(&kv);
-        uint4 qo, ko;
-        bf16* qoe = reinterpret_cast<bf16*>(&qo);
-        bf16* koe = reinterpret_cast<bf16*>(&ko);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          qoe[j] = __float2bfloat16(__bfloat162float(qe[j]) * fq);
-          koe[j] = __float2bfloat16(__bfloat162float(ke[j]) * fk);
-        }
-        qg[a * 8 + c16] = qo;
-        kg[a * 8 + c16] = ko;
+      for (int j = 0; j < 8; ++j) {
+        qoe[j] = __float2bfloat16(__bfloat162float(qe[j]) * fq);
+        koe[j] = __float2bfloat16(__bfloat162float(ke[j]) * fk);
       }
-    if (r == 63) *reinterpret_cast<float*>(p.work + tc_region_g(static_cast<size_t>(p.n_chunks) * p.HV) + ch * 4) = glast;
+      qg[c16] = qo;
+      kg[c16] = ko;
+    }
+    if (r == 63 && half == 0)
+      *reinterpret_cast<float*>(p.work + tc_region_g(static_cast<size_t>(p.n_chunks) * p.HV) + ch * 4) = glast;
   }
   __syncthreads();  // sRk complete; every thread is done with the raw q tile
   ok = mbar_wait(mma_bar, 0, p.err, ERR_WAIT_TMEM, abort_flag) && !*abort_flag;
   tc_fence_after();
 
   // A = (k beta) k^T decay, strictly lower, fp32 into the q region: element (r, j) of chunk c at
-  // c * 16384 + r * 256 + (((j >> 2) + r) & 15) * 16 + (j & 3) * 4 bytes (row-rotated float4 groups)
+  // c * 16384 + r * 256 + (((j >> 2) + r) & 15) * 16 + (j & 3) * 4 bytes (row-rotated float4 groups).
+  // Each half builds 32 of the row's 64 columns.
   float* sA = reinterpret_cast<float*>(sQ + c * 16384);
   bf16* regB = reinterpret_cast<bf16*>(p.work + tc_region_b(static_cast<size_t>(p.n_chunks) * p.HV)) + ch * 64 * 64;
 #pragma unroll
-  for (int j0 = 0; j0 < 64; j0 += 16) {
+  for (int jj0 = 0; jj0 < 32; jj0 += 16) {
+    const int j0 = half * 32 + jj0;
     float kk[16], qk[16];
     tmem_ld16(tmem + lane_base + c * 64 + j0, kk);
     tmem_ld16(tmem + lane_base + 128 + c * 64 + j0, qk);
@@ -223,63 +234,68 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
   {
     const float fk = rk * __expf(gs);
 #pragma unroll
-    for (int a = 0; a < 2; ++a)
+    for (int c16 = 0; c16 < 8; ++c16) {
+      uint4* kp = reinterpret_cast<uint4*>(sK + half * 16384 + swz(tile_row, c16));
+      uint4 kv = *kp;
+      bf16* ke = reinterpret_cast<bf16*>(&kv);
 #pragma unroll
-      for (int c16 = 0; c16 < 8; ++c16) {
-        uint4* kp = reinterpret_cast<uint4*>(sK + a * 16384 + swz(tile_row, c16));
-        uint4 kv = *kp;
-        bf16* ke = reinterpret_cast<bf16*>(&kv);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ke[j] = __float2bfloat16(__bfloat162float(ke[j]) * fk);
-        *kp = kv;
-      }
+      for (int j = 0; j < 8; ++j) ke[j] = __float2bfloat16(__bfloat162float(ke[j]) * fk);
+      *kp = kv;
+    }
   }
   __syncthreads();
-  // T = (I + A)^-1: thread (c, r) solves column r of its chunk's T by forward substitution. The column is private
-  // to the thread (sC[j * 128 + i], the v region, free until v is loaded), the reads of A are the same address
-  // across the warp (broadcast), so the loop needs no barrier; it stays rolled to keep the code small.
-  // Column entry j of thread i lives at sC[(j >> 2) * 512 + i * 4 + (j & 3)]: four consecutive entries are one
-  // 16-byte load, and a warp's loads are contiguous.
-  float* sC = reinterpret_cast<float*>(sV);
-#pragma unroll 4
-  for (int j4 = 0; j4 < 16; ++j4)
-    *reinterpret_cast<float4*>(sC + j4 * 512 + i * 4) =
-        make_float4(4 * j4 == r ? 1.f : 0.f, 4 * j4 + 1 == r ? 1.f : 0.f, 4 * j4 + 2 == r ? 1.f : 0.f, 4 * j4 + 3 == r ? 1.f : 0.f);
-  // the odd warp of a chunk owns columns 32..63: their entries above row 32 are zero, so it starts further down
-  const int j4_lo = (warp & 1) ? 8 : 0;
-#pragma unroll 1
-  for (int ii = (warp & 1) ? 33 : 1; ii < 64; ++ii) {
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-    const int ng = (ii + 3) >> 2;  // entries at or right of the diagonal are zero in A
-    const float* arow = sA + ii * 64;
-#pragma unroll 4
-    for (int j4 = j4_lo; j4 < ng; ++j4) {
-      const float4 a4 = *reinterpret_cast<const float4*>(arow + (((j4 + ii) & 15) << 2));
-      const float4 c4 = *reinterpret_cast<const float4*>(sC + j4 * 512 + i * 4);
-      a0 += a4.x * c4.x;
-      a1 += a4.y * c4.y;
-      a2 += a4.z * c4.z;
-      a3 += a4.w * c4.w;
-    }
-    if (ii > r) sC[(ii >> 2) * 512 + i * 4 + (ii & 3)] = -((a0 + a1) + (a2 + a3));
-  }
-  __syncthreads();  // every thread has finished reading A: the region becomes the bf16 operand tile
-  // T diag(beta), block-diagonal, as a K-major A operand: row (c * 64 + ii), K index (c * 64 + r) -> atom c; the
-  // other atom's rows of this chunk are zero. w = (T diag(beta)) (k e^g), u = (T diag(beta)) v.
+  // T = (I + A)^-1 by forward substitution. Lanes (2m, 2m + 1) of a warp own column col = tid >> 1 of T: entry j of
+  // the column lives at sC[(j >> 2) * 512 + col * 4 + (j & 3)] (the v region, free until v is loaded); the pair
+  // splits the groups of four entries of every dot product by parity and adds the halves with one shuffle. A column
+  // is private to its pair and the reads of A are the same addresses across the warp, so only __syncwarp is needed.
   {
-    uint8_t* tile = sQ + c * 16384;
+    const int col = tid >> 1, part = tid & 1;
+    const int cc = col >> 6, rr = col & 63;
+    const float* sAc = reinterpret_cast<const float*>(sQ + cc * 16384);
+    float* sC = reinterpret_cast<float*>(sV);
+    for (int j4 = part; j4 < 16; j4 += 2)
+      *reinterpret_cast<float4*>(sC + j4 * 512 + col * 4) =
+          make_float4(4 * j4 == rr ? 1.f : 0.f, 4 * j4 + 1 == rr ? 1.f : 0.f, 4 * j4 + 2 == rr ? 1.f : 0.f, 4 * j4 + 3 == rr ? 1.f : 0.f);
+    __syncwarp();
+    const int lo = (warp & 3) * 16;  // smallest column of this warp inside its chunk: rows up to it are zero above the diagonal
+#pragma unroll 1
+    for (int ii = lo + 1; ii < 64; ++ii) {
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      const int ng = (ii + 3) >> 2;  // entries at or right of the diagonal are zero in A
+      const float* arow = sAc + ii * 64;
+#pragma unroll 2
+      for (int j4 = (lo >> 2) + part; j4 < ng; j4 += 2) {
+        const float4 a4 = *reinterpret_cast<const float4*>(arow + (((j4 + ii) & 15) << 2));
+        const float4 c4 = *reinterpret_cast<const float4*>(sC + j4 * 512 + col * 4);
+        a0 += a4.x * c4.x;
+        a1 += a4.y * c4.y;
+        a2 += a4.z * c4.z;
+        a3 += a4.w * c4.w;
+      }
+      float acc = (a0 + a1) + (a2 + a3);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      if (part == 0 && ii > rr) sC[(ii >> 2) * 512 + col * 4 + (ii & 3)] = -acc;
+      __syncwarp();
+    }
+    __syncthreads();  // every thread has finished reading A: the region becomes the bf16 operand tile
+    // T diag(beta), block-diagonal, as a K-major A operand: row (cc * 64 + ii), K index (cc * 64 + rr) -> atom cc;
+    // the pair writes alternate rows
+    uint8_t* tile = sQ + cc * 16384;
+    const float bcol = sBeta[col];
 #pragma unroll 8
-    for (int ii = 0; ii < 64; ++ii)
-      *reinterpret_cast<bf16*>(tile + swz(c * 64 + ii, r >> 3) + (r & 7) * 2) =
-          __float2bfloat16(sC[(ii >> 2) * 512 + i * 4 + (ii & 3)] * beta);
+    for (int ii = part; ii < 64; ii += 2)
+      *reinterpret_cast<bf16*>(tile + swz(cc * 64 + ii, rr >> 3) + (rr & 7) * 2) =
+          __float2bfloat16(sC[(ii >> 2) * 512 + col * 4 + (ii & 3)] * bcol);
+  }
+  {  // the other atom's rows of this chunk are zero: w = (T diag(beta)) (k e^g), u = (T diag(beta)) v
     uint8_t* other = sQ + (1 - c) * 16384;
 #pragma unroll
-    for (int c16 = 0; c16 < 8; ++c16) *reinterpret_cast<uint4*>(other + swz(tile_row, c16)) = make_uint4(0, 0, 0, 0);
+    for (int c16 = 0; c16 < 4; ++c16) *reinterpret_cast<uint4*>(other + swz(tile_row, half * 4 + c16)) = make_uint4(0, 0, 0, 0);
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   tc_fence_before();
   __syncthreads();
-  if (i == 0 && ok) {
+  if (tid == 0 && ok) {
     tc_fence_after();
     // the v rows of both chunks replace the scratch columns while the first MMA runs
     mbar_expect_tx(tma_bar, 32768);
@@ -310,12 +326,12 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
   ok = mbar_wait(mma_bar, 1, p.err, ERR_WAIT_TMEM, abort_flag) && !*abort_flag;
   tc_fence_after();
 #pragma unroll 1
-  for (int half = 0; half < 2; ++half) {  // 0: w -> rows [0, 64), 1: u -> rows [64, 128) of the chunk's A-region
-    uint4* dst = reinterpret_cast<uint4*>(regA + (half * 64 + r) * 128);
+  for (int which = 0; which < 2; ++which) {  // 0: w -> rows [0, 64), 1: u -> rows [64, 128) of the chunk's A-region
+    uint4* dst = reinterpret_cast<uint4*>(regA + (which * 64 + r) * 128) + half * 8;
 #pragma unroll
-    for (int c0 = 0; c0 < 128; c0 += 16) {
+    for (int c0 = 0; c0 < 64; c0 += 16) {
       float v[16];
-      tmem_ld16(tmem + lane_base + half * 128 + c0, v);  // warp-collective: never predicated
+      tmem_ld16(tmem + lane_base + which * 128 + half * 64 + c0, v);  // warp-collective: never predicated
       uint4 o[2];
       bf16* oe = reinterpret_cast<bf16*>(o);
 #pragma unroll
@@ -328,6 +344,9 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, 256); }
 }
 
+}  // namespace b200
+
+namespace b200 {
 
 // ------------------------------------------------------------------ state pass
 struct ScanParams {
@@ -594,7 +613,7 @@ extern "C" int b200_gdn_prefill_tc(const void* mixed, int ld, const void* conv_o
   if (tc_map_2d(&tb, static_cast<uint8_t*>(work) + tc_region_b(nch), 64, nch * 64, 64)) return -1;
   WyParams wp{static_cast<const bf16*>(mixed), ld, C + value_dim, C + value_dim + HV,
               static_cast<const ChunkInfoTc*>(chunks), n_chunks, A_log, dt_bias, static_cast<uint8_t*>(work), HK, HV, err};
-  gdn_wy_tc_kernel<<<dim3((n_chunks + 1) / 2, HV), 128, WY_SMEM, st>>>(tc, wp);
+  gdn_wy_tc_kernel<<<dim3((n_chunks + 1) / 2, HV), 256, WY_SMEM, st>>>(tc, wp);
   ScanParams sp{static_cast<const ChunkInfoTc*>(chunks), static_cast<const int2*>(seg_chunks), slots, rec_state,
                 reinterpret_cast<const float*>(static_cast<uint8_t*>(work) + tc_region_g(nch)),
                 static_cast<bf16*>(o_tmp), HV, err};

@@ -29,6 +29,7 @@ from ..config import PAGE_SIZE, EngineConfig, ModelConfig
 from ..models.checkpoint import Weights
 from ..models.qwen36 import Model, PackedBatch
 from ..ops import torch_ops
+from ..obs import looptimers
 from .request import EngineError, Generation, Sampling, TokenEvent
 from .sampling import pick_token
 
@@ -451,11 +452,14 @@ class Engine:
             self._poll_local()
         elif not synced and not self.coordinator.sync(self):
             return False
-        self._admit()
+        with looptimers.stage("admit"):
+            self._admit()
         if self.prefilling:
             self.flush_events()  # a prefill pass is long: do not hold decode tokens behind it
-        did = self._prefill_pass()
-        did = self._decode_step() or did
+        with looptimers.stage("prefill"):
+            did = self._prefill_pass()
+        with looptimers.stage("decode"):
+            did = self._decode_step() or did
         if not self.running or self._graphs is None:
             self.flush_events()  # no graph launch is coming that would deliver them
         return did

@@ -13,6 +13,7 @@ import torch
 
 from ..config import PAGE_SIZE
 from ..models.qwen36 import PackedBatch
+from ..obs import looptimers
 
 
 class _Bucket:
@@ -135,11 +136,16 @@ class DecodeGraphs:
             eng = self.engine
             batch = PackedBatch.uniform(tokens, positions, [g.slot for g in gens], eng._table(gens), 1, eng.device)
             return eng.model.forward(batch), None
-        b.fill(gens, tokens, positions)
+        with looptimers.stage("build"):
+            b.fill(gens, tokens, positions)
+        start, stop = looptimers.gpu_span("gpu_graph")
+        start()
         b.graph.replay()
+        stop()
         self.engine.flush_events()  # the previous step's tokens go out while the GPU runs this one
         b.h_picks.copy_(b.picks, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        with looptimers.stage("wait"):
+            torch.cuda.current_stream().synchronize()
         return b.hidden[:n], b.h_picks[:n]
 
 
