@@ -51,6 +51,12 @@ struct WyParams {
 
 constexpr int WY_SMEM = 3 * 32768 + 1024 /*align*/ + 4096 /*small arrays + barriers*/;
 
+// In-kernel phase clocks: thread 0 of CTA (0, 0) stamps clock64() at the phase boundaries of the WY kernel; the host
+// reads the last launch's stamps with b200_gdn_wy_phase_clocks (the reference's HIP kernel has the same kind of
+// phase clocks behind its PROF template argument, engine/fast/hip/gdn_chain.hip:163-165, 367-385).
+__device__ long long g_wy_clocks[12];
+#define WY_STAMP(k) do { if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) g_wy_clocks[k] = clock64(); } while (0)
+
 // 256 threads. Row phases: thread (i = tid & 127, half = tid >> 7) works on token row i = TMEM lane i and on one
 // 64-column half of it. Substitution phase: thread (col = tid >> 1, part = tid & 1) owns column col of T together with
 // its neighbour lane; the pair splits every dot product and meets in one shuffle.
@@ -109,6 +115,7 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
       }
     }
   }
+  WY_STAMP(0);
   // gates and their inclusive scan inside each chunk (two warps per chunk; both halves compute the same values)
   float g = 0.f, beta = 0.f;
   if (valid) {
@@ -129,6 +136,7 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
   __syncthreads();
   const float glast = sG[c * 64 + 63];
 
+  WY_STAMP(1);  // gates done
   bool ok = mbar_wait(tma_bar, 0, p.err, ERR_WAIT_FULL, abort_flag);
   tc_fence_after();
   __syncthreads();
@@ -147,6 +155,7 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
     }
     umma_commit(mma_bar);
   }
+  WY_STAMP(2);  // q / k tiles arrived, Gram MMAs issued
   // squared norms: each half sums its 64 columns of the q and k rows
   const uint32_t tile_row = i;  // row inside each 128-row atom
   {
@@ -197,10 +206,12 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
     if (r == 63 && half == 0)
       *reinterpret_cast<float*>(p.work + tc_region_g(static_cast<size_t>(p.n_chunks) * p.HV) + ch * 4) = glast;
   }
+  WY_STAMP(3);  // norms + decayed copies written
   __syncthreads();  // sRk complete; every thread is done with the raw q tile
   ok = mbar_wait(mma_bar, 0, p.err, ERR_WAIT_TMEM, abort_flag) && !*abort_flag;
   tc_fence_after();
 
+  WY_STAMP(4);  // Gram matrices in TMEM
   // A = (k beta) k^T decay, strictly lower, fp32 into the q region: element (r, j) of chunk c at
   // c * 16384 + r * 256 + (((j >> 2) + r) & 15) * 16 + (j & 3) * 4 bytes (row-rotated float4 groups).
   // Each half builds 32 of the row's 64 columns.
@@ -244,6 +255,7 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
     }
   }
   __syncthreads();
+  WY_STAMP(5);  // A built, k scaled
   // T = (I + A)^-1 by forward substitution. Lanes (2m, 2m + 1) of a warp own column col = tid >> 1 of T: entry j of
   // the column lives at sC[(j >> 2) * 512 + col * 4 + (j & 3)] (the v region, free until v is loaded); the pair
   // splits the groups of four entries of every dot product by parity and adds the halves with one shuffle. A column
@@ -277,6 +289,7 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
       if (part == 0 && ii > rr) sC[(ii >> 2) * 512 + col * 4 + (ii & 3)] = -acc;
       __syncwarp();
     }
+    WY_STAMP(6);  // substitution done (this warp)
     __syncthreads();  // every thread has finished reading A: the region becomes the bf16 operand tile
     // T diag(beta), block-diagonal, as a K-major A operand: row (cc * 64 + ii), K index (cc * 64 + rr) -> atom cc;
     // the pair writes alternate rows
@@ -292,6 +305,7 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
 #pragma unroll
     for (int c16 = 0; c16 < 4; ++c16) *reinterpret_cast<uint4*>(other + swz(tile_row, half * 4 + c16)) = make_uint4(0, 0, 0, 0);
   }
+  WY_STAMP(7);  // T tile written
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   tc_fence_before();
   __syncthreads();
@@ -323,8 +337,10 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
     }
     umma_commit(mma_bar);
   }
+  WY_STAMP(8);  // second pair of MMAs issued
   ok = mbar_wait(mma_bar, 1, p.err, ERR_WAIT_TMEM, abort_flag) && !*abort_flag;
   tc_fence_after();
+  WY_STAMP(9);  // w / u in TMEM
 #pragma unroll 1
   for (int which = 0; which < 2; ++which) {  // 0: w -> rows [0, 64), 1: u -> rows [64, 128) of the chunk's A-region
     uint4* dst = reinterpret_cast<uint4*>(regA + (which * 64 + r) * 128) + half * 8;
@@ -339,6 +355,7 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
       if (present && ok) { dst[c0 / 8] = o[0]; dst[c0 / 8 + 1] = o[1]; }
     }
   }
+  WY_STAMP(10);  // w / u written
   tc_fence_before();
   __syncthreads();
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, 256); }
@@ -587,6 +604,11 @@ int tc_map_2d(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, ui
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -2;
 }
 }  // namespace
+
+// Phase clocks of CTA (0, 0) of the last WY launch on the current device: 11 clock64() stamps (see WY_STAMP).
+extern "C" int b200_gdn_wy_phase_clocks(long long* out11) {
+  return cudaMemcpyFromSymbol(out11, g_wy_clocks, 11 * sizeof(long long)) == cudaSuccess ? 0 : -1;
+}
 
 // Workspace bytes per (chunk, head) of the tensor-core path (fits inside the fp32 path's workspace).
 extern "C" int b200_gdn_prefill_tc_work_bytes() { return 65536 + 8192 + 4; }
