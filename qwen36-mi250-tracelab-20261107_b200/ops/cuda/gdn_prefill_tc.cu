@@ -49,7 +49,7 @@ struct WyParams {
   int* err;
 };
 
-constexpr int WY_SMEM = 3 * 32768 + 1024 /*align*/ + 4096 /*small arrays + barriers*/;
+constexpr int WY_SMEM = 3 * 32768 + 1024 /*align*/ + 5120 /*small arrays + barriers*/;
 
 // In-kernel phase clocks: thread 0 of CTA (0, 0) stamps clock64() at the phase boundaries of the WY kernel; the host
 // reads the last launch's stamps with b200_gdn_wy_phase_clocks (the reference's HIP kernel has the same kind of
@@ -71,7 +71,9 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
   float* sRk = sG + 128;                               // [128] 1 / |k|
   float* sBeta = sRk + 128;                            // [128]
   float* sPart = sBeta + 128;                          // [2][128][2] partial squared norms of the two row halves
-  float* sTot = sPart + 512;                           // [4] warp totals of the scan
+  float* sFq = sPart + 512;                            // [128] row factors of the decayed q copy
+  float* sFk = sFq + 128;                              // [128] row factors of the decayed k copy
+  float* sTot = sFk + 128;                             // [4] warp totals of the scan
   uint64_t* bars = reinterpret_cast<uint64_t*>(sTot + 8);
   uint64_t* tma_bar = bars;
   uint64_t* mma_bar = bars + 1;
@@ -179,32 +181,42 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
   __syncthreads();
   const float rq = rsqrtf(sPart[i * 2] + sPart[(128 + i) * 2] + 1e-6f) * 0.08838834764831845f;  // 1 / |q| / sqrt(128)
   const float rk = rsqrtf(sPart[i * 2 + 1] + sPart[(128 + i) * 2 + 1] + 1e-6f);
-  if (half == 0) sRk[i] = rk;
+  if (half == 0) {
+    sRk[i] = rk;
+    sFq[i] = rq * __expf(gs);
+    sFk[i] = rk * __expf(glast - gs);
+  }
   const size_t ch = static_cast<size_t>(present ? chunk_idx : 0) * p.HV + h;
   bf16* regA = reinterpret_cast<bf16*>(p.work) + ch * 256 * 128;
-  if (present) {  // the decayed copies the state pass consumes: this thread's 64 columns of row r
-    const float fq = rq * __expf(gs), fk = rk * __expf(glast - gs);
-    uint4* qg = reinterpret_cast<uint4*>(regA + (128 + r) * 128) + half * 8;
-    uint4* kg = reinterpret_cast<uint4*>(regA + (192 + r) * 128) + half * 8;
+  if (present && r == 63 && half == 0)
+    *reinterpret_cast<float*>(p.work + tc_region_g(static_cast<size_t>(p.n_chunks) * p.HV) + ch * 4) = glast;
+  __syncthreads();
+  // the decayed copies the state pass consumes, q e^g / |q| / sqrt(dk) and k e^{g_last - g} / |k|: warp w copies rows
+  // [16 w, 16 w + 16); 16 lanes cover the 256 bytes of one row, so every store instruction writes two whole rows
+#pragma unroll 2
+  for (int it = 0; it < 8; ++it) {
+    const int row = warp * 16 + it * 2 + (lane >> 4), chunk = lane & 15;
+    const int cpr = row >> 6, rrow = row & 63;
+    const int cidx = 2 * blockIdx.x + cpr;
+    const uint32_t off = (chunk >> 3) * 16384 + swz(row, chunk & 7);
+    const uint4 qv = *reinterpret_cast<const uint4*>(sQ + off);
+    const uint4 kv = *reinterpret_cast<const uint4*>(sK + off);
+    const float fq = sFq[row], fk = sFk[row];
+    const bf16* qe = reinterpret_cast<const bf16*>(&qv);
+    const bf16* ke = reinterpret_cast<const bf16*>(&kv);
+    uint4 qo, ko;
+    bf16* qoe = reinterpret_cast<bf16*>(&qo);
+    bf16* koe = reinterpret_cast<bf16*>(&ko);
 #pragma unroll
-    for (int c16 = 0; c16 < 8; ++c16) {
-      const uint4 qv = *reinterpret_cast<const uint4*>(sQ + half * 16384 + swz(tile_row, c16));
-      const uint4 kv = *reinterpret_cast<const uint4*>(sK + half * 16384 + swz(tile_row, c16));
-      const bf16* qe = reinterpret_cast<const bf16*>(&qv);
-      const bf16* ke = reinterpret_cast<const bf16*>(&kv);
-      uint4 qo, ko;
-      bf16* qoe = reinterpret_cast<bf16*>(&qo);
-      bf16* koe = reinterpret_cast<bf16*>(&ko);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        qoe[j] = __float2bfloat16(__bfloat162float(qe[j]) * fq);
-        koe[j] = __float2bfloat16(__bfloat162float(ke[j]) * fk);
-      }
-      qg[c16] = qo;
-      kg[c16] = ko;
+    for (int j = 0; j < 8; ++j) {
+      qoe[j] = __float2bfloat16(__bfloat162float(qe[j]) * fq);
+      koe[j] = __float2bfloat16(__bfloat162float(ke[j]) * fk);
     }
-    if (r == 63 && half == 0)
-      *reinterpret_cast<float*>(p.work + tc_region_g(static_cast<size_t>(p.n_chunks) * p.HV) + ch * 4) = glast;
+    if (cidx < p.n_chunks) {
+      bf16* base = reinterpret_cast<bf16*>(p.work) + (static_cast<size_t>(cidx) * p.HV + h) * 256 * 128;
+      reinterpret_cast<uint4*>(base + (128 + rrow) * 128)[chunk] = qo;
+      reinterpret_cast<uint4*>(base + (192 + rrow) * 128)[chunk] = ko;
+    }
   }
   WY_STAMP(3);  // norms + decayed copies written
   __syncthreads();  // sRk complete; every thread is done with the raw q tile
@@ -265,28 +277,59 @@ gdn_wy_tc_kernel(const __grid_constant__ CUtensorMap tmConv, WyParams p) {
     const int cc = col >> 6, rr = col & 63;
     const float* sAc = reinterpret_cast<const float*>(sQ + cc * 16384);
     float* sC = reinterpret_cast<float*>(sV);
-    for (int j4 = part; j4 < 16; j4 += 2)
-      *reinterpret_cast<float4*>(sC + j4 * 512 + col * 4) =
-          make_float4(4 * j4 == rr ? 1.f : 0.f, 4 * j4 + 1 == rr ? 1.f : 0.f, 4 * j4 + 2 == rr ? 1.f : 0.f, 4 * j4 + 3 == rr ? 1.f : 0.f);
-    __syncwarp();
-    const int lo = (warp & 3) * 16;  // smallest column of this warp inside its chunk: rows up to it are zero above the diagonal
+    // Blocked by 16 rows so that a column entry is read from shared memory once per BLOCK, not once per row: for
+    // block b, first the panel acc[i] = sum over earlier blocks' entries j of A[16 b + i][j] T[j] (the pair splits
+    // the groups of four j by parity and meets in 16 shuffles), then the 16 x 16 triangle with the block's own
+    // entries in registers, then one store of the block's 16 entries. Blocks that lie entirely above every diagonal
+    // of the warp's columns are zero and skipped.
+    const int lo = (warp & 3) * 16;  // smallest column of this warp inside its chunk
 #pragma unroll 1
-    for (int ii = lo + 1; ii < 64; ++ii) {
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-      const int ng = (ii + 3) >> 2;  // entries at or right of the diagonal are zero in A
-      const float* arow = sAc + ii * 64;
-#pragma unroll 2
-      for (int j4 = (lo >> 2) + part; j4 < ng; j4 += 2) {
-        const float4 a4 = *reinterpret_cast<const float4*>(arow + (((j4 + ii) & 15) << 2));
-        const float4 c4 = *reinterpret_cast<const float4*>(sC + j4 * 512 + col * 4);
-        a0 += a4.x * c4.x;
-        a1 += a4.y * c4.y;
-        a2 += a4.z * c4.z;
-        a3 += a4.w * c4.w;
+    for (int blk = 0; blk < 4; ++blk) {
+      float t[16];
+      if (16 * blk + 15 < lo) {  // warp-uniform
+        if (part == 0) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) *reinterpret_cast<float4*>(sC + (4 * blk + q4) * 512 + col * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        continue;
       }
-      float acc = (a0 + a1) + (a2 + a3);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      if (part == 0 && ii > rr) sC[(ii >> 2) * 512 + col * 4 + (ii & 3)] = -acc;
+      float acc[16];
+#pragma unroll
+      for (int ii = 0; ii < 16; ++ii) acc[ii] = 0.f;
+#pragma unroll 1
+      for (int j4 = (lo >> 2) + part; j4 < 4 * blk; j4 += 2) {
+        const float4 c4 = *reinterpret_cast<const float4*>(sC + j4 * 512 + col * 4);
+#pragma unroll
+        for (int ii = 0; ii < 16; ++ii) {
+          const int row = 16 * blk + ii;
+          const float4 a4 = *reinterpret_cast<const float4*>(sAc + row * 64 + (((j4 + row) & 15) << 2));
+          acc[ii] += (a4.x * c4.x + a4.y * c4.y) + (a4.z * c4.z + a4.w * c4.w);
+        }
+      }
+#pragma unroll
+      for (int ii = 0; ii < 16; ++ii) acc[ii] += __shfl_xor_sync(0xffffffffu, acc[ii], 1);
+      // the block's own triangle: both lanes of the pair compute it (entries in registers, static indices)
+#pragma unroll
+      for (int ii = 0; ii < 16; ++ii) {
+        const int row = 16 * blk + ii;
+        float a = acc[ii];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          if (4 * q4 < ii) {
+            const float4 a4 = *reinterpret_cast<const float4*>(sAc + row * 64 + (((4 * blk + q4 + row) & 15) << 2));
+            if (4 * q4 + 0 < ii) a += a4.x * t[4 * q4 + 0];
+            if (4 * q4 + 1 < ii) a += a4.y * t[4 * q4 + 1];
+            if (4 * q4 + 2 < ii) a += a4.z * t[4 * q4 + 2];
+            if (4 * q4 + 3 < ii) a += a4.w * t[4 * q4 + 3];
+          }
+        }
+        t[ii] = row > rr ? -a : (row == rr ? 1.f : 0.f);
+      }
+      if (part == 0) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+          *reinterpret_cast<float4*>(sC + (4 * blk + q4) * 512 + col * 4) = make_float4(t[4 * q4], t[4 * q4 + 1], t[4 * q4 + 2], t[4 * q4 + 3]);
+      }
       __syncwarp();
     }
     WY_STAMP(6);  // substitution done (this warp)
