@@ -153,12 +153,9 @@ def case_gemm_decode(small):
     """Dense projections at decode size (128 rows): GDN in_proj 12352 x 2048 and out_proj 2048 x 4096."""
     for name, N, K in (("in_proj", 12352, 2048), ("out_proj", 2048, 4096), ("router", 257, 2048)):
         x, w = bf(128, K), bf(N, K, scale=0.02)
-        for bt in (0, 64):  # 0: the default token tile (128 rows, one CTA per SM); 64: two tiles, two CTAs per SM
-            for decode in (False, True):  # decode passes split K over a cluster when the GEMM has few tiles
-                C.DECODE_MODE = decode
-                us = timed(lambda: C.linear(x, w, bt=bt))
-                report(f"gemm_decode_{name}_b128", us, w.numel() * 2, 2 * 128 * N * K, bt=bt or 128, split_k=C.split_k(N, K))
-        C.DECODE_MODE = False
+        for bt in (0, 16, 32, 64, 128):  # 0: what the engine picks; smaller token tiles = more CTAs streaming the weights
+            us = timed(lambda: C.linear(x, w, bt=bt))
+            report(f"gemm_decode_{name}_b128", us, w.numel() * 2, 2 * 128 * N * K, bt=bt or "auto")
 
 
 def case_gemm_prefill(small):

@@ -62,8 +62,11 @@ struct Cfg {
   static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
   // small token tiles (decode) leave room for two CTAs per SM: one CTA's pipeline fill and epilogue
   // overlap the other's main loop, which matters when K is short (the MoE down projection has 8 k-blocks)
-  static constexpr int CTAS_PER_SM = BT <= 64 ? 2 : 1;
-  static constexpr int BUDGET = BT <= 64 ? 108 * 1024 : 200 * 1024;
+  // The fused gate/up GEMM at 16-row token tiles runs three CTAs per SM with two deep stages each: the same bytes in
+  // flight per SM, but a decode step's ~1300 tiles then fill 2.9 waves of 444 CTAs instead of 4.4 waves of 296, and
+  // the partial last wave is what the weight-streaming time loses.
+  static constexpr int CTAS_PER_SM = (BT <= 16 && EPI == EPI_SILU_MUL) ? 3 : BT <= 64 ? 2 : 1;
+  static constexpr int BUDGET = CTAS_PER_SM == 3 ? 72 * 1024 : BT <= 64 ? 108 * 1024 : 200 * 1024;
   static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int ACC_COLS = A_TILES * BT;  // one accumulator stage
