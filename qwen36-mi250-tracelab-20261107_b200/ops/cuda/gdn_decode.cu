@@ -26,34 +26,61 @@ namespace b200 {
 template <int KW>
 __global__ void gdn_conv_step_kernel(const bf16* mixed, int ld, const int* slots, bf16* conv_state, const bf16* conv_w,
                                      bf16* out, bf16* ring_conv, int C, int G) {
+  // a thread owns 8 consecutive channels: 16-byte loads of the inputs, 48 / 64 contiguous bytes of state / weights
   const int b = blockIdx.y;
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (c >= C) return;
   const int slot = slots[b];
   bf16* st = conv_state + (static_cast<size_t>(slot) * C + c) * (KW - 1);
-  float win[KW];
-  float w[KW];
+  float win[8][KW];
+  float w[8][KW];
+  {
+    bf16 sv[8 * (KW - 1)], wv[8 * KW];
 #pragma unroll
-  for (int k = 0; k < KW - 1; ++k) win[k] = __bfloat162float(st[k]);
+    for (int i = 0; i < (KW - 1); ++i) reinterpret_cast<uint4*>(sv)[i] = reinterpret_cast<const uint4*>(st)[i];
 #pragma unroll
-  for (int k = 0; k < KW; ++k) w[k] = __bfloat162float(conv_w[c * KW + k]);
-  for (int j = 0; j < G; ++j) {
-    const size_t row = static_cast<size_t>(b) * G + j;
-    win[KW - 1] = __bfloat162float(mixed[row * ld + c]);
-    float acc = 0.f;
+    for (int i = 0; i < KW; ++i) reinterpret_cast<uint4*>(wv)[i] = reinterpret_cast<const uint4*>(conv_w + static_cast<size_t>(c) * KW)[i];
 #pragma unroll
-    for (int k = 0; k < KW; ++k) acc += win[k] * w[k];
-    out[row * C + c] = __float2bfloat16(silu_f(acc));
+    for (int ch = 0; ch < 8; ++ch) {
 #pragma unroll
-    for (int k = 0; k < KW - 1; ++k) win[k] = win[k + 1];
-    if (ring_conv) {
-      bf16* r = ring_conv + ((static_cast<size_t>(b) * G + j) * C + c) * (KW - 1);
+      for (int k = 0; k < KW - 1; ++k) win[ch][k] = __bfloat162float(sv[ch * (KW - 1) + k]);
 #pragma unroll
-      for (int k = 0; k < KW - 1; ++k) r[k] = __float2bfloat16(win[k]);
+      for (int k = 0; k < KW; ++k) w[ch][k] = __bfloat162float(wv[ch * KW + k]);
     }
   }
+  for (int j = 0; j < G; ++j) {
+    const size_t row = static_cast<size_t>(b) * G + j;
+    bf16 xv[8], ov[8];
+    *reinterpret_cast<uint4*>(xv) = *reinterpret_cast<const uint4*>(mixed + row * ld + c);
 #pragma unroll
-  for (int k = 0; k < KW - 1; ++k) st[k] = __float2bfloat16(win[k]);
+    for (int ch = 0; ch < 8; ++ch) {
+      win[ch][KW - 1] = __bfloat162float(xv[ch]);
+      float acc = 0.f;
+#pragma unroll
+      for (int k = 0; k < KW; ++k) acc += win[ch][k] * w[ch][k];
+      ov[ch] = __float2bfloat16(silu_f(acc));
+#pragma unroll
+      for (int k = 0; k < KW - 1; ++k) win[ch][k] = win[ch][k + 1];
+    }
+    *reinterpret_cast<uint4*>(out + row * C + c) = *reinterpret_cast<const uint4*>(ov);
+    if (ring_conv) {
+      bf16 rv[8 * (KW - 1)];
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch)
+#pragma unroll
+        for (int k = 0; k < KW - 1; ++k) rv[ch * (KW - 1) + k] = __float2bfloat16(win[ch][k]);
+      uint4* r = reinterpret_cast<uint4*>(ring_conv + ((static_cast<size_t>(b) * G + j) * C + c) * (KW - 1));
+#pragma unroll
+      for (int i = 0; i < (KW - 1); ++i) r[i] = reinterpret_cast<const uint4*>(rv)[i];
+    }
+  }
+  bf16 sv[8 * (KW - 1)];
+#pragma unroll
+  for (int ch = 0; ch < 8; ++ch)
+#pragma unroll
+    for (int k = 0; k < KW - 1; ++k) sv[ch * (KW - 1) + k] = __float2bfloat16(win[ch][k]);
+#pragma unroll
+  for (int i = 0; i < (KW - 1); ++i) reinterpret_cast<uint4*>(st)[i] = reinterpret_cast<const uint4*>(sv)[i];
 }
 
 // ------------------------------------------------------------------ delta-rule step
@@ -249,8 +276,9 @@ extern "C" int b200_gdn_decode(const void* mixed, int ld, const int* slots, void
   if (B <= 0) return 0;
   const int key_dim = HK * DK, value_dim = HV * DV, C = 2 * key_dim + value_dim;
   if (KW != 4) return -7;
-  dim3 cgrid((C + 127) / 128, B);
-  gdn_conv_step_kernel<4><<<cgrid, 128, 0, st>>>(static_cast<const bf16*>(mixed), ld, slots,
+  if (C % 8 || ld % 8) return -7;
+  dim3 cgrid((C / 8 + 63) / 64, B);
+  gdn_conv_step_kernel<4><<<cgrid, 64, 0, st>>>(static_cast<const bf16*>(mixed), ld, slots,
                                                  static_cast<bf16*>(conv_state), static_cast<const bf16*>(conv_w),
                                                  static_cast<bf16*>(conv_out), static_cast<bf16*>(ring_conv), C, G);
   dim3 grid(HV, B);

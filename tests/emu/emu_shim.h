@@ -25,6 +25,7 @@
 namespace b200 {
 
 struct Dim3 { unsigned x = 1, y = 1, z = 1; };
+struct alignas(16) uint4 { unsigned x, y, z, w; };
 inline thread_local Dim3 threadIdx, blockIdx;
 inline Dim3 blockDim, gridDim;
 inline std::barrier<>* cta_barrier = nullptr;
