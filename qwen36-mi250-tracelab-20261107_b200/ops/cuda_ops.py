@@ -414,7 +414,7 @@ def flash_prefill(q: torch.Tensor, gate: torch.Tensor, kv_layer: torch.Tensor, b
     return out
 
 
-SPLIT_PAGES = 8  # pages (512 tokens) of context per decode-attention CTA: fixed, part of the numerics contract
+SPLIT_PAGES = int(__import__("os").environ.get("ENGINE_ATTN_SPLIT_PAGES", "8"))  # pages (64 tokens each) of context per decode-attention CTA: fixed for a server's lifetime, part of the numerics contract
 _decode_tiles: dict = {}
 
 
