@@ -98,7 +98,7 @@ def follower_main(argv: list[str] | None = None) -> None:
     cfg = EngineConfig.from_env(
         model=args.model, max_model_len=args.max_model_len, prefill_chunk_tokens=args.prefill_chunk_tokens,
         prefix_cache_tokens=args.prefix_cache_tokens, prefix_cache_entries=args.prefix_cache_entries,
-        prefix_cache_gib=args.prefix_cache_gib, max_seqs=args.max_seqs, mtp=False,
+        prefix_cache_gib=args.prefix_cache_gib, max_seqs=args.max_seqs,
     )
     engine = build_engine(args.model, args.rank, args.world, dev, cpu_group, cfg)
     print(f"engine: rank {args.rank}/{args.world} ready on {dev}", flush=True)
@@ -111,7 +111,6 @@ def leader_engine(model_dir: str, world: int, cuda: bool, engine_cfg, cfg_args: 
     followers = start_followers(model_dir, world, port, cuda, cfg_args)
     try:
         dev, cpu_group = init_rank(0, world, port, cuda)
-        engine_cfg.mtp = False  # speculation inside a TP replica is not wired yet
         engine = build_engine(model_dir, 0, world, dev, cpu_group, engine_cfg)
     except BaseException:
         for p in followers:

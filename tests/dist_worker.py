@@ -126,6 +126,24 @@ def mode_tp_model(rank, world, dev):
             from b200serve.ops import cuda_ops
 
             cuda_ops.check_errors(dev)
+    # MTP speculation inside the sharded replica: every rank drafts, verifies and accepts identically, and the outputs
+    # stay those of plain decoding
+    import dataclasses
+
+    for name, comm in comms.items():
+        eng = Engine(shard_weights(full, rank, world), dataclasses.replace(ecfg, mtp=True, spec_k=2, spec_kmax=2),
+                     tp=TPContext(rank, world, comm))
+        got = [x.output for x in eng.generate(prompts, s)]
+        mine = torch.tensor(got, device=dev)
+        allr = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        assert all(torch.equal(allr[0], t) for t in allr), name
+        same = sum(a == b for x, y in zip(got, ref) for a, b in zip(x, y))
+        assert eng.stats["mtp_verify_steps"] > 0
+        assert same >= ((0.9 if world == 2 else 0.7) if cuda else 1.0) * sum(len(x) for x in ref), (name, same)
+        if rank == 0:
+            print(f"tp_model[{name} + mtp] world={world}: {same} tokens equal, {eng.stats['mtp_verify_steps']} verify steps, "
+                  f"graphs={'on' if getattr(eng.spec, '_vgraphs', None) is not None else 'off'}", flush=True)
     if cuda:
         # prefill passes of >= 512 rows take the sequence-parallel kernels (GEMM -> reduce-scatter, norm + all-gather
         # push, shard-gated GEMM): same hidden states as the all-reduce path of the same sharded model

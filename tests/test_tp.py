@@ -65,6 +65,28 @@ def test_lockstep_replica_on_two_cpu_ranks():
     assert r.returncode == 0 and "OK lockstep" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
+def test_served_tensor_parallel_replica_speculates_like_a_single_process(tmp_path):
+    """MTP speculation inside a leader + follower replica: same tokens as a single-process server without it."""
+    from http_util import ServerProc, ids_of
+
+    from b200serve.models.tiny import write_tiny_checkpoint
+
+    write_tiny_checkpoint(tmp_path, lm_head_std=0.5)
+    tp = ServerProc(tmp_path, extra=["--gpus-per-replica", "2"], env={"CUDA_VISIBLE_DEVICES": "", "ENGINE_MTP": "1", "ENGINE_SPEC_K": "2"})
+    one = ServerProc(tmp_path, env={"CUDA_VISIBLE_DEVICES": "", "ENGINE_MTP": "0"})
+    try:
+        for n in (40, 130):
+            prompt = [7 + (i * 13) % 500 for i in range(n)]
+            a, _ = tp.completion(prompt, 16)
+            b, _ = one.completion(prompt, 16)
+            assert ids_of(a) == ids_of(b)
+        h = tp.health()
+        assert h.get("mtp_verify_steps", 0) > 0
+    finally:
+        tp.stop()
+        one.stop()
+
+
 def test_served_tensor_parallel_replica_on_cpu_ranks(tmp_path):
     """`--gpus-per-replica 2` on a machine without GPUs: leader + follower processes over gloo, over HTTP."""
     from http_util import ServerProc, ids_of
