@@ -83,6 +83,40 @@ __global__ void gdn_conv_step_kernel(const bf16* mixed, int ld, const int* slots
   for (int i = 0; i < (KW - 1); ++i) reinterpret_cast<uint4*>(st)[i] = reinterpret_cast<const uint4*>(sv)[i];
 }
 
+// One channel per thread: for channel counts or row strides that are not multiples of 8 (odd tensor-parallel shards).
+template <int KW>
+__global__ void gdn_conv_step_scalar_kernel(const bf16* mixed, int ld, const int* slots, bf16* conv_state, const bf16* conv_w,
+                                     bf16* out, bf16* ring_conv, int C, int G) {
+  const int b = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int slot = slots[b];
+  bf16* st = conv_state + (static_cast<size_t>(slot) * C + c) * (KW - 1);
+  float win[KW];
+  float w[KW];
+#pragma unroll
+  for (int k = 0; k < KW - 1; ++k) win[k] = __bfloat162float(st[k]);
+#pragma unroll
+  for (int k = 0; k < KW; ++k) w[k] = __bfloat162float(conv_w[c * KW + k]);
+  for (int j = 0; j < G; ++j) {
+    const size_t row = static_cast<size_t>(b) * G + j;
+    win[KW - 1] = __bfloat162float(mixed[row * ld + c]);
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < KW; ++k) acc += win[k] * w[k];
+    out[row * C + c] = __float2bfloat16(silu_f(acc));
+#pragma unroll
+    for (int k = 0; k < KW - 1; ++k) win[k] = win[k + 1];
+    if (ring_conv) {
+      bf16* r = ring_conv + ((static_cast<size_t>(b) * G + j) * C + c) * (KW - 1);
+#pragma unroll
+      for (int k = 0; k < KW - 1; ++k) r[k] = __float2bfloat16(win[k]);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < KW - 1; ++k) st[k] = __float2bfloat16(win[k]);
+}
+
 // ------------------------------------------------------------------ delta-rule step
 // The DK x DV fp32 state tile of one (sequence, value head) is brought into shared memory by one bulk
 // async copy (TMA, no registers held while it is in flight), updated in place for the G rows of the step,
@@ -276,11 +310,15 @@ extern "C" int b200_gdn_decode(const void* mixed, int ld, const int* slots, void
   if (B <= 0) return 0;
   const int key_dim = HK * DK, value_dim = HV * DV, C = 2 * key_dim + value_dim;
   if (KW != 4) return -7;
-  if (C % 8 || ld % 8) return -7;
-  dim3 cgrid((C / 8 + 63) / 64, B);
-  gdn_conv_step_kernel<4><<<cgrid, 64, 0, st>>>(static_cast<const bf16*>(mixed), ld, slots,
-                                                 static_cast<bf16*>(conv_state), static_cast<const bf16*>(conv_w),
-                                                 static_cast<bf16*>(conv_out), static_cast<bf16*>(ring_conv), C, G);
+  if (C % 8 || ld % 8) {
+    gdn_conv_step_scalar_kernel<4><<<dim3((C + 127) / 128, B), 128, 0, st>>>(
+        static_cast<const bf16*>(mixed), ld, slots, static_cast<bf16*>(conv_state), static_cast<const bf16*>(conv_w),
+        static_cast<bf16*>(conv_out), static_cast<bf16*>(ring_conv), C, G);
+  } else {
+    gdn_conv_step_kernel<4><<<dim3((C / 8 + 63) / 64, B), 64, 0, st>>>(
+        static_cast<const bf16*>(mixed), ld, slots, static_cast<bf16*>(conv_state), static_cast<const bf16*>(conv_w),
+        static_cast<bf16*>(conv_out), static_cast<bf16*>(ring_conv), C, G);
+  }
   dim3 grid(HV, B);
   const int z_off = C, b_off = C + value_dim, a_off = C + value_dim + HV;
 #define LAUNCH_STEP(DKV)                                                                                           \
