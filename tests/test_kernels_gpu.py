@@ -145,7 +145,7 @@ def _gdn_setup(cfg_dims, B, G, seed):
 
 
 @pytest.mark.parametrize("dims,B,G", [((2, 4, 32, 32), 3, 1), ((16, 32, 128, 128), 5, 1), ((16, 32, 128, 128), 2, 4),
-                                      ((2, 4, 32, 32), 4, 3)])
+                                      ((2, 4, 32, 32), 4, 3), ((1, 2, 32, 32), 3, 2)])  # the last: row stride 196, not a multiple of 8
 def test_gdn_decode(C, O, dims, B, G):
     mixed, slots, conv, rec, args = _gdn_setup(dims, B, G, seed=20)
     n_v, dk, dv = dims[1], dims[2], dims[3]
