@@ -52,7 +52,7 @@ struct FlashCfg {
   static constexpr int KV_BYTES = DB * FP_PAGE * 128;  // one of K or V, one stage
   static constexpr int P_BYTES = 128 * 128;
   static constexpr int SMEM = Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024 + 256;
-  static constexpr int TMEM_COLS = (64 + D) <= 128 ? 128 : (64 + D) <= 256 ? 256 : 512;
+  static constexpr int TMEM_COLS = (128 + D) <= 256 ? 256 : 512;  // two score tiles of 64 columns + the output
 };
 
 template <int D, int GROUP>
@@ -71,10 +71,10 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;                // [2]
   uint64_t* kv_empty = bars + 3;               // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* p_full = bars + 6;
-  uint64_t* acc_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* s_full = bars + 5;                 // [2]: one per score tile
+  uint64_t* p_full = bars + 7;
+  uint64_t* acc_done = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -101,7 +101,8 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(s_full, 1);
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
     mbar_init(p_full, 128);
     mbar_init(acc_done, 1);
     *abort_flag = 0;
@@ -114,7 +115,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_S = tmem, tmem_O = tmem + 64;
+  const uint32_t tmem_S = tmem, tmem_O = tmem + 128;  // score tile of page i at tmem_S + (i & 1) * 64
 
   if (warp == 4) {
     if (elect_one()) {
@@ -136,34 +137,45 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (np > 1) load_page(1);
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 64);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, D) | (1u << 16);  // B operand MN-major
+      // Software pipeline: Q K^T of page i + 1 is issued before the wait for the probabilities of page i, into the
+      // other score tile, so the tensor pipe works on the next scores while the softmax threads are busy.
       bool ok = mbar_wait(q_full, 0, p.err, ERR_WAIT_FULL, abort_flag);
-      for (int i = 0; i < np && ok; ++i) {
+      const uint32_t qa = smem_u32(sQ);
+      auto issue_qk = [&](int i) {
         const int s = i & 1;
-        ok = mbar_wait(&kv_full[s], (i >> 1) & 1, p.err, ERR_WAIT_FULL, abort_flag);
-        if (!ok) break;
+        if (!mbar_wait(&kv_full[s], (i >> 1) & 1, p.err, ERR_WAIT_FULL, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * C::KV_BYTES), va = smem_u32(sV + s * C::KV_BYTES);
+        const uint32_t ka = smem_u32(sK + s * C::KV_BYTES);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t blk = kk >> 2, koff = (kk & 3) * 32;
-          umma_bf16(tmem_S, umma_smem_desc(qa + blk * 128 * 128 + koff), umma_smem_desc(ka + blk * FP_PAGE * 128 + koff),
-                    idesc_qk, kk != 0);
+          umma_bf16(tmem_S + s * 64, umma_smem_desc(qa + blk * 128 * 128 + koff),
+                    umma_smem_desc(ka + blk * FP_PAGE * 128 + koff), idesc_qk, kk != 0);
         }
-        umma_commit(s_full);
-        if (i >= 1 && i + 1 < np) {  // the stage of page i-1 is free once its P.V has finished
-          ok = mbar_wait(&kv_empty[(i - 1) & 1], ((i - 1) >> 1) & 1, p.err, ERR_WAIT_EMPTY, abort_flag);
+        umma_commit(&s_full[s]);
+        return true;
+      };
+      ok = ok && issue_qk(0);
+      for (int i = 0; i < np && ok; ++i) {
+        const int s = i & 1;
+        if (i + 1 < np) {
+          ok = issue_qk(i + 1);  // its score tile was last read by the softmax of page i - 1, which has arrived at p_full
           if (!ok) break;
-          load_page(i + 1);
         }
         ok = mbar_wait(p_full, i & 1, p.err, ERR_WAIT_FULL, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t pa = smem_u32(sP);
+        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + s * C::KV_BYTES);
 #pragma unroll
         for (int kk = 0; kk < FP_PAGE / 16; ++kk)
           umma_bf16(tmem_O, umma_smem_desc(pa + kk * 32), umma_smem_desc_mn(va + kk * 2048, FP_PAGE * 128), idesc_pv,
                     (i | kk) != 0);
         umma_commit(&kv_empty[s]);
+        if (i + 2 < np) {  // the stage of page i is free once its P.V has finished
+          ok = mbar_wait(&kv_empty[s], (i >> 1) & 1, p.err, ERR_WAIT_EMPTY, abort_flag);
+          if (!ok) break;
+          load_page(i + 2);
+        }
       }
       umma_commit(acc_done);
     }
@@ -177,12 +189,12 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     for (int i = 0; i < np && ok; ++i) {
-      ok = mbar_wait(s_full, i & 1, p.err, ERR_WAIT_TMEM, abort_flag);
+      ok = mbar_wait(&s_full[i & 1], (i >> 1) & 1, p.err, ERR_WAIT_TMEM, abort_flag);
       if (!ok) break;
       tc_fence_after();
       float sc[64];
 #pragma unroll
-      for (int c = 0; c < 64; c += 16) tmem_ld16(tmem_S + lane_base + c, sc + c);
+      for (int c = 0; c < 64; c += 16) tmem_ld16(tmem_S + (i & 1) * 64 + lane_base + c, sc + c);
       float mx = -INFINITY;
       const int kbase = (first + i) * FP_PAGE;
 #pragma unroll
@@ -191,6 +203,13 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         mx = fmaxf(mx, sc[j]);
       }
       const bool need = mx > m_used + 8.0f;
+      // the scores of this page were computed while P.V of the previous page may still be running: the output tile and
+      // the probability tile may only be touched once that MMA has finished
+      if (i > 0) {
+        ok = mbar_wait(&kv_empty[(i - 1) & 1], ((i - 1) >> 1) & 1, p.err, ERR_WAIT_EMPTY, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+      }
       if (__any_sync(0xffffffffu, need)) {  // warp-uniform: TMEM loads/stores are warp-collective
         const float factor = need ? exp2f(m_used - mx) : 1.0f;  // exp2(-inf) = 0 on the first page
         if (need) { m_used = mx; l *= factor; }
