@@ -50,31 +50,38 @@ struct FlashCfg {
   static constexpr int DB = D / 64;             // 64-element (128-byte) blocks along the head dim
   static constexpr int Q_BYTES = DB * 128 * 128;
   static constexpr int KV_BYTES = DB * FP_PAGE * 128;  // one of K or V, one stage
-  static constexpr int P_BYTES = 128 * 128;
-  static constexpr int SMEM = Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024 + 256;
+  static constexpr int P_BYTES = 128 * 128;  // one probability tile; two are kept
+  // dynamic shared memory is declared 1024-byte aligned (checked at run time), so no alignment slack is budgeted:
+  // with D = 256 the tiles, the barriers and the 2 KB of static exchange arrays fill the 227 KB of an SM
+  static constexpr int SMEM = Q_BYTES + 4 * KV_BYTES + 2 * P_BYTES + 256;
   static constexpr int TMEM_COLS = (128 + D) <= 256 ? 256 : 512;  // two score tiles of 64 columns + the output
 };
 
 template <int D, int GROUP>
-__global__ void __launch_bounds__(160, 1)
+__global__ void __launch_bounds__(288, 1)
 flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKV, FlashParams p) {
   using C = FlashCfg<D>;
   constexpr int DB = C::DB;
   constexpr int R = 128 / GROUP;  // query positions per tile
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {  // the swizzled tiles need this alignment; leave with a status rather than compute garbage
+    if (threadIdx.x == 0) atomicCAS(p.err, 0, ERR_BAD_INDEX);
+    return;
+  }
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + C::Q_BYTES;               // [2 stages][DB][64 x 128 B]
   uint8_t* sV = sK + 2 * C::KV_BYTES;
-  uint8_t* sP = sV + 2 * C::KV_BYTES;          // [128 x 128 B]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::P_BYTES);
+  uint8_t* sP = sV + 2 * C::KV_BYTES;          // [2][128 x 128 B]: page i uses tile i & 1
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * C::P_BYTES);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;                // [2]
   uint64_t* kv_empty = bars + 3;               // [2]
   uint64_t* s_full = bars + 5;                 // [2]: one per score tile
   uint64_t* p_full = bars + 7;
   uint64_t* acc_done = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* x_bar = bars + 9;                  // exchange point of the 256 softmax threads (bounded wait, unlike bar.sync)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -103,21 +110,22 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 256);
     mbar_init(acc_done, 1);
+    mbar_init(x_bar, 256);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmKV);
   }
-  if (warp == 4) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
+  if (warp == 8) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tmem_S = tmem, tmem_O = tmem + 128;  // score tile of page i at tmem_S + (i & 1) * 64
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (elect_one()) {
       auto load_page = [&](int i) {
         const int s = i & 1;
@@ -165,7 +173,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         ok = mbar_wait(p_full, i & 1, p.err, ERR_WAIT_FULL, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + s * C::KV_BYTES);
+        const uint32_t pa = smem_u32(sP + s * C::P_BYTES), va = smem_u32(sV + s * C::KV_BYTES);
 #pragma unroll
         for (int kk = 0; kk < FP_PAGE / 16; ++kk)
           umma_bf16(tmem_O, umma_smem_desc(pa + kk * 32), umma_smem_desc_mn(va + kk * 2048, FP_PAGE * 128), idesc_pv,
@@ -180,55 +188,71 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       umma_commit(acc_done);
     }
   } else {
-    // ---------------- softmax + epilogue: thread r owns TMEM lane r = one (position, head) row
-    const int r = threadIdx.x;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    // ---------------- softmax + epilogue: 256 threads, two per TMEM lane. Thread (r = tid & 127, hf = tid >> 7) owns
+    // row r = one (position, head) and the half hf of everything indexed by a column: 32 of the page's 64 scores,
+    // half of the output columns. The two halves of a row agree on the row maximum through shared memory, so both
+    // take the same rescale decision; their partial row sums are added (half 0 + half 1) at the end.
+    __shared__ float s_mx[2][2][128];  // [page parity][half][row]; reused for the row sums at the end
+    const int r = threadIdx.x & 127, hf = threadIdx.x >> 7;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int lp = r / GROUP, head = r % GROUP;
     const int qpos = pos0 + p0 + lp;
     const bool row_valid = lp < n_pos;
+    constexpr int DH = D / 2;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     for (int i = 0; i < np && ok; ++i) {
       ok = mbar_wait(&s_full[i & 1], (i >> 1) & 1, p.err, ERR_WAIT_TMEM, abort_flag);
       if (!ok) break;
       tc_fence_after();
-      float sc[64];
+      float sc[32];
 #pragma unroll
-      for (int c = 0; c < 64; c += 16) tmem_ld16(tmem_S + (i & 1) * 64 + lane_base + c, sc + c);
+      for (int c = 0; c < 32; c += 16) tmem_ld16(tmem_S + (i & 1) * 64 + hf * 32 + lane_base + c, sc + c);
       float mx = -INFINITY;
-      const int kbase = (first + i) * FP_PAGE;
+      const int kbase = (first + i) * FP_PAGE + hf * 32;
 #pragma unroll
-      for (int j = 0; j < 64; ++j) {
+      for (int j = 0; j < 32; ++j) {
         sc[j] = (kbase + j <= qpos) ? sc[j] * p.scale_log2 : -INFINITY;
         mx = fmaxf(mx, sc[j]);
       }
+      s_mx[i & 1][hf][r] = mx;
+      mbar_arrive(x_bar);
+      ok = mbar_wait(x_bar, i & 1, p.err, ERR_WAIT_FULL, abort_flag);
+      if (!ok) break;
+      mx = fmaxf(mx, s_mx[i & 1][hf ^ 1][r]);
       const bool need = mx > m_used + 8.0f;
-      // the scores of this page were computed while P.V of the previous page may still be running: the output tile and
-      // the probability tile may only be touched once that MMA has finished
-      if (i > 0) {
+      // The scores of this page were computed while P.V of the previous page may still be running. This page's
+      // probability tile was last read by P.V of page i - 2; the output tile may only be rescaled once P.V of page
+      // i - 1 has finished, which is waited for only in the (rare, after the first pages) case of a rescale.
+      if (i >= 2) {
+        ok = mbar_wait(&kv_empty[i & 1], ((i - 2) >> 1) & 1, p.err, ERR_WAIT_EMPTY, abort_flag);
+        if (!ok) break;
+      }
+      const bool any_need = __any_sync(0xffffffffu, need);
+      if (any_need && i > 0) {
         ok = mbar_wait(&kv_empty[(i - 1) & 1], ((i - 1) >> 1) & 1, p.err, ERR_WAIT_EMPTY, abort_flag);
         if (!ok) break;
         tc_fence_after();
       }
-      if (__any_sync(0xffffffffu, need)) {  // warp-uniform: TMEM loads/stores are warp-collective
+      if (any_need) {  // warp-uniform: TMEM loads/stores are warp-collective
         const float factor = need ? exp2f(m_used - mx) : 1.0f;  // exp2(-inf) = 0 on the first page
         if (need) { m_used = mx; l *= factor; }
         if (i > 0) {
 #pragma unroll 1
-          for (int c = 0; c < D; c += 16) {
+          for (int c = 0; c < DH; c += 16) {
             float o[16];
-            tmem_ld16(tmem_O + lane_base + c, o);
+            tmem_ld16(tmem_O + lane_base + hf * DH + c, o);
 #pragma unroll
             for (int j = 0; j < 16; ++j) o[j] *= factor;
-            tmem_st16(tmem_O + lane_base + c, o);
+            tmem_st16(tmem_O + lane_base + hf * DH + c, o);
           }
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
       float sum = 0.f;
-      uint8_t* prow = sP + r * 128;
+      uint8_t* prow = sP + (i & 1) * C::P_BYTES + r * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint4 packed;
         __nv_bfloat162* pe = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
@@ -237,7 +261,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           sum += a + b2;
           pe[j] = __floats2bfloat162_rn(a, b2);
         }
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) * 16)) = packed;  // 128-byte swizzle of the K-major tile
+        *reinterpret_cast<uint4*>(prow + (((hf * 4 + c) ^ (r & 7)) * 16)) = packed;  // 128-byte swizzle of the K-major tile
       }
       l += sum;
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -246,11 +270,18 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     ok = ok && mbar_wait(acc_done, 0, p.err, ERR_WAIT_TMEM, abort_flag) && !*abort_flag;
     tc_fence_after();
+    if (ok) {
+      // every thread has read its partner's last maximum (it arrived at p_full afterwards, and acc_done follows that)
+      s_mx[0][hf][r] = l;
+      mbar_arrive(x_bar);
+      ok = mbar_wait(x_bar, np & 1, p.err, ERR_WAIT_FULL, abort_flag);
+      l = s_mx[0][0][r] + s_mx[0][1][r];
+    }
     if (ok && p.split_pages > 0) {
       const size_t row = static_cast<size_t>(seg_row0 + p0 + lp);
       const size_t slot = (row * p.n_q + kh * GROUP + head) * gridDim.z + blockIdx.z;
 #pragma unroll 1
-      for (int c = 0; c < D; c += 16) {
+      for (int c = hf * DH; c < hf * DH + DH; c += 16) {
         float o[16];
         tmem_ld16(tmem_O + lane_base + c, o);  // warp-collective: never predicated
         if (row_valid) {
@@ -259,7 +290,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int j = 0; j < 4; ++j) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
         }
       }
-      if (row_valid) {
+      if (row_valid && hf == 0) {
         p.part_ml[slot * 2] = m_used * 0.6931471805599453f;  // log2 units -> natural log, as the combine expects
         p.part_ml[slot * 2 + 1] = l;
       }
@@ -269,7 +300,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const size_t row = static_cast<size_t>(seg_row0 + p0 + lp);
       const size_t base = row * (static_cast<size_t>(p.n_q) * D) + static_cast<size_t>(kh * GROUP + head) * D;
 #pragma unroll 1
-      for (int c = 0; c < D; c += 16) {
+      for (int c = hf * DH; c < hf * DH + DH; c += 16) {
         float o[16];
         tmem_ld16(tmem_O + lane_base + c, o);  // warp-collective: never predicated
         if (row_valid) {
@@ -292,7 +323,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) { tc_fence_after(); tmem_dealloc(tmem, C::TMEM_COLS); }
+  if (warp == 8) { tc_fence_after(); tmem_dealloc(tmem, C::TMEM_COLS); }
 }
 
 }  // namespace b200
@@ -331,7 +362,7 @@ int fp_launch(const CUtensorMap& tq, const CUtensorMap& tkv, const FlashParams& 
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashCfg<D>::SMEM) != cudaSuccess) return -3;
     configured = true;
   }
-  kern<<<dim3(n_tiles, p.n_kv, gz), 160, FlashCfg<D>::SMEM, st>>>(tq, tkv, p);
+  kern<<<dim3(n_tiles, p.n_kv, gz), 288, FlashCfg<D>::SMEM, st>>>(tq, tkv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 }  // namespace
