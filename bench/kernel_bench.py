@@ -193,6 +193,25 @@ def case_gdn_prefill(small):
     report(f"gdn_prefill_{nseg}x{L}", us, mixed.numel() * 2 + T * n_v * dv * 2, flops, tensor_cores=C.GDN_PREFILL_TC)
 
 
+def case_attn_prefill(small):
+    """Causal gated flash attention of one prefill pass over the paged KV: one 8192-token sequence (or 8 x 1024 with
+    --small), 16 Q / 2 KV heads, D = 256 (prep kernel + flash kernel)."""
+    nseg, L = (8, 1024) if small else (1, 8192)
+    n_q, n_kv, D = 16, 2, 256
+    T = nseg * L
+    pp = L // 64 + 1
+    kv = bf(nseg * pp + 1, 2, n_kv, 64, D)
+    tables = torch.arange(nseg * pp, dtype=torch.int32, device="cuda").view(nseg, pp) + 1
+    qkv = bf(T, n_q * 2 * D + 2 * n_kv * D)
+    pos = torch.arange(L, dtype=torch.int64, device="cuda").repeat(nseg)
+    seq = torch.repeat_interleave(torch.arange(nseg, dtype=torch.int32, device="cuda"), L)
+    qn, kn = bf(D, scale=0.1), bf(D, scale=0.1)
+    starts = [i * L for i in range(nseg + 1)]
+    us = timed(lambda: C.attention(qkv, pos, seq, tables, kv, qn, kn, n_q, n_kv, D, 64, 1e7, 1e-6, 0, starts, [0] * nseg), iters=5)
+    flops = 4 * nseg * (L * (L + 1) // 2) * n_q * D
+    report(f"attn_prefill_{nseg}x{L}", us, qkv.numel() * 2 + T * n_q * D * 2, flops)
+
+
 CASES = {k[5:]: v for k, v in globals().items() if k.startswith("case_")}
 
 if __name__ == "__main__":
