@@ -39,7 +39,7 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=128, help="concurrent requests per GPU")
     ap.add_argument("--prompt-len", type=int, default=1024)
-    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp_ep"])
+    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp_ep", "dp_ep"])
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (result marked invalid)")
     ap.add_argument("--mtp", type=int, default=0, help="MTP draft depth (0 = plain decode)")
     return ap.parse_args()
@@ -139,7 +139,8 @@ def main() -> None:
 
     mcfg = ModelConfig.qwen36_35b_a3b() if not args.layers else ModelConfig(num_hidden_layers=args.layers)
     tp_mode = args.parallelism == "tp_ep" and world > 1
-    tp_ctx = None
+    ep_mode = args.parallelism == "dp_ep" and world > 1
+    tp_ctx = ep_ctx = None
     if tp_mode:  # one replica over all ranks: same weights and the same requests everywhere, sharded TP + EP
         from b200serve.parallel.tp import FusedComm, TPContext, shard_weights
 
@@ -148,6 +149,17 @@ def main() -> None:
         del full
         torch.cuda.empty_cache()
         tp_ctx = TPContext(rank, world, FusedComm(dev, dist.group.WORLD, slot_elems=1 << 21, max_blocks=4096))
+    elif ep_mode:
+        # data-parallel attention + expert-parallel MoE: every rank serves its own B requests with full dense weights
+        # and 1 / world of the routed experts; rows travel to their experts and back inside every MoE block
+        # (parallel/ep.py). All ranks run identical schedules here, so their forward passes pair up.
+        from b200serve.parallel.ep import EpMoE, shard_experts
+
+        full = random_weights(mcfg, seed=1234, device=dev, dtype=torch.bfloat16)
+        weights = shard_experts(full, rank, world)
+        del full
+        torch.cuda.empty_cache()
+        ep_ctx = EpMoE(dev, dist.group.WORLD, mcfg.num_experts, mcfg.hidden_size, mcfg.num_experts_per_tok, max_rows=8192)
     else:
         weights = random_weights(mcfg, seed=1234 + rank, device=dev, dtype=torch.bfloat16)
     total_out = K + max(W, 3) + 64 + (B * P) // 4096  # room for the tokens decoded while later prompts prefill
@@ -156,7 +168,9 @@ def main() -> None:
         prefill_pack_tokens=8192, kv_pages=B * ((P + 2 * total_out) // 64 + 2) + 2, mtp=bool(args.mtp),
         spec_k=args.mtp, decode_buckets=(B,),
     )
-    engine = Engine(weights, ecfg, tp=tp_ctx)
+    if ep_mode:
+        ecfg.mtp = False
+    engine = Engine(weights, ecfg, tp=tp_ctx, ep=ep_ctx)
     replicas = 1 if tp_mode else world  # independent request streams in the job
 
     def run_phase(timed_steps: int, warm: int, e2e: bool):

@@ -70,10 +70,14 @@ class PackedBatch:
 
 class Model:
     def __init__(self, weights: Weights, num_pages: int, state_slots: int, ops=None,
-                 kv_dtype: torch.dtype | None = None, tp=None) -> None:
+                 kv_dtype: torch.dtype | None = None, tp=None, ep=None) -> None:
         """``weights`` may be one rank's shard (``parallel.tp.shard_weights``); then ``tp`` names the rank
-        group and every mixer / MoE output is summed across it."""
+        group and every mixer / MoE output is summed across it. ``ep`` (a ``parallel.ep.EpMoE``) selects data-parallel
+        attention with expert-parallel MoE instead: this rank serves its own rows with full dense weights, holds only
+        its share of the routed experts (``parallel.ep.shard_experts``) and exchanges rows with the other ranks inside
+        every MoE block, so all ranks must run their forward passes in step."""
         self.tp = tp
+        self.ep = ep
         self.w = weights
         self.cfg: ModelConfig = weights.config
         self.ops = ops or torch_ops
@@ -130,6 +134,8 @@ class Model:
     # ------------------------------------------------------------------ blocks
     def _moe(self, lw: LayerWeights, x: torch.Tensor) -> torch.Tensor:
         cfg, ops = self.cfg, self.ops
+        if self.ep is not None:  # token-sharded expert parallelism: all-to-all dispatch / combine over peer memory
+            return self.ep.forward(x, lw.router, lw.w_gate_up, lw.w_down)
         if self.tp is not None:  # expert parallel: local experts only, partial sums meet in the all-reduce
             part = ops.moe_block(x, lw.router, lw.w_gate_up, lw.w_down, cfg.num_experts, cfg.num_experts_per_tok,
                                  True, expert_map=lw.expert_map, partial_f32=True)

@@ -175,3 +175,28 @@ class EpMoE:
         for p in self._own.values():
             L.b200_symm_free(p)
         self._opened, self._own = [], {}
+
+
+def shard_experts(weights, rank: int, world: int):
+    """This rank's weights for data-parallel attention + expert-parallel MoE: everything dense stays whole, every
+    layer keeps only its ``E / world`` routed experts and a replica of the shared expert (stacked last), in the order
+    ``EpMoE`` expects. The MTP block is dropped (speculation is not combined with this mode)."""
+    import copy
+
+    from ..models.checkpoint import Weights
+
+    cfg = weights.config
+    E = cfg.num_experts
+    if E % world:
+        raise ValueError(f"{E} experts do not split over {world} ranks")
+    per = E // world
+    layers = []
+    for lw in weights.layers:
+        if not lw.shared_merged:
+            raise ValueError("expert parallelism needs the shared expert merged into the expert stack")
+        out = copy.copy(lw)
+        sel = torch.tensor(list(range(rank * per, (rank + 1) * per)) + [E], device=lw.w_gate_up.device)
+        out.w_gate_up = lw.w_gate_up[sel].contiguous()
+        out.w_down = lw.w_down[sel].contiguous()
+        layers.append(out)
+    return Weights(cfg, weights.embed, weights.lm_head, weights.final_norm, layers, None)

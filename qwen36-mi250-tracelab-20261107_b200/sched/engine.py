@@ -44,9 +44,11 @@ def _select_ops(device: torch.device):
 
 
 class Engine:
-    def __init__(self, weights: Weights, cfg: EngineConfig | None = None, ops=None, tp=None) -> None:
+    def __init__(self, weights: Weights, cfg: EngineConfig | None = None, ops=None, tp=None, ep=None) -> None:
         """``tp``: a ``parallel.tp.TPContext`` when ``weights`` is one rank's shard; all ranks of the group
-        then run the same engine on the same requests in lockstep."""
+        then run the same engine on the same requests in lockstep. ``ep``: a ``parallel.ep.EpMoE`` for data-parallel
+        attention with expert-parallel MoE: every rank serves its own requests, but all ranks must issue the same
+        sequence of forward passes (same number of prefill passes and decode steps), which the caller arranges."""
         self.cfg = cfg or EngineConfig()
         self.tp = tp
         self.coordinator = None  # parallel.lockstep.Coordinator in a multi-rank replica
@@ -59,7 +61,7 @@ class Engine:
         self.max_pages_per_seq = (self.max_model_len + PAGE_SIZE - 1) // PAGE_SIZE + 1
         n_slots = c.state_slots or (c.max_seqs * 2 + 2)
         n_pages = c.kv_pages or self._auto_pages(weights, n_slots)
-        self.model = Model(weights, n_pages, n_slots, ops=self.ops, tp=tp)
+        self.model = Model(weights, n_pages, n_slots, ops=self.ops, tp=tp, ep=ep)
         self.pages = PagePool(n_pages)
         self.slots = SlotPool(n_slots)
         page_bytes = self.model.kv[:, 0].numel() * self.model.kv.element_size()

@@ -369,8 +369,43 @@ def mode_seq_parallel(rank, world, dev):
     sp.close()
 
 
+def mode_dp_ep_model(rank, world, dev):
+    """Data-parallel attention + expert-parallel MoE: every rank serves its OWN requests through an engine that holds
+    1 / world of the routed experts; outputs must equal the unsharded engine's on the same requests."""
+    from b200serve.config import EngineConfig, ModelConfig
+    from b200serve.models.checkpoint import random_weights
+    from b200serve.ops import cuda_ops
+    from b200serve.parallel.ep import EpMoE, shard_experts
+    from b200serve.sched.engine import Engine
+    from b200serve.sched.request import Sampling
+
+    cfg = ModelConfig.tiny(num_experts=8)
+    full = random_weights(cfg, seed=0, device="cpu", dtype=torch.float32, std=0.05, lm_head_std=0.5).to(dev, torch.bfloat16)
+    g = torch.Generator().manual_seed(50 + rank)  # different requests on every rank, same shapes (ranks step together)
+    prompts = [torch.randint(3, 1024, (n,), generator=g).tolist() for n in (20, 70, 150, 33)]
+    s = Sampling(max_tokens=12, ignore_eos=True)
+    ecfg = EngineConfig(max_model_len=1024, prefill_chunk_tokens=64, max_seqs=4, mtp=False, kv_pages=128)
+    ref = [x.output for x in Engine(full, ecfg).generate(prompts, s)]
+    ep = EpMoE(dev, dist.group.WORLD, cfg.num_experts, cfg.hidden_size, cfg.num_experts_per_tok, max_rows=512)
+    for graphs in (False, True):
+        import dataclasses
+
+        eng = Engine(shard_experts(full, rank, world), dataclasses.replace(ecfg, cuda_graphs=graphs), ep=ep)
+        got = [x.output for x in eng.generate(prompts, s)]
+        cuda_ops.check_errors(dev)
+        same = sum(a == b for x, y in zip(got, ref) for a, b in zip(x, y))
+        total = sum(len(x) for x in ref)
+        t = torch.tensor([same], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            print(f"dp_ep_model world={world} graphs={graphs}: at least {t.item()}/{total} tokens equal the unsharded engine", flush=True)
+        assert same >= 0.9 * total and all(x[0] == y[0] for x, y in zip(got, ref)), (graphs, same, total)
+        dist.barrier()
+    ep.close()
+
+
 MODES = {"allreduce": mode_allreduce, "ep_moe": mode_ep_moe, "tp_model": mode_tp_model, "lockstep": mode_lockstep,
-         "seq_parallel": mode_seq_parallel}
+         "seq_parallel": mode_seq_parallel, "dp_ep_model": mode_dp_ep_model}
 
 if __name__ == "__main__":
     mode = sys.argv[1]

@@ -146,3 +146,14 @@ def test_two_rank_sequence_parallel_gemms():
                         "seq_parallel"], capture_output=True, text=True, timeout=600,
                        env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
     assert r.returncode == 0 and "OK seq_parallel" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_rank_data_parallel_attention_with_expert_parallel_moe():
+    import os
+
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29651", str(ROOT / "tests/dist_worker.py"),
+                        "dp_ep_model"], capture_output=True, text=True, timeout=600,
+                       env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
+    assert r.returncode == 0 and "OK dp_ep_model" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
