@@ -9,6 +9,12 @@ steps timed on the device with CUDA events (max over ranks). ``e2e`` is the same
 through the public engine API (``Engine.submit`` / ``Engine.step``): each step copies its inputs
 from pinned host memory to the device and reads the sampled tokens back.
 
+On several GPUs every rank serves its own ``--batch`` requests (weak scaling). ``--parallelism``: ``dp`` = independent
+replicas with all weights on every GPU; ``dp_ep`` (what ``auto`` picks for N > 1) = data-parallel attention / GDN with
+expert-parallel MoE: each GPU holds 1 / N of the routed experts and the rows of all ranks meet their experts through the
+fused dispatch / combine kernels over NVLink peer memory, so the expert weights streamed per GPU and step shrink with N;
+``tp_ep`` = ONE tensor + expert parallel replica over all GPUs serving one batch (strong scaling).
+
 With ``--impl reference`` the unmodified reference under ``baseline/_ref`` is run for the same
 metric, or a one-line reason is printed when it cannot run in this image.
 """
@@ -39,7 +45,9 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=128, help="concurrent requests per GPU")
     ap.add_argument("--prompt-len", type=int, default=1024)
-    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp_ep", "dp_ep"])
+    ap.add_argument("--parallelism", default="auto", choices=["auto", "dp", "tp_ep", "dp_ep"],
+                    help="auto: one GPU -> dp; several -> dp_ep (data-parallel attention, expert-parallel MoE over NVLink "
+                         "peer memory), falling back to independent dp replicas if its set-up or trial step fails")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (result marked invalid)")
     ap.add_argument("--mtp", type=int, default=0, help="MTP draft depth (0 = plain decode)")
     return ap.parse_args()
@@ -138,8 +146,11 @@ def main() -> None:
     B, P, K, W = args.batch, args.prompt_len, args.steps, args.warmup
 
     mcfg = ModelConfig.qwen36_35b_a3b() if not args.layers else ModelConfig(num_hidden_layers=args.layers)
-    tp_mode = args.parallelism == "tp_ep" and world > 1
-    ep_mode = args.parallelism == "dp_ep" and world > 1
+    mode = args.parallelism
+    if mode == "auto":
+        mode = "dp_ep" if world > 1 else "dp"
+    tp_mode = mode == "tp_ep" and world > 1
+    ep_mode = mode == "dp_ep" and world > 1
     tp_ctx = ep_ctx = None
     if tp_mode:  # one replica over all ranks: same weights and the same requests everywhere, sharded TP + EP
         from b200serve.parallel.tp import FusedComm, TPContext, shard_weights
@@ -172,6 +183,42 @@ def main() -> None:
         ecfg.mtp = False
     engine = Engine(weights, ecfg, tp=tp_ctx, ep=ep_ctx)
     replicas = 1 if tp_mode else world  # independent request streams in the job
+
+    def all_ranks_ok(ok: bool) -> bool:
+        t = torch.tensor([0 if ok else 1], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item() == 0
+
+    if ep_mode and args.parallelism == "auto":
+        # trial: one short request through prefill and a few decode steps on every rank; any failure anywhere (a
+        # bounded wait that ran out, an allocation) sends every rank to independent replicas instead
+        ok = True
+        try:
+            trial = engine.generate([[1 + (i % 5) for i in range(64)]], Sampling(max_tokens=4, ignore_eos=True))
+            cuda_ops.check_errors(dev)
+            ok = trial[0].done and len(trial[0].output) == 4
+        except Exception as e:  # noqa: BLE001
+            print(f"bench: dp_ep trial failed on rank {rank}: {e!r}", file=sys.stderr, flush=True)
+            ok = False
+        if not all_ranks_ok(ok):
+            if rank == 0:
+                print("bench: falling back to independent data-parallel replicas", file=sys.stderr, flush=True)
+            try:
+                cuda_ops.err_word(dev).zero_()
+            except Exception:  # noqa: BLE001
+                pass
+            try:
+                ep_ctx.close()
+            except Exception:  # noqa: BLE001
+                pass
+            del engine, weights, ep_ctx
+            import gc
+
+            gc.collect()
+            torch.cuda.empty_cache()
+            mode, ep_mode, ep_ctx = "dp", False, None
+            weights = random_weights(mcfg, seed=1234 + rank, device=dev, dtype=torch.bfloat16)
+            engine = Engine(weights, ecfg)
 
     def run_phase(timed_steps: int, warm: int, e2e: bool):
         """Prefill B fresh requests, run `warm` untimed decode steps, then time `timed_steps` steps."""
@@ -255,7 +302,7 @@ def main() -> None:
             "impl": "ours",
             "config": {
                 "model": "Qwen3.6-35B-A3B" + (f"[{args.layers} layers: INVALID]" if args.layers else ""),
-                "global_batch": B * replicas, "seq_len": P, "parallelism": f"{args.parallelism}{world}",
+                "global_batch": B * replicas, "seq_len": P, "parallelism": f"{mode}{world}",
                 "batch_per_gpu": B, "l2": "working set per step (weights + KV + GDN state) far exceeds the 126 MB L2",
                 "mtp_depth": args.mtp,
             },
