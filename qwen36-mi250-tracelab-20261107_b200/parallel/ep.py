@@ -80,24 +80,39 @@ class EpMoE:
             "epoch": 16,
         }
         self._own, self._opened = {}, []
+        def agree(ok: bool, what: str) -> None:
+            """Every rank raises if any rank failed, so that nobody is left waiting in the next collective."""
+            if self.world > 1:
+                t = torch.tensor([0 if ok else 1], device=device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+                ok = t.item() == 0
+            if not ok:
+                self.close()
+                raise RuntimeError(f"expert-parallel set-up failed on some rank: {what}")
+
         with torch.cuda.device(device):
+            ok = True
             for name, nbytes in sizes.items():
                 p = ctypes.c_void_p()
                 if L.b200_symm_alloc(ctypes.byref(p), nbytes):
-                    raise RuntimeError(f"symmetric allocation of {nbytes} bytes failed")
+                    ok = False
+                    break
                 self._own[name] = p.value
             torch.cuda.synchronize(device)
+            agree(ok, "symmetric allocation")
             peers = {k: [self._own[k]] * 1 for k in ("xs", "meta", "pair_out", "counts_all", "flags")}
             if self.world > 1:
-                handles = {}
+                handles, ok = {}, True
                 for name in peers:
                     buf = ctypes.create_string_buffer(64)
                     if L.b200_symm_export(self._own[name], buf):
-                        raise RuntimeError("cudaIpcGetMemHandle failed")
+                        ok = False
                     handles[name] = buf.raw
+                agree(ok, "cudaIpcGetMemHandle")
                 gathered: list = [None] * self.world
                 dist.all_gather_object(gathered, handles, group=group)
                 peers = {k: [] for k in peers}
+                ok = True
                 for r in range(self.world):
                     for name in peers:
                         if r == self.rank:
@@ -105,10 +120,12 @@ class EpMoE:
                             continue
                         p = ctypes.c_void_p()
                         if L.b200_symm_import(gathered[r][name], ctypes.byref(p)):
-                            raise RuntimeError(f"cudaIpcOpenMemHandle failed for rank {r}")
+                            ok = False
+                            peers[name].append(None)
+                            continue
                         peers[name].append(p.value)
                         self._opened.append(p.value)
-                dist.barrier(group=group)
+                agree(ok, "cudaIpcOpenMemHandle")
         ctx = EpCtx()
         for r in range(self.world):
             for name in peers:
@@ -170,9 +187,9 @@ class EpMoE:
     def close(self) -> None:
         L = _lib()
         torch.cuda.synchronize(self.device)
-        for p in self._opened:
+        for p in getattr(self, "_opened", []):
             L.b200_symm_close(p)
-        for p in self._own.values():
+        for p in getattr(self, "_own", {}).values():
             L.b200_symm_free(p)
         self._opened, self._own = [], {}
 
