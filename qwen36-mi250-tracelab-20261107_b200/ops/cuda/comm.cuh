@@ -39,10 +39,13 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-// Wait until *p reaches `want` (wrap-safe). Gives up after WAIT_CYCLES, records ERR_WAIT_PEER.
+// Wait until *p reaches `want` (wrap-safe). Gives up after WAIT_CYCLES, records ERR_WAIT_PEER. Once the error word
+// is set (by this wait or any earlier one of the step) every further wait gives up at once, so a step whose peer is
+// gone costs one timeout, not one per collective.
 __device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t want, int* err) {
   const long long t0 = clock64();
   while (static_cast<int32_t>(ld_acquire_sys(p) - want) < 0) {
+    if (err && *reinterpret_cast<volatile int*>(err) != 0) return false;
     if (clock64() - t0 > WAIT_CYCLES) {
       if (err) atomicCAS(err, 0, ERR_WAIT_PEER);
       return false;
