@@ -142,6 +142,9 @@ def main() -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        # NCCL only carries barriers and a few scalars here; keep it off NVLink multicast objects so that a rank that
+        # dies cannot fault its peers' GPUs through a bound multicast mapping
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
     B, P, K, W = args.batch, args.prompt_len, args.steps, args.warmup
 
