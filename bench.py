@@ -197,9 +197,10 @@ def main() -> None:
         # bounded wait that ran out, an allocation) sends every rank to independent replicas instead
         ok = True
         try:
-            trial = engine.generate([[1 + (i % 5) for i in range(64)]], Sampling(max_tokens=4, ignore_eos=True))
+            trial = engine.generate([[1 + ((i * (j + 3)) % 997) for i in range(200)] for j in range(8)],
+                                    Sampling(max_tokens=4, ignore_eos=True))
             cuda_ops.check_errors(dev)
-            ok = trial[0].done and len(trial[0].output) == 4
+            ok = all(t.done and len(t.output) == 4 for t in trial)
         except Exception as e:  # noqa: BLE001
             print(f"bench: dp_ep trial failed on rank {rank}: {e!r}", file=sys.stderr, flush=True)
             ok = False
