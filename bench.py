@@ -201,6 +201,8 @@ def main() -> None:
                                     Sampling(max_tokens=4, ignore_eos=True))
             cuda_ops.check_errors(dev)
             ok = all(t.done and len(t.output) == 4 for t in trial)
+            if os.environ.get("BENCH_FAIL_EP_TRIAL") == str(rank):  # exercises the fallback below
+                raise RuntimeError("trial failure requested")
         except Exception as e:  # noqa: BLE001
             print(f"bench: dp_ep trial failed on rank {rank}: {e!r}", file=sys.stderr, flush=True)
             ok = False
