@@ -150,6 +150,14 @@ __global__ void ep_signal_kernel(EpCtx c, int which) {
 __global__ void ep_wait_kernel(EpCtx c, int which) {
   if (threadIdx.x < c.world) wait_flag(c.flags[c.rank] + which * MAX_RANKS + threadIdx.x, c.epoch[0], c.err);
 }
+// Both in one launch: thread r releases towards rank r, then waits for rank r's release.
+__global__ void ep_signal_wait_kernel(EpCtx c, int which) {
+  if (threadIdx.x < c.world) {
+    __threadfence_system();
+    st_release_sys(c.flags[threadIdx.x] + which * MAX_RANKS + c.rank, c.epoch[0]);
+    wait_flag(c.flags[c.rank] + which * MAX_RANKS + threadIdx.x, c.epoch[0], c.err);
+  }
+}
 
 // out[t] = bf16(sum_j w[t, j] * pair_out[t * P + j]) in pair order, fp32 accumulation.
 __global__ void ep_combine_kernel(const bf16* pair_out, const float* wts, int P, int H, bf16* out) {
@@ -191,13 +199,11 @@ extern "C" int b200_ep_dispatch(const EpCtx* c, const void* x, const int* idx, c
                                 int n_pairs, int P, int H, cudaStream_t st) {
   if (n_pairs > 0)
     ep_dispatch_kernel<<<n_pairs, 128, 0, st>>>(*c, static_cast<const bf16*>(x), idx, send_base, cursors, P, H);
-  ep_signal_kernel<<<1, 32, 0, st>>>(*c, 1);
-  ep_wait_kernel<<<1, 32, 0, st>>>(*c, 1);
+  ep_signal_wait_kernel<<<1, 32, 0, st>>>(*c, 1);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 extern "C" int b200_ep_combine(const EpCtx* c, const float* wts, int T, int P, int H, void* out, cudaStream_t st) {
-  ep_signal_kernel<<<1, 32, 0, st>>>(*c, 2);
-  ep_wait_kernel<<<1, 32, 0, st>>>(*c, 2);
+  ep_signal_wait_kernel<<<1, 32, 0, st>>>(*c, 2);
   if (T > 0)
     ep_combine_kernel<<<T, 256, 0, st>>>(c->pair_out[c->rank], wts, P, H, static_cast<bf16*>(out));
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
