@@ -33,7 +33,7 @@ struct EpCtx {
 };
 
 // counts[Etot] -> counts_all[me] on every rank; then wait for all sources. One CTA. Also advances the epoch.
-__global__ void ep_counts_kernel(EpCtx c, const int* counts) {
+__device__ __forceinline__ void ep_counts_body(const EpCtx& c, const int* counts) {
   const int Etot = c.E + 1;
   __shared__ uint32_t s_e;
   if (threadIdx.x == 0) { s_e = c.epoch[0] + 1; c.epoch[0] = s_e; }
@@ -50,11 +50,17 @@ __global__ void ep_counts_kernel(EpCtx c, const int* counts) {
     wait_flag(c.flags[c.rank] + 0 * MAX_RANKS + threadIdx.x, e, c.err);
   }
 }
+__global__ void ep_counts_kernel(EpCtx c, const int* counts) { ep_counts_body(c, counts); }
 
 // One CTA of 1024 threads, Etot <= 1024. Outputs: send_base[Etot] (first position of my rows of expert e in
 // its host's buffer), cursors[Etot] = 0, local tile table, n_tiles, n_rows (rows this rank receives).
 __global__ void __launch_bounds__(1024)
-ep_plan_kernel(EpCtx c, int bt, int* send_base, int* cursors, int4* tiles, int* n_tiles, int max_tiles, int* n_rows) {
+ep_plan_kernel(EpCtx c, int bt, int* send_base, int* cursors, int4* tiles, int* n_tiles, int max_tiles, int* n_rows,
+               const int* counts) {
+  if (counts != nullptr) {  // fused form: the count exchange and its wait run in this CTA first
+    ep_counts_body(c, counts);
+    __syncthreads();
+  }
   const int Etot = c.E + 1, E = c.E, R = c.world, me = c.rank;
   const int* ca = c.counts_all[me];
   __shared__ int G[1025];   // exclusive prefix of routed totals in global expert order
@@ -192,7 +198,16 @@ extern "C" int b200_ep_counts(const EpCtx* c, const int* counts, cudaStream_t st
 extern "C" int b200_ep_plan(const EpCtx* c, int bt, int* send_base, int* cursors, void* tiles, int* n_tiles,
                             int max_tiles, int* n_rows, cudaStream_t st) {
   if (c->E + 1 > 1024) return -7;
-  ep_plan_kernel<<<1, 1024, 0, st>>>(*c, bt, send_base, cursors, static_cast<int4*>(tiles), n_tiles, max_tiles, n_rows);
+  ep_plan_kernel<<<1, 1024, 0, st>>>(*c, bt, send_base, cursors, static_cast<int4*>(tiles), n_tiles, max_tiles, n_rows,
+                                     nullptr);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+// Count exchange + plan in one launch (one CTA either way; saves a launch per MoE block).
+extern "C" int b200_ep_counts_plan(const EpCtx* c, const int* counts, int bt, int* send_base, int* cursors, void* tiles,
+                                   int* n_tiles, int max_tiles, int* n_rows, cudaStream_t st) {
+  if (c->E + 1 > 1024) return -7;
+  ep_plan_kernel<<<1, 1024, 0, st>>>(*c, bt, send_base, cursors, static_cast<int4*>(tiles), n_tiles, max_tiles, n_rows,
+                                     counts);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 extern "C" int b200_ep_dispatch(const EpCtx* c, const void* x, const int* idx, const int* send_base, int* cursors,

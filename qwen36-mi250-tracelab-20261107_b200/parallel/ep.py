@@ -44,6 +44,8 @@ def _lib():
         C = ctypes.POINTER(EpCtx)
         L.b200_ep_counts.argtypes = [C, P, P]
         L.b200_ep_plan.argtypes = [C, I, P, P, P, P, I, P, P]
+        L.b200_ep_counts_plan.argtypes = [C, P, I, P, P, P, P, I, P, P]
+        L.b200_ep_counts_plan.restype = I
         L.b200_ep_dispatch.argtypes = [C, P, P, P, P, I, I, I, P]
         L.b200_ep_combine.argtypes = [C, P, I, I, I, P, P]
         L.b200_gemm_grouped_scatter.argtypes = [P, P, I, I, I, I, I, P, P, I, P, P, I, P, P]
@@ -165,9 +167,8 @@ class EpMoE:
         max_tiles = self.per + 1 + self.cap_rows // bt + 1
         tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device=dev)
         C = ctypes.byref(self.ctx)
-        rc |= L.b200_ep_counts(C, counts.data_ptr(), st)
-        rc |= L.b200_ep_plan(C, bt, send_base.data_ptr(), cursors.data_ptr(), tiles.data_ptr(), n_tiles.data_ptr(),
-                             max_tiles, n_rows.data_ptr(), st)
+        rc |= L.b200_ep_counts_plan(C, counts.data_ptr(), bt, send_base.data_ptr(), cursors.data_ptr(), tiles.data_ptr(),
+                                    n_tiles.data_ptr(), max_tiles, n_rows.data_ptr(), st)
         rc |= L.b200_ep_dispatch(C, x.data_ptr(), idx.data_ptr(), send_base.data_ptr(), cursors.data_ptr(), n_pairs, Pn,
                                  H, st)
         act = torch.empty(self.cap_rows, inter, dtype=x.dtype, device=dev)
