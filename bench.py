@@ -180,7 +180,7 @@ def main() -> None:
     ecfg = EngineConfig(
         max_model_len=P + 2 * total_out + 64, max_seqs=B, state_slots=B + 2, prefill_chunk_tokens=2048,
         prefill_pack_tokens=8192, kv_pages=B * ((P + 2 * total_out) // 64 + 2) + 2, mtp=bool(args.mtp),
-        spec_k=args.mtp, decode_buckets=(B,),
+        spec_k=args.mtp, decode_buckets=(B,), pack_weights=not tp_mode,
     )
     if ep_mode:
         ecfg.mtp = False

@@ -37,6 +37,13 @@ def bf(*shape, scale=1.0):
     return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
 
 
+PACK = False  # --packed: tile-pack the GEMM weights first (the layout the serving engine streams)
+
+
+def pk(w, gate_up=False):
+    return C.pack_weight(w, gate_up=gate_up) if PACK else w
+
+
 _flush = None
 
 
@@ -64,7 +71,7 @@ def report(name, us, nbytes, flops, **extra):
     gbs, tfl = nbytes / us / 1e3, flops / us / 1e6
     line = {"case": name, "us": round(us, 2), "bytes": nbytes, "flops": flops, "GBps": round(gbs, 1),
             "TFLOPs": round(tfl, 2), f"frac_of_{kind}_hbm": round(gbs / hbm, 3),
-            f"frac_of_{kind}_bf16": round(tfl / tf, 3), **extra}
+            f"frac_of_{kind}_bf16": round(tfl / tf, 3), "packed": PACK, **extra}
     print(json.dumps(line), flush=True)
 
 
@@ -72,8 +79,8 @@ def report(name, us, nbytes, flops, **extra):
 def case_moe_decode(small):
     """MoE block of one decode step: 128 rows, 256 experts top-8 + shared (weight streaming)."""
     T, E, H, I = 128, (64 if small else 256), 2048, 512
-    x, router = bf(T, H), bf(E + 1, H, scale=0.3)
-    wgu, wd = bf(E + 1, 2 * I, H, scale=0.02), bf(E + 1, H, I, scale=0.02)
+    x, router = bf(T, H), pk(bf(E + 1, H, scale=0.3))
+    wgu, wd = pk(bf(E + 1, 2 * I, H, scale=0.02), True), pk(bf(E + 1, H, I, scale=0.02))
     us = timed(lambda: C.moe_block(x, router, wgu, wd, E, 8, True))
     w_bytes = (wgu.numel() + wd.numel() + router.numel()) * 2
     report("moe_decode_b128", us, w_bytes, 2 * T * 9 * 3 * H * I, experts=E)
@@ -82,7 +89,7 @@ def case_moe_decode(small):
 def case_gemm_grouped(small):
     """The two grouped GEMMs alone on a fixed routing (gate/up + SiLU-mul, then down)."""
     T, E, H, I, P = 128, (64 if small else 256), 2048, 512, 9
-    wgu, wd = bf(E + 1, 2 * I, H, scale=0.02), bf(E + 1, H, I, scale=0.02)
+    wgu, wd = pk(bf(E + 1, 2 * I, H, scale=0.02), True), pk(bf(E + 1, H, I, scale=0.02))
     n_pairs = T * P
     idx = torch.cat([torch.stack([torch.randperm(E, device="cuda")[:8] for _ in range(T)]),
                      torch.full((T, 1), E, device="cuda")], 1).to(torch.int32)
@@ -103,11 +110,11 @@ def case_gemm_grouped(small):
 
     def up():
         L.b200_gemm_grouped(xs.data_ptr(), wgu.data_ptr(), act.data_ptr(), n_pairs, E + 1, I, 2 * I, H, I, 2, I, bt,
-                            tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), 1, st)
+                            tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), 1, C.is_packed(wgu), st)
 
     def down():
         L.b200_gemm_grouped(act.data_ptr(), wd.data_ptr(), out.data_ptr(), n_pairs, E + 1, H, H, I, H, 0, 0, bt,
-                            tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), 1, st)
+                            tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), 1, C.is_packed(wd), st)
 
     report("grouped_gate_up_silu", timed(up), wgu.numel() * 2, 2 * n_pairs * 2 * I * H, experts=E)
     report("grouped_down", timed(down), wd.numel() * 2, 2 * n_pairs * I * H, experts=E)
@@ -144,7 +151,7 @@ def case_attn_decode(small):
 def case_lm_head(small):
     """LM head with fused argmax: 248320 x 2048 weights, 128 rows."""
     V = 65536 if small else 248320
-    x, w = bf(128, 2048), bf(V, 2048, scale=0.02)
+    x, w = bf(128, 2048), pk(bf(V, 2048, scale=0.02))
     us = timed(lambda: C.lm_head_argmax(x, w))
     report("lm_head_argmax_b128", us, w.numel() * 2, 2 * 128 * V * 2048, vocab=V)
 
@@ -152,7 +159,7 @@ def case_lm_head(small):
 def case_gemm_decode(small):
     """Dense projections at decode size (128 rows): GDN in_proj 12352 x 2048 and out_proj 2048 x 4096."""
     for name, N, K in (("in_proj", 12352, 2048), ("out_proj", 2048, 4096), ("router", 257, 2048)):
-        x, w = bf(128, K), bf(N, K, scale=0.02)
+        x, w = bf(128, K), pk(bf(N, K, scale=0.02))
         for bt in (0, 16, 32, 64, 128):  # 0: what the engine picks; smaller token tiles = more CTAs streaming the weights
             us = timed(lambda: C.linear(x, w, bt=bt))
             report(f"gemm_decode_{name}_b128", us, w.numel() * 2, 2 * 128 * N * K, bt=bt or "auto")
@@ -218,7 +225,9 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("cases", nargs="*", default=list(CASES))
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--packed", action="store_true")
     a = ap.parse_args()
+    PACK = a.packed
     for name in a.cases:
         CASES[name](a.small)
     C.check_errors(torch.device("cuda"))

@@ -353,6 +353,8 @@ def load_service(args: argparse.Namespace) -> Service:
         prefix_cache_tokens=args.prefix_cache_tokens, prefix_cache_entries=args.prefix_cache_entries,
         prefix_cache_gib=args.prefix_cache_gib, max_seqs=args.max_seqs,
     )
+    if os.environ.get("ENGINE_PACK_WEIGHTS") is None:
+        cfg.pack_weights = True  # the server owns the weights it loads: stream them tile-packed
     tp = int(args.gpus_per_replica or os.environ.get("ENGINE_TP", "1") or 1)
     followers = []
     if tp > 1:  # a tensor-parallel replica: this process is rank 0, the other ranks are child processes

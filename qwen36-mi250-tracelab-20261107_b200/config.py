@@ -247,6 +247,8 @@ class EngineConfig:
     one_pass_max: int = 4096
     decode_buckets: tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64, 128, 256)
     cuda_graphs: bool = True
+    # tile-pack the GEMM weights on the GPU (in place: the engine then owns the weights; not under tensor parallelism)
+    pack_weights: bool = False
     # parallelism inside one replica
     tp: int = 1
     ep: int = 1
@@ -269,6 +271,7 @@ class EngineConfig:
             "prefill_pack_tokens": "ENGINE_PREFILL_PACK_TOKENS",
             "one_pass_max": "ENGINE_PREFILL_ONE_PASS_MAX",
             "cuda_graphs": "ENGINE_CUDA_GRAPHS",
+            "pack_weights": "ENGINE_PACK_WEIGHTS",
             "tp": "ENGINE_TP",
             "ep": "ENGINE_EP",
             "fused_collectives": "ENGINE_FUSED_COLLECTIVES",

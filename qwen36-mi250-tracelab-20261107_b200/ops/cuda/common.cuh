@@ -11,6 +11,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace b200 {
 
@@ -40,6 +41,44 @@ __device__ __forceinline__ uint32_t elect_one() {
       : "=r"(pred));
   return pred;
 }
+
+// ------------------------------------------------------------------ programmatic dependent launch
+// A kernel launched with `launch_pdl` may start while the kernel before it in the stream is still running: its CTAs
+// are scheduled as that kernel's CTAs retire, so launch latency and the prologue (barrier init, TMEM allocation,
+// descriptor prefetch, loads of weights nobody writes) overlap the predecessor's tail. The contract every such kernel
+// keeps: `pdl_wait()` before the first read of anything an earlier kernel wrote and before the first global write
+// (it returns once every earlier kernel has completed and its writes are visible), `pdl_launch()` once the CTA holds
+// all the resources it will ever ask for (after any TMEM allocation), which lets the next kernel's CTAs queue up.
+// Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#ifdef __CUDACC__
+inline bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("ENGINE_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+// Launch `kern` on `st` with programmatic stream serialization (unless ENGINE_PDL=0). Works under stream capture: the
+// dependency becomes a programmatic edge of the captured graph.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#endif
 
 // ------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {

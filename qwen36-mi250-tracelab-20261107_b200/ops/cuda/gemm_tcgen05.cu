@@ -52,6 +52,9 @@ struct GemmParams {
   int y_rot;         // dense sequence-parallel GEMMs: token tile = (blockIdx.y + y_rot) % gridDim.y, so that each rank
                      // starts with the tiles whose data (or whose consumer) is furthest from being the bottleneck
   int grid_y;        // dense: number of token tiles (set by the launcher)
+  int packed;        // W is stored tile by tile: [expert][weight tile][k-block][128 * A_TILES rows][64], each (tile,
+                     // k-block) one contiguous 16 KB (32 KB with the up half) run, so a stage is one sequential DRAM read
+  int w_tiles;       // packed: weight tiles per expert
 };
 
 template <int BT, int EPI>
@@ -156,7 +159,10 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (!mbar_wait(&empty[s], ph ^ 1, p.err, ERR_WAIT_EMPTY, abort_flag)) { live = false; break; }
         uint8_t* st = smem + s * C::STAGE_BYTES;
         mbar_expect_tx(&full[s], C::STAGE_BYTES);
-        if (GROUPED) {
+        if (p.packed) {
+          tma_load_2d(st, &tmW, &full[s], 0,
+                      ((expert * p.w_tiles + n0 / BM) * num_k_all + kb0 + kb) * (BM * C::A_TILES));
+        } else if (GROUPED) {
           tma_load_3d(st, &tmW, &full[s], (kb0 + kb) * BK, n0, expert);
           if (EPI == EPI_SILU_MUL) tma_load_3d(st + C::A_BYTES, &tmW, &full[s], (kb0 + kb) * BK, p.up_offset + n0, expert);
         } else {
@@ -468,6 +474,33 @@ static int make_map(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, 
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
+// Tile-packed weights: a 2-D view [tiles * box_rows, 64] whose boxes of `box_rows` rows are contiguous runs.
+static int make_map_packed(CUtensorMap* m, const void* base, uint64_t total_rows, uint32_t box_rows) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {BK, total_rows};
+  cuuint64_t strides[1] = {BK * 2};
+  cuuint32_t box[2] = {BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+// Weight map of a launch: `packed` selects the tile-packed layout (N padded to a multiple of 128 per expert, K a
+// multiple of 64; with the SiLU-mul epilogue the gate and up tiles of a k-block are stored back to back).
+static int weight_map(CUtensorMap* m, const void* W, int E, int N, int w_rows, int K, int ldw, bool silu, int packed,
+                      GemmParams* p) {
+  if (!packed) return E > 0 ? make_map(m, W, K, w_rows, E, K, static_cast<uint64_t>(w_rows) * K, BM)
+                            : make_map(m, W, K, w_rows, 0, ldw, 0, BM);
+  if (K % BK) return -7;
+  const uint64_t tiles = (N + BM - 1) / BM, nk = K / BK, a = silu ? 2 : 1;
+  p->packed = 1;
+  p->w_tiles = static_cast<int>(tiles);
+  return make_map_packed(m, W, static_cast<uint64_t>(E > 0 ? E : 1) * tiles * nk * BM * a, static_cast<uint32_t>(BM * a));
+}
+
 template <int BT, int EPI, bool GROUPED>
 static int launch_split(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int grid_y, cudaStream_t st) {
   using C = Cfg<BT, EPI>;
@@ -549,16 +582,16 @@ extern "C" int b200_pick_bt(int T) {
 // with the up half at row `up_offset`), 3 argmax partials (part_max/part_idx sized [ceil(N/128), T]).
 extern "C" int b200_gemm_dense(const void* X, const void* W, void* out, int T, int N, int K, int ldx, int ldw, int ldo,
                                int epi, int up_offset, int bt, float* part_max, int* part_idx, int* err,
-                               int splits, cudaStream_t st) {
+                               int splits, int packed, cudaStream_t st) {
   if (T <= 0) return 0;
   if (splits < 1 || splits > 8 || splits > (K + BK - 1) / BK) splits = 1;
   if (bt <= 0) bt = b200_pick_bt(T);
   if (epi == EPI_SILU_MUL && bt > 128) bt = 128;
   CUtensorMap tw, tx;
   const int w_rows = (epi == EPI_SILU_MUL) ? up_offset + N : N;
-  if (make_map(&tw, W, K, w_rows, 0, ldw, 0, BM)) return -1;
-  if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
   GemmParams p{N, K, T, ldo, out, nullptr, nullptr, up_offset, part_max, part_idx, err, nullptr, CommCtx{}, 0, nullptr, nullptr, splits, nullptr, {}};
+  if (weight_map(&tw, W, 0, N, w_rows, K, ldw, epi == EPI_SILU_MUL, packed, &p)) return -1;
+  if (make_map(&tx, X, K, T, 0, ldx, 0, bt)) return -1;
   const int gy = (T + bt - 1) / bt;
   switch (epi) {
     case EPI_BF16: return dispatch_bt<EPI_BF16, false>(bt, tw, tx, p, gy, st);
@@ -573,13 +606,13 @@ extern "C" int b200_gemm_dense(const void* X, const void* W, void* out, int T, i
 // [tiles[i].y, +tiles[i].z) of expert tiles[i].x; W is [E, rows, K]. `max_tiles` bounds the grid.
 extern "C" int b200_gemm_grouped(const void* X, const void* W, void* out, int cap, int E, int N, int w_rows, int K,
                                  int ldo, int epi, int up_offset, int bt, const void* tiles, const int* n_tiles,
-                                 int max_tiles, int* err, int splits, cudaStream_t st) {
+                                 int max_tiles, int* err, int splits, int packed, cudaStream_t st) {
   if (max_tiles <= 0) return 0;
   if (splits < 1 || splits > 8 || splits > (K + BK - 1) / BK) splits = 1;
   CUtensorMap tw, tx;
-  if (make_map(&tw, W, K, w_rows, E, K, static_cast<uint64_t>(w_rows) * K, BM)) return -1;
-  if (make_map(&tx, X, K, cap, 0, K, 0, bt)) return -1;
   GemmParams p{N, K, cap, ldo, out, reinterpret_cast<const int4*>(tiles), n_tiles, up_offset, nullptr, nullptr, err, nullptr, CommCtx{}, 0, nullptr, nullptr, splits, nullptr, {}};
+  if (weight_map(&tw, W, E, N, w_rows, K, K, epi == EPI_SILU_MUL, packed, &p)) return -1;
+  if (make_map(&tx, X, K, cap, 0, K, 0, bt)) return -1;
   switch (epi) {
     case EPI_BF16: return dispatch_bt<EPI_BF16, true>(bt, tw, tx, p, max_tiles, st);
     case EPI_SILU_MUL: return dispatch_bt<EPI_SILU_MUL, true>(bt, tw, tx, p, max_tiles, st);
@@ -607,13 +640,13 @@ extern "C" int b200_gemm_allreduce(const CommCtx* ctx, const void* X, const void
 // token (`meta[row] = (rank, pair slot)`, `pair_out[rank]` = that rank's [pairs, N] buffer as mapped in this process).
 extern "C" int b200_gemm_grouped_scatter(const void* X, const void* W, int cap, int E, int N, int K, int bt,
                                          const void* tiles, const int* n_tiles, int max_tiles, const void* meta,
-                                         void* const* pair_out, int world, int* err, cudaStream_t st) {
+                                         void* const* pair_out, int world, int* err, int packed, cudaStream_t st) {
   if (max_tiles <= 0) return 0;
   CUtensorMap tw, tx;
-  if (make_map(&tw, W, K, N, E, K, static_cast<uint64_t>(N) * K, BM)) return -1;
-  if (make_map(&tx, X, K, cap, 0, K, 0, bt)) return -1;
   GemmParams p{N, K, cap, N, nullptr, reinterpret_cast<const int4*>(tiles), n_tiles, 0, nullptr, nullptr, err, nullptr,
                CommCtx{}, 0, nullptr, nullptr, 1, static_cast<const int2*>(meta), {}};
+  if (weight_map(&tw, W, E, N, N, K, K, false, packed, &p)) return -1;
+  if (make_map(&tx, X, K, cap, 0, K, 0, bt)) return -1;
   for (int r = 0; r < world && r < MAX_RANKS; ++r) p.pair_out[r] = static_cast<bf16*>(pair_out[r]);
   return dispatch_bt<EPI_SCATTER, true>(bt, tw, tx, p, max_tiles, st);
 }

@@ -54,8 +54,8 @@ P, I, F = c_void_p, c_int, c_float
 
 class _Sig:
     b200_pick_bt = [I]
-    b200_gemm_dense = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, P, I, P]
-    b200_gemm_grouped = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, I, P, I, P]
+    b200_gemm_dense = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, P, I, I, P]
+    b200_gemm_grouped = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, I, P, I, I, P]
     b200_argmax_finish = [P, P, I, I, P, P, P]
     b200_embed = [P, P, P, I, I, I, P]
     b200_add_rmsnorm = [P, P, P, P, P, I, I, F, I, P]
@@ -132,6 +132,75 @@ def split_k(N: int, K: int, grouped: bool = False) -> int:
     return s
 
 
+# --------------------------------------------------------------------------- tile-packed weights
+# A weight streamed once per decode step is best read as long sequential runs. The plain [N, K] layout makes every
+# 128-row x 64-column TMA box 128 separate 128-byte pieces, K * 2 bytes apart; packed, the box of one (weight tile,
+# k-block) is one contiguous 16 KB run and a tile's k-blocks follow each other, so a CTA streams 128 * K * 2
+# sequential bytes. Packing is a permutation done once after loading / sharding; a packed tensor keeps its shape
+# (rows padded to a multiple of 128) but only the GEMM launchers of this module can read it.
+# The mark lives on the tensor object (``w.b200_packed`` = "plain": one tile per box | "gate_up": gate and up tiles back
+# to back), so it cannot outlive the tensor; a view or a copy of a packed tensor is not recognised and must not be made.
+
+
+def is_packed(w: torch.Tensor) -> int:
+    return 1 if getattr(w, "b200_packed", None) else 0
+
+
+def pack_weight(w: torch.Tensor, gate_up: bool = False) -> torch.Tensor:
+    """Tile-pack ``w [..., N, K]`` (``gate_up``: ``[..., 2I, K]`` with the gate rows first) and return the packed
+    tensor: the same storage when ``N`` is a multiple of 128, otherwise a new tensor with zero rows appended.
+    Tensors whose ``K`` is not a multiple of 64 (or ``I`` of 128) are returned unchanged and stay plain."""
+    if w.device.type != "cuda" or w.dtype != torch.bfloat16 or is_packed(w):
+        return w
+    *lead, N, K = w.shape
+    if K % 64 or (gate_up and (N // 2) % 128):
+        return w
+    if not w.is_contiguous():
+        w = w.contiguous()
+    E = 1
+    for d in lead:
+        E *= d
+    if gate_up:
+        I_ = N // 2
+        src = w.view(E, 2, I_ // 128, 128, K // 64, 64).permute(0, 2, 4, 1, 3, 5)
+    else:
+        Np = (N + 127) // 128 * 128
+        if Np != N:
+            padded = torch.zeros(*lead, Np, K, dtype=w.dtype, device=w.device)
+            padded[..., :N, :] = w
+            w, N = padded, Np
+        src = w.view(E, N // 128, 128, K // 64, 64).permute(0, 1, 3, 2, 4)
+    flat = w.view(-1)
+    # expert by expert, so that the temporary stays small next to a 60 GB expert stack
+    per = flat.numel() // E
+    for e in range(E):
+        flat[e * per:(e + 1) * per].copy_(src[e].contiguous().view(-1))
+    w.b200_packed = "gate_up" if gate_up else "plain"
+    return w
+
+
+def pack_weights(weights) -> None:
+    """Tile-pack every GEMM weight of one device's ``Weights`` in place (fields are replaced where rows had to be
+    padded). Call once, after sharding; the torch oracle and the tensor-parallel launchers cannot read packed
+    tensors, so this is for the single-GPU and data-/expert-parallel engines."""
+    def layer(lw) -> None:
+        lw.in_proj = pack_weight(lw.in_proj)
+        lw.out_proj = pack_weight(lw.out_proj)
+        if lw.router is not None:
+            lw.router = pack_weight(lw.router)
+        if lw.w_gate_up is not None:
+            lw.w_gate_up = pack_weight(lw.w_gate_up, gate_up=True)
+            lw.w_down = pack_weight(lw.w_down)
+
+    for lw in weights.layers:
+        layer(lw)
+    if weights.lm_head.data_ptr() != weights.embed.data_ptr():
+        weights.lm_head = pack_weight(weights.lm_head)
+    if weights.mtp is not None:
+        weights.mtp.fc = pack_weight(weights.mtp.fc)
+        layer(weights.mtp.layer)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None, bt: int = 0) -> torch.Tensor:
     """``x [T, K] @ w[N, K].T`` on tcgen05; bf16 in, bf16 (default) or fp32 out."""
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
@@ -149,7 +218,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
         bt = 16
     rc = lib().b200_gemm_dense(
         _ptr(x), _ptr(w), _ptr(out), T, N, K, x.stride(0), w.stride(0), N, EPI_F32 if f32 else EPI_BF16, 0, bt,
-        None, None, _ptr(err_word(x.device)), split_k(N, K), _stream(),
+        None, None, _ptr(err_word(x.device)), split_k(N, K), is_packed(w), _stream(),
     )
     _check(rc, "gemm_dense")
     return out
@@ -162,7 +231,7 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     out = torch.empty(T, inter, dtype=torch.bfloat16, device=x.device)
     rc = lib().b200_gemm_dense(
         _ptr(x), _ptr(w_gate_up), _ptr(out), T, inter, K, x.stride(0), w_gate_up.stride(0), inter, EPI_SILU_MUL,
-        inter, 0, None, None, _ptr(err_word(x.device)), split_k(inter, K), _stream(),
+        inter, 0, None, None, _ptr(err_word(x.device)), split_k(inter, K), 0, _stream(),
     )
     _check(rc, "gemm_dense(silu_mul)")
     return out
@@ -179,7 +248,7 @@ def lm_head_argmax(x: torch.Tensor, w: torch.Tensor, return_value: bool = False)
     val = torch.empty(T, dtype=torch.float32, device=x.device) if return_value else None
     rc = lib().b200_gemm_dense(
         _ptr(x), _ptr(w), None, T, V, K, x.stride(0), w.stride(0), 0, EPI_ARGMAX, 0, 0, _ptr(pmax), _ptr(pidx),
-        _ptr(err_word(x.device)), 1, _stream(),
+        _ptr(err_word(x.device)), 1, is_packed(w), _stream(),
     )
     _check(rc, "gemm_dense(argmax)")
     _check(lib().b200_argmax_finish(_ptr(pmax), _ptr(pidx), n_tiles, T, _ptr(out), _ptr(val), _stream()), "argmax_finish")
@@ -261,11 +330,12 @@ def moe_block(x: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_
     act = torch.empty(n_pairs, inter, dtype=x.dtype, device=dev)
     _check(L.b200_gemm_grouped(_ptr(xs), _ptr(w_gate_up), _ptr(act), n_pairs, Et, inter, 2 * inter, H, inter,
                                EPI_SILU_MUL, inter, bt, _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err),
-                               split_k(inter, H, grouped=True), st),
+                               split_k(inter, H, grouped=True), is_packed(w_gate_up), st),
            "gemm_grouped(gate_up)")
     pair_out = torch.empty(n_pairs, H, dtype=x.dtype, device=dev)
     _check(L.b200_gemm_grouped(_ptr(act), _ptr(w_down), _ptr(pair_out), n_pairs, Et, H, H, inter, H, EPI_BF16, 0, bt,
-                               _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err), split_k(H, inter, grouped=True), st),
+                               _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err), split_k(H, inter, grouped=True),
+                               is_packed(w_down), st),
            "gemm_grouped(down)")
     out = torch.empty(T, H, dtype=torch.float32 if partial_f32 else x.dtype, device=dev)
     _check(L.b200_moe_combine(_ptr(pair_out), _ptr(wts), _ptr(inv), T, Pn, H, None if partial_f32 else _ptr(out),

@@ -48,7 +48,7 @@ def _lib():
         L.b200_ep_counts_plan.restype = I
         L.b200_ep_dispatch.argtypes = [C, P, P, P, P, I, I, I, P]
         L.b200_ep_combine.argtypes = [C, P, I, I, I, P, P]
-        L.b200_gemm_grouped_scatter.argtypes = [P, P, I, I, I, I, I, P, P, I, P, P, I, P, P]
+        L.b200_gemm_grouped_scatter.argtypes = [P, P, I, I, I, I, I, P, P, I, P, P, I, P, I, P]
         for n in ("b200_ep_counts", "b200_ep_plan", "b200_ep_dispatch", "b200_ep_combine", "b200_gemm_grouped_scatter",
                   "b200_ep_ctx_size"):
             getattr(L, n).restype = I
@@ -175,10 +175,12 @@ class EpMoE:
         err = cuda_ops.err_word(dev)
         rc |= K.b200_gemm_grouped(self._own["xs"], w_gate_up_local.data_ptr(), act.data_ptr(), self.cap_rows,
                                   self.per + 1, inter, 2 * inter, H, inter, cuda_ops.EPI_SILU_MUL, inter, bt,
-                                  tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), 1, st)
+                                  tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), 1,
+                                  cuda_ops.is_packed(w_gate_up_local), st)
         rc |= L.b200_gemm_grouped_scatter(act.data_ptr(), w_down_local.data_ptr(), self.cap_rows, self.per + 1, H,
                                           inter, bt, tiles.data_ptr(), n_tiles.data_ptr(), max_tiles,
-                                          self._own["meta"], self._pair_out_ptrs, self.world, err.data_ptr(), st)
+                                          self._own["meta"], self._pair_out_ptrs, self.world, err.data_ptr(),
+                                          cuda_ops.is_packed(w_down_local), st)
         out = torch.empty_like(x)
         rc |= L.b200_ep_combine(C, wts.data_ptr(), T, Pn, H, out.data_ptr(), st)
         if rc:

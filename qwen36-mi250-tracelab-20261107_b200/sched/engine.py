@@ -59,6 +59,8 @@ class Engine:
         self.chunk = max(PAGE_SIZE, (c.prefill_chunk_tokens + PAGE_SIZE - 1) // PAGE_SIZE * PAGE_SIZE)
         self.max_model_len = c.max_model_len
         self.max_pages_per_seq = (self.max_model_len + PAGE_SIZE - 1) // PAGE_SIZE + 1
+        if c.pack_weights and tp is None and hasattr(self.ops, "pack_weights"):
+            self.ops.pack_weights(weights)  # before the KV pool is sized: padded copies replace a few tensors
         n_slots = c.state_slots or (c.max_seqs * 2 + 2)
         n_pages = c.kv_pages or self._auto_pages(weights, n_slots)
         self.model = Model(weights, n_pages, n_slots, ops=self.ops, tp=tp, ep=ep)

@@ -84,3 +84,31 @@ def test_gpu_mtp_speculation_keeps_outputs():
     forced = [g.output for g in eng2.generate(prompts, s)]
     assert forced == plain and eng2.stats["mtp_accepted"] == eng2.stats["mtp_proposed"] > 0
     cuda_ops.check_errors(torch.device("cuda"))
+
+
+def test_gpu_engine_with_tile_packed_weights_keeps_tokens():
+    """Packing the GEMM weights (``EngineConfig.pack_weights``) is a layout change only: same greedy tokens."""
+    import dataclasses
+
+    from b200serve.config import EngineConfig, ModelConfig
+    from b200serve.models.checkpoint import random_weights
+    from b200serve.ops import cuda_ops
+    from b200serve.sched.engine import Engine
+    from b200serve.sched.request import Sampling
+
+    prompts = _prompts(5, seed=3)
+    s = Sampling(max_tokens=12, ignore_eos=True)
+    plain = [g.output for g in _mk().generate(prompts, s)]
+    cfg = ModelConfig.tiny(moe_intermediate_size=128, shared_expert_intermediate_size=128)
+    outs = []
+    for pack in (False, True):
+        w = random_weights(cfg, seed=0, device="cuda", dtype=torch.bfloat16, std=0.05, lm_head_std=0.5)
+        ecfg = EngineConfig(max_model_len=1024, prefill_chunk_tokens=64, max_seqs=8, mtp=False, kv_pages=256,
+                            decode_buckets=(1, 4, 8), pack_weights=pack)
+        eng = Engine(w, ecfg)
+        if pack:
+            assert cuda_ops.is_packed(eng.model.w.layers[0].w_gate_up) and cuda_ops.is_packed(eng.model.w.lm_head)
+        outs.append([g.output for g in eng.generate(prompts, s)])
+        cuda_ops.check_errors(eng.device)
+    assert outs[0] == outs[1]
+    assert len(plain) == len(prompts)

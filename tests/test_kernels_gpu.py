@@ -353,3 +353,33 @@ def test_ring_commit_copies_only_sequences_that_dropped_rows(C):
             want_r[:, slots[b]] = ring[1][:, b, keep[b]]
     C.ring_commit(conv, rec, ring, slots, keep)
     assert torch.equal(conv, want_c) and torch.equal(rec, want_r)
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 256, 64), (16, 300, 128), (128, 12352, 2048), (700, 1024, 512)])
+def test_packed_weights_give_the_same_bits_dense(C, T, N, K):
+    """A tile-packed weight is the same GEMM read through another address map: outputs are bitwise equal
+    (rows are padded to a multiple of 128 and come out as extra zero columns)."""
+    x, w = _bf(T, K, seed=21), _bf(N, K, scale=0.05, seed=22)
+    plain = C.linear(x, w, out_dtype=torch.float32)
+    idx_plain = C.lm_head_argmax(x, w)
+    wp = C.pack_weight(w.clone())
+    assert C.is_packed(wp) and wp.shape[0] == (N + 127) // 128 * 128
+    got = C.linear(x, wp, out_dtype=torch.float32)
+    assert torch.equal(got[:, :N], plain)
+    assert not got[:, N:].any()
+    assert torch.equal(C.linear(x, wp)[:, :N], C.linear(x, w))
+    if N % 128 == 0:
+        assert torch.equal(C.lm_head_argmax(x, wp), idx_plain)
+    C.check_errors(x.device)
+
+
+@pytest.mark.parametrize("T,E,k,H,I", [(3, 8, 2, 128, 128), (128, 64, 8, 2048, 512), (600, 16, 4, 256, 128)])
+def test_packed_weights_give_the_same_bits_moe(C, T, E, k, H, I):
+    x = _bf(T, H, seed=23)
+    router = _bf(E + 1, H, scale=0.3, seed=24)
+    wgu, wd = _bf(E + 1, 2 * I, H, scale=0.05, seed=25), _bf(E + 1, H, I, scale=0.05, seed=26)
+    plain = C.moe_block(x, router, wgu, wd, E, k, True)
+    got = C.moe_block(x, C.pack_weight(router.clone()), C.pack_weight(wgu.clone(), gate_up=True),
+                      C.pack_weight(wd.clone()), E, k, True)
+    assert torch.equal(got, plain)
+    C.check_errors(x.device)
