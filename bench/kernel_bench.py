@@ -93,18 +93,16 @@ def case_gemm_grouped(small):
     n_pairs = T * P
     idx = torch.cat([torch.stack([torch.randperm(E, device="cuda")[:8] for _ in range(T)]),
                      torch.full((T, 1), E, device="cuda")], 1).to(torch.int32)
-    counts = torch.bincount(idx.flatten().long(), minlength=E + 1).to(torch.int32)
-    ints = torch.zeros(2 * (E + 2) + 1 + 2 * n_pairs, dtype=torch.int32, device="cuda")
-    offsets, cursors = ints[: E + 2], ints[E + 2 : 2 * E + 4]
-    n_tiles, perm, inv = ints[2 * E + 4 : 2 * E + 5], ints[2 * E + 5 : 2 * E + 5 + n_pairs], ints[2 * E + 5 + n_pairs :]
+    ints = torch.zeros(E + 3 + 2 * n_pairs, dtype=torch.int32, device="cuda")
+    offsets, n_tiles = ints[: E + 2], ints[E + 2 : E + 3]
+    perm, inv = ints[E + 3 : E + 3 + n_pairs], ints[E + 3 + n_pairs :]
     bt = 16
     max_tiles = E + 1 + n_pairs // bt + 1
     tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device="cuda")
     L, st = C.lib(), torch.cuda.current_stream().cuda_stream
     err = C.err_word(torch.device("cuda"))
-    assert L.b200_moe_plan(counts.data_ptr(), idx.data_ptr(), n_pairs, E + 1, bt, offsets.data_ptr(), cursors.data_ptr(),
-                           tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, perm.data_ptr(), inv.data_ptr(),
-                           err.data_ptr(), st) == 0
+    assert L.b200_moe_plan(idx.data_ptr(), n_pairs, E + 1, bt, offsets.data_ptr(), tiles.data_ptr(), n_tiles.data_ptr(),
+                           max_tiles, perm.data_ptr(), inv.data_ptr(), err.data_ptr(), st) == 0
     xs, act, out = bf(n_pairs, H), torch.empty(n_pairs, I, dtype=torch.bfloat16, device="cuda"), torch.empty(
         n_pairs, H, dtype=torch.bfloat16, device="cuda")
 

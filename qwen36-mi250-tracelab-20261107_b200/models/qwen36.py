@@ -180,15 +180,27 @@ class Model:
             return self.ops.linear(core, w)
         return self.tp.comm.gemm_allreduce(self.ops, core, w)
 
-    def _layer(self, lw, x, res, batch, kv_layer=None, gi=None, ring=None):
+    def _moe_norm(self, lw: LayerWeights, h: torch.Tensor, res: torch.Tensor, norm_w: torch.Tensor):
+        """MoE block, residual add and the RMSNorm that follows it (the next layer's input norm or the final norm);
+        returns ``(new residual, normed)``. On the CUDA path of one GPU the three are one kernel behind the grouped
+        GEMMs (reference: ``engine/fast/fused.py:635-692`` folds combine + shared expert + residual into its down
+        kernel); elsewhere the norm is its own op, with identical rounding points."""
         cfg, ops = self.cfg, self.ops
-        res, h = ops.add_rmsnorm(x, res, lw.input_norm, cfg.rms_norm_eps)
+        if self.tp is None and self.ep is None and lw.shared_merged and getattr(ops, "FUSED_MOE_NORM", False):
+            return ops.moe_block(h, lw.router, lw.w_gate_up, lw.w_down, cfg.num_experts, cfg.num_experts_per_tok, True,
+                                 residual=res, norm_w=norm_w, eps=cfg.rms_norm_eps)
+        return ops.add_rmsnorm(self._moe(lw, h), res, norm_w, cfg.rms_norm_eps)
+
+    def _layer(self, lw, h, res, batch, next_norm, kv_layer=None, gi=None, ring=None):
+        """One decoder layer from its normed input ``h`` and the residual stream ``res``; returns the new residual
+        and the input of the next layer, already normed with ``next_norm``."""
+        cfg, ops = self.cfg, self.ops
         if lw.kind == "linear_attention":
             mix = self._gdn(lw, gi, h, batch, ring)
         else:
             mix = self._attention(lw, kv_layer, h, batch)
         res, h = ops.add_rmsnorm(mix, res, lw.post_norm, cfg.rms_norm_eps)
-        return self._moe(lw, h), res
+        return self._moe_norm(lw, h, res, next_norm)
 
     # ------------------------------------------------------------------ passes
     SP_MIN_ROWS = 512  # prefill passes at least this long take the sequence-parallel collectives under TP
@@ -264,14 +276,15 @@ class Model:
             if sp is not None:
                 return self._forward_sp(batch, sp)
         ops.DECODE_MODE = batch.G > 0  # decode / verify passes may split K across clusters; prefill never does
+        layers = self.w.layers
         x = ops.embed(batch.tokens, self.w.embed)
-        res = None
-        for i, lw in enumerate(self.w.layers):
+        res, h = ops.add_rmsnorm(x, None, layers[0].input_norm, cfg.rms_norm_eps)
+        for i, lw in enumerate(layers):
+            nxt = layers[i + 1].input_norm if i + 1 < len(layers) else self.w.final_norm
             if lw.kind == "linear_attention":
-                x, res = self._layer(lw, x, res, batch, gi=self._gdn_index[i], ring=ring)
+                res, h = self._layer(lw, h, res, batch, nxt, gi=self._gdn_index[i], ring=ring)
             else:
-                x, res = self._layer(lw, x, res, batch, kv_layer=self.kv[self._kv_index[i]])
-        _, h = ops.add_rmsnorm(x, res, self.w.final_norm, cfg.rms_norm_eps)
+                res, h = self._layer(lw, h, res, batch, nxt, kv_layer=self.kv[self._kv_index[i]])
         return h
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
@@ -306,6 +319,6 @@ class Model:
         e = ops.rmsnorm(ops.embed(next_tokens, self.w.embed), m.pre_fc_norm_embedding, cfg.rms_norm_eps)
         h = ops.rmsnorm(hidden, m.pre_fc_norm_hidden, cfg.rms_norm_eps)
         x = ops.linear(torch.cat([e, h], dim=-1), m.fc)
-        x, res = self._layer(m.layer, x, None, batch, kv_layer=self.kv[self.mtp_kv_index])
-        _, y = ops.add_rmsnorm(x, res, m.norm, cfg.rms_norm_eps)
+        res, h = ops.add_rmsnorm(x, None, m.layer.input_norm, cfg.rms_norm_eps)
+        _, y = self._layer(m.layer, h, res, batch, m.norm, kv_layer=self.kv[self.mtp_kv_index])
         return y

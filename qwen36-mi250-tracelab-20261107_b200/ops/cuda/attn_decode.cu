@@ -43,6 +43,8 @@ __global__ void attn_prep_kernel(const bf16* qkv, int ld, const int64_t* positio
                                  bf16* gate_out, bf16* kv, int n_q, int n_kv, int rot, float theta, float eps,
                                  int num_pages, int* err) {
   // one warp per (row, head); heads: [0,n_q) query, [n_q, n_q+n_kv) key, then value
+  pdl_wait();
+  pdl_launch();
   const int row = blockIdx.x;
   const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -228,6 +230,8 @@ paged_attn_kernel(const bf16* q, const bf16* kv, const int* tables, int max_page
 template <int D>
 __global__ void attn_combine_kernel(const float* part_acc, const float* part_ml, const bf16* gate, bf16* out, int n_q,
                                     int Z) {
+  pdl_wait();
+  pdl_launch();
   const int row = blockIdx.x, qh = blockIdx.y;
   const int d = threadIdx.x;  // D threads
   const float* pm = part_ml + (static_cast<size_t>(row) * n_q + qh) * Z * 2;
@@ -258,11 +262,10 @@ extern "C" int b200_attn_prep(const void* qkv, int ld, const int64_t* positions,
   const int heads = n_q + 2 * n_kv;
   dim3 grid(rows, (heads + 7) / 8);
 #define PREP(DD)                                                                                                      \
-  attn_prep_kernel<DD><<<grid, 256, 0, st>>>(static_cast<const bf16*>(qkv), ld, positions, tables, max_pages,        \
-                                             seq_of_row, static_cast<const bf16*>(q_norm),                           \
-                                             static_cast<const bf16*>(k_norm), static_cast<bf16*>(q_out),            \
-                                             static_cast<bf16*>(gate_out), static_cast<bf16*>(kv), n_q, n_kv, rot,   \
-                                             theta, eps, num_pages, err)
+  launch_pdl(attn_prep_kernel<DD>, grid, dim3(256), 0, st, static_cast<const bf16*>(qkv), ld, positions, tables,    \
+             max_pages, seq_of_row, static_cast<const bf16*>(q_norm), static_cast<const bf16*>(k_norm),              \
+             static_cast<bf16*>(q_out), static_cast<bf16*>(gate_out), static_cast<bf16*>(kv), n_q, n_kv, rot, theta, \
+             eps, num_pages, err)
   if (D == 256) PREP(256);
   else if (D == 128) PREP(128);
   else if (D == 64) PREP(64);
@@ -317,9 +320,12 @@ extern "C" int b200_attn_combine(const float* part_acc, const float* part_ml, co
                                  int n_q, int D, int Z, cudaStream_t st) {
   if (rows <= 0) return 0;
   dim3 cgrid(rows, n_q);
-  if (D == 256) attn_combine_kernel<256><<<cgrid, 256, 0, st>>>(part_acc, part_ml, static_cast<const bf16*>(gate), static_cast<bf16*>(out), n_q, Z);
-  else if (D == 128) attn_combine_kernel<128><<<cgrid, 128, 0, st>>>(part_acc, part_ml, static_cast<const bf16*>(gate), static_cast<bf16*>(out), n_q, Z);
-  else if (D == 64) attn_combine_kernel<64><<<cgrid, 64, 0, st>>>(part_acc, part_ml, static_cast<const bf16*>(gate), static_cast<bf16*>(out), n_q, Z);
+  const bf16* g = static_cast<const bf16*>(gate);
+  bf16* o = static_cast<bf16*>(out);
+  cudaError_t rc;
+  if (D == 256) rc = launch_pdl(attn_combine_kernel<256>, cgrid, dim3(256), 0, st, part_acc, part_ml, g, o, n_q, Z);
+  else if (D == 128) rc = launch_pdl(attn_combine_kernel<128>, cgrid, dim3(128), 0, st, part_acc, part_ml, g, o, n_q, Z);
+  else if (D == 64) rc = launch_pdl(attn_combine_kernel<64>, cgrid, dim3(64), 0, st, part_acc, part_ml, g, o, n_q, Z);
   else return -7;
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return rc == cudaSuccess ? 0 : -4;
 }

@@ -21,11 +21,15 @@
 //     that loads the library, from load until the process exits, whether or not this function
 //     is ever called.
 //   * The first call on each device looks up the array's device address (one runtime query, no
-//     launch). Make that first call before any CUDA stream capture begins.
-//   * All calls on a device share the one array. It keeps whatever the previous call left; this
-//     function overwrites every element it later reads, so nothing has to be cleared. Two calls
-//     that can overlap on the GPU (different streams, or concurrent host threads) would overwrite
-//     each other's partial results: serialise them.
+//     launch) and caches it per device ordinal. Make that first call before any CUDA stream capture
+//     begins. Two host threads that make their first call on the same device at the same moment
+//     both store the same address; no lock is taken.
+//   * All calls on a device share the one array. It keeps whatever the previous call left; a call
+//     whose kernels ran to completion overwrites every element it later reads, so nothing has to
+//     be cleared. If an internal bounded wait gives up (*err != 0 afterwards) the partial results
+//     are not written and out_idx / out_val come from the previous call's leftovers: read *err
+//     before trusting the outputs. Two calls that can overlap on the GPU (different streams, or
+//     concurrent host threads) would overwrite each other's partial results: serialise them.
 //   * The function calls no cudaMalloc, cudaFree or allocating library routine.
 //
 // out_idx: int64 [T]; out_val: float [T] with the winning logit, or NULL; ldx / ldw: row strides of

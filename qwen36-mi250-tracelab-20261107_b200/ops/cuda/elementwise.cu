@@ -12,6 +12,8 @@ namespace b200 {
 
 // ------------------------------------------------------------------ embedding
 __global__ void embed_kernel(const int64_t* tokens, const bf16* table, bf16* out, int H, int vocab) {
+  pdl_wait();
+  pdl_launch();
   const int t = blockIdx.x;
   int64_t tok = tokens[t];
   if (tok < 0 || tok >= vocab) tok = 0;
@@ -26,6 +28,8 @@ __global__ void embed_kernel(const int64_t* tokens, const bf16* table, bf16* out
 template <bool ZERO_CENTRED>
 __global__ void add_rmsnorm_kernel(const bf16* x, const bf16* res, const bf16* w, bf16* res_out, bf16* y, int H,
                                    float eps) {
+  pdl_wait();
+  pdl_launch();
   const size_t row = static_cast<size_t>(blockIdx.x) * H;
   extern __shared__ float vals[];  // H floats
   float ss = 0.f;
@@ -71,19 +75,14 @@ __global__ void add_rmsnorm_kernel(const bf16* x, const bf16* res, const bf16* w
 // ------------------------------------------------------------------ MoE routing
 // One warp per row: fp32 softmax over E router logits, iterative top-k with ties to the lower
 // expert id, renormalise, round weights to bf16; pair k (the last) is the shared expert with
-// weight sigmoid(logit[E]) when `shared` is set. Also counts rows per expert.
-constexpr int MAX_PER_LANE = 16;  // E <= 512
-
-__global__ void route_kernel(const float* logits, int ldl, int T, int E, int top_k, int shared, float* wts, int* idx,
-                             int* counts, const int* expert_map) {
-  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (warp_global >= T) return;
-  const float* row = logits + static_cast<size_t>(warp_global) * ldl;
-  float v[MAX_PER_LANE];
+// weight sigmoid(logit[E]) when `shared` is set. PER_LANE * 32 >= E.
+template <int PER_LANE>
+__device__ __forceinline__ void route_row(const float* row, int E, int top_k, int shared, float* wts, int* idx,
+                                          const int* expert_map, int* counts, int lane) {
+  float v[PER_LANE];
   float mx = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < MAX_PER_LANE; ++i) {
+  for (int i = 0; i < PER_LANE; ++i) {
     const int e = i * 32 + lane;
     v[i] = e < E ? row[e] : -INFINITY;
     mx = fmaxf(mx, v[i]);
@@ -91,12 +90,11 @@ __global__ void route_kernel(const float* logits, int ldl, int T, int E, int top
   mx = warp_max(mx);
   float sum = 0.f;
 #pragma unroll
-  for (int i = 0; i < MAX_PER_LANE; ++i) {
+  for (int i = 0; i < PER_LANE; ++i) {
     v[i] = (i * 32 + lane) < E ? expf(v[i] - mx) : -1.0f;
     sum += v[i] > 0.f ? v[i] : 0.f;
   }
   sum = warp_sum(sum);
-  const int P = top_k + (shared ? 1 : 0);
   float sel_w = 0.f;  // lane j keeps the j-th selected probability
   int sel_e = 0;
   float tot = 0.f;
@@ -104,7 +102,7 @@ __global__ void route_kernel(const float* logits, int ldl, int T, int E, int top
     float bm = -1.0f;
     int be = 0x7fffffff;
 #pragma unroll
-    for (int i = 0; i < MAX_PER_LANE; ++i) {
+    for (int i = 0; i < PER_LANE; ++i) {
       const int e = i * 32 + lane;
       if (v[i] > bm) { bm = v[i]; be = e; }  // ascending e within a lane: first maximum kept
     }
@@ -114,7 +112,9 @@ __global__ void route_kernel(const float* logits, int ldl, int T, int E, int top
       const int oe = __shfl_xor_sync(0xffffffffu, be, o);
       if (om > bm || (om == bm && oe < be)) { bm = om; be = oe; }
     }
-    if ((be & 31) == lane) v[be >> 5] = -1.0f;  // remove the winner
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i)
+      if (i * 32 + lane == be) v[i] = -1.0f;  // remove the winner (static indexing keeps v in registers)
     const float pr = bm / sum;
     tot += pr;
     if (lane == k) { sel_w = pr; sel_e = be; }
@@ -123,28 +123,55 @@ __global__ void route_kernel(const float* logits, int ldl, int T, int E, int top
     const float wv = __bfloat162float(__float2bfloat16(sel_w / tot));
     // expert parallelism: experts hosted elsewhere map to -1 and are skipped by the later stages
     const int le = expert_map ? expert_map[sel_e] : sel_e;
-    wts[static_cast<size_t>(warp_global) * P + lane] = wv;
-    idx[static_cast<size_t>(warp_global) * P + lane] = le;
-    if (le >= 0) atomicAdd(&counts[le], 1);
+    wts[lane] = wv;
+    idx[lane] = le;
+    if (counts && le >= 0) atomicAdd(&counts[le], 1);
   }
   if (shared && lane == 0) {
     const float sg = sigmoid_f(row[E]);
     const int le = expert_map ? expert_map[E] : E;
-    wts[static_cast<size_t>(warp_global) * P + top_k] = __bfloat162float(__float2bfloat16(sg));
-    idx[static_cast<size_t>(warp_global) * P + top_k] = le;
-    if (le >= 0) atomicAdd(&counts[le], 1);
+    wts[top_k] = __bfloat162float(__float2bfloat16(sg));
+    idx[top_k] = le;
+    if (counts && le >= 0) atomicAdd(&counts[le], 1);
   }
 }
 
-// One CTA: exclusive offsets per expert, the token-tile table (expert, row0, nrows) and its length;
-// clears the scatter cursors. Experts are laid out in id order, rows of one expert contiguous.
-__global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int* counts, int Et, int bt, int* offsets, int* cursors, int4* tiles, int* n_tiles,
-                int max_tiles) {
-  // block-wide exclusive scan of (rows, tiles) per expert: one expert per thread, Et <= 1024
+constexpr int MAX_PER_LANE = 16;  // E <= 512
+
+// Grid of warps, one row each. `counts` (optional, zeroed by the caller) receives the rows per expert.
+template <int PER_LANE>
+__global__ void route_kernel(const float* logits, int ldl, int T, int E, int top_k, int shared, float* wts, int* idx,
+                             int* counts, const int* expert_map) {
+  pdl_wait();
+  pdl_launch();
+  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp_global >= T) return;
+  const int P = top_k + (shared ? 1 : 0);
+  route_row<PER_LANE>(logits + static_cast<size_t>(warp_global) * ldl, E, top_k, shared,
+                      wts + static_cast<size_t>(warp_global) * P, idx + static_cast<size_t>(warp_global) * P, expert_map,
+                      counts, lane);
+}
+
+// One CTA of 1024 threads turns the (row, pair) -> expert table into everything the grouped GEMMs need, without
+// global atomics or a zeroed workspace: rows per expert (shared-memory histogram), exclusive offsets (experts laid
+// out in id order, rows of one expert contiguous), the token-tile table (expert, row0, nrows) and its length, and
+// the position of every pair in the expert-sorted order (perm / inv). The order inside an expert does not influence
+// any output value: every sorted row is computed on its own.
+__device__ void plan_scatter(const int* idx, int n_pairs, int Et, int bt, int* offsets, int4* tiles, int* n_tiles,
+                             int max_tiles, int* perm, int* inv, int* err) {
+  __shared__ int s_count[1024], s_off[1024], s_cur[1024];
   __shared__ int w_rows[32], w_tiles[32];
   const int e = threadIdx.x, lane = e & 31, w = e >> 5;
-  const int c = e < Et ? counts[e] : 0;
+  s_count[e] = 0;
+  s_cur[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int x = idx[i];
+    if (x >= 0 && x < Et) atomicAdd(&s_count[x], 1);
+  }
+  __syncthreads();
+  const int c = e < Et ? s_count[e] : 0;
   const int t = (c + bt - 1) / bt;
   int sc = c, stl = t;
 #pragma unroll
@@ -166,9 +193,9 @@ moe_plan_kernel(const int* counts, int Et, int bt, int* offsets, int* cursors, i
   __syncthreads();
   const int row0 = sc - c + (w ? w_rows[w - 1] : 0);    // exclusive prefix
   const int tile0 = stl - t + (w ? w_tiles[w - 1] : 0);
+  s_off[e] = row0;
   if (e < Et) {
     offsets[e] = row0;
-    cursors[e] = 0;
     for (int i = 0, ti = tile0; i * bt < c && ti < max_tiles; ++i, ++ti)
       tiles[ti] = make_int4(e, row0 + i * bt, min(bt, c - i * bt), 0);
   }
@@ -177,24 +204,46 @@ moe_plan_kernel(const int* counts, int Et, int bt, int* offsets, int* cursors, i
     const int total = tile0 + t;
     *n_tiles = total < max_tiles ? total : max_tiles;
   }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int x = idx[i];
+    if (x < 0) { inv[i] = -1; continue; }  // pair served by another rank
+    if (x >= Et) { atomicCAS(err, 0, ERR_BAD_INDEX); inv[i] = -1; continue; }
+    const int pos = s_off[x] + atomicAdd(&s_cur[x], 1);
+    perm[pos] = i;
+    inv[i] = pos;
+  }
 }
 
-// Each (row, pair) takes the next free position of its expert's range. The order inside an expert
-// does not influence any output value: every sorted row is computed on its own.
-__global__ void moe_scatter_kernel(const int* idx, int n_pairs, int Et, const int* offsets, int* cursors, int* perm,
-                                   int* inv, int* err) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n_pairs) return;
-  const int e = idx[i];
-  if (e < 0) { inv[i] = -1; return; }  // pair served by another rank
-  if (e >= Et) { atomicCAS(err, 0, ERR_BAD_INDEX); inv[i] = -1; return; }
-  const int pos = offsets[e] + atomicAdd(&cursors[e], 1);
-  perm[pos] = i;
-  inv[i] = pos;
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* idx, int n_pairs, int Et, int bt, int* offsets, int4* tiles, int* n_tiles, int max_tiles,
+                int* perm, int* inv, int* err) {
+  pdl_wait();
+  pdl_launch();
+  plan_scatter(idx, n_pairs, Et, bt, offsets, tiles, n_tiles, max_tiles, perm, inv, err);
+}
+
+// Decode-size batches: routing of every row (one warp each, 32 warps) and the plan in ONE launch.
+template <int PER_LANE>
+__global__ void __launch_bounds__(1024)
+moe_route_plan_kernel(const float* logits, int ldl, int T, int E, int top_k, int shared, float* wts, int* idx,
+                      const int* expert_map, int Et, int bt, int* offsets, int4* tiles, int* n_tiles, int max_tiles,
+                      int* perm, int* inv, int* err) {
+  pdl_wait();
+  pdl_launch();
+  const int P = top_k + (shared ? 1 : 0);
+  const int lane = threadIdx.x & 31;
+  for (int r = threadIdx.x >> 5; r < T; r += 32)
+    route_row<PER_LANE>(logits + static_cast<size_t>(r) * ldl, E, top_k, shared, wts + static_cast<size_t>(r) * P,
+                        idx + static_cast<size_t>(r) * P, expert_map, nullptr, lane);
+  __syncthreads();  // this CTA wrote idx: visible to all its threads after the barrier
+  plan_scatter(idx, T * P, Et, bt, offsets, tiles, n_tiles, max_tiles, perm, inv, err);
 }
 
 // x_sorted[pos] = x[perm[pos] / P]
 __global__ void moe_gather_kernel(const bf16* x, const int* perm, const int* n_valid, int T, int P, int H, bf16* xs) {
+  pdl_wait();
+  pdl_launch();
   const int pos = blockIdx.x;
   if (pos >= *n_valid) return;  // with expert parallelism only the locally served pairs are laid out
   const int t = perm[pos] / P;
@@ -205,9 +254,17 @@ __global__ void moe_gather_kernel(const bf16* x, const int* perm, const int* n_v
 }
 
 // out[t] = bf16( sum_j w[t,j] * pair_out[inv[t,j]] ) in pair order, fp32 accumulation, rounded once.
+// With NORM the same launch also does what add_rmsnorm would do next: res' = bf16(res + out[t]) and
+// y = bf16(res' * rsqrt(mean(res'^2) + eps) * (1 + w)) (zero-centred weight), with the same rounding points.
+template <bool NORM>
 __global__ void moe_combine_kernel(const bf16* pair_out, const float* wts, const int* inv, int P, int H, bf16* out,
-                                   float* out_f32) {
+                                   float* out_f32, const bf16* res, const bf16* norm_w, bf16* res_out, bf16* y,
+                                   float eps) {
+  pdl_wait();
+  pdl_launch();
+  extern __shared__ float vals[];  // NORM: H floats
   const int t = blockIdx.x;
+  float ss = 0.f;
   for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int j = 0; j < P; ++j) {
@@ -219,7 +276,7 @@ __global__ void moe_combine_kernel(const bf16* pair_out, const float* wts, const
 #pragma unroll
       for (int k = 0; k < 8; ++k) acc[k] += wv * __bfloat162float(pe[k]);
     }
-    if (out_f32) {  // a partial sum that still has to be added across ranks
+    if (!NORM && out_f32) {  // a partial sum that still has to be added across ranks
 #pragma unroll
       for (int k = 0; k < 8; ++k) out_f32[static_cast<size_t>(t) * H + i + k] = acc[k];
       continue;
@@ -228,7 +285,41 @@ __global__ void moe_combine_kernel(const bf16* pair_out, const float* wts, const
     bf16* oe = reinterpret_cast<bf16*>(&ov);
 #pragma unroll
     for (int k = 0; k < 8; ++k) oe[k] = __float2bfloat16(acc[k]);
-    *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + i) = ov;
+    if (NORM) {
+      if (res) {
+        uint4 rv = *reinterpret_cast<const uint4*>(res + static_cast<size_t>(t) * H + i);
+        const bf16* re = reinterpret_cast<const bf16*>(&rv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) oe[k] = __float2bfloat16(__bfloat162float(oe[k]) + __bfloat162float(re[k]));
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float f = __bfloat162float(oe[k]);
+        vals[i + k] = f;
+        ss += f * f;
+      }
+      *reinterpret_cast<uint4*>(res_out + static_cast<size_t>(t) * H + i) = ov;
+    } else {
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + i) = ov;
+    }
+  }
+  if (NORM) {
+    __shared__ float part[32];
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < static_cast<int>(blockDim.x >> 5); ++i) tot += part[i];  // fixed order, as add_rmsnorm_kernel
+    const float inv_rms = rsqrtf(tot / H + eps);
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      uint4 wv = *reinterpret_cast<const uint4*>(norm_w + i);
+      const bf16* we = reinterpret_cast<const bf16*>(&wv);
+      uint4 ov;
+      bf16* oe = reinterpret_cast<bf16*>(&ov);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) oe[k] = __float2bfloat16(vals[i + k] * inv_rms * (1.0f + __bfloat162float(we[k])));
+      *reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * H + i) = ov;
+    }
   }
 }
 
@@ -237,11 +328,12 @@ __global__ void moe_combine_kernel(const bf16* pair_out, const float* wts, const
 using namespace b200;
 
 #define CHECK_LAUNCH() return cudaGetLastError() == cudaSuccess ? 0 : -4
+#define LAUNCHED(expr) return (expr) == cudaSuccess ? 0 : -4
 
 extern "C" int b200_embed(const int64_t* tokens, const void* table, void* out, int T, int H, int vocab, cudaStream_t st) {
   if (T <= 0) return 0;
-  embed_kernel<<<T, 128, 0, st>>>(tokens, static_cast<const bf16*>(table), static_cast<bf16*>(out), H, vocab);
-  CHECK_LAUNCH();
+  LAUNCHED(launch_pdl(embed_kernel, dim3(T), dim3(128), 0, st, tokens, static_cast<const bf16*>(table),
+                      static_cast<bf16*>(out), H, vocab));
 }
 
 extern "C" int b200_add_rmsnorm(const void* x, const void* res, const void* w, void* res_out, void* y, int T, int H,
@@ -250,41 +342,65 @@ extern "C" int b200_add_rmsnorm(const void* x, const void* res, const void* w, v
   if (H % 8) return -7;
   const int threads = H >= 2048 ? 256 : 128;
   auto k = zero_centred ? add_rmsnorm_kernel<true> : add_rmsnorm_kernel<false>;
-  k<<<T, threads, H * sizeof(float), st>>>(static_cast<const bf16*>(x), static_cast<const bf16*>(res),
-                                            static_cast<const bf16*>(w), static_cast<bf16*>(res_out),
-                                            static_cast<bf16*>(y), H, eps);
-  CHECK_LAUNCH();
+  LAUNCHED(launch_pdl(k, dim3(T), dim3(threads), H * sizeof(float), st, static_cast<const bf16*>(x),
+                      static_cast<const bf16*>(res), static_cast<const bf16*>(w), static_cast<bf16*>(res_out),
+                      static_cast<bf16*>(y), H, eps));
 }
 
+// Routing only (any number of rows). `counts` may be null; when given it is zeroed here and receives rows per expert.
 extern "C" int b200_moe_route(const float* logits, int ldl, int T, int E, int top_k, int shared, float* wts, int* idx,
                               int* counts, int n_counts, const int* expert_map, cudaStream_t st) {
   if (T <= 0) return 0;
   if (E > 32 * MAX_PER_LANE || top_k > 32) return -7;
-  cudaMemsetAsync(counts, 0, sizeof(int) * n_counts, st);
-  route_kernel<<<(T + 3) / 4, 128, 0, st>>>(logits, ldl, T, E, top_k, shared, wts, idx, counts, expert_map);
-  CHECK_LAUNCH();
+  if (counts) cudaMemsetAsync(counts, 0, sizeof(int) * n_counts, st);
+  auto k = E <= 256 ? route_kernel<8> : route_kernel<MAX_PER_LANE>;
+  LAUNCHED(launch_pdl(k, dim3((T + 3) / 4), dim3(128), 0, st, logits, ldl, T, E, top_k, shared, wts, idx, counts,
+                      expert_map));
 }
 
-extern "C" int b200_moe_plan(const int* counts, const int* idx, int n_pairs, int Et, int bt, int* offsets, int* cursors,
-                             void* tiles, int* n_tiles, int max_tiles, int* perm, int* inv, int* err, cudaStream_t st) {
+// Expert-sorted layout of the (row, pair) table `idx` [n_pairs]: offsets [Et + 1], tile table, perm / inv [n_pairs].
+extern "C" int b200_moe_plan(const int* idx, int n_pairs, int Et, int bt, int* offsets, void* tiles, int* n_tiles,
+                             int max_tiles, int* perm, int* inv, int* err, cudaStream_t st) {
   if (Et > 1024) return -7;
-  moe_plan_kernel<<<1, 1024, 0, st>>>(counts, Et, bt, offsets, cursors, static_cast<int4*>(tiles), n_tiles, max_tiles);
-  moe_scatter_kernel<<<(n_pairs + 255) / 256, 256, 0, st>>>(idx, n_pairs, Et, offsets, cursors, perm, inv, err);
-  CHECK_LAUNCH();
+  LAUNCHED(launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, st, idx, n_pairs, Et, bt, offsets,
+                      static_cast<int4*>(tiles), n_tiles, max_tiles, perm, inv, err));
+}
+
+// Routing and plan of a decode-size batch (T <= 256 rows) in one launch.
+extern "C" int b200_moe_route_plan(const float* logits, int ldl, int T, int E, int top_k, int shared, float* wts,
+                                   int* idx, const int* expert_map, int Et, int bt, int* offsets, void* tiles,
+                                   int* n_tiles, int max_tiles, int* perm, int* inv, int* err, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (E > 32 * MAX_PER_LANE || top_k > 32 || Et > 1024) return -7;
+  auto k = E <= 256 ? moe_route_plan_kernel<8> : moe_route_plan_kernel<MAX_PER_LANE>;
+  LAUNCHED(launch_pdl(k, dim3(1), dim3(1024), 0, st, logits, ldl, T, E, top_k, shared, wts, idx, expert_map, Et, bt,
+                      offsets, static_cast<int4*>(tiles), n_tiles, max_tiles, perm, inv, err));
 }
 
 extern "C" int b200_moe_gather(const void* x, const int* perm, const int* n_valid, int n_pairs, int T, int P, int H,
                                void* xs, cudaStream_t st) {
   if (n_pairs <= 0) return 0;
-  moe_gather_kernel<<<n_pairs, 128, 0, st>>>(static_cast<const bf16*>(x), perm, n_valid, T, P, H,
-                                             static_cast<bf16*>(xs));
-  CHECK_LAUNCH();
+  LAUNCHED(launch_pdl(moe_gather_kernel, dim3(n_pairs), dim3(128), 0, st, static_cast<const bf16*>(x), perm, n_valid, T,
+                      P, H, static_cast<bf16*>(xs)));
 }
 
 extern "C" int b200_moe_combine(const void* pair_out, const float* wts, const int* inv, int T, int P, int H, void* out,
                                 float* out_f32, cudaStream_t st) {
   if (T <= 0) return 0;
-  moe_combine_kernel<<<T, 256, 0, st>>>(static_cast<const bf16*>(pair_out), wts, inv, P, H, static_cast<bf16*>(out),
-                                        out_f32);
-  CHECK_LAUNCH();
+  LAUNCHED(launch_pdl(moe_combine_kernel<false>, dim3(T), dim3(256), 0, st, static_cast<const bf16*>(pair_out), wts,
+                      inv, P, H, static_cast<bf16*>(out), out_f32, static_cast<const bf16*>(nullptr),
+                      static_cast<const bf16*>(nullptr), static_cast<bf16*>(nullptr), static_cast<bf16*>(nullptr), 0.f));
+}
+
+// Combine, residual add and the next (zero-centred) RMSNorm in one launch: res_out = bf16(res + combine),
+// y = norm(res_out) * (1 + norm_w). `res` may be null (res_out = combine).
+extern "C" int b200_moe_combine_norm(const void* pair_out, const float* wts, const int* inv, int T, int P, int H,
+                                     const void* res, const void* norm_w, void* res_out, void* y, float eps,
+                                     cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8) return -7;
+  LAUNCHED(launch_pdl(moe_combine_kernel<true>, dim3(T), dim3(256), H * sizeof(float), st,
+                      static_cast<const bf16*>(pair_out), wts, inv, P, H, static_cast<bf16*>(nullptr),
+                      static_cast<float*>(nullptr), static_cast<const bf16*>(res), static_cast<const bf16*>(norm_w),
+                      static_cast<bf16*>(res_out), static_cast<bf16*>(y), eps));
 }

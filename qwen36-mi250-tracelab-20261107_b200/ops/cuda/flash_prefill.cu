@@ -85,6 +85,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
+  pdl_wait();  // the tile table, positions and Q / K / V all come from kernels earlier in the stream
   const int4 tile = p.tiles[blockIdx.x];
   const int seg = tile.x, p0 = tile.y, seg_row0 = tile.z, seg_len = tile.w;
   const int kh = blockIdx.y;
@@ -123,6 +124,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  pdl_launch();  // this CTA holds its TMEM columns: the next kernel's CTAs may queue behind it
   const uint32_t tmem_S = tmem, tmem_O = tmem + 128;  // score tile of page i at tmem_S + (i & 1) * 64
 
   if (warp == 8) {
@@ -362,8 +364,7 @@ int fp_launch(const CUtensorMap& tq, const CUtensorMap& tkv, const FlashParams& 
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashCfg<D>::SMEM) != cudaSuccess) return -3;
     configured = true;
   }
-  kern<<<dim3(n_tiles, p.n_kv, gz), 288, FlashCfg<D>::SMEM, st>>>(tq, tkv, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(kern, dim3(n_tiles, p.n_kv, gz), dim3(288), FlashCfg<D>::SMEM, st, tq, tkv, p) == cudaSuccess ? 0 : -4;
 }
 }  // namespace
 

@@ -27,6 +27,8 @@ template <int KW>
 __global__ void gdn_conv_step_kernel(const bf16* mixed, int ld, const int* slots, bf16* conv_state, const bf16* conv_w,
                                      bf16* out, bf16* ring_conv, int C, int G) {
   // a thread owns 8 consecutive channels: 16-byte loads of the inputs, 48 / 64 contiguous bytes of state / weights
+  pdl_wait();
+  pdl_launch();
   const int b = blockIdx.y;
   const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (c >= C) return;
@@ -87,6 +89,8 @@ __global__ void gdn_conv_step_kernel(const bf16* mixed, int ld, const int* slots
 template <int KW>
 __global__ void gdn_conv_step_scalar_kernel(const bf16* mixed, int ld, const int* slots, bf16* conv_state, const bf16* conv_w,
                                      bf16* out, bf16* ring_conv, int C, int G) {
+  pdl_wait();
+  pdl_launch();
   const int b = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
@@ -161,16 +165,19 @@ gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
   const int hk = h / (HV / HK);
   const int key_dim = HK * DK;
   const int C = 2 * key_dim + HV * DV;
-  const int slot = slots[b];
-  float* S = rec_state + ((static_cast<size_t>(slot) * HV + h) * DK) * DV;
 
-  __shared__ float sq[DK], sk[DK];
+  __align__(16) __shared__ float sq[DK], sk[DK];
   __shared__ float red[4][DV][2];
   __shared__ float nred[4][3];
   __shared__ float wred[4 * DV / 32];
   __shared__ uint64_t bar;
   __shared__ int s_abort;
 
+  // The recurrent state was last written by an earlier decode step or prefill pass, never by the kernel just before
+  // this one (the conv step), and the slot table is an input of the whole pass: the tile is requested before the
+  // dependency wait, so its latency overlaps the tail of the conv kernel and this CTA's own row set-up.
+  const int slot = slots[b];
+  float* S = rec_state + ((static_cast<size_t>(slot) * HV + h) * DK) * DV;
   if (threadIdx.x == 0) {
     mbar_init(&bar, 1);
     s_abort = 0;
@@ -178,24 +185,33 @@ gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
     mbar_expect_tx(&bar, TILE_BYTES);
     bulk_load(sS, S, TILE_BYTES, &bar);
   }
+  pdl_wait();
+  pdl_launch();
   __syncthreads();
-  if (!mbar_wait(&bar, 0, err, ERR_WAIT_FULL, &s_abort)) return;  // status recorded; the state is left as it was
+  const float gw = __bfloat162float(gnorm_w[c]);
+  const float a_log = A_log[h], dtb = dt_bias[h];
 
   for (int j = 0; j < G; ++j) {
     const size_t row = static_cast<size_t>(b) * G + j;
     const bf16* co = conv_out + row * C;
-    // q and k of the key head: L2 normalise (q also scaled by DK^-0.5)
-    float ssq = 0.f, ssk = 0.f, sqk = 0.f;
+    // q and k of the key head: L2 normalise (q also scaled by DK^-0.5). Threads beyond DK contribute zeros; the
+    // shuffles stay unconditional (every thread of the CTA takes part, which the host build of this file needs)
+    float qv = 0.f, kv = 0.f;
     if (threadIdx.x < DK) {
-      const float qv = __bfloat162float(co[hk * DK + threadIdx.x]);
-      const float kv = __bfloat162float(co[key_dim + hk * DK + threadIdx.x]);
+      qv = __bfloat162float(co[hk * DK + threadIdx.x]);
+      kv = __bfloat162float(co[key_dim + hk * DK + threadIdx.x]);
       sq[threadIdx.x] = qv; sk[threadIdx.x] = kv;
-      ssq = qv * qv; ssk = kv * kv; sqk = qv * kv;
     }
-    ssq = warp_sum(ssq); ssk = warp_sum(ssk); sqk = warp_sum(sqk);
+    const float a = __bfloat162float(mixed[row * ld + a_off + h]);
+    const float bb = __bfloat162float(mixed[row * ld + b_off + h]);
+    const float v = __bfloat162float(co[2 * key_dim + h * DV + c]);
+    const float z = (p == 0) ? __bfloat162float(mixed[row * ld + z_off + h * DV + c]) : 0.f;
+    const float ssq = warp_sum(qv * qv), ssk = warp_sum(kv * kv), sqk = warp_sum(qv * kv);
     if ((threadIdx.x & 31) == 0 && threadIdx.x < DK) {
       nred[threadIdx.x >> 5][0] = ssq; nred[threadIdx.x >> 5][1] = ssk; nred[threadIdx.x >> 5][2] = sqk;
     }
+    const float decay = __expf(-__expf(a_log) * softplus_f(a + dtb));
+    const float beta = sigmoid_f(bb);
     __syncthreads();
     float tq = 0.f, tk = 0.f, tqk = 0.f;
 #pragma unroll
@@ -204,49 +220,68 @@ gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
     const float ks = rsqrtf(tk + 1e-6f);
     const float kq = tqk * qs * ks;  // k . q of the normalised vectors
 
-    const float a = __bfloat162float(mixed[row * ld + a_off + h]);
-    const float bb = __bfloat162float(mixed[row * ld + b_off + h]);
-    const float decay = __expf(-__expf(A_log[h]) * softplus_f(a + dt_bias[h]));
-    const float beta = sigmoid_f(bb);
+    // the first row's inputs are in registers: only now wait for the state tile
+    if (j == 0 && !mbar_wait(&bar, 0, err, ERR_WAIT_FULL, &s_abort)) return;  // status recorded; the state is left as it was
 
-    // pass 1: partial S^T k and S^T q over this thread's key rows (state decayed first)
+    // pass 1: partial S^T k and S^T q over this thread's key rows, on the raw tile and the raw k / q: the decay and
+    // the two normalisation factors are common to the whole sum and are applied once to its result. The column
+    // segment stays in registers for pass 2; k and q come as 16-byte broadcast reads.
     float pk = 0.f, pq = 0.f;
+    float colv[KP];
     float* col = sS + static_cast<size_t>(p * KP) * DV + c;
-#pragma unroll 8
-    for (int i = 0; i < KP; ++i) {
-      const float v = col[i * DV] * decay;
-      pk += v * (sk[p * KP + i] * ks);
-      pq += v * (sq[p * KP + i] * qs);
+    const float4* k4 = reinterpret_cast<const float4*>(sk + p * KP);
+    const float4* q4 = reinterpret_cast<const float4*>(sq + p * KP);
+#pragma unroll
+    for (int i4 = 0; i4 < KP / 4; ++i4) {
+      const float4 kk = k4[i4], qq = q4[i4];
+      const float ke[4] = {kk.x, kk.y, kk.z, kk.w}, qe[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float sv = col[(i4 * 4 + u) * DV];
+        colv[i4 * 4 + u] = sv;
+        pk += sv * ke[u];
+        pq += sv * qe[u];
+      }
     }
     red[p][c][0] = pk; red[p][c][1] = pq;
     __syncthreads();
-    const float kv_mem = (red[0][c][0] + red[1][c][0]) + (red[2][c][0] + red[3][c][0]);
-    const float sq_mem = (red[0][c][1] + red[1][c][1]) + (red[2][c][1] + red[3][c][1]);
-    const float v = __bfloat162float(co[2 * key_dim + h * DV + c]);
+    const float kv_mem = ((red[0][c][0] + red[1][c][0]) + (red[2][c][0] + red[3][c][0])) * (decay * ks);
+    const float sq_mem = ((red[0][c][1] + red[1][c][1]) + (red[2][c][1] + red[3][c][1])) * (decay * qs);
     const float delta = (v - kv_mem) * beta;
     // pass 2: S = decay * S + k delta^T, in place
-#pragma unroll 8
-    for (int i = 0; i < KP; ++i) col[i * DV] = col[i * DV] * decay + (sk[p * KP + i] * ks) * delta;
+    const float kd = ks * delta;
+#pragma unroll
+    for (int i4 = 0; i4 < KP / 4; ++i4) {
+      const float4 kk = k4[i4];
+      const float ke[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) col[(i4 * 4 + u) * DV] = colv[i4 * 4 + u] * decay + ke[u] * kd;
+    }
     const float o = sq_mem + delta * kq;  // = S_new^T q
 
     // gated RMSNorm over the head's DV outputs
     const bf16 ob = __float2bfloat16(o);
     const float of = __bfloat162float(ob);
-    float ss = (p == 0) ? of * of : 0.f;
-    ss = warp_sum(ss);
+    const float ss = warp_sum((p == 0) ? of * of : 0.f);
     if ((threadIdx.x & 31) == 0) wred[threadIdx.x >> 5] = ss;
-    if (ring_rec) proxy_fence();
+    proxy_fence();  // the tile as updated by this thread, for the bulk stores issued after the barrier
     __syncthreads();
-    float tot = 0.f;
-#pragma unroll
-    for (int i = 0; i < DV / 32; ++i) tot += wred[i];  // partition 0's warps only
-    if (p == 0) {
-      const float inv = rsqrtf(tot / DV + eps);
-      const float z = __bfloat162float(mixed[row * ld + z_off + h * DV + c]);
-      const float nb = __bfloat162float(__float2bfloat16(of * inv));
-      out[row * (HV * DV) + h * DV + c] = __float2bfloat16(__bfloat162float(gnorm_w[c]) * nb * silu_f(z));
+    if (j + 1 == G) {
+      // last row: the slot (and the ring entry of this row) get the tile while the outputs are still being formed
+      if (threadIdx.x == 0) {
+        if (ring_rec) bulk_store(ring_rec + (((static_cast<size_t>(b) * G + j) * HV + h) * DK) * DV, sS, TILE_BYTES);
+        bulk_store(S, sS, TILE_BYTES);
+      }
     }
-    if (ring_rec) {  // keep the state after this row; the tile may only change again once the store has read it
+    if (p == 0) {
+      float tot = 0.f;
+#pragma unroll
+      for (int i = 0; i < DV / 32; ++i) tot += wred[i];  // partition 0's warps only
+      const float inv = rsqrtf(tot / DV + eps);
+      const float nb = __bfloat162float(__float2bfloat16(of * inv));
+      out[row * (HV * DV) + h * DV + c] = __float2bfloat16(gw * nb * silu_f(z));
+    }
+    if (ring_rec && j + 1 < G) {  // keep the state after this row; the tile may only change again once the store has read it
       if (threadIdx.x == 0) {
         bulk_store(ring_rec + (((static_cast<size_t>(b) * G + j) * HV + h) * DK) * DV, sS, TILE_BYTES);
         bulk_store_wait_read();
@@ -254,12 +289,7 @@ gdn_step_kernel(const bf16* conv_out,   // [B*G, C]  q | k | v after conv+silu
       __syncthreads();
     }
   }
-  proxy_fence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    bulk_store(S, sS, TILE_BYTES);
-    bulk_store_wait_read();
-  }
+  if (threadIdx.x == 0) bulk_store_wait_read();  // shared memory must outlive the stores that read it
 }
 
 }  // namespace b200
@@ -311,13 +341,15 @@ extern "C" int b200_gdn_decode(const void* mixed, int ld, const int* slots, void
   const int key_dim = HK * DK, value_dim = HV * DV, C = 2 * key_dim + value_dim;
   if (KW != 4) return -7;
   if (C % 8 || ld % 8) {
-    gdn_conv_step_scalar_kernel<4><<<dim3((C + 127) / 128, B), 128, 0, st>>>(
-        static_cast<const bf16*>(mixed), ld, slots, static_cast<bf16*>(conv_state), static_cast<const bf16*>(conv_w),
-        static_cast<bf16*>(conv_out), static_cast<bf16*>(ring_conv), C, G);
+    if (launch_pdl(gdn_conv_step_scalar_kernel<4>, dim3((C + 127) / 128, B), dim3(128), 0, st,
+                   static_cast<const bf16*>(mixed), ld, slots, static_cast<bf16*>(conv_state),
+                   static_cast<const bf16*>(conv_w), static_cast<bf16*>(conv_out), static_cast<bf16*>(ring_conv), C,
+                   G) != cudaSuccess) return -4;
   } else {
-    gdn_conv_step_kernel<4><<<dim3((C / 8 + 63) / 64, B), 64, 0, st>>>(
-        static_cast<const bf16*>(mixed), ld, slots, static_cast<bf16*>(conv_state), static_cast<const bf16*>(conv_w),
-        static_cast<bf16*>(conv_out), static_cast<bf16*>(ring_conv), C, G);
+    if (launch_pdl(gdn_conv_step_kernel<4>, dim3((C / 8 + 63) / 64, B), dim3(64), 0, st,
+                   static_cast<const bf16*>(mixed), ld, slots, static_cast<bf16*>(conv_state),
+                   static_cast<const bf16*>(conv_w), static_cast<bf16*>(conv_out), static_cast<bf16*>(ring_conv), C,
+                   G) != cudaSuccess) return -4;
   }
   dim3 grid(HV, B);
   const int z_off = C, b_off = C + value_dim, a_off = C + value_dim + HV;
@@ -325,15 +357,17 @@ extern "C" int b200_gdn_decode(const void* mixed, int ld, const int* slots, void
   do {                                                                                                             \
     auto kern = gdn_step_kernel<DKV, DKV>;                                                                         \
     constexpr int smem = DKV * DKV * 4;                                                                            \
-    static bool configured = false;                                                                                \
-    if (!configured) {                                                                                             \
+    static bool configured[64] = {};                                                                               \
+    int dev = 0;                                                                                                   \
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -3;                                     \
+    if (!configured[dev]) {                                                                                        \
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3; \
-      configured = true;                                                                                           \
+      configured[dev] = true;                                                                                      \
     }                                                                                                              \
-    kern<<<grid, 4 * DKV, smem, st>>>(                                                                             \
-        static_cast<const bf16*>(conv_out), static_cast<const bf16*>(mixed), ld, z_off, b_off, a_off, slots,       \
-        static_cast<float*>(rec_state), A_log, dt_bias, static_cast<const bf16*>(gnorm_w),                         \
-        static_cast<bf16*>(out), ring_rec, HK, HV, G, eps, err);                                                   \
+    if (launch_pdl(kern, grid, dim3(4 * DKV), smem, st, static_cast<const bf16*>(conv_out),                        \
+                   static_cast<const bf16*>(mixed), ld, z_off, b_off, a_off, slots, static_cast<float*>(rec_state), \
+                   A_log, dt_bias, static_cast<const bf16*>(gnorm_w), static_cast<bf16*>(out), ring_rec, HK, HV, G, \
+                   eps, err) != cudaSuccess) return -4;                                                            \
   } while (0)
   if (DK == 128 && DV == 128) LAUNCH_STEP(128);
   else if (DK == 32 && DV == 32) LAUNCH_STEP(32);

@@ -26,6 +26,7 @@ namespace b200 {
 constexpr int BM = 128;  // weight rows per tile (TMEM lanes)
 constexpr int BK = 64;   // bf16 per operand row per stage (128 bytes)
 constexpr int UMMA_K = 16;
+constexpr int MAX_DEVICES = 64;  // per-device launch state (function attributes, SM counts)
 
 enum Epilogue : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_ARGMAX = 3, EPI_ALLREDUCE = 4, EPI_SCATTER = 5, EPI_REDUCE_SCATTER = 6 };
 
@@ -98,6 +99,9 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __shared__ int red_idx[4][BT > 0 ? BT : 1];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // The grouped tile table is written by the kernel just before this one: wait for it before the first read.
+  // Dense launches wait later (the producer streams the first weight stages before it waits).
+  if (GROUPED) pdl_wait();
   // Persistent tile loop: CTA b takes output tiles b, b + gridDim.x, ... (weight tile fastest, so CTAs that run
   // together share the activation tile). A split-K cluster takes the single tile its grid position names.
   const int tiles_n = (p.N + BM - 1) / BM;
@@ -147,6 +151,26 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     if (elect_one()) {
       int it = 0;  // k-blocks issued so far, over all tiles of this CTA
       bool live = true;
+      // Dense weights are written by nobody in the stream: fill the first stages of this CTA's first tile with weight
+      // tiles before waiting for the previous kernel (whose output is X), so that their latency hides behind its tail.
+      int pre = 0;
+      if (!GROUPED && !SPLIT && tile0 < total) {
+        int n0, by, expert, row0, nrows;
+        tile_geom(tile0, n0, by, expert, row0, nrows);
+        pre = num_k < C::STAGES ? num_k : C::STAGES;
+        for (int kb = 0; kb < pre; ++kb) {
+          uint8_t* st = smem + kb * C::STAGE_BYTES;
+          mbar_expect_tx(&full[kb], C::STAGE_BYTES);
+          if (p.packed) {
+            tma_load_2d(st, &tmW, &full[kb], 0, ((n0 / BM) * num_k_all + kb) * (BM * C::A_TILES));
+          } else {
+            tma_load_2d(st, &tmW, &full[kb], kb * BK, n0);
+            if (EPI == EPI_SILU_MUL) tma_load_2d(st + C::A_BYTES, &tmW, &full[kb], kb * BK, p.up_offset + n0);
+          }
+        }
+      }
+      pdl_wait();
+      pdl_launch();
       for (int tile = tile0; tile < total && live; tile += tstep) {
       int n0, by, expert, row0, nrows;
       tile_geom(tile, n0, by, expert, row0, nrows);
@@ -156,8 +180,9 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       for (int kb = 0; kb < num_k; ++kb, ++it) {
         const int s = it % C::STAGES;
         const uint32_t ph = (it / C::STAGES) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1, p.err, ERR_WAIT_EMPTY, abort_flag)) { live = false; break; }
         uint8_t* st = smem + s * C::STAGE_BYTES;
+        if (it >= pre) {
+        if (!mbar_wait(&empty[s], ph ^ 1, p.err, ERR_WAIT_EMPTY, abort_flag)) { live = false; break; }
         mbar_expect_tx(&full[s], C::STAGE_BYTES);
         if (p.packed) {
           tma_load_2d(st, &tmW, &full[s], 0,
@@ -168,6 +193,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         } else {
           tma_load_2d(st, &tmW, &full[s], (kb0 + kb) * BK, n0);
           if (EPI == EPI_SILU_MUL) tma_load_2d(st + C::A_BYTES, &tmW, &full[s], (kb0 + kb) * BK, p.up_offset + n0);
+        }
         }
         tma_load_2d(st + C::A_TILES * C::A_BYTES, &tmX, &full[s], (kb0 + kb) * BK, row0);
       }
@@ -209,6 +235,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     if (SPLIT) { __syncwarp(); cluster_sync(); }
   } else {
     // ---------------- epilogue: warp q owns TMEM lanes [32q, 32q+32)
+    pdl_wait();  // first global write of the CTA comes from here
     const int q = warp & 3;
     int lt = 0;
     for (int tile = tile0; tile < total; tile += tstep, ++lt) {
@@ -421,6 +448,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 // Reduce the LM-head partials of each row over the vocabulary tiles, first maximum wins.
 __global__ void argmax_finish_kernel(const float* part_max, const int* part_idx, int n_tiles, int T, int64_t* out,
                                      float* out_val) {
+  pdl_wait();
+  pdl_launch();
   const int t = blockIdx.x;
   float m = -INFINITY; int idx = 0x7fffffff;
   for (int i = threadIdx.x; i < n_tiles; i += blockDim.x) {
@@ -505,10 +534,12 @@ template <int BT, int EPI, bool GROUPED>
 static int launch_split(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int grid_y, cudaStream_t st) {
   using C = Cfg<BT, EPI>;
   auto kern = gemm_swapab_kernel<BT, EPI, GROUPED, true>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[MAX_DEVICES] = {};  // a function attribute is set per device
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -3;
+  if (!configured[dev]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess) return -3;
-    configured = true;
+    configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.N + BM - 1) / BM, grid_y, p.splits);
@@ -534,22 +565,25 @@ static int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams
     if (p.splits > 1) return launch_split<BT, EPI, GROUPED>(tw, tx, p, grid_y, st);
   }
   auto kern = gemm_swapab_kernel<BT, EPI, GROUPED, false>;
-  static bool configured = false;
-  if (!configured) {
+  // per device: the shared-memory attribute is set on the device that is current, and the persistent grid is sized
+  // from that device's SM count (a process may drive several GPUs)
+  static bool configured[MAX_DEVICES] = {};
+  static int resident_of[MAX_DEVICES] = {};  // CTAs the device holds at once: the persistent grid is never larger
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -3;
+  if (!configured[dev]) {
+    int sms = 0;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess) return -3;
-    configured = true;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -3;
+    resident_of[dev] = sms * C::CTAS_PER_SM;
+    configured[dev] = true;
   }
-  static int resident = 0;  // CTAs the device holds at once: the persistent grid is never larger
-  if (!resident) {
-    int dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -3;
-    resident = sms * C::CTAS_PER_SM;
-  }
+  const int resident = resident_of[dev];
   GemmParams q = p;
   q.grid_y = grid_y;
   const long long tiles = static_cast<long long>((p.N + BM - 1) / BM) * grid_y;
-  kern<<<static_cast<unsigned>(tiles < resident ? tiles : resident), 192, C::SMEM, st>>>(tw, tx, q);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(kern, dim3(static_cast<unsigned>(tiles < resident ? tiles : resident)), dim3(192), C::SMEM, st, tw,
+                    tx, q) == cudaSuccess ? 0 : -4;
 }
 
 template <int EPI, bool GROUPED>
@@ -696,8 +730,8 @@ extern "C" int b200_gemm_gathered(const void* X, const void* W, void* out, int T
 extern "C" int b200_argmax_finish(const float* part_max, const int* part_idx, int n_tiles, int T, int64_t* out,
                                   float* out_val, cudaStream_t st) {
   if (T <= 0) return 0;
-  argmax_finish_kernel<<<T, 256, 0, st>>>(part_max, part_idx, n_tiles, T, out, out_val);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(argmax_finish_kernel, dim3(T), dim3(256), 0, st, part_max, part_idx, n_tiles, T, out, out_val) ==
+                 cudaSuccess ? 0 : -4;
 }
 
 // ------------------------------------------------------------------ allocation-free greedy head
@@ -710,7 +744,7 @@ extern "C" int b200_argmax_finish(const float* part_max, const int* part_idx, in
 namespace {
 constexpr size_t NOALLOC_PART_ELEMS = static_cast<size_t>(B200_NOALLOC_MAX_ROWS) * B200_NOALLOC_MAX_TILES;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_PART_ELEMS * (sizeof(float) + sizeof(int))];
-constexpr int NOALLOC_MAX_DEVICES = 64;
+constexpr int NOALLOC_MAX_DEVICES = MAX_DEVICES;
 void* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
 }  // namespace
 

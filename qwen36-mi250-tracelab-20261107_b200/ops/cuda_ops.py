@@ -60,7 +60,9 @@ class _Sig:
     b200_embed = [P, P, P, I, I, I, P]
     b200_add_rmsnorm = [P, P, P, P, P, I, I, F, I, P]
     b200_moe_route = [P, I, I, I, I, I, P, P, P, I, P, P]
-    b200_moe_plan = [P, P, I, I, I, P, P, P, P, I, P, P, P, P]
+    b200_moe_plan = [P, I, I, I, P, P, P, I, P, P, P, P]
+    b200_moe_route_plan = [P, I, I, I, I, I, P, P, P, I, I, P, P, P, I, P, P, P, P]
+    b200_moe_combine_norm = [P, P, P, I, I, I, P, P, P, P, F, P]
     b200_moe_gather = [P, P, P, I, I, I, I, P, P]
     b200_moe_combine = [P, P, P, I, I, I, P, P, P]
     b200_gdn_decode = [P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P]
@@ -292,14 +294,23 @@ def moe_bt(T: int, pairs_per_row: int, n_experts: int) -> int:
     return 128
 
 
+FUSED_MOE_NORM = True  # Model._moe_norm: combine + residual add + next RMSNorm as one kernel
+ROUTE_PLAN_MAX_ROWS = 32  # up to one row per warp of a single CTA, routing and the expert plan run as one launch
+# (measured at 128 rows: 30 us in one CTA against 5 + 3 us as a grid of warps followed by the plan CTA)
+
+
 def moe_block(x: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, n_experts: int,
               top_k: int, shared_merged: bool, expert_map: torch.Tensor | None = None,
-              partial_f32: bool = False, logits: torch.Tensor | None = None) -> torch.Tensor:
+              partial_f32: bool = False, logits: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+              norm_w: torch.Tensor | None = None, eps: float = 1e-6):
     """Router GEMM, top-k, expert-sorted grouped gate/up + SiLU-mul, grouped down, weighted combine.
 
     With ``expert_map`` (global expert id -> local slot or -1) only the pairs of locally hosted experts
     are computed; ``partial_f32`` returns the fp32 partial sum that the caller adds across ranks. ``logits``
-    (fp32 ``[T, rows of router]``) skips the router GEMM when the caller has already run it."""
+    (fp32 ``[T, rows of router]``) skips the router GEMM when the caller has already run it. With ``norm_w`` the
+    combine kernel also adds ``residual`` and applies the next RMSNorm, and the call returns
+    ``(new residual, normed)`` exactly as ``add_rmsnorm(moe_out, residual, norm_w, eps)`` would (reference:
+    the fused down + combine + residual kernel, ``engine/fast/fused.py:635-692``)."""
     T, H = x.shape
     dev = x.device
     Et = w_gate_up.shape[0]
@@ -313,18 +324,21 @@ def moe_block(x: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_
         logits = linear(x, router, out_dtype=torch.float32)
     wts = torch.empty(T, Pn, dtype=torch.float32, device=dev)
     idx = torch.empty(T, Pn, dtype=torch.int32, device=dev)
-    ints = torch.empty(3 * (Et + 1) + 1 + 2 * n_pairs, dtype=torch.int32, device=dev)
-    counts, offsets, cursors = ints[: Et + 1], ints[Et + 1 : 2 * Et + 2], ints[2 * Et + 2 : 3 * Et + 3]
-    n_tiles = ints[3 * Et + 3 : 3 * Et + 4]
-    perm = ints[3 * Et + 4 : 3 * Et + 4 + n_pairs]
-    inv = ints[3 * Et + 4 + n_pairs :]
-    _check(L.b200_moe_route(_ptr(logits), logits.stride(0), T, n_experts, top_k, int(shared_merged), _ptr(wts),
-                            _ptr(idx), _ptr(counts), Et + 1, _ptr(expert_map), st), "moe_route")
+    ints = torch.empty(Et + 2 + 2 * n_pairs, dtype=torch.int32, device=dev)
+    offsets, n_tiles = ints[: Et + 1], ints[Et + 1 : Et + 2]
+    perm, inv = ints[Et + 2 : Et + 2 + n_pairs], ints[Et + 2 + n_pairs :]
     bt = moe_bt(T, Pn, n_experts)
     max_tiles = min(Et, n_pairs) + n_pairs // bt + 1
     tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device=dev)
-    _check(L.b200_moe_plan(_ptr(counts), _ptr(idx), n_pairs, Et, bt, _ptr(offsets), _ptr(cursors), _ptr(tiles),
-                           _ptr(n_tiles), max_tiles, _ptr(perm), _ptr(inv), _ptr(err), st), "moe_plan")
+    if T <= ROUTE_PLAN_MAX_ROWS:
+        _check(L.b200_moe_route_plan(_ptr(logits), logits.stride(0), T, n_experts, top_k, int(shared_merged), _ptr(wts),
+                                     _ptr(idx), _ptr(expert_map), Et, bt, _ptr(offsets), _ptr(tiles), _ptr(n_tiles),
+                                     max_tiles, _ptr(perm), _ptr(inv), _ptr(err), st), "moe_route_plan")
+    else:
+        _check(L.b200_moe_route(_ptr(logits), logits.stride(0), T, n_experts, top_k, int(shared_merged), _ptr(wts),
+                                _ptr(idx), None, 0, _ptr(expert_map), st), "moe_route")
+        _check(L.b200_moe_plan(_ptr(idx), n_pairs, Et, bt, _ptr(offsets), _ptr(tiles), _ptr(n_tiles), max_tiles,
+                               _ptr(perm), _ptr(inv), _ptr(err), st), "moe_plan")
     xs = torch.empty(n_pairs, H, dtype=x.dtype, device=dev)
     _check(L.b200_moe_gather(_ptr(x), _ptr(perm), _ptr(offsets[Et:]), n_pairs, T, Pn, H, _ptr(xs), st), "moe_gather")
     act = torch.empty(n_pairs, inter, dtype=x.dtype, device=dev)
@@ -337,6 +351,12 @@ def moe_block(x: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_
                                _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err), split_k(H, inter, grouped=True),
                                is_packed(w_down), st),
            "gemm_grouped(down)")
+    if norm_w is not None and not partial_f32:
+        new_res = torch.empty(T, H, dtype=x.dtype, device=dev)
+        y = torch.empty(T, H, dtype=x.dtype, device=dev)
+        _check(L.b200_moe_combine_norm(_ptr(pair_out), _ptr(wts), _ptr(inv), T, Pn, H, _ptr(residual), _ptr(norm_w),
+                                       _ptr(new_res), _ptr(y), eps, st), "moe_combine_norm")
+        return new_res, y
     out = torch.empty(T, H, dtype=torch.float32 if partial_f32 else x.dtype, device=dev)
     _check(L.b200_moe_combine(_ptr(pair_out), _ptr(wts), _ptr(inv), T, Pn, H, None if partial_f32 else _ptr(out),
                               _ptr(out) if partial_f32 else None, st), "moe_combine")

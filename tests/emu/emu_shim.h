@@ -26,6 +26,7 @@ namespace b200 {
 
 struct Dim3 { unsigned x = 1, y = 1, z = 1; };
 struct alignas(16) uint4 { unsigned x, y, z, w; };
+struct alignas(16) float4 { float x, y, z, w; };
 inline thread_local Dim3 threadIdx, blockIdx;
 inline Dim3 blockDim, gridDim;
 inline std::barrier<>* cta_barrier = nullptr;
@@ -80,6 +81,8 @@ inline void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t*) { s
 inline void bulk_store(void* dst, const void* src, uint32_t bytes) { std::memcpy(dst, src, bytes); }
 inline void bulk_store_wait_read() {}
 inline void proxy_fence() {}
+inline void pdl_wait() {}
+inline void pdl_launch() {}
 
 // Run `body` as one CTA of `threads` threads at block index (bx, by).
 inline void run_cta(unsigned threads, unsigned bx, unsigned by, const std::function<void()>& body) {

@@ -383,3 +383,19 @@ def test_packed_weights_give_the_same_bits_moe(C, T, E, k, H, I):
                       C.pack_weight(wd.clone()), E, k, True)
     assert torch.equal(got, plain)
     C.check_errors(x.device)
+
+
+@pytest.mark.parametrize("T,E,k,H,I", [(5, 8, 2, 128, 64), (128, 64, 8, 2048, 512), (300, 16, 4, 256, 128)])
+def test_moe_block_with_fused_residual_norm(C, T, E, k, H, I):
+    """Combine + residual add + next RMSNorm in one kernel gives the bits of the separate norm kernel."""
+    x, res = _bf(T, H, seed=31), _bf(T, H, seed=32)
+    router = _bf(E + 1, H, scale=0.3, seed=33)
+    wgu, wd = _bf(E + 1, 2 * I, H, scale=0.05, seed=34), _bf(E + 1, H, I, scale=0.05, seed=35)
+    nw = _bf(H, scale=0.1, seed=36)
+    want_res, want_y = C.add_rmsnorm(C.moe_block(x, router, wgu, wd, E, k, True), res, nw, 1e-6)
+    got_res, got_y = C.moe_block(x, router, wgu, wd, E, k, True, residual=res, norm_w=nw, eps=1e-6)
+    assert torch.equal(got_res, want_res) and torch.equal(got_y, want_y)
+    want_res, want_y = C.add_rmsnorm(C.moe_block(x, router, wgu, wd, E, k, True), None, nw, 1e-6)
+    got_res, got_y = C.moe_block(x, router, wgu, wd, E, k, True, residual=None, norm_w=nw, eps=1e-6)
+    assert torch.equal(got_res, want_res) and torch.equal(got_y, want_y)
+    C.check_errors(x.device)
