@@ -102,17 +102,17 @@ def case_gemm_grouped(small):
     L, st = C.lib(), torch.cuda.current_stream().cuda_stream
     err = C.err_word(torch.device("cuda"))
     assert L.b200_moe_plan(idx.data_ptr(), n_pairs, E + 1, bt, offsets.data_ptr(), tiles.data_ptr(), n_tiles.data_ptr(),
-                           max_tiles, perm.data_ptr(), inv.data_ptr(), err.data_ptr(), st) == 0
+                           max_tiles, perm.data_ptr(), inv.data_ptr(), err.data_ptr(), P, None, st) == 0
     xs, act, out = bf(n_pairs, H), torch.empty(n_pairs, I, dtype=torch.bfloat16, device="cuda"), torch.empty(
         n_pairs, H, dtype=torch.bfloat16, device="cuda")
 
     def up():
         L.b200_gemm_grouped(xs.data_ptr(), wgu.data_ptr(), act.data_ptr(), n_pairs, E + 1, I, 2 * I, H, I, 2, I, bt,
-                            tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), 1, C.is_packed(wgu), st)
+                            tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), 1, C.is_packed(wgu), None, 0, st)
 
     def down():
         L.b200_gemm_grouped(act.data_ptr(), wd.data_ptr(), out.data_ptr(), n_pairs, E + 1, H, H, I, H, 0, 0, bt,
-                            tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), 1, C.is_packed(wd), st)
+                            tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), 1, C.is_packed(wd), None, 0, st)
 
     report("grouped_gate_up_silu", timed(up), wgu.numel() * 2, 2 * n_pairs * 2 * I * H, experts=E)
     report("grouped_down", timed(down), wd.numel() * 2, 2 * n_pairs * I * H, experts=E)

@@ -159,7 +159,7 @@ __global__ void route_kernel(const float* logits, int ldl, int T, int E, int top
 // the position of every pair in the expert-sorted order (perm / inv). The order inside an expert does not influence
 // any output value: every sorted row is computed on its own.
 __device__ void plan_scatter(const int* idx, int n_pairs, int Et, int bt, int* offsets, int4* tiles, int* n_tiles,
-                             int max_tiles, int* perm, int* inv, int* err) {
+                             int max_tiles, int* perm, int* inv, int* err, int P, int* src_rows) {
   __shared__ int s_count[1024], s_off[1024], s_cur[1024];
   __shared__ int w_rows[32], w_tiles[32];
   const int e = threadIdx.x, lane = e & 31, w = e >> 5;
@@ -212,15 +212,16 @@ __device__ void plan_scatter(const int* idx, int n_pairs, int Et, int bt, int* o
     const int pos = s_off[x] + atomicAdd(&s_cur[x], 1);
     perm[pos] = i;
     inv[i] = pos;
+    if (src_rows) src_rows[pos] = i / P;  // the activation row behind sorted position pos (for a gathering GEMM)
   }
 }
 
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int* idx, int n_pairs, int Et, int bt, int* offsets, int4* tiles, int* n_tiles, int max_tiles,
-                int* perm, int* inv, int* err) {
+                int* perm, int* inv, int* err, int P, int* src_rows) {
   pdl_wait();
   pdl_launch();
-  plan_scatter(idx, n_pairs, Et, bt, offsets, tiles, n_tiles, max_tiles, perm, inv, err);
+  plan_scatter(idx, n_pairs, Et, bt, offsets, tiles, n_tiles, max_tiles, perm, inv, err, P, src_rows);
 }
 
 // Decode-size batches: routing of every row (one warp each, 32 warps) and the plan in ONE launch.
@@ -228,7 +229,7 @@ template <int PER_LANE>
 __global__ void __launch_bounds__(1024)
 moe_route_plan_kernel(const float* logits, int ldl, int T, int E, int top_k, int shared, float* wts, int* idx,
                       const int* expert_map, int Et, int bt, int* offsets, int4* tiles, int* n_tiles, int max_tiles,
-                      int* perm, int* inv, int* err) {
+                      int* perm, int* inv, int* err, int* src_rows) {
   pdl_wait();
   pdl_launch();
   const int P = top_k + (shared ? 1 : 0);
@@ -237,7 +238,7 @@ moe_route_plan_kernel(const float* logits, int ldl, int T, int E, int top_k, int
     route_row<PER_LANE>(logits + static_cast<size_t>(r) * ldl, E, top_k, shared, wts + static_cast<size_t>(r) * P,
                         idx + static_cast<size_t>(r) * P, expert_map, nullptr, lane);
   __syncthreads();  // this CTA wrote idx: visible to all its threads after the barrier
-  plan_scatter(idx, T * P, Et, bt, offsets, tiles, n_tiles, max_tiles, perm, inv, err);
+  plan_scatter(idx, T * P, Et, bt, offsets, tiles, n_tiles, max_tiles, perm, inv, err, P, src_rows);
 }
 
 // x_sorted[pos] = x[perm[pos] / P]
@@ -359,22 +360,24 @@ extern "C" int b200_moe_route(const float* logits, int ldl, int T, int E, int to
 }
 
 // Expert-sorted layout of the (row, pair) table `idx` [n_pairs]: offsets [Et + 1], tile table, perm / inv [n_pairs].
+// `src_rows` (optional, [n_pairs]) receives row = pair / P of every sorted position.
 extern "C" int b200_moe_plan(const int* idx, int n_pairs, int Et, int bt, int* offsets, void* tiles, int* n_tiles,
-                             int max_tiles, int* perm, int* inv, int* err, cudaStream_t st) {
-  if (Et > 1024) return -7;
+                             int max_tiles, int* perm, int* inv, int* err, int P, int* src_rows, cudaStream_t st) {
+  if (Et > 1024 || P <= 0) return -7;
   LAUNCHED(launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, st, idx, n_pairs, Et, bt, offsets,
-                      static_cast<int4*>(tiles), n_tiles, max_tiles, perm, inv, err));
+                      static_cast<int4*>(tiles), n_tiles, max_tiles, perm, inv, err, P, src_rows));
 }
 
 // Routing and plan of a decode-size batch (T <= 256 rows) in one launch.
 extern "C" int b200_moe_route_plan(const float* logits, int ldl, int T, int E, int top_k, int shared, float* wts,
                                    int* idx, const int* expert_map, int Et, int bt, int* offsets, void* tiles,
-                                   int* n_tiles, int max_tiles, int* perm, int* inv, int* err, cudaStream_t st) {
+                                   int* n_tiles, int max_tiles, int* perm, int* inv, int* err, int* src_rows,
+                                   cudaStream_t st) {
   if (T <= 0) return 0;
   if (E > 32 * MAX_PER_LANE || top_k > 32 || Et > 1024) return -7;
   auto k = E <= 256 ? moe_route_plan_kernel<8> : moe_route_plan_kernel<MAX_PER_LANE>;
   LAUNCHED(launch_pdl(k, dim3(1), dim3(1024), 0, st, logits, ldl, T, E, top_k, shared, wts, idx, expert_map, Et, bt,
-                      offsets, static_cast<int4*>(tiles), n_tiles, max_tiles, perm, inv, err));
+                      offsets, static_cast<int4*>(tiles), n_tiles, max_tiles, perm, inv, err, src_rows));
 }
 
 extern "C" int b200_moe_gather(const void* x, const int* perm, const int* n_valid, int n_pairs, int T, int P, int H,

@@ -53,6 +53,11 @@ struct GemmParams {
   int y_rot;         // dense sequence-parallel GEMMs: token tile = (blockIdx.y + y_rot) % gridDim.y, so that each rank
                      // starts with the tiles whose data (or whose consumer) is furthest from being the bottleneck
   int grid_y;        // dense: number of token tiles (set by the launcher)
+  const int* gather_rows;  // grouped, token tiles <= 32 rows: sorted position -> row of `gx`; the producer warp then
+                     // fetches each activation row by index (16-byte async copies into the swizzled operand layout)
+                     // instead of reading an expert-sorted copy through the tensor map
+  const bf16* gx;    // gather source [rows, ldgx]
+  int ldgx;
   int packed;        // W is stored tile by tile: [expert][weight tile][k-block][128 * A_TILES rows][64], each (tile,
                      // k-block) one contiguous 16 KB (32 KB with the up half) run, so a stage is one sequential DRAM read
   int w_tiles;       // packed: weight tiles per expert
@@ -119,7 +124,10 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const int num_k = SPLIT ? max(0, min(num_k_all, kb0 + k_per) - kb0) : num_k_all;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    // a gathering producer: lane 0's expect_tx arrival for the weight tile plus one arrival per lane when that
+    // lane's row copies have landed
+    const uint32_t full_count = (GROUPED && BT <= 32 && p.gather_rows != nullptr) ? 33 : 1;
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], full_count); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
     *abort_flag = 0;
     mbar_fence_init();
@@ -147,7 +155,55 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
   };
 
-  if (warp == 0) {
+  if (warp == 0 && GROUPED && BT <= 32 && p.gather_rows != nullptr) {
+    // ---------------- gathering producer (all 32 lanes): weights by TMA from lane 0, activation rows by index.
+    // Chunk q = lane + 32 i of a k-block is bytes [16 (q & 7), +16) of tile row q >> 3; it lands where the 128-byte
+    // swizzle of the K-major operand layout puts it: row r at (r >> 3) * 1024 + (r & 7) * 128, chunk j at
+    // ((j ^ (r & 7)) * 16). Rows beyond the tile's row count are left as they are: an MMA column depends on its own
+    // row only, and the epilogue never stores those columns.
+    constexpr int PER_LANE = BT / 4 > 0 ? BT / 4 : 1;
+    int it = 0;
+    bool live = true;
+    const int j = lane & 7;
+    for (int tile = tile0; tile < total && live; tile += tstep) {
+      int n0, by, expert, row0, nrows;
+      tile_geom(tile, n0, by, expert, row0, nrows);
+      const bf16* src[PER_LANE];
+#pragma unroll
+      for (int i = 0; i < PER_LANE; ++i) {
+        const int r = (lane >> 3) + 4 * i;
+        const int g = r < nrows ? p.gather_rows[row0 + r] : -1;
+        src[i] = g >= 0 ? p.gx + static_cast<size_t>(g) * p.ldgx + j * 8 : nullptr;
+      }
+      for (int kb = 0; kb < num_k; ++kb, ++it) {
+        const int s = it % C::STAGES;
+        const uint32_t ph = (it / C::STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, p.err, ERR_WAIT_EMPTY, abort_flag)) { live = false; break; }
+        uint8_t* st = smem + s * C::STAGE_BYTES;
+        if (lane == 0) {
+          mbar_expect_tx(&full[s], C::A_TILES * C::A_BYTES);
+          if (p.packed) {
+            tma_load_2d(st, &tmW, &full[s], 0,
+                        ((expert * p.w_tiles + n0 / BM) * num_k_all + kb0 + kb) * (BM * C::A_TILES));
+          } else {
+            tma_load_3d(st, &tmW, &full[s], (kb0 + kb) * BK, n0, expert);
+            if (EPI == EPI_SILU_MUL) tma_load_3d(st + C::A_BYTES, &tmW, &full[s], (kb0 + kb) * BK, p.up_offset + n0, expert);
+          }
+        }
+        const uint32_t xb = smem_u32(st + C::A_TILES * C::A_BYTES);
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) {
+          const int r = (lane >> 3) + 4 * i;
+          if (src[i] != nullptr) {
+            const uint32_t dst = xb + (r >> 3) * 1024 + (r & 7) * 128 + ((j ^ (r & 7)) << 4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src[i] + (kb0 + kb) * BK) : "memory");
+          }
+        }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[s])) : "memory");
+      }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");  // no copy of this lane may outlive the CTA's shared memory
+  } else if (warp == 0) {
     if (elect_one()) {
       int it = 0;  // k-blocks issued so far, over all tiles of this CTA
       bool live = true;
@@ -216,6 +272,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const uint32_t ph = (it / C::STAGES) & 1;
         ok = mbar_wait(&full[s], ph, p.err, ERR_WAIT_FULL, abort_flag);
         if (!ok) break;
+        // rows that the gathering producer wrote through the generic proxy must be visible to the tensor core's reads
+        if (GROUPED && BT <= 32 && p.gather_rows != nullptr) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
         const uint32_t b_addr = a_addr + C::A_TILES * C::A_BYTES;
@@ -640,13 +698,22 @@ extern "C" int b200_gemm_dense(const void* X, const void* W, void* out, int T, i
 // [tiles[i].y, +tiles[i].z) of expert tiles[i].x; W is [E, rows, K]. `max_tiles` bounds the grid.
 extern "C" int b200_gemm_grouped(const void* X, const void* W, void* out, int cap, int E, int N, int w_rows, int K,
                                  int ldo, int epi, int up_offset, int bt, const void* tiles, const int* n_tiles,
-                                 int max_tiles, int* err, int splits, int packed, cudaStream_t st) {
+                                 int max_tiles, int* err, int splits, int packed, const int* gather_rows, int ldx,
+                                 cudaStream_t st) {
+  // gather_rows != null (token tiles of at most 32 rows): X is [any rows, ldx] and sorted position i reads row
+  // gather_rows[i] of it; otherwise X is the expert-sorted buffer [cap, K] itself.
   if (max_tiles <= 0) return 0;
+  if (gather_rows != nullptr && (bt > 32 || splits > 1 || ldx % 8)) return -7;
   if (splits < 1 || splits > 8 || splits > (K + BK - 1) / BK) splits = 1;
   CUtensorMap tw, tx;
   GemmParams p{N, K, cap, ldo, out, reinterpret_cast<const int4*>(tiles), n_tiles, up_offset, nullptr, nullptr, err, nullptr, CommCtx{}, 0, nullptr, nullptr, splits, nullptr, {}};
   if (weight_map(&tw, W, E, N, w_rows, K, K, epi == EPI_SILU_MUL, packed, &p)) return -1;
-  if (make_map(&tx, X, K, cap, 0, K, 0, bt)) return -1;
+  if (gather_rows != nullptr) {
+    p.gather_rows = gather_rows;
+    p.gx = static_cast<const bf16*>(X);
+    p.ldgx = ldx;
+    if (make_map(&tx, X, K, bt, 0, ldx, 0, bt)) return -1;  // unused by the gathering producer, but a valid map
+  } else if (make_map(&tx, X, K, cap, 0, K, 0, bt)) return -1;
   switch (epi) {
     case EPI_BF16: return dispatch_bt<EPI_BF16, true>(bt, tw, tx, p, max_tiles, st);
     case EPI_SILU_MUL: return dispatch_bt<EPI_SILU_MUL, true>(bt, tw, tx, p, max_tiles, st);

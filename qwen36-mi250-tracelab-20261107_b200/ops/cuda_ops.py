@@ -55,13 +55,13 @@ P, I, F = c_void_p, c_int, c_float
 class _Sig:
     b200_pick_bt = [I]
     b200_gemm_dense = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, P, I, I, P]
-    b200_gemm_grouped = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, I, P, I, I, P]
+    b200_gemm_grouped = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, I, P, I, I, P, I, P]
     b200_argmax_finish = [P, P, I, I, P, P, P]
     b200_embed = [P, P, P, I, I, I, P]
     b200_add_rmsnorm = [P, P, P, P, P, I, I, F, I, P]
     b200_moe_route = [P, I, I, I, I, I, P, P, P, I, P, P]
-    b200_moe_plan = [P, I, I, I, P, P, P, I, P, P, P, P]
-    b200_moe_route_plan = [P, I, I, I, I, I, P, P, P, I, I, P, P, P, I, P, P, P, P]
+    b200_moe_plan = [P, I, I, I, P, P, P, I, P, P, P, I, P, P]
+    b200_moe_route_plan = [P, I, I, I, I, I, P, P, P, I, I, P, P, P, I, P, P, P, P, P]
     b200_moe_combine_norm = [P, P, P, I, I, I, P, P, P, P, F, P]
     b200_moe_gather = [P, P, P, I, I, I, I, P, P]
     b200_moe_combine = [P, P, P, I, I, I, P, P, P]
@@ -294,6 +294,7 @@ def moe_bt(T: int, pairs_per_row: int, n_experts: int) -> int:
     return 128
 
 
+GATHER_MAX_BT = int(__import__("os").environ.get("ENGINE_MOE_GATHER_BT", "32"))  # 0 turns the in-GEMM row gather off
 FUSED_MOE_NORM = True  # Model._moe_norm: combine + residual add + next RMSNorm as one kernel
 ROUTE_PLAN_MAX_ROWS = 32  # up to one row per warp of a single CTA, routing and the expert plan run as one launch
 # (measured at 128 rows: 30 us in one CTA against 5 + 3 us as a grid of warps followed by the plan CTA)
@@ -324,32 +325,40 @@ def moe_block(x: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_
         logits = linear(x, router, out_dtype=torch.float32)
     wts = torch.empty(T, Pn, dtype=torch.float32, device=dev)
     idx = torch.empty(T, Pn, dtype=torch.int32, device=dev)
-    ints = torch.empty(Et + 2 + 2 * n_pairs, dtype=torch.int32, device=dev)
+    ints = torch.empty(Et + 2 + 3 * n_pairs, dtype=torch.int32, device=dev)
     offsets, n_tiles = ints[: Et + 1], ints[Et + 1 : Et + 2]
-    perm, inv = ints[Et + 2 : Et + 2 + n_pairs], ints[Et + 2 + n_pairs :]
+    perm, inv = ints[Et + 2 : Et + 2 + n_pairs], ints[Et + 2 + n_pairs : Et + 2 + 2 * n_pairs]
     bt = moe_bt(T, Pn, n_experts)
+    # small token tiles: the gate/up GEMM fetches each activation row by index, so no expert-sorted copy of x is made
+    gather = bt <= GATHER_MAX_BT and x.stride(0) % 8 == 0 and x.stride(1) == 1
+    src_rows = ints[Et + 2 + 2 * n_pairs :] if gather else None
     max_tiles = min(Et, n_pairs) + n_pairs // bt + 1
     tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device=dev)
     if T <= ROUTE_PLAN_MAX_ROWS:
         _check(L.b200_moe_route_plan(_ptr(logits), logits.stride(0), T, n_experts, top_k, int(shared_merged), _ptr(wts),
                                      _ptr(idx), _ptr(expert_map), Et, bt, _ptr(offsets), _ptr(tiles), _ptr(n_tiles),
-                                     max_tiles, _ptr(perm), _ptr(inv), _ptr(err), st), "moe_route_plan")
+                                     max_tiles, _ptr(perm), _ptr(inv), _ptr(err), _ptr(src_rows), st), "moe_route_plan")
     else:
         _check(L.b200_moe_route(_ptr(logits), logits.stride(0), T, n_experts, top_k, int(shared_merged), _ptr(wts),
                                 _ptr(idx), None, 0, _ptr(expert_map), st), "moe_route")
         _check(L.b200_moe_plan(_ptr(idx), n_pairs, Et, bt, _ptr(offsets), _ptr(tiles), _ptr(n_tiles), max_tiles,
-                               _ptr(perm), _ptr(inv), _ptr(err), st), "moe_plan")
-    xs = torch.empty(n_pairs, H, dtype=x.dtype, device=dev)
-    _check(L.b200_moe_gather(_ptr(x), _ptr(perm), _ptr(offsets[Et:]), n_pairs, T, Pn, H, _ptr(xs), st), "moe_gather")
+                               _ptr(perm), _ptr(inv), _ptr(err), Pn, _ptr(src_rows), st), "moe_plan")
     act = torch.empty(n_pairs, inter, dtype=x.dtype, device=dev)
-    _check(L.b200_gemm_grouped(_ptr(xs), _ptr(w_gate_up), _ptr(act), n_pairs, Et, inter, 2 * inter, H, inter,
-                               EPI_SILU_MUL, inter, bt, _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err),
-                               split_k(inter, H, grouped=True), is_packed(w_gate_up), st),
-           "gemm_grouped(gate_up)")
+    if gather:
+        _check(L.b200_gemm_grouped(_ptr(x), _ptr(w_gate_up), _ptr(act), n_pairs, Et, inter, 2 * inter, H, inter,
+                                   EPI_SILU_MUL, inter, bt, _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err), 1,
+                                   is_packed(w_gate_up), _ptr(src_rows), x.stride(0), st), "gemm_grouped(gate_up, gather)")
+    else:
+        xs = torch.empty(n_pairs, H, dtype=x.dtype, device=dev)
+        _check(L.b200_moe_gather(_ptr(x), _ptr(perm), _ptr(offsets[Et:]), n_pairs, T, Pn, H, _ptr(xs), st), "moe_gather")
+        _check(L.b200_gemm_grouped(_ptr(xs), _ptr(w_gate_up), _ptr(act), n_pairs, Et, inter, 2 * inter, H, inter,
+                                   EPI_SILU_MUL, inter, bt, _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err),
+                                   split_k(inter, H, grouped=True), is_packed(w_gate_up), None, 0, st),
+               "gemm_grouped(gate_up)")
     pair_out = torch.empty(n_pairs, H, dtype=x.dtype, device=dev)
     _check(L.b200_gemm_grouped(_ptr(act), _ptr(w_down), _ptr(pair_out), n_pairs, Et, H, H, inter, H, EPI_BF16, 0, bt,
                                _ptr(tiles), _ptr(n_tiles), max_tiles, _ptr(err), split_k(H, inter, grouped=True),
-                               is_packed(w_down), st),
+                               is_packed(w_down), None, 0, st),
            "gemm_grouped(down)")
     if norm_w is not None and not partial_f32:
         new_res = torch.empty(T, H, dtype=x.dtype, device=dev)

@@ -176,7 +176,7 @@ class EpMoE:
         rc |= K.b200_gemm_grouped(self._own["xs"], w_gate_up_local.data_ptr(), act.data_ptr(), self.cap_rows,
                                   self.per + 1, inter, 2 * inter, H, inter, cuda_ops.EPI_SILU_MUL, inter, bt,
                                   tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), 1,
-                                  cuda_ops.is_packed(w_gate_up_local), st)
+                                  cuda_ops.is_packed(w_gate_up_local), None, 0, st)
         rc |= L.b200_gemm_grouped_scatter(act.data_ptr(), w_down_local.data_ptr(), self.cap_rows, self.per + 1, H,
                                           inter, bt, tiles.data_ptr(), n_tiles.data_ptr(), max_tiles,
                                           self._own["meta"], self._pair_out_ptrs, self.world, err.data_ptr(),
