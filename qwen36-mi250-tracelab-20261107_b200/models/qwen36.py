@@ -186,7 +186,10 @@ class Model:
         GEMMs (reference: ``engine/fast/fused.py:635-692`` folds combine + shared expert + residual into its down
         kernel); elsewhere the norm is its own op, with identical rounding points."""
         cfg, ops = self.cfg, self.ops
-        if self.tp is None and self.ep is None and lw.shared_merged and getattr(ops, "FUSED_MOE_NORM", False):
+        if self.ep is not None:  # the combine kernel of the expert-parallel block carries the residual add and the norm
+            return self.ep.forward(h, lw.router, lw.w_gate_up, lw.w_down, residual=res, norm_w=norm_w,
+                                   eps=cfg.rms_norm_eps)
+        if self.tp is None and lw.shared_merged and getattr(ops, "FUSED_MOE_NORM", False):
             return ops.moe_block(h, lw.router, lw.w_gate_up, lw.w_down, cfg.num_experts, cfg.num_experts_per_tok, True,
                                  residual=res, norm_w=norm_w, eps=cfg.rms_norm_eps)
         return ops.add_rmsnorm(self._moe(lw, h), res, norm_w, cfg.rms_norm_eps)

@@ -1,173 +1,201 @@
 // Expert-parallel MoE over NVLink peer memory for token-sharded activations: every rank holds its own
 // rows and E / R of the routed experts (plus a replica of the shared expert).
 //
-//   ep_counts   : publish this rank's per-expert pair counts to every rank and wait for everyone's
-//   ep_plan     : from all counts, the row layout of every host's buffer (expert-major, source-major inside
-//                 an expert) -> where this rank's pairs go, and the local tile table of the grouped GEMMs
-//   ep_dispatch : the all-to-all. One CTA per (row, pair): the activation row is stored straight into the
-//                 hosting rank's expert-sorted buffer (peer store), with (source rank, pair slot) beside it
-//   ep_signal / ep_wait : release / acquire flags around the peer stores (bounded waits)
-//   grouped GEMMs (gemm_tcgen05.cu): gate/up + SiLU-mul on the received rows, then the down projection whose
-//                 epilogue scatters each output row back to the token's owner (the combine all-to-all)
-//   ep_combine  : after all hosts have signalled, the top-k weighted sum in pair order
+//   ep_send     : the dispatch all-to-all. One CTA per (row, pair): the activation row is stored straight into the
+//                 hosting rank's receive buffer, in the region reserved for this source rank, in arrival order,
+//                 with (local expert, pair index) beside it. Nothing has to be agreed beforehand: the last CTA
+//                 to finish publishes how many rows each host got and releases this source's arrival flag there.
+//   ep_plan     : on the host, waits for every source's flag (the one rendezvous of the dispatch), then sorts the
+//                 received rows by expert WITHOUT moving them: the token-tile table of the grouped GEMMs plus, for
+//                 every sorted position, the row of the receive buffer behind it (the gate/up GEMM's producer
+//                 fetches rows by that index) and where its result goes (source rank, pair index).
+//   grouped GEMMs (gemm_tcgen05.cu): gate/up + SiLU-mul over the received rows, then the down projection whose
+//                 epilogue stores each output row into the pair slot of the token's owner (the combine
+//                 all-to-all, peer stores from the epilogue).
+//   ep_combine  : releases "my results are out" towards every rank, waits for every host's release (the one
+//                 rendezvous of the combine), then the top-k weighted sum in pair order, optionally with the
+//                 residual add and the next RMSNorm.
 //
+// Two waits per MoE block, both inside kernels that do other work, no count exchange, no separate signal launches.
 // The reference has no expert parallelism (its TP halves every expert, engine/fast/tp.py:19-21, 716-736).
 // All buffers are symmetric CUDA IPC mappings; flags carry a device-resident epoch so that the sequence can
-// be captured in a CUDA graph. No multimem, no TMA on peer memory.
+// be captured in a CUDA graph. No multimem, no TMA on peer memory. Every wait is bounded (comm.cuh).
+//
+// Buffer reuse between consecutive calls needs no extra synchronisation: a source can only start the next call's
+// sends after its own combine, which waited for every host's release, which a host issues after its down GEMM (and
+// so after its gate/up GEMM has read the receive buffer); a host can only overwrite a rank's pair slots after its
+// next plan, which waited for that rank's next send, which follows that rank's combine.
 #include "comm.cuh"
 
 namespace b200 {
 
 struct EpCtx {
-  bf16* xs[MAX_RANKS];          // [cap_rows, H] expert-sorted incoming rows of each rank
-  int2* meta[MAX_RANKS];        // [cap_rows] (source rank, pair slot)
+  bf16* xs[MAX_RANKS];          // receive buffer of each rank: [R source regions][cap_src rows][H]
+  int2* meta[MAX_RANKS];        // per received row: (local expert, pair index at the source)
   bf16* pair_out[MAX_RANKS];    // [max_pairs, H] expert outputs returned to each rank
-  int* counts_all[MAX_RANKS];   // [R, Etot] per-expert pair counts of every source
-  uint32_t* flags[MAX_RANKS];   // [3, R]: counts / dispatch / combine arrival epochs per source
+  int* cnt[MAX_RANKS];          // [R] rows each source sent to this rank in the current call
+  uint32_t* flags[MAX_RANKS];   // [2][MAX_RANKS]: dispatch / combine arrival epochs per source
   uint32_t* epoch;              // this rank's call counter (device resident)
+  int* cursors;                 // this rank's send cursors [R] and the CTA ticket [1]; zero between calls
   int* err;
   int rank, world;
   int E;                        // routed experts (global); expert id E is the shared expert, hosted by everyone
   int per;                      // routed experts per rank
-  int cap_rows, max_pairs;
+  int cap_src, max_pairs;
 };
 
-// counts[Etot] -> counts_all[me] on every rank; then wait for all sources. One CTA. Also advances the epoch.
-__device__ __forceinline__ void ep_counts_body(const EpCtx& c, const int* counts) {
-  const int Etot = c.E + 1;
-  __shared__ uint32_t s_e;
-  if (threadIdx.x == 0) { s_e = c.epoch[0] + 1; c.epoch[0] = s_e; }
-  __syncthreads();
-  const uint32_t e = s_e;
-  for (int i = threadIdx.x; i < Etot; i += blockDim.x) {
-    const int v = counts[i];
-    for (int r = 0; r < c.world; ++r) c.counts_all[r][c.rank * Etot + i] = v;
-  }
-  __syncthreads();
-  if (threadIdx.x < c.world) {
-    __threadfence_system();
-    st_release_sys(c.flags[threadIdx.x] + 0 * MAX_RANKS + c.rank, e);
-    wait_flag(c.flags[c.rank] + 0 * MAX_RANKS + threadIdx.x, e, c.err);
-  }
-}
-__global__ void ep_counts_kernel(EpCtx c, const int* counts) { ep_counts_body(c, counts); }
-
-// One CTA of 1024 threads, Etot <= 1024. Outputs: send_base[Etot] (first position of my rows of expert e in
-// its host's buffer), cursors[Etot] = 0, local tile table, n_tiles, n_rows (rows this rank receives).
-__global__ void __launch_bounds__(1024)
-ep_plan_kernel(EpCtx c, int bt, int* send_base, int* cursors, int4* tiles, int* n_tiles, int max_tiles, int* n_rows,
-               const int* counts) {
-  if (counts != nullptr) {  // fused form: the count exchange and its wait run in this CTA first
-    ep_counts_body(c, counts);
-    __syncthreads();
-  }
-  const int Etot = c.E + 1, E = c.E, R = c.world, me = c.rank;
-  const int* ca = c.counts_all[me];
-  __shared__ int G[1025];   // exclusive prefix of routed totals in global expert order
-  __shared__ int wsum[32];
-  const int e = threadIdx.x, lane = e & 31, w = e >> 5;
-  int tot = 0, before_me = 0;
-  if (e < E) {
-    for (int s = 0; s < R; ++s) { const int v = ca[s * Etot + e]; tot += v; if (s < me) before_me += v; }
-  }
-  int sc = tot;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) { const int a = __shfl_up_sync(0xffffffffu, sc, o); if (lane >= o) sc += a; }
-  if (lane == 31) wsum[w] = sc;
-  __syncthreads();
-  if (w == 0) {
-    int a = wsum[lane];
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) { const int x = __shfl_up_sync(0xffffffffu, a, o); if (lane >= o) a += x; }
-    wsum[lane] = a;
-  }
-  __syncthreads();
-  const int excl = sc - tot + (w ? wsum[w - 1] : 0);
-  if (e <= E) G[e] = excl;  // thread E has tot = 0, so G[E] is the number of routed pairs
-  __syncthreads();
-  if (e < E) {
-    const int host = e / c.per;
-    send_base[e] = (G[e] - G[host * c.per]) + before_me;
-    cursors[e] = 0;
-  }
-  if (e == E) {  // shared expert: my own rows, after my routed rows
-    send_base[E] = G[(me + 1) * c.per] - G[me * c.per];
-    cursors[E] = 0;
-  }
-  // local tile table: my routed experts in id order, then the shared expert
-  const bool mine = e < E && e / c.per == me;
-  const int rows_e = mine ? tot : (e == E ? ca[me * Etot + E] : 0);
-  const int nt = (rows_e + bt - 1) / bt;
-  int st = nt;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) { const int a = __shfl_up_sync(0xffffffffu, st, o); if (lane >= o) st += a; }
-  __syncthreads();
-  if (lane == 31) wsum[w] = st;
-  __syncthreads();
-  if (w == 0) {
-    int a = wsum[lane];
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) { const int x = __shfl_up_sync(0xffffffffu, a, o); if (lane >= o) a += x; }
-    wsum[lane] = a;
-  }
-  __syncthreads();
-  const int tile0 = st - nt + (w ? wsum[w - 1] : 0);
-  if (rows_e > 0) {
-    const int local = e == E ? c.per : e - me * c.per;
-    const int row0 = e == E ? G[(me + 1) * c.per] - G[me * c.per] : G[e] - G[me * c.per];
-    for (int i = 0, ti = tile0; i * bt < rows_e && ti < max_tiles; ++i, ++ti)
-      tiles[ti] = make_int4(local, row0 + i * bt, min(bt, rows_e - i * bt), 0);
-  }
-  if (e == E) {
-    const int total_tiles = tile0 + nt;
-    *n_tiles = total_tiles < max_tiles ? total_tiles : max_tiles;
-    const int rows = G[(me + 1) * c.per] - G[me * c.per] + ca[me * Etot + E];
-    *n_rows = rows;
-    if (rows > c.cap_rows) atomicCAS(c.err, 0, ERR_BAD_INDEX);
-  }
-}
-
-// One CTA per (row, pair) of this rank: copy the activation row into its host's sorted buffer.
-__global__ void ep_dispatch_kernel(EpCtx c, const bf16* x, const int* idx, const int* send_base, int* cursors, int P,
-                                   int H) {
+// One CTA per (row, pair) of this rank (at least one CTA, so that a rank without rows still reports in).
+__global__ void ep_send_kernel(EpCtx c, const bf16* x, const int* idx, int n_pairs, int P, int H) {
   const int pair = blockIdx.x;
-  const int e = idx[pair];
-  if (e < 0 || e > c.E) return;
-  const int host = e == c.E ? c.rank : e / c.per;
-  __shared__ int s_pos;
-  if (threadIdx.x == 0) s_pos = send_base[e] + atomicAdd(&cursors[e], 1);
+  if (pair < n_pairs) {
+    const int e = idx[pair];
+    if (e >= 0 && e <= c.E) {
+      const int host = e == c.E ? c.rank : e / c.per;
+      const int local = e == c.E ? c.per : e - host * c.per;
+      __shared__ int s_pos;
+      if (threadIdx.x == 0) s_pos = atomicAdd(&c.cursors[host], 1);
+      __syncthreads();
+      const int pos = s_pos;
+      if (pos < c.cap_src) {
+        const size_t slot = static_cast<size_t>(c.rank) * c.cap_src + pos;
+        const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(pair / P) * H);
+        uint4* dst = reinterpret_cast<uint4*>(c.xs[host] + slot * H);
+        for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+        if (threadIdx.x == 0) c.meta[host][slot] = make_int2(local, pair);
+      } else if (threadIdx.x == 0) {
+        atomicCAS(c.err, 0, ERR_BAD_INDEX);  // more rows for one host than its region holds
+      }
+    } else if (threadIdx.x == 0) {
+      atomicCAS(c.err, 0, ERR_BAD_INDEX);
+    }
+  }
+  // last CTA out: publish the per-host counts and release this source's flag on every host
+  __threadfence_system();
   __syncthreads();
-  const int pos = s_pos;
-  if (pos >= c.cap_rows) { if (threadIdx.x == 0) atomicCAS(c.err, 0, ERR_BAD_INDEX); return; }
-  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(pair / P) * H);
-  uint4* dst = reinterpret_cast<uint4*>(c.xs[host] + static_cast<size_t>(pos) * H);
+  __shared__ int s_last;
+  if (threadIdx.x == 0) s_last = atomicAdd(&c.cursors[MAX_RANKS], 1) == static_cast<int>(gridDim.x) - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence_system();
+  const uint32_t e = c.epoch[0] + 1;
+  if (threadIdx.x < c.world) {
+    const int r = threadIdx.x;
+    const int n = atomicAdd(&c.cursors[r], 0);
+    c.cnt[r][c.rank] = n < c.cap_src ? n : c.cap_src;
+    __threadfence_system();
+    st_release_sys(c.flags[r] + 0 * MAX_RANKS + c.rank, e);
+    c.cursors[r] = 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) { c.cursors[MAX_RANKS] = 0; c.epoch[0] = e; }
+}
+
+// One CTA of 1024 threads on the host side: wait for every source, then lay the received rows out by expert
+// (local experts in id order, the shared expert last) without moving them.
+__global__ void __launch_bounds__(1024)
+ep_plan_kernel(EpCtx c, int bt, int4* tiles, int* n_tiles, int max_tiles, int* gather_rows, int2* ret_meta,
+               int* n_rows) {
+  const int R = c.world, me = c.rank, El = c.per + 1;
+  __shared__ int s_cnt[MAX_RANKS];
+  __shared__ int s_count[1024], s_off[1024], s_cur[1024];
+  __shared__ int w_rows[32], w_tiles[32];
+  __shared__ int s_ok;
+  const int e = threadIdx.x, lane = e & 31, w = e >> 5;
+  if (e == 0) s_ok = 1;
+  s_count[e] = 0;
+  s_cur[e] = 0;
+  __syncthreads();
+  if (e < R) {
+    if (!wait_flag(c.flags[me] + 0 * MAX_RANKS + e, c.epoch[0], c.err)) s_ok = 0;
+    const int n = c.cnt[me][e];
+    s_cnt[e] = (n >= 0 && n <= c.cap_src) ? n : 0;
+    if (n < 0 || n > c.cap_src) atomicCAS(c.err, 0, ERR_BAD_INDEX);
+  }
+  __syncthreads();
+  if (!s_ok) {  // a source never arrived: publish an empty plan so that the GEMMs behind run zero tiles
+    if (e == 0) { *n_tiles = 0; *n_rows = 0; }
+    return;
+  }
+  const int2* meta = c.meta[me];
+  for (int r = 0; r < R; ++r)
+    for (int i = threadIdx.x; i < s_cnt[r]; i += blockDim.x) {
+      const int le = meta[static_cast<size_t>(r) * c.cap_src + i].x;
+      if (le >= 0 && le < El) atomicAdd(&s_count[le], 1);
+    }
+  __syncthreads();
+  const int cn = e < El ? s_count[e] : 0;
+  const int t = (cn + bt - 1) / bt;
+  int sc = cn, stl = t;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, sc, o), b2 = __shfl_up_sync(0xffffffffu, stl, o);
+    if (lane >= o) { sc += a; stl += b2; }
+  }
+  if (lane == 31) { w_rows[w] = sc; w_tiles[w] = stl; }
+  __syncthreads();
+  if (w == 0) {
+    int a = w_rows[lane], b2 = w_tiles[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int x = __shfl_up_sync(0xffffffffu, a, o), y = __shfl_up_sync(0xffffffffu, b2, o);
+      if (lane >= o) { a += x; b2 += y; }
+    }
+    w_rows[lane] = a; w_tiles[lane] = b2;
+  }
+  __syncthreads();
+  const int row0 = sc - cn + (w ? w_rows[w - 1] : 0);
+  const int tile0 = stl - t + (w ? w_tiles[w - 1] : 0);
+  s_off[e] = row0;
+  if (e < El)
+    for (int i = 0, ti = tile0; i * bt < cn && ti < max_tiles; ++i, ++ti)
+      tiles[ti] = make_int4(e, row0 + i * bt, min(bt, cn - i * bt), 0);
+  if (e == El - 1) {
+    const int total = tile0 + t;
+    *n_tiles = total < max_tiles ? total : max_tiles;
+    *n_rows = row0 + cn;
+  }
+  __syncthreads();
+  for (int r = 0; r < R; ++r)
+    for (int i = threadIdx.x; i < s_cnt[r]; i += blockDim.x) {
+      const int slot = r * c.cap_src + i;
+      const int2 m = meta[slot];
+      if (m.x < 0 || m.x >= El) { atomicCAS(c.err, 0, ERR_BAD_INDEX); continue; }
+      const int pos = s_off[m.x] + atomicAdd(&s_cur[m.x], 1);
+      gather_rows[pos] = slot;
+      ret_meta[pos] = make_int2(r, m.y);
+    }
+}
+
+// sorted[pos] = xs[rows[pos]] for the first *n_valid positions: the expert-sorted copy that token tiles wider than
+// the gathering GEMM's limit (prefill sizes) read through their tensor map.
+__global__ void ep_compact_kernel(const bf16* xs, const int* rows, const int* n_valid, int H, bf16* sorted) {
+  const int pos = blockIdx.x;
+  if (pos >= *n_valid) return;
+  const uint4* src = reinterpret_cast<const uint4*>(xs + static_cast<size_t>(rows[pos]) * H);
+  uint4* dst = reinterpret_cast<uint4*>(sorted + static_cast<size_t>(pos) * H);
   for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
-  if (threadIdx.x == 0) c.meta[host][pos] = make_int2(c.rank, pair);
 }
 
-// Release flag `which` (1 = dispatch done, 2 = combine done) towards every rank, for the current epoch.
-__global__ void ep_signal_kernel(EpCtx c, int which) {
-  if (threadIdx.x < c.world) {
+// Release "my expert outputs are out" towards every rank, wait for every host's release, then
+// out[t] = bf16(sum_j w[t, j] * pair_out[t * P + j]) in pair order, fp32 accumulation. With NORM the launch also adds
+// the residual and applies the next zero-centred RMSNorm with the rounding points of add_rmsnorm_kernel.
+template <bool NORM>
+__global__ void ep_combine_kernel(EpCtx c, const float* wts, int T, int P, int H, bf16* out, const bf16* res,
+                                  const bf16* norm_w, bf16* res_out, bf16* y, float eps) {
+  extern __shared__ float vals[];  // NORM: H floats
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x < c.world) {
     __threadfence_system();
-    st_release_sys(c.flags[threadIdx.x] + which * MAX_RANKS + c.rank, c.epoch[0]);
+    st_release_sys(c.flags[threadIdx.x] + 1 * MAX_RANKS + c.rank, c.epoch[0]);
   }
-}
-// Wait until every source has released flag `which` for the current epoch.
-__global__ void ep_wait_kernel(EpCtx c, int which) {
-  if (threadIdx.x < c.world) wait_flag(c.flags[c.rank] + which * MAX_RANKS + threadIdx.x, c.epoch[0], c.err);
-}
-// Both in one launch: thread r releases towards rank r, then waits for rank r's release.
-__global__ void ep_signal_wait_kernel(EpCtx c, int which) {
-  if (threadIdx.x < c.world) {
-    __threadfence_system();
-    st_release_sys(c.flags[threadIdx.x] + which * MAX_RANKS + c.rank, c.epoch[0]);
-    wait_flag(c.flags[c.rank] + which * MAX_RANKS + threadIdx.x, c.epoch[0], c.err);
-  }
-}
-
-// out[t] = bf16(sum_j w[t, j] * pair_out[t * P + j]) in pair order, fp32 accumulation.
-__global__ void ep_combine_kernel(const bf16* pair_out, const float* wts, int P, int H, bf16* out) {
+  if (threadIdx.x < c.world && !wait_flag(c.flags[c.rank] + 1 * MAX_RANKS + threadIdx.x, c.epoch[0], c.err)) s_ok = 0;
+  __syncthreads();
   const int t = blockIdx.x;
+  if (!s_ok || t >= T) return;
+  const bf16* pair_out = c.pair_out[c.rank];
+  float ss = 0.f;
   for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int j = 0; j < P; ++j) {
@@ -181,7 +209,41 @@ __global__ void ep_combine_kernel(const bf16* pair_out, const float* wts, int P,
     bf16* oe = reinterpret_cast<bf16*>(&ov);
 #pragma unroll
     for (int k = 0; k < 8; ++k) oe[k] = __float2bfloat16(acc[k]);
-    *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + i) = ov;
+    if (NORM) {
+      if (res) {
+        uint4 rv = *reinterpret_cast<const uint4*>(res + static_cast<size_t>(t) * H + i);
+        const bf16* re = reinterpret_cast<const bf16*>(&rv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) oe[k] = __float2bfloat16(__bfloat162float(oe[k]) + __bfloat162float(re[k]));
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float f = __bfloat162float(oe[k]);
+        vals[i + k] = f;
+        ss += f * f;
+      }
+      *reinterpret_cast<uint4*>(res_out + static_cast<size_t>(t) * H + i) = ov;
+    } else {
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + i) = ov;
+    }
+  }
+  if (NORM) {
+    __shared__ float part[32];
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < static_cast<int>(blockDim.x >> 5); ++i) tot += part[i];
+    const float inv_rms = rsqrtf(tot / H + eps);
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      uint4 wv = *reinterpret_cast<const uint4*>(norm_w + i);
+      const bf16* we = reinterpret_cast<const bf16*>(&wv);
+      uint4 ov;
+      bf16* oe = reinterpret_cast<bf16*>(&ov);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) oe[k] = __float2bfloat16(vals[i + k] * inv_rms * (1.0f + __bfloat162float(we[k])));
+      *reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * H + i) = ov;
+    }
   }
 }
 
@@ -191,35 +253,36 @@ using namespace b200;
 
 extern "C" int b200_ep_ctx_size() { return static_cast<int>(sizeof(EpCtx)); }
 
-extern "C" int b200_ep_counts(const EpCtx* c, const int* counts, cudaStream_t st) {
-  ep_counts_kernel<<<1, 256, 0, st>>>(*c, counts);
+// x [T, H] (row stride H), idx [n_pairs] global expert of every (row, pair); P pairs per row.
+extern "C" int b200_ep_send(const EpCtx* c, const void* x, const int* idx, int n_pairs, int P, int H, cudaStream_t st) {
+  if (H % 8 || P <= 0) return -7;
+  ep_send_kernel<<<n_pairs > 0 ? n_pairs : 1, 128, 0, st>>>(*c, static_cast<const bf16*>(x), idx, n_pairs, P, H);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
-extern "C" int b200_ep_plan(const EpCtx* c, int bt, int* send_base, int* cursors, void* tiles, int* n_tiles,
-                            int max_tiles, int* n_rows, cudaStream_t st) {
-  if (c->E + 1 > 1024) return -7;
-  ep_plan_kernel<<<1, 1024, 0, st>>>(*c, bt, send_base, cursors, static_cast<int4*>(tiles), n_tiles, max_tiles, n_rows,
-                                     nullptr);
+extern "C" int b200_ep_plan(const EpCtx* c, int bt, void* tiles, int* n_tiles, int max_tiles, int* gather_rows,
+                            void* ret_meta, int* n_rows, cudaStream_t st) {
+  if (c->per + 1 > 1024) return -7;
+  ep_plan_kernel<<<1, 1024, 0, st>>>(*c, bt, static_cast<int4*>(tiles), n_tiles, max_tiles, gather_rows,
+                                     static_cast<int2*>(ret_meta), n_rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
-// Count exchange + plan in one launch (one CTA either way; saves a launch per MoE block).
-extern "C" int b200_ep_counts_plan(const EpCtx* c, const int* counts, int bt, int* send_base, int* cursors, void* tiles,
-                                   int* n_tiles, int max_tiles, int* n_rows, cudaStream_t st) {
-  if (c->E + 1 > 1024) return -7;
-  ep_plan_kernel<<<1, 1024, 0, st>>>(*c, bt, send_base, cursors, static_cast<int4*>(tiles), n_tiles, max_tiles, n_rows,
-                                     counts);
+extern "C" int b200_ep_compact(const void* xs, const int* rows, const int* n_valid, int max_rows, int H, void* sorted,
+                               cudaStream_t st) {
+  if (max_rows <= 0) return 0;
+  ep_compact_kernel<<<max_rows, 128, 0, st>>>(static_cast<const bf16*>(xs), rows, n_valid, H, static_cast<bf16*>(sorted));
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
-extern "C" int b200_ep_dispatch(const EpCtx* c, const void* x, const int* idx, const int* send_base, int* cursors,
-                                int n_pairs, int P, int H, cudaStream_t st) {
-  if (n_pairs > 0)
-    ep_dispatch_kernel<<<n_pairs, 128, 0, st>>>(*c, static_cast<const bf16*>(x), idx, send_base, cursors, P, H);
-  ep_signal_wait_kernel<<<1, 32, 0, st>>>(*c, 1);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
-}
-extern "C" int b200_ep_combine(const EpCtx* c, const float* wts, int T, int P, int H, void* out, cudaStream_t st) {
-  ep_signal_wait_kernel<<<1, 32, 0, st>>>(*c, 2);
-  if (T > 0)
-    ep_combine_kernel<<<T, 256, 0, st>>>(c->pair_out[c->rank], wts, P, H, static_cast<bf16*>(out));
+// out [T, H] = weighted sum; or, with norm_w: res_out = bf16(res + sum), y = norm(res_out) * (1 + norm_w).
+extern "C" int b200_ep_combine(const EpCtx* c, const float* wts, int T, int P, int H, void* out, const void* res,
+                               const void* norm_w, void* res_out, void* y, float eps, cudaStream_t st) {
+  if (H % 8) return -7;
+  const int grid = T > 0 ? T : 1;
+  if (norm_w != nullptr)
+    ep_combine_kernel<true><<<grid, 256, H * sizeof(float), st>>>(
+        *c, wts, T, P, H, nullptr, static_cast<const bf16*>(res), static_cast<const bf16*>(norm_w),
+        static_cast<bf16*>(res_out), static_cast<bf16*>(y), eps);
+  else
+    ep_combine_kernel<false><<<grid, 256, 0, st>>>(*c, wts, T, P, H, static_cast<bf16*>(out), nullptr, nullptr, nullptr,
+                                                   nullptr, 0.f);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

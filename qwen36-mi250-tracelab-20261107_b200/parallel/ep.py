@@ -1,10 +1,11 @@
 """Expert-parallel MoE block for token-sharded activations (each rank owns different rows).
 
 ``EpMoE.forward`` runs, on every rank of the group and in the same order: router GEMM + top-k on the
-rank's own rows, a count exchange, the dispatch all-to-all (rows stored straight into the hosting
-rank's expert-sorted buffer over NVLink), the grouped gate/up GEMM, the grouped down GEMM whose
-epilogue scatters every output row back to its owner (the combine all-to-all), and the top-k
-weighted sum. Kernels: ``ops/cuda/ep_moe.cu`` and the ``EPI_SCATTER`` epilogue of
+rank's own rows, the dispatch all-to-all (rows stored straight into the hosting rank's receive region
+for this source over NVLink, no count exchange first), a plan kernel that waits for every source and
+sorts the received rows by expert without moving them, the grouped gate/up GEMM whose producer fetches
+those rows by index, the grouped down GEMM whose epilogue scatters every output row back to its owner
+(the combine all-to-all), and the top-k weighted sum (with the residual add and next RMSNorm). Kernels: ``ops/cuda/ep_moe.cu`` and the ``EPI_SCATTER`` epilogue of
 ``ops/cuda/gemm_tcgen05.cu``; buffers are CUDA IPC symmetric memory as in ``parallel/symm.py``.
 The reference has no expert parallelism; this is the BASELINE configuration's EP path.
 """
@@ -24,15 +25,16 @@ class EpCtx(ctypes.Structure):
         ("xs", ctypes.c_void_p * MAX_RANKS),
         ("meta", ctypes.c_void_p * MAX_RANKS),
         ("pair_out", ctypes.c_void_p * MAX_RANKS),
-        ("counts_all", ctypes.c_void_p * MAX_RANKS),
+        ("cnt", ctypes.c_void_p * MAX_RANKS),
         ("flags", ctypes.c_void_p * MAX_RANKS),
         ("epoch", ctypes.c_void_p),
+        ("cursors", ctypes.c_void_p),
         ("err", ctypes.c_void_p),
         ("rank", ctypes.c_int),
         ("world", ctypes.c_int),
         ("E", ctypes.c_int),
         ("per", ctypes.c_int),
-        ("cap_rows", ctypes.c_int),
+        ("cap_src", ctypes.c_int),
         ("max_pairs", ctypes.c_int),
     ]
 
@@ -40,16 +42,14 @@ class EpCtx(ctypes.Structure):
 def _lib():
     L = _symm_lib()
     if not getattr(L, "_ep_ready", False):
-        P, I = ctypes.c_void_p, ctypes.c_int
+        P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
         C = ctypes.POINTER(EpCtx)
-        L.b200_ep_counts.argtypes = [C, P, P]
-        L.b200_ep_plan.argtypes = [C, I, P, P, P, P, I, P, P]
-        L.b200_ep_counts_plan.argtypes = [C, P, I, P, P, P, P, I, P, P]
-        L.b200_ep_counts_plan.restype = I
-        L.b200_ep_dispatch.argtypes = [C, P, P, P, P, I, I, I, P]
-        L.b200_ep_combine.argtypes = [C, P, I, I, I, P, P]
+        L.b200_ep_send.argtypes = [C, P, P, I, I, I, P]
+        L.b200_ep_plan.argtypes = [C, I, P, P, I, P, P, P, P]
+        L.b200_ep_compact.argtypes = [P, P, P, I, I, P, P]
+        L.b200_ep_combine.argtypes = [C, P, I, I, I, P, P, P, P, P, F, P]
         L.b200_gemm_grouped_scatter.argtypes = [P, P, I, I, I, I, I, P, P, I, P, P, I, P, I, P]
-        for n in ("b200_ep_counts", "b200_ep_plan", "b200_ep_dispatch", "b200_ep_combine", "b200_gemm_grouped_scatter",
+        for n in ("b200_ep_send", "b200_ep_plan", "b200_ep_compact", "b200_ep_combine", "b200_gemm_grouped_scatter",
                   "b200_ep_ctx_size"):
             getattr(L, n).restype = I
         assert L.b200_ep_ctx_size() == ctypes.sizeof(EpCtx), "EpCtx layout mismatch"
@@ -58,9 +58,12 @@ def _lib():
 
 
 class EpMoE:
-    def __init__(self, device: torch.device, group, n_experts: int, hidden: int, top_k: int, max_rows: int) -> None:
-        """``max_rows``: most rows any rank brings to one call; buffers are sized for the worst case in which
-        every pair of every rank lands on one host."""
+    def __init__(self, device: torch.device, group, n_experts: int, hidden: int, top_k: int, max_rows: int,
+                 capacity_factor: float | None = None) -> None:
+        """``max_rows``: most rows any rank brings to one call. Every rank keeps one receive region per source rank;
+        a region holds ``cap_src`` rows. By default that is the worst case (every pair of a source lands on one
+        host); ``capacity_factor`` f sizes it for f times the uniform share instead (plus the shared expert's rows),
+        and a call that needs more sets the error word rather than dropping rows silently."""
         import torch.distributed as dist
 
         self.device, self.group = device, group
@@ -69,19 +72,28 @@ class EpMoE:
         self.E, self.H, self.top_k = n_experts, hidden, top_k
         self.P = top_k + 1
         self.per = n_experts // self.world
+        self.max_rows = max_rows
         self.max_pairs = max_rows * self.P
-        self.cap_rows = self.max_pairs * self.world
+        worst = self.max_pairs
+        if capacity_factor is None:
+            self.cap_src = worst
+        else:
+            share = -(-max_rows * top_k // self.world)
+            self.cap_src = min(worst, max(256, int(capacity_factor * share)) + max_rows)
+        self.cap_rows = self.cap_src * self.world
         L = _lib()
-        Etot = n_experts + 1
         sizes = {
             "xs": self.cap_rows * hidden * 2,
             "meta": self.cap_rows * 8,
             "pair_out": self.max_pairs * hidden * 2,
-            "counts_all": self.world * Etot * 4,
-            "flags": 3 * MAX_RANKS * 4,
+            "cnt": MAX_RANKS * 4,
+            "flags": 2 * MAX_RANKS * 4,
             "epoch": 16,
+            "cursors": (MAX_RANKS + 1) * 4,
         }
         self._own, self._opened = {}, []
+        self._work: dict = {}
+
         def agree(ok: bool, what: str) -> None:
             """Every rank raises if any rank failed, so that nobody is left waiting in the next collective."""
             if self.world > 1:
@@ -92,6 +104,7 @@ class EpMoE:
                 self.close()
                 raise RuntimeError(f"expert-parallel set-up failed on some rank: {what}")
 
+        shared = ("xs", "meta", "pair_out", "cnt", "flags")
         with torch.cuda.device(device):
             ok = True
             for name, nbytes in sizes.items():
@@ -102,7 +115,7 @@ class EpMoE:
                 self._own[name] = p.value
             torch.cuda.synchronize(device)
             agree(ok, "symmetric allocation")
-            peers = {k: [self._own[k]] * 1 for k in ("xs", "meta", "pair_out", "counts_all", "flags")}
+            peers = {k: [self._own[k]] * 1 for k in shared}
             if self.world > 1:
                 handles, ok = {}, True
                 for name in peers:
@@ -133,9 +146,10 @@ class EpMoE:
             for name in peers:
                 getattr(ctx, name)[r] = peers[name][r]
         ctx.epoch = self._own["epoch"]
+        ctx.cursors = self._own["cursors"]
         ctx.err = cuda_ops.err_word(device).data_ptr()
         ctx.rank, ctx.world, ctx.E, ctx.per = self.rank, self.world, n_experts, self.per
-        ctx.cap_rows, ctx.max_pairs = self.cap_rows, self.max_pairs
+        ctx.cap_src, ctx.max_pairs = self.cap_src, self.max_pairs
         self.ctx = ctx
         self._pair_out_ptrs = (ctypes.c_void_p * MAX_RANKS)(*[peers["pair_out"][r] if r < self.world else None
                                                              for r in range(MAX_RANKS)])
@@ -146,43 +160,76 @@ class EpMoE:
         sel = torch.tensor(ids, device=w_gate_up.device)
         return w_gate_up[sel].contiguous(), w_down[sel].contiguous()
 
+    def _buffers(self, inter: int, dtype: torch.dtype):
+        """Host-side work buffers of the received rows (activations, tile table, sort indices), made once per expert
+        width: their size depends on the receive capacity only, never on a call's row count."""
+        w = self._work.get(inter)
+        if w is None:
+            dev = self.device
+            max_tiles = self.per + 1 + self.cap_rows // 16 + 1  # enough for the narrowest token tile
+            w = self._work[inter] = dict(
+                act=torch.empty(self.cap_rows, inter, dtype=dtype, device=dev),
+                tiles=torch.empty(max_tiles, 4, dtype=torch.int32, device=dev),
+                gather_rows=torch.zeros(self.cap_rows, dtype=torch.int32, device=dev),
+                ret_meta=torch.zeros(self.cap_rows, 2, dtype=torch.int32, device=dev),
+                ints=torch.zeros(2, dtype=torch.int32, device=dev),
+                sorted=None, max_tiles=max_tiles,
+            )
+        return w
+
     def forward(self, x: torch.Tensor, router: torch.Tensor, w_gate_up_local: torch.Tensor,
-                w_down_local: torch.Tensor) -> torch.Tensor:
+                w_down_local: torch.Tensor, residual: torch.Tensor | None = None, norm_w: torch.Tensor | None = None,
+                eps: float = 1e-6):
+        """The MoE block of this rank's rows. With ``norm_w`` the combine kernel also adds ``residual`` and applies
+        the next RMSNorm, and the call returns ``(new residual, normed)``; otherwise it returns the block's output."""
         T, H = x.shape
-        assert T * self.P <= self.max_pairs and H == self.H
+        assert T * self.P <= self.max_pairs and H == self.H and x.is_contiguous()
         dev, L, st = x.device, _lib(), torch.cuda.current_stream().cuda_stream
         K = cuda_ops.lib()
-        E, Pn, Etot = self.E, self.P, self.E + 1
+        E, Pn = self.E, self.P
         inter = w_down_local.shape[2]
         n_pairs = T * Pn
         logits = cuda_ops.linear(x, router, out_dtype=torch.float32)
         wts = torch.empty(T, Pn, dtype=torch.float32, device=dev)
         idx = torch.empty(T, Pn, dtype=torch.int32, device=dev)
-        ints = torch.zeros(3 * Etot + 2, dtype=torch.int32, device=dev)
-        counts, send_base, cursors = ints[:Etot], ints[Etot : 2 * Etot], ints[2 * Etot : 3 * Etot]
-        n_tiles, n_rows = ints[3 * Etot : 3 * Etot + 1], ints[3 * Etot + 1 :]
         rc = K.b200_moe_route(logits.data_ptr(), logits.stride(0), T, E, self.top_k, 1, wts.data_ptr(), idx.data_ptr(),
-                              counts.data_ptr(), Etot, None, st)
-        bt = cuda_ops.moe_bt(T * self.world, Pn, E)
-        max_tiles = self.per + 1 + self.cap_rows // bt + 1
-        tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device=dev)
+                              None, 0, None, st)
         C = ctypes.byref(self.ctx)
-        rc |= L.b200_ep_counts_plan(C, counts.data_ptr(), bt, send_base.data_ptr(), cursors.data_ptr(), tiles.data_ptr(),
-                                    n_tiles.data_ptr(), max_tiles, n_rows.data_ptr(), st)
-        rc |= L.b200_ep_dispatch(C, x.data_ptr(), idx.data_ptr(), send_base.data_ptr(), cursors.data_ptr(), n_pairs, Pn,
-                                 H, st)
-        act = torch.empty(self.cap_rows, inter, dtype=x.dtype, device=dev)
+        rc |= L.b200_ep_send(C, x.data_ptr(), idx.data_ptr(), n_pairs, Pn, H, st)
+        # token tile of this host's GEMMs from the rows it can expect (its own count times the ranks); a row's bits
+        # do not depend on it, so ranks with different batches need not agree
+        bt = cuda_ops.moe_bt(max(T, 1) * self.world, Pn, E)
+        w = self._buffers(inter, x.dtype)
+        n_tiles, n_rows = w["ints"][:1], w["ints"][1:]
+        rc |= L.b200_ep_plan(C, bt, w["tiles"].data_ptr(), n_tiles.data_ptr(), w["max_tiles"],
+                             w["gather_rows"].data_ptr(), w["ret_meta"].data_ptr(), n_rows.data_ptr(), st)
         err = cuda_ops.err_word(dev)
-        rc |= K.b200_gemm_grouped(self._own["xs"], w_gate_up_local.data_ptr(), act.data_ptr(), self.cap_rows,
-                                  self.per + 1, inter, 2 * inter, H, inter, cuda_ops.EPI_SILU_MUL, inter, bt,
-                                  tiles.data_ptr(), n_tiles.data_ptr(), max_tiles, err.data_ptr(), 1,
-                                  cuda_ops.is_packed(w_gate_up_local), None, 0, st)
-        rc |= L.b200_gemm_grouped_scatter(act.data_ptr(), w_down_local.data_ptr(), self.cap_rows, self.per + 1, H,
-                                          inter, bt, tiles.data_ptr(), n_tiles.data_ptr(), max_tiles,
-                                          self._own["meta"], self._pair_out_ptrs, self.world, err.data_ptr(),
+        if bt <= cuda_ops.GATHER_MAX_BT:
+            rc |= K.b200_gemm_grouped(self._own["xs"], w_gate_up_local.data_ptr(), w["act"].data_ptr(), self.cap_rows,
+                                      self.per + 1, inter, 2 * inter, H, inter, cuda_ops.EPI_SILU_MUL, inter, bt,
+                                      w["tiles"].data_ptr(), n_tiles.data_ptr(), w["max_tiles"], err.data_ptr(), 1,
+                                      cuda_ops.is_packed(w_gate_up_local), w["gather_rows"].data_ptr(), H, st)
+        else:
+            if w["sorted"] is None:
+                w["sorted"] = torch.empty(self.cap_rows, H, dtype=x.dtype, device=dev)
+            rc |= L.b200_ep_compact(self._own["xs"], w["gather_rows"].data_ptr(), n_rows.data_ptr(),
+                                    min(self.cap_rows, n_pairs * self.world), H, w["sorted"].data_ptr(), st)
+            rc |= K.b200_gemm_grouped(w["sorted"].data_ptr(), w_gate_up_local.data_ptr(), w["act"].data_ptr(),
+                                      self.cap_rows, self.per + 1, inter, 2 * inter, H, inter, cuda_ops.EPI_SILU_MUL,
+                                      inter, bt, w["tiles"].data_ptr(), n_tiles.data_ptr(), w["max_tiles"],
+                                      err.data_ptr(), 1, cuda_ops.is_packed(w_gate_up_local), None, 0, st)
+        rc |= L.b200_gemm_grouped_scatter(w["act"].data_ptr(), w_down_local.data_ptr(), self.cap_rows, self.per + 1, H,
+                                          inter, bt, w["tiles"].data_ptr(), n_tiles.data_ptr(), w["max_tiles"],
+                                          w["ret_meta"].data_ptr(), self._pair_out_ptrs, self.world, err.data_ptr(),
                                           cuda_ops.is_packed(w_down_local), st)
-        out = torch.empty_like(x)
-        rc |= L.b200_ep_combine(C, wts.data_ptr(), T, Pn, H, out.data_ptr(), st)
+        if norm_w is not None:
+            new_res, y = torch.empty_like(x), torch.empty_like(x)
+            rc |= L.b200_ep_combine(C, wts.data_ptr(), T, Pn, H, None, None if residual is None else residual.data_ptr(),
+                                    norm_w.data_ptr(), new_res.data_ptr(), y.data_ptr(), eps, st)
+            out = (new_res, y)
+        else:
+            out = torch.empty_like(x)
+            rc |= L.b200_ep_combine(C, wts.data_ptr(), T, Pn, H, out.data_ptr(), None, None, None, None, 0.0, st)
         if rc:
             raise cuda_ops.KernelError(f"expert-parallel MoE failed with code {rc}")
         return out

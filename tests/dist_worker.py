@@ -399,7 +399,7 @@ def mode_dp_ep_model(rank, world, dev):
         dist.all_reduce(t, op=dist.ReduceOp.MIN)
         if rank == 0:
             print(f"dp_ep_model world={world} graphs={graphs}: at least {t.item()}/{total} tokens equal the unsharded engine", flush=True)
-        assert same >= 0.9 * total and all(x[0] == y[0] for x, y in zip(got, ref)), (graphs, same, total)
+        assert same == total, (graphs, same, total)  # the sharded MoE block is bitwise equal to the local one
         dist.barrier()
     ep.close()
 

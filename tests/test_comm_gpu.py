@@ -85,14 +85,46 @@ def test_expert_parallel_moe_loopback_matches_the_local_block():
     router = (torch.randn(E + 1, H, device=dev, generator=g) * 0.3).to(torch.bfloat16)
     wgu = (torch.randn(E + 1, 2 * I, H, device=dev, generator=g) * 0.05).to(torch.bfloat16)
     wd = (torch.randn(E + 1, H, I, device=dev, generator=g) * 0.05).to(torch.bfloat16)
-    ep = EpMoE(dev, None, E, H, k, max_rows=200)
+    ep = EpMoE(dev, None, E, H, k, max_rows=600)
     lgu, ld = ep.local_experts(wgu, wd)
-    for T in (1, 50, 200):
+    nw = (torch.randn(H, device=dev, generator=g) * 0.1).to(torch.bfloat16)
+    for T in (1, 50, 200, 600, 3):  # 600 rows: token tiles too wide for the gathering GEMM, rows are compacted first
         x = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+        res = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
         got = ep.forward(x, router, lgu, ld)
         ref = cuda_ops.moe_block(x, router, wgu, wd, E, k, True)
         cuda_ops.check_errors(dev)
         assert torch.equal(got, ref), (T, (got.float() - ref.float()).abs().max().item())
+        got_res, got_y = ep.forward(x, router, lgu, ld, residual=res, norm_w=nw, eps=1e-6)
+        ref_res, ref_y = cuda_ops.add_rmsnorm(ref, res, nw, 1e-6)
+        cuda_ops.check_errors(dev)
+        assert torch.equal(got_res, ref_res) and torch.equal(got_y, ref_y), T
+    ep.close()
+
+
+def test_expert_parallel_moe_reports_a_full_receive_region():
+    """A capacity factor below what a call needs must set the error word, never drop rows silently."""
+    from b200serve.ops import cuda_ops
+    from b200serve.parallel.ep import EpMoE
+
+    dev = torch.device("cuda")
+    E, H, I, k = 16, 256, 128, 2
+    g = torch.Generator(device=dev).manual_seed(4)
+    router = (torch.randn(E + 1, H, device=dev, generator=g) * 0.3).to(torch.bfloat16)
+    wgu = (torch.randn(E + 1, 2 * I, H, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    wd = (torch.randn(E + 1, H, I, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    ep = EpMoE(dev, None, E, H, k, max_rows=512, capacity_factor=0.1)
+    assert ep.cap_src < 512 * 3
+    lgu, ld = ep.local_experts(wgu, wd)
+    x = torch.randn(512, H, device=dev, generator=g).to(torch.bfloat16)
+    ep.forward(x, router, lgu, ld)
+    with pytest.raises(cuda_ops.KernelError):
+        cuda_ops.check_errors(dev)
+    # the context stays usable for calls that fit
+    x = torch.randn(8, H, device=dev, generator=g).to(torch.bfloat16)
+    got = ep.forward(x, router, lgu, ld)
+    cuda_ops.check_errors(dev)
+    assert torch.equal(got, cuda_ops.moe_block(x, router, wgu, wd, E, k, True))
     ep.close()
 
 
