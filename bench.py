@@ -34,7 +34,7 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-BASELINE_TOK_S = None  # BASELINE.md: the reference publishes no number for this hardware
+BASELINE_TOK_S = None  # the reference publishes no number for this hardware
 
 
 def parse() -> argparse.Namespace:
@@ -50,6 +50,9 @@ def parse() -> argparse.Namespace:
                          "peer memory), falling back to independent dp replicas if its set-up or trial step fails")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (result marked invalid)")
     ap.add_argument("--mtp", type=int, default=0, help="MTP draft depth (0 = plain decode)")
+    ap.add_argument("--no-serving-config", action="store_true",
+                    help="skip the second measurement (256 concurrent requests in total, 2048-token prompts, 256 output "
+                         "tokens, prefill included), reported under the key 'serving_256x2048x256'")
     return ap.parse_args()
 
 
@@ -103,22 +106,128 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def reference_arm(args: argparse.Namespace) -> None:
+REF_ENV = {
+    # what the reference needs to start on a CUDA machine (its defaults assume two MI250 GCDs per replica):
+    "ENGINE_TP": "1",            # its TP all-reduce loads libamdhip64.so (engine/fast/tp.py:341-343, 517-518)
+    "ENGINE_GDN_HIP": "0",       # its served GDN kernel is compiled with hipRTC (engine/fast/gdn_hip.py:163)
+    "ENGINE_MTP": "0",           # plain decode, as the other arm measures
+}
+
+
+def reference_unavailable() -> str | None:
+    """Why the unmodified reference under baseline/_ref cannot run here, or None when it can be tried."""
     import importlib.util
 
-    out = {"impl": "reference"}
-    ref = ROOT / "baseline" / "_ref" / "engine"
-    if not ref.exists():
-        out["unavailable"] = ("reference is not pip-installable (no setup.py/pyproject.toml) and baseline/_ref/engine "
-                              "is absent on this box")
-    elif importlib.util.find_spec("accelerate") is None:
-        out["unavailable"] = ("reference Generator.load calls from_pretrained(device_map='auto') on CUDA "
-                              "(engine/generator.py:651-663), which needs the accelerate package: not in this image "
-                              "nor in /opt/wheelhouse")
-    else:
-        out["unavailable"] = "reference run path not exercised in this image (accelerate appeared; rerun needed)"
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps(out), flush=True)
+    if not (ROOT / "baseline" / "_ref" / "engine").exists():
+        return ("reference is not pip-installable (no setup.py/pyproject.toml) and baseline/_ref/engine "
+                "is absent on this box")
+    if importlib.util.find_spec("accelerate") is None:
+        return ("reference Generator.load calls from_pretrained(device_map='auto') on CUDA "
+                "(engine/generator.py:651-663), which needs the accelerate package: not in this image "
+                "nor in /opt/wheelhouse")
+    return None
+
+
+def reference_arm(args: argparse.Namespace) -> None:
+    """The same metric through the reference's own public API (`Generator.load / start_many / decode`,
+    engine/generator.py:636, 766, 1026), stock code path, none of this repository's kernels or engine on it."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    why = reference_unavailable()
+    if why is not None:
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+        return
+    try:
+        line = _reference_run(args, rank, world)
+    except Exception as e:  # noqa: BLE001 - the arm must always print one line and exit 0
+        import traceback
+
+        tb = traceback.extract_tb(e.__traceback__)[-1]
+        line = {"impl": "reference", "unavailable": f"reference run failed at {Path(tb.filename).name}:{tb.lineno}: {e!r}"[:400]}
+    if rank == 0 and line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def _reference_run(args: argparse.Namespace, rank: int, world: int) -> dict | None:
+    import tempfile
+
+    import torch
+    import torch.distributed as dist
+
+    os.environ.update({k: os.environ.get(k, v) for k, v in REF_ENV.items()})
+    B, P, K, W = args.batch, args.prompt_len, args.steps, max(args.warmup, 3)
+    os.environ.setdefault("ENGINE_SLOTS", str(B))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ["CUDA_VISIBLE_DEVICES"] = os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",")[local] \
+        if os.environ.get("CUDA_VISIBLE_DEVICES") else str(local)  # one GPU per rank: a data-parallel replica each
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=dev)
+    # a random-init checkpoint of the named architecture in HF layout, written by this repository's checkpoint writer
+    # (the only part of this repository the arm uses; it is input data, not on the timed path)
+    from b200serve.config import ModelConfig
+    from b200serve.models.checkpoint import random_weights, save_checkpoint
+    from b200serve.models.tiny import build_tokenizer
+
+    ckpt = Path(os.environ.get("BENCH_REF_CKPT") or tempfile.mkdtemp(prefix=f"ref-ckpt-{rank}-"))
+    if not (ckpt / "config.json").exists():
+        mcfg = ModelConfig.qwen36_35b_a3b()
+        save_checkpoint(random_weights(mcfg, seed=1234 + rank, device="cpu", dtype=torch.bfloat16), ckpt)
+        build_tokenizer(512).save_pretrained(str(ckpt))
+    sys.path.insert(0, str(ROOT / "baseline" / "_ref"))
+    from engine.generator import Generator
+    from engine.protocol import Sampling
+
+    total_out = K + W + 8
+    gen = Generator.load(str(ckpt), None, max_model_len=P + total_out + 64, chunk_tokens=2048,
+                         prefix_cache_tokens=0, prefix_cache_entries=0)
+    vocab = gen.model.config.get_text_config().vocab_size
+    g = torch.Generator().manual_seed(99 + rank)
+    reqs = [(tuple(torch.randint(0, vocab, (P,), generator=g).tolist()),
+             Sampling(max_tokens=total_out, temperature=0.0, ignore_eos=True)) for _ in range(B)]
+    gens = gen.start_many(reqs)
+    bad = [x for x in gens if isinstance(x, Exception)]
+    if bad:
+        raise bad[0]
+
+    def step() -> None:
+        for x in gens:
+            x.next_step()  # picks the token from the stored logits (a device-to-host read per request)
+        gen.decode(gens)
+
+    for _ in range(W):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    a.record()
+    for _ in range(K):
+        step()
+    b.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    ms = a.elapsed_time(b)
+    if world > 1:
+        t = torch.tensor([ms, wall], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, wall = float(t[0]), float(t[1])
+        dist.destroy_process_group()
+    value = world * B * K / (ms / 1e3)
+    return {
+        "metric": "output tok/s (whole box, max over ranks), decode", "value": round(value, 1), "unit": "tok/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (uniform-random prompt tokens, random-init weights)", "impl": "reference",
+        "config": {"model": "Qwen3.6-35B-A3B", "global_batch": B * world, "seq_len": P, "parallelism": f"dp{world}",
+                   "flags": {k: os.environ[k] for k in list(REF_ENV) + ["ENGINE_SLOTS"]}},
+        "e2e": {"value": round(world * B * K / wall, 1), "unit": "tok/s",
+                "note": "the reference's step reads every request's token on the host; same loop as the timed one"},
+    }
 
 
 def main() -> None:
@@ -177,10 +286,16 @@ def main() -> None:
     else:
         weights = random_weights(mcfg, seed=1234 + rank, device=dev, dtype=torch.bfloat16)
     total_out = K + max(W, 3) + 64 + (B * P) // 4096  # room for the tokens decoded while later prompts prefill
+    # second workload: 256 concurrent requests over the whole job, 2048-token prompts, 256 output tokens
+    S_REQ, S_PROMPT, S_OUT = 256, 2048, 256
+    serving = not args.no_serving_config and not args.layers and not args.mtp
+    n_serv = (S_REQ if tp_mode else S_REQ // world) if serving else 0
+    seqs = max(B, n_serv)
+    pages = max(B * ((P + 2 * total_out) // 64 + 2), n_serv * ((S_PROMPT + S_OUT) // 64 + 3)) + 2
     ecfg = EngineConfig(
-        max_model_len=P + 2 * total_out + 64, max_seqs=B, state_slots=B + 2, prefill_chunk_tokens=2048,
-        prefill_pack_tokens=8192, kv_pages=B * ((P + 2 * total_out) // 64 + 2) + 2, mtp=bool(args.mtp),
-        spec_k=args.mtp, decode_buckets=(B,), pack_weights=not tp_mode,
+        max_model_len=max(P + 2 * total_out + 64, S_PROMPT + S_OUT + 64), max_seqs=seqs, state_slots=seqs + 2,
+        prefill_chunk_tokens=2048, prefill_pack_tokens=8192, kv_pages=pages, mtp=bool(args.mtp),
+        spec_k=args.mtp, decode_buckets=tuple(sorted({B, seqs})), pack_weights=not tp_mode,
     )
     if ep_mode:
         ecfg.mtp = False
@@ -254,7 +369,9 @@ def main() -> None:
             for _ in range(timed_steps):
                 engine.step()
         else:
-            bucket = next(b for b in engine._graphs.buckets.values() if b.size == B)
+            bucket = next((b for b in engine._graphs.buckets.values() if b.size == B), None)
+            if bucket is None:
+                raise RuntimeError(f"no captured decode graph for batch {B}: {engine._graphs.errors}")
             for _ in range(timed_steps):
                 bucket.graph.replay()
                 bucket.tokens.copy_(bucket.picks)  # feed the picks back on the device
@@ -272,6 +389,36 @@ def main() -> None:
         engine.step()
         return ms, wall, produced
 
+    def run_serving():
+        """All requests of the second workload arrive at once on every replica; timed from submission to the last
+        token through the public engine API (prefill included), wall clock around a device synchronise."""
+        engine.cache.clear()
+        g = torch.Generator().manual_seed(7 + (0 if tp_mode else rank))
+        first, last = {}, {}
+
+        def on_event(gen, ev):
+            if ev.token is not None:
+                now = time.perf_counter()
+                first.setdefault(gen.id, now)
+                last[gen.id] = now
+
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        gens = [engine.submit(Generation(torch.randint(0, mcfg.vocab_size, (S_PROMPT,), generator=g).tolist(),
+                                         Sampling(max_tokens=S_OUT, ignore_eos=True), on_event=on_event))
+                for _ in range(n_serv)]
+        while any(not x.done for x in gens):
+            engine.step()
+        engine.flush_events()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        ok = all(len(x.output) == S_OUT for x in gens)
+        ttft = sorted(first[x.id] - t0 for x in gens)
+        tpot = sorted((last[x.id] - first[x.id]) / (S_OUT - 1) for x in gens)
+        return wall, ok, ttft[len(ttft) // 2] * 1e3, tpot[len(tpot) // 2] * 1e3
+
     sampler = ClockSampler(local)
     # e2e first (through the public API), then the device-resident kernel loop on the same engine
     e2e_ms, e2e_wall, e2e_tokens = run_phase(K, W, e2e=True)
@@ -280,6 +427,10 @@ def main() -> None:
     ms, _wall, tokens = run_phase(K, max(W, 3), e2e=False)
     clocks = sampler.stop()
     cuda_ops.check_errors(dev)
+    serving_line = None
+    if serving:
+        s_wall, s_ok, s_ttft, s_tpot = run_serving()
+        cuda_ops.check_errors(dev)
 
     def reduce_max(x: float) -> float:
         if world == 1:
@@ -288,6 +439,17 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    if serving:
+        s_wall = reduce_max(s_wall)
+        s_bad = reduce_max(0.0 if s_ok else 1.0)
+        serving_line = {
+            "value": round(S_REQ * S_OUT / s_wall, 1), "unit": "output tok/s, prefill included", "wall_s": round(s_wall, 3),
+            "ttft_p50_ms": round(reduce_max(s_ttft), 1), "tpot_p50_ms": round(reduce_max(s_tpot), 2),
+            "complete": s_bad == 0.0,
+            "config": {"requests": S_REQ, "prompt_len": S_PROMPT, "output_len": S_OUT, "requests_per_gpu": n_serv,
+                       "arrival": "all at once", "timing": "wall clock around a device synchronise, max over ranks; "
+                       "TTFT / TPOT are each rank's medians, the slowest rank reported"},
+        }
     ms = reduce_max(ms)
     e2e_s = reduce_max(max(e2e_wall, e2e_ms / 1e3))
     value = replicas * tokens / (ms / 1e3)
@@ -295,10 +457,8 @@ def main() -> None:
     bucket = next(b for b in engine._graphs.buckets.values() if b.size == B)
     h2d = bucket.host_buf.numel()  # tokens, positions, slots and page tables: one pinned buffer, one copy per step
     d2h = bucket.h_picks.numel() * 8
-    n_gdn, n_attn = len(mcfg.gdn_layers), len(mcfg.attention_layers)
-    # kernels per decode step: 2 norms + 2 projections + router + 7 MoE kernels per layer, 2 (GDN) or 3 (attention)
-    # mixer kernels, embedding, final norm, LM head + argmax reduce
-    launches_per_step = (n_gdn + n_attn) * 12 + n_gdn * 2 + n_attn * 3 + 4
+    # kernels of this library inside one replay of the captured decode step, counted by its launchers at capture
+    launches_per_step = bucket.launches
     if rank == 0:
         line = {
             "metric": "output tok/s (whole box, max over ranks), decode", "value": round(value, 1), "unit": "tok/s",
@@ -316,7 +476,11 @@ def main() -> None:
             "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3 / K, 4)},
             "gpu_launches": launches_per_step * K,
+            "gpu_launches_note": "kernels of this library inside the timed region (counted at graph capture, times "
+                                 "steps); torch adds two elementwise launches per step to feed the picks back",
         }
+        if serving_line is not None:
+            line["serving_256x2048x256"] = serving_line
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -37,6 +37,7 @@ class EngineWorker(threading.Thread):
         self.wake = threading.Event()
         self.stopping = False
         self.fatal: BaseException | None = None
+        self.fatal_streak = 0  # consecutive iterations that raised: the loop is wedged when this keeps growing
 
     def submit(self, gen: Generation) -> None:
         self.engine.submit(gen)
@@ -49,11 +50,17 @@ class EngineWorker(threading.Thread):
                 looptimers.begin()
                 busy = eng.step()
                 looptimers.end(len(eng.running))
+                self.fatal_streak = 0
             except BaseException as e:  # noqa: BLE001 - keep the failure visible on /health
                 self.fatal = e
+                self.fatal_streak += 1
                 import traceback
 
                 traceback.print_exc()
+                try:  # nobody may be left waiting on a request this loop can no longer advance
+                    eng.fail_all(f"engine loop failed: {e!r}")
+                except Exception:  # noqa: BLE001
+                    traceback.print_exc()
                 time.sleep(0.05)
                 continue
             if not busy and not eng.has_work():
@@ -202,7 +209,15 @@ class Service:
         return list(request.prompt)
 
     def health(self) -> dict[str, Any]:
-        body: dict[str, Any] = {"status": "ok" if self.worker.fatal is None else "degraded"}
+        # "ok": serving. "degraded": the engine loop raised at some point but recovered. "unavailable": the rank group
+        # was torn down or the loop keeps raising; /health then answers 503 so that a front takes the replica out.
+        if self.engine.broken is not None or self.worker.fatal_streak >= 3:
+            status = "unavailable"
+        else:
+            status = "ok" if self.worker.fatal is None else "degraded"
+        body: dict[str, Any] = {"status": status}
+        if self.worker.fatal is not None:
+            body["last_loop_error"] = repr(self.worker.fatal)
         body.update(self.engine.health())
         if self.codec is not None:
             body.update(self.codec.encoder.stats)
@@ -238,7 +253,8 @@ class Handler(BaseHTTPRequestHandler):
     def do_GET(self) -> None:
         svc = self.server.service  # type: ignore[attr-defined]
         if self.path == "/health":
-            self._json(200, svc.health())
+            body = svc.health()
+            self._json(503 if body["status"] == "unavailable" else 200, body)
         elif self.path == "/v1/models":
             self._json(200, protocol.models_body(svc.model_name, svc.engine.max_model_len))
         else:

@@ -54,6 +54,12 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 #ifdef __CUDACC__
+// Kernel launches issued by this library since it was loaded (the launchers count; a replayed CUDA graph does not
+// pass through them, so the number of kernels in a graph is the count taken around its capture).
+inline unsigned long long& launch_counter() {
+  static unsigned long long n = 0;
+  return n;
+}
 inline bool pdl_enabled() {
   static int on = -1;
   if (on < 0) {
@@ -76,6 +82,7 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  ++launch_counter();
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 #endif

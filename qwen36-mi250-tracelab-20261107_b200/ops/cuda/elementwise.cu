@@ -407,3 +407,6 @@ extern "C" int b200_moe_combine_norm(const void* pair_out, const float* wts, con
                       static_cast<float*>(nullptr), static_cast<const bf16*>(res), static_cast<const bf16*>(norm_w),
                       static_cast<bf16*>(res_out), static_cast<bf16*>(y), eps));
 }
+
+// Kernels launched through this library so far (see launch_counter in common.cuh).
+extern "C" unsigned long long b200_launch_count() { return launch_counter(); }

@@ -256,12 +256,14 @@ extern "C" int b200_ep_ctx_size() { return static_cast<int>(sizeof(EpCtx)); }
 // x [T, H] (row stride H), idx [n_pairs] global expert of every (row, pair); P pairs per row.
 extern "C" int b200_ep_send(const EpCtx* c, const void* x, const int* idx, int n_pairs, int P, int H, cudaStream_t st) {
   if (H % 8 || P <= 0) return -7;
+  ++launch_counter();
   ep_send_kernel<<<n_pairs > 0 ? n_pairs : 1, 128, 0, st>>>(*c, static_cast<const bf16*>(x), idx, n_pairs, P, H);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 extern "C" int b200_ep_plan(const EpCtx* c, int bt, void* tiles, int* n_tiles, int max_tiles, int* gather_rows,
                             void* ret_meta, int* n_rows, cudaStream_t st) {
   if (c->per + 1 > 1024) return -7;
+  ++launch_counter();
   ep_plan_kernel<<<1, 1024, 0, st>>>(*c, bt, static_cast<int4*>(tiles), n_tiles, max_tiles, gather_rows,
                                      static_cast<int2*>(ret_meta), n_rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
@@ -269,6 +271,7 @@ extern "C" int b200_ep_plan(const EpCtx* c, int bt, void* tiles, int* n_tiles, i
 extern "C" int b200_ep_compact(const void* xs, const int* rows, const int* n_valid, int max_rows, int H, void* sorted,
                                cudaStream_t st) {
   if (max_rows <= 0) return 0;
+  ++launch_counter();
   ep_compact_kernel<<<max_rows, 128, 0, st>>>(static_cast<const bf16*>(xs), rows, n_valid, H, static_cast<bf16*>(sorted));
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -277,6 +280,7 @@ extern "C" int b200_ep_combine(const EpCtx* c, const float* wts, int T, int P, i
                                const void* norm_w, void* res_out, void* y, float eps, cudaStream_t st) {
   if (H % 8) return -7;
   const int grid = T > 0 ? T : 1;
+  ++launch_counter();
   if (norm_w != nullptr)
     ep_combine_kernel<true><<<grid, 256, H * sizeof(float), st>>>(
         *c, wts, T, P, H, nullptr, static_cast<const bf16*>(res), static_cast<const bf16*>(norm_w),

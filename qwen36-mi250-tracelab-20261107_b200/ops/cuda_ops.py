@@ -75,6 +75,14 @@ class _Sig:
     b200_attn_combine = [P, P, P, P, I, I, I, I, P]
 
 
+def launch_count() -> int:
+    """Kernels launched through the library so far; taken around a graph capture it is the graph's kernel count."""
+    fn = lib().b200_launch_count
+    fn.restype = ctypes.c_ulonglong
+    fn.argtypes = []
+    return int(fn())
+
+
 def _ptr(t: torch.Tensor | None):
     return None if t is None else t.data_ptr()
 

@@ -52,6 +52,17 @@ class Coordinator:
     # ------------------------------------------------------------------ both sides
     def sync(self, engine) -> bool:
         """Exchange this iteration's events; returns False when the replica is shutting down."""
+        # Did any rank see a device-side failure (a peer wait that ran out, an index check) or an escaped exception in
+        # the last iteration? Such a rank skipped stores the others made: the group is out of step for good. All ranks
+        # learn of it here, before the next launch, and every one of them tears its engine down (fails what is in
+        # flight, refuses new work, reports it on /health).
+        import torch
+
+        flag = torch.tensor([1 if engine.device_error_pending else 0], dtype=torch.int32)
+        self.dist.all_reduce(flag, op=self.dist.ReduceOp.MAX, group=self.group)
+        if int(flag.item()):
+            engine.device_error_pending = False
+            engine.tear_down("a device-side failure or an escaped exception on one rank of the group")
         msg = [self._collect(engine) if self.is_leader else None]
         self.dist.broadcast_object_list(msg, src=self.leader, group=self.group)
         m = msg[0]

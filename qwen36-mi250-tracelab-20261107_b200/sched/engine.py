@@ -62,7 +62,7 @@ class Engine:
         if c.pack_weights and tp is None and hasattr(self.ops, "pack_weights"):
             self.ops.pack_weights(weights)  # before the KV pool is sized: padded copies replace a few tensors
         n_slots = c.state_slots or (c.max_seqs * 2 + 2)
-        n_pages = c.kv_pages or self._auto_pages(weights, n_slots)
+        n_pages = c.kv_pages or self._agree_min(self._auto_pages(weights, n_slots), tp)
         self.model = Model(weights, n_pages, n_slots, ops=self.ops, tp=tp, ep=ep)
         self.pages = PagePool(n_pages)
         self.slots = SlotPool(n_slots)
@@ -80,10 +80,14 @@ class Engine:
         self.prefilling: list[Generation] = []
         self.running: list[Generation] = []
         self._deferred: list = []
+        self._flushed = False
+        self.multi_rank = tp is not None or ep is not None
+        self.broken: str | None = None  # set when a rank group can no longer be trusted to be in step
+        self.device_error_pending = False  # multi-rank: a device-side failure seen since the last agreement
         self.stats = dict(
             decode_steps=0, decoded_tokens=0, largest_batch=0, prefill_passes=0, prefill_segments=0,
             prefilled_tokens=0, cached_tokens=0, requests=0, finished=0, failed=0,
-            mtp_verify_steps=0, mtp_proposed=0, mtp_accepted=0,
+            mtp_verify_steps=0, mtp_proposed=0, mtp_accepted=0, device_errors=0, step_errors=0,
         )
         self._graphs = None
         # library collectives (the NCCL baseline path) stay out of CUDA graphs; the fused NVLink kernels go in
@@ -111,6 +115,20 @@ class Engine:
         if pages < min(need, 64):
             raise RuntimeError(f"not enough device memory for the KV pool ({pages} pages)")
         return pages
+
+    def _agree_min(self, value: int, tp) -> int:
+        """The smallest ``value`` over the ranks of a tensor-parallel replica. Capacities derived from a rank's own
+        free memory differ between GPUs (other contexts, other users' jobs), but the lockstep design needs every rank
+        to allocate, evict and refuse identically, so all ranks adopt the tightest budget."""
+        group = getattr(getattr(tp, "comm", None), "group", None)
+        if tp is None or group is None:
+            return value
+        import torch.distributed as dist
+
+        on_gpu = dist.get_backend(group) == "nccl"
+        t = torch.tensor([value], dtype=torch.int64, device=self.device if on_gpu else "cpu")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+        return int(t.item())
 
     # ------------------------------------------------------------------ public API
     def submit(self, gen: Generation) -> Generation:
@@ -269,6 +287,7 @@ class Engine:
         )
         try:
             hidden = self.model.forward(batch)
+            self.check_device()
         except Exception as e:  # fail the packed requests only; the engine keeps serving
             for g in picked:
                 self.prefilling.remove(g)
@@ -318,9 +337,17 @@ class Engine:
                 self._finish(gen, "cancelled")
         if not self.running:
             return False
-        if self.spec is not None and self.spec.step(self.running):
-            self._reap()
-            return True
+        if self.spec is not None:
+            try:
+                stepped = self.spec.step(self.running)
+            except Exception as e:  # a failed verify step fails its requests; the engine keeps serving
+                for g in list(self.running):
+                    self.running.remove(g)
+                    self._fail(g, EngineError(f"decode failed: {e}", 500, "internal_error"))
+                return True
+            if stepped:
+                self._reap()
+                return True
         batch_gens = []
         for gen in list(self.running):
             try:
@@ -342,6 +369,7 @@ class Engine:
                 batch = PackedBatch.uniform(tokens, positions, [g.slot for g in batch_gens], self._table(batch_gens), 1, self.device)
                 hidden = self.model.forward(batch)
                 greedy = None
+                self.check_device()
         except Exception as e:
             for g in batch_gens:
                 self.running.remove(g)
@@ -431,6 +459,51 @@ class Engine:
         g.finish_reason = "error"
         self._emit(g, TokenEvent(None, "error", err))
 
+    # ------------------------------------------------------------------ failures
+    def check_device(self, code: int | None = None) -> None:
+        """Raise if a kernel of the pass just run recorded a failure in the device error word (a bounded wait that
+        gave up, an index out of range): the kernels then skipped their stores, so whatever the pass produced must
+        not be sampled from. ``code`` is the word when the caller has already copied it to the host; otherwise it is
+        read here (synchronises). The word is cleared, since a set word makes every later peer wait give up at once.
+        In a multi-rank engine the failure is also latched for the ranks' next agreement."""
+        if not hasattr(self.ops, "err_word"):
+            return
+        word = self.ops.err_word(self.device)
+        if code is None:
+            code = int(word.item())
+        if code:
+            word.zero_()
+            self.stats["device_errors"] += 1
+            if self.multi_rank:
+                self.device_error_pending = True
+            raise self.ops.KernelError(f"device-side failure {code} in this pass")
+
+    def fail_all(self, reason: str, status: int = 500) -> None:
+        """Fail every request the engine holds and give their slots and pages back."""
+        err = EngineError(reason, status, "internal_error" if status == 500 else "service_unavailable")
+        while True:
+            try:
+                self.waiting.append(self._inbox.get_nowait())
+            except queue.Empty:
+                break
+        for g in self.waiting + self.prefilling + self.running:
+            if not g.done:
+                self._fail(g, err)
+        self.waiting, self.prefilling, self.running = [], [], []
+        if self.spec is not None and hasattr(self.spec, "reset"):
+            self.spec.reset()
+        self.flush_events()
+
+    def tear_down(self, reason: str) -> None:
+        """A rank group whose members may be out of step (a peer wait ran out, a rank raised where the others did
+        not) cannot serve correct tokens any more: fail what is in flight, refuse what comes, report it on
+        ``/health`` so that the front takes the replica out (reference: the router stops everything when a replica
+        dies, ``engine/router.py:568-578``)."""
+        if self.broken is None:
+            self.broken = reason
+            print(f"engine: rank group torn down: {reason}", flush=True)
+        self.fail_all(f"replica unavailable: {reason}", 503)
+
     # ------------------------------------------------------------------ event delivery
     def _emit(self, g: Generation, ev: TokenEvent) -> None:
         """Token events are handed to their consumers (the HTTP handler threads) only at points where this thread
@@ -441,6 +514,7 @@ class Engine:
         self._deferred.append((g, ev))
 
     def flush_events(self) -> None:
+        self._flushed = True
         if self._deferred:
             pending, self._deferred = self._deferred, []
             for g, ev in pending:
@@ -452,20 +526,44 @@ class Engine:
 
         In a tensor-parallel replica the ranks first exchange the iteration's new requests and
         cancellations (``parallel.lockstep``); ``synced`` says the caller has already done so."""
+        self._flushed = False
         if self.coordinator is None:
             self._poll_local()
         elif not synced and not self.coordinator.sync(self):
             return False
-        with looptimers.stage("admit"):
-            self._admit()
-        if self.prefilling:
-            self.flush_events()  # a prefill pass is long: do not hold decode tokens behind it
-        with looptimers.stage("prefill"):
-            did = self._prefill_pass()
-        with looptimers.stage("decode"):
-            did = self._decode_step() or did
-        if not self.running or self._graphs is None:
-            self.flush_events()  # no graph launch is coming that would deliver them
+        if self.broken is not None:
+            self.fail_all(f"replica unavailable: {self.broken}", 503)
+            return False
+        if self.device_error_pending and self.coordinator is None:
+            # no agreement channel (the caller steps the ranks itself): this rank stops trusting the group at once
+            self.tear_down("a device-side wait or check failed on this rank")
+            return False
+        try:
+            with looptimers.stage("admit"):
+                self._admit()
+            if self.prefilling:
+                self.flush_events()  # a prefill pass is long: do not hold decode tokens behind it
+            self._flushed = False  # only a delivery after this iteration's passes counts below
+            with looptimers.stage("prefill"):
+                did = self._prefill_pass()
+            with looptimers.stage("decode"):
+                did = self._decode_step() or did
+        except Exception as e:  # noqa: BLE001
+            # Anything that escapes the per-pass handlers (sampling, emission, bookkeeping) would otherwise leave
+            # requests half-advanced and fail again on every iteration: fail everything in flight, start clean
+            # (reference: a failed step is reported to every request of the step, engine/server.py:291-296)
+            import traceback
+
+            traceback.print_exc()
+            self.stats["step_errors"] += 1
+            self.fail_all(f"engine step failed: {e!r}")
+            if self.multi_rank:
+                self.device_error_pending = True  # the ranks can no longer be assumed to be in step
+            return True
+        if not self.running or self._graphs is None or not self._flushed:
+            # no graph launch is coming that would deliver them, or this iteration ran without one (eager fallback
+            # after a failed capture, a batch outside the buckets): tokens must still stream once per step
+            self.flush_events()
         return did
 
     def warmup(self) -> None:
@@ -488,6 +586,7 @@ class Engine:
         out = dict(self.stats)
         cs = self.cache.stats
         out.update(
+            broken=self.broken,
             prefix_cache_entries=len(self.cache), prefix_cache_bytes=self.cache.bytes,
             prefix_cache_tail_hits=cs.tail_hits, prefix_cache_snapshot_hits=cs.snapshot_hits,
             prefix_cache_evictions=cs.evictions, kv_pages_free=self.pages.free, kv_pages_total=self.pages.num_pages - 1,

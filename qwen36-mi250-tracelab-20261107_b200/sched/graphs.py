@@ -41,8 +41,10 @@ class _Bucket:
         self.np_tokens, self.np_positions, self.np_slots, self.np_tables = (t.numpy() for t in h)
         self.seq = torch.arange(size, dtype=torch.int32, device=dev)
         self.h_picks = torch.zeros(size, dtype=torch.int64)
+        self.h_err = torch.zeros(1, dtype=torch.int32)
         if dev.type == "cuda":
             self.h_picks = self.h_picks.pin_memory()
+            self.h_err = self.h_err.pin_memory()
         self.rows: list = [None] * size  # (request id, page count, last page) whose table each row currently holds
         self.live = 0
         self.batch = PackedBatch(self.tokens, self.positions, self.seq, self.slots, self.tables, 1)
@@ -86,8 +88,11 @@ class _Bucket:
             body()
         torch.cuda.current_stream().wait_stream(s)
         g = torch.cuda.CUDAGraph()
+        count = getattr(engine.ops, "launch_count", None)
+        n0 = count() if count else 0
         with torch.cuda.graph(g):
             self.hidden, self.picks = body()
+        self.launches = (count() - n0) if count else 0  # kernels of this library in one replay
         self.graph = g
 
 
@@ -144,8 +149,13 @@ class DecodeGraphs:
         stop()
         self.engine.flush_events()  # the previous step's tokens go out while the GPU runs this one
         b.h_picks.copy_(b.picks, non_blocking=True)
+        err = getattr(self.engine.ops, "err_word", None)
+        if err is not None:  # the device error word travels with the picks: one more 4-byte copy, no extra sync
+            b.h_err.copy_(err(self.engine.device), non_blocking=True)
         with looptimers.stage("wait"):
             torch.cuda.current_stream().synchronize()
+        if err is not None:
+            self.engine.check_device(int(b.h_err[0]))
         return b.hidden[:n], b.h_picks[:n]
 
 
@@ -178,6 +188,7 @@ class _VerifyBucket:
         self.batch = PackedBatch(self.tokens, self.positions, self.seq, self.slots, self.tables, G)
         self.ring = ring
         self.h_out = torch.zeros(size * G + size + size * kmax, dtype=torch.int64).pin_memory()
+        self.h_err = torch.zeros(1, dtype=torch.int32).pin_memory()
         self.rows: list = [None] * size
         self.live = 0
         self.graph: torch.cuda.CUDAGraph | None = None
@@ -282,7 +293,9 @@ class VerifyGraphs:
         b.graph.replay()
         self.engine.flush_events()
         b.h_out.copy_(b.out, non_blocking=True)
+        b.h_err.copy_(self.engine.ops.err_word(self.engine.device), non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        self.engine.check_device(int(b.h_err[0]))
         G, size = b.G, b.size
         out = b.h_out
         picks = out[: size * G].view(size, G)[:n].tolist()

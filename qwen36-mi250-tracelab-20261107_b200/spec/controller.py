@@ -238,6 +238,7 @@ class SpecController:
         base_pos = batch.positions.view(B, G)[:, 0] + acc + 1
         self._chain_links(gens, h, d, base_pos, drafts)
         eng.flush_events()
+        eng.check_device()
         return picks.view(B, G).tolist(), acc.tolist(), torch.stack(drafts, dim=1).tolist(), ring, batch.slots
 
     def _book(self, gens, elig, n_valid, k, picks_h, acc_h, drafts_h, ring, slots_t) -> None:
@@ -282,6 +283,10 @@ class SpecController:
             st["mtp_verify_steps"] += 1
             st["mtp_proposed"] += sum(n_valid)
             st["mtp_accepted"] += sum(min(a, n) for a, n, e in zip(acc_h, n_valid, elig) if e)
+
+    def reset(self) -> None:
+        """After the engine failed everything in flight: no per-request state lives here beyond the requests'."""
+        return None
 
     def settle(self, gen) -> None:
         """Nothing to undo: a verify step commits exactly the rows whose tokens were booked."""

@@ -65,6 +65,16 @@ def test_lockstep_replica_on_two_cpu_ranks():
     assert r.returncode == 0 and "OK lockstep" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
+def test_ranks_with_different_memory_budgets_agree_on_the_smallest_kv_pool():
+    r = _launch("kv_agree", 2, 29625, env={"CUDA_VISIBLE_DEVICES": ""})
+    assert r.returncode == 0 and "OK kv_agree" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_a_failure_on_one_rank_tears_the_whole_lockstep_replica_down():
+    r = _launch("lockstep_failure", 2, 29626, env={"CUDA_VISIBLE_DEVICES": ""})
+    assert r.returncode == 0 and "OK lockstep_failure" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
 def test_served_tensor_parallel_replica_speculates_like_a_single_process(tmp_path):
     """MTP speculation inside a leader + follower replica: same tokens as a single-process server without it."""
     from http_util import ServerProc, ids_of
