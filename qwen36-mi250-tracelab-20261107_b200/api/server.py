@@ -64,7 +64,9 @@ class EngineWorker(threading.Thread):
                 time.sleep(0.05)
                 continue
             if not busy and not eng.has_work():
-                self.wake.wait(timeout=0.05)
+                # replicas that run their passes together agree before every pass: an idle one must come back quickly,
+                # or it holds up the others' requests
+                self.wake.wait(timeout=0.001 if eng.tick is not None and eng.broken is None else 0.05)
                 self.wake.clear()
 
     def stop(self) -> None:
@@ -352,6 +354,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--replica-devices", default=env("ENGINE_REPLICA_DEVICES"))
     ap.add_argument("--device", default=env("ENGINE_DEVICE", "auto"), choices=["auto", "cpu", "cuda"])
     ap.add_argument("--max-seqs", type=int, default=int(env("ENGINE_SLOTS", "128")))
+    ap.add_argument("--expert-parallel", action="store_true", default=env("ENGINE_EP", "0") not in ("", "0"),
+                    help="the replicas of this server form one expert-parallel group: each holds all dense weights and "
+                         "1/N of the routed experts (one GPU per replica)")
     return ap
 
 
@@ -373,7 +378,28 @@ def load_service(args: argparse.Namespace) -> Service:
         cfg.pack_weights = True  # the server owns the weights it loads: stream them tile-packed
     tp = int(args.gpus_per_replica or os.environ.get("ENGINE_TP", "1") or 1)
     followers = []
-    if tp > 1:  # a tensor-parallel replica: this process is rank 0, the other ranks are child processes
+    from ..parallel import dpep
+
+    if dpep.env_group() is not None:
+        # one of N replicas that share their MoE blocks (data-parallel attention, expert-parallel experts)
+        tp = 1
+        weights = None
+        if args.model.startswith("random:"):
+            import tempfile
+
+            from ..config import ModelConfig
+            from ..models.checkpoint import random_weights
+            from ..models.tiny import build_tokenizer
+
+            device = torch.device("cuda", dpep.env_group()[3]) if use_cuda else torch.device("cpu")
+            mcfg = ModelConfig.tiny() if args.model == "random:tiny" else ModelConfig.qwen36_35b_a3b()
+            weights = random_weights(mcfg, seed=0, device=device, dtype=torch.bfloat16 if use_cuda else torch.float32)
+            tok_dir = tempfile.mkdtemp(prefix="b200serve-tok-")
+            build_tokenizer(512).save_pretrained(tok_dir)
+            args.model_dir_for_tokenizer = tok_dir
+        engine = dpep.build_engine(args.model, cfg, use_cuda, weights=weights)
+        device = engine.device
+    elif tp > 1:  # a tensor-parallel replica: this process is rank 0, the other ranks are child processes
         from ..parallel import replica
 
         passthrough = ["--max-model-len", str(args.max_model_len), "--prefill-chunk-tokens",
@@ -417,6 +443,8 @@ def main(argv: list[str] | None = None) -> None:
     args = build_parser().parse_args(argv)
     from ..router import router
 
+    if args.expert_parallel:
+        os.environ["ENGINE_EP"] = "1"
     layout = router.resolve_layout(args.replicas, args.gpus_per_replica, args.replica_devices)
     if layout is not None and len(layout) > 1:
         router.serve(sys.argv[1:] if argv is None else argv, args.host, args.port, layout)
@@ -431,6 +459,9 @@ def main(argv: list[str] | None = None) -> None:
         pass
     finally:
         service.worker.stop()
+        if service.engine.tick is not None:
+            service.worker.join(timeout=5)
+            service.engine.tick.stop(service.engine)
         if service.engine.coordinator is not None:
             service.worker.join(timeout=5)
             service.engine.coordinator.stop(service.engine)

@@ -261,11 +261,13 @@ def _pack_moe(router, gate_up, down, sh_gu, sh_down, sh_gate) -> dict[str, Any]:
 
 
 def load_checkpoint(path: str | Path, device: str | torch.device = "cpu", dtype: torch.dtype | None = None,
-                    shard: tuple[int, int] | None = None) -> Weights:
+                    shard: tuple[int, int] | None = None, experts: tuple[int, int] | None = None) -> Weights:
     """Read a HF-layout checkpoint directory into engine ``Weights`` on ``device``.
 
     ``shard = (rank, world)`` keeps only that rank's tensor/expert-parallel part: every layer is
-    cut on the host right after it is read, so a rank never holds more than one full layer."""
+    cut on the host right after it is read, so a rank never holds more than one full layer.
+    ``experts = (rank, world)`` keeps all dense weights and only that rank's routed experts plus the shared one
+    (data-parallel attention with expert-parallel MoE, ``parallel/ep.py``); the MTP block is not loaded then."""
     path = Path(path)
     cfg = ModelConfig.from_pretrained(path)
     src = _TensorSource(path)
@@ -280,11 +282,15 @@ def load_checkpoint(path: str | Path, device: str | torch.device = "cpu", dtype:
         cut = lambda lw, i: shard_layer(lw, cfg, rank, world, i)  # noqa: E731
         per = (cfg.vocab_size + world - 1) // world
         v0, v1 = rank * per, min(cfg.vocab_size, (rank + 1) * per)
+    if experts is not None and experts[1] > 1:
+        from ..parallel.ep import shard_layer_experts
+
+        cut = lambda lw, i: shard_layer_experts(lw, cfg.num_experts, experts[0], experts[1])  # noqa: E731
     layers = []
     for i, kind in enumerate(cfg.layer_types):
         layers.append(_layer_to(cut(_load_layer(src, f"layers.{i}.", kind, cfg), i), device, dtype))
     mtp = None
-    if cfg.mtp_num_hidden_layers and src.has("mtp.fc.weight"):
+    if cfg.mtp_num_hidden_layers and src.has("mtp.fc.weight") and not (experts is not None and experts[1] > 1):
         lw = cut(_load_layer(src, "mtp.layers.0.", "full_attention", cfg), len(cfg.layer_types))
         mtp = MTPWeights(
             fc=src.get("mtp.fc.weight").to(device=device, dtype=dtype),

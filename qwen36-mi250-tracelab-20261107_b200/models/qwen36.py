@@ -290,6 +290,15 @@ class Model:
                 res, h = self._layer(lw, h, res, batch, nxt, kv_layer=self.kv[self._kv_index[i]])
         return h
 
+    def forward_empty(self) -> None:
+        """This rank's share of a pass in which it has no rows (data-parallel attention with expert-parallel MoE): it
+        still hosts experts for the other ranks' rows, so it takes part in every layer's dispatch and combine."""
+        assert self.ep is not None
+        x = torch.empty(0, self.cfg.hidden_size, dtype=self.dtype, device=self.device)
+        for lw in self.w.layers:
+            self.ep.forward(x, lw.router, lw.w_gate_up, lw.w_down, residual=None, norm_w=lw.post_norm,
+                            eps=self.cfg.rms_norm_eps)
+
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         out = self.ops.linear(hidden, self.w.lm_head, out_dtype=torch.float32)
         if self.tp is None:

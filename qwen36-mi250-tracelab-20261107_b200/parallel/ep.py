@@ -244,26 +244,28 @@ class EpMoE:
         self._opened, self._own = [], {}
 
 
+def shard_layer_experts(lw, n_experts: int, rank: int, world: int):
+    """One layer with only this rank's ``E / world`` routed experts and the shared expert (stacked last)."""
+    import copy
+
+    if n_experts % world:
+        raise ValueError(f"{n_experts} experts do not split over {world} ranks")
+    if not lw.shared_merged:
+        raise ValueError("expert parallelism needs the shared expert merged into the expert stack")
+    per = n_experts // world
+    out = copy.copy(lw)
+    sel = torch.tensor(list(range(rank * per, (rank + 1) * per)) + [n_experts], device=lw.w_gate_up.device)
+    out.w_gate_up = lw.w_gate_up[sel].contiguous()
+    out.w_down = lw.w_down[sel].contiguous()
+    return out
+
+
 def shard_experts(weights, rank: int, world: int):
     """This rank's weights for data-parallel attention + expert-parallel MoE: everything dense stays whole, every
     layer keeps only its ``E / world`` routed experts and a replica of the shared expert (stacked last), in the order
-    ``EpMoE`` expects. The MTP block is dropped (speculation is not combined with this mode)."""
-    import copy
-
+    ``EpMoE`` expects. The MTP block is dropped (drafting would make the ranks' pass sequences differ)."""
     from ..models.checkpoint import Weights
 
     cfg = weights.config
-    E = cfg.num_experts
-    if E % world:
-        raise ValueError(f"{E} experts do not split over {world} ranks")
-    per = E // world
-    layers = []
-    for lw in weights.layers:
-        if not lw.shared_merged:
-            raise ValueError("expert parallelism needs the shared expert merged into the expert stack")
-        out = copy.copy(lw)
-        sel = torch.tensor(list(range(rank * per, (rank + 1) * per)) + [E], device=lw.w_gate_up.device)
-        out.w_gate_up = lw.w_gate_up[sel].contiguous()
-        out.w_down = lw.w_down[sel].contiguous()
-        layers.append(out)
+    layers = [shard_layer_experts(lw, cfg.num_experts, rank, world) for lw in weights.layers]
     return Weights(cfg, weights.embed, weights.lm_head, weights.final_norm, layers, None)

@@ -208,11 +208,23 @@ def start_replicas(argv: list[str], layout: list[list[int]], pin: bool = True) -
                 slices = cpu_place.replica_slices(topo, layout)
         except Exception as e:  # noqa: BLE001
             print(f"cpu_place: placement skipped ({e})", flush=True)
+    # ENGINE_EP=1 (--expert-parallel): the replicas form ONE expert-parallel group (parallel/dpep.py): each keeps the
+    # dense weights and 1 / N of the routed experts, and their MoE blocks exchange rows over NVLink. Peer memory is
+    # mapped by CUDA IPC, so every replica has to see all GPUs of the group; it runs on the one named ENGINE_EP_LOCAL.
+    ep_group = os.environ.get("ENGINE_EP", "0") not in ("", "0") and len(layout) > 1
+    ep_port = _free_port() if ep_group else 0
+    all_devices = [d for grp in layout for d in grp]
     replicas = []
     for i, devices in enumerate(layout):
         port = _free_port()
         env = dict(os.environ)
         env.update(device_env(devices))
+        if ep_group:
+            if any(len(grp) > 1 for grp in layout):
+                raise ValueError("an expert-parallel group takes one GPU per replica")
+            env.update(device_env(all_devices))
+            env.update(ENGINE_EP_WORLD=str(len(layout)), ENGINE_EP_RANK=str(i), ENGINE_EP_PORT=str(ep_port),
+                       ENGINE_EP_LOCAL=str(all_devices.index(devices[0]) if devices else i))
         cpus = None
         if slices is not None:
             cpus = slices[i].cpus

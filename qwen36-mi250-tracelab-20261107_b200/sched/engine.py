@@ -52,6 +52,7 @@ class Engine:
         self.cfg = cfg or EngineConfig()
         self.tp = tp
         self.coordinator = None  # parallel.lockstep.Coordinator in a multi-rank replica
+        self.tick = None  # parallel.dpep.TickCoordinator: data-parallel replicas that share expert-parallel MoE blocks
         self.mcfg: ModelConfig = weights.config
         self.device = weights.device
         self.ops = ops or _select_ops(self.device)
@@ -278,6 +279,14 @@ class Engine:
             budget -= b - a
             if budget <= 0:
                 break
+        if self.tick is not None:
+            # Replicas that share their MoE blocks run every pass together: a prefill pass happens on all of them as
+            # soon as one has a span to compute; a replica without one joins with an empty pass (it still hosts
+            # experts for the others' rows).
+            if not self.tick.any(self, bool(picked)):
+                return False
+            if not picked:
+                return self._empty_pass()
         if not picked:
             return False
         spans = [g.spans[0] for g in picked]
@@ -329,13 +338,23 @@ class Engine:
         if not self.cache.store_snapshot(gen.prompt, gen.computed, gen.pages, slot):
             self.slots.release(slot)
 
+    def _empty_pass(self) -> bool:
+        """This replica's part of a pass in which it has no rows of its own."""
+        try:
+            self.model.forward_empty()
+            self.check_device()
+        except Exception as e:  # noqa: BLE001
+            print(f"engine: empty pass failed: {e!r}", flush=True)
+            self.device_error_pending = True
+        return True
+
     # ------------------------------------------------------------------ decode
     def _decode_step(self) -> bool:
         for gen in list(self.running):
             if gen.cancel_now:
                 self.running.remove(gen)
                 self._finish(gen, "cancelled")
-        if not self.running:
+        if not self.running and self.tick is None:
             return False
         if self.spec is not None:
             try:
@@ -356,6 +375,11 @@ class Engine:
             except OutOfCapacity:
                 self.running.remove(gen)
                 self._fail(gen, EngineError("the KV cache is full", 503, "service_unavailable"))
+        if self.tick is not None:
+            if not self.tick.any(self, bool(batch_gens)):
+                return False
+            if not batch_gens:
+                return self._empty_pass()
         if not batch_gens:
             return False
         B = len(batch_gens)

@@ -109,6 +109,10 @@ class DecodeGraphs:
         self.width = self.widths[-1]
         self.buckets: dict = {}
         self.errors: dict = {}
+        # Replicas that share expert-parallel MoE blocks must launch the same passes: capturing a graph runs the pass
+        # once for real, so every shape is captured at start-up (``warm``), on all replicas in the same order, and
+        # never later; a shape without a graph runs kernel by kernel.
+        self.frozen = False
 
     def usable(self, gens) -> bool:
         if len(gens) > self.sizes[-1]:
@@ -120,7 +124,7 @@ class DecodeGraphs:
         width = next(w for w in self.widths if w >= pages)
         key = (size, width)
         b = self.buckets.get(key)
-        if b is None and key not in self.errors:
+        if b is None and key not in self.errors and not self.frozen:
             b = _Bucket(self.engine, size, width)
             try:
                 b.capture(self.engine)
@@ -131,8 +135,11 @@ class DecodeGraphs:
         return b
 
     def warm(self) -> None:
-        for s in self.sizes:
-            self._bucket(s)
+        every_width = self.engine.tick is not None
+        for w in (self.widths if every_width else self.widths[:1]):
+            for s in self.sizes:
+                self._bucket(s, w)
+        self.frozen = every_width
 
     def run(self, gens, tokens, positions):
         n = len(gens)
@@ -140,7 +147,9 @@ class DecodeGraphs:
         if b is None:
             eng = self.engine
             batch = PackedBatch.uniform(tokens, positions, [g.slot for g in gens], eng._table(gens), 1, eng.device)
-            return eng.model.forward(batch), None
+            hidden = eng.model.forward(batch)
+            eng.check_device()
+            return hidden, None
         with looptimers.stage("build"):
             b.fill(gens, tokens, positions)
         start, stop = looptimers.gpu_span("gpu_graph")
@@ -265,6 +274,10 @@ class VerifyGraphs:
         self.pool = torch.cuda.graph_pool_handle()
         self.buckets: dict = {}
         self.errors: dict = {}
+        # Replicas that share expert-parallel MoE blocks must launch the same passes: capturing a graph runs the pass
+        # once for real, so every shape is captured at start-up (``warm``), on all replicas in the same order, and
+        # never later; a shape without a graph runs kernel by kernel.
+        self.frozen = False
 
     def usable(self, gens) -> bool:
         return self.decode.usable(gens)

@@ -189,3 +189,86 @@ def test_two_rank_data_parallel_attention_with_expert_parallel_moe():
                         "dp_ep_model"], capture_output=True, text=True, timeout=600,
                        env={**os.environ, "NCCL_NVLS_ENABLE": "0"})
     assert r.returncode == 0 and "OK dp_ep_model" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def _gemm_allreduce(comm, x, w, residual=None, bt=0):
+    """The tensor-parallel output projection (GEMM whose epilogue is the all-reduce) on a symmetric context."""
+    from b200serve.ops import cuda_ops
+    from b200serve.parallel import symm
+
+    L = symm._lib()
+    P, I = ctypes.c_void_p, ctypes.c_int
+    L.b200_gemm_allreduce.argtypes = [ctypes.c_void_p, P, P, P, P, I, I, I, I, I, I, P]
+    L.b200_gemm_allreduce.restype = I
+    T, K = x.shape
+    N = w.shape[0]
+    out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+    rc = L.b200_gemm_allreduce(ctypes.byref(comm.ctx), x.data_ptr(), w.data_ptr(),
+                               None if residual is None else residual.data_ptr(), out.data_ptr(), T, N, K, x.stride(0),
+                               w.stride(0), bt, torch.cuda.current_stream().cuda_stream)
+    if rc:
+        raise cuda_ops.KernelError(f"gemm_allreduce failed with code {rc}")
+    return out
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 256, 128), (33, 2048, 512), (128, 2048, 4096)])
+def test_gemm_with_allreduce_epilogue_loopback_against_fp32(T, N, K):
+    """One-rank group: the tile goes TMEM -> receive slot -> rank-order sum (+ residual) -> bf16. Checked against the
+    fp32 product, and bit for bit against the plain GEMM followed by the same rounding steps."""
+    from b200serve.ops import cuda_ops
+    from b200serve.parallel.symm import SymmComm
+
+    dev = torch.device("cuda")
+    comm = SymmComm(dev, None, slot_elems=1 << 19, max_blocks=512)
+    g = torch.Generator(device=dev).manual_seed(T + N)
+    w = (torch.randn(N, K, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    for rep in range(3):  # epochs advance, receive parities alternate
+        x = torch.randn(T, K, device=dev, generator=g).to(torch.bfloat16)
+        r = torch.randn(T, N, device=dev, generator=g).to(torch.bfloat16)
+        ref = x.float() @ w.float().t()
+        got = _gemm_allreduce(comm, x, w)
+        err = (got.float() - ref).abs().max().item()
+        assert err <= 2e-2 * max(1.0, ref.abs().max().item()), (rep, err)
+        assert torch.equal(got, cuda_ops.linear(x, w))
+        got_r = _gemm_allreduce(comm, x, w, r)
+        want_r = (cuda_ops.linear(x, w).float() + r.float()).to(torch.bfloat16)
+        assert torch.equal(got_r, want_r)
+    cuda_ops.check_errors(dev)
+    comm.close()
+
+
+def test_two_thousand_back_to_back_collectives_never_read_a_stale_slot():
+    """Stale-read stress: every call's inputs depend on the call number, every result is checked (on the device, one
+    read-back at the end). Covers the push all-reduce, the GEMM + all-reduce epilogue and the expert-parallel block,
+    whose flags and receive slots are reused with alternating parity / advancing epochs
+    (reference: epoch-dependent fill + check over thousands of calls, tools/tp_bench.py:231-250)."""
+    from b200serve.ops import cuda_ops
+    from b200serve.parallel.ep import EpMoE
+    from b200serve.parallel.symm import SymmComm
+
+    dev = torch.device("cuda")
+    comm = SymmComm(dev, None, slot_elems=1 << 16, max_blocks=64)
+    g = torch.Generator(device=dev).manual_seed(9)
+    base = torch.randn(8, 512, device=dev, generator=g)
+    w = (torch.randn(256, 512, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    E, H, I, k = 8, 256, 128, 2
+    router = (torch.randn(E + 1, H, device=dev, generator=g) * 0.3).to(torch.bfloat16)
+    wgu = (torch.randn(E + 1, 2 * I, H, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    wd = (torch.randn(E + 1, H, I, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    ep = EpMoE(dev, None, E, H, k, max_rows=16)
+    lgu, ld = ep.local_experts(wgu, wd)
+    xe = torch.randn(16, H, device=dev, generator=g)
+    bad = torch.zeros(3, dtype=torch.int64, device=dev)
+    for i in range(2000):
+        x = (base + 0.01 * (i % 97)).to(torch.bfloat16)
+        res = (base * 0.5 - 0.02 * (i % 31)).to(torch.bfloat16)
+        bad[0] += (comm.allreduce(x, res) != x + res).any()
+        want = (cuda_ops.linear(x, w).float() + 0.0).to(torch.bfloat16)
+        bad[1] += (_gemm_allreduce(comm, x, w) != want).any()
+        if i % 4 == 0:  # the MoE block is a dozen launches: every fourth call keeps the test short
+            rows = (xe + 0.01 * (i % 53)).to(torch.bfloat16)[: 1 + i % 16]
+            bad[2] += (ep.forward(rows, router, lgu, ld) != cuda_ops.moe_block(rows, router, wgu, wd, E, k, True)).any()
+    assert bad.tolist() == [0, 0, 0]
+    cuda_ops.check_errors(dev)
+    ep.close()
+    comm.close()

@@ -399,3 +399,20 @@ def test_moe_block_with_fused_residual_norm(C, T, E, k, H, I):
     got_res, got_y = C.moe_block(x, router, wgu, wd, E, k, True, residual=None, norm_w=nw, eps=1e-6)
     assert torch.equal(got_res, want_res) and torch.equal(got_y, want_y)
     C.check_errors(x.device)
+
+
+@pytest.mark.parametrize("packed", [False, True])
+def test_lm_head_argmax_at_full_vocabulary_against_fp32(C, packed):
+    """248320 x 2048 LM head (the served size): the fused argmax must pick a token whose fp32 logit is the fp32
+    maximum up to accumulation-order noise, and must agree exactly with the argmax of the kernel's own fp32 logits."""
+    V, K, T = 248320, 2048, 9
+    x, w = _bf(T, K, seed=41), _bf(V, K, scale=0.02, seed=42)
+    ref = x.float() @ w.float().t()
+    own = C.linear(x, w, out_dtype=torch.float32)
+    wk = C.pack_weight(w.clone()) if packed else w
+    idx, val = C.lm_head_argmax(x, wk, return_value=True)
+    assert torch.equal(idx, own.argmax(-1)) and torch.equal(val, own.max(-1).values)
+    picked = ref.gather(1, idx[:, None])[:, 0]
+    top = ref.max(-1).values
+    assert ((top - picked) <= 2e-3 * top.abs().clamp_min(1.0)).all(), (top - picked).max().item()
+    C.check_errors(x.device)
