@@ -217,6 +217,50 @@ def case_attn_prefill(small):
     report(f"attn_prefill_{nseg}x{L}", us, qkv.numel() * 2 + T * n_q * D * 2, flops)
 
 
+def case_glue(small):
+    """Row-wise glue of a decode step at 128 rows: residual add + RMSNorm, embedding gather, the MTP block's input
+    kernel and the chain-acceptance kernel of a verify step (4 rows per sequence)."""
+    T, H, V = 128, 2048, 248320 if not small else 32768
+    x, r, w = bf(T, H), bf(T, H), bf(H, scale=0.1)
+    report("add_rmsnorm_b128", timed(lambda: C.add_rmsnorm(x, r, w, 1e-6)), 4 * T * H * 2, 0)
+    table = bf(V, H, scale=0.02)
+    tok = torch.randint(0, V, (T,), device="cuda")
+    report("embed_b128", timed(lambda: C.embed(tok, table)), 2 * T * H * 2, 0)
+    report("mtp_in_b128", timed(lambda: C.mtp_in(tok, table, x, w, w, 1e-6)), 4 * T * H * 2, 0)
+    G = 4
+    picks, toks = torch.randint(0, 9, (T * G,), device="cuda"), torch.randint(0, 9, (T * G,), device="cuda")
+    nv = torch.full((T,), G - 1, dtype=torch.int32, device="cuda")
+    pos = torch.arange(T * G, device="cuda")
+    y = bf(T * G, H)
+    report("chain_accept_b128x4", timed(lambda: C.chain_accept(toks, picks, nv, pos, y, G, 2)), 2 * T * H * 2, 0)
+
+
+def case_allreduce_loopback(small):
+    """One-shot push all-reduce of a decode-size message (128 x 2048 bf16) on a one-rank group: the kernel's own
+    cost without the NVLink hop (stores into this GPU's receive slot, flag release / wait, rank-order sum)."""
+    from b200serve.parallel.symm import SymmComm
+
+    comm = SymmComm(torch.device("cuda"), None, slot_elems=1 << 19, max_blocks=512)
+    x, r = bf(128, 2048), bf(128, 2048)
+    report("allreduce_push_loopback_128x2048", timed(lambda: comm.allreduce(x, r)), 3 * x.numel() * 2, 0)
+    comm.close()
+
+
+def case_ep_loopback(small):
+    """The expert-parallel MoE block on a one-rank group at decode size: send, plan, gathering gate/up GEMM, scatter
+    epilogue of the down GEMM, combine + residual + norm (every kernel of the multi-GPU path, peer stores local)."""
+    from b200serve.parallel.ep import EpMoE
+
+    T, E, H, I = 128, (64 if small else 256), 2048, 512
+    router = pk(bf(E + 1, H, scale=0.3))
+    wgu, wd = pk(bf(E + 1, 2 * I, H, scale=0.02), True), pk(bf(E + 1, H, I, scale=0.02))
+    ep = EpMoE(torch.device("cuda"), None, E, H, 8, max_rows=T)
+    x, r, w = bf(T, H), bf(T, H), bf(H, scale=0.1)
+    us = timed(lambda: ep.forward(x, router, wgu, wd, residual=r, norm_w=w))
+    report(f"ep_moe_loopback_b{T}", us, (wgu.numel() + wd.numel() + router.numel()) * 2, 2 * T * 9 * 3 * H * I, experts=E)
+    ep.close()
+
+
 CASES = {k[5:]: v for k, v in globals().items() if k.startswith("case_")}
 
 if __name__ == "__main__":

@@ -1,0 +1,159 @@
+"""Parity gates on the GPU: what the reference checks with its gate scripts before a change is served.
+
+    python bench/parity_gate.py [--layers 8] [--prompts 8] [--prompt-len 384] [--tokens 48] [--depth 3]
+
+Three gates on one random-init model of the full layer shapes (``--layers`` of them: 3 Gated DeltaNet + 1 attention
+per group, 256 experts, real head sizes), each printed as one JSON line with ``"pass"``:
+
+1. ``teacher_forced_top1``: a plain PyTorch run of the same bf16 weights (``ops.torch_ops``, the oracle of every
+   kernel test: same rounding points, library matmuls) generates greedy continuations; the sm_100a path is then fed
+   exactly those tokens, once through its
+   prefill kernels (one packed pass) and once through its decode kernels (token by token, batched), and must pick
+   the oracle's token at >= 98.5 % of the positions (reference threshold: ``tools/combine_k_check.sh:8-12``,
+   method: ``tools/tp_parity.py``, ``engine/bench_step.py:424-437``). Also reports the largest logit difference.
+2. ``spec_equals_plain``: greedy outputs with MTP speculation at ``--depth`` equal the outputs without it for all
+   prompts (reference: ``tools/chain_gate.py``, "spec == plain 8/8").
+3. ``bitwise_repeatable``: the same batch generated three times through the captured decode graphs gives identical
+   tokens and bit-identical final logits (reference: ``tools/topk_epi_check.py``).
+
+Exit code 0 when every gate passes.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+from b200serve.config import PAGE_SIZE, EngineConfig, ModelConfig  # noqa: E402
+from b200serve.models.checkpoint import random_weights  # noqa: E402
+from b200serve.models.qwen36 import Model, PackedBatch  # noqa: E402
+from b200serve.ops import cuda_ops, torch_ops  # noqa: E402
+from b200serve.sched.engine import Engine  # noqa: E402
+from b200serve.sched.request import Sampling  # noqa: E402
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--prompts", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=384)
+    ap.add_argument("--tokens", type=int, default=48)
+    ap.add_argument("--depth", type=int, default=3)
+    ap.add_argument("--router-scale", type=float, default=16.0)
+    ap.add_argument("--tiny", action="store_true", help="the CPU-sized architecture (quick self-check of this script)")
+    a = ap.parse_args()
+    dev = torch.device("cuda")
+    cfg = ModelConfig.tiny() if a.tiny else ModelConfig(num_hidden_layers=a.layers)
+    # a wide LM head gives greedy margins that bf16 rounding cannot flip at random (the reference's tiny fixture does
+    # the same, .vibesys/shared/cpu_check/tiny_checkpoint.py:24-150); everything else is N(0, 0.02)
+    w16 = random_weights(cfg, seed=0, device=dev, dtype=torch.bfloat16, std=0.02, lm_head_std=0.5)
+    # Random routers score all 256 experts almost equally, so the 8th and 9th expert of a row differ in the last bits
+    # and any two correct implementations pick different experts; trained routers are decisive. Scaling the random
+    # router makes the choice decisive here too (both sides share the weights), so the gate measures the kernels.
+    for lw in w16.layers:
+        lw.router[: cfg.num_experts].mul_(a.router_scale)
+    w32 = w16  # the oracle runs the same bf16 weights through plain PyTorch ops
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(3, cfg.vocab_size, (a.prompt_len + 17 * i,), generator=g).tolist() for i in range(a.prompts)]
+    samp = Sampling(max_tokens=a.tokens, ignore_eos=True)
+    ok_all = True
+
+    # ---------------------------------------------------------------- gate 1
+    ecfg = EngineConfig(max_model_len=4096, prefill_chunk_tokens=2048, max_seqs=a.prompts, mtp=False, kv_pages=1024,
+                        cuda_graphs=False)
+    oracle = Engine(w32, ecfg, ops=torch_ops)
+    want = [x.output for x in oracle.generate(prompts, samp)]
+    del oracle
+    torch.cuda.empty_cache()
+    pages_per = (a.prompt_len + 17 * a.prompts + a.tokens) // PAGE_SIZE + 2
+    B = a.prompts
+    tables = (torch.arange(B * pages_per, dtype=torch.int32).view(B, pages_per) + 1)
+
+    def logits_of(model, rows):
+        return model.logits(rows).float()
+
+    ref_model = Model(w32, num_pages=B * pages_per + 1, state_slots=B + 1, ops=torch_ops)
+    got_model = Model(w16, num_pages=B * pages_per + 1, state_slots=B + 1, ops=cuda_ops)
+    slots = list(range(1, B + 1))
+    # (a) prefill kernels: prompt + continuation in one packed pass; row p + j - 1 predicts continuation token j
+    seqs = [p + o[:-1] for p, o in zip(prompts, want)]
+    agree = total = 0
+    max_diff = 0.0
+    for model in (ref_model, got_model):
+        model.hid = model.forward(PackedBatch.prefill(seqs, slots, [0] * B, tables, dev))
+    start = 0
+    for p, o, s in zip(prompts, want, seqs):
+        rows = torch.arange(start + len(p) - 1, start + len(s), device=dev)
+        lr, lg = logits_of(ref_model, ref_model.hid[rows]), logits_of(got_model, got_model.hid[rows])
+        agree += int((lg.argmax(-1).cpu() == torch.tensor(o)).sum())
+        total += len(o)
+        max_diff = max(max_diff, float((lr - lg).abs().max()))
+        start += len(s)
+    r1 = agree / total
+    # (b) decode kernels: fresh state, prompts prefilled, then the oracle's tokens fed step by step
+    got2 = Model(w16, num_pages=B * pages_per + 1, state_slots=B + 1, ops=cuda_ops)
+    h = got2.forward(PackedBatch.prefill(prompts, slots, [0] * B, tables, dev))
+    ends = torch.tensor([sum(len(p) for p in prompts[: i + 1]) - 1 for i in range(B)], device=dev)
+    picks = got2.greedy(h[ends]).cpu()
+    agree2 = int((picks == torch.tensor([o[0] for o in want])).sum())
+    total2 = B
+    for j in range(1, a.tokens):
+        toks = [o[j - 1] for o in want]
+        pos = [len(p) + j - 1 for p in prompts]
+        h = got2.forward(PackedBatch.uniform(toks, pos, slots, tables, 1, dev))
+        picks = got2.greedy(h).cpu()
+        agree2 += int((picks == torch.tensor([o[j] for o in want])).sum())
+        total2 += B
+    r2 = agree2 / total2
+    cuda_ops.check_errors(dev)
+    ok = r1 >= 0.985 and r2 >= 0.985
+    ok_all &= ok
+    print(json.dumps({"gate": "teacher_forced_top1", "pass": ok, "prefill_kernels": round(r1, 4), "decode_kernels": round(r2, 4),
+                      "positions": total, "threshold": 0.985, "max_logit_diff_prefill": round(max_diff, 4),
+                      "layers": cfg.num_hidden_layers, "router_scale": a.router_scale,
+                      "oracle": "plain PyTorch ops on the same bf16 weights"}), flush=True)
+    del ref_model, got_model, got2, w32
+    torch.cuda.empty_cache()
+
+    # ---------------------------------------------------------------- gate 2
+    base = dict(max_model_len=4096, prefill_chunk_tokens=2048, max_seqs=a.prompts, kv_pages=1024)
+    plain = [x.output for x in Engine(w16, EngineConfig(mtp=False, **base)).generate(prompts, samp)]
+    spec_eng = Engine(w16, EngineConfig(mtp=True, spec_k=a.depth, spec_kmax=a.depth, **base))
+    spec = [x.output for x in spec_eng.generate(prompts, samp)]
+    same = sum(x == y for x, y in zip(plain, spec))
+    cuda_ops.check_errors(dev)
+    ok = same == len(prompts) and spec_eng.stats["mtp_verify_steps"] > 0
+    ok_all &= ok
+    print(json.dumps({"gate": "spec_equals_plain", "pass": ok, "equal": f"{same}/{len(prompts)}", "depth": a.depth,
+                      "verify_steps": spec_eng.stats["mtp_verify_steps"], "proposed": spec_eng.stats["mtp_proposed"],
+                      "accepted": spec_eng.stats["mtp_accepted"]}), flush=True)
+    del spec_eng
+    torch.cuda.empty_cache()
+
+    # ---------------------------------------------------------------- gate 3
+    eng = Engine(w16, EngineConfig(mtp=False, decode_buckets=(a.prompts,), **base))
+    runs, finals = [], []
+    for _ in range(3):
+        eng.cache.clear()
+        gens = eng.generate(prompts, samp)
+        runs.append([x.output for x in gens])
+        bucket = next(iter(eng._graphs.buckets.values()))
+        finals.append(eng.model.logits(bucket.hidden[: a.prompts]).clone())
+    same_tokens = runs[0] == runs[1] == runs[2]
+    same_bits = torch.equal(finals[0], finals[1]) and torch.equal(finals[1], finals[2])
+    cuda_ops.check_errors(dev)
+    ok = same_tokens and same_bits and bool(eng._graphs.buckets) and not eng._graphs.errors
+    ok_all &= ok
+    print(json.dumps({"gate": "bitwise_repeatable", "pass": ok, "tokens_equal": same_tokens, "final_logits_bitwise_equal": same_bits,
+                      "runs": 3, "graph_replays_per_run": a.tokens - 1}), flush=True)
+    return 0 if ok_all else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

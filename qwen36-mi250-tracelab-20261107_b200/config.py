@@ -247,6 +247,8 @@ class EngineConfig:
     one_pass_max: int = 4096
     decode_buckets: tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64, 128, 256)
     cuda_graphs: bool = True
+    graphs_on_cpu: bool = False  # tests: run the decode-graph scheduling (buckets, run-ahead) without a CUDA device
+    run_ahead: bool = True  # launch decode step n + 1 from device-built inputs before the host has read step n
     # tile-pack the GEMM weights on the GPU (in place: the engine then owns the weights; not under tensor parallelism)
     pack_weights: bool = False
     # parallelism inside one replica
@@ -256,7 +258,7 @@ class EngineConfig:
     # speculation
     mtp: bool = True
     spec_k: int = 0  # 0: policy picks; >0: fixed draft depth
-    spec_kmax: int = 3
+    spec_kmax: int = 3  # deepest draft chain the policy may choose (up to 7, as the reference's k in {1,3,4,5,7})
     # observability
     loop_timers: bool = False
     req_stamps: bool = False
@@ -271,6 +273,7 @@ class EngineConfig:
             "prefill_pack_tokens": "ENGINE_PREFILL_PACK_TOKENS",
             "one_pass_max": "ENGINE_PREFILL_ONE_PASS_MAX",
             "cuda_graphs": "ENGINE_CUDA_GRAPHS",
+            "run_ahead": "ENGINE_RUNAHEAD",
             "pack_weights": "ENGINE_PACK_WEIGHTS",
             "tp": "ENGINE_TP",
             "ep": "ENGINE_EP",

@@ -313,12 +313,20 @@ class Model:
         dist.all_gather(parts, pad, group=self.tp.comm.group)
         return torch.cat(parts, dim=1)[:, :V]
 
-    def greedy(self, hidden: torch.Tensor) -> torch.Tensor:
-        """Greedy next token of each row (LM head with fused argmax on the CUDA path)."""
+    def greedy(self, hidden: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Greedy next token of each row (LM head with fused argmax on the CUDA path). ``out``: int64 ``[rows]``
+        tensor that receives the picks (the captured speculative step assembles its result vector in place)."""
         if self.tp is None:
-            return self.ops.lm_head_argmax(hidden, self.w.lm_head)
-        idx, val = self.ops.lm_head_argmax(hidden, self.w.lm_head, return_value=True)
-        return self.tp.comm.argmax(val, idx + self.w.vocab_start)
+            if out is not None and self.ops is not torch_ops:
+                return self.ops.lm_head_argmax(hidden, self.w.lm_head, out=out)
+            picks = self.ops.lm_head_argmax(hidden, self.w.lm_head)
+        else:
+            idx, val = self.ops.lm_head_argmax(hidden, self.w.lm_head, return_value=True)
+            picks = self.tp.comm.argmax(val, idx + self.w.vocab_start)
+        if out is not None:
+            out.copy_(picks)
+            return out
+        return picks
 
     def mtp_forward(self, hidden: torch.Tensor, next_tokens: torch.Tensor, batch: PackedBatch) -> torch.Tensor:
         """The MTP block over packed rows: row ``t`` pairs base hidden ``H[t]`` with token ``x[t+1]``.
@@ -328,9 +336,14 @@ class Model:
         ``t+2``; reference: ``engine/mtp.py:7-12, 112-151``).
         """
         cfg, ops, m = self.cfg, self.ops, self.w.mtp
-        e = ops.rmsnorm(ops.embed(next_tokens, self.w.embed), m.pre_fc_norm_embedding, cfg.rms_norm_eps)
-        h = ops.rmsnorm(hidden, m.pre_fc_norm_hidden, cfg.rms_norm_eps)
-        x = ops.linear(torch.cat([e, h], dim=-1), m.fc)
+        if hasattr(ops, "mtp_in") and hidden.is_contiguous():  # embedding gather, both pre-norms and the concat: one kernel
+            x_in = ops.mtp_in(next_tokens, self.w.embed, hidden, m.pre_fc_norm_embedding, m.pre_fc_norm_hidden,
+                              cfg.rms_norm_eps)
+        else:
+            e = ops.rmsnorm(ops.embed(next_tokens, self.w.embed), m.pre_fc_norm_embedding, cfg.rms_norm_eps)
+            h = ops.rmsnorm(hidden, m.pre_fc_norm_hidden, cfg.rms_norm_eps)
+            x_in = torch.cat([e, h], dim=-1)
+        x = ops.linear(x_in, m.fc)
         res, h = ops.add_rmsnorm(x, None, m.layer.input_norm, cfg.rms_norm_eps)
         _, y = self._layer(m.layer, h, res, batch, m.norm, kv_layer=self.kv[self.mtp_kv_index])
         return y

@@ -324,6 +324,78 @@ __global__ void moe_combine_kernel(const bf16* pair_out, const float* wts, const
   }
 }
 
+// ------------------------------------------------------------------ MTP / speculative-chain glue
+// Input of the MTP block for packed rows: out[t] = [ rmsnorm(embed[tok[t]]) * (1 + w_e) | rmsnorm(hidden[t]) * (1 + w_h) ]
+// (zero-centred norms, fp32 math, bf16 out), one CTA per row (reference: _mtp_in_kernel, engine/fast/kernels.py:524-542).
+__global__ void mtp_in_kernel(const int64_t* tokens, const bf16* embed, const bf16* hidden, const bf16* w_e,
+                              const bf16* w_h, bf16* out, int H, int vocab, float eps) {
+  pdl_wait();
+  pdl_launch();
+  const int t = blockIdx.x;
+  int64_t tok = tokens[t];
+  if (tok < 0 || tok >= vocab) tok = 0;
+  extern __shared__ float vals[];  // H floats
+  __shared__ float part[32];
+  for (int half = 0; half < 2; ++half) {
+    const bf16* src = half == 0 ? embed + tok * H : hidden + static_cast<size_t>(t) * H;
+    const bf16* w = half == 0 ? w_e : w_h;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      uint4 xv = *reinterpret_cast<const uint4*>(src + i);
+      const bf16* xe = reinterpret_cast<const bf16*>(&xv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float f = __bfloat162float(xe[j]);
+        vals[i + j] = f;
+        ss += f * f;
+      }
+    }
+    ss = warp_sum(ss);
+    __syncthreads();  // part[] of the first half has been read by everyone
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < static_cast<int>(blockDim.x >> 5); ++i) tot += part[i];
+    const float inv = rsqrtf(tot / H + eps);
+    bf16* dst = out + static_cast<size_t>(t) * 2 * H + half * H;
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      uint4 wv = *reinterpret_cast<const uint4*>(w + i);
+      const bf16* we = reinterpret_cast<const bf16*>(&wv);
+      uint4 ov;
+      bf16* oe = reinterpret_cast<bf16*>(&ov);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) oe[j] = __float2bfloat16(vals[i + j] * inv * (1.0f + __bfloat162float(we[j])));
+      *reinterpret_cast<uint4*>(dst + i) = ov;
+    }
+  }
+}
+
+// After a verify pass over G = k + 1 rows per sequence: the number of leading drafts that equal the model's pick of
+// the row before them (acc), the MTP hidden of the last accepted row (the chain's first link starts from it), and
+// the positions of the chain's later links. One CTA per sequence (reference: _chain_accept_kernel,
+// engine/fast/kernels.py:544-571; _chain_next_kernel, engine/fast/tp.py:296-318).
+__global__ void chain_accept_kernel(const int64_t* tokens, const int64_t* picks, const int* n_valid,
+                                    const int64_t* positions, const bf16* y, int G, int H, int links, int B,
+                                    int64_t* acc_out, bf16* h_sel, int64_t* link_pos) {
+  pdl_wait();
+  pdl_launch();
+  const int b = blockIdx.x;
+  __shared__ int s_acc;
+  if (threadIdx.x == 0) {
+    int a = 0;
+    const int nv = n_valid[b] < G - 1 ? n_valid[b] : G - 1;
+    while (a < nv && tokens[static_cast<size_t>(b) * G + a + 1] == picks[static_cast<size_t>(b) * G + a]) ++a;
+    s_acc = a;
+    acc_out[b] = a;
+    const int64_t base = positions[static_cast<size_t>(b) * G] + a + 1;
+    for (int j = 0; j < links; ++j) link_pos[static_cast<size_t>(j) * B + b] = base + j;
+  }
+  __syncthreads();
+  const uint4* src = reinterpret_cast<const uint4*>(y + (static_cast<size_t>(b) * G + s_acc) * H);
+  uint4* dst = reinterpret_cast<uint4*>(h_sel + static_cast<size_t>(b) * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -406,6 +478,26 @@ extern "C" int b200_moe_combine_norm(const void* pair_out, const float* wts, con
                       static_cast<const bf16*>(pair_out), wts, inv, P, H, static_cast<bf16*>(nullptr),
                       static_cast<float*>(nullptr), static_cast<const bf16*>(res), static_cast<const bf16*>(norm_w),
                       static_cast<bf16*>(res_out), static_cast<bf16*>(y), eps));
+}
+
+extern "C" int b200_mtp_in(const int64_t* tokens, const void* embed, const void* hidden, const void* w_e,
+                           const void* w_h, void* out, int T, int H, int vocab, float eps, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8) return -7;
+  LAUNCHED(launch_pdl(mtp_in_kernel, dim3(T), dim3(H >= 2048 ? 256 : 128), H * sizeof(float), st, tokens,
+                      static_cast<const bf16*>(embed), static_cast<const bf16*>(hidden), static_cast<const bf16*>(w_e),
+                      static_cast<const bf16*>(w_h), static_cast<bf16*>(out), H, vocab, eps));
+}
+
+// tokens / picks / positions [B * G] int64, n_valid [B] int32, y [B * G, H]; acc [B] int64, h_sel [B, H],
+// link_pos [links, B] int64 (positions of chain links 2 .. links + 1).
+extern "C" int b200_chain_accept(const int64_t* tokens, const int64_t* picks, const int* n_valid,
+                                 const int64_t* positions, const void* y, int B, int G, int H, int links, int64_t* acc,
+                                 void* h_sel, int64_t* link_pos, cudaStream_t st) {
+  if (B <= 0) return 0;
+  if (H % 8 || G < 1) return -7;
+  LAUNCHED(launch_pdl(chain_accept_kernel, dim3(B), dim3(128), 0, st, tokens, picks, n_valid, positions,
+                      static_cast<const bf16*>(y), G, H, links, B, acc, static_cast<bf16*>(h_sel), link_pos));
 }
 
 // Kernels launched through this library so far (see launch_counter in common.cuh).

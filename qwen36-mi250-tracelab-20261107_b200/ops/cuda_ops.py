@@ -63,6 +63,8 @@ class _Sig:
     b200_moe_plan = [P, I, I, I, P, P, P, I, P, P, P, I, P, P]
     b200_moe_route_plan = [P, I, I, I, I, I, P, P, P, I, I, P, P, P, I, P, P, P, P, P]
     b200_moe_combine_norm = [P, P, P, I, I, I, P, P, P, P, F, P]
+    b200_mtp_in = [P, P, P, P, P, P, I, I, I, F, P]
+    b200_chain_accept = [P, P, P, P, P, I, I, I, I, P, P, P, P]
     b200_moe_gather = [P, P, P, I, I, I, I, P, P]
     b200_moe_combine = [P, P, P, I, I, I, P, P, P]
     b200_gdn_decode = [P, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P]
@@ -247,14 +249,17 @@ def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def lm_head_argmax(x: torch.Tensor, w: torch.Tensor, return_value: bool = False):
-    """Greedy token per row: LM-head GEMM with per-tile argmax partials, then one reduce. Ties to the lower id."""
+def lm_head_argmax(x: torch.Tensor, w: torch.Tensor, return_value: bool = False, out: torch.Tensor | None = None):
+    """Greedy token per row: LM-head GEMM with per-tile argmax partials, then one reduce. Ties to the lower id.
+    ``out`` (int64 ``[T]``, contiguous) receives the picks in place of a new tensor."""
     T, K = x.shape
     V = w.shape[0]
     n_tiles = (V + 127) // 128
     pmax = torch.empty(n_tiles, T, dtype=torch.float32, device=x.device)
     pidx = torch.empty(n_tiles, T, dtype=torch.int32, device=x.device)
-    out = torch.empty(T, dtype=torch.int64, device=x.device)
+    if out is None:
+        out = torch.empty(T, dtype=torch.int64, device=x.device)
+    assert out.dtype == torch.int64 and out.is_contiguous() and out.numel() == T
     val = torch.empty(T, dtype=torch.float32, device=x.device) if return_value else None
     rc = lib().b200_gemm_dense(
         _ptr(x), _ptr(w), None, T, V, K, x.stride(0), w.stride(0), 0, EPI_ARGMAX, 0, 0, _ptr(pmax), _ptr(pidx),
@@ -283,6 +288,31 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     if not x2.is_contiguous():
         x2 = x2.contiguous()
     return add_rmsnorm(x2, None, w, eps)[1].view(shape)
+
+
+def mtp_in(tokens: torch.Tensor, embed_table: torch.Tensor, hidden: torch.Tensor, w_e: torch.Tensor, w_h: torch.Tensor,
+           eps: float) -> torch.Tensor:
+    """``[rmsnorm(embed[tokens]) | rmsnorm(hidden)]`` (zero-centred norms), the MTP block's ``fc`` input, one launch."""
+    T, H = hidden.shape
+    out = torch.empty(T, 2 * H, dtype=hidden.dtype, device=hidden.device)
+    _check(lib().b200_mtp_in(_ptr(tokens), _ptr(embed_table), _ptr(hidden), _ptr(w_e), _ptr(w_h), _ptr(out), T, H,
+                             embed_table.shape[0], eps, _stream()), "mtp_in")
+    return out
+
+
+def chain_accept(tokens: torch.Tensor, picks: torch.Tensor, n_valid: torch.Tensor, positions: torch.Tensor,
+                 y: torch.Tensor, G: int, links: int, acc_out: torch.Tensor | None = None):
+    """Greedy chain acceptance of a verify pass (``G`` rows per sequence) in one launch: accepted draft count per
+    sequence, the MTP hidden row of the last accepted position, and the positions of ``links`` further chain links."""
+    B = tokens.numel() // G
+    H = y.shape[1]
+    dev = y.device
+    acc = acc_out if acc_out is not None else torch.empty(B, dtype=torch.int64, device=dev)
+    h_sel = torch.empty(B, H, dtype=y.dtype, device=dev)
+    link_pos = torch.empty(max(links, 1), B, dtype=torch.int64, device=dev)
+    _check(lib().b200_chain_accept(_ptr(tokens), _ptr(picks), _ptr(n_valid), _ptr(positions), _ptr(y), B, G, H, links,
+                                   _ptr(acc), _ptr(h_sel), _ptr(link_pos), _stream()), "chain_accept")
+    return acc, h_sel, link_pos
 
 
 def embed(tokens: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
@@ -416,6 +446,43 @@ def ring_commit(conv_state, rec_state, ring, slots: torch.Tensor, keep_rows: tor
     _check(rc, "ring_commit")
 
 
+_meta_memo: dict = {}  # the span tables of the pass being run: every layer of a pass asks for the same ones
+
+
+def _memo(key, make):
+    """Single-entry memo per kind of table: the 40 layers of a prefill pass share one host build and one copy."""
+    hit = _meta_memo.get(key[0])
+    if hit is not None and hit[0] == key:
+        return hit[1]
+    val = make()
+    _meta_memo[key[0]] = (key, val)
+    return val
+
+
+def _gdn_prefill_meta(seg_starts, seg_slots, T: int, dev):
+    def make():
+        nseg = len(seg_slots)
+        chunks, seg_chunks, seq_of_row = [], [], []
+        for i in range(nseg):
+            a, b = seg_starts[i], seg_starts[i + 1]
+            first = len(chunks)
+            for r0 in range(a, b, 64):
+                chunks.append((i, r0, min(64, b - r0), int(r0 == a)))
+            seg_chunks.append((first, len(chunks) - first))
+            seq_of_row.extend([i] * (b - a))
+        meta = torch.tensor([c for ch in chunks for c in ch] + [c for sc in seg_chunks for c in sc] + seq_of_row
+                            + list(seg_starts) + list(seg_slots), dtype=torch.int32).to(dev, non_blocking=True)
+        o = 0
+        chunks_t = meta[o : o + 4 * len(chunks)]; o += 4 * len(chunks)
+        segc_t = meta[o : o + 2 * nseg]; o += 2 * nseg
+        sor_t = meta[o : o + T]; o += T
+        start_t = meta[o : o + nseg + 1]; o += nseg + 1
+        slots_t = meta[o : o + nseg]
+        return len(chunks), chunks_t, segc_t, sor_t, start_t, slots_t
+
+    return _memo(("gdn", tuple(seg_starts), tuple(seg_slots), T, str(dev)), make)
+
+
 def gdn_prefill(mixed, seg_starts, seg_slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnorm_w, n_k, n_v, dk,
                 dv, eps) -> torch.Tensor:
     """Chunked prefill of the gated delta rule over packed spans (conv, WY transform, state scan, gated norm)."""
@@ -426,31 +493,16 @@ def gdn_prefill(mixed, seg_starts, seg_slots, conv_state, rec_state, conv_w, A_l
     T = mixed.shape[0]
     dev = mixed.device
     nseg = len(seg_slots)
-    chunks, seg_chunks, seq_of_row = [], [], []
-    for i in range(nseg):
-        a, b = seg_starts[i], seg_starts[i + 1]
-        first = len(chunks)
-        for r0 in range(a, b, 64):
-            chunks.append((i, r0, min(64, b - r0), int(r0 == a)))
-        seg_chunks.append((first, len(chunks) - first))
-        seq_of_row.extend([i] * (b - a))
-    meta = torch.tensor([c for ch in chunks for c in ch] + [c for sc in seg_chunks for c in sc] + seq_of_row
-                        + list(seg_starts) + list(seg_slots), dtype=torch.int32).to(dev, non_blocking=True)
-    o = 0
-    chunks_t = meta[o : o + 4 * len(chunks)]; o += 4 * len(chunks)
-    segc_t = meta[o : o + 2 * nseg]; o += 2 * nseg
-    sor_t = meta[o : o + T]; o += T
-    start_t = meta[o : o + nseg + 1]; o += nseg + 1
-    slots_t = meta[o : o + nseg]
+    n_chunks, chunks_t, segc_t, sor_t, start_t, slots_t = _gdn_prefill_meta(seg_starts, seg_slots, T, dev)
     C = 2 * n_k * dk + n_v * dv
     stride = lib().b200_gdn_prefill_work_stride(dk)
-    work = torch.empty(len(chunks) * n_v * stride, dtype=torch.float32, device=dev)
+    work = torch.empty(n_chunks * n_v * stride, dtype=torch.float32, device=dev)
     conv_out = torch.empty(T, C, dtype=mixed.dtype, device=dev)
     o_tmp = torch.empty(T, n_v * dv, dtype=mixed.dtype, device=dev)
     out = torch.empty(T, n_v * dv, dtype=mixed.dtype, device=dev)
     rc = lib().b200_gdn_prefill(
         _ptr(mixed), mixed.stride(0), _ptr(sor_t), _ptr(start_t), _ptr(slots_t), _ptr(conv_state), _ptr(rec_state),
-        _ptr(conv_w), _ptr(A_log), _ptr(dt_bias), _ptr(gnorm_w), _ptr(conv_out), _ptr(chunks_t), len(chunks),
+        _ptr(conv_w), _ptr(A_log), _ptr(dt_bias), _ptr(gnorm_w), _ptr(conv_out), _ptr(chunks_t), n_chunks,
         _ptr(segc_t), nseg, _ptr(work), _ptr(o_tmp), _ptr(out), T, n_k, n_v, dk, dv, eps, int(GDN_PREFILL_TC),
         _ptr(err_word(dev)), _stream(),
     )
@@ -505,16 +557,20 @@ def flash_prefill(q: torch.Tensor, gate: torch.Tensor, kv_layer: torch.Tensor, b
     T, n_q, D = q.shape
     n_kv = kv_layer.shape[2]
     R = 128 // (n_q // n_kv)
-    tiles = []
-    for i in range(len(seg_starts) - 1):
-        n = seg_starts[i + 1] - seg_starts[i]
-        tiles.extend((i, p0, seg_starts[i], n) for p0 in range(0, n, R))
     dev = q.device
-    tiles_t = torch.tensor(tiles, dtype=torch.int32).reshape(-1, 4).to(dev, non_blocking=True)
-    pos0_t = torch.tensor(seg_pos0, dtype=torch.int32).to(dev, non_blocking=True)
+
+    def make():
+        tiles = []
+        for i in range(len(seg_starts) - 1):
+            n = seg_starts[i + 1] - seg_starts[i]
+            tiles.extend((i, p0, seg_starts[i], n) for p0 in range(0, n, R))
+        return (len(tiles), torch.tensor(tiles, dtype=torch.int32).reshape(-1, 4).to(dev, non_blocking=True),
+                torch.tensor(seg_pos0, dtype=torch.int32).to(dev, non_blocking=True))
+
+    n_tiles, tiles_t, pos0_t = _memo(("flash", tuple(seg_starts), tuple(seg_pos0), R, str(dev)), make)
     out = torch.empty(T, n_q * D, dtype=q.dtype, device=dev)
     rc = lib().b200_flash_prefill(
-        _ptr(q), _ptr(gate), _ptr(kv_layer), _ptr(out), _ptr(tiles_t), len(tiles), _ptr(pos0_t), _ptr(block_tables),
+        _ptr(q), _ptr(gate), _ptr(kv_layer), _ptr(out), _ptr(tiles_t), n_tiles, _ptr(pos0_t), _ptr(block_tables),
         block_tables.stride(0), kv_layer.shape[0], T, n_q, n_kv, D, 0, 1, None, None, _ptr(err_word(dev)), _stream(),
     )
     _check(rc, "flash_prefill")

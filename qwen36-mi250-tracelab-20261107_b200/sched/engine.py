@@ -88,14 +88,16 @@ class Engine:
         self.stats = dict(
             decode_steps=0, decoded_tokens=0, largest_batch=0, prefill_passes=0, prefill_segments=0,
             prefilled_tokens=0, cached_tokens=0, requests=0, finished=0, failed=0,
-            mtp_verify_steps=0, mtp_proposed=0, mtp_accepted=0, device_errors=0, step_errors=0,
+            mtp_verify_steps=0, mtp_proposed=0, mtp_accepted=0, device_errors=0, step_errors=0, ahead_steps=0,
         )
         self._graphs = None
         # library collectives (the NCCL baseline path) stay out of CUDA graphs; the fused NVLink kernels go in
-        if self.device.type == "cuda" and c.cuda_graphs and (tp is None or tp.comm.fused):
+        emulate = c.cuda_graphs and c.graphs_on_cpu and self.device.type != "cuda"
+        if (self.device.type == "cuda" or emulate) and c.cuda_graphs and (tp is None or getattr(tp.comm, "fused", False) or emulate):
             from .graphs import DecodeGraphs
 
             self._graphs = DecodeGraphs(self)
+        self._pending = None  # a decode step in flight (launched ahead of the host's bookkeeping)
         self.spec = None
         if c.mtp and weights.mtp is not None:
             from ..spec.controller import SpecController
@@ -137,7 +139,7 @@ class Engine:
         return gen
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.prefilling or self.running) or not self._inbox.empty()
+        return bool(self.waiting or self.prefilling or self.running or self._pending) or not self._inbox.empty()
 
     def generate(self, prompts: Iterable[list[int]], sampling: Sampling | list[Sampling]) -> list[Generation]:
         """Offline convenience: run the given prompts to completion and return their generations."""
@@ -349,7 +351,66 @@ class Engine:
         return True
 
     # ------------------------------------------------------------------ decode
+    def _ahead_ok(self, gens) -> bool:
+        """May the step AFTER the one in flight be launched for the same requests before the host has seen the one in
+        flight? Only when that next step is certain to run unchanged: nothing waits to be admitted or prefilled, the
+        requests in flight are all the running ones, none of them can stop on a token (greedy, ``ignore_eos``, no
+        EOS masking pending), none is cancelled, and each still needs a token after the step in flight
+        (reference: ``_ahead_safe``, engine/speculative.py:266-274)."""
+        c = self.cfg
+        if not c.run_ahead or self.tick is not None or self.spec is not None:
+            return False
+        if self.waiting or self.prefilling or (self.coordinator is None and not self._inbox.empty()):
+            return False
+        if len(gens) != len(self.running) or any(a is not b for a, b in zip(gens, self.running)):
+            return False
+        for g in gens:
+            s = g.sampling
+            if not (s.greedy and s.ignore_eos) or g.cancel_now or len(g.output) < s.min_tokens:
+                return False
+            if len(g.output) + 1 >= s.max_tokens:  # it finishes at the step in flight
+                return False
+        return True
+
+    def _collect_pending(self) -> None:
+        """Read the step in flight, book its tokens."""
+        h, self._pending = self._pending, None
+        gens = h["gens"]
+        try:
+            hidden, greedy = self._graphs.collect(h)
+        except Exception as e:
+            for g in gens:
+                if g in self.running:
+                    self.running.remove(g)
+                self._fail(g, EngineError(f"decode failed: {e}", 500, "internal_error"))
+            return
+        for g in gens:
+            g.computed += 1
+        B = len(gens)
+        self.stats["decode_steps"] += 1
+        self.stats["decoded_tokens"] += B
+        self.stats["largest_batch"] = max(self.stats["largest_batch"], B)
+        need_logits = any(self._needs_logits(g) for g in gens)
+        self._sample_and_emit(gens, hidden, greedy if not need_logits else None)
+        self._reap()
+
     def _decode_step(self) -> bool:
+        if self._pending is not None:
+            # a step launched ahead is in flight for exactly these requests: maybe start the one after it, then read it
+            h = self._pending
+            if self._ahead_ok(h["gens"]):
+                try:
+                    for g in h["gens"]:
+                        self._ensure_pages(g, g.computed + 3)
+                    nxt = self._graphs.launch_next(h)
+                    self.stats["ahead_steps"] += 1
+                except OutOfCapacity:
+                    nxt = None
+                self._collect_pending()
+                self._pending = nxt
+            else:
+                self._collect_pending()
+            return True
         for gen in list(self.running):
             if gen.cancel_now:
                 self.running.remove(gen)
@@ -388,12 +449,15 @@ class Engine:
         need_logits = any(self._needs_logits(g) for g in batch_gens)
         try:
             if self._graphs is not None and self._graphs.usable(batch_gens):
-                hidden, greedy = self._graphs.run(batch_gens, tokens, positions)
-            else:
-                batch = PackedBatch.uniform(tokens, positions, [g.slot for g in batch_gens], self._table(batch_gens), 1, self.device)
-                hidden = self.model.forward(batch)
-                greedy = None
-                self.check_device()
+                handle = self._graphs.launch(batch_gens, tokens, positions)
+                if handle is not None:
+                    # in flight: the step after it may start before this one is read (see _ahead_ok)
+                    self._pending = handle
+                    return self._decode_step()
+            batch = PackedBatch.uniform(tokens, positions, [g.slot for g in batch_gens], self._table(batch_gens), 1, self.device)
+            hidden = self.model.forward(batch)
+            greedy = None
+            self.check_device()
         except Exception as e:
             for g in batch_gens:
                 self.running.remove(g)
@@ -514,6 +578,7 @@ class Engine:
             if not g.done:
                 self._fail(g, err)
         self.waiting, self.prefilling, self.running = [], [], []
+        self._pending = None
         if self.spec is not None and hasattr(self.spec, "reset"):
             self.spec.reset()
         self.flush_events()

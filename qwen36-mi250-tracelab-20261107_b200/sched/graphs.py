@@ -27,6 +27,7 @@ class _Bucket:
         n_tok, n_pos, n_slot, n_tab = size * 8, size * 8, size * 4, size * width * 4
         offs = [0, n_tok, n_tok + n_pos, n_tok + n_pos + ((n_slot + 15) // 16) * 16]
         total = offs[3] + n_tab
+        self.tab_off = offs[3]
         self.dev_buf = torch.zeros(total, dtype=torch.uint8, device=dev)
         self.host_buf = torch.zeros(total, dtype=torch.uint8)
         if dev.type == "cuda":
@@ -40,11 +41,15 @@ class _Bucket:
         h = views(self.host_buf)
         self.np_tokens, self.np_positions, self.np_slots, self.np_tables = (t.numpy() for t in h)
         self.seq = torch.arange(size, dtype=torch.int32, device=dev)
-        self.h_picks = torch.zeros(size, dtype=torch.int64)
-        self.h_err = torch.zeros(1, dtype=torch.int32)
+        # results come back into one of two pinned buffers: a step launched ahead must not overwrite what the host
+        # has not read yet
+        self.h_picks2 = [torch.zeros(size, dtype=torch.int64) for _ in range(2)]
+        self.h_err2 = [torch.zeros(1, dtype=torch.int32) for _ in range(2)]
         if dev.type == "cuda":
-            self.h_picks = self.h_picks.pin_memory()
-            self.h_err = self.h_err.pin_memory()
+            self.h_picks2 = [t.pin_memory() for t in self.h_picks2]
+            self.h_err2 = [t.pin_memory() for t in self.h_err2]
+        self.h_picks, self.h_err = self.h_picks2[0], self.h_err2[0]
+        self.parity = 0
         self.rows: list = [None] * size  # (request id, page count, last page) whose table each row currently holds
         self.live = 0
         self.batch = PackedBatch(self.tokens, self.positions, self.seq, self.slots, self.tables, 1)
@@ -75,6 +80,29 @@ class _Bucket:
                 tab[i, k:] = 0
         self.dev_buf.copy_(self.host_buf, non_blocking=True)
 
+    def refresh_tables(self, gens) -> None:
+        """Before a step whose tokens and positions are built on the device: only page-table rows that grew are sent."""
+        changed = False
+        rows, tab = self.rows, self.np_tables
+        for i, g in enumerate(gens):
+            sig = (g.id, len(g.pages), g.pages[-1] if g.pages else 0)
+            if rows[i] != sig:
+                rows[i] = sig
+                k = len(g.pages)
+                tab[i, :k] = g.pages
+                tab[i, k:] = 0
+                changed = True
+        if changed:
+            self.dev_buf[self.tab_off :].copy_(self.host_buf[self.tab_off :], non_blocking=True)
+
+    def replay(self) -> None:
+        if self.graph is not None:
+            self.graph.replay()
+        else:  # no CUDA device: the same body, run kernel by kernel into the same static buffers
+            h, p = self._body()
+            self.hidden.copy_(h)
+            self.picks.copy_(p)
+
     def capture(self, engine) -> None:
         model = engine.model
 
@@ -82,6 +110,12 @@ class _Bucket:
             h = model.forward(self.batch)
             return h, model.greedy(h)
 
+        self._body = body
+        if engine.device.type != "cuda":
+            self.hidden, self.picks = body()
+            self.hidden, self.picks = self.hidden.clone(), self.picks.clone()
+            self.launches = 0
+            return
         s = torch.cuda.Stream(device=engine.device)
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
@@ -142,30 +176,63 @@ class DecodeGraphs:
         self.frozen = every_width
 
     def run(self, gens, tokens, positions):
-        n = len(gens)
-        b = self._bucket(n, max(len(g.pages) for g in gens))
-        if b is None:
+        """One decode step from host inputs, launched and collected."""
+        h = self.launch(gens, tokens, positions)
+        if h is None:
             eng = self.engine
             batch = PackedBatch.uniform(tokens, positions, [g.slot for g in gens], eng._table(gens), 1, eng.device)
             hidden = eng.model.forward(batch)
             eng.check_device()
             return hidden, None
+        return self.collect(h)
+
+    # A step in flight: launched, results not read yet. ``launch_next`` starts the step after it from inputs built on
+    # the device (tokens = this step's picks, positions + 1) before the host has read this step's result, so the
+    # GPU never waits for the host's bookkeeping (reference: run-ahead, engine/speculative.py:266-274, 427-451;
+    # input builder engine/fast/tp.py:296-318).
+    def launch(self, gens, tokens, positions):
+        n = len(gens)
+        b = self._bucket(n, max(len(g.pages) for g in gens))
+        if b is None:
+            return None
         with looptimers.stage("build"):
             b.fill(gens, tokens, positions)
+        return self._start(b, gens)
+
+    def launch_next(self, handle):
+        b, gens = handle["bucket"], handle["gens"]
+        b.refresh_tables(gens)
+        n = len(gens)
+        b.tokens[:n].copy_(b.picks[:n])  # stream-ordered after the step that produced the picks
+        b.positions[:n].add_(1)
+        return self._start(b, gens)
+
+    def _start(self, b, gens):
         start, stop = looptimers.gpu_span("gpu_graph")
         start()
-        b.graph.replay()
+        b.replay()
         stop()
         self.engine.flush_events()  # the previous step's tokens go out while the GPU runs this one
-        b.h_picks.copy_(b.picks, non_blocking=True)
+        par = b.parity
+        b.parity ^= 1
+        b.h_picks2[par].copy_(b.picks, non_blocking=True)
         err = getattr(self.engine.ops, "err_word", None)
         if err is not None:  # the device error word travels with the picks: one more 4-byte copy, no extra sync
-            b.h_err.copy_(err(self.engine.device), non_blocking=True)
+            b.h_err2[par].copy_(err(self.engine.device), non_blocking=True)
+        ev = None
+        if self.engine.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+        return {"bucket": b, "gens": list(gens), "parity": par, "event": ev, "err": err is not None}
+
+    def collect(self, handle):
+        b, n, par = handle["bucket"], len(handle["gens"]), handle["parity"]
         with looptimers.stage("wait"):
-            torch.cuda.current_stream().synchronize()
-        if err is not None:
-            self.engine.check_device(int(b.h_err[0]))
-        return b.hidden[:n], b.h_picks[:n]
+            if handle["event"] is not None:
+                handle["event"].synchronize()
+        if handle["err"]:
+            self.engine.check_device(int(b.h_err2[par][0]))
+        return b.hidden[:n], b.h_picks2[par][:n]
 
 
 class _VerifyBucket:
@@ -204,29 +271,26 @@ class _VerifyBucket:
         self.out = None
 
     def _body(self, model):
-        size, G, k = self.size, self.G, self.k
+        """Verify pass, greedy picks, chain acceptance, MTP block and draft chain; returns the int64 vector
+        ``[picks (size * G) | accepted (size) | drafts (kmax links x size)]`` the host reads back. The acceptance
+        arithmetic and the gathers around it are one kernel (``chain_accept``), and every argmax writes its picks
+        straight into the result vector."""
+        size, G, kmax = self.size, self.G, self.kmax
         dev = self.tokens.device
+        ops = model.ops
+        out = torch.empty(size * G + size + size * kmax, dtype=torch.int64, device=dev)
+        picks, acc_out = out[: size * G], out[size * G : size * G + size]
+        dr0 = size * G + size
         hidden = model.forward(self.batch, ring=self.ring)
-        picks = model.greedy(hidden)
-        pk = picks.view(size, G)
-        if k > 0:
-            tok = self.tokens.view(size, G)
-            valid = torch.arange(k, device=dev)[None, :] < self.n_valid[:, None]
-            match = ((tok[:, 1:] == pk[:, :-1]) & valid).long()
-            acc = torch.cumprod(match, dim=1).sum(dim=1)
-        else:
-            acc = torch.zeros(size, dtype=torch.long, device=dev)
+        model.greedy(hidden, out=picks)
         y = model.mtp_forward(hidden, picks, self.batch)
-        h = y[torch.arange(size, device=dev) * G + acc]
-        d = model.greedy(h)
-        drafts = [d]
-        base = self.positions.view(size, G)[:, 0] + acc + 1
-        for j in range(1, self.kmax):
-            link = PackedBatch(d, base + (j - 1), self.seq1, self.slots, self.tables, 1)
+        _acc, h, link_pos = ops.chain_accept(self.tokens, picks, self.n_valid, self.positions, y, G, kmax - 1, acc_out=acc_out)
+        d = model.greedy(h, out=out[dr0 : dr0 + size])
+        for j in range(1, kmax):
+            link = PackedBatch(d, link_pos[j - 1], self.seq1, self.slots, self.tables, 1)
             h = model.mtp_forward(h, d, link)
-            d = model.greedy(h)
-            drafts.append(d)
-        return torch.cat([picks, acc, torch.stack(drafts, dim=1).reshape(-1)])
+            d = model.greedy(h, out=out[dr0 + j * size : dr0 + (j + 1) * size])
+        return out
 
     def capture(self, engine, pool) -> None:
         s = torch.cuda.Stream(device=engine.device)
@@ -313,5 +377,5 @@ class VerifyGraphs:
         out = b.h_out
         picks = out[: size * G].view(size, G)[:n].tolist()
         acc = out[size * G : size * G + size][:n].tolist()
-        drafts = out[size * G + size :].view(size, self.kmax)[:n].tolist()
+        drafts = out[size * G + size :].view(self.kmax, size)[:, :n].t().tolist()
         return picks, acc, drafts, b.ring, b.slots[:n]

@@ -45,12 +45,31 @@ class DepthPolicy:
     max_rows: int = 256  # B * (k + 1) bound of one verify pass
 
     def cost(self, B: int, k: int) -> float:
+        """Cost of a depth-``k`` step over ``B`` sequences. With a measured table: the entry of the smallest measured
+        batch bucket that holds ``B`` (the largest one beyond it); a depth the bucket was not measured at is
+        extended linearly from its two deepest measured depths (a verify step grows by k + 1 rows per sequence and
+        one more draft link per depth). Without a table: a fixed part plus a per-row part."""
         if self.table:
-            keys = [b for (b, kk) in self.table if kk == k and b >= B]
-            if keys:
-                return self.table[(min(keys), k)]
-            return math.inf  # a measured table lists every depth that may run
+            buckets = sorted({b for (b, _k) in self.table})
+            b = next((x for x in buckets if x >= B), buckets[-1])
+            if (b, k) in self.table:
+                return self.table[(b, k)]
+            ks = sorted(kk for (bb, kk) in self.table if bb == b)
+            if len(ks) >= 2:
+                k1, k2 = ks[-2], ks[-1]
+                slope = (self.table[(b, k2)] - self.table[(b, k1)]) / (k2 - k1)
+                return self.table[(b, k2)] + slope * (k - k2)
+            return math.inf
         return 1.0 + self.row_cost * k * max(1.0, math.log2(B + 1))
+
+    def load_table(self, path) -> None:
+        """Read a ``{"ms": {batch: {depth: ms}}}`` file as written next to this module (measured with
+        ``bench/mtp_bench.py``; the reference keeps such a table per (slot bucket, k), engine/speculative.py:127-136)."""
+        import json
+        from pathlib import Path
+
+        data = json.loads(Path(path).read_text())["ms"]
+        self.table = {(int(b), int(k)): float(ms) for b, row in data.items() for k, ms in row.items()}
 
     def expected_tokens(self, k: int) -> float:
         e, p = 1.0, 1.0
@@ -83,7 +102,15 @@ class SpecController:
     def __init__(self, engine) -> None:
         self.engine = engine
         c = engine.cfg
-        self.policy = DepthPolicy(kmax=max(1, c.spec_kmax), fixed=c.spec_k)
+        self.policy = DepthPolicy(kmax=max(1, min(c.spec_kmax, 7)), fixed=c.spec_k)
+        # the step-cost model: a measured table for this hardware when serving on a GPU (ENGINE_SPEC_COST names another
+        # file, "model" selects the built-in formula); the formula on CPU
+        import os
+        from pathlib import Path
+
+        src = os.environ.get("ENGINE_SPEC_COST", "")
+        if src != "model" and (src or engine.device.type == "cuda"):
+            self.policy.load_table(src or Path(__file__).with_name("cost_table_b200.json"))
         self.k_hist: dict[int, int] = {}
         self.draft_override = None  # tests: callable(gen, k) -> list[int] forcing the drafts of a step
         self._ring_store = None

@@ -242,28 +242,14 @@ def mode_ep_moe(rank, world, dev):
             ref = torch_ops.moe_experts(x.float(), wts.float(), idx, wgu.float(), wd.float())
             err = (got.float() - ref).abs().max().item()
             assert err <= 3e-2 * max(1.0, ref.abs().max().item()), (T, err)
-    # device-timed, max over ranks
-    x = torch.randn(128, H, device=dev, generator=gx).to(torch.bfloat16)
-    for _ in range(3):
-        ep.forward(x, router, lgu, ld)
-    torch.cuda.synchronize(); dist.barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(20):
-        ep.forward(x, router, lgu, ld)
-    b.record(); torch.cuda.synchronize()
-    t = torch.tensor([a.elapsed_time(b) / 20 * 1e3], device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    if rank == 0:
-        print(f"ep_moe world={world} 128 rows/rank E={E}: {t.item():.1f} us per block", flush=True)
     cuda_ops.check_errors(dev)
     dist.barrier()
     ep.close()
 
 
 def mode_seq_parallel(rank, world, dev):
-    """GEMM -> reduce-scatter, norm + all-gather push, gathered GEMM: numerics against NCCL + fp32, then timing
-    of the fused pipeline against reduce_scatter / all_gather / torch.matmul."""
+    """GEMM -> reduce-scatter, norm + all-gather push, gathered GEMM: numerics against NCCL + fp32 (the timing of the
+    same pipeline against the library collectives lives in bench/collective_bench.py)."""
     from b200serve.ops import cuda_ops, torch_ops
     from b200serve.parallel.sp import SeqParallel
 
@@ -299,71 +285,6 @@ def mode_seq_parallel(rank, world, dev):
             e2 = (y.float() - want_y).abs().max().item()
             assert e2 <= 0.02 * want_y.abs().max().item() + 1e-3, ("gathered", T, rep, e2)
             dist.barrier()
-    # timing at a prefill size: T = 8192 rows, out_proj K-shard 4096 / world, in_proj 12352 / world columns
-    T, Ks, N2 = 8192, 4096 // world, 12352 // world // 8 * 8
-    rpr = T // world
-    x = (torch.randn(T, Ks, device=dev) * 0.5).to(torch.bfloat16)
-    w_o = (torch.randn(H, Ks, device=dev) * 0.05).to(torch.bfloat16)
-    w_n = torch.zeros(H, device=dev, dtype=torch.bfloat16)
-    w_i = (torch.randn(N2, H, device=dev) * 0.05).to(torch.bfloat16)
-    res = torch.randn(rpr, H, device=dev).to(torch.bfloat16)
-
-    def fused():
-        rows = sp.gemm_reduce_scatter(x, w_o)
-        return sp.gemm_gathered(sp.reduce_norm_allgather(rows, res, w_n, eps)[1], w_i)
-
-    rs_out = torch.empty(rpr, H, device=dev, dtype=torch.bfloat16)
-    ag_out = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
-
-    def library():
-        part = x @ w_o.t()
-        dist.reduce_scatter_tensor(rs_out, part)
-        mine = torch_ops.rmsnorm(rs_out + res, w_n, eps)
-        dist.all_gather_into_tensor(ag_out, mine)
-        return ag_out @ w_i.t()
-
-    def allreduce_path():
-        h = cuda_ops.linear(x, w_o, out_dtype=torch.float32)
-        dist.all_reduce(h)
-        return cuda_ops.linear(cuda_ops.rmsnorm(h.to(torch.bfloat16), w_n, eps), w_i)
-
-    names = {}
-    for name, fn in (("fused", fused), ("nccl_rs_ag_cublas", library), ("gemm_nccl_allreduce", allreduce_path)):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize(); dist.barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(10):
-            fn()
-        b.record(); torch.cuda.synchronize()
-        t = torch.tensor([a.elapsed_time(b) / 10 * 1e3], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        names[name] = t.item()
-    # where the fused pipeline spends its time (events between the three kernels, summed over 10 iterations)
-    stage_lines = []
-    for cap in (64, 128, 256):
-        sp.bt_cap = cap
-        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(10)]
-        torch.cuda.synchronize(); dist.barrier()
-        for it in range(10):
-            ev[it][0].record()
-            rows = sp.gemm_reduce_scatter(x, w_o)
-            ev[it][1].record()
-            full = sp.reduce_norm_allgather(rows, res, w_n, eps)[1]
-            ev[it][2].record()
-            sp.gemm_gathered(full, w_i)
-            ev[it][3].record()
-        torch.cuda.synchronize()
-        parts = [sum(ev[it][i].elapsed_time(ev[it][i + 1]) for it in range(10)) * 100 for i in range(3)]
-        stage_lines.append(f"  token tile <= {cap}, rank 0: gemm+push {parts[0]:.1f} us, reduce+norm+gather {parts[1]:.1f} us, "
-                           f"gathered gemm {parts[2]:.1f} us")
-    if rank == 0:
-        print("\n".join(stage_lines), flush=True)
-        flops = 2 * T * H * Ks + 2 * T * N2 * H
-        nv = (world - 1) / world * T * H * (4 + 2)
-        print(f"seq_parallel world={world} T={T}: " + ", ".join(f"{k} {v:.1f} us" for k, v in names.items()) +
-              f"; {flops / names['fused'] / 1e6:.0f} TFLOP/s per GPU, NVLink bytes out per GPU {nv / 1e6:.1f} MB", flush=True)
     cuda_ops.check_errors(dev)
     dist.barrier()
     sp.close()

@@ -122,3 +122,70 @@ def test_tokens_are_delivered_every_step_when_the_graph_path_is_not_taken(weight
         eng.step()
         assert len(events) == seen + 1  # one token per step, delivered within that step
         seen = len(events)
+
+
+# --------------------------------------------------------------------------- run-ahead (decode-graph scheduling on CPU)
+def _graph_engine(weights, run_ahead, **kw):
+    cfg = EngineConfig(max_model_len=1024, prefill_chunk_tokens=64, max_seqs=8, mtp=False, graphs_on_cpu=True,
+                       run_ahead=run_ahead, decode_buckets=(1, 2, 4, 8), **kw)
+    return Engine(weights, cfg)
+
+
+def test_run_ahead_keeps_tokens_lengths_and_cache_identical(weights):
+    """Step n + 1 is launched from device-built inputs before step n is read: same tokens as without it, exact
+    lengths, page growth across the 64-token boundary, and session tails that later requests can resume from."""
+    prompts = [[3 + (i * (7 + s)) % 900 for i in range(n)] for s, n in enumerate((40, 61, 130))]
+    samp = [Sampling(max_tokens=m, ignore_eos=True) for m in (90, 33, 7)]
+    outs, stats = [], []
+    for ahead in (False, True):
+        eng = _graph_engine(weights, ahead)
+        assert eng._graphs is not None
+        gens = eng.generate(prompts, samp)
+        outs.append([g.output for g in gens])
+        stats.append(dict(eng.stats))
+        assert [len(g.output) for g in gens] == [90, 33, 7]
+        # a second round on top of the first: resumes from the tail that a run-ahead engine parked
+        again = eng.generate([prompts[0] + gens[0].output + [5, 6, 7]], Sampling(max_tokens=9, ignore_eos=True))[0]
+        outs[-1].append(again.output)
+        assert again.cached_tokens == len(prompts[0]) + 90 - 1
+    assert outs[0] == outs[1]
+    assert stats[0]["ahead_steps"] == 0 and stats[1]["ahead_steps"] > 50
+    ref = _engine(weights).generate(prompts, samp)
+    assert [g.output for g in ref] == outs[1][:3]
+
+
+def test_run_ahead_stops_for_requests_that_can_end_on_a_token_and_for_new_arrivals(weights):
+    eng = _graph_engine(weights, True)
+    a, _ = _submit(eng, 40, max_tokens=60)
+    for _ in range(8):
+        eng.step()
+    ahead0 = eng.stats["ahead_steps"]
+    assert ahead0 > 0 and eng._pending is not None
+    b = eng.submit(Generation([9, 8, 7, 6, 5, 4], Sampling(max_tokens=50, ignore_eos=False)))  # may stop on EOS
+    for _ in range(3):
+        eng.step()
+    assert b in eng.running and eng._pending is None  # the pipeline drained and did not restart: b can end any time
+    mid = eng.stats["ahead_steps"]
+    while not (a.done and b.done):
+        eng.step()
+    assert eng.stats["ahead_steps"] <= mid + 60  # only once b is gone may a run ahead again
+    solo = _engine(weights).generate([a.prompt, b.prompt], [a.sampling, b.sampling])
+    assert a.output == solo[0].output and b.output == solo[1].output
+
+
+def test_a_cancelled_request_keeps_the_token_of_the_step_in_flight(weights):
+    """The step launched ahead already advanced the request's state: its token is booked before the cancellation, so
+    the parked tail matches the state."""
+    eng = _graph_engine(weights, True)
+    a, ev = _submit(eng, 40, max_tokens=200)
+    for _ in range(6):
+        eng.step()
+    assert eng._pending is not None
+    a.cancelled.set()
+    n0 = len(a.output)
+    for _ in range(3):
+        eng.step()
+    assert a.finish_reason == "cancelled" and len(a.output) == n0 + 1 and eng._pending is None
+    nxt = eng.generate([a.prompt + a.output + [4, 4]], Sampling(max_tokens=5, ignore_eos=True))[0]
+    cold = _engine(weights).generate([a.prompt + a.output + [4, 4]], Sampling(max_tokens=5, ignore_eos=True))[0]
+    assert nxt.cached_tokens > 0 and nxt.output == cold.output

@@ -416,3 +416,38 @@ def test_lm_head_argmax_at_full_vocabulary_against_fp32(C, packed):
     top = ref.max(-1).values
     assert ((top - picked) <= 2e-3 * top.abs().clamp_min(1.0)).all(), (top - picked).max().item()
     C.check_errors(x.device)
+
+
+def test_mtp_input_kernel_matches_its_parts(C):
+    T, H, V = 37, 2048, 5000
+    table, hidden = _bf(V, H, seed=51), _bf(T, H, seed=52)
+    we, wh = _bf(H, scale=0.1, seed=53), _bf(H, scale=0.1, seed=54)
+    tok = torch.randint(0, V, (T,), device="cuda")
+    got = C.mtp_in(tok, table, hidden, we, wh, 1e-6)
+    want = torch.cat([C.rmsnorm(C.embed(tok, table), we, 1e-6), C.rmsnorm(hidden, wh, 1e-6)], dim=-1)
+    assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("B,G,kmax", [(1, 1, 1), (5, 4, 3), (64, 3, 2)])
+def test_chain_accept_kernel_matches_the_tensor_formulation(C, B, G, kmax):
+    g = torch.Generator(device="cuda").manual_seed(B * G)
+    H, k = 256, G - 1
+    picks = torch.randint(0, 6, (B * G,), device="cuda", generator=g)
+    tokens = torch.randint(0, 6, (B * G,), device="cuda", generator=g)
+    tok2 = tokens.view(B, G).clone()
+    for b in range(0, B, 2):  # half of the sequences: a run of correct drafts of random length
+        n = int(torch.randint(0, k + 1, (1,)).item())
+        tok2[b, 1 : 1 + n] = picks.view(B, G)[b, :n]
+    tokens = tok2.reshape(-1).contiguous()
+    n_valid = torch.randint(0, k + 1, (B,), device="cuda", generator=g).to(torch.int32)
+    positions = (torch.randint(10, 500, (B, 1), device="cuda", generator=g) + torch.arange(G, device="cuda")).reshape(-1)
+    y = _bf(B * G, H, seed=61)
+    acc, h, link_pos = C.chain_accept(tokens, picks, n_valid, positions, y, G, kmax - 1)
+    valid = torch.arange(k, device="cuda")[None, :] < n_valid[:, None]
+    match = ((tokens.view(B, G)[:, 1:] == picks.view(B, G)[:, :-1]) & valid).long()
+    want = torch.cumprod(match, dim=1).sum(dim=1) if k > 0 else torch.zeros(B, dtype=torch.long, device="cuda")
+    assert torch.equal(acc, want)
+    assert torch.equal(h, y[torch.arange(B, device="cuda") * G + want])
+    base = positions.view(B, G)[:, 0] + want + 1
+    for j in range(kmax - 1):
+        assert torch.equal(link_pos[j], base + j)

@@ -124,3 +124,28 @@ def test_depth_policy_host_logic():
     before = list(pol.accept)
     pol.observe(3, 1)  # draft 1 accepted, draft 2 rejected, draft 3 untested
     assert pol.accept[0] > before[0] and pol.accept[1] < before[1] and pol.accept[2] == before[2]
+
+
+def test_depth_policy_reads_a_measured_cost_table_and_extends_it_to_deeper_chains(tmp_path):
+    import json
+    from pathlib import Path
+
+    from b200serve.spec.controller import DepthPolicy
+
+    shipped = Path(__import__("b200serve").__file__).resolve().parent.parent / "qwen36-mi250-tracelab-20261107_b200/spec/cost_table_b200.json"
+    p = DepthPolicy(kmax=7)
+    p.load_table(shipped)
+    assert p.cost(1, 0) < p.cost(1, 1) < p.cost(1, 3) and p.cost(5, 2) == p.cost(8, 2)  # bucket of the next larger batch
+    assert p.cost(1, 5) == pytest.approx(p.cost(1, 3) + 2 * (p.cost(1, 3) - p.cost(1, 2)))  # beyond the measured depths
+    assert p.cost(200, 1) == p.cost(64, 1)  # beyond the largest measured bucket
+    # high acceptance at batch 1 pays for deep chains, low acceptance or a big batch does not
+    p.accept = [0.9] * 7
+    assert p.choose(1, 7) >= 4
+    p.accept = [0.2] * 7
+    assert p.choose(64, 7) == 0
+    custom = tmp_path / "t.json"
+    custom.write_text(json.dumps({"ms": {"4": {"0": 1.0, "1": 1.1}}}))
+    q = DepthPolicy(kmax=2)
+    q.load_table(custom)
+    q.accept = [0.8, 0.8]
+    assert q.choose(2, 2) == 2
