@@ -69,11 +69,15 @@ __global__ void ep_send_kernel(EpCtx c, const bf16* x, const int* idx, int n_pai
       atomicCAS(c.err, 0, ERR_BAD_INDEX);
     }
   }
-  // last CTA out: publish the per-host counts and release this source's flag on every host
-  __threadfence_system();
+  // last CTA out: publish the per-host counts and release this source's flag on every host. The CTA's peer stores
+  // are ordered before the ticket by the barrier followed by ONE system-scope fence of the thread that takes the
+  // ticket (a fence per thread cost 3x the kernel's time: the profile showed every warp stalled on it).
   __syncthreads();
   __shared__ int s_last;
-  if (threadIdx.x == 0) s_last = atomicAdd(&c.cursors[MAX_RANKS], 1) == static_cast<int>(gridDim.x) - 1;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    s_last = atomicAdd(&c.cursors[MAX_RANKS], 1) == static_cast<int>(gridDim.x) - 1;
+  }
   __syncthreads();
   if (!s_last) return;
   __threadfence_system();
