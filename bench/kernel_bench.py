@@ -163,6 +163,23 @@ def case_gemm_decode(small):
             report(f"gemm_decode_{name}_b128", us, w.numel() * 2, 2 * 128 * N * K, bt=bt or "auto")
 
 
+def case_gemm_decode_splitk(small):
+    """Decode-size projections with the K loop split over a thread-block cluster (DSMEM reduction in rank order):
+    token tile x split factor sweep, to see where spreading one weight tile over several SMs pays."""
+    L, st = C.lib(), torch.cuda.current_stream().cuda_stream
+    err = C.err_word(torch.device("cuda"))
+    for name, N, K in (("in_proj", 12352, 2048), ("qkv_proj", 9216, 2048), ("out_proj", 2048, 4096)):
+        x, w = bf(128, K), bf(N, K, scale=0.02)
+        out = torch.empty(128, N, dtype=torch.bfloat16, device="cuda")
+        for bt in (16, 64, 128):
+            for splits in (1, 2, 4, 8):
+                def run():
+                    rc = L.b200_gemm_dense(x.data_ptr(), w.data_ptr(), out.data_ptr(), 128, N, K, K, K, N, 0, 0, bt, None,
+                                           None, err.data_ptr(), splits, 0, st)
+                    assert rc == 0, rc
+                report(f"gemm_decode_{name}_b128", timed(run), w.numel() * 2, 2 * 128 * N * K, bt=bt, splits=splits)
+
+
 def case_gemm_prefill(small):
     """Dense projection at prefill size: 8192 rows x (12352 x 2048), compute bound."""
     T = 2048 if small else 8192
