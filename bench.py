@@ -45,6 +45,9 @@ def parse() -> argparse.Namespace:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=128, help="concurrent requests per GPU")
     ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--kernel-table", action="store_true",
+                    help="after the timed run, replay a few steps under the CUDA activity profiler on rank 0 and print "
+                         "per-kernel device time per step to stderr")
     ap.add_argument("--parallelism", default="auto", choices=["auto", "dp", "tp_ep", "dp_ep"],
                     help="auto: one GPU -> dp; several -> dp_ep (data-parallel attention, expert-parallel MoE over NVLink "
                          "peer memory), falling back to independent dp replicas if its set-up or trial step fails")
@@ -341,8 +344,10 @@ def main() -> None:
             weights = random_weights(mcfg, seed=1234 + rank, device=dev, dtype=torch.bfloat16)
             engine = Engine(weights, ecfg)
 
-    def run_phase(timed_steps: int, warm: int, e2e: bool):
-        """Prefill B fresh requests, run `warm` untimed decode steps, then time `timed_steps` steps."""
+    def run_phase(timed_steps: int, warm: int, e2e: bool, table: bool = False):
+        """Prefill B fresh requests, run `warm` untimed decode steps, then time `timed_steps` steps. With `table`,
+        rank 0 records the replays with the CUDA activity profiler and prints per-kernel time per step to stderr
+        (a diagnostic: numbers of such a pass are never reported as the bench value)."""
         engine.cache.clear()
         g = torch.Generator().manual_seed(99 + (0 if tp_mode else rank) + (1000 if e2e else 0))
         gens = [
@@ -364,6 +369,12 @@ def main() -> None:
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         produced0 = sum(len(x.output) for x in gens)
         t0 = time.perf_counter()
+        prof = None
+        if table and rank == 0:
+            from torch.profiler import ProfilerActivity, profile
+
+            prof = profile(activities=[ProfilerActivity.CUDA])
+            prof.__enter__()
         start.record()
         if e2e:
             for _ in range(timed_steps):
@@ -379,6 +390,14 @@ def main() -> None:
         end.record()
         torch.cuda.synchronize()
         wall = time.perf_counter() - t0
+        if prof is not None:
+            prof.__exit__(None, None, None)
+            rows = sorted(prof.key_averages(), key=lambda r: -r.device_time_total)
+            print(f"per-kernel device time per step over {timed_steps} replays (rank 0):", file=sys.stderr)
+            for r in rows[:40]:
+                print(f"  {r.device_time_total / timed_steps:9.1f} us  {r.count / timed_steps:6.1f} launches  {r.key[:110]}",
+                      file=sys.stderr)
+            sys.stderr.flush()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
@@ -433,6 +452,9 @@ def main() -> None:
     ms, _wall, tokens = run_phase(K, max(W, 3), e2e=False)
     clocks = sampler.stop()
     cuda_ops.check_errors(dev)
+    if args.kernel_table:
+        run_phase(min(K, 5), 3, e2e=False, table=True)
+        cuda_ops.check_errors(dev)
     serving_line = None
     if serving:
         s_wall, s_ok, s_ttft, s_tpot = run_serving()

@@ -171,7 +171,7 @@ def case_gemm_decode_splitk(small):
     for name, N, K in (("in_proj", 12352, 2048), ("qkv_proj", 9216, 2048), ("out_proj", 2048, 4096)):
         x, w = bf(128, K), bf(N, K, scale=0.02)
         out = torch.empty(128, N, dtype=torch.bfloat16, device="cuda")
-        for bt in (16, 64, 128):
+        for bt in (16, 32, 64, 128):
             for splits in (1, 2, 4, 8):
                 def run():
                     rc = L.b200_gemm_dense(x.data_ptr(), w.data_ptr(), out.data_ptr(), 128, N, K, K, K, N, 0, 0, bt, None,

@@ -5,17 +5,21 @@
 Three gates on one random-init model of the full layer shapes (``--layers`` of them: 3 Gated DeltaNet + 1 attention
 per group, 256 experts, real head sizes), each printed as one JSON line with ``"pass"``:
 
-1. ``teacher_forced_top1``: a plain PyTorch run of the same bf16 weights (``ops.torch_ops``, the oracle of every
-   kernel test: same rounding points, library matmuls) generates greedy continuations; the sm_100a path is then fed
-   exactly those tokens, once through its
-   prefill kernels (one packed pass) and once through its decode kernels (token by token, batched). The reference
-   asks for top-1 agreement >= 98.5 % on the trained checkpoint (``tools/combine_k_check.sh:8-12``, method
-   ``tools/tp_parity.py``, ``engine/bench_step.py:424-437``). A random-init LM head has no preferred token: the best
-   and second-best of 248320 logits are about 0.2 standard deviations apart, so two correct bf16 implementations
-   already disagree on a good part of the positions. The gate therefore counts the positions where the oracle's
-   own margin is at least ``--margin`` logit standard deviations (a decided position): there the pick must agree at
-   >= 98.5 %, and the row-wise relative logit error must stay below ``--max-rel`` at the median. The overall
-   agreement and the error distribution are printed beside it.
+1. ``teacher_forced``: a plain PyTorch run of the same bf16 weights (``ops.torch_ops``, the oracle of every kernel
+   test: same rounding points, library matmuls) is the teacher. The reference asks for top-1 agreement >= 98.5 % on
+   the trained checkpoint (``tools/combine_k_check.sh:8-12``, method ``tools/tp_parity.py``,
+   ``engine/bench_step.py:424-437``). A trained network is well conditioned; a random-init one is not: its layers add
+   as much as the residual carries, a 0.5 % difference in one layer's output grows through the stack, and the best
+   two of 248320 random logits are 0.2 standard deviations apart. So the gate forces the teacher's values layer by
+   layer instead of only token by token:
+   (a) every layer of the sm_100a path (once through the prefill kernels on packed prompts, once through the decode
+   kernels for ``--decode-steps`` steps on the caches those prefill kernels wrote) gets the teacher's own layer
+   input and must reproduce what the teacher's layer adds to the residual within ``--max-layer-rel`` (relative
+   L2), with the same expert sets for >= 98.5 % of the rows;
+   (b) the LM head on the teacher's final hidden states must pick the teacher's token for >= 98.5 % of the rows.
+   The free-running comparison (teacher's tokens fed to the whole sm_100a model, agreement on all positions and on
+   the positions where the teacher's own margin is at least ``--margin`` logit standard deviations, relative logit
+   error) is printed beside it and does not gate.
 2. ``spec_equals_plain``: greedy outputs with MTP speculation at ``--depth`` equal the outputs without it for all
    prompts (reference: ``tools/chain_gate.py``, "spec == plain 8/8").
 3. ``bitwise_repeatable``: the same batch generated three times through the captured decode graphs gives identical
@@ -52,7 +56,9 @@ def main() -> int:
     ap.add_argument("--depth", type=int, default=3)
     ap.add_argument("--router-scale", type=float, default=16.0)
     ap.add_argument("--margin", type=float, default=0.5, help="oracle top-1 margin (in logit standard deviations) of a decided position")
-    ap.add_argument("--max-rel", type=float, default=0.05, help="bound on the median row-wise relative logit error")
+    ap.add_argument("--max-layer-rel", type=float, default=0.03,
+                    help="bound on the relative error of what one layer adds to the residual, teacher's input forced")
+    ap.add_argument("--decode-steps", type=int, default=4, help="layer-wise forced decode steps")
     ap.add_argument("--tiny", action="store_true", help="the CPU-sized architecture (quick self-check of this script)")
     a = ap.parse_args()
     dev = torch.device("cuda")
@@ -81,14 +87,55 @@ def main() -> int:
     pages_per = (a.prompt_len + 17 * a.prompts + a.tokens) // PAGE_SIZE + 2
     B = a.prompts
     tables = (torch.arange(B * pages_per, dtype=torch.int32).view(B, pages_per) + 1)
+    slots = list(range(1, B + 1))
+    eps = cfg.rms_norm_eps
 
-    def logits_of(model, rows):
-        return model.logits(rows).float()
+    def rel(x, y):
+        return ((x.float() - y.float()).norm() / y.float().norm().clamp_min(1e-12)).item()
+
+    def layerwise(ref, got, batch, decode):
+        """Both models run every layer on the teacher's input; returns per-layer errors and the teacher's output."""
+        torch_ops.DECODE_MODE = cuda_ops.DECODE_MODE = decode
+        res, h = torch_ops.add_rmsnorm(torch_ops.embed(batch.tokens, w16.embed), None, w16.layers[0].input_norm, eps)
+        rows = []
+        for i, lw in enumerate(w16.layers):
+            nxt = w16.layers[i + 1].input_norm if i + 1 < len(w16.layers) else w16.final_norm
+            kw = (lambda m: dict(gi=m._gdn_index[i])) if lw.kind == "linear_attention" else \
+                 (lambda m: dict(kv_layer=m.kv[m._kv_index[i]]))
+            rt, ht = ref._layer(lw, h, res, batch, nxt, **kw(ref))
+            rc, hc = got._layer(lw, h.clone(), res.clone(), batch, nxt, **kw(got))
+            # expert choice of each path's router GEMM on one normed input (the layer's own input rows)
+            lt = torch_ops.linear(h, lw.router, out_dtype=torch.float32)[:, : cfg.num_experts]
+            lc = cuda_ops.linear(h, lw.router, out_dtype=torch.float32)[:, : cfg.num_experts]
+            it = torch_ops.router_topk(lt, cfg.num_experts_per_tok)[1].sort(-1).values
+            ic = torch_ops.router_topk(lc, cfg.num_experts_per_tok)[1].sort(-1).values
+            rows.append({"layer": i, "kind": lw.kind[:6], "added_rel": rel(rc.float() - res.float(), rt.float() - res.float()),
+                         "normed_rel": rel(hc, ht), "same_experts": (it == ic).all(-1).float().mean().item()})
+            res, h = rt, ht
+        return rows, h
 
     ref_model = Model(w32, num_pages=B * pages_per + 1, state_slots=B + 1, ops=torch_ops)
     got_model = Model(w16, num_pages=B * pages_per + 1, state_slots=B + 1, ops=cuda_ops)
-    slots = list(range(1, B + 1))
-    # (a) prefill kernels: prompt + continuation in one packed pass; row p + j - 1 predicts continuation token j
+    pre_rows, h_pre = layerwise(ref_model, got_model, PackedBatch.prefill(prompts, slots, [0] * B, tables, dev), False)
+    dec_rows, h_dec = [], []
+    for j in range(a.decode_steps):
+        toks = [o[j] for o in want]
+        pos = [len(p) + j for p in prompts]
+        rows, hj = layerwise(ref_model, got_model, PackedBatch.uniform(toks, pos, slots, tables, 1, dev), True)
+        dec_rows.append(rows)
+        h_dec.append(hj)
+    sample = torch.cat([h_pre[:: max(1, h_pre.shape[0] // 512)], *h_dec])
+    head_ok = (got_model.logits(sample).argmax(-1) == ref_model.logits(sample).argmax(-1)).float().mean().item()
+    worst_pre = max(r["added_rel"] for r in pre_rows)
+    worst_dec = max(r["added_rel"] for rows in dec_rows for r in rows) if dec_rows else 0.0
+    same_exp = min([r["same_experts"] for r in pre_rows] + [r["same_experts"] for rows in dec_rows for r in rows])
+    cuda_ops.check_errors(dev)
+    del ref_model, got_model
+    torch.cuda.empty_cache()
+
+    # free-running part (printed, not gating): the teacher's tokens through the whole sm_100a model
+    ref_model = Model(w32, num_pages=B * pages_per + 1, state_slots=B + 1, ops=torch_ops)
+    got_model = Model(w16, num_pages=B * pages_per + 1, state_slots=B + 1, ops=cuda_ops)
     seqs = [p + o[:-1] for p, o in zip(prompts, want)]
     agree = total = decided = decided_ok = 0
     rels = []
@@ -96,9 +143,9 @@ def main() -> int:
         model.hid = model.forward(PackedBatch.prefill(seqs, slots, [0] * B, tables, dev))
     start = 0
     margins = {}
-    for si, (p, o, s) in enumerate(zip(prompts, want, seqs)):
-        rows = torch.arange(start + len(p) - 1, start + len(s), device=dev)
-        lr, lg = logits_of(ref_model, ref_model.hid[rows]), logits_of(got_model, got_model.hid[rows])
+    for si, (p, o, s_) in enumerate(zip(prompts, want, seqs)):
+        rows = torch.arange(start + len(p) - 1, start + len(s_), device=dev)
+        lr, lg = ref_model.logits(ref_model.hid[rows]).float(), got_model.logits(got_model.hid[rows]).float()
         hit = lg.argmax(-1).cpu() == torch.tensor(o)
         top2 = lr.topk(2, dim=-1).values
         sure = ((top2[:, 0] - top2[:, 1]) >= a.margin * lr.std(dim=-1)).cpu()
@@ -108,12 +155,8 @@ def main() -> int:
         decided += int(sure.sum())
         decided_ok += int((hit & sure).sum())
         rels.extend(((lg - lr).norm(dim=-1) / lr.norm(dim=-1)).tolist())
-        start += len(s)
-    r1 = agree / total
-    r1d = decided_ok / max(decided, 1)
+        start += len(s_)
     rels.sort()
-    med_rel, p90_rel = rels[len(rels) // 2], rels[int(len(rels) * 0.9)]
-    # (b) decode kernels: fresh state, prompts prefilled, then the oracle's tokens fed step by step
     got2 = Model(w16, num_pages=B * pages_per + 1, state_slots=B + 1, ops=cuda_ops)
     h = got2.forward(PackedBatch.prefill(prompts, slots, [0] * B, tables, dev))
     ends = torch.tensor([sum(len(p) for p in prompts[: i + 1]) - 1 for i in range(B)], device=dev)
@@ -133,16 +176,24 @@ def main() -> int:
         total2 += B
         dec2 += int(sure.sum())
         dec2_ok += int((hit & sure).sum())
-    r2 = agree2 / total2
-    r2d = dec2_ok / max(dec2, 1)
     cuda_ops.check_errors(dev)
-    ok = r1d >= 0.985 and r2d >= 0.985 and med_rel <= a.max_rel and decided >= total // 10
+    ok = worst_pre <= a.max_layer_rel and worst_dec <= a.max_layer_rel and same_exp >= 0.985 and head_ok >= 0.985
     ok_all &= ok
-    print(json.dumps({"gate": "teacher_forced_top1", "pass": ok,
-                      "decided_positions": {"count": decided, "of": total, "margin_sigmas": a.margin,
-                                            "prefill_kernels": round(r1d, 4), "decode_kernels": round(r2d, 4), "threshold": 0.985},
-                      "all_positions": {"prefill_kernels": round(r1, 4), "decode_kernels": round(r2, 4)},
-                      "rel_logit_error": {"median": round(med_rel, 4), "p90": round(p90_rel, 4), "bound_on_median": a.max_rel},
+    print(json.dumps({"gate": "teacher_forced", "pass": ok,
+                      "layerwise": {"bound_added_rel": a.max_layer_rel, "prefill_kernels_worst": round(worst_pre, 4),
+                                    "decode_kernels_worst": round(worst_dec, 4), "decode_steps": a.decode_steps,
+                                    "same_expert_sets_min": round(same_exp, 4),
+                                    "prefill_per_layer": [round(r["added_rel"], 4) for r in pre_rows],
+                                    "decode_per_layer_max": [round(max(rows[i]["added_rel"] for rows in dec_rows), 4)
+                                                             for i in range(len(pre_rows))] if dec_rows else []},
+                      "lm_head_top1_on_teacher_hidden": round(head_ok, 4),
+                      "free_running": {"all_positions": {"prefill_kernels": round(agree / total, 4),
+                                                         "decode_kernels": round(agree2 / total2, 4)},
+                                       "decided_positions": {"count": decided, "of": total, "margin_sigmas": a.margin,
+                                                             "prefill_kernels": round(decided_ok / max(decided, 1), 4),
+                                                             "decode_kernels": round(dec2_ok / max(dec2, 1), 4)},
+                                       "rel_logit_error": {"median": round(rels[len(rels) // 2], 4),
+                                                           "p90": round(rels[int(len(rels) * 0.9)], 4)}},
                       "layers": cfg.num_hidden_layers, "router_scale": a.router_scale,
                       "oracle": "plain PyTorch ops on the same bf16 weights"}), flush=True)
     del ref_model, got_model, got2, w32

@@ -219,10 +219,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     T, K = x.shape
     N = w.shape[0]
     f32 = out_dtype == torch.float32
-    out = torch.empty(T, N, dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
     if T == 0:
-        return out
+        return torch.empty(T, N, dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
     assert x.stride(1) == 1 and w.stride(1) == 1 and K % 8 == 0
+    out = torch.empty(T, N, dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
     if bt == 0 and 16 < T <= 256 and N <= 32 * 128:
         # few weight tiles (out_proj: 16, router: 3): 16-row token tiles put 8x more CTAs on the K loop, which is what
         # a latency-bound decode GEMM needs (measured at 128 rows: out_proj 27.4 -> 21.4 us, router 19.4 -> 13.2 us).
