@@ -126,6 +126,50 @@ def mode_tp_model(rank, world, dev):
             from b200serve.ops import cuda_ops
 
             cuda_ops.check_errors(dev)
+    # Teacher forced: the unsharded model's tokens through the sharded model, hidden states and logits compared
+    # position by position (a free-running token comparison cannot tell reordered bf16 sums from a sharding error:
+    # one flipped near-tie changes the rest of that sequence). One packed prefill pass over prompt + continuation,
+    # then decode steps on the caches it wrote.
+    from b200serve.models.qwen36 import Model, PackedBatch
+    from b200serve.ops import torch_ops
+
+    ops = torch_ops
+    if cuda:
+        from b200serve.ops import cuda_ops as ops
+    n = len(prompts)
+    tables = torch.arange(n * 8, dtype=torch.int32).view(n, 8) + 1
+    slots = list(range(1, n + 1))
+    seqs = [p + o[:-4] for p, o in zip(prompts, ref)]
+    for name, comm in comms.items():
+        one = Model(full, num_pages=n * 8 + 1, state_slots=n + 1, ops=ops)
+        tpm = Model(shard_weights(full, rank, world), num_pages=n * 8 + 1, state_slots=n + 1, ops=ops,
+                    tp=TPContext(rank, world, comm))
+        pairs = []
+        batch = PackedBatch.prefill(seqs, slots, [0] * n, tables, dev)
+        pairs.append((one.forward(batch), tpm.forward(batch)))
+        for j in range(4, 1, -1):  # the held-back continuation tokens, one decode step each
+            toks = [o[-j] for o in ref]
+            pos = [len(p) + len(o) - j for p, o in zip(prompts, ref)]
+            batch = PackedBatch.uniform(toks, pos, slots, tables, 1, dev)
+            pairs.append((one.forward(batch), tpm.forward(batch)))
+        h1, h2 = torch.cat([a for a, _ in pairs]), torch.cat([b for _, b in pairs])
+        l1, l2 = one.logits(h1).float(), tpm.logits(h2).float()
+        rel_h = ((h2.float() - h1.float()).norm() / h1.float().norm()).item()
+        rel_l = ((l2 - l1).norm() / l1.norm()).item()
+        top2 = l1.topk(2, dim=-1).values
+        sure = (top2[:, 0] - top2[:, 1]) >= 0.5 * l1.std(dim=-1)
+        hit = l1.argmax(-1) == l2.argmax(-1)
+        top1, top1_sure = hit.float().mean().item(), hit[sure].float().mean().item() if bool(sure.any()) else 1.0
+        if rank == 0:
+            print(f"tp_model[{name} teacher-forced] world={world}: hidden rel err {rel_h:.2e}, logits rel err {rel_l:.2e}, "
+                  f"top-1 {top1:.4f} ({int(sure.sum())} of {len(hit)} decided positions: {top1_sure:.4f})", flush=True)
+        if cuda:
+            ops.check_errors(dev)
+            assert rel_h <= 0.05 and rel_l <= 0.05, (name, rel_h, rel_l)
+            assert top1_sure >= 0.985, (name, top1_sure)
+        else:
+            assert rel_h <= 1e-4 and rel_l <= 1e-4 and top1 == 1.0, (name, rel_h, rel_l, top1)
+        del one, tpm
     # MTP speculation inside the sharded replica: every rank drafts, verifies and accepts identically, and the outputs
     # stay those of plain decoding
     import dataclasses
