@@ -346,8 +346,9 @@ def main() -> None:
 
     def run_phase(timed_steps: int, warm: int, e2e: bool, table: bool = False):
         """Prefill B fresh requests, run `warm` untimed decode steps, then time `timed_steps` steps. With `table`,
-        rank 0 records the replays with the CUDA activity profiler and prints per-kernel time per step to stderr
-        (a diagnostic: numbers of such a pass are never reported as the bench value)."""
+        the replays are recorded with the CUDA activity profiler and rank 0 prints per-kernel time per step to stderr
+        (a diagnostic: numbers of such a pass are never reported as the bench value; with programmatic dependent
+        launch a kernel's duration includes its wait for the kernel before it, ENGINE_PDL=0 gives plain durations)."""
         engine.cache.clear()
         g = torch.Generator().manual_seed(99 + (0 if tp_mode else rank) + (1000 if e2e else 0))
         gens = [
@@ -370,7 +371,7 @@ def main() -> None:
         produced0 = sum(len(x.output) for x in gens)
         t0 = time.perf_counter()
         prof = None
-        if table and rank == 0:
+        if table:  # every rank records (the ranks wait on one another: all of them must run equally slowed)
             from torch.profiler import ProfilerActivity, profile
 
             prof = profile(activities=[ProfilerActivity.CUDA])
@@ -392,6 +393,7 @@ def main() -> None:
         wall = time.perf_counter() - t0
         if prof is not None:
             prof.__exit__(None, None, None)
+        if prof is not None and rank == 0:
             rows = sorted(prof.key_averages(), key=lambda r: -r.device_time_total)
             print(f"per-kernel device time per step over {timed_steps} replays (rank 0):", file=sys.stderr)
             for r in rows[:40]:

@@ -167,7 +167,7 @@ __device__ void plan_scatter(const int* idx, int n_pairs, int Et, int bt, int* o
   s_cur[e] = 0;
   __syncthreads();
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-    const int x = idx[i];
+    const int x = __ldcg(idx + i);  // through L2: other CTAs of the same launch may have written it
     if (x >= 0 && x < Et) atomicAdd(&s_count[x], 1);
   }
   __syncthreads();
@@ -206,7 +206,7 @@ __device__ void plan_scatter(const int* idx, int n_pairs, int Et, int bt, int* o
   }
   __syncthreads();
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-    const int x = idx[i];
+    const int x = __ldcg(idx + i);
     if (x < 0) { inv[i] = -1; continue; }  // pair served by another rank
     if (x >= Et) { atomicCAS(err, 0, ERR_BAD_INDEX); inv[i] = -1; continue; }
     const int pos = s_off[x] + atomicAdd(&s_cur[x], 1);
@@ -238,6 +238,36 @@ moe_route_plan_kernel(const float* logits, int ldl, int T, int E, int top_k, int
     route_row<PER_LANE>(logits + static_cast<size_t>(r) * ldl, E, top_k, shared, wts + static_cast<size_t>(r) * P,
                         idx + static_cast<size_t>(r) * P, expert_map, nullptr, lane);
   __syncthreads();  // this CTA wrote idx: visible to all its threads after the barrier
+  plan_scatter(idx, T * P, Et, bt, offsets, tiles, n_tiles, max_tiles, perm, inv, err, P, src_rows);
+}
+
+// Any number of rows, still one launch: a grid of 1024-thread CTAs routes 32 rows each; the CTA that finishes last
+// (a ticket counter in global memory, which it puts back to zero for the next launch) builds the plan from the whole
+// index table. Everything the other CTAs wrote is visible to it: they fence before taking their ticket.
+template <int PER_LANE>
+__global__ void __launch_bounds__(1024)
+moe_route_plan_grid_kernel(const float* logits, int ldl, int T, int E, int top_k, int shared, float* wts, int* idx,
+                           const int* expert_map, int Et, int bt, int* offsets, int4* tiles, int* n_tiles,
+                           int max_tiles, int* perm, int* inv, int* err, int* src_rows, unsigned int* ticket) {
+  pdl_wait();
+  pdl_launch();
+  __shared__ int s_last;
+  const int P = top_k + (shared ? 1 : 0);
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 32 + (threadIdx.x >> 5);
+  if (r < T)
+    route_row<PER_LANE>(logits + static_cast<size_t>(r) * ldl, E, top_k, shared, wts + static_cast<size_t>(r) * P,
+                        idx + static_cast<size_t>(r) * P, expert_map, nullptr, lane);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int t = atomicAdd(ticket, 1u);
+    s_last = t == gridDim.x - 1;
+    if (s_last) *ticket = 0;  // every CTA has taken its ticket: ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
   plan_scatter(idx, T * P, Et, bt, offsets, tiles, n_tiles, max_tiles, perm, inv, err, P, src_rows);
 }
 
@@ -440,16 +470,22 @@ extern "C" int b200_moe_plan(const int* idx, int n_pairs, int Et, int bt, int* o
                       static_cast<int4*>(tiles), n_tiles, max_tiles, perm, inv, err, P, src_rows));
 }
 
-// Routing and plan of a decode-size batch (T <= 256 rows) in one launch.
+// Routing and plan in one launch. `ticket`: one zero-initialised word per stream (the kernel leaves it zero); with at
+// most 32 rows a single CTA does everything and the word is not touched.
 extern "C" int b200_moe_route_plan(const float* logits, int ldl, int T, int E, int top_k, int shared, float* wts,
                                    int* idx, const int* expert_map, int Et, int bt, int* offsets, void* tiles,
                                    int* n_tiles, int max_tiles, int* perm, int* inv, int* err, int* src_rows,
-                                   cudaStream_t st) {
+                                   unsigned int* ticket, cudaStream_t st) {
   if (T <= 0) return 0;
   if (E > 32 * MAX_PER_LANE || top_k > 32 || Et > 1024) return -7;
-  auto k = E <= 256 ? moe_route_plan_kernel<8> : moe_route_plan_kernel<MAX_PER_LANE>;
-  LAUNCHED(launch_pdl(k, dim3(1), dim3(1024), 0, st, logits, ldl, T, E, top_k, shared, wts, idx, expert_map, Et, bt,
-                      offsets, static_cast<int4*>(tiles), n_tiles, max_tiles, perm, inv, err, src_rows));
+  if (T <= 32 || ticket == nullptr) {
+    auto k = E <= 256 ? moe_route_plan_kernel<8> : moe_route_plan_kernel<MAX_PER_LANE>;
+    LAUNCHED(launch_pdl(k, dim3(1), dim3(1024), 0, st, logits, ldl, T, E, top_k, shared, wts, idx, expert_map, Et, bt,
+                        offsets, static_cast<int4*>(tiles), n_tiles, max_tiles, perm, inv, err, src_rows));
+  }
+  auto k = E <= 256 ? moe_route_plan_grid_kernel<8> : moe_route_plan_grid_kernel<MAX_PER_LANE>;
+  LAUNCHED(launch_pdl(k, dim3((T + 31) / 32), dim3(1024), 0, st, logits, ldl, T, E, top_k, shared, wts, idx, expert_map,
+                      Et, bt, offsets, static_cast<int4*>(tiles), n_tiles, max_tiles, perm, inv, err, src_rows, ticket));
 }
 
 extern "C" int b200_moe_gather(const void* x, const int* perm, const int* n_valid, int n_pairs, int T, int P, int H,

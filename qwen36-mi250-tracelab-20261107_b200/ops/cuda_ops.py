@@ -61,7 +61,7 @@ class _Sig:
     b200_add_rmsnorm = [P, P, P, P, P, I, I, F, I, P]
     b200_moe_route = [P, I, I, I, I, I, P, P, P, I, P, P]
     b200_moe_plan = [P, I, I, I, P, P, P, I, P, P, P, I, P, P]
-    b200_moe_route_plan = [P, I, I, I, I, I, P, P, P, I, I, P, P, P, I, P, P, P, P, P]
+    b200_moe_route_plan = [P, I, I, I, I, I, P, P, P, I, I, P, P, P, I, P, P, P, P, P, P]
     b200_moe_combine_norm = [P, P, P, I, I, I, P, P, P, P, F, P]
     b200_mtp_in = [P, P, P, P, P, P, I, I, I, F, P]
     b200_chain_accept = [P, P, P, P, P, I, I, I, I, P, P, P, P]
@@ -99,6 +99,20 @@ def _check(rc: int, what: str) -> None:
 
 
 _err: dict[int, torch.Tensor] = {}
+_tickets: dict[int, torch.Tensor] = {}
+
+
+def _ticket(device: torch.device) -> torch.Tensor:
+    """The counter word of kernels whose last CTA finishes the job: zero between launches (the kernel puts it back).
+    One per device, like the error word: the engine issues every pass of a device on one stream, and launches that
+    share the word must be ordered."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _tickets:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("first use of the ticket word inside a graph capture: run the pass once eagerly first")
+        _tickets[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+    return _tickets[idx]
 
 
 def err_word(device: torch.device) -> torch.Tensor:
@@ -372,15 +386,11 @@ def moe_block(x: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_
     src_rows = ints[Et + 2 + 2 * n_pairs :] if gather else None
     max_tiles = min(Et, n_pairs) + n_pairs // bt + 1
     tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device=dev)
-    if T <= ROUTE_PLAN_MAX_ROWS:
-        _check(L.b200_moe_route_plan(_ptr(logits), logits.stride(0), T, n_experts, top_k, int(shared_merged), _ptr(wts),
-                                     _ptr(idx), _ptr(expert_map), Et, bt, _ptr(offsets), _ptr(tiles), _ptr(n_tiles),
-                                     max_tiles, _ptr(perm), _ptr(inv), _ptr(err), _ptr(src_rows), st), "moe_route_plan")
-    else:
-        _check(L.b200_moe_route(_ptr(logits), logits.stride(0), T, n_experts, top_k, int(shared_merged), _ptr(wts),
-                                _ptr(idx), None, 0, _ptr(expert_map), st), "moe_route")
-        _check(L.b200_moe_plan(_ptr(idx), n_pairs, Et, bt, _ptr(offsets), _ptr(tiles), _ptr(n_tiles), max_tiles,
-                               _ptr(perm), _ptr(inv), _ptr(err), Pn, _ptr(src_rows), st), "moe_plan")
+    # routing and plan in one launch: up to 32 rows in a single CTA, more rows as a grid whose last CTA builds the plan
+    _check(L.b200_moe_route_plan(_ptr(logits), logits.stride(0), T, n_experts, top_k, int(shared_merged), _ptr(wts),
+                                 _ptr(idx), _ptr(expert_map), Et, bt, _ptr(offsets), _ptr(tiles), _ptr(n_tiles),
+                                 max_tiles, _ptr(perm), _ptr(inv), _ptr(err), _ptr(src_rows), _ptr(_ticket(dev)), st),
+           "moe_route_plan")
     act = torch.empty(n_pairs, inter, dtype=x.dtype, device=dev)
     if gather:
         _check(L.b200_gemm_grouped(_ptr(x), _ptr(w_gate_up), _ptr(act), n_pairs, Et, inter, 2 * inter, H, inter,

@@ -46,8 +46,8 @@ class DepthPolicy:
 
     def cost(self, B: int, k: int) -> float:
         """Cost of a depth-``k`` step over ``B`` sequences. With a measured table: the entry of the smallest measured
-        batch bucket that holds ``B`` (the largest one beyond it); a depth the bucket was not measured at is
-        extended linearly from its two deepest measured depths (a verify step grows by k + 1 rows per sequence and
+        batch bucket that holds ``B`` (the largest one beyond it); a depth the bucket was not measured at lies on
+        the line through its measured neighbours, or through the two deepest measured depths when it is deeper (a verify step grows by k + 1 rows per sequence and
         one more draft link per depth). Without a table: a fixed part plus a per-row part."""
         if self.table:
             buckets = sorted({b for (b, _k) in self.table})
@@ -56,9 +56,12 @@ class DepthPolicy:
                 return self.table[(b, k)]
             ks = sorted(kk for (bb, kk) in self.table if bb == b)
             if len(ks) >= 2:
-                k1, k2 = ks[-2], ks[-1]
+                below = [kk for kk in ks if kk < k]
+                above = [kk for kk in ks if kk > k]
+                # between two measured depths: on the line through them; beyond the deepest: on the last two's line
+                k1, k2 = (below[-1], above[0]) if below and above else (ks[-2], ks[-1]) if below else (ks[0], ks[1])
                 slope = (self.table[(b, k2)] - self.table[(b, k1)]) / (k2 - k1)
-                return self.table[(b, k2)] + slope * (k - k2)
+                return self.table[(b, k1)] + slope * (k - k1)
             return math.inf
         return 1.0 + self.row_cost * k * max(1.0, math.log2(B + 1))
 

@@ -136,7 +136,8 @@ def test_depth_policy_reads_a_measured_cost_table_and_extends_it_to_deeper_chain
     p = DepthPolicy(kmax=7)
     p.load_table(shipped)
     assert p.cost(1, 0) < p.cost(1, 1) < p.cost(1, 3) and p.cost(5, 2) == p.cost(8, 2)  # bucket of the next larger batch
-    assert p.cost(1, 5) == pytest.approx(p.cost(1, 3) + 2 * (p.cost(1, 3) - p.cost(1, 2)))  # beyond the measured depths
+    assert p.cost(1, 5) == pytest.approx(7.63) and p.cost(1, 4) == pytest.approx((p.cost(1, 3) + p.cost(1, 5)) / 2)  # measured; between
+    assert p.cost(64, 5) == pytest.approx(p.cost(64, 3) + 2 * (p.cost(64, 3) - p.cost(64, 2)))  # beyond the measured depths
     assert p.cost(200, 1) == p.cost(64, 1)  # beyond the largest measured bucket
     # high acceptance at batch 1 pays for deep chains, low acceptance or a big batch does not
     p.accept = [0.9] * 7
