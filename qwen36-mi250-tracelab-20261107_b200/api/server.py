@@ -354,6 +354,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--replica-devices", default=env("ENGINE_REPLICA_DEVICES"))
     ap.add_argument("--device", default=env("ENGINE_DEVICE", "auto"), choices=["auto", "cpu", "cuda"])
     ap.add_argument("--max-seqs", type=int, default=int(env("ENGINE_SLOTS", "128")))
+    ap.add_argument("--replica-split", default=env("ENGINE_REPLICA_SPLIT", "tensor"), choices=["tensor", "layers"],
+                    help="how a replica of several GPUs (--gpus-per-replica) divides the model: every layer sharded "
+                         "across them, or a run of whole layers on each (a capacity measure: one GPU computes at a time)")
     ap.add_argument("--expert-parallel", action="store_true", default=env("ENGINE_EP", "0") not in ("", "0"),
                     help="the replicas of this server form one expert-parallel group: each holds all dense weights and "
                          "1/N of the routed experts (one GPU per replica)")
@@ -406,7 +409,7 @@ def load_service(args: argparse.Namespace) -> Service:
                        str(args.prefill_chunk_tokens), "--prefix-cache-tokens", str(args.prefix_cache_tokens),
                        "--prefix-cache-entries", str(args.prefix_cache_entries), "--prefix-cache-gib",
                        str(args.prefix_cache_gib), "--max-seqs", str(args.max_seqs)]
-        engine, followers = replica.leader_engine(args.model, tp, use_cuda, cfg, passthrough)
+        engine, followers = replica.leader_engine(args.model, tp, use_cuda, cfg, passthrough, split=args.replica_split)
         device = engine.device
     elif args.model.startswith("random:"):
         # benchmark mode: random-init weights of a named architecture created on the device, no checkpoint on disk

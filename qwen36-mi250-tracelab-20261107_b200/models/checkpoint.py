@@ -261,13 +261,16 @@ def _pack_moe(router, gate_up, down, sh_gu, sh_down, sh_gate) -> dict[str, Any]:
 
 
 def load_checkpoint(path: str | Path, device: str | torch.device = "cpu", dtype: torch.dtype | None = None,
-                    shard: tuple[int, int] | None = None, experts: tuple[int, int] | None = None) -> Weights:
+                    shard: tuple[int, int] | None = None, experts: tuple[int, int] | None = None,
+                    layers: tuple[int, int] | None = None) -> Weights:
     """Read a HF-layout checkpoint directory into engine ``Weights`` on ``device``.
 
     ``shard = (rank, world)`` keeps only that rank's tensor/expert-parallel part: every layer is
     cut on the host right after it is read, so a rank never holds more than one full layer.
     ``experts = (rank, world)`` keeps all dense weights and only that rank's routed experts plus the shared one
-    (data-parallel attention with expert-parallel MoE, ``parallel/ep.py``); the MTP block is not loaded then."""
+    (data-parallel attention with expert-parallel MoE, ``parallel/ep.py``); the MTP block is not loaded then.
+    ``layers = (rank, world)`` reads only that rank's run of layers of a layer-split replica (``parallel/pp.py``): the
+    result is what ``parallel.pp.split_layers`` makes of the full weights, without ever holding them."""
     path = Path(path)
     cfg = ModelConfig.from_pretrained(path)
     src = _TensorSource(path)
@@ -286,6 +289,21 @@ def load_checkpoint(path: str | Path, device: str | torch.device = "cpu", dtype:
         from ..parallel.ep import shard_layer_experts
 
         cut = lambda lw, i: shard_layer_experts(lw, cfg.num_experts, experts[0], experts[1])  # noqa: E731
+    if layers is not None and layers[1] > 1:
+        import copy
+
+        from ..parallel.pp import layer_range
+
+        first, end = layer_range(len(cfg.layer_types), layers[0], layers[1])
+        local = copy.deepcopy(cfg)
+        local.layer_types = list(cfg.layer_types[first:end])
+        local.num_hidden_layers = end - first
+        local.mtp_num_hidden_layers = 0
+        run = [_layer_to(_load_layer(src, f"layers.{i}.", cfg.layer_types[i], cfg), device, dtype) for i in range(first, end)]
+        boundary = src.get(f"layers.{end}.input_layernorm.weight") if end < len(cfg.layer_types) else src.get("norm.weight")
+        return Weights(local, src.get("embed_tokens.weight").to(device=device, dtype=dtype),
+                       src.get("lm_head.weight").to(device=device, dtype=dtype).contiguous(),
+                       boundary.to(device=device, dtype=dtype), run, None, vocab_start=0, full_vocab=cfg.vocab_size)
     layers = []
     for i, kind in enumerate(cfg.layer_types):
         layers.append(_layer_to(cut(_load_layer(src, f"layers.{i}.", kind, cfg), i), device, dtype))

@@ -70,14 +70,17 @@ class PackedBatch:
 
 class Model:
     def __init__(self, weights: Weights, num_pages: int, state_slots: int, ops=None,
-                 kv_dtype: torch.dtype | None = None, tp=None, ep=None) -> None:
+                 kv_dtype: torch.dtype | None = None, tp=None, ep=None, pp=None) -> None:
         """``weights`` may be one rank's shard (``parallel.tp.shard_weights``); then ``tp`` names the rank
         group and every mixer / MoE output is summed across it. ``ep`` (a ``parallel.ep.EpMoE``) selects data-parallel
         attention with expert-parallel MoE instead: this rank serves its own rows with full dense weights, holds only
         its share of the routed experts (``parallel.ep.shard_experts``) and exchanges rows with the other ranks inside
-        every MoE block, so all ranks must run their forward passes in step."""
+        every MoE block, so all ranks must run their forward passes in step. ``pp`` (a ``parallel.pp.PPContext``) marks
+        ``weights`` as one rank's run of layers (``parallel.pp.split_layers``): the pass receives its input rows from the
+        rank before and hands its output to the rank after."""
         self.tp = tp
         self.ep = ep
+        self.pp = pp
         self.w = weights
         self.cfg: ModelConfig = weights.config
         self.ops = ops or torch_ops
@@ -280,14 +283,20 @@ class Model:
                 return self._forward_sp(batch, sp)
         ops.DECODE_MODE = batch.G > 0  # decode / verify passes may split K across clusters; prefill never does
         layers = self.w.layers
-        x = ops.embed(batch.tokens, self.w.embed)
-        res, h = ops.add_rmsnorm(x, None, layers[0].input_norm, cfg.rms_norm_eps)
+        pp = self.pp
+        if pp is not None and not pp.is_first:
+            res, h = pp.recv(batch.tokens.shape[0], cfg.hidden_size, self.dtype, self.device)
+        else:
+            x = ops.embed(batch.tokens, self.w.embed)
+            res, h = ops.add_rmsnorm(x, None, layers[0].input_norm, cfg.rms_norm_eps)
         for i, lw in enumerate(layers):
             nxt = layers[i + 1].input_norm if i + 1 < len(layers) else self.w.final_norm
             if lw.kind == "linear_attention":
                 res, h = self._layer(lw, h, res, batch, nxt, gi=self._gdn_index[i], ring=ring)
             else:
                 res, h = self._layer(lw, h, res, batch, nxt, kv_layer=self.kv[self._kv_index[i]])
+        if pp is not None and not pp.is_last:
+            pp.send(res, h)  # normed with the next rank's first input norm (carried in final_norm)
         return h
 
     def forward_empty(self) -> None:
@@ -300,6 +309,9 @@ class Model:
                             eps=self.cfg.rms_norm_eps)
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        if self.pp is not None:  # only the last rank's hidden state is the stack's output
+            out = self.ops.linear(hidden, self.w.lm_head, out_dtype=torch.float32) if self.pp.is_last else None
+            return self.pp.share(out, (hidden.shape[0], self.w.lm_head.shape[0]), torch.float32, self.device)
         out = self.ops.linear(hidden, self.w.lm_head, out_dtype=torch.float32)
         if self.tp is None:
             return out
@@ -316,6 +328,13 @@ class Model:
     def greedy(self, hidden: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """Greedy next token of each row (LM head with fused argmax on the CUDA path). ``out``: int64 ``[rows]``
         tensor that receives the picks (the captured speculative step assembles its result vector in place)."""
+        if self.pp is not None:
+            picks = self.ops.lm_head_argmax(hidden, self.w.lm_head) if self.pp.is_last else None
+            picks = self.pp.share(picks, (hidden.shape[0],), torch.int64, self.device)
+            if out is not None:
+                out.copy_(picks)
+                return out
+            return picks
         if self.tp is None:
             if out is not None and self.ops is not torch_ops:
                 return self.ops.lm_head_argmax(hidden, self.w.lm_head, out=out)

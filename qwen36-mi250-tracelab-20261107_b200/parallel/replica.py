@@ -44,7 +44,9 @@ def init_rank(rank: int, world: int, port: int, cuda: bool):
     return dev, cpu_group
 
 
-def build_engine(model_dir: str, rank: int, world: int, dev: torch.device, cpu_group, engine_cfg):
+def build_engine(model_dir: str, rank: int, world: int, dev: torch.device, cpu_group, engine_cfg, split: str = "tensor"):
+    """One rank's engine of a replica over ``world`` devices. ``split``: "tensor" shards every layer (heads, experts,
+    vocabulary) across the ranks; "layers" gives each rank a run of whole layers (parallel/pp.py)."""
     import torch.distributed as dist
 
     from ..models.checkpoint import load_checkpoint
@@ -53,6 +55,13 @@ def build_engine(model_dir: str, rank: int, world: int, dev: torch.device, cpu_g
     from .tp import DistComm, FusedComm, TPContext
 
     dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    if split == "layers":
+        from .pp import PPContext
+
+        weights = load_checkpoint(model_dir, device=dev, dtype=dtype, layers=(rank, world))
+        engine = Engine(weights, engine_cfg, pp=PPContext(rank, world))
+        engine.coordinator = Coordinator(cpu_group, rank)
+        return engine
     weights = load_checkpoint(model_dir, device=dev, dtype=dtype, shard=(rank, world))
     if dev.type == "cuda" and engine_cfg.fused_collectives:
         comm = FusedComm(dev, dist.group.WORLD)
@@ -63,11 +72,12 @@ def build_engine(model_dir: str, rank: int, world: int, dev: torch.device, cpu_g
     return engine
 
 
-def start_followers(model_dir: str, world: int, port: int, cuda: bool, cfg_args: list[str]) -> list[subprocess.Popen]:
+def start_followers(model_dir: str, world: int, port: int, cuda: bool, cfg_args: list[str],
+                    split: str = "tensor") -> list[subprocess.Popen]:
     procs = []
     for r in range(1, world):
         cmd = [sys.executable, "-m", "b200serve.parallel.replica", "--model", model_dir, "--rank", str(r), "--world",
-               str(world), "--port", str(port), "--device", "cuda" if cuda else "cpu", *cfg_args]
+               str(world), "--port", str(port), "--device", "cuda" if cuda else "cpu", "--split", split, *cfg_args]
         procs.append(subprocess.Popen(cmd, env=dict(os.environ)))
     return procs
 
@@ -79,6 +89,7 @@ def follower_main(argv: list[str] | None = None) -> None:
     ap.add_argument("--world", type=int, required=True)
     ap.add_argument("--port", type=int, required=True)
     ap.add_argument("--device", default="cuda")
+    ap.add_argument("--split", default="tensor", choices=["tensor", "layers"])
     ap.add_argument("--max-model-len", type=int, default=262144)
     ap.add_argument("--prefill-chunk-tokens", type=int, default=2048)
     ap.add_argument("--prefix-cache-tokens", type=int, default=4194304)
@@ -100,18 +111,18 @@ def follower_main(argv: list[str] | None = None) -> None:
         prefix_cache_tokens=args.prefix_cache_tokens, prefix_cache_entries=args.prefix_cache_entries,
         prefix_cache_gib=args.prefix_cache_gib, max_seqs=args.max_seqs,
     )
-    engine = build_engine(args.model, args.rank, args.world, dev, cpu_group, cfg)
+    engine = build_engine(args.model, args.rank, args.world, dev, cpu_group, cfg, split=args.split)
     print(f"engine: rank {args.rank}/{args.world} ready on {dev}", flush=True)
     engine.coordinator.follow(engine)
 
 
-def leader_engine(model_dir: str, world: int, cuda: bool, engine_cfg, cfg_args: list[str]):
+def leader_engine(model_dir: str, world: int, cuda: bool, engine_cfg, cfg_args: list[str], split: str = "tensor"):
     """Start the followers, build rank 0's engine; returns ``(engine, follower processes)``."""
     port = _free_port()
-    followers = start_followers(model_dir, world, port, cuda, cfg_args)
+    followers = start_followers(model_dir, world, port, cuda, cfg_args, split)
     try:
         dev, cpu_group = init_rank(0, world, port, cuda)
-        engine = build_engine(model_dir, 0, world, dev, cpu_group, engine_cfg)
+        engine = build_engine(model_dir, 0, world, dev, cpu_group, engine_cfg, split=split)
     except BaseException:
         for p in followers:
             p.terminate()

@@ -44,13 +44,20 @@ def _select_ops(device: torch.device):
 
 
 class Engine:
-    def __init__(self, weights: Weights, cfg: EngineConfig | None = None, ops=None, tp=None, ep=None) -> None:
+    def __init__(self, weights: Weights, cfg: EngineConfig | None = None, ops=None, tp=None, ep=None, pp=None) -> None:
         """``tp``: a ``parallel.tp.TPContext`` when ``weights`` is one rank's shard; all ranks of the group
         then run the same engine on the same requests in lockstep. ``ep``: a ``parallel.ep.EpMoE`` for data-parallel
         attention with expert-parallel MoE: every rank serves its own requests, but all ranks must issue the same
-        sequence of forward passes (same number of prefill passes and decode steps), which the caller arranges."""
+        sequence of forward passes (same number of prefill passes and decode steps), which the caller arranges.
+        ``pp``: a ``parallel.pp.PPContext`` when ``weights`` is one rank's run of layers (``parallel.pp.split_layers``);
+        the ranks run in lockstep like a tensor-parallel replica, launch eagerly and do not speculate."""
         self.cfg = cfg or EngineConfig()
+        if pp is not None:
+            import dataclasses
+
+            self.cfg = dataclasses.replace(self.cfg, cuda_graphs=False, mtp=False)
         self.tp = tp
+        self.pp = pp
         self.coordinator = None  # parallel.lockstep.Coordinator in a multi-rank replica
         self.tick = None  # parallel.dpep.TickCoordinator: data-parallel replicas that share expert-parallel MoE blocks
         self.mcfg: ModelConfig = weights.config
@@ -63,8 +70,8 @@ class Engine:
         if c.pack_weights and tp is None and hasattr(self.ops, "pack_weights"):
             self.ops.pack_weights(weights)  # before the KV pool is sized: padded copies replace a few tensors
         n_slots = c.state_slots or (c.max_seqs * 2 + 2)
-        n_pages = c.kv_pages or self._agree_min(self._auto_pages(weights, n_slots), tp)
-        self.model = Model(weights, n_pages, n_slots, ops=self.ops, tp=tp, ep=ep)
+        n_pages = c.kv_pages or self._agree_min(self._auto_pages(weights, n_slots), tp if tp is not None else pp)
+        self.model = Model(weights, n_pages, n_slots, ops=self.ops, tp=tp, ep=ep, pp=pp)
         self.pages = PagePool(n_pages)
         self.slots = SlotPool(n_slots)
         page_bytes = self.model.kv[:, 0].numel() * self.model.kv.element_size()
@@ -82,7 +89,7 @@ class Engine:
         self.running: list[Generation] = []
         self._deferred: list = []
         self._flushed = False
-        self.multi_rank = tp is not None or ep is not None
+        self.multi_rank = tp is not None or ep is not None or pp is not None
         self.broken: str | None = None  # set when a rank group can no longer be trusted to be in step
         self.device_error_pending = False  # multi-rank: a device-side failure seen since the last agreement
         self.stats = dict(
@@ -120,13 +127,18 @@ class Engine:
         return pages
 
     def _agree_min(self, value: int, tp) -> int:
-        """The smallest ``value`` over the ranks of a tensor-parallel replica. Capacities derived from a rank's own
+        """The smallest ``value`` over the ranks of a tensor-parallel or layer-split replica. Capacities derived from a rank's own
         free memory differ between GPUs (other contexts, other users' jobs), but the lockstep design needs every rank
         to allocate, evict and refuse identically, so all ranks adopt the tightest budget."""
-        group = getattr(getattr(tp, "comm", None), "group", None)
-        if tp is None or group is None:
+        if tp is None:
             return value
         import torch.distributed as dist
+
+        group = getattr(getattr(tp, "comm", None), "group", None)
+        if group is None and hasattr(tp, "is_last"):  # a layer-split replica: its own group, or all ranks
+            group = tp.group if tp.group is not None else dist.group.WORLD
+        if group is None:
+            return value
 
         on_gpu = dist.get_backend(group) == "nccl"
         t = torch.tensor([value], dtype=torch.int64, device=self.device if on_gpu else "cpu")

@@ -217,6 +217,53 @@ def mode_tp_model(rank, world, dev):
             print(f"tp_model[seq_parallel prefill] world={world}: max err {err:.4g}", flush=True)
 
 
+def mode_pp_model(rank, world, dev):
+    """Layer-split engine (each rank a run of layers) against the unsplit engine on the same requests."""
+    from b200serve.config import EngineConfig, ModelConfig
+    from b200serve.models.checkpoint import random_weights
+    from b200serve.parallel.pp import PPContext, layer_range, split_layers
+    from b200serve.sched.engine import Engine
+    from b200serve.sched.request import Sampling
+
+    cuda = dev.type == "cuda"
+    dtype = torch.bfloat16 if cuda else torch.float32
+    cfg = ModelConfig.tiny(num_experts=8, num_hidden_layers=8)
+    full = random_weights(cfg, seed=0, device="cpu", dtype=torch.float32, std=0.05, lm_head_std=0.5).to(dev, dtype)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(3, 1024, (n,), generator=g).tolist() for n in (20, 70, 150, 33)]
+    greedy = Sampling(max_tokens=12, ignore_eos=True)
+    sampled = Sampling(max_tokens=12, ignore_eos=True, temperature=0.8, top_p=0.9, seed=11)
+    ecfg = EngineConfig(max_model_len=1024, prefill_chunk_tokens=64, max_seqs=4, mtp=False, kv_pages=128)
+    ref = [x.output for x in Engine(full, ecfg).generate(prompts, [greedy, greedy, sampled, greedy])]
+    part = split_layers(full, rank, world)
+    first, end = layer_range(8, rank, world)
+    assert len(part.layers) == end - first and part.config.layer_types == cfg.layer_types[first:end]
+    eng = Engine(part, ecfg, pp=PPContext(rank, world))
+    assert eng._graphs is None and eng.spec is None
+    got = [x.output for x in eng.generate(prompts, [greedy, greedy, sampled, greedy])]
+    # a follow-up request that reuses the parked prefix: the per-rank caches stay consistent
+    nxt = prompts[1] + ref[1] + [7, 8, 9]
+    more = eng.generate([nxt], Sampling(max_tokens=6, ignore_eos=True))[0]
+    if cuda:
+        from b200serve.ops import cuda_ops
+
+        cuda_ops.check_errors(dev)
+        same = sum(a == b for x, y in zip(got, ref) for a, b in zip(x, y))
+        total = sum(len(x) for x in ref)
+        # same kernels, same order of operations: only the placement differs
+        assert same == total, (same, total)
+    else:
+        assert got == ref, (got, ref)
+        want = Engine(full, ecfg).generate([nxt], Sampling(max_tokens=6, ignore_eos=True))[0]
+        assert more.output == want.output and more.cached_tokens > 0
+    mine = torch.tensor(got, device=dev)
+    allr = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(allr, mine)
+    assert all(torch.equal(allr[0], t) for t in allr)
+    if rank == 0:
+        print(f"pp_model world={world}: tokens equal the unsplit engine on every rank (layers {first}..{end - 1} here)", flush=True)
+
+
 def mode_lockstep(rank, world, dev):
     """Leader/follower replica: only rank 0 sees the requests (and a cancellation); followers mirror it."""
     from b200serve.config import EngineConfig, ModelConfig
@@ -370,7 +417,7 @@ def mode_dp_ep_model(rank, world, dev):
 
 
 MODES = {"allreduce": mode_allreduce, "ep_moe": mode_ep_moe, "tp_model": mode_tp_model, "lockstep": mode_lockstep,
-         "seq_parallel": mode_seq_parallel, "dp_ep_model": mode_dp_ep_model}
+         "seq_parallel": mode_seq_parallel, "dp_ep_model": mode_dp_ep_model, "pp_model": mode_pp_model}
 
 if __name__ == "__main__":
     mode = sys.argv[1]

@@ -97,6 +97,41 @@ def test_served_tensor_parallel_replica_speculates_like_a_single_process(tmp_pat
         one.stop()
 
 
+@pytest.mark.parametrize("world,port", [(2, 29641), (3, 29642)])
+def test_layer_split_replica_on_cpu_ranks_matches_the_unsplit_engine(world, port):
+    r = _launch("pp_model", world, port, env={"CUDA_VISIBLE_DEVICES": ""})
+    assert r.returncode == 0 and "OK pp_model" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_layer_split_replica_on_two_gpus_matches_the_unsplit_engine():
+    r = _launch("pp_model", 2, 29643, env={"NCCL_NVLS_ENABLE": "0"})
+    assert r.returncode == 0 and "OK pp_model" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_served_layer_split_replica_on_cpu_ranks(tmp_path):
+    """`--gpus-per-replica 2 --replica-split layers` without GPUs: each process loads only its run of layers."""
+    from http_util import ServerProc, ids_of
+
+    from b200serve.models.tiny import write_tiny_checkpoint
+
+    write_tiny_checkpoint(tmp_path, lm_head_std=0.5)
+    pp = ServerProc(tmp_path, extra=["--gpus-per-replica", "2", "--replica-split", "layers"],
+                    env={"CUDA_VISIBLE_DEVICES": "", "ENGINE_MTP": "0"})
+    one = ServerProc(tmp_path, env={"CUDA_VISIBLE_DEVICES": "", "ENGINE_MTP": "0"})
+    try:
+        prompt = [5 + (i * 11) % 300 for i in range(100)]
+        a, _ = pp.completion(prompt, 12)
+        b, _ = one.completion(prompt, 12)
+        assert ids_of(a) == ids_of(b)
+        again, u2 = pp.completion(prompt, 12)
+        assert u2["prompt_tokens_details"]["cached_tokens"] > 0 and ids_of(again) == ids_of(a)
+    finally:
+        pp.stop()
+        one.stop()
+
+
 def test_served_tensor_parallel_replica_on_cpu_ranks(tmp_path):
     """`--gpus-per-replica 2` on a machine without GPUs: leader + follower processes over gloo, over HTTP."""
     from http_util import ServerProc, ids_of
