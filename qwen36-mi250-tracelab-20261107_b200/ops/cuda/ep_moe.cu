@@ -1,10 +1,12 @@
 // Expert-parallel MoE over NVLink peer memory for token-sharded activations: every rank holds its own
 // rows and E / R of the routed experts (plus a replica of the shared expert).
 //
-//   ep_send     : the dispatch all-to-all. One CTA per (row, pair): the activation row is stored straight into the
-//                 hosting rank's receive buffer, in the region reserved for this source rank, in arrival order,
-//                 with (local expert, pair index) beside it. Nothing has to be agreed beforehand: the last CTA
-//                 to finish publishes how many rows each host got and releases this source's arrival flag there.
+//   ep_route_send : routing and the dispatch all-to-all in one launch. One CTA per row: its first warp turns the
+//                 row's router logits into (expert, weight) pairs, then one warp per pair stores the activation
+//                 row straight into the hosting rank's receive buffer, in the region reserved for this source rank,
+//                 in arrival order, with (local expert, pair index) beside it. Nothing has to be agreed beforehand:
+//                 the last CTA to finish publishes how many rows each host got and releases this source's arrival
+//                 flag there.
 //   ep_plan     : on the host, waits for every source's flag (the one rendezvous of the dispatch), then sorts the
 //                 received rows by expert WITHOUT moving them: the token-tile table of the grouped GEMMs plus, for
 //                 every sorted position, the row of the receive buffer behind it (the gate/up GEMM's producer
@@ -26,6 +28,7 @@
 // so after its gate/up GEMM has read the receive buffer); a host can only overwrite a rank's pair slots after its
 // next plan, which waited for that rank's next send, which follows that rank's combine.
 #include "comm.cuh"
+#include "moe_route.cuh"
 
 namespace b200 {
 
@@ -33,8 +36,9 @@ struct EpCtx {
   bf16* xs[MAX_RANKS];          // receive buffer of each rank: [R source regions][cap_src rows][H]
   int2* meta[MAX_RANKS];        // per received row: (local expert, pair index at the source)
   bf16* pair_out[MAX_RANKS];    // [max_pairs, H] expert outputs returned to each rank
-  int* cnt[MAX_RANKS];          // [R] rows each source sent to this rank in the current call
-  uint32_t* flags[MAX_RANKS];   // [2][MAX_RANKS]: dispatch / combine arrival epochs per source
+  unsigned long long* arrive[MAX_RANKS];  // [R] per source: (call epoch << 32) | rows that source sent to this rank
+                                // in that call: count and arrival flag travel in ONE release store
+  uint32_t* flags[MAX_RANKS];   // [2][MAX_RANKS]: row 1 = combine arrival epochs per source (row 0 unused)
   uint32_t* epoch;              // this rank's call counter (device resident)
   int* cursors;                 // this rank's send cursors [R] and the CTA ticket [1]; zero between calls
   int* err;
@@ -44,34 +48,10 @@ struct EpCtx {
   int cap_src, max_pairs;
 };
 
-// One CTA per (row, pair) of this rank (at least one CTA, so that a rank without rows still reports in).
-__global__ void ep_send_kernel(EpCtx c, const bf16* x, const int* idx, int n_pairs, int P, int H) {
-  const int pair = blockIdx.x;
-  if (pair < n_pairs) {
-    const int e = idx[pair];
-    if (e >= 0 && e <= c.E) {
-      const int host = e == c.E ? c.rank : e / c.per;
-      const int local = e == c.E ? c.per : e - host * c.per;
-      __shared__ int s_pos;
-      if (threadIdx.x == 0) s_pos = atomicAdd(&c.cursors[host], 1);
-      __syncthreads();
-      const int pos = s_pos;
-      if (pos < c.cap_src) {
-        const size_t slot = static_cast<size_t>(c.rank) * c.cap_src + pos;
-        const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(pair / P) * H);
-        uint4* dst = reinterpret_cast<uint4*>(c.xs[host] + slot * H);
-        for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
-        if (threadIdx.x == 0) c.meta[host][slot] = make_int2(local, pair);
-      } else if (threadIdx.x == 0) {
-        atomicCAS(c.err, 0, ERR_BAD_INDEX);  // more rows for one host than its region holds
-      }
-    } else if (threadIdx.x == 0) {
-      atomicCAS(c.err, 0, ERR_BAD_INDEX);
-    }
-  }
-  // last CTA out: publish the per-host counts and release this source's flag on every host. The CTA's peer stores
-  // are ordered before the ticket by the barrier followed by ONE system-scope fence of the thread that takes the
-  // ticket (a fence per thread cost 3x the kernel's time: the profile showed every warp stalled on it).
+// Last CTA out: release (epoch, rows sent) of this source on every host. The CTA's peer stores
+// are ordered before the ticket by the barrier followed by ONE system-scope fence of the thread that takes the
+// ticket (a fence per thread cost 3x the kernel's time: the profile showed every warp stalled on it).
+__device__ __forceinline__ void ep_send_finish(const EpCtx& c) {
   __syncthreads();
   __shared__ int s_last;
   if (threadIdx.x == 0) {
@@ -85,13 +65,58 @@ __global__ void ep_send_kernel(EpCtx c, const bf16* x, const int* idx, int n_pai
   if (threadIdx.x < c.world) {
     const int r = threadIdx.x;
     const int n = atomicAdd(&c.cursors[r], 0);
-    c.cnt[r][c.rank] = n < c.cap_src ? n : c.cap_src;
-    __threadfence_system();
-    st_release_sys(c.flags[r] + 0 * MAX_RANKS + c.rank, e);
+    const unsigned long long word = (static_cast<unsigned long long>(e) << 32) | static_cast<unsigned>(n < c.cap_src ? n : c.cap_src);
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(c.arrive[r] + c.rank), "l"(word) : "memory");
     c.cursors[r] = 0;
   }
   __syncthreads();
   if (threadIdx.x == 0) { c.cursors[MAX_RANKS] = 0; c.epoch[0] = e; }
+}
+
+// One pair of one row by the calling warp: take the next slot of this source's region on the expert's host, store the
+// row and its (local expert, pair index) there.
+__device__ __forceinline__ void ep_send_pair(const EpCtx& c, const bf16* xrow, int e, int pair, int H, int lane) {
+  if (e < 0 || e > c.E) {
+    if (lane == 0) atomicCAS(c.err, 0, ERR_BAD_INDEX);
+    return;
+  }
+  const int host = e == c.E ? c.rank : e / c.per;
+  const int local = e == c.E ? c.per : e - host * c.per;
+  int pos = lane == 0 ? atomicAdd(&c.cursors[host], 1) : 0;
+  pos = __shfl_sync(0xffffffffu, pos, 0);
+  if (pos < c.cap_src) {
+    const size_t slot = static_cast<size_t>(c.rank) * c.cap_src + pos;
+    const uint4* src = reinterpret_cast<const uint4*>(xrow);
+    uint4* dst = reinterpret_cast<uint4*>(c.xs[host] + slot * H);
+    for (int i = lane; i < H / 8; i += 32) dst[i] = src[i];
+    if (lane == 0) c.meta[host][slot] = make_int2(local, pair);
+  } else if (lane == 0) {
+    atomicCAS(c.err, 0, ERR_BAD_INDEX);  // more rows for one host than its region holds
+  }
+}
+
+// Routing fused with the dispatch: one CTA of 32 * P threads per row (at least one CTA). Warp 0 routes the row
+// (softmax, top-k, ties to the lower id, bf16-rounded weights; the shared expert as pair P - 1) into `wts` / `idx`,
+// then warp p sends pair p.
+template <int PER_LANE>
+__global__ void ep_route_send_kernel(EpCtx c, const bf16* x, const float* logits, int ldl, int T, int top_k, int P,
+                                     int H, float* wts, int* idx) {
+  pdl_wait();
+  pdl_launch();
+  __shared__ int s_idx[32];
+  const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (row < T) {
+    if (warp == 0) {
+      route_row<PER_LANE>(logits + static_cast<size_t>(row) * ldl, c.E, top_k, P > top_k ? 1 : 0,
+                          wts + static_cast<size_t>(row) * P, s_idx, nullptr, nullptr, lane);
+      __syncwarp();
+      if (lane < P) idx[static_cast<size_t>(row) * P + lane] = s_idx[lane];
+    }
+    __syncthreads();
+    if (warp < P)
+      ep_send_pair(c, x + static_cast<size_t>(row) * H, s_idx[warp], row * P + warp, H, lane);
+  }
+  ep_send_finish(c);
 }
 
 // One CTA of 1024 threads on the host side: wait for every source, then lay the received rows out by expert
@@ -108,10 +133,25 @@ ep_plan_kernel(EpCtx c, int bt, int4* tiles, int* n_tiles, int max_tiles, int* g
   if (e == 0) s_ok = 1;
   s_count[e] = 0;
   s_cur[e] = 0;
+  pdl_wait();  // this rank's send kernel advanced the epoch
+  pdl_launch();
   __syncthreads();
   if (e < R) {
-    if (!wait_flag(c.flags[me] + 0 * MAX_RANKS + e, c.epoch[0], c.err)) s_ok = 0;
-    const int n = c.cnt[me][e];
+    // bounded wait for source e's (epoch, count) word of this call
+    const uint32_t want = c.epoch[0];
+    const unsigned long long* p = c.arrive[me] + e;
+    unsigned long long word;
+    const long long t0 = clock64();
+    bool ok = true;
+    for (;;) {
+      asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(word) : "l"(p) : "memory");
+      if (static_cast<int32_t>(static_cast<uint32_t>(word >> 32) - want) >= 0) break;
+      if (*reinterpret_cast<volatile int*>(c.err) != 0) { ok = false; break; }
+      if (clock64() - t0 > WAIT_CYCLES) { atomicCAS(c.err, 0, ERR_WAIT_PEER); ok = false; break; }
+      __nanosleep(20);
+    }
+    if (!ok) s_ok = 0;
+    const int n = ok ? static_cast<int>(static_cast<uint32_t>(word)) : 0;
     s_cnt[e] = (n >= 0 && n <= c.cap_src) ? n : 0;
     if (n < 0 || n > c.cap_src) atomicCAS(c.err, 0, ERR_BAD_INDEX);
   }
@@ -173,6 +213,8 @@ ep_plan_kernel(EpCtx c, int bt, int4* tiles, int* n_tiles, int max_tiles, int* g
 // sorted[pos] = xs[rows[pos]] for the first *n_valid positions: the expert-sorted copy that token tiles wider than
 // the gathering GEMM's limit (prefill sizes) read through their tensor map.
 __global__ void ep_compact_kernel(const bf16* xs, const int* rows, const int* n_valid, int H, bf16* sorted) {
+  pdl_wait();
+  pdl_launch();
   const int pos = blockIdx.x;
   if (pos >= *n_valid) return;
   const uint4* src = reinterpret_cast<const uint4*>(xs + static_cast<size_t>(rows[pos]) * H);
@@ -189,6 +231,8 @@ __global__ void ep_combine_kernel(EpCtx c, const float* wts, int T, int P, int H
   extern __shared__ float vals[];  // NORM: H floats
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
+  pdl_wait();  // the down projection's peer stores of this rank are complete
+  pdl_launch();
   __syncthreads();
   if (blockIdx.x == 0 && threadIdx.x < c.world) {
     __threadfence_system();
@@ -257,40 +301,37 @@ using namespace b200;
 
 extern "C" int b200_ep_ctx_size() { return static_cast<int>(sizeof(EpCtx)); }
 
-// x [T, H] (row stride H), idx [n_pairs] global expert of every (row, pair); P pairs per row.
-extern "C" int b200_ep_send(const EpCtx* c, const void* x, const int* idx, int n_pairs, int P, int H, cudaStream_t st) {
-  if (H % 8 || P <= 0) return -7;
-  ++launch_counter();
-  ep_send_kernel<<<n_pairs > 0 ? n_pairs : 1, 128, 0, st>>>(*c, static_cast<const bf16*>(x), idx, n_pairs, P, H);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+// Routing of logits [T, ldl] (E routed experts + the shared expert's gate when P = top_k + 1) and the dispatch of
+// x [T, H] in one launch; writes wts / idx [T, P] for the combine.
+extern "C" int b200_ep_route_send(const EpCtx* c, const void* x, const float* logits, int ldl, int T, int top_k, int P,
+                                  int H, float* wts, int* idx, cudaStream_t st) {
+  if (H % 8 || P <= 0 || P > 32 || top_k > P || c->E > 32 * MAX_PER_LANE) return -7;
+  auto k = c->E <= 256 ? ep_route_send_kernel<8> : ep_route_send_kernel<MAX_PER_LANE>;
+  return launch_pdl(k, dim3(T > 0 ? T : 1), dim3(32 * P), 0, st, *c, static_cast<const bf16*>(x), logits, ldl, T, top_k,
+                    P, H, wts, idx) == cudaSuccess ? 0 : -4;
 }
 extern "C" int b200_ep_plan(const EpCtx* c, int bt, void* tiles, int* n_tiles, int max_tiles, int* gather_rows,
                             void* ret_meta, int* n_rows, cudaStream_t st) {
   if (c->per + 1 > 1024) return -7;
-  ++launch_counter();
-  ep_plan_kernel<<<1, 1024, 0, st>>>(*c, bt, static_cast<int4*>(tiles), n_tiles, max_tiles, gather_rows,
-                                     static_cast<int2*>(ret_meta), n_rows);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(ep_plan_kernel, dim3(1), dim3(1024), 0, st, *c, bt, static_cast<int4*>(tiles), n_tiles, max_tiles,
+                    gather_rows, static_cast<int2*>(ret_meta), n_rows) == cudaSuccess ? 0 : -4;
 }
 extern "C" int b200_ep_compact(const void* xs, const int* rows, const int* n_valid, int max_rows, int H, void* sorted,
                                cudaStream_t st) {
   if (max_rows <= 0) return 0;
-  ++launch_counter();
-  ep_compact_kernel<<<max_rows, 128, 0, st>>>(static_cast<const bf16*>(xs), rows, n_valid, H, static_cast<bf16*>(sorted));
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(ep_compact_kernel, dim3(max_rows), dim3(128), 0, st, static_cast<const bf16*>(xs), rows, n_valid, H,
+                    static_cast<bf16*>(sorted)) == cudaSuccess ? 0 : -4;
 }
 // out [T, H] = weighted sum; or, with norm_w: res_out = bf16(res + sum), y = norm(res_out) * (1 + norm_w).
 extern "C" int b200_ep_combine(const EpCtx* c, const float* wts, int T, int P, int H, void* out, const void* res,
                                const void* norm_w, void* res_out, void* y, float eps, cudaStream_t st) {
   if (H % 8) return -7;
   const int grid = T > 0 ? T : 1;
-  ++launch_counter();
   if (norm_w != nullptr)
-    ep_combine_kernel<true><<<grid, 256, H * sizeof(float), st>>>(
-        *c, wts, T, P, H, nullptr, static_cast<const bf16*>(res), static_cast<const bf16*>(norm_w),
-        static_cast<bf16*>(res_out), static_cast<bf16*>(y), eps);
-  else
-    ep_combine_kernel<false><<<grid, 256, 0, st>>>(*c, wts, T, P, H, static_cast<bf16*>(out), nullptr, nullptr, nullptr,
-                                                   nullptr, 0.f);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+    return launch_pdl(ep_combine_kernel<true>, dim3(grid), dim3(256), H * sizeof(float), st, *c, wts, T, P, H,
+                      static_cast<bf16*>(nullptr), static_cast<const bf16*>(res), static_cast<const bf16*>(norm_w),
+                      static_cast<bf16*>(res_out), static_cast<bf16*>(y), eps) == cudaSuccess ? 0 : -4;
+  return launch_pdl(ep_combine_kernel<false>, dim3(grid), dim3(256), 0, st, *c, wts, T, P, H, static_cast<bf16*>(out),
+                    static_cast<const bf16*>(nullptr), static_cast<const bf16*>(nullptr), static_cast<bf16*>(nullptr),
+                    static_cast<bf16*>(nullptr), 0.f) == cudaSuccess ? 0 : -4;
 }

@@ -45,43 +45,52 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uin
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
-template <int D>
+// DEC (decode: one query position per tile, so GROUP <= 8 real rows): the Q and P operands keep only their first
+// 8-row swizzle atom per 128-byte block (1 KB instead of 16 KB); the MMA still reads 128 rows from those bases, the
+// other 120 come from whatever shared memory follows (the K/V stages) and land in accumulator rows nobody reads: an
+// output row of an MMA depends on its own A row only. The 106 KB this frees hold a third K/V stage, so two pages
+// are on their way while one is being used.
+template <int D, bool DEC = false>
 struct FlashCfg {
   static constexpr int DB = D / 64;             // 64-element (128-byte) blocks along the head dim
-  static constexpr int Q_BYTES = DB * 128 * 128;
+  static constexpr int Q_BLOCK = DEC ? 1024 : 128 * 128;  // bytes between the 64-element blocks of the Q tile
+  static constexpr int Q_BYTES = DB * Q_BLOCK;
   static constexpr int KV_BYTES = DB * FP_PAGE * 128;  // one of K or V, one stage
-  static constexpr int P_BYTES = 128 * 128;  // one probability tile; two are kept
+  static constexpr int P_BYTES = DEC ? 1024 : 128 * 128;  // one probability tile; two are kept
+  static constexpr int ST = DEC ? 3 : 2;        // K/V stages
   // dynamic shared memory is declared 1024-byte aligned (checked at run time), so no alignment slack is budgeted:
   // with D = 256 the tiles, the barriers and the 2 KB of static exchange arrays fill the 227 KB of an SM
-  static constexpr int SMEM = Q_BYTES + 4 * KV_BYTES + 2 * P_BYTES + 256;
+  static constexpr int SMEM = Q_BYTES + 2 * ST * KV_BYTES + 2 * P_BYTES + 256;
   static constexpr int TMEM_COLS = (128 + D) <= 256 ? 256 : 512;  // two score tiles of 64 columns + the output
 };
 
-template <int D, int GROUP>
+template <int D, int GROUP, bool DEC = false>
 __global__ void __launch_bounds__(288, 1)
 flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKV, FlashParams p) {
-  using C = FlashCfg<D>;
+  using C = FlashCfg<D, DEC>;
   constexpr int DB = C::DB;
-  constexpr int R = 128 / GROUP;  // query positions per tile
+  constexpr int ST = C::ST;
+  constexpr int R = DEC ? 1 : 128 / GROUP;  // query positions per tile
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (smem_u32(smem) & 1023u) {  // the swizzled tiles need this alignment; leave with a status rather than compute garbage
     if (threadIdx.x == 0) atomicCAS(p.err, 0, ERR_BAD_INDEX);
     return;
   }
+  // Q and P first: in the decode form the MMAs read past their real rows into the K/V stages that follow
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + C::Q_BYTES;               // [2 stages][DB][64 x 128 B]
-  uint8_t* sV = sK + 2 * C::KV_BYTES;
-  uint8_t* sP = sV + 2 * C::KV_BYTES;          // [2][128 x 128 B]: page i uses tile i & 1
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * C::P_BYTES);
+  uint8_t* sP = sQ + C::Q_BYTES;               // [2][128 x 128 B] (decode: [2][8 x 128 B]): page i uses tile i & 1
+  uint8_t* sK = sP + 2 * C::P_BYTES;           // [ST stages][DB][64 x 128 B]
+  uint8_t* sV = sK + ST * C::KV_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + ST * C::KV_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;                // [2]
-  uint64_t* kv_empty = bars + 3;               // [2]
-  uint64_t* s_full = bars + 5;                 // [2]: one per score tile
-  uint64_t* p_full = bars + 7;
-  uint64_t* acc_done = bars + 8;
-  uint64_t* x_bar = bars + 9;                  // exchange point of the 256 softmax threads (bounded wait, unlike bar.sync)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* kv_full = bars + 1;                // [ST]
+  uint64_t* kv_empty = bars + 4;               // [ST]: completes when P.V of the page in that stage has finished
+  uint64_t* s_full = bars + 7;                 // [2]: one per score tile
+  uint64_t* p_full = bars + 9;
+  uint64_t* acc_done = bars + 10;
+  uint64_t* x_bar = bars + 11;                 // exchange point of the 256 softmax threads (bounded wait, unlike bar.sync)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -108,7 +117,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int s = 0; s < ST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
     mbar_init(p_full, 256);
@@ -130,7 +139,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (warp == 8) {
     if (elect_one()) {
       auto load_page = [&](int i) {
-        const int s = i & 1;
+        const int s = i % ST;
         int page = p.tables[static_cast<size_t>(seg) * p.max_pages + first + i];
         if (page < 0 || page >= p.num_pages) { atomicCAS(p.err, 0, ERR_BAD_INDEX); page = 0; }
         const int krow = ((page * 2 + 0) * p.n_kv + kh) * FP_PAGE;
@@ -141,10 +150,9 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tma_load_2d(sV + s * C::KV_BYTES + a * FP_PAGE * 128, &tmKV, &kv_full[s], a * 64, vrow);
         }
       };
-      mbar_expect_tx(q_full, C::Q_BYTES);
-      for (int a = 0; a < DB; ++a) tma_load_4d(sQ + a * 128 * 128, &tmQ, q_full, a * 64, 0, kh, seg_row0 + p0);
-      load_page(0);
-      if (np > 1) load_page(1);
+      mbar_expect_tx(q_full, DEC ? DB * GROUP * 128 : C::Q_BYTES);  // decode: GROUP rows of 128 bytes per block
+      for (int a = 0; a < DB; ++a) tma_load_4d(sQ + a * C::Q_BLOCK, &tmQ, q_full, a * 64, 0, kh, seg_row0 + p0);
+      for (int i = 0; i < ST && i < np; ++i) load_page(i);
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 64);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, D) | (1u << 16);  // B operand MN-major
       // Software pipeline: Q K^T of page i + 1 is issued before the wait for the probabilities of page i, into the
@@ -152,40 +160,42 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       bool ok = mbar_wait(q_full, 0, p.err, ERR_WAIT_FULL, abort_flag);
       const uint32_t qa = smem_u32(sQ);
       auto issue_qk = [&](int i) {
-        const int s = i & 1;
-        if (!mbar_wait(&kv_full[s], (i >> 1) & 1, p.err, ERR_WAIT_FULL, abort_flag)) return false;
+        const int s = i % ST;
+        if (!mbar_wait(&kv_full[s], (i / ST) & 1, p.err, ERR_WAIT_FULL, abort_flag)) return false;
         tc_fence_after();
         const uint32_t ka = smem_u32(sK + s * C::KV_BYTES);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t blk = kk >> 2, koff = (kk & 3) * 32;
-          umma_bf16(tmem_S + s * 64, umma_smem_desc(qa + blk * 128 * 128 + koff),
+          umma_bf16(tmem_S + (i & 1) * 64, umma_smem_desc(qa + blk * C::Q_BLOCK + koff),
                     umma_smem_desc(ka + blk * FP_PAGE * 128 + koff), idesc_qk, kk != 0);
         }
-        umma_commit(&s_full[s]);
+        umma_commit(&s_full[i & 1]);
         return true;
       };
       ok = ok && issue_qk(0);
       for (int i = 0; i < np && ok; ++i) {
-        const int s = i & 1;
+        const int s = i % ST;
         if (i + 1 < np) {
           ok = issue_qk(i + 1);  // its score tile was last read by the softmax of page i - 1, which has arrived at p_full
           if (!ok) break;
         }
         ok = mbar_wait(p_full, i & 1, p.err, ERR_WAIT_FULL, abort_flag);
         if (!ok) break;
+        if (i >= 1 && i - 1 + ST < np) {
+          // the stage of page i - 1 is free once its P.V has finished (long ago by now: the softmax of page i ran in
+          // between); refill it, so that ST - 1 pages are loaded or on their way while page i is used
+          ok = mbar_wait(&kv_empty[(i - 1) % ST], ((i - 1) / ST) & 1, p.err, ERR_WAIT_EMPTY, abort_flag);
+          if (!ok) break;
+          load_page(i - 1 + ST);
+        }
         tc_fence_after();
-        const uint32_t pa = smem_u32(sP + s * C::P_BYTES), va = smem_u32(sV + s * C::KV_BYTES);
+        const uint32_t pa = smem_u32(sP + (i & 1) * C::P_BYTES), va = smem_u32(sV + s * C::KV_BYTES);
 #pragma unroll
         for (int kk = 0; kk < FP_PAGE / 16; ++kk)
           umma_bf16(tmem_O, umma_smem_desc(pa + kk * 32), umma_smem_desc_mn(va + kk * 2048, FP_PAGE * 128), idesc_pv,
                     (i | kk) != 0);
         umma_commit(&kv_empty[s]);
-        if (i + 2 < np) {  // the stage of page i is free once its P.V has finished
-          ok = mbar_wait(&kv_empty[s], (i >> 1) & 1, p.err, ERR_WAIT_EMPTY, abort_flag);
-          if (!ok) break;
-          load_page(i + 2);
-        }
       }
       umma_commit(acc_done);
     }
@@ -214,7 +224,9 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const int kbase = (first + i) * FP_PAGE + hf * 32;
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
-        sc[j] = (kbase + j <= qpos) ? sc[j] * p.scale_log2 : -INFINITY;
+        // decode: rows past the real ones hold whatever the MMA read behind the Q atom; masked, so that they never
+        // ask for a rescale of the output tile
+        sc[j] = (kbase + j <= qpos && (!DEC || row_valid)) ? sc[j] * p.scale_log2 : -INFINITY;
         mx = fmaxf(mx, sc[j]);
       }
       s_mx[i & 1][hf][r] = mx;
@@ -227,12 +239,12 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       // probability tile was last read by P.V of page i - 2; the output tile may only be rescaled once P.V of page
       // i - 1 has finished, which is waited for only in the (rare, after the first pages) case of a rescale.
       if (i >= 2) {
-        ok = mbar_wait(&kv_empty[i & 1], ((i - 2) >> 1) & 1, p.err, ERR_WAIT_EMPTY, abort_flag);
+        ok = mbar_wait(&kv_empty[(i - 2) % ST], ((i - 2) / ST) & 1, p.err, ERR_WAIT_EMPTY, abort_flag);
         if (!ok) break;
       }
       const bool any_need = __any_sync(0xffffffffu, need);
       if (any_need && i > 0) {
-        ok = mbar_wait(&kv_empty[(i - 1) & 1], ((i - 1) >> 1) & 1, p.err, ERR_WAIT_EMPTY, abort_flag);
+        ok = mbar_wait(&kv_empty[(i - 1) % ST], ((i - 1) / ST) & 1, p.err, ERR_WAIT_EMPTY, abort_flag);
         if (!ok) break;
         tc_fence_after();
       }
@@ -253,6 +265,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       float sum = 0.f;
       uint8_t* prow = sP + (i & 1) * C::P_BYTES + r * 128;
+      if (!DEC || r < 8)  // decode: the probability tile holds one 8-row atom; the other rows' scores are not kept
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint4 packed;
@@ -356,15 +369,17 @@ int fp_make_map(CUtensorMap* m, const void* base, int rank, const cuuint64_t* di
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
-template <int D, int GROUP>
+template <int D, int GROUP, bool DEC>
 int fp_launch(const CUtensorMap& tq, const CUtensorMap& tkv, const FlashParams& p, int n_tiles, int gz, cudaStream_t st) {
-  auto kern = flash_prefill_kernel<D, GROUP>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashCfg<D>::SMEM) != cudaSuccess) return -3;
-    configured = true;
+  auto kern = flash_prefill_kernel<D, GROUP, DEC>;
+  static bool configured[64] = {};  // a function attribute is set per device
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -3;
+  if (!configured[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashCfg<D, DEC>::SMEM) != cudaSuccess) return -3;
+    configured[dev] = true;
   }
-  return launch_pdl(kern, dim3(n_tiles, p.n_kv, gz), dim3(288), FlashCfg<D>::SMEM, st, tq, tkv, p) == cudaSuccess ? 0 : -4;
+  return launch_pdl(kern, dim3(n_tiles, p.n_kv, gz), dim3(288), FlashCfg<D, DEC>::SMEM, st, tq, tkv, p) == cudaSuccess ? 0 : -4;
 }
 }  // namespace
 
@@ -374,7 +389,9 @@ int fp_launch(const CUtensorMap& tq, const CUtensorMap& tkv, const FlashParams& 
 extern "C" int b200_flash_prefill(const void* q, const void* gate, const void* kv, void* out, const void* tiles,
                                   int n_tiles, const int* seg_pos0, const int* tables, int max_pages, int num_pages,
                                   int T, int n_q, int n_kv, int D, int split_pages, int n_splits, float* part_acc,
-                                  float* part_ml, int* err, cudaStream_t st) {
+                                  float* part_ml, int one_position, int* err, cudaStream_t st) {
+  // one_position != 0: every tile holds a single query position (plain decode): the form with small Q / P tiles
+  // and three K/V stages is used
   if (n_tiles <= 0) return 0;
   const int group = n_q / n_kv;
   if (group * n_kv != n_q || (D != 64 && D != 128 && D != 256) || 128 % group) return -7;
@@ -384,7 +401,7 @@ extern "C" int b200_flash_prefill(const void* q, const void* gate, const void* k
                           static_cast<cuuint64_t>(T)};
     cuuint64_t strides[3] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(group) * D * 2,
                              static_cast<cuuint64_t>(n_q) * D * 2};
-    cuuint32_t box[4] = {64, static_cast<cuuint32_t>(group), 1, static_cast<cuuint32_t>(128 / group)};
+    cuuint32_t box[4] = {64, static_cast<cuuint32_t>(group), 1, static_cast<cuuint32_t>(one_position ? 1 : 128 / group)};
     if (fp_make_map(&tq, q, 4, dims, strides, box)) return -1;
   }
   {
@@ -397,13 +414,20 @@ extern "C" int b200_flash_prefill(const void* q, const void* gate, const void* k
                 static_cast<bf16*>(out), n_q, n_kv, 1.4426950408889634f / sqrtf(static_cast<float>(D)), err,
                 split_pages, part_acc, part_ml};
   const int gz = split_pages > 0 ? n_splits : 1;
-#define FP_GROUPS(DD)                                              \
-  switch (group) {                                                 \
-    case 1: return fp_launch<DD, 1>(tq, tkv, p, n_tiles, gz, st);      \
-    case 2: return fp_launch<DD, 2>(tq, tkv, p, n_tiles, gz, st);      \
-    case 4: return fp_launch<DD, 4>(tq, tkv, p, n_tiles, gz, st);      \
-    case 8: return fp_launch<DD, 8>(tq, tkv, p, n_tiles, gz, st);      \
-    default: return -7;                                            \
+#define FP_GROUPS(DD)                                                         \
+  if (one_position) switch (group) {                                          \
+    case 1: return fp_launch<DD, 1, true>(tq, tkv, p, n_tiles, gz, st);           \
+    case 2: return fp_launch<DD, 2, true>(tq, tkv, p, n_tiles, gz, st);           \
+    case 4: return fp_launch<DD, 4, true>(tq, tkv, p, n_tiles, gz, st);           \
+    case 8: return fp_launch<DD, 8, true>(tq, tkv, p, n_tiles, gz, st);           \
+    default: return -7;                                                       \
+  }                                                                           \
+  switch (group) {                                                            \
+    case 1: return fp_launch<DD, 1, false>(tq, tkv, p, n_tiles, gz, st);          \
+    case 2: return fp_launch<DD, 2, false>(tq, tkv, p, n_tiles, gz, st);          \
+    case 4: return fp_launch<DD, 4, false>(tq, tkv, p, n_tiles, gz, st);          \
+    case 8: return fp_launch<DD, 8, false>(tq, tkv, p, n_tiles, gz, st);          \
+    default: return -7;                                                       \
   }
   if (D == 256) { FP_GROUPS(256) }
   if (D == 128) { FP_GROUPS(128) }

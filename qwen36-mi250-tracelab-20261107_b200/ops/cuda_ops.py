@@ -73,7 +73,7 @@ class _Sig:
     b200_gdn_prefill = [P, I, P, P, P, P, P, P, P, P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, F, I, P, P]
     b200_gdn_prefill_work_stride = [I]
     b200_ring_commit = [P, P, P, P, P, P, I, I, I, I, I, ctypes.c_ulonglong, ctypes.c_ulonglong, P]
-    b200_flash_prefill = [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, P, P, P]
+    b200_flash_prefill = [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P, P, I, P, P]
     b200_attn_combine = [P, P, P, P, I, I, I, I, P]
 
 
@@ -348,6 +348,7 @@ def moe_bt(T: int, pairs_per_row: int, n_experts: int) -> int:
 
 GATHER_MAX_BT = int(__import__("os").environ.get("ENGINE_MOE_GATHER_BT", "32"))  # 0 turns the in-GEMM row gather off
 FUSED_MOE_NORM = True  # Model._moe_norm: combine + residual add + next RMSNorm as one kernel
+ROUTE_PLAN_SPLIT = __import__("os").environ.get("ENGINE_ROUTE_PLAN_SPLIT", "0") == "1"  # routing and plan as two launches
 ROUTE_PLAN_MAX_ROWS = 32  # up to one row per warp of a single CTA, routing and the expert plan run as one launch
 # (measured at 128 rows: 30 us in one CTA against 5 + 3 us as a grid of warps followed by the plan CTA)
 
@@ -386,11 +387,17 @@ def moe_block(x: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_
     src_rows = ints[Et + 2 + 2 * n_pairs :] if gather else None
     max_tiles = min(Et, n_pairs) + n_pairs // bt + 1
     tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device=dev)
-    # routing and plan in one launch: up to 32 rows in a single CTA, more rows as a grid whose last CTA builds the plan
-    _check(L.b200_moe_route_plan(_ptr(logits), logits.stride(0), T, n_experts, top_k, int(shared_merged), _ptr(wts),
-                                 _ptr(idx), _ptr(expert_map), Et, bt, _ptr(offsets), _ptr(tiles), _ptr(n_tiles),
-                                 max_tiles, _ptr(perm), _ptr(inv), _ptr(err), _ptr(src_rows), _ptr(_ticket(dev)), st),
-           "moe_route_plan")
+    if ROUTE_PLAN_SPLIT and T > ROUTE_PLAN_MAX_ROWS:
+        _check(L.b200_moe_route(_ptr(logits), logits.stride(0), T, n_experts, top_k, int(shared_merged), _ptr(wts),
+                                _ptr(idx), None, 0, _ptr(expert_map), st), "moe_route")
+        _check(L.b200_moe_plan(_ptr(idx), n_pairs, Et, bt, _ptr(offsets), _ptr(tiles), _ptr(n_tiles), max_tiles,
+                               _ptr(perm), _ptr(inv), _ptr(err), Pn, _ptr(src_rows), st), "moe_plan")
+    else:
+        # routing and plan in one launch: up to 32 rows in a single CTA, more as a grid whose last CTA builds the plan
+        _check(L.b200_moe_route_plan(_ptr(logits), logits.stride(0), T, n_experts, top_k, int(shared_merged),
+                                     _ptr(wts), _ptr(idx), _ptr(expert_map), Et, bt, _ptr(offsets), _ptr(tiles),
+                                     _ptr(n_tiles), max_tiles, _ptr(perm), _ptr(inv), _ptr(err), _ptr(src_rows),
+                                     _ptr(_ticket(dev)), st), "moe_route_plan")
     act = torch.empty(n_pairs, inter, dtype=x.dtype, device=dev)
     if gather:
         _check(L.b200_gemm_grouped(_ptr(x), _ptr(w_gate_up), _ptr(act), n_pairs, Et, inter, 2 * inter, H, inter,
@@ -581,12 +588,13 @@ def flash_prefill(q: torch.Tensor, gate: torch.Tensor, kv_layer: torch.Tensor, b
     out = torch.empty(T, n_q * D, dtype=q.dtype, device=dev)
     rc = lib().b200_flash_prefill(
         _ptr(q), _ptr(gate), _ptr(kv_layer), _ptr(out), _ptr(tiles_t), n_tiles, _ptr(pos0_t), _ptr(block_tables),
-        block_tables.stride(0), kv_layer.shape[0], T, n_q, n_kv, D, 0, 1, None, None, _ptr(err_word(dev)), _stream(),
+        block_tables.stride(0), kv_layer.shape[0], T, n_q, n_kv, D, 0, 1, None, None, 0, _ptr(err_word(dev)), _stream(),
     )
     _check(rc, "flash_prefill")
     return out
 
 
+DECODE_ATTN_SMALL_TILES = __import__("os").environ.get("ENGINE_ATTN_DECODE_FORM", "1") == "1"  # 8-row Q / P atoms, 3 K/V stages
 SPLIT_PAGES = int(__import__("os").environ.get("ENGINE_ATTN_SPLIT_PAGES", "8"))  # pages (64 tokens each) of context per decode-attention CTA: fixed for a server's lifetime, part of the numerics contract
 _decode_tiles: dict = {}
 
@@ -616,7 +624,7 @@ def flash_decode(q: torch.Tensor, gate: torch.Tensor, kv_layer: torch.Tensor, bl
     rc = L.b200_flash_prefill(
         _ptr(q), _ptr(gate), _ptr(kv_layer), None, _ptr(tiles), B, _ptr(pos0), _ptr(block_tables),
         block_tables.stride(0), kv_layer.shape[0], rows, n_q, n_kv, D, SPLIT_PAGES, n_splits, _ptr(part_acc),
-        _ptr(part_ml), _ptr(err_word(dev)), _stream(),
+        _ptr(part_ml), 1 if (G == 1 and DECODE_ATTN_SMALL_TILES and n_q // n_kv <= 8) else 0, _ptr(err_word(dev)), _stream(),
     )
     _check(rc, "flash_decode")
     _check(L.b200_attn_combine(_ptr(part_acc), _ptr(part_ml), _ptr(gate), _ptr(out), rows, n_q, D, n_splits, _stream()),

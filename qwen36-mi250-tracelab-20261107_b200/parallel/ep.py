@@ -25,7 +25,7 @@ class EpCtx(ctypes.Structure):
         ("xs", ctypes.c_void_p * MAX_RANKS),
         ("meta", ctypes.c_void_p * MAX_RANKS),
         ("pair_out", ctypes.c_void_p * MAX_RANKS),
-        ("cnt", ctypes.c_void_p * MAX_RANKS),
+        ("arrive", ctypes.c_void_p * MAX_RANKS),
         ("flags", ctypes.c_void_p * MAX_RANKS),
         ("epoch", ctypes.c_void_p),
         ("cursors", ctypes.c_void_p),
@@ -44,12 +44,12 @@ def _lib():
     if not getattr(L, "_ep_ready", False):
         P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
         C = ctypes.POINTER(EpCtx)
-        L.b200_ep_send.argtypes = [C, P, P, I, I, I, P]
+        L.b200_ep_route_send.argtypes = [C, P, P, I, I, I, I, I, P, P, P]
         L.b200_ep_plan.argtypes = [C, I, P, P, I, P, P, P, P]
         L.b200_ep_compact.argtypes = [P, P, P, I, I, P, P]
         L.b200_ep_combine.argtypes = [C, P, I, I, I, P, P, P, P, P, F, P]
         L.b200_gemm_grouped_scatter.argtypes = [P, P, I, I, I, I, I, P, P, I, P, P, I, P, I, P]
-        for n in ("b200_ep_send", "b200_ep_plan", "b200_ep_compact", "b200_ep_combine", "b200_gemm_grouped_scatter",
+        for n in ("b200_ep_route_send", "b200_ep_plan", "b200_ep_compact", "b200_ep_combine", "b200_gemm_grouped_scatter",
                   "b200_ep_ctx_size"):
             getattr(L, n).restype = I
         assert L.b200_ep_ctx_size() == ctypes.sizeof(EpCtx), "EpCtx layout mismatch"
@@ -86,7 +86,7 @@ class EpMoE:
             "xs": self.cap_rows * hidden * 2,
             "meta": self.cap_rows * 8,
             "pair_out": self.max_pairs * hidden * 2,
-            "cnt": MAX_RANKS * 4,
+            "arrive": MAX_RANKS * 8,
             "flags": 2 * MAX_RANKS * 4,
             "epoch": 16,
             "cursors": (MAX_RANKS + 1) * 4,
@@ -104,7 +104,7 @@ class EpMoE:
                 self.close()
                 raise RuntimeError(f"expert-parallel set-up failed on some rank: {what}")
 
-        shared = ("xs", "meta", "pair_out", "cnt", "flags")
+        shared = ("xs", "meta", "pair_out", "arrive", "flags")
         with torch.cuda.device(device):
             ok = True
             for name, nbytes in sizes.items():
@@ -192,10 +192,10 @@ class EpMoE:
         logits = cuda_ops.linear(x, router, out_dtype=torch.float32)
         wts = torch.empty(T, Pn, dtype=torch.float32, device=dev)
         idx = torch.empty(T, Pn, dtype=torch.int32, device=dev)
-        rc = K.b200_moe_route(logits.data_ptr(), logits.stride(0), T, E, self.top_k, 1, wts.data_ptr(), idx.data_ptr(),
-                              None, 0, None, st)
         C = ctypes.byref(self.ctx)
-        rc |= L.b200_ep_send(C, x.data_ptr(), idx.data_ptr(), n_pairs, Pn, H, st)
+        # routing and dispatch in one launch: a CTA per row routes it, then sends its pairs to their hosts
+        rc = L.b200_ep_route_send(C, x.data_ptr(), logits.data_ptr(), logits.stride(0), T, self.top_k, Pn, H,
+                                  wts.data_ptr(), idx.data_ptr(), st)
         # token tile of this host's GEMMs from the rows it can expect (its own count times the ranks); a row's bits
         # do not depend on it, so ranks with different batches need not agree
         bt = cuda_ops.moe_bt(max(T, 1) * self.world, Pn, E)
