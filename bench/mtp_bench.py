@@ -1,6 +1,6 @@
 """MTP speculative decoding through the engine: output tok/s, step count and acceptance by draft depth.
 
-    python bench/mtp_bench.py [--batches 1,8,64] [--depths 0,1,2,3] [--prompt-len 4096] [--output-len 256]
+    python bench/mtp_bench.py [--batches 1,8,64] [--depths 0,1,2,3] [--prompt-len 4096] [--output-len 256] [--draft-ivf 4096]
 
 Random-init Qwen3.6-35B-A3B (``--tiny`` for the CPU-sized model), synthetic prompts, greedy, exact output length.
 Depth 0 is plain decoding. With random weights the draft head agrees with the model only by chance, so the
@@ -36,6 +36,8 @@ def main() -> None:
     ap.add_argument("--prompt-len", type=int, default=4096)
     ap.add_argument("--output-len", type=int, default=256)
     ap.add_argument("--tiny", action="store_true")
+    ap.add_argument("--draft-ivf", type=int, default=0,
+                    help="clusters of the vocabulary shortlist index for draft picks (0: drafts read the whole LM head)")
     a = ap.parse_args()
     cuda = torch.cuda.is_available()
     dev = torch.device("cuda" if cuda else "cpu")
@@ -45,7 +47,7 @@ def main() -> None:
     g = torch.Generator().manual_seed(0)
     for depth in [int(x) for x in a.depths.split(",")]:
         ecfg = EngineConfig(max_model_len=a.prompt_len + a.output_len + 64, max_seqs=max(batches), mtp=depth > 0,
-                            spec_k=depth, spec_kmax=max(depth, 1), prefix_cache_entries=0)
+                            spec_k=depth, spec_kmax=max(depth, 1), prefix_cache_entries=0, draft_ivf=a.draft_ivf)
         eng = Engine(w, ecfg)
         for B in batches:
             prompts = [torch.randint(3, cfg.vocab_size, (a.prompt_len,), generator=g).tolist() for _ in range(B)]

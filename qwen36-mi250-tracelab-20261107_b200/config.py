@@ -259,6 +259,10 @@ class EngineConfig:
     mtp: bool = True
     spec_k: int = 0  # 0: policy picks; >0: fixed draft depth
     spec_kmax: int = 3  # deepest draft chain the policy may choose (up to 7, as the reference's k in {1,3,4,5,7})
+    # draft tokens from a vocabulary shortlist (spec/ivf.py) instead of the full LM head: 0 = off, else the number of
+    # clusters of the index built at load; draft_ivf_probes clusters are scored exactly per draft
+    draft_ivf: int = 0
+    draft_ivf_probes: int = 64
     # observability
     loop_timers: bool = False
     req_stamps: bool = False
@@ -281,6 +285,8 @@ class EngineConfig:
             "mtp": "ENGINE_MTP",
             "spec_k": "ENGINE_SPEC_K",
             "spec_kmax": "ENGINE_SPEC_KMAX",
+            "draft_ivf": "ENGINE_DRAFT_IVF",
+            "draft_ivf_probes": "ENGINE_DRAFT_IVF_PROBES",
             "loop_timers": "ENGINE_LOOP_TIMERS",
             "req_stamps": "ENGINE_REQ_STAMPS",
             "device": "ENGINE_DEVICE",

@@ -81,6 +81,7 @@ class Model:
         self.tp = tp
         self.ep = ep
         self.pp = pp
+        self.draft_index = None  # spec.ivf.IvfIndex: draft picks from a vocabulary shortlist instead of the full head
         self.w = weights
         self.cfg: ModelConfig = weights.config
         self.ops = ops or torch_ops
@@ -346,6 +347,13 @@ class Model:
             out.copy_(picks)
             return out
         return picks
+
+    def draft_pick(self, hidden: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Draft token of each row of the MTP block's output: the full greedy head, or the best token of a
+        vocabulary shortlist when a draft index is attached (only a guess is needed: the verify pass decides)."""
+        if self.draft_index is None or self.tp is not None:
+            return self.greedy(hidden, out=out)
+        return self.draft_index.pick(self.ops, hidden, self.w.lm_head, out=out)
 
     def mtp_forward(self, hidden: torch.Tensor, next_tokens: torch.Tensor, batch: PackedBatch) -> torch.Tensor:
         """The MTP block over packed rows: row ``t`` pairs base hidden ``H[t]`` with token ``x[t+1]``.

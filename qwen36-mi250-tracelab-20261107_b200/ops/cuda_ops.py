@@ -57,6 +57,7 @@ class _Sig:
     b200_gemm_dense = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, P, I, I, P]
     b200_gemm_grouped = [P, P, P, I, I, I, I, I, I, I, I, I, P, P, I, P, I, I, P, I, P]
     b200_argmax_finish = [P, P, I, I, P, P, P]
+    b200_ivf_pick = [P, I, P, I, I, I, P, I, P, P, I, I, P, P, I, P, P]
     b200_embed = [P, P, P, I, I, I, P]
     b200_add_rmsnorm = [P, P, P, P, P, I, I, F, I, P]
     b200_moe_route = [P, I, I, I, I, I, P, P, P, I, P, P]
@@ -282,6 +283,27 @@ def lm_head_argmax(x: torch.Tensor, w: torch.Tensor, return_value: bool = False,
     _check(rc, "gemm_dense(argmax)")
     _check(lib().b200_argmax_finish(_ptr(pmax), _ptr(pidx), n_tiles, T, _ptr(out), _ptr(val), _stream()), "argmax_finish")
     return (out, val) if return_value else out
+
+
+def ivf_pick(hidden: torch.Tensor, lm_head: torch.Tensor, probes: torch.Tensor, offsets: torch.Tensor,
+             order: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Best LM-head row of every row of ``hidden`` among the members of its probed clusters (``spec/ivf.py``):
+    gathered GEMV over the plain or tile-packed head, then the argmax reduce of the LM head."""
+    R, H = hidden.shape
+    P = probes.shape[1]
+    dev = hidden.device
+    assert probes.dtype == torch.int32 and probes.is_contiguous() and hidden.stride(1) == 1
+    pmax = torch.empty(P, R, dtype=torch.float32, device=dev)
+    pidx = torch.empty(P, R, dtype=torch.int32, device=dev)
+    if out is None:
+        out = torch.empty(R, dtype=torch.int64, device=dev)
+    assert out.dtype == torch.int64 and out.is_contiguous() and out.numel() == R
+    rc = lib().b200_ivf_pick(_ptr(hidden), hidden.stride(0), _ptr(lm_head), lm_head.stride(0), is_packed(lm_head), H,
+                             _ptr(probes), P, _ptr(offsets), _ptr(order), offsets.numel() - 1, order.numel(),
+                             _ptr(pmax), _ptr(pidx), R, _ptr(err_word(dev)), _stream())
+    _check(rc, "ivf_pick")
+    _check(lib().b200_argmax_finish(_ptr(pmax), _ptr(pidx), P, R, _ptr(out), None, _stream()), "argmax_finish")
+    return out
 
 
 # --------------------------------------------------------------------------- norms

@@ -67,11 +67,18 @@ class Engine:
         self.chunk = max(PAGE_SIZE, (c.prefill_chunk_tokens + PAGE_SIZE - 1) // PAGE_SIZE * PAGE_SIZE)
         self.max_model_len = c.max_model_len
         self.max_pages_per_seq = (self.max_model_len + PAGE_SIZE - 1) // PAGE_SIZE + 1
+        draft_index = None
+        if c.draft_ivf and c.mtp and weights.mtp is not None and tp is None and pp is None:
+            from ..spec.ivf import IvfIndex
+
+            # from the plain head, before it is tile-packed; deterministic, so every restart builds the same index
+            draft_index = IvfIndex.build(weights.lm_head, n_clusters=c.draft_ivf, probes=c.draft_ivf_probes)
         if c.pack_weights and tp is None and hasattr(self.ops, "pack_weights"):
             self.ops.pack_weights(weights)  # before the KV pool is sized: padded copies replace a few tensors
         n_slots = c.state_slots or (c.max_seqs * 2 + 2)
         n_pages = c.kv_pages or self._agree_min(self._auto_pages(weights, n_slots), tp if tp is not None else pp)
         self.model = Model(weights, n_pages, n_slots, ops=self.ops, tp=tp, ep=ep, pp=pp)
+        self.model.draft_index = draft_index
         self.pages = PagePool(n_pages)
         self.slots = SlotPool(n_slots)
         page_bytes = self.model.kv[:, 0].numel() * self.model.kv.element_size()

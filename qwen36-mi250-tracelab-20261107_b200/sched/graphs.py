@@ -285,11 +285,11 @@ class _VerifyBucket:
         model.greedy(hidden, out=picks)
         y = model.mtp_forward(hidden, picks, self.batch)
         _acc, h, link_pos = ops.chain_accept(self.tokens, picks, self.n_valid, self.positions, y, G, kmax - 1, acc_out=acc_out)
-        d = model.greedy(h, out=out[dr0 : dr0 + size])
+        d = model.draft_pick(h, out=out[dr0 : dr0 + size])
         for j in range(1, kmax):
             link = PackedBatch(d, link_pos[j - 1], self.seq1, self.slots, self.tables, 1)
             h = model.mtp_forward(h, d, link)
-            d = model.greedy(h, out=out[dr0 + j * size : dr0 + (j + 1) * size])
+            d = model.draft_pick(h, out=out[dr0 + j * size : dr0 + (j + 1) * size])
         return out
 
     def capture(self, engine, pool) -> None:

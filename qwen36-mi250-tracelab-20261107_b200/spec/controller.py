@@ -163,7 +163,7 @@ class SpecController:
         if last_gens:
             rows = torch.tensor(last_rows, device=eng.device)
             h = y[rows]
-            d = eng.model.greedy(h)
+            d = eng.model.draft_pick(h)
             drafts = [d]
             pos = torch.tensor([g.computed for g in last_gens], dtype=torch.int64, device=eng.device)
             self._chain_links(last_gens, h, d, pos, drafts)
@@ -188,7 +188,7 @@ class SpecController:
         for j in range(1, kmax):
             b = PackedBatch(d, pos + (j - 1), seq, slots, tables, 1)
             h = eng.model.mtp_forward(h, d, b)
-            d = eng.model.greedy(h)
+            d = eng.model.draft_pick(h)
             drafts.append(d)
 
     # ------------------------------------------------------------------ the verify step
@@ -263,7 +263,7 @@ class SpecController:
         y = eng.model.mtp_forward(hidden, picks, batch)
         sel = torch.arange(B, device=eng.device) * G + acc
         h = y[sel]
-        d = eng.model.greedy(h)
+        d = eng.model.draft_pick(h)
         drafts = [d]
         base_pos = batch.positions.view(B, G)[:, 0] + acc + 1
         self._chain_links(gens, h, d, base_pos, drafts)

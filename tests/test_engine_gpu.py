@@ -84,6 +84,14 @@ def test_gpu_mtp_speculation_keeps_outputs():
     forced = [g.output for g in eng2.generate(prompts, s)]
     assert forced == plain and eng2.stats["mtp_accepted"] == eng2.stats["mtp_proposed"] > 0
     cuda_ops.check_errors(torch.device("cuda"))
+    # drafts from the vocabulary shortlist (captured in the verify graphs, tile-packed head): same outputs
+    w2 = random_weights(cfg, seed=0, device="cuda", dtype=torch.bfloat16, std=0.05, lm_head_std=0.5)
+    eng3 = Engine(w2, EngineConfig(max_model_len=1024, prefill_chunk_tokens=64, max_seqs=8, mtp=True, spec_k=2, kv_pages=256,
+                                   decode_buckets=(4, 8), draft_ivf=16, draft_ivf_probes=4, pack_weights=True))
+    assert eng3.model.draft_index is not None
+    short = [g.output for g in eng3.generate(prompts, s)]
+    assert short == plain and eng3.stats["mtp_verify_steps"] > 0
+    cuda_ops.check_errors(torch.device("cuda"))
 
 
 def test_gpu_engine_with_tile_packed_weights_keeps_tokens():

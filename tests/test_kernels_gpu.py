@@ -451,3 +451,29 @@ def test_chain_accept_kernel_matches_the_tensor_formulation(C, B, G, kmax):
     base = positions.view(B, G)[:, 0] + want + 1
     for j in range(kmax - 1):
         assert torch.equal(link_pos[j], base + j)
+
+
+@pytest.mark.parametrize("packed", [False, True])
+def test_ivf_pick_kernel_scores_the_probed_clusters_exactly(C, packed):
+    """The gathered GEMV of the shortlist draft against plain PyTorch on the same candidates, plain and tile-packed head."""
+    from b200serve.spec.ivf import IvfIndex
+
+    V, H, R = 20000, 2048, 9
+    head = _bf(V, H, scale=0.05, seed=51)
+    idx = IvfIndex.build(head, n_clusters=128, probes=8)
+    h = _bf(R, H, seed=52)
+    scores = C.linear(h, idx.centroids, out_dtype=torch.float32)[:, :128]
+    probes = torch.topk(scores, 8, dim=-1).indices.to(torch.int32)
+    want = idx.pick_reference(h, head, probes)
+    w = C.pack_weight(head.clone()) if packed else head
+    got = C.ivf_pick(h, w, probes, idx.offsets, idx.order)
+    # equal scores up to the accumulation order: the picked rows must score within rounding of the reference's
+    ref_logit = (head[want].float() * h.float()).sum(-1)
+    got_logit = (head[got].float() * h.float()).sum(-1)
+    assert torch.allclose(got_logit, ref_logit, rtol=1e-3, atol=1e-3)
+    assert (got == want).float().mean() >= 0.8
+    # through the index object (centroid GEMM, top-k, kernel): the same picks
+    assert torch.equal(idx.pick(C, h, w), got)
+    out = torch.empty(R, dtype=torch.int64, device="cuda")
+    assert idx.pick(C, h, w, out=out) is out and torch.equal(out, got)
+    C.check_errors(h.device)

@@ -150,3 +150,46 @@ def test_depth_policy_reads_a_measured_cost_table_and_extends_it_to_deeper_chain
     q.load_table(custom)
     q.accept = [0.8, 0.8]
     assert q.choose(2, 2) == 2
+
+
+def test_shortlist_index_is_deterministic_and_exact_when_every_cluster_is_probed():
+    from b200serve.ops import torch_ops
+    from b200serve.spec.ivf import IvfIndex
+
+    g = torch.Generator().manual_seed(4)
+    head = torch.randn(1000, 64, generator=g)
+    a = IvfIndex.build(head, n_clusters=32, probes=32)
+    b = IvfIndex.build(head, n_clusters=32, probes=32)
+    assert torch.equal(a.order, b.order) and torch.equal(a.offsets, b.offsets) and torch.equal(a.centroids, b.centroids)
+    # a partition of the vocabulary
+    assert sorted(a.order.tolist()) == list(range(1000)) and int(a.offsets[-1]) == 1000
+    h = torch.randn(9, 64, generator=g)
+    full = (h @ head.t()).argmax(-1)
+    assert torch.equal(a.pick(torch_ops, h, head), full)  # all clusters probed: the shortlist is the vocabulary
+    # a few probes: the pick is the best member of the probed clusters, and it is the full argmax whenever the
+    # argmax row's cluster was probed
+    few = IvfIndex(a.centroids, a.order, a.offsets, probes=4)
+    picks = few.pick(torch_ops, h, head)
+    scores = h @ a.centroids.float().t()
+    probed = scores.topk(4, dim=-1).indices
+    cluster_of = torch.empty(1000, dtype=torch.long)
+    off = a.offsets.tolist()
+    for c in range(32):
+        cluster_of[a.order[off[c]:off[c + 1]].long()] = c
+    for r in range(9):
+        members = torch.cat([a.order[off[c]:off[c + 1]] for c in probed[r].tolist()]).long()
+        assert int(picks[r]) in members.tolist()
+        assert float(h[r] @ head[picks[r]]) == pytest.approx(float((head[members] @ h[r]).max()))
+        if int(cluster_of[full[r]]) in probed[r].tolist():
+            assert int(picks[r]) == int(full[r])
+
+
+def test_shortlist_drafts_never_change_outputs(weights, plain):
+    """Drafts from the vocabulary shortlist are only guesses: served outputs stay those of plain decoding."""
+    prompts, outs = plain
+    eng = Engine(weights, EngineConfig(max_model_len=1024, prefill_chunk_tokens=64, max_seqs=8, mtp=True, spec_k=2,
+                                       spec_kmax=3, draft_ivf=16, draft_ivf_probes=4))
+    assert eng.model.draft_index is not None and eng.model.draft_index.n_clusters == 16
+    got = [g.output for g in eng.generate(prompts, Sampling(max_tokens=20, ignore_eos=True))]
+    assert got == outs
+    assert eng.stats["mtp_verify_steps"] > 0 and eng.stats["mtp_proposed"] > 0
