@@ -193,6 +193,15 @@ class Model:
         if self.ep is not None:  # the combine kernel of the expert-parallel block carries the residual add and the norm
             return self.ep.forward(h, lw.router, lw.w_gate_up, lw.w_down, residual=res, norm_w=norm_w,
                                    eps=cfg.rms_norm_eps)
+        if self.tp is not None and hasattr(self.tp.comm, "allreduce_norm"):
+            # tensor + expert parallel: the partial sums of the local experts meet in an all-reduce whose kernel also
+            # adds the residual and applies the next norm (one launch instead of three)
+            part = ops.moe_block(h, lw.router, lw.w_gate_up, lw.w_down, cfg.num_experts, cfg.num_experts_per_tok,
+                                 True, expert_map=lw.expert_map, partial_f32=True)
+            fused = self.tp.comm.allreduce_norm(part, res, norm_w, cfg.rms_norm_eps)
+            if fused is not None:
+                return fused
+            return ops.add_rmsnorm(self.tp.comm.allreduce(part, None, h.dtype), res, norm_w, cfg.rms_norm_eps)
         if self.tp is None and lw.shared_merged and getattr(ops, "FUSED_MOE_NORM", False):
             return ops.moe_block(h, lw.router, lw.w_gate_up, lw.w_down, cfg.num_experts, cfg.num_experts_per_tok, True,
                                  residual=res, norm_w=norm_w, eps=cfg.rms_norm_eps)

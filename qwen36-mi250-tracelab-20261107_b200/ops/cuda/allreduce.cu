@@ -21,9 +21,16 @@ __device__ __forceinline__ float to_f<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ float to_f<bf16>(bf16 v) { return __bfloat162float(v); }
 
+// With `norm_w` (rows of H elements, H dividing the block's 4096 elements, so a block owns whole rows) the kernel also
+// applies the zero-centred RMSNorm that follows the residual add: y = norm(out) * (1 + norm_w), with the rounding
+// points of add_rmsnorm_kernel (the sum is rounded to bf16, the residual added, rounded again; the norm reads those
+// bf16 values). One launch replaces all-reduce + add + norm (reference: engine/fast/tp.py:220-257).
 template <typename TIn>
 __global__ void __launch_bounds__(AR_THREADS)
-allreduce_push_kernel(CommCtx c, const TIn* in, const bf16* residual, bf16* out, float* out_f32, size_t n) {
+allreduce_push_kernel(CommCtx c, const TIn* in, const bf16* residual, bf16* out, float* out_f32, size_t n,
+                      const bf16* norm_w, bf16* y, int H, float eps) {
+  __shared__ float s_row[AR_ELEMS];   // norm: the block's new residual rows as the bf16 values just stored
+  __shared__ float s_ss[AR_ELEMS / 64];
   const int blk = blockIdx.x;
   const size_t base = static_cast<size_t>(blk) * AR_ELEMS;
   __shared__ uint32_t s_epoch;
@@ -72,9 +79,30 @@ allreduce_push_kernel(CommCtx c, const TIn* in, const bf16* residual, bf16* out,
       if (out_f32) out_f32[g + k] = v;
       if (out) {
         if (residual) v = __bfloat162float(__float2bfloat16(v)) + __bfloat162float(residual[g + k]);
-        out[g + k] = __float2bfloat16(v);
+        const bf16 o = __float2bfloat16(v);
+        out[g + k] = o;
+        if (norm_w) s_row[i + k] = __bfloat162float(o);
       }
     }
+  }
+  if (norm_w == nullptr) return;
+  __syncthreads();
+  // rows of this block: r = 0 .. AR_ELEMS / H - 1; one warp per row at a time
+  const int rows_here = AR_ELEMS / H;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int r = warp; r < rows_here; r += AR_THREADS / 32) {
+    if (base + static_cast<size_t>(r) * H >= n) break;
+    float ss = 0.f;
+    for (int i = lane; i < H; i += 32) { const float f = s_row[r * H + i]; ss += f * f; }
+    ss = warp_sum(ss);
+    if (lane == 0) s_ss[r] = rsqrtf(ss / H + eps);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < AR_ELEMS; i += AR_THREADS) {
+    const size_t g = base + i;
+    if (g >= n) break;
+    const int r = i / H, col = i - r * H;
+    y[g] = __float2bfloat16(s_row[i] * s_ss[r] * (1.0f + __bfloat162float(norm_w[col])));
   }
 }
 
@@ -93,11 +121,32 @@ extern "C" int b200_allreduce_push(const CommCtx* ctx, const void* in, int in_is
   if (in_is_f32)
     allreduce_push_kernel<float><<<blocks, AR_THREADS, 0, st>>>(*ctx, static_cast<const float*>(in),
                                                                static_cast<const bf16*>(residual),
-                                                               static_cast<bf16*>(out), out_f32, n);
+                                                               static_cast<bf16*>(out), out_f32, n, nullptr, nullptr, 0, 0.f);
   else
     allreduce_push_kernel<bf16><<<blocks, AR_THREADS, 0, st>>>(*ctx, static_cast<const bf16*>(in),
                                                               static_cast<const bf16*>(residual),
-                                                              static_cast<bf16*>(out), out_f32, n);
+                                                              static_cast<bf16*>(out), out_f32, n, nullptr, nullptr, 0, 0.f);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// All-reduce of rows [T, H] + residual add + the RMSNorm that follows, in one launch: out = bf16(bf16(sum) + residual)
+// (residual optional), y = norm(out) * (1 + norm_w). H must divide 4096 (a block of the all-reduce owns whole rows).
+extern "C" int b200_allreduce_push_norm(const CommCtx* ctx, const void* in, int in_is_f32, const void* residual,
+                                        void* out, const void* norm_w, void* y, int T, int H, float eps,
+                                        cudaStream_t st) {
+  const unsigned long long n = static_cast<unsigned long long>(T) * H;
+  if (n == 0) return 0;
+  if (H < 64 || AR_ELEMS % H || n > ctx->slot_elems) return -7;
+  const int blocks = static_cast<int>((n + AR_ELEMS - 1) / AR_ELEMS);
+  if (blocks > ctx->max_blocks) return -7;
+  if (in_is_f32)
+    allreduce_push_kernel<float><<<blocks, AR_THREADS, 0, st>>>(
+        *ctx, static_cast<const float*>(in), static_cast<const bf16*>(residual), static_cast<bf16*>(out), nullptr, n,
+        static_cast<const bf16*>(norm_w), static_cast<bf16*>(y), H, eps);
+  else
+    allreduce_push_kernel<bf16><<<blocks, AR_THREADS, 0, st>>>(
+        *ctx, static_cast<const bf16*>(in), static_cast<const bf16*>(residual), static_cast<bf16*>(out), nullptr, n,
+        static_cast<const bf16*>(norm_w), static_cast<bf16*>(y), H, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -138,6 +138,31 @@ class SymmComm:
             raise cuda_ops.KernelError(f"allreduce_push failed with code {rc}")
         return out
 
+    def allreduce_norm(self, partial: torch.Tensor, residual: torch.Tensor | None, norm_w: torch.Tensor, eps: float):
+        """Sum rows ``partial [T, H]`` over the group, add ``residual`` and apply the zero-centred RMSNorm that follows,
+        all in the all-reduce kernel; returns ``(new residual, normed)`` with the bits of the separate kernels."""
+        assert partial.is_contiguous() and partial.dim() == 2
+        T, H = partial.shape
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=partial.device)
+        y = torch.empty_like(out)
+        L = _lib()
+        if not getattr(L, "_arn_ready", False):
+            P, I = ctypes.c_void_p, ctypes.c_int
+            L.b200_allreduce_push_norm.argtypes = [P, P, I, P, P, P, P, I, I, ctypes.c_float, P]
+            L.b200_allreduce_push_norm.restype = I
+            L._arn_ready = True
+        rc = L.b200_allreduce_push_norm(
+            ctypes.byref(self.ctx), partial.data_ptr(), int(partial.dtype == torch.float32),
+            None if residual is None else residual.data_ptr(), out.data_ptr(), norm_w.data_ptr(), y.data_ptr(), T, H, eps,
+            torch.cuda.current_stream().cuda_stream,
+        )
+        if rc:
+            raise cuda_ops.KernelError(f"allreduce_push_norm failed with code {rc}")
+        return out, y
+
+    def norm_fits(self, T: int, H: int) -> bool:
+        return H >= 64 and AR_ELEMS % H == 0 and self.fits(T * H)
+
     def close(self) -> None:
         L = _lib()
         torch.cuda.synchronize(self.device)

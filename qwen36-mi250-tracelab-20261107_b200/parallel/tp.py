@@ -91,6 +91,13 @@ class FusedComm(DistComm):
             return self.symm.allreduce(partial.contiguous(), residual)
         return super().allreduce(partial, residual, out_dtype)
 
+    def allreduce_norm(self, partial, residual, norm_w, eps):
+        """All-reduce + residual add + the next RMSNorm in one kernel when the rows fit a block of the push
+        all-reduce; ``None`` otherwise (the caller then runs the separate ops)."""
+        if partial.is_cuda and partial.dim() == 2 and self.symm.norm_fits(*partial.shape) and norm_w.dtype == torch.bfloat16:
+            return self.symm.allreduce_norm(partial.contiguous(), residual, norm_w, eps)
+        return None
+
     def argmax(self, val: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
         """Cross-rank greedy pick without a library collective (so that it can live inside a CUDA graph):
         every rank fills its own row of a ``[world, T, 2]`` fp32 table (value, index; indices below 2^24

@@ -28,6 +28,31 @@ def test_loopback_allreduce_adds_residual():
     comm.close()
 
 
+@pytest.mark.parametrize("T,H", [(33, 2048), (5, 128), (128, 2048), (3, 4096)])
+def test_loopback_allreduce_with_residual_and_norm_matches_the_separate_kernels(T, H):
+    """All-reduce + residual + next RMSNorm in one launch against all-reduce, then the add + norm kernel."""
+    from b200serve.ops import cuda_ops
+    from b200serve.parallel.symm import SymmComm
+
+    dev = torch.device("cuda")
+    comm = SymmComm(dev, None, slot_elems=1 << 20, max_blocks=256)
+    assert comm.norm_fits(T, H)
+    for rep in range(3):
+        part = torch.randn(T, H, device=dev)  # fp32 partial, as the expert-parallel MoE block produces
+        res = torch.randn(T, H, device=dev).to(torch.bfloat16)
+        w = (torch.randn(H, device=dev) * 0.1).to(torch.bfloat16)
+        want_res, want_y = cuda_ops.add_rmsnorm(comm.allreduce(part), res, w, 1e-6)
+        got_res, got_y = comm.allreduce_norm(part, res, w, 1e-6)
+        assert torch.equal(got_res, want_res)
+        # the sum of squares is added in another order: at most one bf16 step apart
+        assert torch.allclose(got_y.float(), want_y.float(), rtol=1e-2, atol=1e-3)
+        want_res, want_y = cuda_ops.add_rmsnorm(comm.allreduce(part), None, w, 1e-6)
+        got_res, got_y = comm.allreduce_norm(part, None, w, 1e-6)
+        assert torch.equal(got_res, want_res) and torch.allclose(got_y.float(), want_y.float(), rtol=1e-2, atol=1e-3)
+    cuda_ops.check_errors(dev)
+    comm.close()
+
+
 def test_absent_peer_times_out_with_a_status_and_leaves_the_context_usable():
     """A two-rank context whose second rank never runs: the bounded wait gives up after about a
     second, the kernel records ERR_WAIT_PEER and returns, and later launches still work."""
