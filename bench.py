@@ -356,8 +356,12 @@ def main() -> None:
                                      Sampling(max_tokens=total_out, ignore_eos=True)))
             for _ in range(B)
         ]
+        t_limit = time.perf_counter() + 600.0
         while engine.prefilling or engine.waiting or not engine._inbox.empty():
             engine.step()  # prefill passes (each also advances already-running requests by one token)
+            if engine.stats["device_errors"] or engine.broken or time.perf_counter() > t_limit:
+                raise RuntimeError(f"prefill phase did not complete: device_errors={engine.stats['device_errors']}, "
+                                   f"broken={engine.broken}")
         if not e2e:  # the device-resident loop runs ahead of the host: give every request its pages now
             for x in gens:
                 engine._ensure_pages(x, x.computed + timed_steps + 2)
@@ -430,8 +434,11 @@ def main() -> None:
         gens = [engine.submit(Generation(torch.randint(0, mcfg.vocab_size, (S_PROMPT,), generator=g).tolist(),
                                          Sampling(max_tokens=S_OUT, ignore_eos=True), on_event=on_event))
                 for _ in range(n_serv)]
+        t_limit = time.perf_counter() + 900.0
         while any(not x.done for x in gens):
             engine.step()
+            if engine.broken or time.perf_counter() > t_limit:
+                raise RuntimeError(f"serving workload did not complete: broken={engine.broken}")
         engine.flush_events()
         torch.cuda.synchronize()
         wall = time.perf_counter() - t0

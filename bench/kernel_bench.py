@@ -278,6 +278,22 @@ def case_ep_loopback(small):
     ep.close()
 
 
+def case_draft_ivf(small):
+    """Shortlist draft pick (centroid GEMM, top-k, gathered GEMV, reduce) beside the full LM head with fused argmax,
+    8 rows, 64 of 4096 clusters probed."""
+    from b200serve.spec.ivf import IvfIndex
+
+    V, H, R = (65536 if small else 248320), 2048, 8
+    head = bf(V, H, scale=0.02)
+    idx = IvfIndex.build(head, n_clusters=1024 if small else 4096, probes=64, iters=2)
+    w = pk(head)
+    x = bf(R, H)
+    report(f"lm_head_argmax_b{R}", timed(lambda: C.lm_head_argmax(x, w)), V * H * 2, 2 * R * V * H)
+    cand = int((idx.offsets[1:] - idx.offsets[:-1]).float().mean().item() * 64)
+    report(f"draft_ivf_pick_b{R}", timed(lambda: idx.pick(C, x, w)), (idx.centroids.numel() + R * cand * H) * 2,
+           2 * R * (idx.n_clusters + cand) * H, clusters=idx.n_clusters, probes=64, candidates_per_row=cand)
+
+
 CASES = {k[5:]: v for k, v in globals().items() if k.startswith("case_")}
 
 if __name__ == "__main__":

@@ -174,21 +174,26 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         return true;
       };
       ok = ok && issue_qk(0);
+      // The stage of page i - 1 is free once its P.V has finished; it takes page i - 1 + ST. With two stages that is
+      // page i + 1, which Q K^T needs in this very iteration, so the refill comes first (and waits for the P.V just
+      // issued). With three stages page i + 1 is already there and the refill waits until the softmax of page i has
+      // run, by when P.V of page i - 1 is long done: two pages are loaded or on their way while page i is used.
+      auto refill = [&](int i) {
+        if (i < 1 || i - 1 + ST >= np) return true;
+        if (!mbar_wait(&kv_empty[(i - 1) % ST], ((i - 1) / ST) & 1, p.err, ERR_WAIT_EMPTY, abort_flag)) return false;
+        load_page(i - 1 + ST);
+        return true;
+      };
       for (int i = 0; i < np && ok; ++i) {
         const int s = i % ST;
+        if (ST == 2) { ok = refill(i); if (!ok) break; }
         if (i + 1 < np) {
           ok = issue_qk(i + 1);  // its score tile was last read by the softmax of page i - 1, which has arrived at p_full
           if (!ok) break;
         }
         ok = mbar_wait(p_full, i & 1, p.err, ERR_WAIT_FULL, abort_flag);
         if (!ok) break;
-        if (i >= 1 && i - 1 + ST < np) {
-          // the stage of page i - 1 is free once its P.V has finished (long ago by now: the softmax of page i ran in
-          // between); refill it, so that ST - 1 pages are loaded or on their way while page i is used
-          ok = mbar_wait(&kv_empty[(i - 1) % ST], ((i - 1) / ST) & 1, p.err, ERR_WAIT_EMPTY, abort_flag);
-          if (!ok) break;
-          load_page(i - 1 + ST);
-        }
+        if (ST > 2) { ok = refill(i); if (!ok) break; }
         tc_fence_after();
         const uint32_t pa = smem_u32(sP + (i & 1) * C::P_BYTES), va = smem_u32(sV + s * C::KV_BYTES);
 #pragma unroll

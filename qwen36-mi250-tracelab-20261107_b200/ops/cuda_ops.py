@@ -359,8 +359,13 @@ def embed(tokens: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 
 
 # --------------------------------------------------------------------------- MoE
+_MOE_BT_FIXED = int(__import__("os").environ.get("ENGINE_MOE_BT", "0"))
+
+
 def moe_bt(T: int, pairs_per_row: int, n_experts: int) -> int:
-    """Token-tile width of the grouped GEMMs from the expected rows per routed expert."""
+    """Token-tile width of the grouped GEMMs from the expected rows per routed expert (``ENGINE_MOE_BT`` fixes it)."""
+    if _MOE_BT_FIXED:
+        return _MOE_BT_FIXED
     per = T * max(1, pairs_per_row - 1) / max(1, n_experts)
     for bt in (16, 32, 64, 128):
         if per <= bt:
