@@ -6,7 +6,7 @@
 #   bench/run_serving_configs.sh trace       # replay of bench/sample_trace.csv with 8 session slots
 #   bench/run_serving_configs.sh long        # one 131072-token prompt prefilled in 8192-token chunks (TTFT)
 #
-# Extra server flags go in SERVER_FLAGS (e.g. "--gpus-per-replica 2"); results are appended as JSON lines to
+# MODEL / VOCAB name another model (random:tiny with VOCAB=1000 runs on CPU). Extra server flags go in SERVER_FLAGS (e.g. "--gpus-per-replica 2"); results are appended as JSON lines to
 # ${OUT:-serve_results.jsonl}. Greedy, ignore_eos, exact output lengths; timing is taken on the client.
 set -u
 MODE=${1:-decode}
@@ -21,14 +21,14 @@ case $MODE in
 esac
 # the server runs in its own process group (front, replicas, follower ranks), which is ended as a whole at exit;
 # every client run and the wait for /health are bounded, so the script always ends by itself
-ENGINE_MTP=${ENGINE_MTP:-0} setsid python "$ROOT/main.py" --model random:qwen36 --served-model-name q --port "$PORT" \
+ENGINE_MTP=${ENGINE_MTP:-0} setsid python "$ROOT/main.py" --model ${MODEL:-random:qwen36} --served-model-name q --port "$PORT" \
   --max-model-len $LEN --prefill-chunk-tokens $CHUNK --max-seqs $SEQS ${SERVER_FLAGS:-} > "${OUT%.jsonl}.server.log" 2>&1 &
 SERVER=$!
 trap 'kill -- -$SERVER 2>/dev/null; sleep 2; kill -9 -- -$SERVER 2>/dev/null; wait $SERVER 2>/dev/null' EXIT
 UP=0
 for _ in $(seq 1 ${HEALTH_WAIT:-600}); do curl -s -m 2 -o /dev/null "$URL/health" && UP=1 && break; sleep 1; done
 if [ $UP = 0 ]; then echo "server did not come up" >> "$OUT"; tail -5 "${OUT%.jsonl}.server.log" >> "$OUT"; cat "$OUT"; exit 1; fi
-B="timeout ${CLIENT_TIMEOUT:-900} python $ROOT/bench/serve_bench.py --url $URL --model q"
+B="timeout ${CLIENT_TIMEOUT:-900} python $ROOT/bench/serve_bench.py --url $URL --model q --vocab ${VOCAB:-248320}"
 run() { echo "{\"config\": \"$1\"}" >> "$OUT"; shift; "$@" >> "$OUT" 2>&1; }
 case $MODE in
   decode)

@@ -78,7 +78,12 @@ def start_followers(model_dir: str, world: int, port: int, cuda: bool, cfg_args:
     for r in range(1, world):
         cmd = [sys.executable, "-m", "b200serve.parallel.replica", "--model", model_dir, "--rank", str(r), "--world",
                str(world), "--port", str(port), "--device", "cuda" if cuda else "cpu", "--split", split, *cfg_args]
-        procs.append(subprocess.Popen(cmd, env=dict(os.environ)))
+        env = dict(os.environ)
+        import b200serve
+
+        root = os.path.dirname(os.path.dirname(os.path.abspath(b200serve.__file__)))
+        env["PYTHONPATH"] = root + (os.pathsep + env["PYTHONPATH"] if env.get("PYTHONPATH") else "")
+        procs.append(subprocess.Popen(cmd, env=env))
     return procs
 
 

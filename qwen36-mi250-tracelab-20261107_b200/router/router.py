@@ -231,6 +231,11 @@ def start_replicas(argv: list[str], layout: list[list[int]], pin: bool = True) -
             env.update(cpu_place.thread_caps(len(cpus)))
             env["ENGINE_CPUS"] = cpu_place.format_cpu_list(cpus)
             env["ENGINE_RANK_CPUS"] = cpu_place.format_cpu_list(slices[i].rank_cpus)
+        # the children import the package by name whatever directory the front was started from
+        import b200serve
+
+        root = os.path.dirname(os.path.dirname(os.path.abspath(b200serve.__file__)))
+        env["PYTHONPATH"] = root + (os.pathsep + env["PYTHONPATH"] if env.get("PYTHONPATH") else "")
         cmd = [sys.executable, "-m", "b200serve.api.server", *base, "--host", "127.0.0.1", "--port", str(port),
                "--replicas", "1"]
         proc = subprocess.Popen(cmd, env=env, preexec_fn=_child_preexec(cpus))
