@@ -45,8 +45,15 @@ class EngineWorker(threading.Thread):
 
     def run(self) -> None:
         eng = self.engine
+        # ENGINE_STALL_DUMP_S = N: when one iteration of the loop takes longer than N seconds, the stacks of all threads
+        # are written to stderr (once per stall), so that a wedged replica shows where it waits
+        stall = float(os.environ.get("ENGINE_STALL_DUMP_S", "0") or 0)
+        if stall > 0:
+            import faulthandler
         while not self.stopping:
             try:
+                if stall > 0:
+                    faulthandler.dump_traceback_later(stall, repeat=False, exit=False)
                 looptimers.begin()
                 busy = eng.step()
                 looptimers.end(len(eng.running))

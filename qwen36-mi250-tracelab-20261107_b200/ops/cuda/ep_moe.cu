@@ -215,11 +215,14 @@ ep_plan_kernel(EpCtx c, int bt, int4* tiles, int* n_tiles, int max_tiles, int* g
 __global__ void ep_compact_kernel(const bf16* xs, const int* rows, const int* n_valid, int H, bf16* sorted) {
   pdl_wait();
   pdl_launch();
-  const int pos = blockIdx.x;
-  if (pos >= *n_valid) return;
-  const uint4* src = reinterpret_cast<const uint4*>(xs + static_cast<size_t>(rows[pos]) * H);
-  uint4* dst = reinterpret_cast<uint4*>(sorted + static_cast<size_t>(pos) * H);
-  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+  // grid-stride over the rows that arrived: their number is known on the device only and may be far above what this
+  // rank sent itself (a peer with a long prefill pass), so the grid is sized for the machine, not for a row count
+  const int n = *n_valid;
+  for (int pos = blockIdx.x; pos < n; pos += gridDim.x) {
+    const uint4* src = reinterpret_cast<const uint4*>(xs + static_cast<size_t>(rows[pos]) * H);
+    uint4* dst = reinterpret_cast<uint4*>(sorted + static_cast<size_t>(pos) * H);
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+  }
 }
 
 // Release "my expert outputs are out" towards every rank, wait for every host's release, then
@@ -319,8 +322,8 @@ extern "C" int b200_ep_plan(const EpCtx* c, int bt, void* tiles, int* n_tiles, i
 extern "C" int b200_ep_compact(const void* xs, const int* rows, const int* n_valid, int max_rows, int H, void* sorted,
                                cudaStream_t st) {
   if (max_rows <= 0) return 0;
-  return launch_pdl(ep_compact_kernel, dim3(max_rows), dim3(128), 0, st, static_cast<const bf16*>(xs), rows, n_valid, H,
-                    static_cast<bf16*>(sorted)) == cudaSuccess ? 0 : -4;
+  return launch_pdl(ep_compact_kernel, dim3(max_rows < 4096 ? max_rows : 4096), dim3(128), 0, st,
+                    static_cast<const bf16*>(xs), rows, n_valid, H, static_cast<bf16*>(sorted)) == cudaSuccess ? 0 : -4;
 }
 // out [T, H] = weighted sum; or, with norm_w: res_out = bf16(res + sum), y = norm(res_out) * (1 + norm_w).
 extern "C" int b200_ep_combine(const EpCtx* c, const float* wts, int T, int P, int H, void* out, const void* res,

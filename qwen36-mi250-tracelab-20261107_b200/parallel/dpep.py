@@ -65,6 +65,20 @@ class TickCoordinator:
             return False
         return bool(int(msg[0]))
 
+    def rendezvous(self, engine) -> None:
+        """All replicas meet here with idle devices. Used between the graph captures of the warm-up: capturing and
+        instantiating a graph takes a replica anything from tens of milliseconds to over a second, and the eager run
+        that precedes the next capture contains peer waits that give up after about a second."""
+        if self.stopped:
+            return
+        if engine.device.type == "cuda":
+            torch.cuda.synchronize(engine.device)
+        try:
+            self.dist.barrier(group=self.group)
+        except Exception as e:  # noqa: BLE001
+            self.stopped = True
+            engine.tear_down(f"lost the other replicas of the expert-parallel group: {e!r}")
+
     def stop(self, engine) -> None:
         """Tell the other replicas that this one leaves (they tear down at their next agreement)."""
         self.stopping = True

@@ -212,8 +212,8 @@ class EpMoE:
         else:
             if w["sorted"] is None:
                 w["sorted"] = torch.empty(self.cap_rows, H, dtype=x.dtype, device=dev)
-            rc |= L.b200_ep_compact(self._own["xs"], w["gather_rows"].data_ptr(), n_rows.data_ptr(),
-                                    min(self.cap_rows, n_pairs * self.world), H, w["sorted"].data_ptr(), st)
+            rc |= L.b200_ep_compact(self._own["xs"], w["gather_rows"].data_ptr(), n_rows.data_ptr(), self.cap_rows, H,
+                                    w["sorted"].data_ptr(), st)
             rc |= K.b200_gemm_grouped(w["sorted"].data_ptr(), w_gate_up_local.data_ptr(), w["act"].data_ptr(),
                                       self.cap_rows, self.per + 1, inter, 2 * inter, H, inter, cuda_ops.EPI_SILU_MUL,
                                       inter, bt, w["tiles"].data_ptr(), n_tiles.data_ptr(), w["max_tiles"],

@@ -583,6 +583,9 @@ class Engine:
             self.stats["device_errors"] += 1
             if self.multi_rank:
                 self.device_error_pending = True
+            names = {1: "a TMA stage never arrived", 2: "no pipeline stage became free", 3: "an accumulator never completed",
+                     4: "a peer's flag never arrived", 5: "an index was out of range"}
+            print(f"engine: device-side failure {code} ({names.get(code, 'unknown')}) in the pass just run", flush=True)
             raise self.ops.KernelError(f"device-side failure {code} in this pass")
 
     def fail_all(self, reason: str, status: int = 500) -> None:
@@ -685,6 +688,10 @@ class Engine:
             self._graphs.warm()
             if self.device.type == "cuda":
                 torch.cuda.synchronize(self.device)
+        if self.device.type == "cuda" and hasattr(self.ops, "check_errors"):
+            self.ops.check_errors(self.device)  # a failure of the warm-up stops the start, not the first request
+        if self.tick is not None:
+            self.tick.rendezvous(self)
         self.cache.clear()
         for k in self.stats:
             self.stats[k] = 0

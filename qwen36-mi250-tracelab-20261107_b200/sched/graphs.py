@@ -172,6 +172,8 @@ class DecodeGraphs:
         every_width = self.engine.tick is not None
         for w in (self.widths if every_width else self.widths[:1]):
             for s in self.sizes:
+                if every_width:
+                    self.engine.tick.rendezvous(self.engine)  # replicas capture in step: their eager runs pair up
                 self._bucket(s, w)
         self.frozen = every_width
 

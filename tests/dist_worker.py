@@ -318,10 +318,12 @@ def mode_ep_moe(rank, world, dev):
     router = (torch.randn(E + 1, H, device=dev, generator=g) * 0.3).to(torch.bfloat16)
     wgu = (torch.randn(E + 1, 2 * I, H, device=dev, generator=g) * 0.05).to(torch.bfloat16)
     wd = (torch.randn(E + 1, H, I, device=dev, generator=g) * 0.05).to(torch.bfloat16)
-    ep = EpMoE(dev, dist.group.WORLD, E, H, k, max_rows=300)
+    ep = EpMoE(dev, dist.group.WORLD, E, H, k, max_rows=2100)
     lgu, ld = ep.local_experts(wgu, wd)
     gx = torch.Generator(device=dev).manual_seed(100 + rank)  # rows: different on every rank
-    for T in (1, 37 + 5 * rank, 256, 0 if rank == 0 else 9):
+    # the last size: wide token tiles (the expert-sorted copy of the received rows) on a rank that receives several
+    # times the rows it sends
+    for T in (1, 37 + 5 * rank, 256, 0 if rank == 0 else 9, 280 if rank == 0 else 2000):
         x = torch.randn(T, H, device=dev, generator=gx).to(torch.bfloat16)
         got = ep.forward(x, router, lgu, ld)
         cuda_ops.check_errors(dev)
