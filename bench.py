@@ -285,7 +285,8 @@ def main() -> None:
         weights = shard_experts(full, rank, world)
         del full
         torch.cuda.empty_cache()
-        ep_ctx = EpMoE(dev, dist.group.WORLD, mcfg.num_experts, mcfg.hidden_size, mcfg.num_experts_per_tok, max_rows=8192)
+        ep_ctx = EpMoE(dev, dist.group.WORLD, mcfg.num_experts, mcfg.hidden_size, mcfg.num_experts_per_tok, max_rows=8192,
+                       wait_s=5.0)  # the ranks step on their own clocks in the serving workload
     else:
         weights = random_weights(mcfg, seed=1234 + rank, device=dev, dtype=torch.bfloat16)
     total_out = K + max(W, 3) + 64 + (B * P) // 4096  # room for the tokens decoded while later prompts prefill

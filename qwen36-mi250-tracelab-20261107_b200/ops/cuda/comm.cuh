@@ -42,11 +42,14 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 // Wait until *p reaches `want` (wrap-safe). Gives up after WAIT_CYCLES, records ERR_WAIT_PEER. Once the error word
 // is set (by this wait or any earlier one of the step) every further wait gives up at once, so a step whose peer is
 // gone costs one timeout, not one per collective.
-__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t want, int* err) {
+// `limit`: clock ticks before giving up. A second is right for kernels whose peers were launched by the same host
+// thread or in the same captured graph; replicas that launch their passes from separate processes (each under its own
+// interpreter lock, with its own request threads) give their peer waits a limit set by the host (EpCtx::wait_cycles).
+__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t want, int* err, long long limit = WAIT_CYCLES) {
   const long long t0 = clock64();
   while (static_cast<int32_t>(ld_acquire_sys(p) - want) < 0) {
     if (err && *reinterpret_cast<volatile int*>(err) != 0) return false;
-    if (clock64() - t0 > WAIT_CYCLES) {
+    if (clock64() - t0 > limit) {
       if (err) atomicCAS(err, 0, ERR_WAIT_PEER);
       return false;
     }

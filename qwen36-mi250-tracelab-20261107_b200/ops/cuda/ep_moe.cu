@@ -46,6 +46,7 @@ struct EpCtx {
   int E;                        // routed experts (global); expert id E is the shared expert, hosted by everyone
   int per;                      // routed experts per rank
   int cap_src, max_pairs;
+  long long wait_cycles;        // clock ticks a peer wait may take before it gives up with ERR_WAIT_PEER
 };
 
 // Last CTA out: release (epoch, rows sent) of this source on every host. The CTA's peer stores
@@ -147,7 +148,7 @@ ep_plan_kernel(EpCtx c, int bt, int4* tiles, int* n_tiles, int max_tiles, int* g
       asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(word) : "l"(p) : "memory");
       if (static_cast<int32_t>(static_cast<uint32_t>(word >> 32) - want) >= 0) break;
       if (*reinterpret_cast<volatile int*>(c.err) != 0) { ok = false; break; }
-      if (clock64() - t0 > WAIT_CYCLES) { atomicCAS(c.err, 0, ERR_WAIT_PEER); ok = false; break; }
+      if (clock64() - t0 > c.wait_cycles) { atomicCAS(c.err, 0, ERR_WAIT_PEER); ok = false; break; }
       __nanosleep(20);
     }
     if (!ok) s_ok = 0;
@@ -241,7 +242,7 @@ __global__ void ep_combine_kernel(EpCtx c, const float* wts, int T, int P, int H
     __threadfence_system();
     st_release_sys(c.flags[threadIdx.x] + 1 * MAX_RANKS + c.rank, c.epoch[0]);
   }
-  if (threadIdx.x < c.world && !wait_flag(c.flags[c.rank] + 1 * MAX_RANKS + threadIdx.x, c.epoch[0], c.err)) s_ok = 0;
+  if (threadIdx.x < c.world && !wait_flag(c.flags[c.rank] + 1 * MAX_RANKS + threadIdx.x, c.epoch[0], c.err, c.wait_cycles)) s_ok = 0;
   __syncthreads();
   const int t = blockIdx.x;
   if (!s_ok || t >= T) return;

@@ -32,14 +32,18 @@ class KernelError(RuntimeError):
     pass
 
 
-def lib() -> ctypes.CDLL:
+def lib() -> ctypes.PyDLL:
     global _lib
     if _lib is None:
         path = lib_path()
         if not path.exists():
             raise KernelError(f"{path} is missing: run `python -m b200serve.ops.build` (or __graft_entry__.build())")
         t0 = time.perf_counter()
-        _lib = ctypes.CDLL(str(path))
+        # PyDLL: the interpreter lock stays with the calling thread during a call. Every entry point is an
+        # asynchronous launch of a few microseconds; giving the lock up around each one (what CDLL does) makes the
+        # engine thread queue for it again behind the request threads several hundred times per pass, which under a
+        # burst of requests stretched one pass to seconds.
+        _lib = ctypes.PyDLL(str(path))
         buildlog.record("load", path.name, time.perf_counter() - t0)
         for name in dir(_Sig):
             if name.startswith("b200_"):

@@ -181,8 +181,12 @@ def build_engine(model: str, engine_cfg, use_cuda: bool, weights=None):
     mcfg = weights.config
     cfg = dataclasses.replace(engine_cfg, mtp=False)  # drafts would make the replicas' pass sequences differ
     if use_cuda:
+        # Each replica launches its passes from its own process, next to its own request threads: between the
+        # agreement on a pass and the launch of its kernels the interpreter lock may go to those threads for a while,
+        # so the peer waits get seconds, not the one second of ranks driven by one program.
         ep = EpMoE(dev, dist.group.WORLD, mcfg.num_experts, mcfg.hidden_size, mcfg.num_experts_per_tok,
-                   max_rows=max(cfg.prefill_pack_tokens, cfg.max_seqs))
+                   max_rows=max(cfg.prefill_pack_tokens, cfg.max_seqs),
+                   wait_s=float(os.environ.get("ENGINE_EP_WAIT_S", "20")))
     else:
         ep = GlooEpMoE(dist.group.WORLD, mcfg.num_experts, mcfg.num_experts_per_tok)
     engine = Engine(weights, cfg, ep=ep)

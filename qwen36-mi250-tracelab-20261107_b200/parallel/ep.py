@@ -36,6 +36,7 @@ class EpCtx(ctypes.Structure):
         ("per", ctypes.c_int),
         ("cap_src", ctypes.c_int),
         ("max_pairs", ctypes.c_int),
+        ("wait_cycles", ctypes.c_longlong),
     ]
 
 
@@ -59,11 +60,13 @@ def _lib():
 
 class EpMoE:
     def __init__(self, device: torch.device, group, n_experts: int, hidden: int, top_k: int, max_rows: int,
-                 capacity_factor: float | None = None) -> None:
+                 capacity_factor: float | None = None, wait_s: float = 1.0) -> None:
         """``max_rows``: most rows any rank brings to one call. Every rank keeps one receive region per source rank;
         a region holds ``cap_src`` rows. By default that is the worst case (every pair of a source lands on one
         host); ``capacity_factor`` f sizes it for f times the uniform share instead (plus the shared expert's rows),
-        and a call that needs more sets the error word rather than dropping rows silently."""
+        and a call that needs more sets the error word rather than dropping rows silently. ``wait_s``: how long a
+        kernel waits for a peer's rows or results before it gives up with a status (about a second when the ranks are
+        driven in step by one program; replicas that launch from separate server processes need more slack)."""
         import torch.distributed as dist
 
         self.device, self.group = device, group
@@ -150,6 +153,7 @@ class EpMoE:
         ctx.err = cuda_ops.err_word(device).data_ptr()
         ctx.rank, ctx.world, ctx.E, ctx.per = self.rank, self.world, n_experts, self.per
         ctx.cap_src, ctx.max_pairs = self.cap_src, self.max_pairs
+        ctx.wait_cycles = int(max(0.05, wait_s) * 2.0e9)  # clock64 ticks at about 2 GHz
         self.ctx = ctx
         self._pair_out_ptrs = (ctypes.c_void_p * MAX_RANKS)(*[peers["pair_out"][r] if r < self.world else None
                                                              for r in range(MAX_RANKS)])
