@@ -40,11 +40,16 @@ class TickCoordinator:
         self.stopping = False
         self.stopped = False
         self.ticks = 0
+        self.trace = os.environ.get("ENGINE_TICK_TRACE", "0") == "1"  # log every agreement that leads to a pass
+        self._last_traced = False
 
-    def any(self, engine, want: bool) -> bool:
+    def any(self, engine, want: bool, what: str = "") -> bool:
         """True when at least one replica has rows for the pass about to run. Also spreads failure and shutdown."""
         if self.stopped:
             return False
+        if self.trace and (want or self._last_traced):
+            print(f"tick {self.ticks} {what}: want={int(want)} running={len(engine.running)} "
+                  f"prefilling={len(engine.prefilling)}", flush=True)
         msg = torch.tensor([1 if want else 0, 1 if engine.device_error_pending else 0, 1 if self.stopping else 0],
                            dtype=torch.int32)
         try:
@@ -63,6 +68,9 @@ class TickCoordinator:
             self.stopped = True
             engine.tear_down("the expert-parallel group is shutting down")
             return False
+        if self.trace and (int(msg[0]) or self._last_traced):
+            print(f"tick {self.ticks - 1} {what}: agreed={int(msg[0])}", flush=True)
+        self._last_traced = bool(int(msg[0]))
         return bool(int(msg[0]))
 
     def rendezvous(self, engine) -> None:
@@ -187,6 +195,11 @@ def build_engine(model: str, engine_cfg, use_cuda: bool, weights=None):
         ep = EpMoE(dev, dist.group.WORLD, mcfg.num_experts, mcfg.hidden_size, mcfg.num_experts_per_tok,
                    max_rows=max(cfg.prefill_pack_tokens, cfg.max_seqs),
                    wait_s=float(os.environ.get("ENGINE_EP_WAIT_S", "20")))
+        # the block's work buffers (activations of the received rows, their expert-sorted copy, tile tables) are
+        # made now, before the engine sizes its KV pool from the memory that is left; the captured decode graphs and
+        # a prefill pass of the packed size still need their share afterwards
+        ep.reserve(mcfg.moe_intermediate_size, dtype)
+        cfg = dataclasses.replace(cfg, reserve_gb=cfg.reserve_gb + float(os.environ.get("ENGINE_EP_RESERVE_GB", "4")))
     else:
         ep = GlooEpMoE(dist.group.WORLD, mcfg.num_experts, mcfg.num_experts_per_tok)
     engine = Engine(weights, cfg, ep=ep)

@@ -181,6 +181,13 @@ class EpMoE:
             )
         return w
 
+    def reserve(self, inter: int, dtype: torch.dtype) -> None:
+        """Allocate every work buffer a call can need for experts of width ``inter`` now (a server does this before it
+        sizes its KV pool, so that the first long prefill pass does not find the memory gone)."""
+        w = self._buffers(inter, dtype)
+        if w["sorted"] is None:
+            w["sorted"] = torch.empty(self.cap_rows, self.H, dtype=dtype, device=self.device)
+
     def forward(self, x: torch.Tensor, router: torch.Tensor, w_gate_up_local: torch.Tensor,
                 w_down_local: torch.Tensor, residual: torch.Tensor | None = None, norm_w: torch.Tensor | None = None,
                 eps: float = 1e-6):

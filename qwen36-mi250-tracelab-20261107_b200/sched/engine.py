@@ -304,7 +304,7 @@ class Engine:
             # Replicas that share their MoE blocks run every pass together: a prefill pass happens on all of them as
             # soon as one has a span to compute; a replica without one joins with an empty pass (it still hosts
             # experts for the others' rows).
-            if not self.tick.any(self, bool(picked)):
+            if not self.tick.any(self, bool(picked), "prefill"):
                 return False
             if not picked:
                 return self._empty_pass()
@@ -318,10 +318,16 @@ class Engine:
         try:
             hidden = self.model.forward(batch)
             self.check_device()
+            if self.tick is not None and self.tick.trace:
+                print(f"pass done: prefill of {batch.tokens.shape[0]} rows", flush=True)
         except Exception as e:  # fail the packed requests only; the engine keeps serving
+            print(f"engine: prefill pass of {batch.tokens.shape[0]} rows failed: {e!r}", flush=True)
             for g in picked:
                 self.prefilling.remove(g)
                 self._fail(g, EngineError(f"prefill failed: {e}", 500, "internal_error"))
+            if self.multi_rank:
+                # the pass stopped part-way: the other ranks ran kernels that this one never launched
+                self.device_error_pending = True
             return True
         self.stats["prefill_passes"] += 1
         self.stats["prefill_segments"] += len(picked)
@@ -364,6 +370,8 @@ class Engine:
         try:
             self.model.forward_empty()
             self.check_device()
+            if self.tick is not None and self.tick.trace:
+                print("pass done: empty", flush=True)
         except Exception as e:  # noqa: BLE001
             print(f"engine: empty pass failed: {e!r}", flush=True)
             self.device_error_pending = True
@@ -456,7 +464,7 @@ class Engine:
                 self.running.remove(gen)
                 self._fail(gen, EngineError("the KV cache is full", 503, "service_unavailable"))
         if self.tick is not None:
-            if not self.tick.any(self, bool(batch_gens)):
+            if not self.tick.any(self, bool(batch_gens), "decode"):
                 return False
             if not batch_gens:
                 return self._empty_pass()
@@ -478,9 +486,12 @@ class Engine:
             greedy = None
             self.check_device()
         except Exception as e:
+            print(f"engine: decode step of {len(batch_gens)} rows failed: {e!r}", flush=True)
             for g in batch_gens:
                 self.running.remove(g)
                 self._fail(g, EngineError(f"decode failed: {e}", 500, "internal_error"))
+            if self.multi_rank:
+                self.device_error_pending = True
             return True
         for g in batch_gens:
             g.computed += 1
