@@ -203,46 +203,49 @@ class EpMoE:
         logits = cuda_ops.linear(x, router, out_dtype=torch.float32)
         wts = torch.empty(T, Pn, dtype=torch.float32, device=dev)
         idx = torch.empty(T, Pn, dtype=torch.int32, device=dev)
+        codes: list = []  # every launcher's return code: a failure names the call
         C = ctypes.byref(self.ctx)
         # routing and dispatch in one launch: a CTA per row routes it, then sends its pairs to their hosts
-        rc = L.b200_ep_route_send(C, x.data_ptr(), logits.data_ptr(), logits.stride(0), T, self.top_k, Pn, H,
-                                  wts.data_ptr(), idx.data_ptr(), st)
+        codes.append(("route_send", L.b200_ep_route_send(C, x.data_ptr(), logits.data_ptr(), logits.stride(0), T, self.top_k, Pn, H,
+                                  wts.data_ptr(), idx.data_ptr(), st)))
         # token tile of this host's GEMMs from the rows it can expect (its own count times the ranks); a row's bits
         # do not depend on it, so ranks with different batches need not agree
         bt = cuda_ops.moe_bt(max(T, 1) * self.world, Pn, E)
         w = self._buffers(inter, x.dtype)
         n_tiles, n_rows = w["ints"][:1], w["ints"][1:]
-        rc |= L.b200_ep_plan(C, bt, w["tiles"].data_ptr(), n_tiles.data_ptr(), w["max_tiles"],
-                             w["gather_rows"].data_ptr(), w["ret_meta"].data_ptr(), n_rows.data_ptr(), st)
+        codes.append(("plan", L.b200_ep_plan(C, bt, w["tiles"].data_ptr(), n_tiles.data_ptr(), w["max_tiles"],
+                             w["gather_rows"].data_ptr(), w["ret_meta"].data_ptr(), n_rows.data_ptr(), st)))
         err = cuda_ops.err_word(dev)
         if bt <= cuda_ops.GATHER_MAX_BT:
-            rc |= K.b200_gemm_grouped(self._own["xs"], w_gate_up_local.data_ptr(), w["act"].data_ptr(), self.cap_rows,
+            codes.append(("gate_up(gather)", K.b200_gemm_grouped(self._own["xs"], w_gate_up_local.data_ptr(), w["act"].data_ptr(), self.cap_rows,
                                       self.per + 1, inter, 2 * inter, H, inter, cuda_ops.EPI_SILU_MUL, inter, bt,
                                       w["tiles"].data_ptr(), n_tiles.data_ptr(), w["max_tiles"], err.data_ptr(), 1,
-                                      cuda_ops.is_packed(w_gate_up_local), w["gather_rows"].data_ptr(), H, st)
+                                      cuda_ops.is_packed(w_gate_up_local), w["gather_rows"].data_ptr(), H, st)))
         else:
             if w["sorted"] is None:
                 w["sorted"] = torch.empty(self.cap_rows, H, dtype=x.dtype, device=dev)
-            rc |= L.b200_ep_compact(self._own["xs"], w["gather_rows"].data_ptr(), n_rows.data_ptr(), self.cap_rows, H,
-                                    w["sorted"].data_ptr(), st)
-            rc |= K.b200_gemm_grouped(w["sorted"].data_ptr(), w_gate_up_local.data_ptr(), w["act"].data_ptr(),
+            codes.append(("compact", L.b200_ep_compact(self._own["xs"], w["gather_rows"].data_ptr(), n_rows.data_ptr(), self.cap_rows, H,
+                                    w["sorted"].data_ptr(), st)))
+            codes.append(("gate_up", K.b200_gemm_grouped(w["sorted"].data_ptr(), w_gate_up_local.data_ptr(), w["act"].data_ptr(),
                                       self.cap_rows, self.per + 1, inter, 2 * inter, H, inter, cuda_ops.EPI_SILU_MUL,
                                       inter, bt, w["tiles"].data_ptr(), n_tiles.data_ptr(), w["max_tiles"],
-                                      err.data_ptr(), 1, cuda_ops.is_packed(w_gate_up_local), None, 0, st)
-        rc |= L.b200_gemm_grouped_scatter(w["act"].data_ptr(), w_down_local.data_ptr(), self.cap_rows, self.per + 1, H,
+                                      err.data_ptr(), 1, cuda_ops.is_packed(w_gate_up_local), None, 0, st)))
+        codes.append(("down(scatter)", L.b200_gemm_grouped_scatter(w["act"].data_ptr(), w_down_local.data_ptr(), self.cap_rows, self.per + 1, H,
                                           inter, bt, w["tiles"].data_ptr(), n_tiles.data_ptr(), w["max_tiles"],
                                           w["ret_meta"].data_ptr(), self._pair_out_ptrs, self.world, err.data_ptr(),
-                                          cuda_ops.is_packed(w_down_local), st)
+                                          cuda_ops.is_packed(w_down_local), st)))
         if norm_w is not None:
             new_res, y = torch.empty_like(x), torch.empty_like(x)
-            rc |= L.b200_ep_combine(C, wts.data_ptr(), T, Pn, H, None, None if residual is None else residual.data_ptr(),
-                                    norm_w.data_ptr(), new_res.data_ptr(), y.data_ptr(), eps, st)
+            codes.append(("combine", L.b200_ep_combine(C, wts.data_ptr(), T, Pn, H, None,
+                                                     None if residual is None else residual.data_ptr(), norm_w.data_ptr(),
+                                                     new_res.data_ptr(), y.data_ptr(), eps, st)))
             out = (new_res, y)
         else:
             out = torch.empty_like(x)
-            rc |= L.b200_ep_combine(C, wts.data_ptr(), T, Pn, H, out.data_ptr(), None, None, None, None, 0.0, st)
-        if rc:
-            raise cuda_ops.KernelError(f"expert-parallel MoE failed with code {rc}")
+            codes.append(("combine", L.b200_ep_combine(C, wts.data_ptr(), T, Pn, H, out.data_ptr(), None, None, None, None, 0.0, st)))
+        bad = [(n, c) for n, c in codes if c]
+        if bad:
+            raise cuda_ops.KernelError(f"expert-parallel MoE failed: {bad} (rows {T}, token tile {bt})")
         return out
 
     def close(self) -> None:
