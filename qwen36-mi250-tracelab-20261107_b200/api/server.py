@@ -45,6 +45,12 @@ class EngineWorker(threading.Thread):
 
     def run(self) -> None:
         eng = self.engine
+        if getattr(eng.device, "type", "cpu") == "cuda":
+            # the current CUDA device is a property of the host thread and starts at 0 in every new thread: without
+            # this, a replica on any other device would launch its kernels on device 0's stream
+            import torch
+
+            torch.cuda.set_device(eng.device)
         # ENGINE_STALL_DUMP_S = N: when one iteration of the loop takes longer than N seconds, the stacks of all threads
         # are written to stderr (once per stall), so that a wedged replica shows where it waits
         stall = float(os.environ.get("ENGINE_STALL_DUMP_S", "0") or 0)
