@@ -122,7 +122,13 @@ def _ticket(device: torch.device) -> torch.Tensor:
 
 def err_word(device: torch.device) -> torch.Tensor:
     """The per-device error word kernels write when a bounded wait or an index check fails."""
-    idx = device.index if device.index is not None else torch.cuda.current_device()
+    cur = torch.cuda.current_device()
+    idx = device.index if device.index is not None else cur
+    if idx != cur:
+        # launches go to the calling thread's current device and stream; the current device is a property of the
+        # host thread (0 in every new thread), so a worker thread of a replica on another device must select it first
+        raise KernelError(f"tensors on cuda:{idx} but the calling thread's current device is cuda:{cur}: "
+                          f"call torch.cuda.set_device({idx}) in this thread")
     if idx not in _err:
         _err[idx] = torch.zeros(1, dtype=torch.int32, device=device)
     return _err[idx]
