@@ -115,7 +115,7 @@ def _ticket(device: torch.device) -> torch.Tensor:
     if idx not in _tickets:
         if torch.cuda.is_current_stream_capturing():
             raise KernelError("first use of the ticket word inside a graph capture: run the pass once eagerly first")
-        _tickets[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+        _tickets[idx] = torch.zeros(1 + 2 * 1024, dtype=torch.int32, device=device)  # ticket, expert counts, expert cursors
         torch.cuda.synchronize(device)
     return _tickets[idx]
 
