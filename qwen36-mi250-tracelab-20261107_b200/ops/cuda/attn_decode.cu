@@ -37,6 +37,29 @@ __device__ __forceinline__ void load_bf16_vec(const bf16* p, float* out) {
   }
 }
 
+// PER consecutive floats rounded to bf16 with one vector store; copy_bf16_vec moves PER bf16 as they are.
+template <int PER>
+__device__ __forceinline__ void store_bf16_vec(bf16* p, const float* v) {
+  bf16 e[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) e[i] = __float2bfloat16(v[i]);
+  if constexpr (PER == 8) *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(e);
+  else if constexpr (PER == 4) *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(e);
+  else {
+#pragma unroll
+    for (int i = 0; i < PER; ++i) p[i] = e[i];
+  }
+}
+template <int PER>
+__device__ __forceinline__ void copy_bf16_vec(bf16* dst, const bf16* src) {
+  if constexpr (PER == 8) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+  else if constexpr (PER == 4) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(src);
+  else {
+#pragma unroll
+    for (int i = 0; i < PER; ++i) dst[i] = src[i];
+  }
+}
+
 template <int D>
 __global__ void attn_prep_kernel(const bf16* qkv, int ld, const int64_t* positions, const int* tables, int max_pages,
                                  const int* seq_of_row, const bf16* q_norm, const bf16* k_norm, bf16* q_out,
@@ -57,49 +80,61 @@ __global__ void attn_prep_kernel(const bf16* qkv, int ld, const int64_t* positio
   else if (head < n_q + n_kv) { src = qkv + static_cast<size_t>(row) * ld + n_q * 2 * D + (head - n_q) * D; nw = k_norm; }
   else src = qkv + static_cast<size_t>(row) * ld + n_q * 2 * D + n_kv * D + (head - n_q - n_kv) * D;
 
-  // lane owns dims lane + 32*i (pairs (d, d + rot/2) of the rotary part fall in the same lane when rot/2 % 32 == 0;
-  // otherwise fetched by shuffle-free direct reads below)
+  // lane owns the PER consecutive dims [lane * PER, +PER): one vector load / store per tensor; the rotary partner
+  // (d, d + rot/2) of a dim lives in another lane and is read through shared memory
+  const int d0 = lane * PER;
   float v[PER];
-#pragma unroll
-  for (int i = 0; i < PER; ++i) v[i] = __bfloat162float(src[lane + 32 * i]);
+  load_bf16_vec<PER>(src + d0, v);
   if (nw) {
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < PER; ++i) ss += v[i] * v[i];
     ss = warp_sum(ss);
     const float inv = rsqrtf(ss / D + eps);
+    float g[PER];
+    load_bf16_vec<PER>(nw + d0, g);
 #pragma unroll
-    for (int i = 0; i < PER; ++i)
-      v[i] = __bfloat162float(__float2bfloat16(v[i] * inv * (1.0f + __bfloat162float(nw[lane + 32 * i]))));
+    for (int i = 0; i < PER; ++i) v[i] = __bfloat162float(__float2bfloat16(v[i] * inv * (1.0f + g[i])));
     // partial RoPE, half-split pairing: (d, d + rot/2) for d < rot/2
     const int half = rot / 2;
     __shared__ float tmp[8][D];
     float* t = tmp[threadIdx.x >> 5];
 #pragma unroll
-    for (int i = 0; i < PER; ++i) t[lane + 32 * i] = v[i];
+    for (int i = 0; i < PER; ++i) t[d0 + i] = v[i];
     __syncwarp();
+    // the rotation itself is spread over all lanes (dim lane + 32 i), two transcendental evaluations per lane instead
+    // of PER of them on the few lanes that own the rotary dims, and goes back through shared memory
+    float rotated[(D / 32)];
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
+    for (int i = 0; i < D / 32; ++i) {
       const int d = lane + 32 * i;
+      rotated[i] = 0.f;
       if (d < rot) {
         const int fi = d < half ? d : d - half;
         const float inv_freq = powf(theta, -2.0f * fi / rot);
-        float s, c;
-        sincosf(static_cast<float>(pos) * inv_freq, &s, &c);
-        const float cb = __bfloat162float(__float2bfloat16(c)), sb = __bfloat162float(__float2bfloat16(s));
+        float sn, c;
+        sincosf(static_cast<float>(pos) * inv_freq, &sn, &c);
+        const float cb = __bfloat162float(__float2bfloat16(c)), sb = __bfloat162float(__float2bfloat16(sn));
         const float other = d < half ? -t[d + half] : t[d - half];
-        v[i] = __bfloat162float(__float2bfloat16(t[d] * cb)) + __bfloat162float(__float2bfloat16(other * sb));
+        rotated[i] = __bfloat162float(__float2bfloat16(t[d] * cb)) + __bfloat162float(__float2bfloat16(other * sb));
       }
+    }
+    __syncwarp();  // every lane has read its partners before anyone overwrites them
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < rot) t[d] = rotated[i];
+    }
+    __syncwarp();
+    if (d0 < rot) {
+#pragma unroll
+      for (int i = 0; i < PER; ++i)
+        if (d0 + i < rot) v[i] = t[d0 + i];
     }
   }
   if (head < n_q) {
-    bf16* dq = q_out + (static_cast<size_t>(row) * n_q + head) * D;
-    bf16* dg = gate_out + (static_cast<size_t>(row) * n_q + head) * D;
-#pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      dq[lane + 32 * i] = __float2bfloat16(v[i]);
-      dg[lane + 32 * i] = src[D + lane + 32 * i];
-    }
+    store_bf16_vec<PER>(q_out + (static_cast<size_t>(row) * n_q + head) * D + d0, v);
+    copy_bf16_vec<PER>(gate_out + (static_cast<size_t>(row) * n_q + head) * D + d0, src + D + d0);
   } else {
     const int seq = seq_of_row[row];
     const int page = tables[static_cast<size_t>(seq) * max_pages + pos / PAGE];
@@ -107,8 +142,7 @@ __global__ void attn_prep_kernel(const bf16* qkv, int ld, const int64_t* positio
     const int which = head < n_q + n_kv ? 0 : 1;
     const int kh = which ? head - n_q - n_kv : head - n_q;
     bf16* dst = kv + ((((static_cast<size_t>(page) * 2 + which) * n_kv + kh) * PAGE) + pos % PAGE) * D;
-#pragma unroll
-    for (int i = 0; i < PER; ++i) dst[lane + 32 * i] = __float2bfloat16(v[i]);
+    store_bf16_vec<PER>(dst + d0, v);
   }
 }
 

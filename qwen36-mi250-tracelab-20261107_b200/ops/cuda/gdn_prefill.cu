@@ -31,13 +31,16 @@ struct ChunkInfo {  // one per (sequence chunk)
 
 // ------------------------------------------------------------------ conv
 // x: [T, ld] (conv input at columns [0, C)); seg_start[seg] = first row of the span; out: [T, C] bf16.
-// A thread owns 8 consecutive channels (16-byte loads) over 32 rows and slides a 3-row window down them, so each
-// input element is read once; the window is rebuilt from the slot's conv state wherever a span starts.
+// A thread owns 8 consecutive channels (16-byte loads) over CONV_ROWS rows and slides a 3-row window down them, so each
+// input element is read once; the window is rebuilt from the three rows above at the start of a run, or from the slot's
+// conv state where a span starts. (Measured at 8192 rows x 8192 channels: 131 us with runs of 32 rows, 136 us with
+// runs of 8, 143 us with eight rows' loads issued together: the kernel is not bound by the latency of its row loads.)
+constexpr int CONV_ROWS = 32;
 __global__ void __launch_bounds__(128)
 gdn_conv_prefill_kernel(const bf16* x, int ld, const int* seq_of_row, const int* seg_start, const int* slots,
                         const bf16* conv_state, const bf16* conv_w, bf16* out, int T, int C) {
   const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
-  const int r0 = blockIdx.y * 32;
+  const int r0 = blockIdx.y * CONV_ROWS;
   if (c >= C) return;
   float w[8][4];
   {
@@ -51,7 +54,7 @@ gdn_conv_prefill_kernel(const bf16* x, int ld, const int* seq_of_row, const int*
       for (int k = 0; k < 4; ++k) w[ch][k] = __bfloat162float(we[ch * 4 + k]);
   }
   float win[3][8];  // inputs of rows r-3, r-2, r-1
-  const int r1 = min(T, r0 + 32);
+  const int r1 = min(T, r0 + CONV_ROWS);
   for (int r = r0; r < r1; ++r) {
     const int seg = seq_of_row[r];
     const int s0 = seg_start[seg];
@@ -378,19 +381,35 @@ __global__ void gdn_gated_norm_kernel(const bf16* o, const bf16* mixed, int ld, 
   const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (gw >= rows * HV) return;
   const int row = gw / HV, h = gw % HV;
-  constexpr int PER = DV / 32;
+  constexpr int PER = DV / 32;  // consecutive elements per lane: one vector load each of o, z and w
+  static_assert(PER == 1 || PER == 2 || PER == 4, "head dim 32, 64 or 128");
+  const size_t o_at = (static_cast<size_t>(row) * HV + h) * DV + lane * PER;
+  const size_t z_at = static_cast<size_t>(row) * ld + z_off + h * DV + lane * PER;
+  bf16 ov[PER], zv[PER], wv[PER], rv[PER];
+  if constexpr (PER == 4) {
+    *reinterpret_cast<uint2*>(ov) = *reinterpret_cast<const uint2*>(o + o_at);
+    *reinterpret_cast<uint2*>(zv) = *reinterpret_cast<const uint2*>(mixed + z_at);
+    *reinterpret_cast<uint2*>(wv) = *reinterpret_cast<const uint2*>(w + lane * PER);
+  } else if constexpr (PER == 2) {
+    *reinterpret_cast<uint32_t*>(ov) = *reinterpret_cast<const uint32_t*>(o + o_at);
+    *reinterpret_cast<uint32_t*>(zv) = *reinterpret_cast<const uint32_t*>(mixed + z_at);
+    *reinterpret_cast<uint32_t*>(wv) = *reinterpret_cast<const uint32_t*>(w + lane * PER);
+  } else {
+    ov[0] = o[o_at]; zv[0] = mixed[z_at]; wv[0] = w[lane];
+  }
   float v[PER], ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < PER; ++i) { v[i] = __bfloat162float(o[(static_cast<size_t>(row) * HV + h) * DV + lane + 32 * i]); ss += v[i] * v[i]; }
+  for (int i = 0; i < PER; ++i) { v[i] = __bfloat162float(ov[i]); ss += v[i] * v[i]; }
   ss = warp_sum(ss);
   const float inv = rsqrtf(ss / DV + eps);
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
-    const int d = lane + 32 * i;
-    const float z = __bfloat162float(mixed[static_cast<size_t>(row) * ld + z_off + h * DV + d]);
     const float nb = __bfloat162float(__float2bfloat16(v[i] * inv));
-    out[(static_cast<size_t>(row) * HV + h) * DV + d] = __float2bfloat16(__bfloat162float(w[d]) * nb * silu_f(z));
+    rv[i] = __float2bfloat16(__bfloat162float(wv[i]) * nb * silu_f(__bfloat162float(zv[i])));
   }
+  if constexpr (PER == 4) *reinterpret_cast<uint2*>(out + o_at) = *reinterpret_cast<const uint2*>(rv);
+  else if constexpr (PER == 2) *reinterpret_cast<uint32_t*>(out + o_at) = *reinterpret_cast<const uint32_t*>(rv);
+  else out[o_at] = rv[0];
 }
 
 }  // namespace b200
@@ -445,7 +464,7 @@ extern "C" int b200_gdn_prefill(const void* mixed, int ld, const int* seq_of_row
   if (DK != DV) return -7;
   const int C = 2 * HK * DK + HV * DV;
   if (C % 8 || ld % 8) return -7;
-  gdn_conv_prefill_kernel<<<dim3((C / 8 + 127) / 128, (T + 31) / 32), 128, 0, st>>>(
+  gdn_conv_prefill_kernel<<<dim3((C / 8 + 127) / 128, (T + CONV_ROWS - 1) / CONV_ROWS), 128, 0, st>>>(
       static_cast<const bf16*>(mixed), ld, seq_of_row, seg_start, slots, static_cast<const bf16*>(conv_state),
       static_cast<const bf16*>(conv_w), static_cast<bf16*>(conv_out), T, C);
   gdn_conv_state_update_kernel<<<dim3((C + 127) / 128, n_seg), 128, 0, st>>>(
