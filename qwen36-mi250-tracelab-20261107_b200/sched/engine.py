@@ -72,6 +72,8 @@ class Engine:
             from ..spec.ivf import IvfIndex
 
             # from the plain head, before it is tile-packed; deterministic, so every restart builds the same index
+            if getattr(weights.lm_head, "b200_packed", None):
+                raise ValueError("draft_ivf needs the LM head in its plain layout: build the engine before packing")
             draft_index = IvfIndex.build(weights.lm_head, n_clusters=c.draft_ivf, probes=c.draft_ivf_probes)
         if c.pack_weights and tp is None and hasattr(self.ops, "pack_weights"):
             self.ops.pack_weights(weights)  # before the KV pool is sized: padded copies replace a few tensors
