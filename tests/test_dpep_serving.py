@@ -113,3 +113,27 @@ def test_the_front_stops_when_a_replica_dies(tiny_dir):
         if proc.poll() is None:
             proc.terminate()
             proc.wait(timeout=30)
+
+
+def _launch_ranks(mode: str, nproc: int, port: int, env: dict):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), str(ROOT / "tests/dist_worker.py"), mode]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=600, env={**os.environ, **env})
+
+
+def test_replicas_with_their_own_request_streams_on_cpu_ranks():
+    """Each replica loops over ``Engine.step`` on its own; requests arrive at different times, in different numbers and
+    lengths; idle replicas join with empty passes: every request's tokens equal the unsharded engine's."""
+    r = _launch_ranks("dp_ep_served", 2, 29661, {"CUDA_VISIBLE_DEVICES": ""})
+    assert r.returncode == 0 and "OK dp_ep_served" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.gpu
+def test_replicas_with_their_own_request_streams_on_two_gpus():
+    """The same on the NVLink kernels: decode from the graphs captured at warm-up, peer waits inside the kernels."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    r = _launch_ranks("dp_ep_served", 2, 29662, {"NCCL_NVLS_ENABLE": "0"})
+    assert r.returncode == 0 and "OK dp_ep_served" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
