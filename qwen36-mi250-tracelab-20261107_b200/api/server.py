@@ -22,7 +22,7 @@ from typing import Any, Iterator
 
 from ..config import EngineConfig
 from ..obs import buildlog, looptimers, reqstamps
-from ..sched.request import EngineError, Generation, TokenEvent
+from ..sched.request import EngineError, Generation, TokenEvent  # noqa: F401 - named in annotations
 from . import protocol
 from .protocol import ChatRequest, CompletionRequest, Envelope, RequestError, Usage
 from .text import Detokenizer, StopMatcher

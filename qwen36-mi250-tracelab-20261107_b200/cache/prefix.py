@@ -24,7 +24,7 @@ from __future__ import annotations
 import hashlib
 from array import array
 from collections import OrderedDict
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 from ..config import PAGE_SIZE
 from .pools import PagePool, SlotPool

@@ -16,7 +16,6 @@ import signal
 import socket
 import subprocess
 import sys
-import time
 from datetime import timedelta
 
 import torch

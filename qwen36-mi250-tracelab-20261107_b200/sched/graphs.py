@@ -11,7 +11,6 @@ from __future__ import annotations
 
 import torch
 
-from ..config import PAGE_SIZE
 from ..models.qwen36 import PackedBatch
 from ..obs import looptimers
 

@@ -20,7 +20,6 @@ from dataclasses import dataclass, field
 
 import torch
 
-from ..config import PAGE_SIZE
 from ..models.qwen36 import PackedBatch
 from ..sched.sampling import pick_token
 
