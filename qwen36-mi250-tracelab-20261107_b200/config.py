@@ -249,6 +249,10 @@ class EngineConfig:
     cuda_graphs: bool = True
     graphs_on_cpu: bool = False  # tests: run the decode-graph scheduling (buckets, run-ahead) without a CUDA device
     run_ahead: bool = True  # launch decode step n + 1 from device-built inputs before the host has read step n
+    # captured prefill passes for one request's short span (a session's next turn, a short prompt): padded row counts
+    # of the graphs; a span of up to rows - 64 tokens fits the graph of `rows`
+    prefill_graphs: bool = False
+    prefill_graph_rows: tuple[int, ...] = (128, 256, 512, 1024)
     # tile-pack the GEMM weights on the GPU (in place: the engine then owns the weights; not under tensor parallelism)
     pack_weights: bool = False
     # parallelism inside one replica
@@ -278,6 +282,7 @@ class EngineConfig:
             "one_pass_max": "ENGINE_PREFILL_ONE_PASS_MAX",
             "cuda_graphs": "ENGINE_CUDA_GRAPHS",
             "run_ahead": "ENGINE_RUNAHEAD",
+            "prefill_graphs": "ENGINE_PREFILL_GRAPHS",
             "pack_weights": "ENGINE_PACK_WEIGHTS",
             "tp": "ENGINE_TP",
             "ep": "ENGINE_EP",

@@ -40,6 +40,7 @@ class PackedBatch:
     seg_starts: list[int] | None = None
     seg_slots: list[int] | None = None
     seg_pos0: list[int] | None = None
+    meta: object | None = None  # ragged prefill from fixed-shape device tables (``sched/graphs.py`` ``PrefillTables``)
 
     @classmethod
     def prefill(cls, token_lists, slots, pos0, block_tables, device) -> "PackedBatch":
@@ -160,6 +161,7 @@ class Model:
             qkv, batch.positions, batch.seq_of_row, batch.block_tables, kv_layer, lw.q_norm, lw.k_norm,
             cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rotary_dim, cfg.rope_theta,
             cfg.rms_norm_eps, batch.G, batch.seg_starts, batch.seg_pos0,
+            **({} if batch.meta is None else {"meta": batch.meta.flash}),
         )
         return self._out_proj(core, lw.out_proj)
 
@@ -172,7 +174,8 @@ class Model:
         )
         conv, rec = self.conv_state[gi], self.rec_state[gi]
         if batch.G == 0:
-            core = ops.gdn_prefill(mixed, batch.seg_starts, batch.seg_slots, conv, rec, *args)
+            core = ops.gdn_prefill(mixed, batch.seg_starts, batch.seg_slots, conv, rec, *args,
+                                   **({} if batch.meta is None else {"meta": batch.meta.gdn}))
         else:
             r = None if ring is None else (ring[0][gi], ring[1][gi])
             core = ops.gdn_decode(mixed, batch.slots, conv, rec, *args, G=batch.G, ring=r)

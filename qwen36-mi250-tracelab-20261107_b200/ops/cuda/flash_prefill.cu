@@ -100,6 +100,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int kh = blockIdx.y;
   const int pos0 = p.seg_pos0[seg];
   const int n_pos = min(R, seg_len - p0);
+  if (n_pos <= 0) return;  // filler entry: a captured prefill pass keeps its tile table at a fixed length
   const int np_all = (pos0 + p0 + n_pos - 1) / FP_PAGE + 1;  // pages that hold visible keys
   // split mode: a fixed number of consecutive pages per CTA, so the partition of a sequence's context
   // depends on its own length only, never on what else is in the batch

@@ -540,16 +540,22 @@ def _gdn_prefill_meta(seg_starts, seg_slots, T: int, dev):
 
 
 def gdn_prefill(mixed, seg_starts, seg_slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnorm_w, n_k, n_v, dk,
-                dv, eps) -> torch.Tensor:
-    """Chunked prefill of the gated delta rule over packed spans (conv, WY transform, state scan, gated norm)."""
+                dv, eps, meta=None) -> torch.Tensor:
+    """Chunked prefill of the gated delta rule over packed spans (conv, WY transform, state scan, gated norm).
+
+    ``meta``: the span tables as device tensors that the caller keeps up to date (``PrefillTables.gdn``); the host
+    lists are then not read, which lets the call be captured in a CUDA graph."""
     if dk != dv or dk not in (32, 64, 128) or conv_w.shape[1] != 4 or mixed.stride(0) % 8 or (n_k * dk) % 4:
         return torch_ops.gdn_prefill_batched(
             mixed, seg_starts, seg_slots, conv_state, rec_state, conv_w, A_log, dt_bias, gnorm_w, n_k, n_v, dk, dv, eps
         )
     T = mixed.shape[0]
     dev = mixed.device
-    nseg = len(seg_slots)
-    n_chunks, chunks_t, segc_t, sor_t, start_t, slots_t = _gdn_prefill_meta(seg_starts, seg_slots, T, dev)
+    if meta is not None:
+        nseg, n_chunks, chunks_t, segc_t, sor_t, start_t, slots_t = meta
+    else:
+        nseg = len(seg_slots)
+        n_chunks, chunks_t, segc_t, sor_t, start_t, slots_t = _gdn_prefill_meta(seg_starts, seg_slots, T, dev)
     C = 2 * n_k * dk + n_v * dv
     stride = lib().b200_gdn_prefill_work_stride(dk)
     work = torch.empty(n_chunks * n_v * stride, dtype=torch.float32, device=dev)
@@ -568,7 +574,7 @@ def gdn_prefill(mixed, seg_starts, seg_slots, conv_state, rec_state, conv_w, A_l
 
 # --------------------------------------------------------------------------- attention
 def attention(qkv, positions, seq_of_row, block_tables, kv_layer, q_norm, k_norm, n_q, n_kv, head_dim, rotary_dim,
-              theta, eps, G: int, seg_starts=None, seg_pos0=None) -> torch.Tensor:
+              theta, eps, G: int, seg_starts=None, seg_pos0=None, meta=None) -> torch.Tensor:
     """q/k norm + RoPE + KV page write, then gated attention over the paged cache.
 
     ``G > 0``: every sequence has exactly ``G`` rows (decode ``G = 1``, verify ``G = k + 1``) and the
@@ -589,7 +595,7 @@ def attention(qkv, positions, seq_of_row, block_tables, kv_layer, q_norm, k_norm
     if G == 0:
         group = n_q // n_kv
         if head_dim in (64, 128, 256) and group in (1, 2, 4, 8):
-            return flash_prefill(q, gate, kv_layer, block_tables, seg_starts, seg_pos0)
+            return flash_prefill(q, gate, kv_layer, block_tables, seg_starts, seg_pos0, meta=meta)
         return torch_ops.paged_attention(q, gate, kv_layer, block_tables, seg_starts, seg_pos0)
     B = rows // G
     if head_dim in (64, 128, 256) and (n_q // n_kv) in (1, 2, 4, 8):
@@ -606,10 +612,12 @@ def attention(qkv, positions, seq_of_row, block_tables, kv_layer, q_norm, k_norm
 
 
 def flash_prefill(q: torch.Tensor, gate: torch.Tensor, kv_layer: torch.Tensor, block_tables: torch.Tensor,
-                  seg_starts: list[int], seg_pos0: list[int]) -> torch.Tensor:
+                  seg_starts: list[int], seg_pos0: list[int], meta=None) -> torch.Tensor:
     """Causal gated attention of ragged prefill spans over the paged cache (tcgen05 flash kernel).
 
-    ``q [T, n_q, D]`` normed and rotated; the spans' K/V are already in their pages."""
+    ``q [T, n_q, D]`` normed and rotated; the spans' K/V are already in their pages. ``meta``: ``(rows per tile,
+    n_tiles, tiles [n_tiles, 4], pos0 [nseg])`` kept on the device by the caller (``PrefillTables.flash``; entries
+    with a span length of 0 are fillers that their CTAs skip); the host lists are then not read."""
     T, n_q, D = q.shape
     n_kv = kv_layer.shape[2]
     R = 128 // (n_q // n_kv)
@@ -623,7 +631,12 @@ def flash_prefill(q: torch.Tensor, gate: torch.Tensor, kv_layer: torch.Tensor, b
         return (len(tiles), torch.tensor(tiles, dtype=torch.int32).reshape(-1, 4).to(dev, non_blocking=True),
                 torch.tensor(seg_pos0, dtype=torch.int32).to(dev, non_blocking=True))
 
-    n_tiles, tiles_t, pos0_t = _memo(("flash", tuple(seg_starts), tuple(seg_pos0), R, str(dev)), make)
+    if meta is not None:
+        r_meta, n_tiles, tiles_t, pos0_t = meta
+        if r_meta != R:
+            raise ValueError(f"flash_prefill: the tile table was built for {r_meta} positions per tile, the kernel takes {R}")
+    else:
+        n_tiles, tiles_t, pos0_t = _memo(("flash", tuple(seg_starts), tuple(seg_pos0), R, str(dev)), make)
     out = torch.empty(T, n_q * D, dtype=q.dtype, device=dev)
     rc = lib().b200_flash_prefill(
         _ptr(q), _ptr(gate), _ptr(kv_layer), _ptr(out), _ptr(tiles_t), n_tiles, _ptr(pos0_t), _ptr(block_tables),

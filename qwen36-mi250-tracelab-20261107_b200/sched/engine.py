@@ -105,6 +105,7 @@ class Engine:
             decode_steps=0, decoded_tokens=0, largest_batch=0, prefill_passes=0, prefill_segments=0,
             prefilled_tokens=0, cached_tokens=0, requests=0, finished=0, failed=0,
             mtp_verify_steps=0, mtp_proposed=0, mtp_accepted=0, device_errors=0, step_errors=0, ahead_steps=0,
+            prefill_graph_passes=0,
         )
         self._graphs = None
         # library collectives (the NCCL baseline path) stay out of CUDA graphs; the fused NVLink kernels go in
@@ -114,11 +115,17 @@ class Engine:
 
             self._graphs = DecodeGraphs(self)
         self._pending = None  # a decode step in flight (launched ahead of the host's bookkeeping)
+        self._pgraphs = None  # captured prefill passes (built after the speculative controller: they include its block)
         self.spec = None
         if c.mtp and weights.mtp is not None:
             from ..spec.controller import SpecController
 
             self.spec = SpecController(self)
+        if c.prefill_graphs and c.cuda_graphs:
+            from .graphs import PrefillGraphs
+
+            if PrefillGraphs.supported(self):
+                self._pgraphs = PrefillGraphs(self)
 
     # ------------------------------------------------------------------ sizing
     def _auto_pages(self, weights: Weights, n_slots: int) -> int:
@@ -313,17 +320,22 @@ class Engine:
         if not picked:
             return False
         spans = [g.spans[0] for g in picked]
-        batch = PackedBatch.prefill(
-            [g.prompt[a:b] for g, (a, b) in zip(picked, spans)], [g.slot for g in picked],
-            [a for a, _ in spans], self._table(picked), self.device,
-        )
+        graph = self._pgraphs.pick(picked, spans) if self._pgraphs is not None else None
         try:
-            hidden = self.model.forward(batch)
+            if graph is not None:  # one request's short span: a single replay instead of a launch-bound pass
+                hidden, batch = self._pgraphs.run(graph, picked[0], *spans[0])
+                self.stats["prefill_graph_passes"] += 1
+            else:
+                batch = PackedBatch.prefill(
+                    [g.prompt[a:b] for g, (a, b) in zip(picked, spans)], [g.slot for g in picked],
+                    [a for a, _ in spans], self._table(picked), self.device,
+                )
+                hidden = self.model.forward(batch)
             self.check_device()
             if self.tick is not None and self.tick.trace:
                 print(f"pass done: prefill of {batch.tokens.shape[0]} rows", flush=True)
         except Exception as e:  # fail the packed requests only; the engine keeps serving
-            print(f"engine: prefill pass of {batch.tokens.shape[0]} rows failed: {e!r}", flush=True)
+            print(f"engine: prefill pass of {sum(b - a for a, b in spans)} tokens failed: {e!r}", flush=True)
             for g in picked:
                 self.prefilling.remove(g)
                 self._fail(g, EngineError(f"prefill failed: {e}", 500, "internal_error"))
@@ -344,7 +356,10 @@ class Engine:
                 finished_rows.append(batch.seg_starts[i + 1] - 1)
                 finished.append(g)
         if self.spec is not None:
-            self.spec.after_prefill(picked, spans, batch, hidden)
+            if graph is not None:  # the captured pass ran the MTP block over the span already
+                picked[0].mtp_computed = spans[0][1]
+            else:
+                self.spec.after_prefill(picked, spans, batch, hidden)
         if finished:
             rows = torch.tensor(finished_rows, device=self.device)
             self._sample_and_emit(finished, hidden[rows])
@@ -697,6 +712,8 @@ class Engine:
         n = min(self.chunk + 8, self.max_model_len - 8)
         g = self.generate([[1 + (i % 7) for i in range(n)]], Sampling(max_tokens=3, ignore_eos=True))[0]
         assert g.done
+        if self._pgraphs is not None:
+            self._pgraphs.warm()
         if self._graphs is not None:
             self._graphs.warm()
             if self.device.type == "cuda":

@@ -380,3 +380,249 @@ class VerifyGraphs:
         acc = out[size * G : size * G + size][:n].tolist()
         drafts = out[size * G + size :].view(self.kmax, size)[:, :n].t().tolist()
         return picks, acc, drafts, b.ring, b.slots[:n]
+
+
+# --------------------------------------------------------------------------- captured prefill passes
+GDN_CHUNK_ROWS = 64  # rows per chunk of the gated-delta-rule prefill kernels
+
+
+def prefill_layout(n: int, rows: int) -> list[int]:
+    """Span starts ``[0, n, n + a, rows]`` of a padded prefill pass: the real span of ``n`` tokens, then two filler
+    spans (scratch slot, scratch page) of ``a`` and ``rows - n - a`` rows. ``a`` completes the real span's last
+    64-row chunk (32 when there is nothing to complete), so the three spans always split into ``rows / 64 + 1``
+    chunks: the chunk count, like every other launch parameter of the pass, does not depend on ``n``."""
+    if rows % GDN_CHUNK_ROWS or not 1 <= n <= rows - GDN_CHUNK_ROWS:
+        raise ValueError(f"a padded pass of {rows} rows takes 1..{rows - GDN_CHUNK_ROWS} tokens, not {n}")
+    r = n % GDN_CHUNK_ROWS
+    a = GDN_CHUNK_ROWS - r if r else GDN_CHUNK_ROWS // 2
+    return [0, n, n + a, rows]
+
+
+def span_chunks(starts: list[int]) -> tuple[list[tuple[int, int, int, int]], list[tuple[int, int]]]:
+    """``(span, first row, rows, is the span's first chunk)`` per 64-row chunk, span by span, and ``(first chunk,
+    chunk count)`` per span: the tables of the gated-delta-rule prefill kernels."""
+    chunks, per_span = [], []
+    for i in range(len(starts) - 1):
+        a, b = starts[i], starts[i + 1]
+        first = len(chunks)
+        for r0 in range(a, b, GDN_CHUNK_ROWS):
+            chunks.append((i, r0, min(GDN_CHUNK_ROWS, b - r0), int(r0 == a)))
+        per_span.append((first, len(chunks) - first))
+    return chunks, per_span
+
+
+def span_tiles(starts: list[int], r_tile: int, n_tiles: int) -> list[tuple[int, int, int, int]]:
+    """``(span, offset in the span, the span's first row, the span's rows)`` per query tile of the flash kernel,
+    filled up to ``n_tiles`` entries with fillers of a zero-row span, which their CTAs skip."""
+    tiles = []
+    for i in range(len(starts) - 1):
+        n = starts[i + 1] - starts[i]
+        tiles.extend((i, p0, starts[i], n) for p0 in range(0, n, r_tile))
+    if len(tiles) > n_tiles:
+        raise ValueError("more query tiles than the table holds")
+    return tiles + [(0, 0, 0, 0)] * (n_tiles - len(tiles))
+
+
+class PrefillTables:
+    """Span tables of a ragged prefill pass as fixed-shape device tensors that the owner rewrites before each run
+    (what ``cuda_ops.gdn_prefill`` / ``flash_prefill`` otherwise build from host lists, pass by pass)."""
+
+    __slots__ = ("gdn", "flash")
+
+    def __init__(self, gdn, flash) -> None:
+        self.gdn, self.flash = gdn, flash
+
+
+class _PrefillBucket:
+    """One captured prefill pass of ``rows`` packed rows: ONE request's span of up to ``rows - 64`` tokens plus filler
+    rows that run on the scratch slot and the scratch page (``prefill_layout``). Tokens, positions, the MTP block's
+    shifted tokens, the span tables and the page table live in one device buffer mirrored by one pinned host
+    buffer: a pass costs one host-to-device copy and one graph replay instead of some twenty launches per layer
+    (reference: prefill graphs per padded size with device-side counts, ``engine/fast/tp.py:1088-1200``)."""
+
+    N_SPANS = 3
+
+    def __init__(self, engine, rows: int, width: int, r_tile: int) -> None:
+        dev = engine.device
+        self.rows, self.width, self.r_tile = rows, width, r_tile
+        self.cap = rows - GDN_CHUNK_ROWS
+        self.n_chunks = rows // GDN_CHUNK_ROWS + 1
+        self.n_tiles = rows // r_tile + self.N_SPANS
+        sizes = [("tokens", rows * 8), ("positions", rows * 8), ("nxt", rows * 8), ("seq", rows * 4),
+                 ("chunks", self.n_chunks * 16), ("per_span", self.N_SPANS * 8), ("starts", (self.N_SPANS + 1) * 4),
+                 ("slots", self.N_SPANS * 4), ("tiles", self.n_tiles * 16), ("pos0", self.N_SPANS * 4),
+                 ("tables", self.N_SPANS * width * 4)]
+        offs, o = {}, 0
+        for name, nbytes in sizes:  # every table starts on a 16-byte boundary (the kernels read some as int4)
+            offs[name] = (o, nbytes)
+            o += (nbytes + 15) // 16 * 16
+        self.dev_buf = torch.zeros(o, dtype=torch.uint8, device=dev)
+        self.host_buf = torch.zeros(o, dtype=torch.uint8)
+        if dev.type == "cuda":
+            self.host_buf = self.host_buf.pin_memory()
+
+        def views(buf):
+            v = {}
+            for name, (a, nbytes) in offs.items():
+                dt = torch.int64 if name in ("tokens", "positions", "nxt") else torch.int32
+                v[name] = buf[a : a + nbytes].view(dt)
+            v["tables"] = v["tables"].view(self.N_SPANS, width)
+            return v
+
+        d = views(self.dev_buf)
+        self.np = {k: t.numpy() for k, t in views(self.host_buf).items()}
+        self.tokens, self.positions, self.nxt = d["tokens"], d["positions"], d["nxt"]
+        meta = None
+        if dev.type == "cuda":
+            meta = PrefillTables(
+                (self.N_SPANS, self.n_chunks, d["chunks"], d["per_span"], d["seq"], d["starts"], d["slots"]),
+                (r_tile, self.n_tiles, d["tiles"].view(-1, 4), d["pos0"]),
+            )
+        self.batch = PackedBatch(self.tokens, self.positions, d["seq"], d["slots"], d["tables"], 0,
+                                 [0, 0, 0, 0], [0, 0, 0], [0, 0, 0], meta)
+        self.with_mtp = engine.spec is not None
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.hidden = None
+        self.launches = 0
+
+    def fill(self, tokens, nxt, pos0: int, slot: int, pages) -> None:
+        """Write one request's span (``tokens`` at positions ``pos0...``, state slot, page list) and its filler rows."""
+        import numpy as np
+
+        n, rows, v = len(tokens), self.rows, self.np
+        starts = prefill_layout(n, rows)
+        v["tokens"][:n] = tokens
+        v["tokens"][n:] = 0
+        v["nxt"][:n] = nxt
+        v["nxt"][n:] = 0
+        v["positions"][:n] = np.arange(pos0, pos0 + n)
+        for i in (1, 2):  # filler spans start at position 0 of the scratch page
+            v["positions"][starts[i] : starts[i + 1]] = np.arange(starts[i + 1] - starts[i])
+            v["seq"][starts[i] : starts[i + 1]] = i
+        v["seq"][:n] = 0
+        chunks, per_span = span_chunks(starts)
+        assert len(chunks) == self.n_chunks
+        v["chunks"][:] = np.asarray(chunks, dtype=np.int32).reshape(-1)
+        v["per_span"][:] = np.asarray(per_span, dtype=np.int32).reshape(-1)
+        v["starts"][:] = starts
+        v["slots"][:] = (slot, 0, 0)
+        v["tiles"][:] = np.asarray(span_tiles(starts, self.r_tile, self.n_tiles), dtype=np.int32).reshape(-1)
+        v["pos0"][:] = (pos0, 0, 0)
+        k = len(pages)
+        v["tables"][0, :k] = pages
+        v["tables"][0, k:] = 0
+        # the kernel-by-kernel form of the same pass (no CUDA device) reads the spans from these host lists
+        self.batch.seg_starts, self.batch.seg_slots, self.batch.seg_pos0 = starts, [slot, 0, 0], [pos0, 0, 0]
+        self.dev_buf.copy_(self.host_buf, non_blocking=True)
+
+    def _body(self, model):
+        h = model.forward(self.batch)
+        if self.with_mtp:  # the MTP block sees the prompt rows too: (token t + 1, hidden t) fills its own KV pages
+            model.mtp_forward(h, self.nxt, self.batch)
+        return h
+
+    def capture(self, engine) -> None:
+        """Capture with every row on the scratch slot and page, so that the two runs a capture needs touch no request."""
+        n = min(self.cap, GDN_CHUNK_ROWS)
+        self.fill([0] * n, [0] * n, 0, 0, [])
+        model = engine.model
+        if engine.device.type != "cuda":
+            return
+        s = torch.cuda.Stream(device=engine.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._body(model)
+        torch.cuda.current_stream().wait_stream(s)
+        g = torch.cuda.CUDAGraph()
+        count = getattr(engine.ops, "launch_count", None)
+        n0 = count() if count else 0
+        with torch.cuda.graph(g):
+            self.hidden = self._body(model)
+        self.launches = (count() - n0) if count else 0
+        self.graph = g
+
+    def replay(self, model) -> torch.Tensor:
+        if self.graph is not None:
+            self.graph.replay()
+            return self.hidden
+        return self._body(model)
+
+
+class PrefillGraphs:
+    """Captured prefill passes for short spans (a session's next turn on top of its cached context, a short prompt):
+    such a pass is bound by its launches, not by its arithmetic. One graph per padded row count; a pass that packs
+    several requests, or a span longer than the largest graph, runs kernel by kernel as before."""
+
+    def __init__(self, engine) -> None:
+        self.engine = engine
+        cfg = engine.mcfg
+        group = cfg.num_attention_heads // max(cfg.num_key_value_heads, 1)
+        self.r_tile = 128 // group if group in (1, 2, 4, 8) else 16
+        limit = min(engine.chunk, engine.cfg.prefill_pack_tokens)
+        rows = sorted(int(r) for r in engine.cfg.prefill_graph_rows)
+        if any(r % GDN_CHUNK_ROWS or r < 2 * GDN_CHUNK_ROWS for r in rows):
+            raise ValueError("prefill graph sizes are multiples of 64 rows, 128 at least")
+        # sizes beyond the first one that holds a whole chunk are never picked
+        self.sizes = [r for i, r in enumerate(rows) if i == 0 or rows[i - 1] - GDN_CHUNK_ROWS < limit]
+        # the filler spans count their positions from 0 on the scratch page: the table has to be that wide at least
+        self.width = max(engine.max_pages_per_seq, self.sizes[-1] // GDN_CHUNK_ROWS)
+        self.buckets: dict = {}
+        self.errors: dict = {}
+
+    @staticmethod
+    def supported(engine) -> bool:
+        """Single-process engines whose spans take the native kernels on a GPU (their calls read device tables only)
+        or the PyTorch forms on the CPU (tests of the padding logic)."""
+        if engine.multi_rank or engine.tick is not None:
+            return False
+        if engine.device.type != "cuda":
+            return bool(engine.cfg.graphs_on_cpu)
+        c = engine.mcfg
+        group = c.num_attention_heads // max(c.num_key_value_heads, 1)
+        attn = c.head_dim in (64, 128, 256) and group in (1, 2, 4, 8) and c.num_attention_heads % c.num_key_value_heads == 0
+        dk, dv = c.linear_key_head_dim, c.linear_value_head_dim
+        gdn = dk == dv and dk in (32, 64, 128) and c.linear_conv_kernel_dim == 4 and (c.linear_num_key_heads * dk) % 4 == 0
+        return attn and gdn
+
+    def _bucket(self, n: int) -> _PrefillBucket | None:
+        rows = next((r for r in self.sizes if r - GDN_CHUNK_ROWS >= n), None)
+        if rows is None:
+            return None
+        b = self.buckets.get(rows)
+        if b is None and rows not in self.errors:
+            try:
+                b = _PrefillBucket(self.engine, rows, self.width, self.r_tile)
+                b.capture(self.engine)
+            except Exception as e:  # noqa: BLE001 - remember the failure; such spans run kernel by kernel
+                self.errors[rows] = repr(e)
+                return None
+            self.buckets[rows] = b
+        return b
+
+    def warm(self) -> None:
+        for r in self.sizes:
+            self._bucket(r - GDN_CHUNK_ROWS)
+
+    def pick(self, gens, spans) -> _PrefillBucket | None:
+        """The graph for this pass, or None when it has to run kernel by kernel."""
+        if len(gens) != 1:
+            return None
+        g, (a, b) = gens[0], spans[0]
+        if len(g.pages) > self.width:
+            return None
+        if self.engine.spec is not None and b == len(g.prompt) and g.next_token is not None:
+            return None  # a resumed request drafts from its last prompt row right away: the general path does that
+        return self._bucket(b - a)
+
+    def run(self, bucket: _PrefillBucket, gen, a: int, b: int):
+        """Run ``gen``'s span ``[a, b)``; returns ``(hidden [rows, H], batch)`` with the span in rows ``0 .. b - a``."""
+        toks = gen.prompt[a:b]
+        nxt = gen.prompt[a + 1 : b + 1]
+        if len(nxt) < len(toks):
+            nxt = nxt + [0]  # the last prompt row's partner is the first sampled token: its row is redone at decode
+        bucket.fill(toks, nxt, a, gen.slot, gen.pages)
+        start, stop = looptimers.gpu_span("gpu_prefill_graph")
+        start()
+        hidden = bucket.replay(self.engine.model)
+        stop()
+        return hidden, bucket.batch

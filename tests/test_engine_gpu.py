@@ -120,3 +120,38 @@ def test_gpu_engine_with_tile_packed_weights_keeps_tokens():
         cuda_ops.check_errors(eng.device)
     assert outs[0] == outs[1]
     assert len(plain) == len(prompts)
+
+
+def test_gpu_captured_prefill_passes_keep_tokens():
+    """One request's short spans as padded, captured passes (filler rows on the scratch slot and page, fixed-length
+    span tables on the device): same tokens as the passes run kernel by kernel, first turn and next turn, with the
+    MTP block inside the graph."""
+    from b200serve.config import EngineConfig, ModelConfig
+    from b200serve.models.checkpoint import random_weights
+    from b200serve.ops import cuda_ops
+    from b200serve.sched.engine import Engine
+    from b200serve.sched.request import Sampling
+
+    cfg = ModelConfig.tiny(head_dim=64, num_attention_heads=4, num_key_value_heads=1)
+    w = random_weights(cfg, seed=0, device="cuda", dtype=torch.bfloat16, std=0.05, lm_head_std=0.5)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(3, 1024, (n,), generator=g).tolist() for n in (1, 37, 64, 65, 200, 256, 300, 700)]
+    s = Sampling(max_tokens=8, ignore_eos=True)
+
+    def mk(graphs):
+        return Engine(w, EngineConfig(max_model_len=2048, prefill_chunk_tokens=256, max_seqs=4, mtp=True, spec_k=2, kv_pages=160,
+                                      prefill_graphs=graphs, decode_buckets=(1, 4)))
+
+    plain, padded = mk(False), mk(True)
+    assert padded._pgraphs is not None
+    for p in prompts:
+        a = plain.generate([p], s)[0]
+        b = padded.generate([p], s)[0]
+        assert a.output == b.output, len(p)
+        turn = p + a.output + [9, 8, 7, 6, 5]
+        assert plain.generate([turn], s)[0].output == padded.generate([turn], s)[0].output, len(p)
+    assert not padded._pgraphs.errors, padded._pgraphs.errors
+    assert sorted(padded._pgraphs.buckets) == [128, 256, 512]
+    assert all(b.graph is not None and b.launches > 0 for b in padded._pgraphs.buckets.values())
+    assert padded.stats["prefill_graph_passes"] > len(prompts)
+    cuda_ops.check_errors(torch.device("cuda"))
