@@ -83,8 +83,15 @@ class PrefixCache:
     def _chain(self, tokens, upto_blocks: int) -> list[bytes]:
         """Chain hashes after 0, 1, ..., ``upto_blocks`` full blocks."""
         out = [b"\0" * 16]
+        if upto_blocks <= 0:
+            return out
+        # one conversion of the covered tokens to bytes, then a digest per block over slices of it (the per-block
+        # list slice + array conversion was most of a lookup's time on long prompts)
+        src = tokens if isinstance(tokens, array) and tokens.typecode == "q" else array("q", tokens[: upto_blocks * self.block])
+        raw = memoryview(src).cast("B")
+        step = self.block * 8
         for i in range(upto_blocks):
-            out.append(_block_hash(out[-1], tokens[i * self.block : (i + 1) * self.block]))
+            out.append(hashlib.blake2b(raw[i * step : (i + 1) * step], key=out[-1], digest_size=16).digest())
         return out
 
     def __len__(self) -> int:

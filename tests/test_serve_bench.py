@@ -31,3 +31,22 @@ def test_serve_bench_single_round_and_sessions(tmp_path):
         assert out["requests"] == 5 and out["output_tokens"] == 20 and out["cached_tokens"] > 0
     finally:
         s.stop()
+
+
+def test_host_probes_run_without_a_gpu(tmp_path):
+    """The CPU-side probes (incremental tokenizer, page / slot / prefix pools, CPU placement) report sane figures."""
+    import importlib.util
+    from pathlib import Path
+
+    from b200serve.models.tiny import write_tiny_checkpoint
+
+    spec = importlib.util.spec_from_file_location("host_probe", Path(__file__).resolve().parents[1] / "bench/host_probe.py")
+    hp = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(hp)
+    write_tiny_checkpoint(tmp_path)
+    t = hp.main(["tokenize", "--model", str(tmp_path), "--rounds", "3", "--sessions", "3", "--turn-chars", "600"])
+    assert t["ids_equal"] and t["reused_chars"] > t["encoded_chars"] > 0
+    k = hp.main(["kv-pool", "--sessions", "8", "--prompt-tokens", "700", "--rounds", "3"])
+    assert k["tail_hit_rate"] == round(2 / 3, 3) and 0.5 < k["cached_token_share"] < 1 and k["entries"] == 8
+    c = hp.main(["cpu-place", "--replicas", "2", "--gpus-per-replica", "1"])
+    assert len(c["replicas"]) == 2 and all(r["rank_cpus"] for r in c["replicas"])
