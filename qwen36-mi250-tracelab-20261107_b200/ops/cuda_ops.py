@@ -17,7 +17,6 @@ from ctypes import c_float, c_int, c_void_p
 
 import torch
 
-from ..config import PAGE_SIZE
 from ..obs import buildlog
 from . import torch_ops
 from .build import lib_path

@@ -96,8 +96,6 @@ def test_gpu_mtp_speculation_keeps_outputs():
 
 def test_gpu_engine_with_tile_packed_weights_keeps_tokens():
     """Packing the GEMM weights (``EngineConfig.pack_weights``) is a layout change only: same greedy tokens."""
-    import dataclasses
-
     from b200serve.config import EngineConfig, ModelConfig
     from b200serve.models.checkpoint import random_weights
     from b200serve.ops import cuda_ops

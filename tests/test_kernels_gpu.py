@@ -106,8 +106,6 @@ def test_moe_block(C, O, T, E, k, H, I):
 
 
 def test_route_ties_pick_lower_id(C):
-    import ctypes  # noqa: F401
-
     T, E, k = 4, 256, 8
     logits = torch.zeros(T, E + 1, device="cuda")
     logits[1, 100:120] = 1.0
