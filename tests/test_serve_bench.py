@@ -50,3 +50,29 @@ def test_host_probes_run_without_a_gpu(tmp_path):
     assert k["tail_hit_rate"] == round(2 / 3, 3) and 0.5 < k["cached_token_share"] < 1 and k["entries"] == 8
     c = hp.main(["cpu-place", "--replicas", "2", "--gpus-per-replica", "1"])
     assert len(c["replicas"]) == 2 and all(r["rank_cpus"] for r in c["replicas"])
+
+
+def test_service_checker_against_a_tiny_server(tmp_path):
+    """Determinism and stream == non-stream hold on a random-weight server; the echo gate, which needs a real model,
+    fails there and turns the verdict (and the exit code) to a failure."""
+    import importlib.util
+    from pathlib import Path
+
+    from http_util import ServerProc
+
+    from b200serve.models.tiny import write_tiny_checkpoint
+
+    spec = importlib.util.spec_from_file_location("service_check", Path(__file__).resolve().parents[1] / "bench/service_check.py")
+    sc = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sc)
+    write_tiny_checkpoint(tmp_path, lm_head_std=0.5)
+    srv = ServerProc(tmp_path, env={"CUDA_VISIBLE_DEVICES": ""})
+    try:
+        assert sc.main(["--url", srv.url, "--model", srv.model, "--gates", "determinism,stream", "--n", "4", "--concurrency", "4"]) == 0
+        out = sc.run_gates(srv.url, srv.model, ["echo", "determinism"], 3, 3, seed=1)
+        assert out["error_count"] == 0 and out["gates"]["determinism"]["pass"]
+        assert not out["gates"]["echo"]["pass"] and not out["pass"]
+        bad = sc.run_gates(srv.url, "no-such-model", ["determinism"], 2, 2, seed=1)
+        assert bad["error_count"] > 0 and not bad["pass"]
+    finally:
+        srv.stop()
