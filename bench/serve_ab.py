@@ -96,7 +96,7 @@ def run_load(url: str, prompts: list[list[int]], out_len: int, concurrency: int)
     wall = time.perf_counter() - t0
     ttft = [r["stamps"][0] - r["start"] for r in results if r["stamps"]]
     tpot = [(r["stamps"][-1] - r["stamps"][0]) / (len(r["ids"]) - 1) for r in results if len(r["ids"]) > 1]
-    return {"ids": [r["ids"] for r in results], "output_tok_s": round(sum(len(r["ids"]) for r in results) / wall, 1),
+    return {"ids": [r["ids"] for r in results], "failed": sum(1 for r in results if r["error"]), "output_tok_s": round(sum(len(r["ids"]) for r in results) / wall, 1),
             "ttft_p50_ms": round(1e3 * pct(ttft, 0.5), 2), "tpot_p50_ms": round(1e3 * pct(tpot, 0.5), 3),
             "tpot_p90_ms": round(1e3 * pct(tpot, 0.9), 3)}
 

@@ -19,6 +19,11 @@ round r's prompt + its output ids + new random tokens, so the server's session-t
 round r of a session sends the first ``prefix_len`` tokens of what the session has seen so far (its previous
 prompt plus the ids the server generated) followed by ``input_len`` new random tokens, asks for exactly
 ``output_len`` tokens, then sleeps ``tool_wait_after_ms``. ``--concurrency`` is the number of session slots.
+
+A run is ``valid`` only when every planned step ran, none failed and the output total equals the requested one
+(``attempted_steps`` / ``success_steps`` / ``failed_steps`` / ``target_output_tokens`` in the JSON line, the rule
+of the reference's replay harness, ``.vibesys/shared/tracelab/replay.py:37-66``); otherwise the exit code is 1.
+A failed step ends its session.
 """
 
 from __future__ import annotations
@@ -26,6 +31,7 @@ from __future__ import annotations
 import argparse
 import json
 import random
+import sys
 import threading
 import time
 
@@ -43,21 +49,28 @@ def stream_once(url: str, model: str, prompt: list[int], max_tokens: int) -> dic
     body = {"model": model, "prompt": prompt, "max_tokens": max_tokens, "temperature": 0, "ignore_eos": True,
             "return_token_ids": True, "stream": True, "stream_options": {"include_usage": True}}
     t0 = time.perf_counter()
-    stamps, ids, usage = [], [], None
-    with requests.post(url + "/v1/completions", json=body, stream=True, timeout=3600) as r:
-        r.raise_for_status()
-        for line in r.iter_lines():
-            if not line.startswith(b"data: ") or line == b"data: [DONE]":
-                continue
-            ev = json.loads(line[6:])
-            if ev.get("usage"):
-                usage = ev["usage"]
-            for ch in ev.get("choices", []):
-                toks = ch.get("token_ids") or []
-                if toks:
-                    stamps.append(time.perf_counter())
-                    ids.extend(toks)
-    return {"start": t0, "stamps": stamps, "ids": ids, "usage": usage or {}}
+    stamps, ids, usage, error = [], [], None, None
+    try:
+        with requests.post(url + "/v1/completions", json=body, stream=True, timeout=3600) as r:
+            r.raise_for_status()
+            for line in r.iter_lines():
+                if not line.startswith(b"data: ") or line == b"data: [DONE]":
+                    continue
+                ev = json.loads(line[6:])
+                if ev.get("error"):
+                    error = str(ev["error"])[:200]
+                if ev.get("usage"):
+                    usage = ev["usage"]
+                for ch in ev.get("choices", []):
+                    toks = ch.get("token_ids") or []
+                    if toks:
+                        stamps.append(time.perf_counter())
+                        ids.extend(toks)
+    except (requests.RequestException, ValueError) as e:  # a failed step is counted, and ends its session's later rounds
+        error = f"{type(e).__name__}: {e}"[:200]
+    if error is None and len(ids) != max_tokens:
+        error = f"{len(ids)} tokens for max_tokens={max_tokens} with ignore_eos"
+    return {"start": t0, "stamps": stamps, "ids": ids, "usage": usage or {}, "target": max_tokens, "error": error}
 
 
 def pct(vals: list[float], p: float) -> float | None:
@@ -100,6 +113,8 @@ def main() -> None:
             res["round"] = r
             with lock:
                 results.append(res)
+            if res["error"]:
+                return
             prompt = prompt + res["ids"] + [srng.randint(lo_v, hi_v) for _ in range(srng.randint(*grow))]
 
     def run_trace(rows: list[dict], srng: random.Random) -> None:
@@ -113,15 +128,17 @@ def main() -> None:
                 res["round"] = int(row["round_idx"])
                 with lock:
                     results.append(res)
+                if res["error"]:
+                    return
                 seen = prompt + res["ids"]
                 time.sleep(int(row.get("tool_wait_after_ms") or 0) / 1e3)
 
     threads = []
     t_arrive = 0.0
+    by_session: dict[str, list[dict]] = {}
     if a.trace:
         import csv
 
-        by_session: dict[str, list[dict]] = {}
         with open(a.trace, newline="") as f:
             for row in csv.DictReader(f):
                 by_session.setdefault(row["session_id"], []).append(row)
@@ -156,9 +173,17 @@ def main() -> None:
     first_round = [r["stamps"][0] - r["start"] for r in results if r["stamps"] and r["round"] == 0]
     later = [r["stamps"][0] - r["start"] for r in results if r["stamps"] and r["round"] > 0]
     tokens = sum(len(r["ids"]) for r in results)
+    failed = [r for r in results if r["error"]]
+    planned = sum(len(v) for v in by_session.values()) if a.trace else None
+    target = sum(int(row["output_len"]) for v in by_session.values() for row in v) if a.trace else sum(r["target"] for r in results)
+    # a replay counts only when every planned step ran, none failed and the output total is exact (the rule of the
+    # reference's harness, .vibesys/shared/tracelab/replay.py:37-66)
+    valid = not failed and tokens == target and (planned is None or planned == len(results))
     ms = lambda v: None if v is None else round(v * 1e3, 2)  # noqa: E731
     print(json.dumps({
         "requests": len(results), "output_tokens": tokens, "wall_s": round(wall, 3),
+        "attempted_steps": len(results), "success_steps": len(results) - len(failed), "failed_steps": len(failed),
+        "planned_steps": planned, "target_output_tokens": target, "valid": valid, "errors": [r["error"] for r in failed][:3],
         "output_tok_s": round(tokens / wall, 1),
         "ttft_ms": {"p50": ms(pct(ttft, 0.5)), "p90": ms(pct(ttft, 0.9))},
         "ttft_first_round_ms_p50": ms(pct(first_round, 0.5)), "ttft_later_rounds_ms_p50": ms(pct(later, 0.5)),
@@ -166,6 +191,8 @@ def main() -> None:
         "prompt_tokens": sum(r["usage"].get("prompt_tokens", 0) for r in results),
         "cached_tokens": sum((r["usage"].get("prompt_tokens_details") or {}).get("cached_tokens", 0) for r in results),
     }), flush=True)
+    if not valid:
+        sys.exit(1)
 
 
 if __name__ == "__main__":

@@ -29,6 +29,13 @@ def test_serve_bench_single_round_and_sessions(tmp_path):
         assert r.returncode == 0, r.stderr[-2000:]
         out = json.loads(r.stdout.strip().splitlines()[-1])
         assert out["requests"] == 5 and out["output_tokens"] == 20 and out["cached_tokens"] > 0
+        assert out["valid"] and out["planned_steps"] == out["success_steps"] == 5 and out["failed_steps"] == 0
+        assert out["target_output_tokens"] == 20
+        # a replay with failed steps is reported as invalid and the tool exits non-zero
+        r = subprocess.run(base[:-4] + ["--model", "no-such-model", "--vocab", "1024", "--concurrency", "2", "--trace", str(trace)],
+                           capture_output=True, text=True, timeout=300)
+        out = json.loads(r.stdout.strip().splitlines()[-1])
+        assert r.returncode == 1 and not out["valid"] and out["failed_steps"] == 2 and out["success_steps"] == 0
     finally:
         s.stop()
 
