@@ -2,10 +2,13 @@
 ``/v1/chat/completions`` (streaming over SSE or not).
 
 Threads: one engine worker owns the model and runs ``Engine.step()``; every HTTP connection has
-its own handler thread that parses, tokenises, then turns the request's token events into text
-(incremental detokenisation, stop strings, reasoning/content split) and writes the response. The
-port opens only after the weights are loaded, so ``/health`` 200 means ready (reference:
-``engine/server.py:1-21, 488-620, 623-729``; there, detokenisation runs on the engine thread).
+its own handler thread that parses, tokenises, answers refusals and sends the first chunk; from
+then on ONE writer thread (``StreamWriter``) turns the token events of all requests into text
+(incremental detokenisation, stop strings, reasoning/content split) and writes the SSE chunks,
+so a decode step of 128 requests wakes one thread instead of 128 (``ENGINE_STREAM_WRITER=0``:
+every handler thread consumes its own events, as before). The port opens only after the weights
+are loaded, so ``/health`` 200 means ready (reference: ``engine/server.py:1-21, 488-620, 623-729``;
+there, detokenisation runs on the engine thread).
 """
 
 from __future__ import annotations
@@ -14,6 +17,7 @@ import argparse
 import json
 import os
 import queue
+import socket
 import sys
 import threading
 import time
@@ -127,6 +131,220 @@ class _TextStream:
         return "", out
 
 
+class RequestState:
+    """Token events of one request -> response objects: chunks (and an optional usage chunk) when streaming, else
+    one body at the end. Push style, so that either the request's own thread or the shared writer can drive it."""
+
+    def __init__(self, service, request: CompletionRequest | ChatRequest, prompt_len: int, gen: Generation) -> None:
+        self.service, self.request, self.gen = service, request, gen
+        self.chat = isinstance(request, ChatRequest)
+        self.env = Envelope(service.model_name, "chat.completion" if self.chat else "text_completion")
+        self.text = _TextStream(service.codec, request.sampling.stop, self.chat and request.thinking)
+        self.usage = Usage(prompt_len)
+        self.ids: list[int] = []
+        self.first = True
+
+    def feed(self, ev: TokenEvent) -> tuple[list[dict[str, Any]], bool]:
+        """Returns ``(objects to send now, the request is finished)``; raises ``RequestError`` for an error event."""
+        request, chat, env, text, usage = self.request, self.chat, self.env, self.text, self.usage
+        if ev.error is not None:
+            raise RequestError(str(ev.error), ev.error.status)
+        out: list[dict[str, Any]] = []
+        if self.first:
+            self.first = False
+            usage.cached_tokens = self.gen.cached_tokens
+            if request.stream and chat:
+                out.append(protocol.chat_chunk(env, {"role": "assistant", "content": ""}, None, None,
+                                               request.return_token_ids))
+        reasoning = content = ""
+        if ev.token is not None:
+            self.ids.append(ev.token)
+            usage.completion_tokens += 1
+            reasoning, content = text.push(ev.token)
+        done = ev.finish_reason
+        if text.stopped:
+            done = "stop"
+            self.gen.cancelled.set()
+            self.service.worker.wake.set()
+        elif done is not None:
+            r2, c2 = text.flush()
+            reasoning, content = reasoning + r2, content + c2
+            if text.stopped:
+                done = "stop"
+        if done == "cancelled":
+            done = "stop"
+        if request.stream:
+            if chat:
+                delta: dict[str, Any] = {"content": content}
+                if reasoning:
+                    delta = {"reasoning_content": reasoning, **({"content": content} if content else {})}
+                out.append(protocol.chat_chunk(env, delta, ev.token, done, request.return_token_ids))
+            else:
+                out.append(protocol.completion_chunk(env, content, ev.token, done, request.return_token_ids))
+        if done is None:
+            return out, False
+        if request.stream:
+            if request.include_usage:
+                out.append(protocol.usage_chunk(env, usage))
+        elif chat:
+            out.append(protocol.chat_response(env, "".join(text.content),
+                                              "".join(text.reasoning) if request.thinking else None, self.ids, done,
+                                              usage, request.return_token_ids))
+        else:
+            out.append(protocol.completion_response(env, "".join(text.content), self.ids, done, usage,
+                                                    request.return_token_ids))
+        return out, True
+
+
+def sse(objects: list[dict[str, Any]]) -> bytes:
+    return b"".join(b"data: " + json.dumps(o).encode() + b"\n\n" for o in objects)
+
+
+class Stream:
+    """One request between its handler thread and the shared writer. Events first queue up for the handler thread
+    (``next_direct``: refusals must become HTTP statuses, and the first chunk follows the headers), then
+    ``hand_over`` redirects them, in order, to the writer thread, and the handler sleeps until ``finished``."""
+
+    def __init__(self, service, request: CompletionRequest | ChatRequest, prompt: list[int]) -> None:
+        self.service = service
+        self.q: "queue.SimpleQueue[TokenEvent]" = queue.SimpleQueue()
+        self.lock = threading.Lock()
+        self.to_writer = False
+        self.gen = Generation(prompt, request.sampling, on_event=self._sink)
+        self.state = RequestState(service, request, len(prompt), self.gen)
+        self.sock: socket.socket | None = None  # set for SSE responses: the writer sends on it
+        self.backlog = bytearray()  # bytes the socket did not take yet
+        self.objects: list[dict[str, Any]] = []  # non-streaming: the body, once finished
+        self.error: RequestError | None = None
+        self.dead = False  # the client went away
+        self.finished = threading.Event()
+
+    def _sink(self, gen: Generation, ev: TokenEvent) -> None:  # engine thread
+        with self.lock:
+            if self.to_writer:
+                self.service.writer.inbox.put((self, ev))
+            else:
+                self.q.put(ev)
+
+    def next_direct(self) -> tuple[list[dict[str, Any]], bool]:
+        """Handler thread, before the hand-over: wait for the next event and run it through the state machine."""
+        return self.state.feed(self.q.get())
+
+    def hand_over(self, sock: socket.socket | None) -> None:
+        """From here on the writer thread consumes this request's events (those already queued go first)."""
+        with self.lock:
+            self.sock = sock
+            while True:
+                try:
+                    self.service.writer.inbox.put((self, self.q.get_nowait()))
+                except queue.Empty:
+                    break
+            self.to_writer = True
+
+    def cancel(self) -> None:
+        if not self.gen.done:
+            self.gen.cancelled.set()
+            self.service.worker.wake.set()
+
+
+class StreamWriter(threading.Thread):
+    """The one thread that turns token events of all handed-over requests into response bytes. SSE chunks go out
+    with non-blocking sends; what a socket does not take is kept per request and retried (a client that stops
+    reading cannot stall the others; past ``MAX_BACKLOG`` bytes it is treated as gone). When a request finishes,
+    its handler thread wakes once, sends any remainder with a blocking write and closes the connection."""
+
+    MAX_BACKLOG = 8 << 20
+
+    def __init__(self) -> None:
+        super().__init__(daemon=True, name="stream-writer")
+        self.inbox: "queue.SimpleQueue[tuple[Stream, TokenEvent] | None]" = queue.SimpleQueue()
+        self.backlogged: set[Stream] = set()
+        self.stats = {"writer_batches": 0, "writer_events": 0, "writer_partial_sends": 0}
+
+    def run(self) -> None:
+        while True:
+            try:
+                item = self.inbox.get(timeout=0.01 if self.backlogged else None)
+            except queue.Empty:
+                item = False
+            if item is None:
+                return
+            batch = [item] if item else []
+            while True:
+                try:
+                    nxt = self.inbox.get_nowait()
+                except queue.Empty:
+                    break
+                if nxt is None:
+                    return
+                batch.append(nxt)
+            self.stats["writer_batches"] += 1
+            self.stats["writer_events"] += len(batch)
+            for stream, ev in batch:
+                try:
+                    self._handle(stream, ev)
+                except Exception as e:  # noqa: BLE001 - one request's failure must not end the thread
+                    stream.error = stream.error or RequestError(f"internal error: {e}", 500)
+                    stream.cancel()
+                    self._finish(stream)
+            for stream in list(self.backlogged):
+                self._send(stream, b"")
+
+    def stop(self) -> None:
+        self.inbox.put(None)
+
+    def _handle(self, stream: Stream, ev: TokenEvent) -> None:
+        if stream.finished.is_set():
+            return  # events after the end (a cancelled request's last event)
+        try:
+            out, done = stream.state.feed(ev)
+        except RequestError as e:
+            stream.error = e
+            self._finish(stream)
+            return
+        if stream.sock is None:
+            stream.objects.extend(out)
+        else:
+            self._send(stream, sse(out) + (b"data: [DONE]\n\n" if done else b""))
+        if done and not stream.finished.is_set():
+            self._finish(stream)
+
+    def _send(self, stream: Stream, data: bytes) -> None:
+        if stream.dead:
+            return
+        buf = stream.backlog
+        if buf:
+            buf += data
+            data = bytes(buf)
+        if not data:
+            return
+        try:
+            n = stream.sock.send(data, socket.MSG_DONTWAIT)  # type: ignore[union-attr]
+        except (BlockingIOError, InterruptedError):
+            n = 0
+        except OSError:  # the client went away: stop generating for it
+            stream.dead = True
+            stream.cancel()
+            self._finish(stream)
+            return
+        if n == len(data):
+            buf.clear()
+            self.backlogged.discard(stream)
+            return
+        self.stats["writer_partial_sends"] += 1
+        del buf[:]
+        buf += data[n:]
+        self.backlogged.add(stream)
+        if len(buf) > self.MAX_BACKLOG:
+            stream.dead = True
+            stream.cancel()
+            self._finish(stream)
+
+    def _finish(self, stream: Stream) -> None:
+        self.backlogged.discard(stream)
+        stream.finished.set()
+
+
 class Service:
     """Everything the handlers need: engine worker, tokenizer, served model name."""
 
@@ -136,6 +354,10 @@ class Service:
         self.model_name = model_name
         self.worker = EngineWorker(engine)
         self.worker.start()
+        self.writer: StreamWriter | None = None
+        if os.environ.get("ENGINE_STREAM_WRITER", "1") == "1":
+            self.writer = StreamWriter()
+            self.writer.start()
 
     # ------------------------------------------------------------------ request -> events
     def _events(self, prompt: list[int], sampling) -> tuple[Generation, "queue.Queue[TokenEvent]"]:
@@ -149,67 +371,25 @@ class Service:
 
         Raises ``RequestError`` before the first yield when the engine refuses the request.
         """
-        chat = isinstance(request, ChatRequest)
         gen, q = self._events(prompt, request.sampling)
-        env = Envelope(self.model_name, "chat.completion" if chat else "text_completion")
-        text = _TextStream(self.codec, request.sampling.stop, chat and request.thinking)
-        usage = Usage(len(prompt))
-        ids: list[int] = []
-        finish = "length"
-        first = True
+        state = RequestState(self, request, len(prompt), gen)
         try:
             while True:
-                ev = q.get()
-                if ev.error is not None:
-                    raise RequestError(str(ev.error), ev.error.status)
-                if first:
-                    first = False
-                    usage.cached_tokens = gen.cached_tokens
-                    if request.stream and chat:
-                        yield protocol.chat_chunk(env, {"role": "assistant", "content": ""}, None, None,
-                                                  request.return_token_ids)
-                reasoning = content = ""
-                if ev.token is not None:
-                    ids.append(ev.token)
-                    usage.completion_tokens += 1
-                    reasoning, content = text.push(ev.token)
-                done = ev.finish_reason
-                if text.stopped:
-                    done = "stop"
-                    gen.cancelled.set()
-                    self.worker.wake.set()
-                elif done is not None:
-                    r2, c2 = text.flush()
-                    reasoning, content = reasoning + r2, content + c2
-                    if text.stopped:
-                        done = "stop"
-                if done == "cancelled":
-                    done = "stop"
-                if request.stream:
-                    if chat:
-                        delta: dict[str, Any] = {"content": content}
-                        if reasoning:
-                            delta = {"reasoning_content": reasoning, **({"content": content} if content else {})}
-                        yield protocol.chat_chunk(env, delta, ev.token, done, request.return_token_ids)
-                    else:
-                        yield protocol.completion_chunk(env, content, ev.token, done, request.return_token_ids)
-                if done is not None:
-                    finish = done
+                out, done = state.feed(q.get())
+                yield from out
+                if done:
                     break
-            if request.stream:
-                if request.include_usage:
-                    yield protocol.usage_chunk(env, usage)
-            elif chat:
-                yield protocol.chat_response(env, "".join(text.content),
-                                             "".join(text.reasoning) if request.thinking else None, ids, finish,
-                                             usage, request.return_token_ids)
-            else:
-                yield protocol.completion_response(env, "".join(text.content), ids, finish, usage,
-                                                   request.return_token_ids)
         finally:
             if not gen.done:
                 gen.cancelled.set()  # client went away or the consumer stopped early
                 self.worker.wake.set()
+
+    def open(self, request: CompletionRequest | ChatRequest, prompt: list[int]) -> "Stream":
+        """Submit the request; its events are consumed through the returned ``Stream`` (first by the caller, then by
+        the shared writer thread)."""
+        stream = Stream(self, request, prompt)
+        self.worker.submit(stream.gen)
+        return stream
 
     def tokenize(self, request: CompletionRequest | ChatRequest) -> list[int]:
         if isinstance(request, ChatRequest):
@@ -236,6 +416,8 @@ class Service:
         body.update(self.engine.health())
         if self.codec is not None:
             body.update(self.codec.encoder.stats)
+        if self.writer is not None:
+            body.update(self.writer.stats)
         if looptimers.ENABLED:
             body["loop_timers"] = looptimers.summary()
         if reqstamps.ENABLED:
@@ -297,6 +479,9 @@ class Handler(BaseHTTPRequestHandler):
             prompt = svc.tokenize(request)
             svc.engine.validate(prompt, request.sampling)
             reqstamps.mark(stamp, "tokenized")
+            if svc.writer is not None:
+                self._respond_shared(svc, request, prompt, stamp)
+                return
             events = svc.run(request, prompt)
             first = next(events)  # engine refusals surface here, before any header is sent
         except RequestError as e:
@@ -334,6 +519,55 @@ class Handler(BaseHTTPRequestHandler):
             events.close()  # runs the generator's finally: cancels the generation
         finally:
             self.close_connection = True
+            reqstamps.finish(stamp)
+
+    def _respond_shared(self, svc: "Service", request, prompt: list[int], stamp) -> None:
+        """Answer through the shared writer thread: this thread handles refusals, the headers and the first chunk,
+        then sleeps until the request is finished."""
+        stream = svc.open(request, prompt)
+        try:
+            if not request.stream:
+                stream.hand_over(None)
+                stream.finished.wait()
+                reqstamps.mark(stamp, "first_event")
+                if stream.error is not None:
+                    self._error(str(stream.error), stream.error.status)
+                elif not stream.objects:
+                    self._error("the request produced no response", 500)
+                else:
+                    self._json(200, stream.objects[-1])
+                return
+            try:
+                out, done = stream.next_direct()  # engine refusals surface here, before any header is sent
+            except RequestError as e:
+                self._error(str(e), e.status)
+                return
+            reqstamps.mark(stamp, "first_event")
+            self.send_response(200)
+            self.send_header("Content-Type", "text/event-stream")
+            self.send_header("Cache-Control", "no-cache")
+            self.send_header("Connection", "close")
+            self.end_headers()
+            self.wfile.write(sse(out) + (b"data: [DONE]\n\n" if done else b""))
+            self.wfile.flush()
+            reqstamps.mark(stamp, "first_byte")
+            if not done:
+                stream.hand_over(self.connection)
+                stream.finished.wait()
+                if stream.backlog and not stream.dead:
+                    self.wfile.write(bytes(stream.backlog))  # what the socket had not taken yet: a blocking write now
+                    self.wfile.flush()
+        except (BrokenPipeError, ConnectionResetError, OSError):
+            pass
+        except Exception as e:  # noqa: BLE001
+            try:
+                self._error(f"internal error: {e}", 500)
+            except OSError:
+                pass
+        finally:
+            stream.cancel()  # no-op when the generation is done: the client went away or this thread stopped early
+            if request.stream:
+                self.close_connection = True
             reqstamps.finish(stamp)
 
 
