@@ -155,3 +155,39 @@ def test_writer_keeps_what_a_socket_does_not_take():
     w.MAX_BACKLOG = 16
     w._send(big, b"z" * 17)  # a reader that never reads is given up once its backlog passes the limit
     assert big.dead and big.cancelled == 1 and big.finished.is_set() and big not in w.backlogged
+
+
+def test_stand_in_model_server_isolates_the_host_path():
+    """``bench/null_model_server.py``: with a 5 ms virtual step and 8 streams the served TPOT stays close to 5 ms."""
+    import os
+    import subprocess
+    import sys
+
+    from http_util import ROOT, free_port
+
+    port = free_port()
+    srv = subprocess.Popen([sys.executable, str(ROOT / "bench/null_model_server.py"), "--port", str(port), "--step-ms", "5",
+                            "--max-seqs", "8"], env=dict(os.environ, OMP_NUM_THREADS="2"), cwd=str(ROOT))
+    try:
+        deadline = time.time() + 180
+        while time.time() < deadline:
+            try:
+                if requests.get(f"http://127.0.0.1:{port}/health", timeout=2).status_code == 200:
+                    break
+            except requests.RequestException:
+                time.sleep(0.3)
+        r = subprocess.run([sys.executable, str(ROOT / "bench/serve_bench.py"), "--url", f"http://127.0.0.1:{port}", "--model", "q",
+                            "--vocab", "1000", "--concurrency", "8", "--requests", "8", "--prompt-len", "32", "--output-len", "100"],
+                           capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2000:]
+        out = json.loads(r.stdout.strip().splitlines()[-1])
+        assert out["valid"] and out["output_tokens"] == 800
+        assert 4.5 <= out["tpot_ms"]["p50"] <= 15.0  # the virtual step plus a bounded host share
+        h = requests.get(f"http://127.0.0.1:{port}/health", timeout=5).json()
+        assert h["ahead_steps"] > 50  # run-ahead scheduling is what runs
+    finally:
+        srv.terminate()
+        try:
+            srv.wait(timeout=10)
+        except subprocess.TimeoutExpired:
+            srv.kill()
