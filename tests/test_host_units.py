@@ -180,3 +180,37 @@ def test_affinity_follows_growing_prompts_and_balances_new_sessions():
     r4 = a.route(router.affinity_key("/v1/completions", {"prompt": text}))
     assert a.route(router.affinity_key("/v1/completions", {"prompt": text + " more"})) == r4
     assert a.routed_by_affinity == 3
+
+
+def test_direct_decode_matches_the_tokenizer_wrapper(tmp_path):
+    """The detokenizer's shortcut through the tokenizer's backend gives the wrapper's text, streamed or whole."""
+    import random
+
+    from b200serve.api.text import Detokenizer, decoder_of
+    from b200serve.api.tokenizer import TextCodec
+    from b200serve.models.tiny import write_tiny_checkpoint
+
+    write_tiny_checkpoint(tmp_path)
+    tok = TextCodec(tmp_path).tok
+    dec = decoder_of(tok)
+    assert dec is decoder_of(tok)  # chosen once per tokenizer
+    rng = random.Random(1)
+    ids = [rng.randrange(0, len(tok)) for _ in range(1500)]
+    for i in range(0, 1400, 37):
+        assert dec(ids[i : i + 9]) == tok.decode(ids[i : i + 9], skip_special_tokens=True)
+    det = Detokenizer(tok)
+    parts = [det.push(t) for t in ids] + [det.flush()]
+    assert "".join(parts) == tok.decode(ids, skip_special_tokens=True)
+
+    class Odd:  # a tokenizer whose wrapper post-processes the text: the shortcut must not be taken
+        clean_up_tokenization_spaces = True
+        backend_tokenizer = tok.backend_tokenizer
+
+        def decode(self, ids, skip_special_tokens=True):
+            return tok.decode(ids, skip_special_tokens=skip_special_tokens).replace(" ", "_")
+
+        def __len__(self):
+            return len(tok)
+
+    odd = Odd()
+    assert decoder_of(odd)(ids[:8]) == odd.decode(ids[:8])
