@@ -288,7 +288,12 @@ class StreamWriter(threading.Thread):
                     stream.cancel()
                     self._finish(stream)
             for stream in list(self.backlogged):
-                self._send(stream, b"")
+                try:
+                    self._send(stream, b"")
+                except Exception:  # noqa: BLE001
+                    stream.dead = True
+                    stream.cancel()
+                    self._finish(stream)
 
     def stop(self) -> None:
         self.inbox.put(None)
@@ -521,6 +526,15 @@ class Handler(BaseHTTPRequestHandler):
             self.close_connection = True
             reqstamps.finish(stamp)
 
+    @staticmethod
+    def _await(svc: "Service", stream: "Stream") -> None:
+        """Sleep until the writer thread has finished the request (and notice if that thread is gone)."""
+        while not stream.finished.wait(2.0):
+            if not svc.writer.is_alive():
+                stream.error = stream.error or RequestError("the response writer stopped", 500)
+                stream.cancel()
+                return
+
     def _respond_shared(self, svc: "Service", request, prompt: list[int], stamp) -> None:
         """Answer through the shared writer thread: this thread handles refusals, the headers and the first chunk,
         then sleeps until the request is finished."""
@@ -528,7 +542,7 @@ class Handler(BaseHTTPRequestHandler):
         try:
             if not request.stream:
                 stream.hand_over(None)
-                stream.finished.wait()
+                self._await(svc, stream)
                 reqstamps.mark(stamp, "first_event")
                 if stream.error is not None:
                     self._error(str(stream.error), stream.error.status)
@@ -553,7 +567,7 @@ class Handler(BaseHTTPRequestHandler):
             reqstamps.mark(stamp, "first_byte")
             if not done:
                 stream.hand_over(self.connection)
-                stream.finished.wait()
+                self._await(svc, stream)
                 if stream.backlog and not stream.dead:
                     self.wfile.write(bytes(stream.backlog))  # what the socket had not taken yet: a blocking write now
                     self.wfile.flush()
