@@ -25,6 +25,7 @@ namespace b200 {
 
 constexpr int BM = 128;  // weight rows per tile (TMEM lanes)
 constexpr int BK = 64;   // bf16 per operand row per stage (128 bytes)
+constexpr int GATHER_BT_MAX = 64;  // widest token tile whose rows the grouped GEMM's producer warp can fetch by index
 constexpr int UMMA_K = 16;
 constexpr int MAX_DEVICES = 64;  // per-device launch state (function attributes, SM counts)
 
@@ -53,7 +54,7 @@ struct GemmParams {
   int y_rot;         // dense sequence-parallel GEMMs: token tile = (blockIdx.y + y_rot) % gridDim.y, so that each rank
                      // starts with the tiles whose data (or whose consumer) is furthest from being the bottleneck
   int grid_y;        // dense: number of token tiles (set by the launcher)
-  const int* gather_rows;  // grouped, token tiles <= 32 rows: sorted position -> row of `gx`; the producer warp then
+  const int* gather_rows;  // grouped, token tiles <= 64 rows: sorted position -> row of `gx`; the producer warp then
                      // fetches each activation row by index (16-byte async copies into the swizzled operand layout)
                      // instead of reading an expert-sorted copy through the tensor map
   const bf16* gx;    // gather source [rows, ldgx]
@@ -126,7 +127,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   if (threadIdx.x == 0) {
     // a gathering producer: lane 0's expect_tx arrival for the weight tile plus one arrival per lane when that
     // lane's row copies have landed
-    const uint32_t full_count = (GROUPED && BT <= 32 && p.gather_rows != nullptr) ? 33 : 1;
+    const uint32_t full_count = (GROUPED && BT <= GATHER_BT_MAX && p.gather_rows != nullptr) ? 33 : 1;
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], full_count); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
     *abort_flag = 0;
@@ -155,7 +156,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
   };
 
-  if (warp == 0 && GROUPED && BT <= 32 && p.gather_rows != nullptr) {
+  if (warp == 0 && GROUPED && BT <= GATHER_BT_MAX && p.gather_rows != nullptr) {
     // ---------------- gathering producer (all 32 lanes): weights by TMA from lane 0, activation rows by index.
     // Chunk q = lane + 32 i of a k-block is bytes [16 (q & 7), +16) of tile row q >> 3; it lands where the 128-byte
     // swizzle of the K-major operand layout puts it: row r at (r >> 3) * 1024 + (r & 7) * 128, chunk j at
@@ -273,7 +274,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         ok = mbar_wait(&full[s], ph, p.err, ERR_WAIT_FULL, abort_flag);
         if (!ok) break;
         // rows that the gathering producer wrote through the generic proxy must be visible to the tensor core's reads
-        if (GROUPED && BT <= 32 && p.gather_rows != nullptr) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (GROUPED && BT <= GATHER_BT_MAX && p.gather_rows != nullptr) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
         const uint32_t b_addr = a_addr + C::A_TILES * C::A_BYTES;
@@ -700,10 +701,10 @@ extern "C" int b200_gemm_grouped(const void* X, const void* W, void* out, int ca
                                  int ldo, int epi, int up_offset, int bt, const void* tiles, const int* n_tiles,
                                  int max_tiles, int* err, int splits, int packed, const int* gather_rows, int ldx,
                                  cudaStream_t st) {
-  // gather_rows != null (token tiles of at most 32 rows): X is [any rows, ldx] and sorted position i reads row
+  // gather_rows != null (token tiles of at most 64 rows): X is [any rows, ldx] and sorted position i reads row
   // gather_rows[i] of it; otherwise X is the expert-sorted buffer [cap, K] itself.
   if (max_tiles <= 0) return 0;
-  if (gather_rows != nullptr && (bt > 32 || splits > 1 || ldx % 8)) return -7;
+  if (gather_rows != nullptr && (bt > GATHER_BT_MAX || splits > 1 || ldx % 8)) return -7;
   if (splits < 1 || splits > 8 || splits > (K + BK - 1) / BK) splits = 1;
   CUtensorMap tw, tx;
   GemmParams p{N, K, cap, ldo, out, reinterpret_cast<const int4*>(tiles), n_tiles, up_offset, nullptr, nullptr, err, nullptr, CommCtx{}, 0, nullptr, nullptr, splits, nullptr, {}};

@@ -475,3 +475,25 @@ def test_ivf_pick_kernel_scores_the_probed_clusters_exactly(C, packed):
     out = torch.empty(R, dtype=torch.int64, device="cuda")
     assert idx.pick(C, h, w, out=out) is out and torch.equal(out, got)
     C.check_errors(h.device)
+
+
+@pytest.mark.parametrize("T,E,k,H,I,packed", [(700, 64, 4, 256, 128, False), (600, 16, 4, 2048, 512, True), (2500, 32, 8, 512, 256, True)])
+def test_row_gather_inside_the_64_row_grouped_gemm_is_bitwise_neutral(C, T, E, k, H, I, packed):
+    """Prefill-size MoE blocks use 64-row token tiles; fetching their rows by index inside the gate/up GEMM must give
+    the bits of the path that first copies the rows into expert order."""
+    x = _bf(T, H, seed=33)
+    router = _bf(E + 1, H, scale=0.3, seed=34)
+    wgu, wd = _bf(E + 1, 2 * I, H, scale=0.05, seed=35), _bf(E + 1, H, I, scale=0.05, seed=36)
+    if packed:
+        router, wgu, wd = C.pack_weight(router), C.pack_weight(wgu, gate_up=True), C.pack_weight(wd)
+    assert C.moe_bt(T, k + 1, E) == 64
+    keep = C.GATHER_MAX_BT
+    try:
+        C.GATHER_MAX_BT = 0
+        copied = C.moe_block(x, router, wgu, wd, E, k, True)
+        C.GATHER_MAX_BT = 64
+        gathered = C.moe_block(x, router, wgu, wd, E, k, True)
+    finally:
+        C.GATHER_MAX_BT = keep
+    C.check_errors(x.device)
+    assert torch.equal(gathered, copied)
