@@ -59,6 +59,11 @@ def _lib():
 
 
 class EpMoE:
+    # widest token tile whose rows the gate/up GEMM fetches by index from the receive buffer; wider tiles (prefill-size
+    # blocks) are compacted into expert order first. The local block gathers up to 64 rows; here the 32-row form is the
+    # one measured on 2 and 4 GPUs.
+    GATHER_MAX_BT = 32
+
     def __init__(self, device: torch.device, group, n_experts: int, hidden: int, top_k: int, max_rows: int,
                  capacity_factor: float | None = None, wait_s: float = 1.0) -> None:
         """``max_rows``: most rows any rank brings to one call. Every rank keeps one receive region per source rank;
@@ -216,7 +221,7 @@ class EpMoE:
         codes.append(("plan", L.b200_ep_plan(C, bt, w["tiles"].data_ptr(), n_tiles.data_ptr(), w["max_tiles"],
                              w["gather_rows"].data_ptr(), w["ret_meta"].data_ptr(), n_rows.data_ptr(), st)))
         err = cuda_ops.err_word(dev)
-        if bt <= cuda_ops.GATHER_MAX_BT:
+        if bt <= min(cuda_ops.GATHER_MAX_BT, self.GATHER_MAX_BT):
             codes.append(("gate_up(gather)", K.b200_gemm_grouped(self._own["xs"], w_gate_up_local.data_ptr(), w["act"].data_ptr(), self.cap_rows,
                                       self.per + 1, inter, 2 * inter, H, inter, cuda_ops.EPI_SILU_MUL, inter, bt,
                                       w["tiles"].data_ptr(), n_tiles.data_ptr(), w["max_tiles"], err.data_ptr(), 1,
