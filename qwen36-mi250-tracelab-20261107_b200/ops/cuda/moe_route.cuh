@@ -2,7 +2,11 @@
 // expert-parallel dispatch (ep_moe.cu).
 #pragma once
 
+#ifdef B200_EMU  // host build of the routing body for tests/emu (shuffles and atomics come from the shim)
+#include "emu_shim.h"
+#else
 #include "common.cuh"
+#endif
 
 namespace b200 {
 

@@ -6,6 +6,7 @@
 // (The reference checks its HIP kernel the same way: tools/emu/gdn_hip_emu.cpp, tools/emu/gdn_hip_emu_shim.h.)
 #pragma once
 
+#include <atomic>
 #include <barrier>
 #include <cmath>
 #include <cstdint>
@@ -71,6 +72,21 @@ inline float warp_sum(float v) {
   for (int o = 16; o > 0; o >>= 1) v += shfl_xor(v, o);
   return v;
 }
+inline float warp_max(float v) {
+  for (int o = 16; o > 0; o >>= 1) v = std::fmax(v, shfl_xor(v, o));
+  return v;
+}
+// The CUDA spelling of the shuffle, for 4-byte values (the routing kernel exchanges a float and an int per round).
+template <typename T>
+inline T __shfl_xor_sync(unsigned, T v, int mask) {
+  static_assert(sizeof(T) == sizeof(float), "4-byte values only");
+  float f;
+  std::memcpy(&f, &v, sizeof f);
+  f = shfl_xor(f, mask);
+  std::memcpy(&v, &f, sizeof f);
+  return v;
+}
+inline int atomicAdd(int* p, int v) { return std::atomic_ref<int>(*p).fetch_add(v); }
 
 enum ErrCode : int { ERR_NONE = 0, ERR_WAIT_FULL = 1 };
 inline void mbar_init(uint64_t*, uint32_t) {}

@@ -17,3 +17,14 @@ def test_gdn_step_kernel_body_on_the_host(tmp_path):
     assert build.returncode == 0, build.stderr[-3000:]
     run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
     assert run.returncode == 0 and run.stdout.startswith("OK"), run.stdout + run.stderr
+
+
+def test_router_row_body_on_the_host(tmp_path):
+    """``ops/cuda/moe_route.cuh`` (softmax, top-k with ties to the lower id, renormalised bf16 weights, expert map,
+    counts) compiled as host C++: one std::thread per lane, shuffles through the shim, against float64."""
+    exe = tmp_path / "route_emu"
+    build = subprocess.run(["g++", "-std=c++20", "-O1", "-pthread", "-DB200_EMU", "-I", str(ROOT / "tests/emu"), "-x", "c++",
+                            str(ROOT / "tests/emu/route_emu.cpp"), "-o", str(exe)], capture_output=True, text=True, timeout=300)
+    assert build.returncode == 0, build.stderr[-3000:]
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0 and run.stdout.startswith("OK"), run.stdout + run.stderr
