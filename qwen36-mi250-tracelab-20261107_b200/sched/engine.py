@@ -31,7 +31,7 @@ from ..models.qwen36 import Model, PackedBatch
 from ..ops import torch_ops
 from ..obs import looptimers
 from .request import EngineError, Generation, Sampling, TokenEvent
-from .sampling import pick_token
+from .sampling import pick_tokens
 
 
 def _select_ops(device: torch.device):
@@ -539,11 +539,13 @@ class Engine:
             if greedy is None:
                 greedy = self.model.greedy(hidden)
             picks = greedy[: len(gens)].tolist()
-            logits = self.model.logits(hidden[torch.tensor(need, device=self.device)]).float().cpu()
-            for j, i in enumerate(need):
-                g = gens[i]
-                mask_eos = len(g.output) < g.sampling.min_tokens
-                picks[i] = pick_token(logits[j], g.sampling, g.rng, self.eos if mask_eos else None)
+            # sampled / EOS-masked rows: filtered and drawn on the device, only the picked ids come back
+            logits = self.model.logits(hidden[torch.tensor(need, device=self.device)])
+            rows = [gens[i] for i in need]
+            chosen = pick_tokens(logits, [g.sampling for g in rows], [g.rng for g in rows],
+                                 [self.eos if len(g.output) < g.sampling.min_tokens else None for g in rows])
+            for i, tok in zip(need, chosen):
+                picks[i] = tok
         for g, tok in zip(gens, picks):
             self._accept_token(g, int(tok))
 

@@ -21,7 +21,7 @@ from dataclasses import dataclass, field
 import torch
 
 from ..models.qwen36 import PackedBatch
-from ..sched.sampling import pick_token
+from ..sched.sampling import pick_tokens
 
 DECAY = 0.9
 
@@ -250,11 +250,10 @@ class SpecController:
         need = [i for i, g in enumerate(gens) if eng._needs_logits(g)]
         if need:
             rows0 = torch.tensor([i * G for i in need], device=eng.device)
-            logits = eng.model.logits(hidden[rows0]).float().cpu()
-            for j, i in enumerate(need):
-                g = gens[i]
-                mask_eos = len(g.output) < g.sampling.min_tokens
-                sampled[i] = pick_token(logits[j], g.sampling, g.rng, eng.eos if mask_eos else None)
+            rows = [gens[i] for i in need]
+            chosen = pick_tokens(eng.model.logits(hidden[rows0]), [g.sampling for g in rows], [g.rng for g in rows],
+                                 [eng.eos if len(g.output) < g.sampling.min_tokens else None for g in rows])
+            sampled.update(zip(need, chosen))
             fix = torch.tensor([[i * G, t] for i, t in sampled.items()], device=eng.device)
             picks = picks.clone()
             picks[fix[:, 0]] = fix[:, 1]
