@@ -86,3 +86,26 @@ def test_packed_and_long_spans_run_the_general_path():
     long_prompt = torch.randint(3, 1024, (1500,), generator=g).tolist()
     out = big.generate([long_prompt], s)[0]
     assert big.stats["prefill_graph_passes"] == 0 and len(out.output) == 4  # 1,500 tokens exceed the largest graph
+
+
+def test_warmup_builds_every_padded_size_and_the_bench_tool_runs_without_a_gpu():
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from b200serve.config import ModelConfig
+    from b200serve.models.checkpoint import random_weights
+
+    w = random_weights(ModelConfig.tiny(), seed=0, dtype=torch.float32, std=0.05, lm_head_std=0.5)
+    eng = _engine(w, False, True, chunk=2048)
+    eng.warmup()
+    assert sorted(eng._pgraphs.buckets) == [128, 256, 512, 1024] and not eng._pgraphs.errors
+    assert eng.stats["prefill_graph_passes"] == 0  # counters start from zero after the warm-up
+    root = Path(__file__).resolve().parents[1]
+    r = subprocess.run([sys.executable, str(root / "bench/prefill_graph_bench.py"), "--tiny", "--start", "200", "--news", "20,90", "--reps", "1"],
+                       capture_output=True, text=True, timeout=600, env={**__import__("os").environ, "CUDA_VISIBLE_DEVICES": ""})
+    assert r.returncode == 0, r.stderr[-2000:]
+    rows = [json.loads(ln) for ln in r.stdout.strip().splitlines() if ln.startswith("{")]
+    assert [x["new_tokens"] for x in rows] == [20, 90] and [x["graph_rows"] for x in rows] == [128, 256]
+    assert all(x["last_row_max_abs_diff"] < 1e-4 for x in rows)
