@@ -89,10 +89,13 @@ class StopMatcher:
         if not self.stops:
             return text
         buf = self.held + text
-        hits = [i for i in (buf.find(s) for s in self.stops) if i >= 0]
+        # the stop string that is complete first wins (of two that end together, the one that starts earlier), which
+        # is what arrives first when the text comes in one character at a time: the cut does not depend on how the
+        # text was chunked, even for stop strings that overlap
+        hits = [(i + len(s), i) for s, i in ((s, buf.find(s)) for s in self.stops) if i >= 0]
         if hits:
             self.stopped, self.held = True, ""
-            return buf[: min(hits)]
+            return buf[: min(hits)[1]]
         n_out = max(len(buf) - self.keep, 0)
         self.held = buf[n_out:]
         return buf[:n_out]
