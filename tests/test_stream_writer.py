@@ -191,3 +191,49 @@ def test_stand_in_model_server_isolates_the_host_path():
             srv.wait(timeout=10)
         except subprocess.TimeoutExpired:
             srv.kill()
+
+
+def test_random_clients_with_disconnects_leave_a_clean_server(server):
+    """24 concurrent clients, streaming or not, some of which hang up mid-stream: every finished request equals the
+    same request sent alone afterwards, and nothing stays behind in the engine."""
+    import random
+    from concurrent.futures import ThreadPoolExecutor
+
+    rng = random.Random(4)
+    jobs = []
+    for i in range(24):
+        n = rng.randrange(4, 40)
+        jobs.append(dict(prompt=[rng.randrange(5, 500) for _ in range(rng.randrange(3, 120))], max_tokens=n,
+                         stream=rng.random() < 0.7, hang_up_after=rng.randrange(1, n) if rng.random() < 0.3 else None))
+
+    def body(j):
+        return {"model": server.model, "prompt": j["prompt"], "max_tokens": j["max_tokens"], "temperature": 0, "ignore_eos": True,
+                "return_token_ids": True}
+
+    def run(j):
+        if not j["stream"]:
+            r = server.post("/v1/completions", body(j))
+            assert r.status_code == 200
+            return r.json()["choices"][0]["token_ids"]
+        ids = []
+        with requests.post(server.url + "/v1/completions", json={**body(j), "stream": True}, stream=True, timeout=120) as r:
+            r.raise_for_status()
+            for line in r.iter_lines():
+                if not line.startswith(b"data: ") or line == b"data: [DONE]":
+                    continue
+                for ch in json.loads(line[6:]).get("choices", []):
+                    ids.extend(ch.get("token_ids") or [])
+                if j["hang_up_after"] is not None and len(ids) >= j["hang_up_after"]:
+                    return ids  # leaving the block closes the connection mid-stream
+        return ids
+
+    with ThreadPoolExecutor(max_workers=24) as pool:
+        got = list(pool.map(run, jobs))
+    h = _idle(server, timeout=60)
+    assert h["running"] == 0 and h["prefilling"] == 0 and h["status"] == "ok"
+    for j, ids in zip(jobs, got):
+        alone = server.post("/v1/completions", body(j)).json()["choices"][0]["token_ids"]
+        if j["stream"] and j["hang_up_after"] is not None:
+            assert ids == alone[: len(ids)] and len(ids) >= j["hang_up_after"]
+        else:
+            assert ids == alone and len(ids) == j["max_tokens"]
