@@ -23,8 +23,6 @@
 
 namespace b200 {
 
-constexpr int TC_CH = 64;
-
 struct ChunkInfoTc {  // same layout as gdn_prefill.cu's ChunkInfo
   int seg, row0, nrows, first;
 };

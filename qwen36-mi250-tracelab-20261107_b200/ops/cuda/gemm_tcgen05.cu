@@ -652,7 +652,9 @@ static int dispatch_bt(int bt, const CUtensorMap& tw, const CUtensorMap& tx, con
     case 32: return launch<32, EPI, GROUPED>(tw, tx, p, grid_y, st);
     case 64: return launch<64, EPI, GROUPED>(tw, tx, p, grid_y, st);
     case 128: return launch<128, EPI, GROUPED>(tw, tx, p, grid_y, st);
-    case 256: if (EPI != EPI_SILU_MUL) return launch<(EPI != EPI_SILU_MUL ? 256 : 128), EPI, GROUPED>(tw, tx, p, grid_y, st);
+    case 256:
+      if (EPI != EPI_SILU_MUL) return launch<(EPI != EPI_SILU_MUL ? 256 : 128), EPI, GROUPED>(tw, tx, p, grid_y, st);
+      return -5;  // the gate/up epilogue has no 256-row form
     default: return -5;
   }
 }
