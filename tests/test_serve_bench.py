@@ -61,7 +61,7 @@ def test_host_probes_run_without_a_gpu(tmp_path):
 
 def test_service_checker_against_a_tiny_server(tmp_path):
     """Determinism and stream == non-stream hold on a random-weight server; the echo gate, which needs a real model,
-    fails there and turns the verdict (and the exit code) to a failure."""
+    fails there and turns the overall result (and the exit code) to a failure."""
     import importlib.util
     from pathlib import Path
 
