@@ -3,7 +3,7 @@
     python bench/serve_bench.py --url http://127.0.0.1:8000 --model NAME --vocab 248320 \
         --concurrency 256 --requests 256 --prompt-len 2048 --output-len 256            # 256 simultaneous requests
     python bench/serve_bench.py ... --sessions 64 --rounds 4-8 --rate 4 --first-len 6000 \
-        --grow 100-2000 --output-len 50-800                                            # multi-round sessions   
+        --grow 100-2000 --output-len 50-800                                            # multi-round sessions
 
 Requests stream token ids (``return_token_ids``), greedy, ``ignore_eos``, exact ``max_tokens``;
 every token's arrival time is recorded on the client. Definitions (same as the reference's own probe,
