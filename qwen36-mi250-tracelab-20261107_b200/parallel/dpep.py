@@ -11,7 +11,8 @@ message carries "a device-side failure was seen" and "shutting down", so that al
 together instead of waiting for a peer that is gone.
 
 The reference has neither expert parallelism nor shared passes between its replicas (``engine/router.py:1-27``:
-independent replicas behind a front); this is the serving form of the BASELINE expert-parallel configuration.
+independent replicas behind a front); this is the serving form of data-parallel attention over expert-parallel MoE
+blocks (``parallel/ep.py``).
 ``GlooEpMoE`` is the CPU stand-in of the NVLink kernels (object all-gathers over gloo, same arithmetic as the
 single-process block) with which the scheduling is tested without GPUs.
 """

@@ -7,7 +7,8 @@ sorts the received rows by expert without moving them, the grouped gate/up GEMM 
 those rows by index, the grouped down GEMM whose epilogue scatters every output row back to its owner
 (the combine all-to-all), and the top-k weighted sum (with the residual add and next RMSNorm). Kernels: ``ops/cuda/ep_moe.cu`` and the ``EPI_SCATTER`` epilogue of
 ``ops/cuda/gemm_tcgen05.cu``; buffers are CUDA IPC symmetric memory as in ``parallel/symm.py``.
-The reference has no expert parallelism; this is the BASELINE configuration's EP path.
+The reference has no expert parallelism (``engine/fast/tp.py:19-21``: tensor parallelism over two devices only);
+this block is what lets the experts of the 35B model be spread over 2, 4 or 8 GPUs with data-parallel attention.
 """
 
 from __future__ import annotations
