@@ -432,6 +432,20 @@ class Service:
         return body
 
 
+def metrics_text(health: dict[str, Any]) -> str:
+    """The numeric fields of ``/health`` in the Prometheus text exposition format (one gauge each, prefix
+    ``engine_``), plus ``engine_up`` (1 while the status is ``ok`` or ``degraded``). The reference reports its
+    counters on ``/health`` only (``engine/server.py:498-512``); this is the same data for a scraper."""
+    lines = ["# TYPE engine_up gauge", f"engine_up {0 if health.get('status') == 'unavailable' else 1}"]
+    for key in sorted(health):
+        v = health[key]
+        if isinstance(v, bool) or not isinstance(v, (int, float)):
+            continue
+        name = "engine_" + "".join(c if c.isalnum() else "_" for c in key)
+        lines += [f"# TYPE {name} gauge", f"{name} {v}"]
+    return "\n".join(lines) + "\n"
+
+
 class Handler(BaseHTTPRequestHandler):
     protocol_version = "HTTP/1.1"
     service: Service  # set on the server class
@@ -459,6 +473,13 @@ class Handler(BaseHTTPRequestHandler):
             self._json(503 if body["status"] == "unavailable" else 200, body)
         elif self.path == "/v1/models":
             self._json(200, protocol.models_body(svc.model_name, svc.engine.max_model_len))
+        elif self.path == "/metrics":
+            data = metrics_text(svc.health()).encode()
+            self.send_response(200)
+            self.send_header("Content-Type", "text/plain; version=0.0.4; charset=utf-8")
+            self.send_header("Content-Length", str(len(data)))
+            self.end_headers()
+            self.wfile.write(data)
         else:
             self._error(f"no route {self.path}", 404)
 

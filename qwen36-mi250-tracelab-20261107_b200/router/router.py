@@ -297,6 +297,16 @@ class FrontHandler(BaseHTTPRequestHandler):
         if self.path == "/health":
             status, body = front.health()
             self._json(status, body)
+        elif self.path == "/metrics":  # the summed counters of all replicas, in the scraper's text format
+            from ..api.server import metrics_text
+
+            _, body = front.health()
+            data = metrics_text(body).encode()
+            self.send_response(200)
+            self.send_header("Content-Type", "text/plain; version=0.0.4; charset=utf-8")
+            self.send_header("Content-Length", str(len(data)))
+            self.end_headers()
+            self.wfile.write(data)
         else:
             self._relay(front.replicas[0], None)
 

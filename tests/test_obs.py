@@ -90,3 +90,21 @@ def test_health_carries_timers_and_stamps_when_switched_on():
         assert h["native_loads_while_serving"] == 0
     finally:
         s.stop()
+
+
+def test_metrics_endpoint_mirrors_the_numeric_health_fields():
+    from b200serve.api.server import metrics_text
+
+    text = metrics_text({"status": "ok", "decode_steps": 12, "kv_pages_free": 7.5, "broken": None, "flag": True, "odd key-name": 3})
+    assert "engine_up 1\n" in text and "engine_decode_steps 12\n" in text and "engine_kv_pages_free 7.5\n" in text
+    assert "engine_odd_key_name 3\n" in text and "flag" not in text and "broken" not in text
+    assert "engine_up 0\n" in metrics_text({"status": "unavailable"})
+    s = ServerProc("random:tiny", env={"CUDA_VISIBLE_DEVICES": ""})
+    try:
+        s.completion(list(range(10, 40)), 4)
+        r = requests.get(s.url + "/metrics", timeout=10)
+        assert r.status_code == 200 and r.headers["content-type"].startswith("text/plain")
+        values = dict(ln.split(" ") for ln in r.text.splitlines() if ln and not ln.startswith("#"))
+        assert values["engine_up"] == "1" and int(values["engine_finished"]) == 1 and int(values["engine_decoded_tokens"]) >= 3
+    finally:
+        s.stop()

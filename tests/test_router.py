@@ -70,6 +70,9 @@ def test_sessions_stay_on_their_replica_and_hit_its_cache(front):
     per = [b["requests"] for b in h1["per_replica"]]
     assert per == [2, 2]  # two sessions, one per replica, both rounds each
     assert "request_stamps" in h1["per_replica"][0]
+    m = requests.get(front + "/metrics")  # the summed counters of both replicas for a scraper
+    vals = dict(ln.split(" ") for ln in m.text.splitlines() if ln and not ln.startswith("#"))
+    assert m.status_code == 200 and vals["engine_up"] == "1" and int(vals["engine_requests"]) == 4 and vals["engine_replicas"] == "2"
 
 
 def test_errors_and_non_streaming_pass_through(front):
