@@ -244,7 +244,9 @@ class EngineConfig:
     kv_fraction: float = 0.85
     reserve_gb: float = 6.0
     prefill_pack_tokens: int = 8192
-    one_pass_max: int = 4096
+    # an uncached prompt part of at most this many tokens is prefilled as one span without a snapshot (0: always
+    # chunk-aligned spans with a snapshot at the last chunk boundary, so that other requests can share the prefix)
+    one_pass_max: int = 0
     decode_buckets: tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64, 128, 256)
     cuda_graphs: bool = True
     graphs_on_cpu: bool = False  # tests: run the decode-graph scheduling (buckets, run-ahead) without a CUDA device

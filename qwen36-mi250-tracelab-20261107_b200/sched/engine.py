@@ -227,9 +227,17 @@ class Engine:
         gen.cached_tokens = gen.computed
         gen.mtp_computed = 0
         L = len(gen.prompt)
-        gen.spans = self._spans(gen.computed, L)
-        boundary = (L - 1) // self.chunk * self.chunk
-        gen.snapshot_at = boundary if boundary > gen.computed else 0
+        if 0 < self.cfg.one_pass_max and L - gen.computed <= self.cfg.one_pass_max:
+            # the uncached part in ONE span, the last token included: one pass, and no state snapshot on the way (the
+            # reference's default for parts of up to 4096 tokens, engine/generator.py:795-816; its sessions resume
+            # from their tails). Off by default here: the snapshot at the last chunk boundary is what lets DIFFERENT
+            # requests share a common prefix such as a system prompt.
+            gen.spans = [(gen.computed, L)]
+            gen.snapshot_at = 0
+        else:
+            gen.spans = self._spans(gen.computed, L)
+            boundary = (L - 1) // self.chunk * self.chunk
+            gen.snapshot_at = boundary if boundary > gen.computed else 0
         if gen.sampling.max_tokens is None:
             gen.sampling.max_tokens = self.max_model_len - L
         if gen.sampling.seed is not None or not gen.sampling.greedy:

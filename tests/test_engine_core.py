@@ -113,3 +113,23 @@ def test_seeded_sampling_is_reproducible(weights):
     a = _engine(weights).generate([p], s)[0].output
     b = _engine(weights).generate([p], s)[0].output
     assert a == b and len(a) == 12
+
+
+def test_one_pass_prefill_runs_a_short_prompt_as_one_span_without_a_snapshot(weights):
+    """``one_pass_max``: the uncached part of a prompt in one pass, the reference's default for up to 4096 tokens;
+    same tokens as the chunked form, tails still resume, but no chunk-boundary state is kept for other requests."""
+    p = _prompts(1, seed=21)[0] * 3  # several chunks long
+    s = Sampling(max_tokens=6, ignore_eos=True)
+    chunked, one = _engine(weights), _engine(weights, one_pass_max=4096)
+    a = chunked.generate([p], s)[0]
+    b = one.generate([p], s)[0]
+    assert a.output == b.output
+    assert one.stats["prefill_passes"] == 1 < chunked.stats["prefill_passes"]
+    other = p[: len(p) - 5] + [3, 4, 5, 6, 7, 8]  # diverges near the end: only a chunk-boundary snapshot could help
+    assert chunked.generate([other], s)[0].cached_tokens > 0
+    assert one.generate([other], s)[0].cached_tokens == 0
+    nxt = p + a.output + [9, 9, 9]  # the next turn of the same session resumes from the tail either way
+    ra, rb = chunked.generate([nxt], s)[0], one.generate([nxt], s)[0]
+    assert ra.output == rb.output and rb.cached_tokens >= len(p)
+    long_one = _engine(weights, one_pass_max=50)  # a part longer than the limit is chunked as before
+    assert long_one.generate([p], s)[0].output == a.output and long_one.stats["prefill_passes"] > 1
