@@ -107,6 +107,12 @@ class Engine:
             mtp_verify_steps=0, mtp_proposed=0, mtp_accepted=0, device_errors=0, step_errors=0, ahead_steps=0,
             prefill_graph_passes=0,
         )
+        if c.loop_timers:  # the switches also come in through the configuration, not only the environment
+            looptimers.ENABLED = True
+        if c.req_stamps:
+            from ..obs import reqstamps
+
+            reqstamps.ENABLED = True
         self._graphs = None
         # library collectives (the NCCL baseline path) stay out of CUDA graphs; the fused NVLink kernels go in
         emulate = c.cuda_graphs and c.graphs_on_cpu and self.device.type != "cuda"
