@@ -305,6 +305,9 @@ class EngineConfig:
         buckets = os.environ.get("ENGINE_DECODE_BUCKETS")
         if buckets:
             cfg.decode_buckets = tuple(sorted({int(b) for b in buckets.split(",")}))
+        rows = os.environ.get("ENGINE_PREFILL_GRAPH_ROWS")
+        if rows:
+            cfg.prefill_graph_rows = tuple(sorted({int(r) for r in rows.split(",")}))
         for k, v in overrides.items():
             if v is not None:
                 setattr(cfg, k, v)
