@@ -28,3 +28,30 @@ def test_router_row_body_on_the_host(tmp_path):
     assert build.returncode == 0, build.stderr[-3000:]
     run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
     assert run.returncode == 0 and run.stdout.startswith("OK"), run.stdout + run.stderr
+
+
+def _tsan_build(src, exe, defines=()):
+    return subprocess.run(["g++", "-std=c++20", "-O1", "-g", "-pthread", "-fsanitize=thread", *defines, "-I", str(ROOT / "tests/emu"),
+                           "-x", "c++", str(src), "-o", str(exe)], capture_output=True, text=True, timeout=600)
+
+
+def test_emulated_kernels_have_no_data_race_and_a_missing_barrier_would_show(tmp_path):
+    """The host builds of the device kernels under ThreadSanitizer (one std::thread per CUDA thread): no race in the
+    GDN step kernel or in the router's row body. The control program shows what the check is worth: the same shim
+    with a barrier left out is reported, with it is not."""
+    import pytest
+
+    control = tmp_path / "race_control"
+    b = _tsan_build(ROOT / "tests/emu/race_control.cpp", control)
+    if b.returncode != 0:
+        pytest.skip("this toolchain has no ThreadSanitizer: " + b.stderr[-300:])
+    ok = subprocess.run([str(control), "with-barrier"], capture_output=True, text=True, timeout=300)
+    assert ok.returncode == 0 and "ThreadSanitizer" not in ok.stderr
+    bad = subprocess.run([str(control), "without-barrier"], capture_output=True, text=True, timeout=300)
+    assert "ThreadSanitizer: data race" in bad.stderr
+    for name in ("gdn_step_emu", "route_emu"):
+        exe = tmp_path / (name + "_tsan")
+        b = _tsan_build(ROOT / f"tests/emu/{name}.cpp", exe, ("-DB200_EMU",))
+        assert b.returncode == 0, b.stderr[-3000:]
+        run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=600)
+        assert run.returncode == 0 and run.stdout.startswith("OK") and "ThreadSanitizer" not in run.stderr, run.stderr[-3000:]
