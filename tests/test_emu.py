@@ -30,6 +30,16 @@ def test_router_row_body_on_the_host(tmp_path):
     assert run.returncode == 0 and run.stdout.startswith("OK"), run.stdout + run.stderr
 
 
+def test_conv_step_kernel_body_on_the_host(tmp_path):
+    """``gdn_conv_step_kernel<4>``: window, weights, SiLU, the state left in the slot and the per-row state ring."""
+    exe = tmp_path / "gdn_conv_emu"
+    build = subprocess.run(["g++", "-std=c++20", "-O1", "-pthread", "-DB200_EMU", "-I", str(ROOT / "tests/emu"), "-x", "c++",
+                            str(ROOT / "tests/emu/gdn_conv_emu.cpp"), "-o", str(exe)], capture_output=True, text=True, timeout=300)
+    assert build.returncode == 0, build.stderr[-3000:]
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0 and run.stdout.startswith("OK"), run.stdout + run.stderr
+
+
 def _tsan_build(src, exe, defines=()):
     return subprocess.run(["g++", "-std=c++20", "-O1", "-g", "-pthread", "-fsanitize=thread", *defines, "-I", str(ROOT / "tests/emu"),
                            "-x", "c++", str(src), "-o", str(exe)], capture_output=True, text=True, timeout=600)
@@ -49,7 +59,7 @@ def test_emulated_kernels_have_no_data_race_and_a_missing_barrier_would_show(tmp
     assert ok.returncode == 0 and "ThreadSanitizer" not in ok.stderr
     bad = subprocess.run([str(control), "without-barrier"], capture_output=True, text=True, timeout=300)
     assert "ThreadSanitizer: data race" in bad.stderr
-    for name in ("gdn_step_emu", "route_emu"):
+    for name in ("gdn_step_emu", "gdn_conv_emu", "route_emu"):
         exe = tmp_path / (name + "_tsan")
         b = _tsan_build(ROOT / f"tests/emu/{name}.cpp", exe, ("-DB200_EMU",))
         assert b.returncode == 0, b.stderr[-3000:]
