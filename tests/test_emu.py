@@ -40,6 +40,17 @@ def test_conv_step_kernel_body_on_the_host(tmp_path):
     assert run.returncode == 0 and run.stdout.startswith("OK"), run.stdout + run.stderr
 
 
+def test_expert_plan_kernels_on_the_host(tmp_path):
+    """``ops/cuda/moe_plan.cuh``: 1024-thread CTAs (shared-memory histogram, two-level scans over warp shuffles,
+    scatter through per-expert cursors, the ticket by which the last CTA of a grid builds the plan) as host C++."""
+    exe = tmp_path / "plan_emu"
+    build = subprocess.run(["g++", "-std=c++20", "-O1", "-pthread", "-DB200_EMU", "-I", str(ROOT / "tests/emu"), "-x", "c++",
+                            str(ROOT / "tests/emu/plan_emu.cpp"), "-o", str(exe)], capture_output=True, text=True, timeout=300)
+    assert build.returncode == 0, build.stderr[-3000:]
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0 and run.stdout.startswith("OK"), run.stdout + run.stderr
+
+
 def _tsan_build(src, exe, defines=()):
     return subprocess.run(["g++", "-std=c++20", "-O1", "-g", "-pthread", "-fsanitize=thread", *defines, "-I", str(ROOT / "tests/emu"),
                            "-x", "c++", str(src), "-o", str(exe)], capture_output=True, text=True, timeout=600)
@@ -59,7 +70,7 @@ def test_emulated_kernels_have_no_data_race_and_a_missing_barrier_would_show(tmp
     assert ok.returncode == 0 and "ThreadSanitizer" not in ok.stderr
     bad = subprocess.run([str(control), "without-barrier"], capture_output=True, text=True, timeout=300)
     assert "ThreadSanitizer: data race" in bad.stderr
-    for name in ("gdn_step_emu", "gdn_conv_emu", "route_emu"):
+    for name in ("gdn_step_emu", "gdn_conv_emu", "route_emu", "plan_emu"):
         exe = tmp_path / (name + "_tsan")
         b = _tsan_build(ROOT / f"tests/emu/{name}.cpp", exe, ("-DB200_EMU",))
         assert b.returncode == 0, b.stderr[-3000:]
